@@ -1,0 +1,158 @@
+// C ABI of the sm_100a kernel library (libftk_sm100.so).
+//
+// Every launcher takes raw device pointers plus a CUDA stream handle and returns
+// 0 on success, a negative value for rejected arguments, or a positive CUDA /
+// driver error code.  Launchers never allocate device memory and never
+// synchronise; the caller owns all buffers.  Asynchronous protocol failures
+// (a bounded wait that ran out) are reported through the per-device status word
+// returned by ftk_status_word() / read by ftk_read_status().
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// GEMM epilogues
+enum {
+  FTK_EPI_NONE = 0,
+  FTK_EPI_GELU_TANH = 1,
+  FTK_EPI_GELU_ERF = 2,
+  FTK_EPI_RELU = 3,
+  // the `resid` operand is the saved pre-activation u; result = acc * f'(u)
+  FTK_EPI_MUL_DGELU_TANH = 4,
+  FTK_EPI_MUL_DGELU_ERF = 5,
+  FTK_EPI_MUL_DRELU = 6,
+};
+
+typedef struct FtkGemmDesc {
+  int M, N, K;
+  int L0, L1;            // batch extents (>=1); batch index l = l0 + L0*l1
+  int a_mn, b_mn;        // 0: operand stored [rows, K]; 1: stored [K, rows]
+  const void* A;         // bf16
+  long long lda, a_s0, a_s1;
+  const void* B;         // bf16
+  long long ldb, b_s0, b_s1;
+  void* D;               // bf16 or fp32, [M, N] row-major per batch
+  long long ldd, d_s0, d_s1;
+  const void* bias;      // bf16 [N] or NULL
+  const void* resid;     // bf16, same shape as D, or NULL
+  long long ldr, r_s0, r_s1;
+  void* aux;             // bf16 pre-activation copy (layout of D) or NULL
+  float alpha;
+  int epi;
+  int out_fp32;
+  int accumulate;        // D += result
+  int force_bn;          // 0 = heuristic, else 128 or 256
+  int max_ctas;          // 0 = all SMs
+} FtkGemmDesc;
+
+int* ftk_status_word(void);               // device pointer (allocated on first use, per device)
+int ftk_read_status(int reset);           // synchronises the device; returns the status word
+int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream);
+
+// ---- attention (causal / full), packed QKV layout ---------------------------------------
+// q/k/v: bf16 element (b, s, h, e) at base[b*bs + s*ss + h*hs + e]; head_dim in {64, 128}.
+// o: same addressing with its own strides.  lse: fp32 [B, H, S], log2 domain.
+typedef struct FtkAttnDesc {
+  int B, H, S, hd;
+  int causal;
+  float scale;           // softmax scale (1/sqrt(hd) by default)
+  const void *q, *k, *v;
+  long long q_bs, q_ss, q_hs;
+  long long k_bs, k_ss, k_hs;
+  long long v_bs, v_ss, v_hs;
+  void* o;
+  long long o_bs, o_ss, o_hs;
+  float* lse;
+  // backward only
+  const void* d_o;       // bf16, addressing of o
+  float* delta;          // fp32 [B, H, S] scratch: rowsum(dO * O)
+  void *dq, *dk, *dv;    // bf16, addressing of q / k / v respectively
+} FtkAttnDesc;
+int ftk_attn_fwd(const FtkAttnDesc* a, void* stream);
+int ftk_attn_bwd(const FtkAttnDesc* a, void* stream);
+
+// ---- row kernels ------------------------------------------------------------------------
+// LayerNorm over the last dim (population variance, eps inside the sqrt), bf16 in/out,
+// fp32 statistics.  If resid_in != NULL the kernel first forms x = x + resid_in, writes it
+// to sum_out (bf16) and normalises that (fused residual-add + LN).
+int ftk_layernorm_fwd(const void* x, const void* resid_in, void* sum_out, const void* gamma,
+                      const void* beta, void* y, float* mean, float* rstd, int rows, int cols,
+                      float eps, void* stream);
+// dx (bf16, optionally += dx_accum_in), and per-block partial dgamma/dbeta reduced in a
+// second fixed-order pass (dgamma/dbeta fp32 [cols]); partial must hold 2*nblk*cols floats,
+// nblk = ftk_layernorm_bwd_blocks(rows).
+int ftk_layernorm_bwd_blocks(int rows);
+int ftk_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
+                      const float* rstd, const void* dx_add, void* dx, float* dgamma, float* dbeta,
+                      float* partial, int rows, int cols, int accumulate_param_grads, void* stream);
+int ftk_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, int rows, int cols,
+                    float eps, void* stream);
+int ftk_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd, void* dx,
+                    float* dgamma, float* partial, int rows, int cols, int accumulate_param_grads,
+                    void* stream);
+// Row softmax over the last dim with the guards of the reference shader (non-finite max ->
+// zeros, zero sum -> zeros).  fp32 or bf16 by `is_bf16`.
+int ftk_softmax_rows(const void* x, void* y, int rows, int cols, int is_bf16, void* stream);
+// Causal row softmax over [L, S, S] score matrices (unfused attention oracle path), bf16.
+int ftk_softmax_causal_bf16(const void* x, void* y, int L, int S, float scale, void* stream);
+int ftk_softmax_bwd_bf16(const void* y, const void* dy, void* dx, long long rows, int cols,
+                         float scale, void* stream);
+
+// Fused softmax-cross-entropy over bf16 logits [rows, ld] (first `vocab` columns valid).
+// losses: fp32 [rows]; dlogits (may alias logits) = (softmax - onehot) * grad_scale, bf16,
+// padded columns written as zero.  targets: int64.
+int ftk_cross_entropy_fwd_bwd(const void* logits, const long long* targets, float* losses,
+                              void* dlogits, int rows, int vocab, int ld, float grad_scale,
+                              void* stream);
+// Fixed-tree mean of `n` fp32 values into out[0] (single block, pairwise tree).
+int ftk_reduce_mean_f32(const float* x, float* out, long long n, float scale, void* stream);
+// Sum of squares with a fixed two-level tree: out[0] += / = sum(x^2).  `partial` holds
+// FTK_SUMSQ_PARTIALS floats (may be NULL for small n).
+#define FTK_SUMSQ_PARTIALS 1024
+int ftk_sumsq_f32(const float* x, float* out, float* partial, long long n, int accumulate,
+                  void* stream);
+
+// ---- elementwise ------------------------------------------------------------------------
+int ftk_gelu_fwd(const void* x, void* y, long long n, int tanh_form, void* stream);
+int ftk_gelu_bwd(const void* x, const void* dy, void* dx, long long n, int tanh_form, void* stream);
+int ftk_add_bf16(const void* a, const void* b, void* out, long long n, void* stream);
+int ftk_cast_f32_to_bf16(const float* x, void* y, long long n, void* stream);
+int ftk_cast_bf16_to_f32(const void* x, float* y, long long n, int accumulate, void* stream);
+// counter-based (Philox-4x32-10) dropout; mask is recomputed in backward from (seed, offset).
+int ftk_dropout_bf16(const void* x, void* y, long long n, float p, unsigned long long seed,
+                     unsigned long long offset, void* stream);
+// column sums of a bf16 [rows, cols] matrix into fp32 [cols] (bias gradients), fixed order.
+int ftk_colsum_bf16(const void* x, float* out, float* partial, int rows, int cols, long long ld,
+                    int accumulate, void* stream);
+int ftk_colsum_blocks(int rows);
+
+// ---- embedding --------------------------------------------------------------------------
+// out[r, :] = wte[ids[r], :] + wpe[r % S, :]  (wpe may be NULL)
+int ftk_embedding_fwd(const long long* ids, const void* wte, const void* wpe, void* out, int rows,
+                      int S, int d, void* stream);
+// Deterministic scatter-add: `sorted_ids`/`order` come from a stable sort of the ids, so
+// each table row is summed by one CTA in ascending source-row order.
+// dwte fp32 [vocab, d] (+=), dwpe fp32 [S, d] (+=); either may be NULL.
+int ftk_embedding_bwd(const long long* sorted_ids, const int* order, const void* dout, float* dwte,
+                      float* dwpe, int rows, int S, int d, void* stream);
+
+// ---- optimizer --------------------------------------------------------------------------
+// Fused AdamW on fp32 master weights with bf16 shadow write-back.  grad fp32.
+// Reference math: ft-optim/src/lib.rs:1040-1054.
+int ftk_adamw(float* master, void* shadow_bf16, const float* grad, float* m, float* v, long long n,
+              float lr, float beta1, float beta2, float eps, float weight_decay, float bc1,
+              float bc2, float grad_scale, void* stream);
+
+// ---- presenter / misc -------------------------------------------------------------------
+// RGBA8 rows (row_bytes stride) -> normalised float4 or half4 headless buffer.
+int ftk_present_rgba8(const unsigned char* src, void* dst, int width, int height,
+                      long long row_bytes, int dst_half, void* stream);
+// 1-D convolution-over-time gather X[t_in, cin] -> Y[t_out, cin*k] with zero padding.
+int ftk_im2col_1d(const float* x, float* y, int t_in, int cin, int k, int stride, int pad,
+                  int t_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,521 @@
+// Row-wise kernels: LayerNorm / RMSNorm forward+backward, softmax, fused
+// softmax-cross-entropy, fixed-tree reductions.  All memory bound: one pass over
+// the data where it fits on chip, 16-byte vector accesses, fp32 statistics.
+//
+// Semantics follow the reference CPU kernels: two-pass LayerNorm with population
+// variance (ft-kernel-cpu/src/lib.rs:5824), RMSNorm (:6418, backward :6503),
+// cross-entropy = lse - logit[target] with gradient softmax - onehot (:6649,:6679),
+// guarded row softmax of the Metal shader (ft-kernel-metal/src/fused.rs:321).
+// Parameter-gradient reductions run in a fixed order (row blocks, then a serial
+// pass over the block partials), so two runs give identical bits.
+#include "ft_sm100.cuh"
+#include "ftk_api.h"
+
+namespace ftk {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]);
+  u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+  return u;
+}
+
+constexpr int ROW_WARPS = 8;     // rows per CTA
+constexpr int ROW_CACHE = 8;     // 8 x (32 lanes x 8 elems) = 2048 columns kept in registers
+
+// ----------------------------------------------------------------------------- LayerNorm fwd
+template <bool RMS>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ resid,
+                __nv_bfloat16* __restrict__ sum_out, const __nv_bfloat16* __restrict__ gamma,
+                const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols,
+                float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * ROW_WARPS + warp;
+  if (row >= rows) return;
+  const int nvec = cols >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+  const uint4* rr = resid ? reinterpret_cast<const uint4*>(resid + (size_t)row * cols) : nullptr;
+  uint4* so = sum_out ? reinterpret_cast<uint4*>(sum_out + (size_t)row * cols) : nullptr;
+  uint4 cache[ROW_CACHE];
+  float s = 0.f;
+  for (int c = 0, v = lane; v < nvec; ++c, v += 32) {
+    uint4 u = xr[v];
+    float f[8];
+    unpack8(u, f);
+    if (rr) {
+      float g[8];
+      unpack8(rr[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += g[i];
+      u = pack8(f);
+      unpack8(u, f);  // statistics are taken on the rounded sum that downstream kernels will read
+      if (so) so[v] = u;
+    }
+    if (c < ROW_CACHE) cache[c] = u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += RMS ? f[i] * f[i] : f[i];
+  }
+  s = warp_sum(s);
+  float mean = 0.f, rstd;
+  const uint4* src = rr ? reinterpret_cast<const uint4*>(so) : xr;
+  if (RMS) {
+    rstd = rsqrtf(s / cols + eps);
+  } else {
+    mean = s / cols;
+    float q = 0.f;
+    for (int c = 0, v = lane; v < nvec; ++c, v += 32) {
+      uint4 u = (c < ROW_CACHE) ? cache[c] : src[v];
+      float f[8];
+      unpack8(u, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float d = f[i] - mean;
+        q += d * d;
+      }
+    }
+    q = warp_sum(q);
+    rstd = rsqrtf(q / cols + eps);
+  }
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+  const uint4* gv = reinterpret_cast<const uint4*>(gamma);
+  const uint4* bv = beta ? reinterpret_cast<const uint4*>(beta) : nullptr;
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * cols);
+  for (int c = 0, v = lane; v < nvec; ++c, v += 32) {
+    uint4 u = (c < ROW_CACHE) ? cache[c] : src[v];
+    float f[8], g[8], b[8];
+    unpack8(u, f);
+    unpack8(__ldg(gv + v), g);
+    if (bv) unpack8(__ldg(bv + v), b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float h = (f[i] - mean) * rstd * g[i];
+      f[i] = bv ? h + b[i] : h;
+    }
+    yr[v] = pack8(f);
+  }
+}
+
+// ----------------------------------------------------------------------------- LayerNorm bwd dx
+template <bool RMS>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                   const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dx_add,
+                   __nv_bfloat16* __restrict__ dx, int rows, int cols) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * ROW_WARPS + warp;
+  if (row >= rows) return;
+  const int nvec = cols >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+  const uint4* dr = reinterpret_cast<const uint4*>(dy + (size_t)row * cols);
+  const uint4* gv = reinterpret_cast<const uint4*>(gamma);
+  const float mean = RMS ? 0.f : mean_in[row];
+  const float rstd = rstd_in[row];
+  // sums of g*dy and g*dy*xhat
+  float s1 = 0.f, s2 = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    float fx[8], fd[8], g[8];
+    unpack8(xr[v], fx);
+    unpack8(dr[v], fd);
+    unpack8(__ldg(gv + v), g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float gd = g[i] * fd[i];
+      float xh = (fx[i] - mean) * rstd;
+      s1 += gd;
+      s2 += gd * xh;
+    }
+  }
+  s1 = warp_sum(s1) / cols;
+  s2 = warp_sum(s2) / cols;
+  if (RMS) s1 = 0.f;
+  const uint4* av = dx_add ? reinterpret_cast<const uint4*>(dx_add + (size_t)row * cols) : nullptr;
+  uint4* ov = reinterpret_cast<uint4*>(dx + (size_t)row * cols);
+  for (int v = lane; v < nvec; v += 32) {
+    float fx[8], fd[8], g[8], a[8];
+    unpack8(xr[v], fx);
+    unpack8(dr[v], fd);
+    unpack8(__ldg(gv + v), g);
+    if (av) unpack8(av[v], a);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float xh = (fx[i] - mean) * rstd;
+      float r = rstd * (g[i] * fd[i] - s1 - xh * s2);
+      fx[i] = av ? r + a[i] : r;
+    }
+    ov[v] = pack8(fx);
+  }
+}
+
+// Column partials: partial[blk][c] = sum over this block's rows of dy*xhat, and of dy.
+// MODE 0: LayerNorm (two outputs), 1: RMSNorm (dgamma only), 2: plain column sum of dy.
+constexpr int COL_ROWS_PER_BLK = 64;
+template <int MODE>
+__global__ void __launch_bounds__(128)
+col_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                   float* __restrict__ partial, int rows, int cols, long long ld, int nblk) {
+  // thread owns 2 adjacent columns
+  const int c = (blockIdx.x * 128 + threadIdx.x) * 2;
+  const int blk = blockIdx.y;
+  if (c >= cols) return;
+  const int r0 = blk * COL_ROWS_PER_BLK;
+  const int r1 = min(rows, r0 + COL_ROWS_PER_BLK);
+  float g0 = 0.f, g1 = 0.f, b0 = 0.f, b1 = 0.f;
+  for (int r = r0; r < r1; ++r) {
+    float2 d = unpack_bf16(*reinterpret_cast<const uint32_t*>(dy + (size_t)r * ld + c));
+    if (MODE == 2) {
+      b0 += d.x; b1 += d.y;
+    } else {
+      float2 xv = unpack_bf16(*reinterpret_cast<const uint32_t*>(x + (size_t)r * ld + c));
+      float mu = MODE == 0 ? mean_in[r] : 0.f;
+      float rs = rstd_in[r];
+      g0 += d.x * (xv.x - mu) * rs;
+      g1 += d.y * (xv.y - mu) * rs;
+      b0 += d.x; b1 += d.y;
+    }
+  }
+  if (MODE == 2) {
+    partial[(size_t)blk * cols + c] = b0;
+    if (c + 1 < cols) partial[(size_t)blk * cols + c + 1] = b1;
+  } else {
+    partial[(size_t)blk * cols + c] = g0;
+    if (c + 1 < cols) partial[(size_t)blk * cols + c + 1] = g1;
+    if (MODE == 0) {
+      float* pb = partial + (size_t)nblk * cols;
+      pb[(size_t)blk * cols + c] = b0;
+      if (c + 1 < cols) pb[(size_t)blk * cols + c + 1] = b1;
+    }
+  }
+}
+// Serial (fixed-order) sum over block partials.
+__global__ void col_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols,
+                                 int nblk, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int b = 0; b < nblk; ++b) s += partial[(size_t)b * cols + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ----------------------------------------------------------------------------- softmax
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+template <typename T>
+__device__ __forceinline__ void stf(T* p, float v);
+template <>
+__device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16(v);
+}
+
+__device__ __forceinline__ float block_reduce(float v, float* red, bool is_max) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  v = is_max ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : (is_max ? -INFINITY : 0.f);
+    t = is_max ? warp_max(t) : warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// One CTA per row; `limit` = number of valid columns in this row (causal rows pass row+1).
+template <typename T>
+__global__ void __launch_bounds__(256)
+softmax_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int cols, int S_causal,
+                    float scale) {
+  __shared__ float red[33];
+  const size_t row = blockIdx.x;
+  const int limit = S_causal > 0 ? (int)(row % S_causal) + 1 : cols;
+  const T* xr = x + row * cols;
+  T* yr = y + row * cols;
+  float m = -INFINITY;
+  for (int c = threadIdx.x; c < limit; c += blockDim.x) m = fmaxf(m, ldf(xr + c) * scale);
+  m = block_reduce(m, red, true);
+  const bool bad = !(fabsf(m) <= 3.0e38f);  // NaN or +-inf
+  float s = 0.f;
+  if (!bad)
+    for (int c = threadIdx.x; c < limit; c += blockDim.x) s += __expf(ldf(xr + c) * scale - m);
+  s = block_reduce(s, red, false);
+  const float inv = (!bad && s > 0.f) ? 1.f / s : 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float v = (c < limit && inv > 0.f) ? __expf(ldf(xr + c) * scale - m) * inv : 0.f;
+    stf(yr + c, v);
+  }
+}
+// dx = scale * y * (dy - sum(dy*y))
+__global__ void __launch_bounds__(256)
+softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ dy,
+                   __nv_bfloat16* __restrict__ dx, int cols, float scale) {
+  __shared__ float red[33];
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16* yr = y + row * cols;
+  const __nv_bfloat16* dr = dy + row * cols;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x)
+    s += __bfloat162float(yr[c]) * __bfloat162float(dr[c]);
+  s = block_reduce(s, red, false);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float p = __bfloat162float(yr[c]);
+    dx[row * cols + c] = __float2bfloat16(scale * p * (__bfloat162float(dr[c]) - s));
+  }
+}
+
+// ----------------------------------------------------------------------------- cross entropy
+// One CTA per row.  The bf16 row is staged in shared memory when it fits, so the
+// logits are read from HBM once and the gradient is written once (in place allowed).
+constexpr int CE_THREADS = 512;
+__global__ void __launch_bounds__(CE_THREADS)
+cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                     float* __restrict__ losses, __nv_bfloat16* __restrict__ dlogits, int vocab,
+                     int ld, float grad_scale, int use_smem) {
+  extern __shared__ uint4 ce_smem[];
+  __shared__ float red[33];
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16* xr = logits + row * ld;
+  const uint4* xv = reinterpret_cast<const uint4*>(xr);
+  const int nvec = ld >> 3;
+  const long long tgt = targets[row];
+  float m = -INFINITY;
+  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+    uint4 u = xv[v];
+    if (use_smem) ce_smem[v] = u;
+    float f[8];
+    unpack8(u, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (v * 8 + i < vocab) m = fmaxf(m, f[i]);
+  }
+  m = block_reduce(m, red, true);
+  const uint4* src = use_smem ? ce_smem : xv;
+  float s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+    float f[8];
+    unpack8(src[v], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (v * 8 + i < vocab) s += __expf(f[i] - m);
+  }
+  s = block_reduce(s, red, false);
+  const float lse = m + __logf(s);
+  if (threadIdx.x == 0) {
+    float xt = (tgt >= 0 && tgt < vocab) ? __bfloat162float(xr[tgt]) : 0.f;
+    losses[row] = (tgt >= 0 && tgt < vocab) ? lse - xt : 0.f;
+  }
+  if (dlogits) {
+    __syncthreads();  // the target logit was read before any in-place write
+    const float inv = 1.f / s;
+    const bool ignore = !(tgt >= 0 && tgt < vocab);
+    uint4* ov = reinterpret_cast<uint4*>(dlogits + row * ld);
+    for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+      float f[8];
+      unpack8(src[v], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = v * 8 + i;
+        float g = 0.f;
+        if (c < vocab && !ignore) g = (__expf(f[i] - m) * inv - (c == tgt ? 1.f : 0.f)) * grad_scale;
+        f[i] = g;
+      }
+      ov[v] = pack8(f);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- reductions
+// Single CTA, fixed tree: each thread sums a strided slice serially, then a fixed
+// shuffle/shared tree combines the 1024 partials.  Result is independent of anything
+// but n, so it replays bit-identically.
+template <bool SQUARE>
+__global__ void __launch_bounds__(1024)
+reduce_one_block_kernel(const float* __restrict__ x, float* __restrict__ out, long long n,
+                        float scale, int accumulate) {
+  __shared__ float red[33];
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < n; i += 1024) {
+    float v = x[i];
+    s += SQUARE ? v * v : v;
+  }
+  s = block_reduce(s, red, false);
+  if (threadIdx.x == 0) out[0] = accumulate ? out[0] + s * scale : s * scale;
+}
+// Two-level version for large buffers: level 1 writes one partial per CTA.
+template <bool SQUARE>
+__global__ void __launch_bounds__(256)
+reduce_level1_kernel(const float* __restrict__ x, float* __restrict__ partial, long long n) {
+  __shared__ float red[33];
+  const long long per = (n + gridDim.x - 1) / gridDim.x;
+  const long long b = per * blockIdx.x, e = (b + per < n) ? b + per : n;
+  float s = 0.f;
+  for (long long i = b + threadIdx.x; i < e; i += 256) {
+    float v = x[i];
+    s += SQUARE ? v * v : v;
+  }
+  s = block_reduce(s, red, false);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
+}  // namespace ftk
+
+using namespace ftk;
+#define STREAM(s) reinterpret_cast<cudaStream_t>(s)
+#define BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
+#define BFW(p) reinterpret_cast<__nv_bfloat16*>(p)
+
+extern "C" int ftk_layernorm_fwd(const void* x, const void* resid_in, void* sum_out,
+                                 const void* gamma, const void* beta, void* y, float* mean,
+                                 float* rstd, int rows, int cols, float eps, void* stream) {
+  if (cols % 8 || rows <= 0) return -2;
+  if (resid_in && !sum_out) return -3;
+  norm_fwd_kernel<false><<<(rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, STREAM(stream)>>>(
+      BF(x), BF(resid_in), BFW(sum_out), BF(gamma), BF(beta), BFW(y), mean, rstd, rows, cols, eps);
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, int rows,
+                               int cols, float eps, void* stream) {
+  if (cols % 8 || rows <= 0) return -2;
+  norm_fwd_kernel<true><<<(rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, STREAM(stream)>>>(
+      BF(x), nullptr, nullptr, BF(gamma), nullptr, BFW(y), nullptr, rstd, rows, cols, eps);
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_layernorm_bwd_blocks(int rows) {
+  return (rows + COL_ROWS_PER_BLK - 1) / COL_ROWS_PER_BLK;
+}
+extern "C" int ftk_colsum_blocks(int rows) { return ftk_layernorm_bwd_blocks(rows); }
+
+extern "C" int ftk_layernorm_bwd(const void* dy, const void* x, const void* gamma,
+                                 const float* mean, const float* rstd, const void* dx_add, void* dx,
+                                 float* dgamma, float* dbeta, float* partial, int rows, int cols,
+                                 int accumulate, void* stream) {
+  if (cols % 8 || rows <= 0) return -2;
+  cudaStream_t s = STREAM(stream);
+  norm_bwd_dx_kernel<false><<<(rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, s>>>(
+      BF(dy), BF(x), BF(gamma), mean, rstd, BF(dx_add), BFW(dx), rows, cols);
+  if (dgamma) {
+    const int nblk = ftk_layernorm_bwd_blocks(rows);
+    dim3 g((cols / 2 + 127) / 128, nblk);
+    col_partial_kernel<0><<<g, 128, 0, s>>>(BF(dy), BF(x), mean, rstd, partial, rows, cols, cols, nblk);
+    col_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, dgamma, cols, nblk, accumulate);
+    col_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial + (size_t)nblk * cols, dbeta, cols,
+                                                         nblk, accumulate);
+  }
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd,
+                               void* dx, float* dgamma, float* partial, int rows, int cols,
+                               int accumulate, void* stream) {
+  if (cols % 8 || rows <= 0) return -2;
+  cudaStream_t s = STREAM(stream);
+  norm_bwd_dx_kernel<true><<<(rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, s>>>(
+      BF(dy), BF(x), BF(gamma), nullptr, rstd, nullptr, BFW(dx), rows, cols);
+  if (dgamma) {
+    const int nblk = ftk_layernorm_bwd_blocks(rows);
+    dim3 g((cols / 2 + 127) / 128, nblk);
+    col_partial_kernel<1><<<g, 128, 0, s>>>(BF(dy), BF(x), nullptr, rstd, partial, rows, cols, cols, nblk);
+    col_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, dgamma, cols, nblk, accumulate);
+  }
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_colsum_bf16(const void* x, float* out, float* partial, int rows, int cols,
+                               long long ld, int accumulate, void* stream) {
+  if (cols % 2 || ld % 2 || rows <= 0) return -2;
+  cudaStream_t s = STREAM(stream);
+  const int nblk = ftk_colsum_blocks(rows);
+  dim3 g((cols / 2 + 127) / 128, nblk);
+  col_partial_kernel<2><<<g, 128, 0, s>>>(BF(x), nullptr, nullptr, nullptr, partial, rows, cols, ld, nblk);
+  col_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, out, cols, nblk, accumulate);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ftk_softmax_rows(const void* x, void* y, int rows, int cols, int is_bf16,
+                                void* stream) {
+  if (rows <= 0 || cols <= 0) return -2;
+  if (is_bf16)
+    softmax_rows_kernel<__nv_bfloat16><<<rows, 256, 0, STREAM(stream)>>>(BF(x), BFW(y), cols, 0, 1.f);
+  else
+    softmax_rows_kernel<float><<<rows, 256, 0, STREAM(stream)>>>(
+        reinterpret_cast<const float*>(x), reinterpret_cast<float*>(y), cols, 0, 1.f);
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_softmax_causal_bf16(const void* x, void* y, int L, int S, float scale,
+                                       void* stream) {
+  if (L <= 0 || S <= 0) return -2;
+  softmax_rows_kernel<__nv_bfloat16><<<(unsigned)((size_t)L * S), 256, 0, STREAM(stream)>>>(
+      BF(x), BFW(y), S, S, scale);
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_softmax_bwd_bf16(const void* y, const void* dy, void* dx, long long rows,
+                                    int cols, float scale, void* stream) {
+  if (rows <= 0 || cols <= 0) return -2;
+  softmax_bwd_kernel<<<(unsigned)rows, 256, 0, STREAM(stream)>>>(BF(y), BF(dy), BFW(dx), cols, scale);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ftk_cross_entropy_fwd_bwd(const void* logits, const long long* targets,
+                                         float* losses, void* dlogits, int rows, int vocab, int ld,
+                                         float grad_scale, void* stream) {
+  if (ld % 8 || vocab > ld || rows <= 0) return -2;
+  const size_t bytes = (size_t)ld * 2;
+  const int use_smem = bytes <= 200 * 1024;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(cross_entropy_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  cross_entropy_kernel<<<rows, CE_THREADS, use_smem ? bytes : 0, STREAM(stream)>>>(
+      BF(logits), targets, losses, BFW(dlogits), vocab, ld, grad_scale, use_smem);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ftk_reduce_mean_f32(const float* x, float* out, long long n, float scale,
+                                   void* stream) {
+  if (n <= 0) return -2;
+  reduce_one_block_kernel<false><<<1, 1024, 0, STREAM(stream)>>>(x, out, n, scale, 0);
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_sumsq_f32(const float* x, float* out, float* partial, long long n,
+                             int accumulate, void* stream) {
+  if (n <= 0) return -2;
+  if (n < (1 << 16) || !partial) {
+    reduce_one_block_kernel<true><<<1, 1024, 0, STREAM(stream)>>>(x, out, n, 1.f, accumulate);
+  } else {
+    // level 1: FTK_SUMSQ_PARTIALS fixed slices; level 2: one block over the partials
+    reduce_level1_kernel<true><<<FTK_SUMSQ_PARTIALS, 256, 0, STREAM(stream)>>>(x, partial, n);
+    reduce_one_block_kernel<false><<<1, 1024, 0, STREAM(stream)>>>(partial, out, FTK_SUMSQ_PARTIALS,
+                                                                    1.f, accumulate);
+  }
+  return (int)cudaGetLastError();
+}

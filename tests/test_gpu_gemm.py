@@ -1,0 +1,121 @@
+"""tcgen05 GEMM numerics against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from frankentorch_b200.ops import kernels
+    return kernels
+
+
+def _rand(shape, dev, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(dev)
+
+
+def _check(out, ref, tol, what):
+    err = (out.float() - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err / denom < tol, f"{what}: max abs err {err:.4g} vs ref max {denom:.4g}"
+
+
+@pytest.mark.parametrize("M,N,K,bn", [
+    (128, 128, 64, 128),      # one tile, one k-block
+    (128, 256, 64, 256),
+    (128, 128, 256, 128),     # k loop
+    (256, 512, 512, 256),     # multiple tiles per CTA ring
+    (1024, 768, 768, 0),
+    (200, 136, 72, 0),        # ragged M, N, K (TMA zero fill + guarded stores)
+    (4096, 2304, 768, 0),     # more tiles than SMs: persistent loop + accumulator ping-pong
+])
+def test_gemm_kmajor(cuda_device, M, N, K, bn):
+    k = _ops()
+    a = _rand((M, K), cuda_device, seed=1)
+    b = _rand((N, K), cuda_device, seed=2)
+    out = k.gemm(a, b, force_bn=bn)
+    k.check_status()
+    ref = a.float() @ b.float().t()
+    _check(out, ref, 2e-2, f"gemm {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (384, 512, 320), (520, 264, 200)])
+def test_gemm_mn_major(cuda_device, a_mn, b_mn, M, N, K):
+    k = _ops()
+    a = _rand((K, M) if a_mn else (M, K), cuda_device, seed=3)
+    b = _rand((K, N) if b_mn else (N, K), cuda_device, seed=4)
+    out = k.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    k.check_status()
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float().t() if b_mn else b.float()
+    _check(out, af @ bf.t(), 2e-2, f"gemm a_mn={a_mn} b_mn={b_mn} {M}x{N}x{K}")
+
+
+def test_gemm_epilogues(cuda_device):
+    k = _ops()
+    M, N, K = 512, 768, 256
+    a = _rand((M, K), cuda_device, 0.5, 5)
+    w = _rand((N, K), cuda_device, 0.1, 6)
+    bias = _rand((N,), cuda_device, 1.0, 7)
+    resid = _rand((M, N), cuda_device, 1.0, 8)
+    pre = a.float() @ w.float().t() + bias.float()
+    out = k.gemm(a, w, bias=bias)
+    _check(out, pre, 2e-2, "bias")
+    aux = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device)
+    out = k.gemm(a, w, bias=bias, epi=k.EPI_GELU_TANH, aux=aux)
+    _check(out, torch.nn.functional.gelu(pre, approximate="tanh"), 2e-2, "gelu_tanh")
+    _check(aux, pre, 2e-2, "aux pre-activation")
+    out = k.gemm(a, w, bias=bias, epi=k.EPI_GELU_ERF)
+    _check(out, torch.nn.functional.gelu(pre), 2e-2, "gelu_erf")
+    out = k.gemm(a, w, bias=bias, resid=resid)
+    _check(out, pre + resid.float(), 2e-2, "bias+residual")
+    # dgelu epilogue: acc * gelu'(u)
+    u = _rand((M, N), cuda_device, 1.0, 9)
+    uf = u.float().requires_grad_(True)
+    torch.nn.functional.gelu(uf, approximate="tanh").sum().backward()
+    out = k.gemm(a, w, resid=u, epi=k.EPI_MUL_DGELU_TANH)
+    _check(out, (a.float() @ w.float().t()) * uf.grad, 2e-2, "mul_dgelu_tanh")
+    # fp32 output with accumulation (weight gradients)
+    acc = torch.ones((M, N), dtype=torch.float32, device=cuda_device)
+    k.gemm(a, w, out=acc, accumulate=True)
+    _check(acc, a.float() @ w.float().t() + 1.0, 1e-2, "fp32 accumulate")
+    k.check_status()
+
+
+def test_linear_grads(cuda_device):
+    k = _ops()
+    M, N, K = 1024, 3072, 768
+    x = _rand((M, K), cuda_device, 1.0, 10)
+    w = _rand((N, K), cuda_device, 0.05, 11)
+    dy = _rand((M, N), cuda_device, 1.0, 12)
+    dx = k.linear_dgrad(dy, w)
+    dw = k.linear_wgrad(dy, x)
+    k.check_status()
+    _check(dx, dy.float() @ w.float(), 2e-2, "dgrad")
+    _check(dw, dy.float().t() @ x.float(), 2e-2, "wgrad")
+
+
+def test_gemm_deterministic(cuda_device):
+    k = _ops()
+    a = _rand((2048, 1024), cuda_device, seed=13)
+    b = _rand((1536, 1024), cuda_device, seed=14)
+    o1 = k.gemm(a, b)
+    o2 = k.gemm(a, b, max_ctas=37)   # different grid, same bits: K is never split
+    k.check_status()
+    assert torch.equal(o1, o2)
+
+
+def test_gemm_batched(cuda_device):
+    k = _ops()
+    L0, L1, M, N, K = 3, 2, 256, 128, 64
+    a = _rand((L1, L0, M, K), cuda_device, seed=15)
+    b = _rand((L1, L0, N, K), cuda_device, seed=16)
+    out = torch.empty((L1, L0, M, N), dtype=torch.bfloat16, device=cuda_device)
+    k.gemm_batched(a, b, out, M=M, N=N, K=K, L0=L0, L1=L1,
+                   a_strides=(K, M * K, L0 * M * K), b_strides=(K, N * K, L0 * N * K),
+                   d_strides=(N, M * N, L0 * M * N), alpha=0.5)
+    k.check_status()
+    ref = 0.5 * torch.einsum("xymk,xynk->xymn", a.float(), b.float())
+    _check(out, ref, 2e-2, "batched")
