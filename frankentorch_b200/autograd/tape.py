@@ -1,0 +1,451 @@
+"""Deterministic Autograd Contract (DAC): the tensor tape.
+
+The tape is append-only; node ids are creation-order indices.  ``backward`` asks the
+native scheduler (``libftcore``: reachability DFS, dependency counts, max-heap ready
+queue that pops the highest node id first) for the execution plan, then runs each
+node's VJP rule in exactly that order on one stream.  Contributions are accumulated
+into the input slots in a fixed per-rule order (first contribution is stored
+verbatim, later ones are added), so gradients and telemetry replay bit-identically.
+
+Reference behaviour: ft-autograd/src/lib.rs :4268 (TensorTape), :11724-15706
+(backward_with_options), :4520-4558 (hooks), :4389 (truncate_graph_to),
+:21135-21173 (persistent leaf gradients), :1285-1333 (errors), and the scheduler
+golden ft_autograd__tests__tensor_scheduler_telemetry_golden.snap.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..runtime import native
+from ..runtime.ledger import ExecutionMode
+
+
+# ------------------------------------------------------------------------------ errors
+class AutogradError(RuntimeError):
+    pass
+
+
+class UnknownTensorNode(AutogradError):
+    pass
+
+
+class TensorRootDoesNotRequireGrad(AutogradError):
+    pass
+
+
+class TensorGraphConsumed(AutogradError):
+    pass
+
+
+class ReentrantDepthExceeded(AutogradError):
+    def __init__(self, current: int, maximum: int):
+        super().__init__(f"reentrant backward depth {current} exceeds maximum {maximum}")
+        self.current, self.max = current, maximum
+
+
+class TensorDependencyUnderflow(AutogradError):
+    pass
+
+
+class TensorGradientShapeMismatch(AutogradError):
+    pass
+
+
+class TensorRequiresGradNonLeaf(AutogradError):
+    pass
+
+
+class TensorRequiresGradNonFloating(AutogradError):
+    pass
+
+
+class BorrowedInputVersionMismatch(AutogradError):
+    def __init__(self, node: int, recorded: int, observed: int):
+        super().__init__(f"node {node}: borrowed input mutated in place (version {recorded} -> {observed})")
+        self.node, self.recorded, self.observed = node, recorded, observed
+
+
+class AnomalyDetected(AutogradError):
+    pass
+
+
+# ------------------------------------------------------------------------------ options / reports
+class ReentrantPolicy:
+    StrictFail = "strict_fail"
+    HardenedBoundedFallback = "hardened_bounded_fallback"
+
+
+@dataclass
+class BackwardOptions:
+    retain_graph: bool = False
+    create_graph: bool = False
+    max_reentrant_depth: int = 0
+    current_reentrant_depth: int = 0
+    policy: str = ReentrantPolicy.StrictFail
+    detect_anomaly: bool = False
+
+    @staticmethod
+    def strict_default() -> "BackwardOptions":
+        return BackwardOptions(policy=ReentrantPolicy.StrictFail, max_reentrant_depth=0)
+
+    @staticmethod
+    def hardened_default() -> "BackwardOptions":
+        return BackwardOptions(policy=ReentrantPolicy.HardenedBoundedFallback, max_reentrant_depth=2)
+
+    @staticmethod
+    def for_mode(mode: ExecutionMode) -> "BackwardOptions":
+        return BackwardOptions.hardened_default() if mode == ExecutionMode.Hardened else BackwardOptions.strict_default()
+
+
+@dataclass
+class TensorBackwardStep:
+    node: int
+    incoming_grad_len: int
+    rule: str
+
+
+@dataclass
+class TensorSchedulerTelemetry:
+    execution_order: List[int]
+    queue_pushes: int
+    queue_pops: int
+    max_queue_len: int
+    dependency_snapshot: List[int]
+    reentrant_depth: int = 0
+    reentrant_guard_triggered: bool = False
+    hardened_fallback_used: bool = False
+
+    def render(self, mode: str = "strict") -> str:
+        """Stable text form (the layout of the reference's golden snapshot)."""
+        return "\n".join([
+            "dependency_snapshot=" + ",".join(map(str, self.dependency_snapshot)),
+            "execution_order=" + ",".join(map(str, self.execution_order)),
+            f"hardened_fallback_used={str(self.hardened_fallback_used).lower()}",
+            f"max_queue_len={self.max_queue_len}",
+            f"mode={mode}",
+            f"queue_pops={self.queue_pops}",
+            f"queue_pushes={self.queue_pushes}",
+            f"reentrant_depth={self.reentrant_depth}",
+            f"reentrant_guard_triggered={str(self.reentrant_guard_triggered).lower()}",
+        ])
+
+
+@dataclass
+class TensorBackwardReport:
+    gradients: Dict[int, torch.Tensor]
+    steps: List[TensorBackwardStep]
+    telemetry: TensorSchedulerTelemetry
+
+    def gradient(self, node: int) -> Optional[torch.Tensor]:
+        return self.gradients.get(int(node))
+
+
+# Marker a VJP rule returns for an input whose gradient it already accumulated in place into
+# the target handed out by ``GradTargets.leaf_target`` (used by GEMM epilogues that write
+# straight into the flat gradient buffer).
+ACCUMULATED = object()
+
+
+class GradTargets:
+    """Lets a VJP rule write a leaf gradient in place instead of returning a temporary."""
+
+    __slots__ = ("_tape", "_node", "_grads")
+
+    def __init__(self, tape: "TensorTape", node: "TensorNode", grads: Optional[dict] = None):
+        self._tape, self._node, self._grads = tape, node, grads
+
+    def take_current(self, input_index: int) -> Optional[torch.Tensor]:
+        """Remove and return the gradient accumulated so far for input ``input_index``.
+
+        A rule that fuses the accumulation into its own kernel (``dx = f(...) + current``)
+        takes the running value and returns the sum as that input's contribution; the sum
+        is formed in the same position of the pop order, so replay stays bit-identical.
+        """
+        if self._grads is None:
+            return None
+        return self._grads.pop(self._node.inputs[input_index], None)
+
+    def leaf_target(self, input_index: int) -> Optional[Tuple[torch.Tensor, bool]]:
+        """``(buffer, has_value)`` for a leaf input with a preallocated gradient buffer."""
+        nid = self._node.inputs[input_index]
+        n = self._tape.nodes[nid]
+        if not (n.is_leaf and n.requires_grad) or n.grad_buffer is None or n.hooks:
+            return None
+        return n.grad_buffer, n.grad_buffer_filled
+
+    def mark_accumulated(self, input_index: int) -> None:
+        self._tape.nodes[self._node.inputs[input_index]].grad_buffer_filled = True
+
+
+class TensorNode:
+    __slots__ = ("id", "op", "inputs", "value", "requires_grad", "is_leaf", "vjp", "rule", "retain_grad",
+                 "hooks", "grad", "grad_buffer", "grad_buffer_filled", "version", "saved", "name")
+
+    def __init__(self, nid, op, inputs, value, requires_grad, is_leaf, vjp, rule):
+        self.id = nid
+        self.op = op
+        self.inputs = inputs
+        self.value = value
+        self.requires_grad = requires_grad
+        self.is_leaf = is_leaf
+        self.vjp = vjp
+        self.rule = rule
+        self.retain_grad = False
+        self.hooks: List[Tuple[int, Callable]] = []
+        self.grad: Optional[torch.Tensor] = None         # persistent accumulated gradient
+        self.grad_buffer: Optional[torch.Tensor] = None   # preallocated view (flat buffers)
+        self.grad_buffer_filled = False
+        self.version = 0
+        self.saved = None
+        self.name = None
+
+
+@dataclass(frozen=True)
+class TensorHookHandle:
+    node: int
+    hook_id: int
+
+
+class TensorTape:
+    """Append-only tape of tensor operations with a deterministic backward pass."""
+
+    def __init__(self, grad_dtype: Optional[torch.dtype] = torch.float64):
+        self._lib = native.load()
+        self._h = self._lib.ftc_tape_new()
+        self.nodes: List[TensorNode] = []
+        self.grad_dtype = grad_dtype      # None: keep the dtype the VJP rule produces
+        self._next_hook = 0
+        self.grad_enabled = True
+        self.accumulate_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor] = lambda a, b: a + b
+        self.last_plan_cache: Dict[Tuple[int, int], Tuple] = {}
+
+    def __del__(self):
+        try:
+            if self._h:
+                self._lib.ftc_tape_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ construction
+    def __len__(self) -> int:
+        return len(self.nodes)
+
+    def _append(self, op, inputs, value, requires_grad, is_leaf, vjp, rule) -> int:
+        arr = (C.c_int64 * max(1, len(inputs)))(*inputs)
+        nid = self._lib.ftc_tape_add_node(self._h, arr, len(inputs), int(requires_grad), int(is_leaf))
+        if nid < 0:
+            raise UnknownTensorNode(f"invalid input ids {inputs}")
+        self.nodes.append(TensorNode(nid, op, tuple(inputs), value, requires_grad, is_leaf, vjp, rule))
+        return int(nid)
+
+    def leaf(self, value: torch.Tensor, requires_grad: bool = False, name: Optional[str] = None) -> int:
+        if requires_grad and not value.is_floating_point() and not value.is_complex():
+            raise TensorRequiresGradNonFloating(f"dtype {value.dtype} cannot require grad")
+        nid = self._append("leaf", (), value, requires_grad, True, None, "leaf")
+        self.nodes[nid].name = name
+        return nid
+
+    def record(self, op: str, inputs: Sequence[int], value: torch.Tensor,
+               vjp: Optional[Callable], rule: str, saved: Any = None) -> int:
+        """Append a computed node.  ``vjp(grad_out, targets) -> sequence of per-input grads``."""
+        for i in inputs:
+            if i < 0 or i >= len(self.nodes):
+                raise UnknownTensorNode(f"node {i}")
+        rg = self.grad_enabled and any(self.nodes[i].requires_grad for i in inputs) and vjp is not None
+        nid = self._append(op, tuple(inputs), value, rg, False, vjp if rg else None, rule)
+        self.nodes[nid].saved = saved if rg else None
+        return nid
+
+    def value(self, nid: int) -> torch.Tensor:
+        return self._node(nid).value
+
+    def _node(self, nid: int) -> TensorNode:
+        if nid < 0 or nid >= len(self.nodes):
+            raise UnknownTensorNode(f"node {nid}")
+        return self.nodes[nid]
+
+    def requires_grad_(self, nid: int, flag: bool = True) -> None:
+        n = self._node(nid)
+        if not n.is_leaf:
+            raise TensorRequiresGradNonLeaf(f"node {nid} is not a leaf")
+        if flag and not n.value.is_floating_point():
+            raise TensorRequiresGradNonFloating(f"node {nid} has dtype {n.value.dtype}")
+        n.requires_grad = flag
+        self._lib.ftc_tape_set_requires_grad(self._h, nid, int(flag))
+
+    def retain_grad(self, nid: int) -> None:
+        self._node(nid).retain_grad = True
+
+    def bump_version(self, nid: int) -> int:
+        n = self._node(nid)
+        n.version += 1
+        return n.version
+
+    def version(self, nid: int) -> int:
+        return self._node(nid).version
+
+    def truncate_graph_to(self, boundary: int) -> None:
+        """Drop nodes with id >= boundary (parameters are low-index leaves and survive)."""
+        boundary = max(0, min(boundary, len(self.nodes)))
+        del self.nodes[boundary:]
+        self._lib.ftc_tape_truncate(self._h, boundary)
+        self.last_plan_cache.clear()
+
+    def clear_graph(self) -> None:
+        self.truncate_graph_to(0)
+
+    # ------------------------------------------------------------------ hooks
+    def register_tensor_hook(self, nid: int, fn: Callable[[torch.Tensor], Optional[torch.Tensor]]) -> TensorHookHandle:
+        n = self._node(nid)
+        hid = self._next_hook
+        self._next_hook += 1
+        n.hooks.append((hid, fn))
+        return TensorHookHandle(nid, hid)
+
+    def remove_tensor_hook(self, handle: TensorHookHandle) -> bool:
+        n = self._node(handle.node)
+        before = len(n.hooks)
+        n.hooks = [(h, f) for (h, f) in n.hooks if h != handle.hook_id]
+        return len(n.hooks) != before
+
+    # ------------------------------------------------------------------ gradient accessors
+    def accumulated_gradient(self, nid: int) -> Optional[torch.Tensor]:
+        n = self._node(nid)
+        if n.grad_buffer is not None:
+            return n.grad_buffer if n.grad_buffer_filled else None
+        return n.grad
+
+    def set_accumulated_gradient(self, nid: int, grad: Optional[torch.Tensor]) -> None:
+        n = self._node(nid)
+        if n.grad_buffer is not None and grad is not None:
+            n.grad_buffer.copy_(grad)
+            n.grad_buffer_filled = True
+        else:
+            n.grad = grad
+
+    def zero_accumulated_gradient(self, nid: int) -> None:
+        n = self._node(nid)
+        n.grad = None
+        n.grad_buffer_filled = False
+
+    def bind_grad_buffer(self, nid: int, buf: torch.Tensor) -> None:
+        """Make ``buf`` (e.g. a view of a flat fp32 gradient arena) the leaf's gradient storage."""
+        n = self._node(nid)
+        if not n.is_leaf:
+            raise TensorRequiresGradNonLeaf(f"node {nid} is not a leaf")
+        n.grad_buffer = buf
+        n.grad_buffer_filled = False
+
+    # ------------------------------------------------------------------ backward
+    def schedule(self, root: int, check_consumed: bool = True):
+        n = len(self.nodes)
+        order = (C.c_int64 * max(1, n))()
+        deps = (C.c_int64 * max(1, n))()
+        stats = (C.c_int64 * 3)()
+        cnt = self._lib.ftc_tape_schedule(self._h, root, int(check_consumed), order, deps, stats)
+        if cnt == -1:
+            raise UnknownTensorNode(f"node {root}")
+        if cnt == -2:
+            raise TensorRootDoesNotRequireGrad(f"node {root} does not require grad")
+        if cnt == -3:
+            raise TensorGraphConsumed("the graph was consumed by an earlier backward; pass retain_graph=True")
+        if cnt < 0:
+            raise TensorDependencyUnderflow(f"scheduler error {cnt}")
+        return list(order[:cnt]), list(deps[:n]), (int(stats[0]), int(stats[1]), int(stats[2]))
+
+    def _cast_grad(self, g: torch.Tensor) -> torch.Tensor:
+        if self.grad_dtype is not None and g.dtype != self.grad_dtype and g.is_floating_point():
+            return g.to(self.grad_dtype)
+        return g
+
+    def backward(self, root: int, options: Optional[BackwardOptions] = None,
+                 seed: Optional[torch.Tensor] = None) -> TensorBackwardReport:
+        opts = options or BackwardOptions()
+        guard = fallback = False
+        if opts.current_reentrant_depth > opts.max_reentrant_depth:
+            if opts.policy == ReentrantPolicy.StrictFail:
+                raise ReentrantDepthExceeded(opts.current_reentrant_depth, opts.max_reentrant_depth)
+            guard = fallback = True
+        depth = min(opts.current_reentrant_depth, opts.max_reentrant_depth)
+        order, deps, (pushes, pops, max_len) = self.schedule(root)
+
+        rootn = self.nodes[root]
+        if seed is None:
+            seed = torch.ones_like(rootn.value, dtype=self.grad_dtype or rootn.value.dtype)
+            seed._ft_unit_seed = True   # lets fused loss rules skip a multiply by one
+        grads: Dict[int, torch.Tensor] = {root: seed}
+        steps: List[TensorBackwardStep] = []
+        nodes = self.nodes
+        for nid in order:
+            node = nodes[nid]
+            incoming = grads.get(nid)
+            if incoming is None:
+                if not node.requires_grad:
+                    continue
+                incoming = torch.zeros_like(node.value, dtype=self.grad_dtype or node.value.dtype)
+            for _, hook in node.hooks:
+                res = hook(incoming)
+                if res is not None:
+                    if tuple(res.shape) != tuple(incoming.shape):
+                        raise TensorGradientShapeMismatch(
+                            f"hook on node {nid} changed the gradient shape {tuple(incoming.shape)} -> {tuple(res.shape)}")
+                    incoming = res
+            grads[nid] = incoming
+            if node.is_leaf:
+                if node.requires_grad:
+                    steps.append(TensorBackwardStep(nid, incoming.numel(), "leaf"))
+                continue
+            if not node.requires_grad or node.vjp is None:
+                continue
+            steps.append(TensorBackwardStep(nid, incoming.numel(), node.rule))
+            contribs = node.vjp(incoming, GradTargets(self, node, grads))
+            if len(contribs) != len(node.inputs):
+                raise TensorGradientShapeMismatch(
+                    f"rule '{node.rule}' returned {len(contribs)} gradients for {len(node.inputs)} inputs")
+            for inp, g in zip(node.inputs, contribs):
+                if g is None or g is ACCUMULATED:
+                    continue
+                if not nodes[inp].requires_grad:
+                    continue
+                g = self._cast_grad(g)
+                prev = grads.get(inp)
+                if prev is None:
+                    grads[inp] = g                      # first contribution: stored verbatim
+                else:
+                    grads[inp] = self.accumulate_fn(prev, g)   # later contributions: added in rule order
+            if opts.detect_anomaly:
+                for inp in node.inputs:
+                    t = grads.get(inp)
+                    if t is not None and not bool(torch.isfinite(t).all()):
+                        raise AnomalyDetected(f"non-finite gradient produced by node {nid} ({node.rule})")
+
+        # persistent gradients: leaves that require grad and nodes marked retain_grad
+        for nid in order:
+            node = nodes[nid]
+            if not node.requires_grad:
+                continue
+            if not (node.is_leaf or node.retain_grad):
+                continue
+            g = grads.get(nid)
+            if g is None:
+                continue
+            if node.grad_buffer is not None:
+                if node.grad_buffer_filled:
+                    node.grad_buffer.add_(g)
+                else:
+                    node.grad_buffer.copy_(g)
+                    node.grad_buffer_filled = True
+            elif node.grad is None:
+                node.grad = g.clone() if g is seed else g
+            else:
+                node.grad = node.grad + g
+
+        if not (opts.retain_graph or opts.create_graph):
+            self._lib.ftc_tape_mark_consumed(self._h)
+        telemetry = TensorSchedulerTelemetry(order, pushes, pops, max_len, deps, depth, guard, fallback)
+        return TensorBackwardReport(grads, steps, telemetry)

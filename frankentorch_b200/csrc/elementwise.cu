@@ -228,6 +228,79 @@ adamw_kernel(float* __restrict__ master, __nv_bfloat16* __restrict__ shadow,
   }
 }
 
+// Device-resident optimizer clock so a captured CUDA graph replays a correct step:
+// hyper = {lr, bias_correction1, bias_correction2, grad_scale}; step is incremented here.
+__global__ void adamw_tick_kernel(long long* __restrict__ step, float* __restrict__ hyper, double b1,
+                                  double b2) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const long long s = *step + 1;
+    *step = s;
+    hyper[1] = (float)(1.0 - pow(b1, (double)s));
+    hyper[2] = (float)(1.0 - pow(b2, (double)s));
+  }
+}
+// hyper[3] = min(1, max_norm / (sqrt(sumsq) + 1e-6))  (clip_grad_norm_, ft-nn/src/lib.rs:740)
+__global__ void clip_scale_kernel(const float* __restrict__ sumsq, float max_norm,
+                                  float* __restrict__ hyper, float* __restrict__ norm_out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const float nrm = sqrtf(*sumsq);
+    if (norm_out) *norm_out = nrm;
+    const float c = max_norm / (nrm + 1e-6f);
+    hyper[3] = c < 1.f ? c : 1.f;
+  }
+}
+__global__ void __launch_bounds__(256)
+adamw_dev_kernel(float* __restrict__ master, __nv_bfloat16* __restrict__ shadow,
+                 const float* __restrict__ grad, float* __restrict__ m, float* __restrict__ v,
+                 long long n, const float* __restrict__ hyper, float b1, float b2, float eps,
+                 float wd) {
+  const float lr = hyper[0], bc1 = hyper[1], bc2 = hyper[2], gscale = hyper[3];
+  const long long n4 = n >> 2;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 g4 = reinterpret_cast<const float4*>(grad)[i];
+    float4 m4 = reinterpret_cast<float4*>(m)[i];
+    float4 v4 = reinterpret_cast<float4*>(v)[i];
+    float4 p4 = reinterpret_cast<float4*>(master)[i];
+    float g[4] = {g4.x, g4.y, g4.z, g4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w};
+    float vv[4] = {v4.x, v4.y, v4.z, v4.w}, pp[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gi = g[k] * gscale;
+      mm[k] = b1 * mm[k] + (1.f - b1) * gi;
+      vv[k] = b2 * vv[k] + (1.f - b2) * gi * gi;
+      const float mh = mm[k] / bc1, vh = vv[k] / bc2;
+      pp[k] -= pp[k] * lr * wd + lr * mh / (sqrtf(vh) + eps);
+    }
+    reinterpret_cast<float4*>(m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    reinterpret_cast<float4*>(master)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+    if (shadow) {
+      uint2 o;
+      o.x = pack_bf16(pp[0], pp[1]);
+      o.y = pack_bf16(pp[2], pp[3]);
+      reinterpret_cast<uint2*>(shadow)[i] = o;
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (long long i = n4 << 2; i < n; ++i) {
+      const float gi = grad[i] * gscale;
+      const float mi = b1 * m[i] + (1.f - b1) * gi;
+      const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+      m[i] = mi;
+      v[i] = vi;
+      float p = master[i];
+      p -= p * lr * wd + lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+      master[i] = p;
+      if (shadow) shadow[i] = __float2bfloat16(p);
+    }
+  }
+}
+__global__ void __launch_bounds__(256) fill_f32_kernel(float* __restrict__ x, long long n, float v) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] = v;
+}
+
 // ------------------------------------------------------------------------ presenter / im2col
 template <bool HALF>
 __global__ void present_rgba8_kernel(const unsigned char* __restrict__ src, void* __restrict__ dst,
@@ -340,5 +413,30 @@ extern "C" int ftk_im2col_1d(const float* x, float* y, int t_in, int cin, int k,
   if (t_in <= 0 || cin <= 0 || k <= 0 || t_out <= 0 || stride <= 0) return -2;
   dim3 b(32, 8), g((cin * k + 31) / 32, (t_out + 7) / 8);
   im2col_1d_kernel<<<g, b, 0, STREAM(stream)>>>(x, y, t_in, cin, k, stride, pad, t_out);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ftk_adamw_tick(long long* step, float* hyper, double b1, double b2, void* stream) {
+  adamw_tick_kernel<<<1, 32, 0, STREAM(stream)>>>(step, hyper, b1, b2);
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_clip_scale(const float* sumsq, float max_norm, float* hyper, float* norm_out,
+                              void* stream) {
+  clip_scale_kernel<<<1, 32, 0, STREAM(stream)>>>(sumsq, max_norm, hyper, norm_out);
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_adamw_dev(float* master, void* shadow, const float* grad, float* m, float* v,
+                             long long n, const float* hyper, float b1, float b2, float eps,
+                             float wd, void* stream) {
+  if (n <= 0) return -2;
+  if (!al16(master) || !al16(grad) || !al16(m) || !al16(v) || (shadow && (reinterpret_cast<uintptr_t>(shadow) & 7)))
+    return -3;
+  adamw_dev_kernel<<<ew_grid(n >> 2, 256), 256, 0, STREAM(stream)>>>(master, BFW(shadow), grad, m, v, n,
+                                                                      hyper, b1, b2, eps, wd);
+  return (int)cudaGetLastError();
+}
+extern "C" int ftk_fill_f32(float* x, long long n, float v, void* stream) {
+  if (n <= 0) return -2;
+  fill_f32_kernel<<<ew_grid(n, 256), 256, 0, STREAM(stream)>>>(x, n, v);
   return (int)cudaGetLastError();
 }

@@ -156,3 +156,19 @@ int ftk_im2col_1d(const float* x, float* y, int t_in, int cin, int k, int stride
 #ifdef __cplusplus
 }
 #endif
+
+// ---- graph-replayable optimizer step (C linkage) --------------------------------------------
+#ifdef __cplusplus
+extern "C" {
+#endif
+// hyper (device, fp32[4]) = {lr, bias_correction1, bias_correction2, grad_scale}; `step`
+// (device, int64) is incremented by the tick so a captured graph advances on every replay.
+int ftk_adamw_tick(long long* step, float* hyper, double beta1, double beta2, void* stream);
+int ftk_clip_scale(const float* sumsq, float max_norm, float* hyper, float* norm_out, void* stream);
+int ftk_adamw_dev(float* master, void* shadow_bf16, const float* grad, float* m, float* v, long long n,
+                  const float* hyper, float beta1, float beta2, float eps, float weight_decay,
+                  void* stream);
+int ftk_fill_f32(float* x, long long n, float v, void* stream);
+#ifdef __cplusplus
+}
+#endif

@@ -95,6 +95,10 @@ def load(build_if_missing: bool = True):
         "ftk_embedding_fwd": [vp, vp, vp, vp, i, i, i, vp],
         "ftk_embedding_bwd": [vp, vp, vp, vp, vp, i, i, i, vp],
         "ftk_adamw": [vp, vp, vp, vp, vp, ll, f, f, f, f, f, f, f, f, vp],
+        "ftk_adamw_tick": [vp, vp, C.c_double, C.c_double, vp],
+        "ftk_clip_scale": [vp, f, vp, vp, vp],
+        "ftk_adamw_dev": [vp, vp, vp, vp, vp, ll, vp, f, f, f, f, vp],
+        "ftk_fill_f32": [vp, ll, f, vp],
         "ftk_present_rgba8": [vp, vp, i, i, ll, i, vp],
         "ftk_im2col_1d": [vp, vp, i, i, i, i, i, i, vp],
     }

@@ -1,0 +1,239 @@
+"""Tape-recording fused operators of the sm_100a backend.
+
+Each function runs the forward kernel(s), appends ONE node to the tape and attaches a
+VJP rule that launches the matching backward kernels.  The rule strings are the
+reference's (`rule` field of every backward step, ft-autograd/src/lib.rs:11807-15602)
+where the op exists there, extended with the fused epilogue in brackets.
+
+Parameter gradients are written in place into the leaf's bound fp32 gradient buffer
+(``TensorTape.bind_grad_buffer``) by the wgrad GEMM epilogue (``accumulate`` when the
+buffer already holds a contribution), so no temporary dW tensor is materialised.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..autograd.tape import ACCUMULATED, TensorTape
+from . import kernels as K
+
+RULE_LINEAR = "d(A@B)/dA=dOut@B^T; d(A@B)/dB=A^T@dOut"
+
+
+def _wgrad_into(targets, idx, dy2d, x2d):
+    """dW (+)= dy^T x, written into the bound gradient buffer when there is one."""
+    tgt = targets.leaf_target(idx)
+    if tgt is not None:
+        buf, filled = tgt
+        K.linear_wgrad(dy2d, x2d, out=buf, accumulate=filled)
+        targets.mark_accumulated(idx)
+        return ACCUMULATED
+    return K.linear_wgrad(dy2d, x2d)
+
+
+def _bgrad_into(targets, idx, dy2d):
+    tgt = targets.leaf_target(idx)
+    if tgt is not None:
+        buf, filled = tgt
+        K.colsum(dy2d, out=buf, accumulate=filled)
+        targets.mark_accumulated(idx)
+        return ACCUMULATED
+    return K.colsum(dy2d)
+
+
+def linear(tape: TensorTape, x: int, w: int, b: Optional[int] = None, *, act: Optional[str] = None,
+           resid: Optional[int] = None) -> int:
+    """``y = act(x @ w^T + b) (+ resid)``; ``w`` is ``[out, in]`` (ft-nn/src/lib.rs:902).
+
+    ``act`` in ``{None, "gelu_tanh", "gelu_erf", "relu"}``.  With an activation the
+    pre-activation is kept (bf16) for the backward epilogue ``dU = (dY W2) * act'(U)``.
+    """
+    xv, wv = tape.value(x), tape.value(w)
+    bv = tape.value(b) if b is not None else None
+    rv = tape.value(resid) if resid is not None else None
+    x2 = xv.reshape(-1, xv.shape[-1])
+    epi = {None: K.EPI_NONE, "gelu_tanh": K.EPI_GELU_TANH, "gelu_erf": K.EPI_GELU_ERF, "relu": K.EPI_RELU}[act]
+    depi = {None: K.EPI_NONE, "gelu_tanh": K.EPI_MUL_DGELU_TANH, "gelu_erf": K.EPI_MUL_DGELU_ERF,
+            "relu": K.EPI_MUL_DRELU}[act]
+    aux = torch.empty((x2.shape[0], wv.shape[0]), dtype=torch.bfloat16, device=xv.device) if act else None
+    r2 = rv.reshape(-1, rv.shape[-1]) if rv is not None else None
+    y = K.linear_fwd(x2, wv, bv, epi=epi, resid=r2, aux=aux)
+    y = y.reshape(*xv.shape[:-1], wv.shape[0])
+    inputs = [x, w] + ([b] if b is not None else []) + ([resid] if resid is not None else [])
+    has_b, has_r = b is not None, resid is not None
+    x_needs = tape.nodes[x].requires_grad
+
+    def vjp(gy, targets):
+        g2 = gy.reshape(-1, gy.shape[-1])
+        if act:
+            # dU = dY * act'(U): elementwise on the saved pre-activation
+            g2 = K.gelu_bwd(aux, g2, tanh_form=(act == "gelu_tanh")) if act != "relu" else \
+                (g2 * (aux > 0)).to(torch.bfloat16)
+        out = []
+        dx = K.linear_dgrad(g2, wv).reshape(xv.shape) if x_needs else None
+        out.append(dx)
+        out.append(_wgrad_into(targets, 1, g2, x2))
+        if has_b:
+            out.append(_bgrad_into(targets, 2, g2))
+        if has_r:
+            out.append(gy)
+        return out
+
+    rule = RULE_LINEAR + (f" [+bias{'+' + act if act else ''}{'+residual' if has_r else ''}]")
+    return tape.record("linear", inputs, y, vjp, rule)
+
+
+def mlp_up_down(tape: TensorTape, x: int, w1: int, b1: int, w2: int, b2: int, resid: int, *,
+                act: str = "gelu_tanh") -> int:
+    """``resid + (act(x w1^T + b1)) w2^T + b2`` as one node.
+
+    Backward fuses ``act'`` into the dgrad epilogue of the second GEMM:
+    ``dU = (dY @ w2) * act'(U)`` is one kernel (no separate elementwise pass).
+    """
+    xv, w1v, b1v, w2v, b2v, rv = (tape.value(i) for i in (x, w1, b1, w2, b2, resid))
+    x2 = xv.reshape(-1, xv.shape[-1])
+    r2 = rv.reshape(-1, rv.shape[-1])
+    epi = {"gelu_tanh": K.EPI_GELU_TANH, "gelu_erf": K.EPI_GELU_ERF, "relu": K.EPI_RELU}[act]
+    depi = {"gelu_tanh": K.EPI_MUL_DGELU_TANH, "gelu_erf": K.EPI_MUL_DGELU_ERF, "relu": K.EPI_MUL_DRELU}[act]
+    u = torch.empty((x2.shape[0], w1v.shape[0]), dtype=torch.bfloat16, device=xv.device)
+    h = K.linear_fwd(x2, w1v, b1v, epi=epi, aux=u)
+    y = K.linear_fwd(h, w2v, b2v, resid=r2).reshape(rv.shape)
+
+    def vjp(gy, targets):
+        g2 = gy.reshape(-1, gy.shape[-1])
+        dw2 = _wgrad_into(targets, 3, g2, h)
+        db2 = _bgrad_into(targets, 4, g2)
+        du = K.linear_dgrad(g2, w2v, epi=depi, resid=u)      # (dY @ w2) * act'(U)
+        dw1 = _wgrad_into(targets, 1, du, x2)
+        db1 = _bgrad_into(targets, 2, du)
+        dx = K.linear_dgrad(du, w1v).reshape(xv.shape)
+        return [dx, dw1, db1, dw2, db2, gy]
+
+    return tape.record("mlp", [x, w1, b1, w2, b2, resid], y, vjp,
+                       RULE_LINEAR + f" [mlp: up+bias+{act}, down+bias+residual]")
+
+
+def layernorm(tape: TensorTape, x: int, gamma: int, beta: int, eps: float = 1e-5) -> int:
+    """LayerNorm over the last dim (ft-nn/src/lib.rs:2042; kernel math lib.rs:5824/6052)."""
+    xv, gv, bv = tape.value(x), tape.value(gamma), tape.value(beta)
+    x2 = xv.reshape(-1, xv.shape[-1])
+    y, mean, rstd, _ = K.layernorm_fwd(x2, gv, bv, eps)
+
+    def vjp(gy, targets):
+        g2 = gy.reshape(-1, gy.shape[-1])
+        # fuse the running gradient of x (the residual branch) into the dx kernel
+        cur = targets.take_current(0)
+        tg, tb = targets.leaf_target(1), targets.leaf_target(2)
+        if tg is not None and tb is not None and tg[1] == tb[1]:
+            dx, _, _ = K.layernorm_bwd(g2, x2, gv, mean, rstd, dx_add=None if cur is None else cur.reshape(x2.shape),
+                                       dgamma=tg[0], dbeta=tb[0], accumulate=tg[1])
+            targets.mark_accumulated(1)
+            targets.mark_accumulated(2)
+            return [dx.reshape(xv.shape), ACCUMULATED, ACCUMULATED]
+        dx, dg, db = K.layernorm_bwd(g2, x2, gv, mean, rstd, dx_add=None if cur is None else cur.reshape(x2.shape))
+        return [dx.reshape(xv.shape), dg, db]
+
+    return tape.record("layer_norm", [x, gamma, beta], y.reshape(xv.shape), vjp, "d(layer_norm(x))/dx,dgamma,dbeta")
+
+
+def rmsnorm(tape: TensorTape, x: int, gamma: int, eps: float = 1e-6) -> int:
+    """RMSNorm (ft-nn/src/lib.rs:6843; kernel math ft-kernel-cpu/src/lib.rs:6418/6503)."""
+    xv, gv = tape.value(x), tape.value(gamma)
+    x2 = xv.reshape(-1, xv.shape[-1])
+    y, rstd = K.rmsnorm_fwd(x2, gv, eps)
+
+    def vjp(gy, targets):
+        g2 = gy.reshape(-1, gy.shape[-1])
+        tg = targets.leaf_target(1)
+        if tg is not None:
+            dx, _ = K.rmsnorm_bwd(g2, x2, gv, rstd, dgamma=tg[0], accumulate=tg[1])
+            targets.mark_accumulated(1)
+            return [dx.reshape(xv.shape), ACCUMULATED]
+        dx, dg = K.rmsnorm_bwd(g2, x2, gv, rstd)
+        return [dx.reshape(xv.shape), dg]
+
+    return tape.record("rms_norm", [x, gamma], y.reshape(xv.shape), vjp, "d(rms_norm(x))/dx,dgamma")
+
+
+def attention_packed(tape: TensorTape, qkv: int, n_heads: int, *, causal: bool = True,
+                     scale: Optional[float] = None) -> int:
+    """Multi-head attention over packed ``[B, S, 3*d]`` projections -> ``[B, S, d]``.
+
+    Heads are addressed in place through strided TMA maps: no split/permute copies
+    (the reference reshapes to [N*H, S, hd], ft-nn/src/lib.rs:5145-5167).
+    """
+    qv = tape.value(qkv)
+    B, S, d3 = qv.shape
+    d = d3 // 3
+    hd = d // n_heads
+    q, k, v = (qv[:, :, i * d:(i + 1) * d].view(B, S, n_heads, hd) for i in range(3))
+    o, lse = K.attention_fwd(q, k, v, causal=causal, scale=scale)
+
+    def vjp(go, targets):
+        dqkv = torch.empty_like(qv)
+        dq, dk, dv = (dqkv[:, :, i * d:(i + 1) * d].view(B, S, n_heads, hd) for i in range(3))
+        K.attention_bwd(q, k, v, o, lse, go.reshape(B, S, n_heads, hd), causal=causal, scale=scale,
+                        dq=dq, dk=dk, dv=dv)
+        return [dqkv]
+
+    return tape.record("sdpa", [qkv], o.view(B, S, d), vjp, "d(sdpa(q,k,v))/dq,dk,dv [flash, recompute P]")
+
+
+def embedding(tape: TensorTape, ids: torch.Tensor, wte: int, wpe: Optional[int], S: int) -> int:
+    """Token (+ position) embedding; backward is a deterministic sorted scatter-add."""
+    wv = tape.value(wte)
+    pv = tape.value(wpe) if wpe is not None else None
+    B = ids.numel() // S
+    out = K.embedding_fwd(ids, wv, pv, S).view(B, S, wv.shape[1])
+    inputs = [wte] + ([wpe] if wpe is not None else [])
+
+    def vjp(go, targets):
+        g2 = go.reshape(-1, go.shape[-1])
+        res = []
+        t0 = targets.leaf_target(0)
+        t1 = targets.leaf_target(1) if wpe is not None else None
+        if t0 is not None and (wpe is None or t1 is not None):
+            for t in (t0, t1):
+                if t is not None and not t[1]:
+                    K.fill_f32(t[0], 0.0)
+            K.embedding_bwd(ids, g2, t0[0], t1[0] if t1 is not None else None, S)
+            targets.mark_accumulated(0)
+            res.append(ACCUMULATED)
+            if wpe is not None:
+                targets.mark_accumulated(1)
+                res.append(ACCUMULATED)
+            return res
+        dwte = torch.zeros(wv.shape, dtype=torch.float32, device=wv.device)
+        dwpe = torch.zeros(pv.shape, dtype=torch.float32, device=wv.device) if pv is not None else None
+        K.embedding_bwd(ids, g2, dwte, dwpe, S)
+        return [dwte] + ([dwpe] if wpe is not None else [])
+
+    return tape.record("embedding", inputs, out, vjp, "d(index_select(x))/dx=scatter_add_grad")
+
+
+def lm_head_cross_entropy(tape: TensorTape, x: int, w: int, targets_ids: torch.Tensor, vocab: int) -> int:
+    """``mean(cross_entropy(x @ w^T, targets))`` with the softmax gradient formed in place.
+
+    The logits ``[rows, padded_vocab]`` are produced by the GEMM, the loss kernel overwrites
+    them with ``(softmax - onehot)/rows`` (ft-kernel-cpu/src/lib.rs:6649/6679), and backward
+    only scales by the incoming scalar and runs the two GEMMs.
+    """
+    xv, wv = tape.value(x), tape.value(w)
+    x2 = xv.reshape(-1, xv.shape[-1])
+    rows = x2.shape[0]
+    logits = K.linear_fwd(x2, wv)
+    losses, dlogits = K.cross_entropy_fwd_bwd(logits, targets_ids.reshape(-1), vocab, 1.0 / rows, inplace=True)
+    loss = K.reduce_mean(losses)
+
+    def vjp(g, targets):
+        # g is the scalar seed (ones for a plain backward); dlogits already carries 1/rows
+        dl = dlogits
+        if not (g.numel() == 1 and g.dtype == torch.float32 and getattr(g, "_ft_unit_seed", False)):
+            dl = (dlogits.float() * g.reshape(()).float()).to(torch.bfloat16)
+        dw = _wgrad_into(targets, 1, dl, x2)
+        dx = K.linear_dgrad(dl, wv).reshape(xv.shape)
+        return [dx, dw]
+
+    return tape.record("lm_head_ce", [x, w], loss.reshape(()), vjp,
+                       RULE_LINEAR + " [+softmax-cross-entropy, mean]")

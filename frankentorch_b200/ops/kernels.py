@@ -401,6 +401,28 @@ def adamw(master, shadow, grad, m, v, *, lr, beta1, beta2, eps, weight_decay, st
          "ftk_adamw")
 
 
+def adamw_tick(step_dev, hyper_dev, beta1, beta2):
+    """Advance the device-resident step counter and bias corrections (graph replayable)."""
+    _chk(_lib.load().ftk_adamw_tick(step_dev.data_ptr(), hyper_dev.data_ptr(), float(beta1), float(beta2),
+                                    _stream()), "ftk_adamw_tick")
+
+
+def clip_scale(sumsq_dev, max_norm, hyper_dev, norm_out=None):
+    _chk(_lib.load().ftk_clip_scale(sumsq_dev.data_ptr(), float(max_norm), hyper_dev.data_ptr(),
+                                    _ptr(norm_out), _stream()), "ftk_clip_scale")
+
+
+def adamw_dev(master, shadow, grad, m, v, hyper_dev, *, beta1, beta2, eps, weight_decay):
+    """AdamW with lr / bias corrections / gradient scale read from device memory."""
+    _chk(_lib.load().ftk_adamw_dev(master.data_ptr(), _ptr(shadow), grad.data_ptr(), m.data_ptr(),
+                                   v.data_ptr(), master.numel(), hyper_dev.data_ptr(), float(beta1),
+                                   float(beta2), float(eps), float(weight_decay), _stream()), "ftk_adamw_dev")
+
+
+def fill_f32(x, value=0.0):
+    _chk(_lib.load().ftk_fill_f32(x.data_ptr(), x.numel(), float(value), _stream()), "ftk_fill_f32")
+
+
 # --------------------------------------------------------------------------------------- misc
 def present_rgba8(src, width, height, row_bytes, half=False):
     dst = torch.empty((height, width, 4), dtype=torch.float16 if half else torch.float32, device=src.device)

@@ -1,0 +1,126 @@
+"""Training engine: one optimizer step of a tape-recorded model, captured in a CUDA graph.
+
+Per step the engine (1) copies the step's token ids / targets from pinned host memory
+into static device buffers, (2) replays the captured graph (forward through the DAC
+tape, deterministic backward in scheduler order, gradient clipping, fused AdamW on the
+flat parameter arena) and (3) reads the loss back to the host.  The tape is recorded
+once, at capture time; replaying the graph re-executes exactly the recorded kernel
+sequence, which is what makes the step replayable bit for bit.
+
+With more than one rank the gradient reduction + sharded AdamW + parameter all-gather
+are delegated to :mod:`frankentorch_b200.parallel` (in-kernel peer loads/stores over
+NVLink); the single-GPU path uses the plain fused AdamW kernel.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..autograd.tape import BackwardOptions
+from ..ops import kernels as K
+
+
+@dataclass
+class OptimConfig:
+    lr: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.01      # AdamW defaults of the reference, ft-optim/src/lib.rs:800
+    grad_clip: Optional[float] = 1.0
+
+
+class TrainEngine:
+    def __init__(self, model, micro_batch: int, seq_len: int, optim: Optional[OptimConfig] = None, *,
+                 use_cuda_graph: bool = True, dp=None):
+        self.model = model
+        self.tape = model.tape
+        self.B, self.S = micro_batch, seq_len
+        self.opt = optim or OptimConfig()
+        self.dp = dp
+        dev = model.device
+        self.ids = torch.zeros((micro_batch, seq_len), dtype=torch.int64, device=dev)
+        self.targets = torch.zeros((micro_batch, seq_len), dtype=torch.int64, device=dev)
+        self.loss_dev = torch.zeros((), dtype=torch.float32, device=dev)
+        self.loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+        self.hyper = torch.tensor([self.opt.lr, 1.0, 1.0, 1.0], dtype=torch.float32, device=dev)
+        self.lr_host = torch.tensor([self.opt.lr], dtype=torch.float32).pin_memory()
+        self.step_dev = torch.zeros((), dtype=torch.int64, device=dev)
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.use_graph = use_cuda_graph
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.launches_per_step = 0
+        self.last_report = None
+        self.steps_done = 0
+
+    # ------------------------------------------------------------------ one step, eager
+    def _optimizer(self) -> None:
+        o, a = self.opt, self.model.arena
+        K.adamw_tick(self.step_dev, self.hyper, o.beta1, o.beta2)
+        if self.dp is not None:
+            self.dp.reduce_and_update(a, self.hyper, o, self.sumsq, self.grad_norm)
+            return
+        if o.grad_clip is not None:
+            K.sumsq(a.grads, out=self.sumsq)
+            K.clip_scale(self.sumsq, o.grad_clip, self.hyper, self.grad_norm)
+        K.adamw_dev(a.master, a.params, a.grads, a.m, a.v, self.hyper,
+                    beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay)
+
+    def _step_body(self) -> None:
+        n0 = K.launch_count()
+        self.model.reset_grads()
+        loss_id = self.model.forward(self.ids, self.targets)
+        self.last_report = self.tape.backward(loss_id, BackwardOptions())
+        self.loss_dev.copy_(self.tape.value(loss_id))
+        self._optimizer()
+        self.tape.truncate_graph_to(self.model.param_boundary)
+        self.launches_per_step = K.launch_count() - n0
+
+    def _ensure_graph(self) -> None:
+        if self.graph is not None or not self.use_graph:
+            return
+        # one eager step on a side stream initialises lazy state (function attributes, status
+        # word, driver entry points) outside of capture; its weight update is undone below
+        a = self.model.arena
+        snap = (a.master.clone(), a.m.clone(), a.v.clone(), self.step_dev.clone(), self.hyper.clone())
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._step_body()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        K.check_status()
+        a.master.copy_(snap[0]); a.m.copy_(snap[1]); a.v.copy_(snap[2])
+        self.step_dev.copy_(snap[3]); self.hyper.copy_(snap[4])
+        a.sync_shadow()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._step_body()
+
+    # ------------------------------------------------------------------ public API
+    def set_lr(self, lr: float) -> None:
+        self.lr_host[0] = lr
+        self.hyper[0:1].copy_(self.lr_host, non_blocking=True)
+
+    def step(self, ids_host: torch.Tensor, targets_host: torch.Tensor, *, read_loss: bool = True):
+        """One optimizer step on a batch given in (pinned) host memory; returns the loss."""
+        self.ids.copy_(ids_host, non_blocking=True)
+        self.targets.copy_(targets_host, non_blocking=True)
+        return self.step_device(read_loss=read_loss)
+
+    def step_device(self, *, read_loss: bool = False):
+        """One step on whatever is already in ``self.ids`` / ``self.targets``."""
+        if self.use_graph:
+            self._ensure_graph()
+            self.graph.replay()
+        else:
+            self._step_body()
+        self.steps_done += 1
+        if read_loss:
+            self.loss_host.copy_(self.loss_dev, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return float(self.loss_host)
+        return None
