@@ -54,6 +54,8 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--dp-impl", default="fused", choices=["fused", "nccl"],
+                    help="multi-GPU gradient path: in-kernel NVLink reduce-scatter+AdamW+all-gather, or NCCL all-reduce")
     return ap.parse_args()
 
 
@@ -152,11 +154,11 @@ def main():
     cfg.max_seq = max(seq, 1) if seq < cfg.max_seq else cfg.max_seq
     tape = TensorTape(grad_dtype=None)
     tape.accumulate_fn = lambda a, b: K.add(a, b) if (a.dtype == torch.bfloat16 and a.is_cuda) else a + b
-    model = GPT(cfg, tape, device=dev, seed=1234)
+    model = GPT(cfg, tape, device=dev, seed=1234, group=dist.group.WORLD if world > 1 else None)
     dp = None
     if world > 1:
-        from frankentorch_b200.parallel.data_parallel import FusedDataParallel
-        dp = FusedDataParallel(model.arena, dist.group.WORLD, dev)
+        from frankentorch_b200.parallel.data_parallel import FusedDataParallel, NcclDataParallel
+        dp = (NcclDataParallel if args.dp_impl == "nccl" else FusedDataParallel)(model.arena, dist.group.WORLD, dev)
     engine = TrainEngine(model, mb, seq, OptimConfig(lr=3e-4, grad_clip=1.0), use_cuda_graph=not args.no_graph, dp=dp)
 
     # synthetic data: tokens uniform over the vocabulary, a fresh pinned batch per step
@@ -232,6 +234,7 @@ def main():
             "vocab": cfg.vocab_size, "params": cfg.param_count(),
             "micro_batch_per_gpu": mb, "global_batch": mb * world, "seq_len": seq,
             "parallelism": f"dp{world}" if world > 1 else "single",
+            "dp_impl": (args.dp_impl if world > 1 else None),
             "optimizer": "AdamW fp32 master + bf16 compute copy, grad clip 1.0",
             "cuda_graph": not args.no_graph,
             "l2": "no flush: one step streams >3 GB of activations, weights and optimizer state (L2 is 126 MB)",

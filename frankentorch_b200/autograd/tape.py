@@ -220,6 +220,9 @@ class TensorTape:
         self.grad_dtype = grad_dtype      # None: keep the dtype the VJP rule produces
         self._next_hook = 0
         self.grad_enabled = True
+        # CPU/f64 sessions keep the reference behaviour (an unreached node sees a zero gradient and
+        # its hooks still run); the GPU training path skips such nodes instead of launching fills.
+        self.materialize_zero_grads = grad_dtype is not None
         self.accumulate_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor] = lambda a, b: a + b
         self.last_plan_cache: Dict[Tuple[int, int], Tuple] = {}
 
@@ -385,7 +388,14 @@ class TensorTape:
             node = nodes[nid]
             incoming = grads.get(nid)
             if incoming is None:
-                if not node.requires_grad:
+                # No gradient reached this node: either it does not require grad, or every rule
+                # that feeds it accumulated in place (bound gradient buffers).  A zero gradient
+                # contributes nothing downstream, so the node is skipped (it still counts in the
+                # execution order, which is a property of the graph alone).
+                if node.is_leaf and node.requires_grad and not node.hooks and node.grad_buffer is not None:
+                    steps.append(TensorBackwardStep(nid, node.value.numel(), "leaf"))
+                    continue
+                if not node.requires_grad or not self.materialize_zero_grads:
                     continue
                 incoming = torch.zeros_like(node.value, dtype=self.grad_dtype or node.value.dtype)
             for _, hook in node.hooks:

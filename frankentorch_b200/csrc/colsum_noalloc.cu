@@ -10,7 +10,7 @@
 
 namespace {
 
-constexpr int kRowsPerBlock = 64;   // same blocking as ftk_colsum_bf16: identical summation order
+constexpr int kRowsPerBlock = 64;   // rows summed by one thread before the cross-block pass
 constexpr int kMaxDevices = 64;
 
 // Scratch for the per-row-block partial sums.  In host code this name is only a stand-in

@@ -45,6 +45,11 @@ typedef struct FtkGemmDesc {
   int accumulate;        // D += result
   int force_bn;          // 0 = heuristic, else 128 or 256
   int max_ctas;          // 0 = all SMs
+  // Deterministic split-K (plain fp32/bf16 store epilogues only): partial tiles go to
+  // `workspace` (fp32, split_count*M*N*4 bytes needed) and are summed in ascending split order.
+  void* workspace;       // NULL disables split-K
+  long long workspace_bytes;
+  int split_k;           // 0 = heuristic, 1 = off, >1 = forced
 } FtkGemmDesc;
 
 int* ftk_status_word(void);               // device pointer (allocated on first use, per device)

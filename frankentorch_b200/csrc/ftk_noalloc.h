@@ -13,9 +13,10 @@
 // fixed array inside the library image instead.
 //
 // What it computes: out[c] (+)= sum over rows r of x[r, c] for a bf16 [rows, cols]
-// matrix with row stride `ld`, in fp32, with the same fixed summation order as
-// ftk_colsum_bf16 (row blocks of 64, then the block partials in ascending order),
-// so both entry points return identical values.
+// matrix with row stride `ld`, in fp32, in a fixed summation order (row blocks of 64
+// summed in ascending row order, then the block partials in ascending order), so a call
+// returns the same bits every time; ftk_colsum_bf16 blocks its rows differently, so the
+// two entry points agree to fp32 rounding, not bit for bit.
 //
 // Limits and rules:
 //   * scratch capacity is FTK_COLSUM_NOALLOC_MAX_FLOATS floats (4 MiB), held by every

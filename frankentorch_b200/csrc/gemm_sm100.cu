@@ -7,12 +7,18 @@
 // ("[K, rows]" row-major), so forward (x W^T), dgrad (dY W) and wgrad (dY^T x) of a
 // Linear layer whose weight is [out, in] (reference: ft-kernel-cpu/src/lib.rs:17162
 // linear_tensor_f64, :17226 linear_backward_f64) run without materialising a
-// transpose.  K is never split, so the result does not depend on the grid size.
+// transpose.
 //
-// One persistent CTA per SM, 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and
-// issues the MMAs, warps 2..5 drain accumulators (each warp reads the TMEM lane
-// quarter warp%4).  Two accumulators let the epilogue of tile i overlap the
-// mainloop of tile i+1.
+// Determinism: within one launch K is reduced in ascending order by one CTA per output
+// tile, so the result does not depend on the grid size.  Weight-gradient shapes (tiny
+// output, very long K) use split-K: each split writes its fp32 partial tile to a
+// workspace and a second kernel adds the partials in ascending split order - a fixed
+// order again, so two runs give identical bits.
+//
+// One persistent CTA per SM, 10 warps: warp 0 issues TMA loads, warp 1 owns TMEM and
+// issues the MMAs, warps 2..9 drain accumulators (warp w reads TMEM lane quarter w%4 and
+// one half of the tile's columns).  Two accumulators let the epilogue of tile i overlap
+// the mainloop of tile i+1.
 #include "ft_sm100.cuh"
 #include "ftk_api.h"
 
@@ -21,7 +27,8 @@ namespace ftk {
 constexpr int G_BM = 128;
 constexpr int G_BK = 64;
 constexpr int G_UMMA_K = 16;
-constexpr int G_THREADS = 192;
+constexpr int G_EPI_WARPS = 8;
+constexpr int G_THREADS = 64 + 32 * G_EPI_WARPS;
 
 struct GemmArgs {
   int M, N, K, L0, L1;
@@ -36,6 +43,8 @@ struct GemmArgs {
   int epi;
   int out_fp32;
   int accumulate;
+  int splits;          // >1: split-K, partial tiles go to `ws` as fp32 [split][M][N]
+  float* ws;
   int* status;
 };
 
@@ -43,20 +52,58 @@ template <int BN>
 struct GemmCfg {
   static constexpr int A_BYTES = G_BM * G_BK * 2;
   static constexpr int B_BYTES = BN * G_BK * 2;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256: powers of two
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+  static constexpr int ACC_STRIDE = (BN == 192) ? 256 : BN;  // TMEM columns between accumulators
+  static constexpr int TMEM_COLS = (BN == 128) ? 256 : 512;  // power of two
   static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ float apply_epi(float v, int epi, float r) {
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Epilogue activations use the hardware tanh (relative error ~2^-11, below bf16 rounding).
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.f + tanh_fast(u));
+}
+__device__ __forceinline__ float gelu_tanh_grad_fast(float x) {
+  const float x2 = x * x;
+  const float t = tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x2));
+  const float du = 0.7978845608028654f * (1.f + 3.f * 0.044715f * x2);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
+}
+
+// v[i] = f(v[i], rr[i]) for the 32 values of one row chunk; the switch is outside the loop.
+__device__ __forceinline__ void apply_epi32(float* v, const float* rr, int epi) {
   switch (epi) {
-    case FTK_EPI_GELU_TANH: return gelu_tanh_f(v);
-    case FTK_EPI_GELU_ERF: return gelu_erf_f(v);
-    case FTK_EPI_MUL_DGELU_TANH: return v * gelu_tanh_grad_f(r);
-    case FTK_EPI_MUL_DGELU_ERF: return v * gelu_erf_grad_f(r);
-    case FTK_EPI_RELU: return v > 0.f ? v : 0.f;
-    case FTK_EPI_MUL_DRELU: return r > 0.f ? v : 0.f;
-    default: return v;
+    case FTK_EPI_GELU_TANH:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
+      break;
+    case FTK_EPI_GELU_ERF:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_erf_f(v[i]);
+      break;
+    case FTK_EPI_RELU:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = v[i] > 0.f ? v[i] : 0.f;
+      break;
+    case FTK_EPI_MUL_DGELU_TANH:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad_fast(rr[i]);
+      break;
+    case FTK_EPI_MUL_DGELU_ERF:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad_f(rr[i]);
+      break;
+    case FTK_EPI_MUL_DRELU:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = rr[i] > 0.f ? v[i] : 0.f;
+      break;
+    default:
+      break;
   }
 }
 
@@ -89,7 +136,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 4);
+      mbar_init(&tempty[i], G_EPI_WARPS);
     }
     *abort_f = 0;
     fence_mbar_init();
@@ -106,8 +153,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
   const int tiles_m = (p.M + G_BM - 1) / G_BM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int tiles_mn = tiles_m * tiles_n;
-  const int total = tiles_mn * p.L0 * p.L1;
-  const int kblocks = (p.K + G_BK - 1) / G_BK;
+  const int nbatch = p.L0 * p.L1;
+  const int total = tiles_mn * nbatch * p.splits;  // work item = (split, batch, n tile, m tile)
+  const int kblocks_all = (p.K + G_BK - 1) / G_BK;
+  const int kb_per_split = (kblocks_all + p.splits - 1) / p.splits;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -118,12 +167,16 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-      const int l = tile / tiles_mn;
-      const int t = tile - l * tiles_mn;
+    for (int item = blockIdx.x; ok && item < total; item += gridDim.x) {
+      const int sp = item / (tiles_mn * nbatch);
+      const int rem = item - sp * (tiles_mn * nbatch);
+      const int l = rem / tiles_mn;
+      const int t = rem - l * tiles_mn;
       const int m_t = t % tiles_m, n_t = t / tiles_m;
       const int l0 = l % p.L0, l1 = l / p.L0;
-      for (int kb = 0; kb < kblocks; ++kb) {
+      const int kb0 = sp * kb_per_split;
+      const int kb1 = min(kblocks_all, kb0 + kb_per_split);
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&empty[s], ph ^ 1u, ctx, FT_ERR_WAIT_EMPTY)) {
           ok = false;
           break;
@@ -166,11 +219,14 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     int acc = 0;
     uint32_t acc_ph = 0;  // bit a = phase of accumulator a
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+    for (int item = blockIdx.x; ok && item < total; item += gridDim.x) {
+      const int sp = item / (tiles_mn * nbatch);
+      const int kb0 = sp * kb_per_split;
+      const int kb1 = min(kblocks_all, kb0 + kb_per_split);
       if (!mbar_wait(&tempty[acc], ((acc_ph >> acc) & 1u) ^ 1u, ctx, FT_ERR_WAIT_TMEM_EMPTY)) break;
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int kb = 0; kb < kblocks; ++kb) {
+      const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&full[s], ph, ctx, FT_ERR_WAIT_FULL)) {
           ok = false;
           break;
@@ -183,10 +239,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
           for (int k = 0; k < G_BK / G_UMMA_K; ++k) {
             umma_bf16(d_tmem, make_smem_desc(a_addr + k * a_adv, a_lbo, 1024),
                       make_smem_desc(b_addr + k * b_adv, b_lbo, 1024), idesc,
-                      (kb | k) != 0 ? 1u : 0u);
+                      (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);
-          if (kb == kblocks - 1) umma_commit(&tfull[acc]);
+          if (kb == kb1 - 1) umma_commit(&tfull[acc]);
         }
         __syncwarp();
         if (++s == Cfg::STAGES) {
@@ -194,20 +250,31 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
           ph ^= 1u;
         }
       }
+      if (kb1 <= kb0 && lane == 0) umma_commit(&tfull[acc]);  // empty split: nothing to wait for
+      __syncwarp();
       acc_ph ^= (1u << acc);
       acc ^= 1;
     }
   } else {
-    // ------------------------------------------------------------ epilogue (4 warps)
-    const int q = warp & 3;
+    // ------------------------------------------------------------ epilogue (8 warps)
+    const int ew = warp - 2;
+    const int q = warp & 3;               // TMEM lane quarter this warp may read
+    const int half = ew >> 2;             // which half of the tile's columns
     const int row_in_tile = q * 32 + lane;
+    constexpr int CHUNKS = BN / 32;
+    constexpr int C_HALF = (CHUNKS + 1) / 2;
+    const int c_begin = half == 0 ? 0 : C_HALF;
+    const int c_end = half == 0 ? C_HALF : CHUNKS;
     int acc = 0;
     uint32_t acc_ph = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-      const int l = tile / tiles_mn;
-      const int t = tile - l * tiles_mn;
+    for (int item = blockIdx.x; item < total; item += gridDim.x) {
+      const int sp = item / (tiles_mn * nbatch);
+      const int rem = item - sp * (tiles_mn * nbatch);
+      const int l = rem / tiles_mn;
+      const int t = rem - l * tiles_mn;
       const int m_t = t % tiles_m, n_t = t / tiles_m;
       const int l0 = l % p.L0, l1 = l / p.L0;
+      const bool empty_split = (sp * kb_per_split >= kblocks_all);
       if (!mbar_wait(&tfull[acc], (acc_ph >> acc) & 1u, ctx, FT_ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const long long row = (long long)m_t * G_BM + row_in_tile;
@@ -215,16 +282,30 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       const long long r_off = l0 * p.r_s0 + l1 * p.r_s1 + row * p.ldr;
       const bool need_r = p.resid != nullptr;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int ci = c_begin; ci < c_end; ++ci) {
+        const int c0 = ci * 32;
         uint32_t r[32];
-        tmem_ld32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld32(tmem_base + acc * Cfg::ACC_STRIDE + c0 + ((uint32_t)(q * 32) << 16), r);
         tmem_ld_wait();
         const int n0 = n_t * BN + c0;
         if (row < p.M && n0 < p.N) {
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          for (int i = 0; i < 32; ++i) v[i] = empty_split ? 0.f : __uint_as_float(r[i]) * p.alpha;
           const bool full_chunk = (n0 + 32 <= p.N);
+          if (p.splits > 1) {
+            // raw partial tile -> workspace [split][batch][M][N] (fp32)
+            float* wp = p.ws + (((long long)sp * nbatch + l) * p.M + row) * p.N + n0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(wp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(wp)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (n0 + i < p.N) wp[i] = v[i];
+            }
+            continue;
+          }
           if (p.bias) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -270,10 +351,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
             for (int i = 0; i < 32; ++i) rr[i] = 0.f;
           }
           const bool r_is_operand = (p.epi >= FTK_EPI_MUL_DGELU_TANH);
-          if (p.epi != FTK_EPI_NONE) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = apply_epi(v[i], p.epi, rr[i]);
-          }
+          if (p.epi != FTK_EPI_NONE) apply_epi32(v, rr, p.epi);
           if (need_r && !r_is_operand) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] += rr[i];
@@ -340,6 +418,42 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+// D (+)= sum over splits (ascending) of ws[split]; 4 outputs per thread.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ D, long long M, long long N,
+                     long long ldd, int splits, int out_fp32, int accumulate) {
+  const long long total4 = (M * N) >> 2;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
+    float4 s = reinterpret_cast<const float4*>(ws)[i];
+    for (int k = 1; k < splits; ++k) {
+      const float4 t = reinterpret_cast<const float4*>(ws + (long long)k * M * N)[i];
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+    const long long e = i << 2;
+    const long long r = e / N, c = e - r * N;
+    if (out_fp32) {
+      float* dp = reinterpret_cast<float*>(D) + r * ldd + c;
+      if (accumulate) {
+        const float4 o = *reinterpret_cast<float4*>(dp);
+        s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+      }
+      *reinterpret_cast<float4*>(dp) = s;
+    } else {
+      __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(D) + r * ldd + c;
+      if (accumulate) {
+        const uint2 o = *reinterpret_cast<uint2*>(dp);
+        const float2 a = unpack_bf16(o.x), b = unpack_bf16(o.y);
+        s.x += a.x; s.y += a.y; s.z += b.x; s.w += b.y;
+      }
+      uint2 o;
+      o.x = pack_bf16(s.x, s.y);
+      o.y = pack_bf16(s.z, s.w);
+      *reinterpret_cast<uint2*>(dp) = o;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -403,8 +517,8 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  long long tiles = (long long)((a.M + G_BM - 1) / G_BM) * ((a.N + BN - 1) / BN) * a.L0 * a.L1;
-  int grid = (int)(tiles < max_ctas ? tiles : max_ctas);
+  long long items = (long long)((a.M + G_BM - 1) / G_BM) * ((a.N + BN - 1) / BN) * a.L0 * a.L1 * a.splits;
+  int grid = (int)(items < max_ctas ? items : max_ctas);
   if (grid <= 0) return 0;
   gemm_bf16_sm100_kernel<BN><<<grid, G_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, a);
   return (int)cudaGetLastError();
@@ -424,18 +538,46 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   if ((L0 > 1 && ((g->a_s0 % 8) || (g->b_s0 % 8))) || (L1 > 1 && ((g->a_s1 % 8) || (g->b_s1 % 8))))
     return -4;
 
-  // pick the N tile that minimises (waves x tile width) on this GPU
   const int sms = g->max_ctas > 0 ? g->max_ctas : num_sms();
-  // A 128x128 tile reads as many shared-memory bytes per MMA cycle as the pipe can supply,
-  // so it costs ~0.86 of a 128x256 tile for half the work (measured); prefer 256 unless the
-  // narrower tile saves whole waves.
-  auto cost = [&](int bn) {
-    long long tiles = (long long)((g->M + G_BM - 1) / G_BM) * ((g->N + bn - 1) / bn) * L0 * L1;
-    long long waves = (tiles + sms - 1) / sms;
-    return (double)waves * (bn == 256 ? 1.0 : 0.86);
+  const long long tiles_m = (g->M + G_BM - 1) / G_BM;
+  // Tile choice: time ~ waves x per-tile cost.  Narrow tiles move more operand bytes per MMA
+  // cycle (measured: a 128-wide tile costs ~0.86 of a 256-wide one for half the work).
+  // Split-K (weight-gradient shapes: few output tiles, long reduction) is considered when the
+  // epilogue is a plain store and the caller supplied a workspace.
+  const int kblocks = (g->K + G_BK - 1) / G_BK;
+  const bool splittable = g->epi == FTK_EPI_NONE && !g->bias && !g->resid && !g->aux && g->workspace &&
+                          (g->N % 4 == 0) && (g->ldd % 4 == 0) && L0 * L1 == 1;
+  auto cost = [&](int bn, int s) {
+    const long long tiles = tiles_m * ((g->N + bn - 1) / bn) * L0 * L1;
+    const long long waves = (tiles * s + sms - 1) / sms;
+    const double w = bn == 256 ? 1.0 : (bn == 192 ? 0.80 : 0.86);
+    return (double)waves * w / s + (s > 1 ? 0.08 + 0.01 * s : 0.0);
   };
-  int bn = g->force_bn ? g->force_bn : (cost(128) < cost(256) ? 128 : 256);
-  if (bn != 128 && bn != 256) return -5;
+  auto split_ok = [&](int s) {
+    if (s == 1) return true;
+    if (!splittable || g->split_k == 1 || kblocks / s < 8) return false;
+    return (long long)s * g->M * g->N * 4 <= g->workspace_bytes;
+  };
+  static const int bn_opts[3] = {256, 192, 128};
+  static const int s_opts[8] = {1, 2, 3, 4, 6, 8, 12, 16};
+  int bn = g->force_bn, splits = 1;
+  double best = 1e30;
+  for (int bi = 0; bi < 3; ++bi) {
+    if (g->force_bn && bn_opts[bi] != g->force_bn) continue;
+    for (int si = 0; si < 8; ++si) {
+      const int s = s_opts[si];
+      if (g->split_k > 1 && s != g->split_k && s != 1) continue;
+      if (!split_ok(s)) continue;
+      const double c = cost(bn_opts[bi], s);
+      if (c < best - 1e-9) {
+        best = c;
+        bn = bn_opts[bi];
+        splits = s;
+      }
+    }
+  }
+  if (g->split_k > 1 && split_ok(g->split_k)) splits = g->split_k;
+  if (bn != 128 && bn != 192 && bn != 256) return -5;
 
   CUtensorMap tmA, tmB;
   int rc;
@@ -459,8 +601,18 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   a.ldr = g->ldr; a.r_s0 = g->r_s0; a.r_s1 = g->r_s1;
   a.aux = reinterpret_cast<__nv_bfloat16*>(g->aux);
   a.alpha = g->alpha; a.epi = g->epi; a.out_fp32 = g->out_fp32; a.accumulate = g->accumulate;
+  a.splits = splits;
+  a.ws = reinterpret_cast<float*>(g->workspace);
   a.status = ftk_status_word();
   if (!a.status) return -6;
-  return bn == 256 ? launch_gemm<256>(tmA, tmB, a, sms, stream)
-                   : launch_gemm<128>(tmA, tmB, a, sms, stream);
+  rc = bn == 256 ? launch_gemm<256>(tmA, tmB, a, sms, stream)
+                 : (bn == 192 ? launch_gemm<192>(tmA, tmB, a, sms, stream)
+                              : launch_gemm<128>(tmA, tmB, a, sms, stream));
+  if (rc || splits == 1) return rc;
+  const long long total4 = ((long long)g->M * g->N) >> 2;
+  long long blocks = (total4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(a.ws, g->D, g->M, g->N, g->ldd, splits,
+                                                            g->out_fp32, g->accumulate);
+  return (int)cudaGetLastError();
 }

@@ -168,53 +168,77 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 
 // Column partials: partial[blk][c] = sum over this block's rows of dy*xhat, and of dy.
 // MODE 0: LayerNorm (two outputs), 1: RMSNorm (dgamma only), 2: plain column sum of dy.
-constexpr int COL_ROWS_PER_BLK = 64;
+// A CTA covers 64 columns x COL_ROWS_PER_BLK rows with 8 row groups of 32 column pairs:
+// each thread sums its rows in ascending order, then thread (group 0) adds the 8 group
+// sums in ascending group order - a fixed tree, independent of scheduling.
+constexpr int COL_ROWS_PER_BLK = 256;
+constexpr int COL_GROUPS = 8;
 template <int MODE>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 col_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                    float* __restrict__ partial, int rows, int cols, long long ld, int nblk) {
-  // thread owns 2 adjacent columns
-  const int c = (blockIdx.x * 128 + threadIdx.x) * 2;
+  __shared__ float sm[4][COL_GROUPS][32];
+  const int cp = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + cp) * 2;
   const int blk = blockIdx.y;
-  if (c >= cols) return;
   const int r0 = blk * COL_ROWS_PER_BLK;
   const int r1 = min(rows, r0 + COL_ROWS_PER_BLK);
   float g0 = 0.f, g1 = 0.f, b0 = 0.f, b1 = 0.f;
-  for (int r = r0; r < r1; ++r) {
-    float2 d = unpack_bf16(*reinterpret_cast<const uint32_t*>(dy + (size_t)r * ld + c));
-    if (MODE == 2) {
-      b0 += d.x; b1 += d.y;
-    } else {
-      float2 xv = unpack_bf16(*reinterpret_cast<const uint32_t*>(x + (size_t)r * ld + c));
-      float mu = MODE == 0 ? mean_in[r] : 0.f;
-      float rs = rstd_in[r];
-      g0 += d.x * (xv.x - mu) * rs;
-      g1 += d.y * (xv.y - mu) * rs;
-      b0 += d.x; b1 += d.y;
+  if (c < cols) {
+    for (int r = r0 + rg; r < r1; r += COL_GROUPS) {
+      float2 d = unpack_bf16(*reinterpret_cast<const uint32_t*>(dy + (size_t)r * ld + c));
+      if (MODE == 2) {
+        b0 += d.x; b1 += d.y;
+      } else {
+        float2 xv = unpack_bf16(*reinterpret_cast<const uint32_t*>(x + (size_t)r * ld + c));
+        float mu = MODE == 0 ? mean_in[r] : 0.f;
+        float rs = rstd_in[r];
+        g0 += d.x * (xv.x - mu) * rs;
+        g1 += d.y * (xv.y - mu) * rs;
+        b0 += d.x; b1 += d.y;
+      }
     }
   }
-  if (MODE == 2) {
-    partial[(size_t)blk * cols + c] = b0;
-    if (c + 1 < cols) partial[(size_t)blk * cols + c + 1] = b1;
-  } else {
-    partial[(size_t)blk * cols + c] = g0;
-    if (c + 1 < cols) partial[(size_t)blk * cols + c + 1] = g1;
-    if (MODE == 0) {
-      float* pb = partial + (size_t)nblk * cols;
-      pb[(size_t)blk * cols + c] = b0;
-      if (c + 1 < cols) pb[(size_t)blk * cols + c + 1] = b1;
+  sm[0][rg][cp] = g0; sm[1][rg][cp] = g1; sm[2][rg][cp] = b0; sm[3][rg][cp] = b1;
+  __syncthreads();
+  if (rg == 0 && c < cols) {
+    float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+#pragma unroll
+    for (int k = 0; k < COL_GROUPS; ++k) {
+      t0 += sm[0][k][cp]; t1 += sm[1][k][cp]; t2 += sm[2][k][cp]; t3 += sm[3][k][cp];
+    }
+    if (MODE == 2) {
+      partial[(size_t)blk * cols + c] = t2;
+      if (c + 1 < cols) partial[(size_t)blk * cols + c + 1] = t3;
+    } else {
+      partial[(size_t)blk * cols + c] = t0;
+      if (c + 1 < cols) partial[(size_t)blk * cols + c + 1] = t1;
+      if (MODE == 0) {
+        float* pb = partial + (size_t)nblk * cols;
+        pb[(size_t)blk * cols + c] = t2;
+        if (c + 1 < cols) pb[(size_t)blk * cols + c + 1] = t3;
+      }
     }
   }
 }
-// Serial (fixed-order) sum over block partials.
-__global__ void col_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols,
-                                 int nblk, int accumulate) {
+// Serial (fixed-order) sum over block partials; `two` reduces a second array (dbeta) in the
+// same launch.
+__global__ void __launch_bounds__(128)
+col_final_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                 const float* __restrict__ partial2, float* __restrict__ out2, int cols, int nblk,
+                 int accumulate) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
-  float s = 0.f;
+  float s = 0.f, t = 0.f;
+#pragma unroll 8
   for (int b = 0; b < nblk; ++b) s += partial[(size_t)b * cols + c];
   out[c] = accumulate ? out[c] + s : s;
+  if (partial2) {
+#pragma unroll 8
+    for (int b = 0; b < nblk; ++b) t += partial2[(size_t)b * cols + c];
+    out2[c] = accumulate ? out2[c] + t : t;
+  }
 }
 
 // ----------------------------------------------------------------------------- softmax
@@ -424,11 +448,10 @@ extern "C" int ftk_layernorm_bwd(const void* dy, const void* x, const void* gamm
       BF(dy), BF(x), BF(gamma), mean, rstd, BF(dx_add), BFW(dx), rows, cols);
   if (dgamma) {
     const int nblk = ftk_layernorm_bwd_blocks(rows);
-    dim3 g((cols / 2 + 127) / 128, nblk);
-    col_partial_kernel<0><<<g, 128, 0, s>>>(BF(dy), BF(x), mean, rstd, partial, rows, cols, cols, nblk);
-    col_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, dgamma, cols, nblk, accumulate);
-    col_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial + (size_t)nblk * cols, dbeta, cols,
-                                                         nblk, accumulate);
+    dim3 g((cols / 2 + 31) / 32, nblk);
+    col_partial_kernel<0><<<g, 256, 0, s>>>(BF(dy), BF(x), mean, rstd, partial, rows, cols, cols, nblk);
+    col_final_kernel<<<(cols + 127) / 128, 128, 0, s>>>(partial, dgamma, partial + (size_t)nblk * cols,
+                                                         dbeta, cols, nblk, accumulate);
   }
   return (int)cudaGetLastError();
 }
@@ -441,9 +464,10 @@ extern "C" int ftk_rmsnorm_bwd(const void* dy, const void* x, const void* gamma,
       BF(dy), BF(x), BF(gamma), nullptr, rstd, nullptr, BFW(dx), rows, cols);
   if (dgamma) {
     const int nblk = ftk_layernorm_bwd_blocks(rows);
-    dim3 g((cols / 2 + 127) / 128, nblk);
-    col_partial_kernel<1><<<g, 128, 0, s>>>(BF(dy), BF(x), nullptr, rstd, partial, rows, cols, cols, nblk);
-    col_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, dgamma, cols, nblk, accumulate);
+    dim3 g((cols / 2 + 31) / 32, nblk);
+    col_partial_kernel<1><<<g, 256, 0, s>>>(BF(dy), BF(x), nullptr, rstd, partial, rows, cols, cols, nblk);
+    col_final_kernel<<<(cols + 127) / 128, 128, 0, s>>>(partial, dgamma, nullptr, nullptr, cols, nblk,
+                                                         accumulate);
   }
   return (int)cudaGetLastError();
 }
@@ -452,9 +476,9 @@ extern "C" int ftk_colsum_bf16(const void* x, float* out, float* partial, int ro
   if (cols % 2 || ld % 2 || rows <= 0) return -2;
   cudaStream_t s = STREAM(stream);
   const int nblk = ftk_colsum_blocks(rows);
-  dim3 g((cols / 2 + 127) / 128, nblk);
-  col_partial_kernel<2><<<g, 128, 0, s>>>(BF(x), nullptr, nullptr, nullptr, partial, rows, cols, ld, nblk);
-  col_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(partial, out, cols, nblk, accumulate);
+  dim3 g((cols / 2 + 31) / 32, nblk);
+  col_partial_kernel<2><<<g, 256, 0, s>>>(BF(x), nullptr, nullptr, nullptr, partial, rows, cols, ld, nblk);
+  col_final_kernel<<<(cols + 127) / 128, 128, 0, s>>>(partial, out, nullptr, nullptr, cols, nblk, accumulate);
   return (int)cudaGetLastError();
 }
 

@@ -58,11 +58,16 @@ class GPTConfig:
 
 
 class ParamArena:
-    """Flat parameter storage: bf16 compute copy + fp32 master/grad/moments, 256-byte aligned slots."""
+    """Flat parameter storage: bf16 compute copy + fp32 master/grad/moments, 256-byte aligned slots.
+
+    With a process ``group`` the gradient and parameter arenas are allocated in peer-visible
+    (symmetric) memory so the multi-GPU kernels can read / write them over NVLink, and the total
+    length is padded so it splits into equal float4-aligned shards.
+    """
 
     ALIGN = 128  # elements
 
-    def __init__(self, specs: List[Tuple[str, Tuple[int, ...]]], device, *, with_optimizer_state: bool = True):
+    def __init__(self, specs: List[Tuple[str, Tuple[int, ...]]], device, *, group=None, pad_multiple: int = 1024):
         self.specs = specs
         self.offsets: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
         off = 0
@@ -70,12 +75,21 @@ class ParamArena:
             n = int(math.prod(shape))
             self.offsets[name] = (off, tuple(shape))
             off += (n + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        off = (off + pad_multiple - 1) // pad_multiple * pad_multiple
         self.numel = off
-        self.params = torch.zeros(off, dtype=torch.bfloat16, device=device)
+        self.symmetric = group is not None
+        if self.symmetric:
+            from ..parallel.symm import SymmetricBuffer
+            self.params_buf = SymmetricBuffer(off * 2, group, device)
+            self.grads_buf = SymmetricBuffer(off * 4, group, device)
+            self.params = self.params_buf.tensor(torch.bfloat16, off)
+            self.grads = self.grads_buf.tensor(torch.float32, off)
+        else:
+            self.params = torch.zeros(off, dtype=torch.bfloat16, device=device)
+            self.grads = torch.zeros(off, dtype=torch.float32, device=device)
         self.master = torch.zeros(off, dtype=torch.float32, device=device)
-        self.grads = torch.zeros(off, dtype=torch.float32, device=device)
-        self.m = torch.zeros(off, dtype=torch.float32, device=device) if with_optimizer_state else None
-        self.v = torch.zeros(off, dtype=torch.float32, device=device) if with_optimizer_state else None
+        self.m = torch.zeros(off, dtype=torch.float32, device=device)
+        self.v = torch.zeros(off, dtype=torch.float32, device=device)
 
     def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
         off, shape = self.offsets[name]
@@ -84,11 +98,15 @@ class ParamArena:
     def sync_shadow(self) -> None:
         self.params.copy_(self.master)
 
+    def drop_full_optimizer_state(self) -> None:
+        """Called by a sharded optimizer that now owns its slice of master / m / v."""
+        self.master = self.m = self.v = None
+
 
 class GPT:
     """GPT-2 style decoder; ``forward`` records the step on a :class:`TensorTape`."""
 
-    def __init__(self, cfg: GPTConfig, tape: TensorTape, device="cuda", seed: int = 1234):
+    def __init__(self, cfg: GPTConfig, tape: TensorTape, device="cuda", seed: int = 1234, *, group=None):
         self.cfg = cfg
         self.tape = tape
         self.device = torch.device(device)
@@ -107,7 +125,11 @@ class GPT:
         specs += [("ln_f.weight", (d,)), ("ln_f.bias", (d,))]
         if not cfg.tie_lm_head:
             specs.append(("lm_head.weight", (Vp, d)))
-        self.arena = ParamArena(specs, self.device)
+        world = 1
+        if group is not None:
+            import torch.distributed as dist
+            world = dist.get_world_size(group)
+        self.arena = ParamArena(specs, self.device, group=group, pad_multiple=1024 * world)
         self._init_weights(seed)
         # parameters are the lowest-index leaves of the tape; the per-step graph is truncated above
         self.leaf: Dict[str, int] = {}

@@ -30,6 +30,7 @@ class FtkGemmDesc(C.Structure):
         ("aux", C.c_void_p),
         ("alpha", C.c_float), ("epi", C.c_int), ("out_fp32", C.c_int), ("accumulate", C.c_int),
         ("force_bn", C.c_int), ("max_ctas", C.c_int),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_longlong), ("split_k", C.c_int),
     ]
 
 

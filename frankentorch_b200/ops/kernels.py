@@ -75,7 +75,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          bias: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
          aux: Optional[torch.Tensor] = None, epi: int = EPI_NONE, alpha: float = 1.0,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-         accumulate: bool = False, force_bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         accumulate: bool = False, force_bn: int = 0, max_ctas: int = 0, split_k: int = 0) -> torch.Tensor:
     """``D = epi(alpha * A @ B^T + bias) (+ resid) (+ D)`` on the tcgen05 GEMM.
 
     ``a`` is ``[M, K]`` (``a_mn=False``) or ``[K, M]`` (``a_mn=True``); ``b`` is
@@ -112,8 +112,26 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError("gemm output must be bf16 or fp32")
     g.accumulate, g.force_bn, g.max_ctas = int(accumulate), int(force_bn), int(max_ctas)
+    g.split_k = int(split_k)
+    if split_k != 1 and bias is None and resid is None and aux is None and epi == EPI_NONE:
+        ws = _gemm_workspace(a.device)
+        g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel() * 4
     _chk(_lib.load().ftk_gemm_bf16(C.byref(g), _stream()), "ftk_gemm_bf16")
     return out
+
+
+_WORKSPACES = {}
+GEMM_WORKSPACE_BYTES = 64 << 20
+
+
+def _gemm_workspace(device) -> torch.Tensor:
+    """Per-device fp32 scratch for split-K partial tiles (allocated once, outside any capture)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = torch.empty(GEMM_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        _WORKSPACES[key] = ws
+    return ws
 
 
 def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int, K: int,

@@ -50,7 +50,8 @@ class TrainEngine:
         self.step_dev = torch.zeros((), dtype=torch.int64, device=dev)
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.use_graph = use_cuda_graph
+        # library collectives (the NCCL baseline path) stay out of graph capture
+        self.use_graph = use_cuda_graph and not getattr(dp, "eager_only", False)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = 0
         self.last_report = None
@@ -61,7 +62,7 @@ class TrainEngine:
         o, a = self.opt, self.model.arena
         K.adamw_tick(self.step_dev, self.hyper, o.beta1, o.beta2)
         if self.dp is not None:
-            self.dp.reduce_and_update(a, self.hyper, o, self.sumsq, self.grad_norm)
+            self.dp.reduce_and_update(a, self.hyper, o, self.sumsq, self.grad_norm, self.step_dev)
             return
         if o.grad_clip is not None:
             K.sumsq(a.grads, out=self.sumsq)
@@ -85,7 +86,9 @@ class TrainEngine:
         # one eager step on a side stream initialises lazy state (function attributes, status
         # word, driver entry points) outside of capture; its weight update is undone below
         a = self.model.arena
-        snap = (a.master.clone(), a.m.clone(), a.v.clone(), self.step_dev.clone(), self.hyper.clone())
+        own = self.dp if (self.dp is not None and a.master is None) else a   # who holds master/m/v
+        snap = (own.master.clone(), own.m.clone(), own.v.clone(), self.step_dev.clone(), self.hyper.clone(),
+                a.params.clone())
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -93,9 +96,10 @@ class TrainEngine:
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         K.check_status()
-        a.master.copy_(snap[0]); a.m.copy_(snap[1]); a.v.copy_(snap[2])
-        self.step_dev.copy_(snap[3]); self.hyper.copy_(snap[4])
-        a.sync_shadow()
+        own.master.copy_(snap[0]); own.m.copy_(snap[1]); own.v.copy_(snap[2])
+        self.hyper.copy_(snap[4])
+        a.params.copy_(snap[5])
+        self.step_dev.copy_(snap[3])   # (the multi-GPU path keeps its own, never-rewinding sequence)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._step_body()

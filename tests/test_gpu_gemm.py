@@ -101,10 +101,32 @@ def test_gemm_deterministic(cuda_device):
     k = _ops()
     a = _rand((2048, 1024), cuda_device, seed=13)
     b = _rand((1536, 1024), cuda_device, seed=14)
-    o1 = k.gemm(a, b)
-    o2 = k.gemm(a, b, max_ctas=37)   # different grid, same bits: K is never split
+    o1 = k.gemm(a, b, force_bn=256)
+    o2 = k.gemm(a, b, force_bn=256, max_ctas=37)   # different grid, same bits: one CTA reduces all of K
     k.check_status()
     assert torch.equal(o1, o2)
+    # run-to-run: the default configuration (whatever tile/split it picks) replays bit for bit
+    assert torch.equal(k.gemm(a, b), k.gemm(a, b))
+
+
+def test_gemm_split_k_deterministic_and_correct(cuda_device):
+    k = _ops()
+    # weight-gradient shape: small output, long reduction -> split-K with fixed-order reduce
+    M, N, Kd = 768, 768, 8192
+    dy = _rand((Kd, M), cuda_device, 0.5, 21)
+    x = _rand((Kd, N), cuda_device, 0.5, 22)
+    ref = dy.float().t() @ x.float()
+    outs = []
+    for split in (0, 1, 4, 6):
+        o = k.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=split)
+        _check(o, ref, 5e-3, f"split_k={split}")
+        outs.append(o)
+    again = k.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=6)
+    assert torch.equal(outs[3], again)
+    acc = torch.ones((M, N), dtype=torch.float32, device=cuda_device)
+    k.gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True, split_k=4)
+    _check(acc, ref + 1.0, 5e-3, "split-k accumulate")
+    k.check_status()
 
 
 def test_gemm_batched(cuda_device):

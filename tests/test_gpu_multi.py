@@ -1,0 +1,27 @@
+"""Multi-GPU paths (run as child processes, one rank per GPU; skipped with fewer than 2 GPUs)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run_workers(script, nproc, port, timeout=300):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, script)]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+def test_fused_data_parallel_matches_nccl_and_replays(cuda_device):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    nproc = 2 if n < 4 else 4
+    p = _run_workers("_dp_worker.py", nproc, 29631)
+    assert p.returncode == 0 and "DP_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
