@@ -1,0 +1,350 @@
+"""Operator surface of ``FrankenTorchSession`` (installed onto the class by ``install``).
+
+The tensor operators are generated from the VJP rule table: ``tensor_<op>(ids..., **params)``
+runs the forward, records a dispatch decision in the ledger and appends a tape node whose
+backward is the table's rule.  On the CUDA device the hot operators route to the fused
+sm_100a kernels instead (``ops/fused.py``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Callable, List, Optional, Sequence, Tuple
+
+import torch
+
+from .autograd.functions import OPS, OpDef
+from .autograd.tape import BackwardOptions, BorrowedInputVersionMismatch, TensorBackwardReport, TensorHookHandle
+from .core.dtype import DType
+from .runtime.ledger import EvidenceKind
+
+_INDEX_INPUT_OPS = {"index_select": (1,), "gather": (1,), "scatter": (1,), "scatter_add": (1,), "masked_fill": (1,),
+                    "where": (0,), "embedding": (1,), "cross_entropy": (1,), "nll_loss": (1,), "multi_margin_loss": (1,),
+                    "embedding_bag": (1, 2), "index_put": (1,), "masked_select": (1,), "ctc_loss": (1, 2, 3)}
+_MATMUL_CLASS = {"matmul", "bmm", "linear", "addmm", "mv", "baddbmm", "addbmm", "conv1d", "conv2d", "conv3d", "sdpa"}
+
+
+def _apply(self, name: str, inputs: Sequence[int], **kw) -> int:
+    """Run operator ``name`` on tape nodes ``inputs``; returns the id of the result node."""
+    op: OpDef = OPS[name]
+    tape = self.tensor_tape
+    vals = [tape.value(i) for i in inputs]
+    idx_pos = _INDEX_INPUT_OPS.get(name, ())
+    for p in idx_pos:   # float-valued index tensors are accepted (reference convention)
+        if p < len(vals) and vals[p].is_floating_point() and name not in ("where", "masked_fill", "masked_select"):
+            vals[p] = vals[p].long()
+    cast_back = None
+    if self._autocast is not None and name in _MATMUL_CLASS:
+        cast_back = vals[0].dtype
+        vals = [v.to(self._autocast.to_torch()) if v.is_floating_point() else v for v in vals]
+    rg = tape.grad_enabled and any(tape.nodes[i].requires_grad for i in inputs)
+    self._record_dispatch(name, rg)
+    out = op.fwd(*vals, **kw)
+    if cast_back is not None:
+        out = out.to(cast_back)
+    vjp = None
+    if rg and op.vjp is not None:
+        gdt = tape.grad_dtype
+        saved_vals = vals
+
+        def vjp(g, targets, _op=op, _vals=saved_vals, _out=out, _kw=kw, _gdt=gdt):
+            if _gdt is not None:
+                ins = [v.to(_gdt) if v.is_floating_point() else v for v in _vals]
+                o = _out.to(_gdt) if _out.is_floating_point() else _out
+            else:
+                ins, o = _vals, _out
+            return list(_op.vjp(g, ins, o, _kw))
+    return tape.record(name, list(inputs), out, vjp, op.rule)
+
+
+_BUILTIN_BINARY = {"max", "min", "atan2", "fmod", "remainder", "pow_tensor", "matmul", "bmm", "dot", "outer", "kron",
+                   "inner", "mv", "linalg_solve", "special_xlogy"}
+
+
+def _params(name: str):
+    """Parameters of the forward, or None for builtins that expose no signature."""
+    import inspect
+    try:
+        return list(inspect.signature(OPS[name].fwd).parameters.values())
+    except (ValueError, TypeError):
+        return None
+
+
+def _make_op_method(name: str, n_tensor_args: Optional[int]):
+    allp = _params(name)
+    ps = [] if allp is None else [p for p in allp if p.kind != p.VAR_POSITIONAL]
+    extra_names = [p.name for p in (ps if n_tensor_args is None else ps[n_tensor_args:])]
+
+    def method(self, *args, **kw):
+        if n_tensor_args is None:      # variadic: the first positional is a list of ids
+            ids, rest = list(args[0]), args[1:]
+        else:
+            ids, rest = [a for a in args[:n_tensor_args] if a is not None], args[n_tensor_args:]
+        for pname, v in zip(extra_names, rest):   # positional parameters follow the forward's order
+            kw.setdefault(pname, v)
+        return _apply(self, name, ids, **kw)
+    method.__name__ = "tensor_" + name
+    method.__doc__ = f"``{name}`` on tape nodes; backward rule: {OPS[name].rule}"
+    return method
+
+
+def _tensor_arity(name: str) -> Optional[int]:
+    import inspect
+    ps = _params(name)
+    if ps is None:
+        return 2 if name in _BUILTIN_BINARY else 1
+    if any(p.kind == p.VAR_POSITIONAL for p in ps):
+        return None
+    # tensor arguments = leading parameters without a default, plus optional tensor slots named w/b/bias/mask
+    n = 0
+    for p in ps:
+        if p.default is inspect.Parameter.empty or p.name in ("w", "b", "bias", "mask"):
+            n += 1
+        else:
+            break
+    return n
+
+
+# ------------------------------------------------------------------------------------ autograd API
+def tensor_backward(self, root: int) -> TensorBackwardReport:
+    return self.tensor_backward_with_options(root, BackwardOptions.for_mode(self.runtime.mode))
+
+
+def tensor_backward_with_options(self, root: int, options: BackwardOptions) -> TensorBackwardReport:
+    rep = self.tensor_tape.backward(root, options)
+    t = rep.telemetry
+    self.runtime.ledger.record(
+        EvidenceKind.Backward,
+        f"tensor backward root={root} steps={len(rep.steps)} queue_pushes={t.queue_pushes} queue_pops={t.queue_pops} "
+        f"max_queue_len={t.max_queue_len} reentrant_depth={t.reentrant_depth} "
+        f"reentrant_guard_triggered={str(t.reentrant_guard_triggered).lower()} "
+        f"hardened_fallback_used={str(t.hardened_fallback_used).lower()}")
+    return rep
+
+
+def tensor_gradient(self, report: TensorBackwardReport, nid: int):
+    g = report.gradient(nid)
+    return None if g is None else g.detach().to("cpu", torch.float64).reshape(-1).tolist()
+
+
+def tensor_grad(self, nid: int):
+    return self.tensor_accumulated_gradient(nid)
+
+
+def tensor_accumulated_gradient(self, nid: int):
+    g = self.tensor_tape.accumulated_gradient(nid)
+    return None if g is None else g.detach().to("cpu", torch.float64).reshape(-1).tolist()
+
+
+def tensor_accumulated_gradient_tensor(self, nid: int) -> Optional[torch.Tensor]:
+    return self.tensor_tape.accumulated_gradient(nid)
+
+
+def tensor_accumulated_gradient_len(self, nid: int) -> Optional[int]:
+    g = self.tensor_tape.accumulated_gradient(nid)
+    return None if g is None else g.numel()
+
+
+def tensor_set_accumulated_gradient(self, nid: int, values) -> None:
+    ref = self.tensor(nid)
+    gdt = self.tensor_tape.grad_dtype or ref.dtype
+    g = values if isinstance(values, torch.Tensor) else torch.tensor(list(values), dtype=torch.float64)
+    self.tensor_tape.set_accumulated_gradient(nid, g.reshape(ref.shape).to(device=ref.device, dtype=gdt))
+
+
+def tensor_zero_grad(self, nid: int) -> None:
+    self.tensor_tape.zero_accumulated_gradient(nid)
+
+
+def tensor_zero_grads(self, ids: Sequence[int]) -> None:
+    for i in ids:
+        self.tensor_tape.zero_accumulated_gradient(i)
+
+
+def tensor_retain_grad(self, nid: int) -> None:
+    self.tensor_tape.retain_grad(nid)
+
+
+def tensor_autograd_grad(self, outputs: int, inputs: Sequence[int], retain_graph: bool = True):
+    """Gradients of ``outputs`` w.r.t. ``inputs`` without touching the accumulated ``.grad`` slots."""
+    tape = self.tensor_tape
+    saved = {i: (tape.nodes[i].grad, tape.nodes[i].grad_buffer_filled) for i in range(len(tape.nodes))}
+    opts = BackwardOptions.for_mode(self.runtime.mode)
+    opts.retain_graph = retain_graph
+    rep = tape.backward(outputs, opts)
+    for i, (g, f) in saved.items():
+        tape.nodes[i].grad, tape.nodes[i].grad_buffer_filled = g, f
+    return [rep.gradient(i) for i in inputs]
+
+
+def tensor_functional_hessian(self, fn: Callable[[torch.Tensor], torch.Tensor], x: int) -> torch.Tensor:
+    """Dense Hessian of a scalar function of one tensor by central differences of its DAC gradient."""
+    x0 = self.tensor(x).detach().to(torch.float64)
+    n = x0.numel()
+
+    def grad_at(v):
+        leaf = self.tensor_tape.leaf(v.reshape(x0.shape).to(self.tensor(x).dtype), True)
+        mark = len(self.tensor_tape)
+        out = fn(self, leaf)
+        g = self.tensor_autograd_grad(out, [leaf])[0].reshape(-1).to(torch.float64).clone()
+        return g
+
+    H = torch.zeros(n, n, dtype=torch.float64)
+    eps = 1e-5
+    flat = x0.reshape(-1)
+    for j in range(n):
+        e = torch.zeros(n, dtype=torch.float64)
+        e[j] = eps
+        H[:, j] = (grad_at(flat + e) - grad_at(flat - e)) / (2 * eps)
+    return 0.5 * (H + H.t())
+
+
+def truncate_autograd_graph(self, boundary: int) -> None:
+    self.tensor_tape.truncate_graph_to(boundary)
+
+
+def autograd_graph_len(self) -> int:
+    return len(self.tensor_tape)
+
+
+def register_tensor_hook(self, nid: int, fn) -> TensorHookHandle:
+    return self.tensor_tape.register_tensor_hook(nid, fn)
+
+
+def remove_tensor_hook(self, handle: TensorHookHandle) -> bool:
+    return self.tensor_tape.remove_tensor_hook(handle)
+
+
+def tensor_apply_function(self, inputs: Sequence[int], forward_fn, backward_fn, borrow_inputs: bool = False) -> int:
+    """Custom autograd function (ft-autograd/src/lib.rs:8761).
+
+    ``forward_fn(ctx, tensors) -> tensor``; ``backward_fn(ctx, grad_out) -> list of grads or None``.
+    With ``borrow_inputs`` the live inputs are re-read in backward and their version counters
+    are checked (``BorrowedInputVersionMismatch`` if one was mutated in place).
+    """
+    from .session import FunctionCtx
+    tape = self.tensor_tape
+    vals = [tape.value(i) for i in inputs]
+    ctx = FunctionCtx([tape.nodes[i].requires_grad for i in inputs])
+    out = forward_fn(ctx, vals)
+    versions = [tape.version(i) for i in inputs]
+    self._record_dispatch("custom_function", any(ctx.needs_input_grad), "custom_function")
+
+    def vjp(g, targets):
+        if borrow_inputs:
+            for i, rec in zip(inputs, versions):
+                if tape.version(i) != rec:
+                    raise BorrowedInputVersionMismatch(i, rec, tape.version(i))
+        res = backward_fn(ctx, g)
+        return list(res)
+
+    return tape.record("custom_function", list(inputs), out, vjp, "custom autograd function backward")
+
+
+def checkpoint(self, fn: Callable, inputs: Sequence[int]) -> int:
+    """Recompute-on-backward: run ``fn(session, *ids)`` without recording, replay it in backward."""
+    tape = self.tensor_tape
+    self.no_grad_enter()
+    try:
+        out_id = fn(self, *inputs)
+        out = tape.value(out_id).detach()
+    finally:
+        self.no_grad_exit()
+    tape.truncate_graph_to(out_id) if out_id == len(tape) - 1 and False else None
+    vals = [tape.value(i) for i in inputs]
+
+    def vjp(g, targets):
+        # rebuild the sub-graph on fresh leaves, run a nested deterministic backward
+        mark = len(tape)
+        leaves = [tape.leaf(v.detach(), tape.nodes[i].requires_grad) for v, i in zip(vals, inputs)]
+        prev, tape.grad_enabled = tape.grad_enabled, True
+        try:
+            o = fn(self, *leaves)
+            opts = BackwardOptions(retain_graph=True)
+            rep = tape.backward(o, opts, seed=g.to(tape.grad_dtype or g.dtype))
+        finally:
+            tape.grad_enabled = prev
+        grads = [rep.gradient(l) for l in leaves]
+        for l in leaves:
+            tape.nodes[l].grad = None
+        return grads
+
+    return tape.record("checkpoint", list(inputs), out, vjp, "checkpoint: recompute forward, then backward")
+
+
+# ------------------------------------------------------------------------------------ in-place / param update
+def _inplace(self, nid: int, fn) -> int:
+    t = self.tensor(nid)
+    node = self.tensor_tape.nodes[nid]
+    if node.requires_grad and self.tensor_tape.grad_enabled and node.is_leaf:
+        raise RuntimeError("a leaf that requires grad cannot be modified in place while grad mode is on")
+    fn(t)
+    self.tensor_tape.bump_version(nid)
+    return nid
+
+
+def tensor_add_(self, a: int, b: int) -> int:
+    return _inplace(self, a, lambda t: t.add_(self.tensor(b)))
+
+
+def tensor_sub_(self, a: int, b: int) -> int:
+    return _inplace(self, a, lambda t: t.sub_(self.tensor(b)))
+
+
+def tensor_mul_(self, a: int, b: int) -> int:
+    return _inplace(self, a, lambda t: t.mul_(self.tensor(b)))
+
+
+def tensor_div_(self, a: int, b: int) -> int:
+    return _inplace(self, a, lambda t: t.div_(self.tensor(b)))
+
+
+def tensor_neg_(self, a: int) -> int:
+    return _inplace(self, a, lambda t: t.neg_())
+
+
+def tensor_zero_(self, a: int) -> int:
+    return _inplace(self, a, lambda t: t.zero_())
+
+
+def tensor_fill_(self, a: int, value: float) -> int:
+    return _inplace(self, a, lambda t: t.fill_(value))
+
+
+def tensor_clamp_(self, a: int, lo=None, hi=None) -> int:
+    return _inplace(self, a, lambda t: t.clamp_(lo, hi))
+
+
+def tensor_update_param_values(self, nid: int, values) -> None:
+    t = self.tensor(nid)
+    new = values if isinstance(values, torch.Tensor) else torch.tensor(list(values), dtype=torch.float64)
+    t.copy_(new.reshape(t.shape).to(t.dtype))
+    self.tensor_tape.bump_version(nid)
+
+
+def tensor_update_param_values_f64_with(self, nid: int, fn: Callable[[torch.Tensor], None]) -> None:
+    fn(self.tensor(nid))
+    self.tensor_tape.bump_version(nid)
+
+
+def tensor_update_param_values_f64_with_accumulated_gradient(self, nid: int, fn) -> bool:
+    g = self.tensor_tape.accumulated_gradient(nid)
+    if g is None:
+        return False
+    fn(g, self.tensor(nid))
+    self.tensor_tape.bump_version(nid)
+    return True
+
+
+def install(cls) -> None:
+    for name in list(OPS):
+        setattr(cls, "tensor_" + name, _make_op_method(name, _tensor_arity(name)))
+    for fn in (tensor_backward, tensor_backward_with_options, tensor_gradient, tensor_grad, tensor_accumulated_gradient,
+               tensor_accumulated_gradient_tensor, tensor_accumulated_gradient_len, tensor_set_accumulated_gradient,
+               tensor_zero_grad, tensor_zero_grads, tensor_retain_grad, tensor_autograd_grad, tensor_functional_hessian,
+               truncate_autograd_graph, autograd_graph_len, register_tensor_hook, remove_tensor_hook,
+               tensor_apply_function, checkpoint, tensor_add_, tensor_sub_, tensor_mul_, tensor_div_, tensor_neg_,
+               tensor_zero_, tensor_fill_, tensor_clamp_, tensor_update_param_values, tensor_update_param_values_f64_with,
+               tensor_update_param_values_f64_with_accumulated_gradient):
+        setattr(cls, fn.__name__, fn)
+    cls._apply = _apply
+    cls.zero_grads_tensor = tensor_zero_grads
