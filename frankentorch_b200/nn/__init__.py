@@ -1,0 +1,11 @@
+"""``frankentorch_b200.nn``: module system and layers on the DAC tape (mirror of ft-nn)."""
+from .layers import *  # noqa: F401,F403
+from .layers import _param  # noqa: F401
+from .module import (LoadStateDictReport, Module, ModuleDict, ModuleError, ModuleList, ParameterDict, ParameterList,
+                     Sequential, StateDict, clip_grad_norm_, clip_grad_value_, module_load_state_dict,
+                     module_state_dict, named_buffers, named_modules, named_parameters, parameters_to_vector,
+                     vector_to_parameters)
+from .transformer import *  # noqa: F401,F403
+from .utils import (MinMaxObserver, PackedSequence, QParams, QuantizedLinear, SpectralNorm, WeightNorm, dequantize,
+                    pack_padded_sequence, pack_sequence, pad_packed_sequence, pad_sequence, quantize_per_tensor,
+                    spectral_norm, weight_norm)
