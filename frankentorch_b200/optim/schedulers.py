@@ -1,0 +1,330 @@
+"""Learning-rate schedulers and the AMP gradient scaler.
+
+Reference: ft-optim/src/lib.rs - ``LRScheduler`` trait :2315-2342 (``step(optimizer, metric)``,
+``get_last_lr``, ``state``/``load_state``), ``SchedulerState{last_epoch,last_lrs,extra}`` :2301,
+the fifteen schedulers :2351-4471, ``GradScaler`` :6093-6264 (init scale 65536, growth 2.0,
+backoff 0.5, growth interval 2000; inf/nan check over the accumulated gradients -> skip the
+step and back off, else unscale in place and step).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class SchedulerState:
+    last_epoch: int = 0
+    last_lrs: List[float] = field(default_factory=list)
+    extra: Dict[str, float] = field(default_factory=dict)
+
+
+class LRScheduler:
+    def __init__(self, optimizer):
+        self.base_lr = optimizer.get_lr()
+        self.last_epoch = 0
+        self.last_lr = self.base_lr
+
+    def _lr_at(self, epoch: int) -> float:
+        raise NotImplementedError
+
+    def step(self, optimizer, metric: Optional[float] = None) -> float:
+        self.last_epoch += 1
+        self.last_lr = self._lr_at(self.last_epoch)
+        optimizer.set_lr(self.last_lr)
+        return self.last_lr
+
+    def get_last_lr(self) -> List[float]:
+        return [self.last_lr]
+
+    def state(self) -> SchedulerState:
+        return SchedulerState(self.last_epoch, [self.last_lr], {"base_lr": self.base_lr})
+
+    def load_state(self, st: SchedulerState) -> None:
+        self.last_epoch = int(st.last_epoch)
+        self.last_lr = st.last_lrs[0] if st.last_lrs else self.base_lr
+        self.base_lr = st.extra.get("base_lr", self.base_lr)
+
+
+class StepLR(LRScheduler):
+    def __init__(self, optimizer, step_size: int, gamma: float = 0.1):
+        super().__init__(optimizer)
+        if step_size <= 0:
+            raise ValueError("step_size must be positive")
+        self.step_size, self.gamma = step_size, gamma
+
+    def _lr_at(self, e):
+        return self.base_lr * self.gamma ** (e // self.step_size)
+
+
+class MultiStepLR(LRScheduler):
+    def __init__(self, optimizer, milestones: Sequence[int], gamma: float = 0.1):
+        super().__init__(optimizer)
+        self.milestones, self.gamma = sorted(milestones), gamma
+
+    def _lr_at(self, e):
+        return self.base_lr * self.gamma ** sum(1 for m in self.milestones if m <= e)
+
+
+class ConstantLR(LRScheduler):
+    def __init__(self, optimizer, factor: float = 1.0 / 3, total_iters: int = 5):
+        super().__init__(optimizer)
+        self.factor, self.total = factor, total_iters
+        optimizer.set_lr(self.base_lr * factor)
+        self.last_lr = self.base_lr * factor
+
+    def _lr_at(self, e):
+        return self.base_lr * (self.factor if e < self.total else 1.0)
+
+
+class LinearLR(LRScheduler):
+    def __init__(self, optimizer, start_factor: float = 1.0 / 3, end_factor: float = 1.0, total_iters: int = 5):
+        super().__init__(optimizer)
+        self.sf, self.ef, self.total = start_factor, end_factor, total_iters
+        optimizer.set_lr(self.base_lr * start_factor)
+        self.last_lr = self.base_lr * start_factor
+
+    def _lr_at(self, e):
+        f = self.sf + (self.ef - self.sf) * min(e, self.total) / self.total
+        return self.base_lr * f
+
+
+class ExponentialLR(LRScheduler):
+    def __init__(self, optimizer, gamma: float):
+        super().__init__(optimizer)
+        self.gamma = gamma
+
+    def _lr_at(self, e):
+        return self.base_lr * self.gamma ** e
+
+
+class PolynomialLR(LRScheduler):
+    def __init__(self, optimizer, total_iters: int = 5, power: float = 1.0):
+        super().__init__(optimizer)
+        self.total, self.power = total_iters, power
+
+    def _lr_at(self, e):
+        return self.base_lr * (1 - min(e, self.total) / self.total) ** self.power
+
+
+class CosineAnnealingLR(LRScheduler):
+    def __init__(self, optimizer, T_max: int, eta_min: float = 0.0):
+        super().__init__(optimizer)
+        self.T_max, self.eta_min = T_max, eta_min
+
+    def _lr_at(self, e):
+        return self.eta_min + (self.base_lr - self.eta_min) * (1 + math.cos(math.pi * e / self.T_max)) / 2
+
+
+class CosineAnnealingWarmRestarts(LRScheduler):
+    def __init__(self, optimizer, T_0: int, T_mult: int = 1, eta_min: float = 0.0):
+        super().__init__(optimizer)
+        if T_0 <= 0 or T_mult < 1:
+            raise ValueError("T_0 must be positive and T_mult >= 1")
+        self.T_0, self.T_mult, self.eta_min = T_0, T_mult, eta_min
+
+    def _lr_at(self, e):
+        t_i, t_cur = self.T_0, e
+        while t_cur >= t_i:
+            t_cur -= t_i
+            t_i *= self.T_mult
+        return self.eta_min + (self.base_lr - self.eta_min) * (1 + math.cos(math.pi * t_cur / t_i)) / 2
+
+
+class LambdaLR(LRScheduler):
+    def __init__(self, optimizer, lr_lambda: Callable[[int], float]):
+        super().__init__(optimizer)
+        self.fn = lr_lambda
+
+    def _lr_at(self, e):
+        return self.base_lr * self.fn(e)
+
+
+class MultiplicativeLR(LRScheduler):
+    def __init__(self, optimizer, lr_lambda: Callable[[int], float]):
+        super().__init__(optimizer)
+        self.fn = lr_lambda
+
+    def step(self, optimizer, metric=None):
+        self.last_epoch += 1
+        self.last_lr = self.last_lr * self.fn(self.last_epoch)
+        optimizer.set_lr(self.last_lr)
+        return self.last_lr
+
+
+class OneCycleLR(LRScheduler):
+    def __init__(self, optimizer, max_lr: float, total_steps: int, pct_start: float = 0.3, div_factor: float = 25.0,
+                 final_div_factor: float = 1e4, anneal: str = "cos"):
+        super().__init__(optimizer)
+        self.max_lr, self.total, self.pct = max_lr, total_steps, pct_start
+        self.initial, self.min_lr, self.anneal = max_lr / div_factor, max_lr / div_factor / final_div_factor, anneal
+        optimizer.set_lr(self.initial)
+        self.last_lr = self.initial
+
+    def _interp(self, a, b, pct):
+        if self.anneal == "cos":
+            return b + (a - b) * (1 + math.cos(math.pi * pct)) / 2
+        return a + (b - a) * pct
+
+    def _lr_at(self, e):
+        if e > self.total:
+            raise ValueError("OneCycleLR stepped past total_steps")
+        up = float(self.pct * self.total) - 1
+        if e <= up:
+            return self._interp(self.initial, self.max_lr, e / up)
+        return self._interp(self.max_lr, self.min_lr, (e - up) / (self.total - 1 - up))
+
+
+class CyclicLR(LRScheduler):
+    def __init__(self, optimizer, base_lr: float, max_lr: float, step_size_up: int = 2000,
+                 step_size_down: Optional[int] = None, mode: str = "triangular", gamma: float = 1.0):
+        super().__init__(optimizer)
+        self.lo, self.hi, self.up, self.down = base_lr, max_lr, step_size_up, step_size_down or step_size_up
+        self.mode, self.gamma = mode, gamma
+        optimizer.set_lr(base_lr)
+        self.last_lr = base_lr
+
+    def _lr_at(self, e):
+        total = self.up + self.down
+        cycle = math.floor(1 + e / total)
+        x = 1 + e / total - cycle
+        pos = x / (self.up / total) if x <= self.up / total else (x - 1) / (self.up / total - 1)
+        scale = {"triangular": 1.0, "triangular2": 1 / (2 ** (cycle - 1)), "exp_range": self.gamma ** e}[self.mode]
+        return self.lo + (self.hi - self.lo) * pos * scale
+
+
+class ReduceLROnPlateau(LRScheduler):
+    def __init__(self, optimizer, mode: str = "min", factor: float = 0.1, patience: int = 10, threshold: float = 1e-4,
+                 cooldown: int = 0, min_lr: float = 0.0):
+        super().__init__(optimizer)
+        self.mode, self.factor, self.patience, self.threshold, self.cooldown, self.min_lr = mode, factor, patience, threshold, cooldown, min_lr
+        self.best = math.inf if mode == "min" else -math.inf
+        self.bad, self.cool = 0, 0
+
+    def step(self, optimizer, metric: Optional[float] = None) -> float:
+        if metric is None:
+            raise ValueError("ReduceLROnPlateau.step needs the monitored metric")
+        self.last_epoch += 1
+        better = metric < self.best * (1 - self.threshold) if self.mode == "min" else metric > self.best * (1 + self.threshold)
+        if better:
+            self.best, self.bad = metric, 0
+        else:
+            self.bad += 1
+        if self.cool > 0:
+            self.cool -= 1
+            self.bad = 0
+        if self.bad > self.patience:
+            self.last_lr = max(self.last_lr * self.factor, self.min_lr)
+            optimizer.set_lr(self.last_lr)
+            self.cool, self.bad = self.cooldown, 0
+        return self.last_lr
+
+    def state(self):
+        st = super().state()
+        st.extra.update(best=self.best, bad=self.bad, cool=self.cool)
+        return st
+
+    def load_state(self, st):
+        super().load_state(st)
+        self.best, self.bad, self.cool = st.extra.get("best", self.best), int(st.extra.get("bad", 0)), int(st.extra.get("cool", 0))
+
+
+class SequentialLR(LRScheduler):
+    def __init__(self, optimizer, schedulers: Sequence[LRScheduler], milestones: Sequence[int]):
+        super().__init__(optimizer)
+        if len(milestones) != len(schedulers) - 1:
+            raise ValueError("SequentialLR needs len(schedulers) - 1 milestones")
+        self.scheds, self.milestones = list(schedulers), list(milestones)
+
+    def step(self, optimizer, metric=None):
+        self.last_epoch += 1
+        idx = sum(1 for m in self.milestones if m <= self.last_epoch)
+        s = self.scheds[idx]
+        if idx > 0 and self.last_epoch == self.milestones[idx - 1]:
+            s.last_epoch = 0
+            self.last_lr = s._lr_at(0) if not isinstance(s, (MultiplicativeLR, ReduceLROnPlateau)) else s.last_lr
+            optimizer.set_lr(self.last_lr)
+        else:
+            self.last_lr = s.step(optimizer, metric)
+        return self.last_lr
+
+
+class ChainedScheduler(LRScheduler):
+    """Applies every scheduler's multiplicative change in turn."""
+
+    def __init__(self, optimizer, schedulers: Sequence[LRScheduler]):
+        super().__init__(optimizer)
+        self.scheds = list(schedulers)
+
+    def step(self, optimizer, metric=None):
+        self.last_epoch += 1
+        lr = optimizer.get_lr()
+        for s in self.scheds:
+            prev = s.last_lr
+            new = s.step(optimizer, metric)
+            lr = lr * (new / prev if prev else 1.0)
+        self.last_lr = lr
+        optimizer.set_lr(lr)
+        return lr
+
+
+class GradScaler:
+    def __init__(self, init_scale: float = 65536.0, growth_factor: float = 2.0, backoff_factor: float = 0.5,
+                 growth_interval: int = 2000, enabled: bool = True):
+        self.scale, self.growth, self.backoff, self.interval, self.enabled = init_scale, growth_factor, backoff_factor, growth_interval, enabled
+        self._good_steps = 0
+        self._found_inf = False
+
+    def get_scale(self) -> float:
+        return self.scale
+
+    def scale_loss(self, session, loss: int) -> int:
+        return session.tensor_mul_scalar(loss, c=self.scale) if self.enabled else loss
+
+    def unscale_(self, session, optimizer) -> bool:
+        """Divide the accumulated gradients by the scale in place; returns True if all are finite."""
+        self._found_inf = False
+        for p in optimizer.params:
+            g = session.tensor_tape.accumulated_gradient(p)
+            if g is None:
+                continue
+            if not bool(torch.isfinite(g).all()):
+                self._found_inf = True
+        if not self._found_inf:
+            for p in optimizer.params:
+                g = session.tensor_tape.accumulated_gradient(p)
+                if g is not None:
+                    g.div_(self.scale)
+        return not self._found_inf
+
+    def step(self, session, optimizer, report=None) -> bool:
+        """Unscale and step; skips the step (returns False) when an inf/nan gradient was found."""
+        if not self.enabled:
+            optimizer.step(session, report)
+            return True
+        if self.unscale_(session, optimizer):
+            optimizer.step(session, report)
+            return True
+        return False
+
+    def update(self) -> None:
+        if not self.enabled:
+            return
+        if self._found_inf:
+            self.scale *= self.backoff
+            self._good_steps = 0
+        else:
+            self._good_steps += 1
+            if self._good_steps >= self.interval:
+                self.scale *= self.growth
+                self._good_steps = 0
+        self._found_inf = False
+
+    def state_dict(self):
+        return {"scale": self.scale, "good_steps": self._good_steps}
+
+    def load_state_dict(self, sd):
+        self.scale, self._good_steps = float(sd["scale"]), int(sd["good_steps"])
