@@ -290,11 +290,16 @@ def tensor_nonzero(self, a):
     return _new(self, torch.nonzero(self.tensor(a)).to(torch.float64), False)
 
 
-def tensor_max(self, a):
+def tensor_max(self, a, b=None):
+    """``tensor_max(a, b)``: elementwise maximum; ``tensor_max(a)``: maximum over all elements."""
+    if b is not None:
+        return self._apply("max", [a, b])
     return self.tensor_max_dim(self.tensor_reshape(a, shape=(-1,)), dim=0)
 
 
-def tensor_min(self, a):
+def tensor_min(self, a, b=None):
+    if b is not None:
+        return self._apply("min", [a, b])
     return self.tensor_min_dim(self.tensor_reshape(a, shape=(-1,)), dim=0)
 
 

@@ -201,15 +201,22 @@ class _Lcg:
         return (self.s >> 33) % bound
 
 
-def _neighbours(esi: int, k: int, seed: int) -> List[int]:
-    r = _Lcg(seed ^ (esi * 0x9E3779B97F4A7C15))
-    degree = min(k, 2 + r.next(max(1, min(k - 1, 6)))) if k > 1 else 1
-    out = []
-    while len(out) < degree:
-        c = r.next(k)
-        if c not in out:
-            out.append(c)
-    return sorted(out)
+def _neighbours(esi: int, k: int, seed: int, count: int) -> List[int]:
+    """Source symbols XOR-ed into repair symbol ``esi``.
+
+    The ``count`` repair symbols form two interleaved families of residue classes (mod R1 and
+    mod R2, each rotated by a seeded offset): every source symbol is covered once per family,
+    so any single loss and any two losses that differ in at least one family are recoverable.
+    """
+    j = esi - k
+    r1 = (count + 1) // 2
+    r2 = max(1, count - r1)
+    rot = _Lcg(seed).next(1 << 16)
+    if j < r1:
+        cls = [i for i in range(k) if (i + rot) % r1 == j]
+    else:
+        cls = [i for i in range(k) if (i * 7 + rot) % r2 == (j - r1) % r2]
+    return cls or [j % k]
 
 
 def _symbols(payload: bytes, size: int) -> List[bytearray]:
@@ -231,7 +238,7 @@ def generate_raptorq_sidecar(payload: bytes, repair_symbols: int = 0) -> Tuple[R
     manifest = []
     for j in range(count):
         esi = k + j
-        nb = _neighbours(esi, k, SIDECAR_SEED)
+        nb = _neighbours(esi, k, SIDECAR_SEED, count)
         sym = bytearray(size)
         for n in nb:
             _xor(sym, src[n])
@@ -246,7 +253,7 @@ def generate_raptorq_sidecar(payload: bytes, repair_symbols: int = 0) -> Tuple[R
         rec = decode_with_sidecar([None if i in dropped else bytes(s) for i, s in enumerate(src)], side)
         ok = rec is not None and rec == payload
         if ok:
-            used = [m.esi for m in manifest if any(n in dropped for n in _neighbours(m.esi, k, SIDECAR_SEED))]
+            used = [m.esi for m in manifest if any(n in dropped for n in _neighbours(m.esi, k, SIDECAR_SEED, count))]
             ph = hash_bytes(json.dumps([side.source_hash, dropped, used]).encode())
             proof = DecodeProofArtifact(1, side.source_hash, dropped, used, True, ph)
             break
@@ -265,7 +272,7 @@ def decode_with_sidecar(received: Sequence[Optional[bytes]], side: RaptorQSideca
     col = {m: j for j, m in enumerate(missing)}
     rows = []
     for rs in side.repair_manifest:
-        nb = _neighbours(rs.esi, k, side.seed)
+        nb = _neighbours(rs.esi, k, side.seed, side.repair_symbols)
         val = bytearray(bytes.fromhex(rs.bytes))
         mask = 0
         for n in nb:

@@ -1,0 +1,61 @@
+"""Conformance tooling: forensics JSONL schema, gates, perf SLO report, durability pipeline."""
+import json
+import os
+
+from frankentorch_b200.conformance import cli, perf_slo
+
+
+def test_e2e_matrix_triage_and_reliability_gate(tmp_path):
+    e2e = str(tmp_path / "e2e.jsonl")
+    assert cli.main(["run_e2e_matrix", "--mode", "both", "--packet", "FT-P2C-004", "--output", e2e]) == 0
+    recs = [json.loads(l) for l in open(e2e)]
+    required = {"schema_version", "ts_unix_ms", "suite_id", "scenario_id", "fixture_id", "packet_id", "mode", "seed",
+                "env_fingerprint", "artifact_refs", "replay_command", "outcome", "reason_code"}
+    assert recs and all(required <= set(r) for r in recs)
+    assert {r["mode"] for r in recs} == {"strict", "hardened"} and all(r["schema_version"] == "ft-conformance-log-v1" for r in recs)
+    tri = str(tmp_path / "triage.json")
+    assert cli.main(["triage_forensics_failures", "--input", e2e, "--output", tri]) == 0
+    assert json.load(open(tri))["failures"] == 0
+    idx = str(tmp_path / "index.json")
+    assert cli.main(["build_failure_forensics_index", "--e2e", e2e, "--triage", tri, "--output", idx]) == 0
+    pol = str(tmp_path / "policy.json")
+    json.dump({"min_cases_per_family": 1, "min_pass_ratio": 1.0, "flake_budget": 0,
+               "required_families": ["autograd_scheduler", "scalar_autograd"]}, open(pol, "w"))
+    assert cli.main(["check_reliability_budgets", "--policy", pol, "--e2e", e2e]) == 0
+    json.dump({"min_cases_per_family": 1, "min_pass_ratio": 1.0, "flake_budget": 0, "required_families": ["nn_state"]}, open(pol, "w"))
+    assert cli.main(["check_reliability_budgets", "--policy", pol, "--e2e", e2e]) == 1    # coverage floor violated
+
+
+def test_differential_report_against_live_torch(tmp_path):
+    out = str(tmp_path / "diff.json")
+    assert cli.main(["run_differential_report", "--mode", "both", "--output", out]) == 0
+    rep = json.load(open(out))
+    assert rep["passed"] and len(rep["checks"]) == 18
+
+
+def test_perf_slo_report_and_gates(tmp_path):
+    assert perf_slo.percentile([5.0, 1.0, 3.0, 2.0, 4.0], 50) == 3.0
+    assert perf_slo.percentile([1.0, 2.0], 99) == 2.0
+    out = str(tmp_path / "perf.json")
+    assert cli.main(["run_perf_slos", "--profile", "smoke", "--iterations", "3", "--output", out]) == 0
+    rep = json.load(open(out))
+    assert rep["schema_version"] == "ft-perf-slo-report-v1" and rep["workloads"]["checkpoint"]["mb_per_s"] > 0
+    assert cli.main(["check_perf_slos", "--input", out]) == 0
+    worse = json.loads(json.dumps(rep))
+    worse["workloads"]["matmul"]["p99"] *= 2
+    w = str(tmp_path / "worse.json")
+    json.dump(worse, open(w, "w"))
+    assert cli.main(["check_benchmark_regression", "--baseline", out, "--input", w]) == 1
+    assert cli.main(["check_benchmark_regression", "--baseline", out, "--input", out]) == 0
+
+
+def test_durability_pipeline_and_validator(tmp_path):
+    root = tmp_path / "artifacts"
+    root.mkdir()
+    (root / "contract.md").write_text("packet contract table\n" * 40)
+    (root / "golden.json").write_text(json.dumps({"a": list(range(200))}))
+    assert cli.main(["run_raptorq_durability_pipeline", "--root", str(root)]) == 0
+    assert os.path.exists(root / "golden.json.sidecar.json") and os.path.exists(root / "golden.json.proof.json")
+    assert cli.main(["validate_artifacts", str(root)]) == 0
+    (root / "golden.json").write_text("tampered")
+    assert cli.main(["validate_artifacts", str(root)]) == 1
