@@ -56,6 +56,39 @@ int* ftk_status_word(void);               // device pointer (allocated on first 
 int ftk_read_status(int reset);           // synchronises the device; returns the status word
 int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream);
 
+// ---- GEMM fused with a collective over NVLink peer memory --------------------------------
+// One kernel: `comm_ctas` CTAs move shards / reduce partials while the rest run the GEMM.
+//  GATHER_A : A = [world * chunk_rows, K] is row-sharded; shard r is read from src[r]
+//             (contiguous [chunk_rows, K], peer or local memory) into g->A (local staging,
+//             lda == K) while tiles of shards already staged are multiplied.
+//  GATHER_B : the same for B = [world * chunk_rows, K] (weights sharded by output row).
+//  SCATTER_D: D = [world * chunk_rows, N] partial sums; rows of rank r go to inbox[r]
+//             (bf16 [world][chunk_rows][N] on rank r) and rank r adds the world partials in
+//             ascending rank order into g->D ([chunk_rows, N], + bias, + resid, accumulate).
+// `epoch` is a device word holding the use count (1, 2, ...) of the flag arrays; the caller
+// advances it before each launch, identically on every rank.  Flag arrays start at zero.
+enum FtkCommMode {
+  FTK_COMM_NONE = 0,
+  FTK_COMM_GATHER_A = 1,
+  FTK_COMM_GATHER_B = 2,
+  FTK_COMM_SCATTER_D = 3,
+};
+#define FTK_MAX_RANKS 8
+typedef struct FtkCommDesc {
+  int mode, rank, world;
+  int comm_ctas;                       // 0 = default
+  int chunk_rows;                      // multiple of 128
+  const void* src[FTK_MAX_RANKS];      // gather: shard pointers (entry `rank` is local)
+  int* sub_flags;                      // gather: [world * chunk_rows / 128] local words
+  int* ready_local;                    // gather: [world] local words, NULL = shards known final
+  int* ready_peer[FTK_MAX_RANKS];      // gather: &ready_local[rank] on each peer
+  void* inbox[FTK_MAX_RANKS];          // scatter: inbox of every rank
+  int* arrive[FTK_MAX_RANKS];          // scatter: [chunk tiles][world] words on every rank
+  const int* epoch;
+} FtkCommDesc;
+int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* c, void* stream);
+int ftk_tick_i32(int* word, void* stream);    // *word += 1 on the stream
+
 // ---- attention (causal / full), packed QKV layout ---------------------------------------
 // q/k/v: bf16 element (b, s, h, e) at base[b*bs + s*ss + h*hs + e]; head_dim in {64, 128}.
 // o: same addressing with its own strides.  lse: fp32 [B, H, S], log2 domain.

@@ -1,0 +1,761 @@
+// Device side of the sm_100a bf16 GEMM: TMA -> 128B-swizzled smem ring -> tcgen05.mma (fp32
+// accumulators in TMEM, double buffered) -> tcgen05.ld epilogue, as one persistent kernel.
+//
+// The same kernel carries three collective-fused forms (template parameter COMM = 1), in
+// which the last `comm_ctas` CTAs of the grid move data over NVLink while the others compute:
+//   gather A / gather B : the row-sharded operand is pulled shard by shard from the peers
+//                         (bulk async copies peer -> smem -> local staging buffer, no cluster
+//                         multicast), a flag per 128-row subtile is published, and the TMA
+//                         producer of a compute CTA waits only for the subtiles its tile reads.
+//                         Tiles are visited own-shard-first in rank-rotated order.
+//   scatter-reduce D    : the epilogue stores each partial tile as bf16 straight into the
+//                         inbox of the rank that owns those rows (peer stores), then raises a
+//                         flag at the owner; the comm CTAs of the owner add the partials of
+//                         all ranks in ascending rank order and apply bias / residual /
+//                         accumulate.  The order is fixed, so the sum is reproducible.
+// Every wait on a flag that another CTA or rank sets is bounded and ends in the status word.
+#pragma once
+#include "ft_sm100.cuh"
+#include "ftk_api.h"
+
+namespace ftk {
+
+constexpr int G_BM = 128;
+constexpr int G_BK = 64;
+constexpr int G_UMMA_K = 16;
+constexpr int G_EPI_WARPS = 8;
+constexpr int G_THREADS = 64 + 32 * G_EPI_WARPS;
+constexpr int G_MAX_RANKS = 8;
+constexpr int G_COPY_SLOT = 32768;   // bytes per bulk copy of the gather ring
+constexpr int G_COPY_SLOTS = 6;
+constexpr long long G_PEER_WAIT_CYCLES = 4000000000ll;
+
+struct GemmArgs {
+  int M, N, K, L0, L1;
+  int a_mn, b_mn;
+  void* D;
+  long long ldd, d_s0, d_s1;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* resid;
+  long long ldr, r_s0, r_s1;
+  __nv_bfloat16* aux;  // optional bf16 copy of the pre-activation (same layout as D)
+  float alpha;
+  int epi;
+  int out_fp32;
+  int accumulate;
+  int splits;          // >1: split-K, partial tiles go to `ws` as fp32 [split][M][N]
+  float* ws;
+  int* status;
+};
+
+struct CommArgs {
+  int mode;                      // FTK_COMM_*
+  int rank, world, comm_ctas;
+  int chunk_rows;                // rows of the sharded operand / output owned by one rank
+  long long sub_bytes;           // bytes of one 128-row subtile of the gathered operand
+  const uint8_t* src[G_MAX_RANKS];   // gather: shard of rank r, contiguous [chunk_rows, K]
+  uint8_t* full;                 // gather: local staging of the whole operand
+  int* sub_flags;                // gather: one word per 128-row subtile, holds the epoch
+  int* ready_local;              // gather: [world] words written by the peers (may be null)
+  int* ready_peer[G_MAX_RANKS];  // gather: word `rank` of peer r's ready_local
+  __nv_bfloat16* inbox[G_MAX_RANKS];  // scatter: inbox of rank r, [world][chunk_rows][N]
+  int* arrive[G_MAX_RANKS];      // scatter: flags of rank r, [tiles of one chunk][world]
+  const int* epoch;              // device word: use count (>= 1) of the flag arrays
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = G_BM * G_BK * 2;
+  static constexpr int B_BYTES = BN * G_BK * 2;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+  static constexpr int ACC_STRIDE = (BN == 192) ? 256 : BN;  // TMEM columns between accumulators
+  static constexpr int TMEM_COLS = (BN == 128) ? 256 : 512;  // power of two
+  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Epilogue activations use the hardware tanh (relative error ~2^-11, below bf16 rounding).
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.f + tanh_fast(u));
+}
+__device__ __forceinline__ float gelu_tanh_grad_fast(float x) {
+  const float x2 = x * x;
+  const float t = tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x2));
+  const float du = 0.7978845608028654f * (1.f + 3.f * 0.044715f * x2);
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
+}
+
+// v[i] = f(v[i], rr[i]) for the 32 values of one row chunk; the switch is outside the loop.
+__device__ __forceinline__ void apply_epi32(float* v, const float* rr, int epi) {
+  switch (epi) {
+    case FTK_EPI_GELU_TANH:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
+      break;
+    case FTK_EPI_GELU_ERF:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_erf_f(v[i]);
+      break;
+    case FTK_EPI_RELU:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = v[i] > 0.f ? v[i] : 0.f;
+      break;
+    case FTK_EPI_MUL_DGELU_TANH:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad_fast(rr[i]);
+      break;
+    case FTK_EPI_MUL_DGELU_ERF:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad_f(rr[i]);
+      break;
+    case FTK_EPI_MUL_DRELU:
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = rr[i] > 0.f ? v[i] : 0.f;
+      break;
+    default:
+      break;
+  }
+}
+
+// ------------------------------------------------------------------ flags between CTAs / ranks
+__device__ __forceinline__ int ld_acq_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acq_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_rel_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_rel_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+// Bounded wait until *p >= want.  SYS selects system scope (flags written by another GPU).
+template <bool SYS>
+__device__ __forceinline__ bool flag_wait(const int* p, int want, const WaitCtx& c) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while ((SYS ? ld_acq_sys(p) : ld_acq_gpu(p)) < want) {
+    __nanosleep(64);
+    if ((++spins & 31u) == 0u) {
+      if (aborted(c)) return false;
+      if (clock64() - t0 > G_PEER_WAIT_CYCLES) {
+        raise_abort(c, FT_ERR_WAIT_PEER);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Bulk async copies without cluster multicast: global (local or peer) -> this CTA's smem, and
+// smem -> local global memory.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Work item -> output tile.  Plain GEMMs walk m fastest; the collective forms walk the row
+// chunks of the sharded dimension in rank-rotated order.
+struct TileCoord {
+  int sp, l, m_t, n_t;
+};
+template <int BN, int COMM>
+__device__ __forceinline__ TileCoord decode_item(int item, const GemmArgs& p, const CommArgs& c,
+                                                 int tiles_m, int tiles_n, int nbatch) {
+  TileCoord t;
+  if (!COMM || c.mode == FTK_COMM_NONE) {
+    const int tiles_mn = tiles_m * tiles_n;
+    t.sp = item / (tiles_mn * nbatch);
+    const int rem = item - t.sp * (tiles_mn * nbatch);
+    t.l = rem / tiles_mn;
+    const int tt = rem - t.l * tiles_mn;
+    t.m_t = tt % tiles_m;
+    t.n_t = tt / tiles_m;
+    return t;
+  }
+  t.sp = 0;
+  t.l = 0;
+  if (c.mode == FTK_COMM_GATHER_B) {
+    const int shift = (int)(((long long)c.rank * c.chunk_rows) / BN);
+    t.n_t = (item / tiles_m + shift) % tiles_n;
+    t.m_t = item % tiles_m;
+  } else {  // row chunks of A (gather) or D (scatter): own chunk first / last
+    const int tpc = c.chunk_rows / G_BM;
+    const int per_chunk = tpc * tiles_n;
+    const int i = item / per_chunk;
+    const int rem = item - i * per_chunk;
+    const int chunk = (c.rank + i + (c.mode == FTK_COMM_SCATTER_D ? 1 : 0)) % c.world;
+    t.n_t = rem / tpc;
+    t.m_t = chunk * tpc + rem % tpc;
+  }
+  return t;
+}
+
+// ------------------------------------------------------------------ comm CTAs: gather
+// Thread 0 loads shard pieces into an smem ring, thread 32 stores them to the local staging
+// buffer and publishes a flag per completed 128-row subtile.
+__device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const CommArgs& c,
+                                            int epoch, int cta, const WaitCtx& ctx) {
+  uint64_t* full = bars;
+  uint64_t* empty = bars + G_COPY_SLOTS;
+  const int spc = c.chunk_rows / G_BM;                 // subtiles per chunk
+  const int n_sub = spc * c.world;
+  const uint32_t piece = c.sub_bytes < G_COPY_SLOT ? (uint32_t)c.sub_bytes : (uint32_t)G_COPY_SLOT;
+  const int pps = (int)(c.sub_bytes / piece);          // pieces per subtile
+  if (threadIdx.x == 0) {
+    // announce that this rank's shard is final for this epoch
+    if (cta == 0 && c.ready_local) {
+      __threadfence_system();
+      for (int r = 0; r < c.world; ++r)
+        if (r != c.rank) st_rel_sys(c.ready_peer[r], epoch);
+    }
+    long long n = 0;
+    int ready_seen = 1 << c.rank;
+    for (int q = cta; q < n_sub; q += c.comm_ctas) {
+      const int chunk = (c.rank + q / spc) % c.world;
+      const int sidx = q % spc;
+      if (c.ready_local && !((ready_seen >> chunk) & 1)) {
+        if (!flag_wait<true>(c.ready_local + chunk, epoch, ctx)) return;
+        ready_seen |= 1 << chunk;
+      }
+      const uint8_t* s = c.src[chunk] + (long long)sidx * c.sub_bytes;
+      for (int pc = 0; pc < pps; ++pc, ++n) {
+        const int slot = (int)(n % G_COPY_SLOTS);
+        const uint32_t ph = (uint32_t)((n / G_COPY_SLOTS) & 1);
+        if (!mbar_wait(&empty[slot], ph ^ 1u, ctx, FT_ERR_WAIT_EMPTY)) return;
+        mbar_arrive_expect_tx(&full[slot], piece);
+        bulk_load(smem + slot * G_COPY_SLOT, s + (long long)pc * piece, piece, &full[slot]);
+      }
+    }
+  } else if (threadIdx.x == 32) {
+    long long n = 0, freed = 0;
+    int q_pub = cta;                                   // next subtile of this CTA to publish
+    auto retire = [&](long long done) {                // pieces [freed, done) are fully stored
+      for (; freed < done; ++freed) {
+        mbar_arrive(&empty[freed % G_COPY_SLOTS]);
+        if ((freed + 1) % pps == 0) {
+          const int chunk = (c.rank + q_pub / spc) % c.world;
+          fence_proxy_async_all();
+          __threadfence();
+          st_rel_gpu(c.sub_flags + chunk * spc + q_pub % spc, epoch);
+          q_pub += c.comm_ctas;
+        }
+      }
+    };
+    for (int q = cta; q < n_sub; q += c.comm_ctas) {
+      const int chunk = (c.rank + q / spc) % c.world;
+      uint8_t* d = c.full + ((long long)chunk * spc + q % spc) * c.sub_bytes;
+      for (int pc = 0; pc < pps; ++pc, ++n) {
+        const int slot = (int)(n % G_COPY_SLOTS);
+        const uint32_t ph = (uint32_t)((n / G_COPY_SLOTS) & 1);
+        if (!mbar_wait(&full[slot], ph, ctx, FT_ERR_WAIT_FULL)) {
+          bulk_wait_group<0>();
+          return;
+        }
+        bulk_store(d + (long long)pc * piece, smem + slot * G_COPY_SLOT, piece);
+        bulk_wait_group<2>();                          // all but the newest two stores landed
+        retire(n + 1 - 2 > 0 ? n + 1 - 2 : 0);
+      }
+    }
+    bulk_wait_group<0>();
+    retire(n);
+  }
+}
+
+// ------------------------------------------------------------------ comm CTAs: ordered reduce
+// Tile (n_t, m_in) of this rank's chunk: out = sum over source ranks (ascending) of the bf16
+// partials in the local inbox, + bias, + residual, (+ previous output).
+template <int BN>
+__device__ __forceinline__ void comm_reduce(const GemmArgs& p, const CommArgs& c, int epoch, int cta,
+                                            const WaitCtx& ctx) {
+  const int tpc = c.chunk_rows / G_BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int n_tiles = tpc * tiles_n;
+  const __nv_bfloat16* inbox = c.inbox[c.rank];
+  const long long src_stride = (long long)c.chunk_rows * p.N;
+  for (int t = cta; t < n_tiles; t += c.comm_ctas) {
+    if ((int)threadIdx.x < c.world) {
+      if (!flag_wait<true>(c.arrive[c.rank] + t * c.world + threadIdx.x, epoch, ctx)) {
+        // fall through to the barrier; everyone sees the abort flag below
+      }
+    }
+    __syncthreads();
+    if (aborted(ctx)) return;
+    const int n_t = t / tpc, m_in = t % tpc;
+    const int n_base = n_t * BN;
+    const int cols = min(BN, p.N - n_base);            // multiple of 8
+    const int vec_per_row = cols >> 3;
+    for (int v = threadIdx.x; v < G_BM * vec_per_row; v += G_THREADS) {
+      const int row = m_in * G_BM + v / vec_per_row;   // row inside this rank's chunk
+      const int col = n_base + ((v % vec_per_row) << 3);
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      const __nv_bfloat16* ip = inbox + (long long)row * p.N + col;
+#pragma unroll 4
+      for (int s = 0; s < c.world; ++s) {
+        const uint4 u = __ldcg(reinterpret_cast<const uint4*>(ip + s * src_stride));
+        const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
+                     f3 = unpack_bf16(u.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      if (p.bias) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(__ldg(p.bias + col + i));
+      }
+      if (p.resid) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p.resid + (long long)row * p.ldr + col);
+        const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
+                     f3 = unpack_bf16(u.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      if (p.out_fp32) {
+        float* dp = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col;
+        float4 a = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        float4 b = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        if (p.accumulate) {
+          const float4 oa = reinterpret_cast<float4*>(dp)[0], ob = reinterpret_cast<float4*>(dp)[1];
+          a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
+          b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
+        }
+        reinterpret_cast<float4*>(dp)[0] = a;
+        reinterpret_cast<float4*>(dp)[1] = b;
+      } else {
+        __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col;
+        if (p.accumulate) {
+          const uint4 u = *reinterpret_cast<const uint4*>(dp);
+          const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
+                       f3 = unpack_bf16(u.w);
+          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+        }
+        uint4 o;
+        o.x = pack_bf16(acc[0], acc[1]);
+        o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]);
+        o.w = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(dp) = o;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int BN, int COMM>
+__global__ void __launch_bounds__(G_THREADS, 1)
+gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
+                       const __grid_constant__ CUtensorMap tmB, const GemmArgs p, const CommArgs c) {
+  using Cfg = GemmCfg<BN>;
+  static_assert(!COMM || G_COPY_SLOTS * G_COPY_SLOT <= Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES),
+                "gather ring must fit the operand ring");
+  static_assert(!COMM || 2 * G_COPY_SLOTS <= 2 * Cfg::STAGES + 4, "barrier space");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + Cfg::STAGES * Cfg::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES));
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::STAGES;
+  uint64_t* tfull = bars + 2 * Cfg::STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  WaitCtx ctx{p.status, abort_f};
+
+  const int n_compute = COMM ? (int)gridDim.x - c.comm_ctas : (int)gridDim.x;
+  const bool comm_cta = COMM && (int)blockIdx.x >= n_compute;
+  const int epoch = COMM ? *c.epoch : 0;
+
+  if (threadIdx.x == 0) {
+    if (comm_cta) {
+      for (int i = 0; i < G_COPY_SLOTS; ++i) {
+        mbar_init(&bars[i], 1);
+        mbar_init(&bars[G_COPY_SLOTS + i], 1);
+      }
+    } else {
+      for (int i = 0; i < Cfg::STAGES; ++i) {
+        mbar_init(&full[i], 1);
+        mbar_init(&empty[i], 1);
+      }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&tfull[i], 1);
+        mbar_init(&tempty[i], G_EPI_WARPS);
+      }
+    }
+    *abort_f = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1 && !comm_cta) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (comm_cta) {
+    if (COMM) {
+      const int cta = (int)blockIdx.x - n_compute;
+      if (c.mode == FTK_COMM_SCATTER_D)
+        comm_reduce<BN>(p, c, epoch, cta, ctx);
+      else
+        comm_gather(smem, bars, c, epoch, cta, ctx);
+    }
+    __syncthreads();
+    return;
+  }
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (p.M + G_BM - 1) / G_BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_mn = tiles_m * tiles_n;
+  const int nbatch = p.L0 * p.L1;
+  const int total = tiles_mn * nbatch * p.splits;  // work item = (split, batch, n tile, m tile)
+  const int kblocks_all = (p.K + G_BK - 1) / G_BK;
+  const int kb_per_split = (kblocks_all + p.splits - 1) / p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+    }
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < total; item += n_compute) {
+      const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
+      const int m_t = t.m_t, n_t = t.n_t;
+      const int l0 = t.l % p.L0, l1 = t.l / p.L0;
+      const int kb0 = t.sp * kb_per_split;
+      const int kb1 = min(kblocks_all, kb0 + kb_per_split);
+      if (COMM && (c.mode == FTK_COMM_GATHER_A || c.mode == FTK_COMM_GATHER_B)) {
+        // the staged subtiles this tile reads must have landed
+        int f0, f1;
+        if (c.mode == FTK_COMM_GATHER_A) {
+          f0 = f1 = m_t;
+        } else {
+          f0 = (n_t * BN) / G_BM;
+          f1 = (min(p.N, n_t * BN + BN) - 1) / G_BM;
+        }
+        int good = 1;
+        if (lane == 0) {
+          for (int f = f0; f <= f1 && good; ++f) good = flag_wait<false>(c.sub_flags + f, epoch, ctx) ? 1 : 0;
+          fence_proxy_async_all();
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) break;
+      }
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&empty[s], ph ^ 1u, ctx, FT_ERR_WAIT_EMPTY)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
+          uint8_t* a_dst = sA + s * Cfg::A_BYTES;
+          uint8_t* b_dst = sB + s * Cfg::B_BYTES;
+          if (!p.a_mn) {
+            tma_load_4d(a_dst, &tmA, &full[s], kb * G_BK, m_t * G_BM, l0, l1);
+          } else {
+#pragma unroll
+            for (int cc = 0; cc < G_BM / 64; ++cc)
+              tma_load_4d(a_dst + cc * (G_BK * 128), &tmA, &full[s], m_t * G_BM + cc * 64, kb * G_BK,
+                          l0, l1);
+          }
+          if (!p.b_mn) {
+            tma_load_4d(b_dst, &tmB, &full[s], kb * G_BK, n_t * BN, l0, l1);
+          } else {
+#pragma unroll
+            for (int cc = 0; cc < BN / 64; ++cc)
+              tma_load_4d(b_dst + cc * (G_BK * 128), &tmB, &full[s], n_t * BN + cc * 64, kb * G_BK,
+                          l0, l1);
+          }
+        }
+        __syncwarp();
+        if (++s == Cfg::STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = make_idesc_bf16(G_BM, BN, p.a_mn, p.b_mn);
+    const uint32_t a_lbo = p.a_mn ? G_BK * 128 : 16, a_adv = p.a_mn ? G_UMMA_K * 128 : G_UMMA_K * 2;
+    const uint32_t b_lbo = p.b_mn ? G_BK * 128 : 16, b_adv = p.b_mn ? G_UMMA_K * 128 : G_UMMA_K * 2;
+    int s = 0;
+    uint32_t ph = 0;
+    int acc = 0;
+    uint32_t acc_ph = 0;  // bit a = phase of accumulator a
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < total; item += n_compute) {
+      const int sp = (COMM && c.mode != FTK_COMM_NONE) ? 0 : item / (tiles_mn * nbatch);
+      const int kb0 = sp * kb_per_split;
+      const int kb1 = min(kblocks_all, kb0 + kb_per_split);
+      if (!mbar_wait(&tempty[acc], ((acc_ph >> acc) & 1u) ^ 1u, ctx, FT_ERR_WAIT_TMEM_EMPTY)) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&full[s], ph, ctx, FT_ERR_WAIT_FULL)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(sA + s * Cfg::A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * Cfg::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < G_BK / G_UMMA_K; ++k) {
+            umma_bf16(d_tmem, make_smem_desc(a_addr + k * a_adv, a_lbo, 1024),
+                      make_smem_desc(b_addr + k * b_adv, b_lbo, 1024), idesc,
+                      (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (kb == kb1 - 1) umma_commit(&tfull[acc]);
+        }
+        __syncwarp();
+        if (++s == Cfg::STAGES) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+      if (kb1 <= kb0 && lane == 0) umma_commit(&tfull[acc]);  // empty split: nothing to wait for
+      __syncwarp();
+      acc_ph ^= (1u << acc);
+      acc ^= 1;
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (8 warps)
+    const int ew = warp - 2;
+    const int q = warp & 3;               // TMEM lane quarter this warp may read
+    const int half = ew >> 2;             // which half of the tile's columns
+    const int row_in_tile = q * 32 + lane;
+    constexpr int CHUNKS = BN / 32;
+    constexpr int C_HALF = (CHUNKS + 1) / 2;
+    const int c_begin = half == 0 ? 0 : C_HALF;
+    const int c_end = half == 0 ? C_HALF : CHUNKS;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int item = blockIdx.x; item < total; item += n_compute) {
+      const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
+      const int sp = t.sp, l = t.l, m_t = t.m_t, n_t = t.n_t;
+      const int l0 = l % p.L0, l1 = l / p.L0;
+      const bool empty_split = (sp * kb_per_split >= kblocks_all);
+      if (!mbar_wait(&tfull[acc], (acc_ph >> acc) & 1u, ctx, FT_ERR_WAIT_TMEM_FULL)) break;
+      tc_fence_after();
+      const long long row = (long long)m_t * G_BM + row_in_tile;
+      if (COMM && c.mode == FTK_COMM_SCATTER_D) {
+        // partial tile -> inbox of the owning rank, slot of this rank; then one flag per tile
+        const int tpc = c.chunk_rows / G_BM;
+        const int owner = m_t / tpc;
+        const long long row_in_chunk = row - (long long)owner * c.chunk_rows;
+        __nv_bfloat16* ob = c.inbox[owner] + ((long long)c.rank * c.chunk_rows + row_in_chunk) * p.N;
+#pragma unroll 1
+        for (int ci = c_begin; ci < c_end; ++ci) {
+          const int c0 = ci * 32;
+          uint32_t r[32];
+          tmem_ld32(tmem_base + acc * Cfg::ACC_STRIDE + c0 + ((uint32_t)(q * 32) << 16), r);
+          tmem_ld_wait();
+          const int n0 = n_t * BN + c0;
+          if (row < p.M && n0 < p.N) {
+            const int nv = min(4, (p.N - n0) >> 3);       // N is a multiple of 8
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (i < nv) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * p.alpha, __uint_as_float(r[8 * i + 1]) * p.alpha);
+                o.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * p.alpha, __uint_as_float(r[8 * i + 3]) * p.alpha);
+                o.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * p.alpha, __uint_as_float(r[8 * i + 5]) * p.alpha);
+                o.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * p.alpha, __uint_as_float(r[8 * i + 7]) * p.alpha);
+                reinterpret_cast<uint4*>(ob + n0)[i] = o;
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
+        if (ew == 0 && lane == 0) {
+          const int t_local = n_t * tpc + (m_t - owner * tpc);
+          st_rel_sys(c.arrive[owner] + t_local * c.world + c.rank, epoch);
+        }
+        acc_ph ^= (1u << acc);
+        acc ^= 1;
+        continue;
+      }
+      const long long d_off = l0 * p.d_s0 + l1 * p.d_s1 + row * p.ldd;
+      const long long r_off = l0 * p.r_s0 + l1 * p.r_s1 + row * p.ldr;
+      const bool need_r = p.resid != nullptr;
+#pragma unroll 1
+      for (int ci = c_begin; ci < c_end; ++ci) {
+        const int c0 = ci * 32;
+        uint32_t r[32];
+        tmem_ld32(tmem_base + acc * Cfg::ACC_STRIDE + c0 + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+        const int n0 = n_t * BN + c0;
+        if (row < p.M && n0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = empty_split ? 0.f : __uint_as_float(r[i]) * p.alpha;
+          const bool full_chunk = (n0 + 32 <= p.N);
+          if (p.splits > 1) {
+            // raw partial tile -> workspace [split][batch][M][N] (fp32)
+            float* wp = p.ws + (((long long)sp * nbatch + l) * p.M + row) * p.N + n0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(wp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(wp)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (n0 + i < p.N) wp[i] = v[i];
+            }
+            continue;
+          }
+          if (p.bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (full_chunk || n0 + i < p.N) v[i] += __bfloat162float(__ldg(p.bias + n0 + i));
+          }
+          if (p.aux) {
+            __nv_bfloat16* ap = p.aux + d_off + n0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(ap) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 o;
+                o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
+                o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+                o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+                o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+                reinterpret_cast<uint4*>(ap)[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (n0 + i < p.N) ap[i] = __float2bfloat16(v[i]);
+            }
+          }
+          float rr[32];
+          if (need_r) {
+            const __nv_bfloat16* rp = p.resid + r_off + n0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 u = __ldg(reinterpret_cast<const uint4*>(rp) + i);
+                float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
+                       f3 = unpack_bf16(u.w);
+                rr[8 * i + 0] = f0.x; rr[8 * i + 1] = f0.y; rr[8 * i + 2] = f1.x;
+                rr[8 * i + 3] = f1.y; rr[8 * i + 4] = f2.x; rr[8 * i + 5] = f2.y;
+                rr[8 * i + 6] = f3.x; rr[8 * i + 7] = f3.y;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                rr[i] = (n0 + i < p.N) ? __bfloat162float(rp[i]) : 0.f;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) rr[i] = 0.f;
+          }
+          const bool r_is_operand = (p.epi >= FTK_EPI_MUL_DGELU_TANH);
+          if (p.epi != FTK_EPI_NONE) apply_epi32(v, rr, p.epi);
+          if (need_r && !r_is_operand) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += rr[i];
+          }
+          if (p.out_fp32) {
+            float* dp = reinterpret_cast<float*>(p.D) + d_off + n0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                if (p.accumulate) {
+                  float4 old = reinterpret_cast<float4*>(dp)[i];
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                reinterpret_cast<float4*>(dp)[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (n0 + i < p.N) dp[i] = p.accumulate ? dp[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + d_off + n0;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if (p.accumulate) {
+                  uint4 u = reinterpret_cast<uint4*>(dp)[i];
+                  float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
+                         f3 = unpack_bf16(u.w);
+                  v[8 * i + 0] += f0.x; v[8 * i + 1] += f0.y; v[8 * i + 2] += f1.x;
+                  v[8 * i + 3] += f1.y; v[8 * i + 4] += f2.x; v[8 * i + 5] += f2.y;
+                  v[8 * i + 6] += f3.x; v[8 * i + 7] += f3.y;
+                }
+                uint4 o;
+                o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
+                o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+                o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+                o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+                reinterpret_cast<uint4*>(dp)[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32; ++i)
+                if (n0 + i < p.N)
+                  dp[i] = __float2bfloat16(p.accumulate ? __bfloat162float(dp[i]) + v[i] : v[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc_ph ^= (1u << acc);
+      acc ^= 1;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (*abort_f) {
+    // give copies and MMAs still in flight time to land before smem/TMEM go away
+    for (int i = 0; i < 100; ++i) __nanosleep(10000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+}  // namespace ftk

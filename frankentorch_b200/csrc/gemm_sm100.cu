@@ -18,405 +18,12 @@
 // One persistent CTA per SM, 10 warps: warp 0 issues TMA loads, warp 1 owns TMEM and
 // issues the MMAs, warps 2..9 drain accumulators (warp w reads TMEM lane quarter w%4 and
 // one half of the tile's columns).  Two accumulators let the epilogue of tile i overlap
-// the mainloop of tile i+1.
-#include "ft_sm100.cuh"
-#include "ftk_api.h"
+// the mainloop of tile i+1.  The device code, including the collective-fused forms
+// (all-gather -> GEMM, GEMM -> reduce-scatter), lives in gemm_kernel.cuh; this file holds
+// the split-K reduction and the host launchers.
+#include "gemm_kernel.cuh"
 
 namespace ftk {
-
-constexpr int G_BM = 128;
-constexpr int G_BK = 64;
-constexpr int G_UMMA_K = 16;
-constexpr int G_EPI_WARPS = 8;
-constexpr int G_THREADS = 64 + 32 * G_EPI_WARPS;
-
-struct GemmArgs {
-  int M, N, K, L0, L1;
-  int a_mn, b_mn;
-  void* D;
-  long long ldd, d_s0, d_s1;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* resid;
-  long long ldr, r_s0, r_s1;
-  __nv_bfloat16* aux;  // optional bf16 copy of the pre-activation (same layout as D)
-  float alpha;
-  int epi;
-  int out_fp32;
-  int accumulate;
-  int splits;          // >1: split-K, partial tiles go to `ws` as fp32 [split][M][N]
-  float* ws;
-  int* status;
-};
-
-template <int BN>
-struct GemmCfg {
-  static constexpr int A_BYTES = G_BM * G_BK * 2;
-  static constexpr int B_BYTES = BN * G_BK * 2;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
-  static constexpr int ACC_STRIDE = (BN == 192) ? 256 : BN;  // TMEM columns between accumulators
-  static constexpr int TMEM_COLS = (BN == 128) ? 256 : 512;  // power of two
-  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
-};
-
-__device__ __forceinline__ float tanh_fast(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// Epilogue activations use the hardware tanh (relative error ~2^-11, below bf16 rounding).
-__device__ __forceinline__ float gelu_tanh_fast(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return 0.5f * x * (1.f + tanh_fast(u));
-}
-__device__ __forceinline__ float gelu_tanh_grad_fast(float x) {
-  const float x2 = x * x;
-  const float t = tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x2));
-  const float du = 0.7978845608028654f * (1.f + 3.f * 0.044715f * x2);
-  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
-}
-
-// v[i] = f(v[i], rr[i]) for the 32 values of one row chunk; the switch is outside the loop.
-__device__ __forceinline__ void apply_epi32(float* v, const float* rr, int epi) {
-  switch (epi) {
-    case FTK_EPI_GELU_TANH:
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
-      break;
-    case FTK_EPI_GELU_ERF:
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = gelu_erf_f(v[i]);
-      break;
-    case FTK_EPI_RELU:
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = v[i] > 0.f ? v[i] : 0.f;
-      break;
-    case FTK_EPI_MUL_DGELU_TANH:
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] *= gelu_tanh_grad_fast(rr[i]);
-      break;
-    case FTK_EPI_MUL_DGELU_ERF:
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad_f(rr[i]);
-      break;
-    case FTK_EPI_MUL_DRELU:
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = rr[i] > 0.f ? v[i] : 0.f;
-      break;
-    default:
-      break;
-  }
-}
-
-template <int BN>
-__global__ void __launch_bounds__(G_THREADS, 1)
-gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
-                       const __grid_constant__ CUtensorMap tmB, const GemmArgs p) {
-  using Cfg = GemmCfg<BN>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~uintptr_t(1023));
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + Cfg::STAGES * Cfg::A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES));
-  uint64_t* full = bars;
-  uint64_t* empty = bars + Cfg::STAGES;
-  uint64_t* tfull = bars + 2 * Cfg::STAGES;
-  uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
-  int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  WaitCtx ctx{p.status, abort_f};
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < Cfg::STAGES; ++i) {
-      mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], G_EPI_WARPS);
-    }
-    *abort_f = 0;
-    fence_mbar_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  const int tiles_m = (p.M + G_BM - 1) / G_BM;
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int tiles_mn = tiles_m * tiles_n;
-  const int nbatch = p.L0 * p.L1;
-  const int total = tiles_mn * nbatch * p.splits;  // work item = (split, batch, n tile, m tile)
-  const int kblocks_all = (p.K + G_BK - 1) / G_BK;
-  const int kb_per_split = (kblocks_all + p.splits - 1) / p.splits;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      tma_prefetch_desc(&tmA);
-      tma_prefetch_desc(&tmB);
-    }
-    int s = 0;
-    uint32_t ph = 0;
-    bool ok = true;
-    for (int item = blockIdx.x; ok && item < total; item += gridDim.x) {
-      const int sp = item / (tiles_mn * nbatch);
-      const int rem = item - sp * (tiles_mn * nbatch);
-      const int l = rem / tiles_mn;
-      const int t = rem - l * tiles_mn;
-      const int m_t = t % tiles_m, n_t = t / tiles_m;
-      const int l0 = l % p.L0, l1 = l / p.L0;
-      const int kb0 = sp * kb_per_split;
-      const int kb1 = min(kblocks_all, kb0 + kb_per_split);
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(&empty[s], ph ^ 1u, ctx, FT_ERR_WAIT_EMPTY)) {
-          ok = false;
-          break;
-        }
-        if (lane == 0) {
-          mbar_arrive_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
-          uint8_t* a_dst = sA + s * Cfg::A_BYTES;
-          uint8_t* b_dst = sB + s * Cfg::B_BYTES;
-          if (!p.a_mn) {
-            tma_load_4d(a_dst, &tmA, &full[s], kb * G_BK, m_t * G_BM, l0, l1);
-          } else {
-#pragma unroll
-            for (int c = 0; c < G_BM / 64; ++c)
-              tma_load_4d(a_dst + c * (G_BK * 128), &tmA, &full[s], m_t * G_BM + c * 64, kb * G_BK,
-                          l0, l1);
-          }
-          if (!p.b_mn) {
-            tma_load_4d(b_dst, &tmB, &full[s], kb * G_BK, n_t * BN, l0, l1);
-          } else {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_4d(b_dst + c * (G_BK * 128), &tmB, &full[s], n_t * BN + c * 64, kb * G_BK,
-                          l0, l1);
-          }
-        }
-        __syncwarp();
-        if (++s == Cfg::STAGES) {
-          s = 0;
-          ph ^= 1u;
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = make_idesc_bf16(G_BM, BN, p.a_mn, p.b_mn);
-    const uint32_t a_lbo = p.a_mn ? G_BK * 128 : 16, a_adv = p.a_mn ? G_UMMA_K * 128 : G_UMMA_K * 2;
-    const uint32_t b_lbo = p.b_mn ? G_BK * 128 : 16, b_adv = p.b_mn ? G_UMMA_K * 128 : G_UMMA_K * 2;
-    int s = 0;
-    uint32_t ph = 0;
-    int acc = 0;
-    uint32_t acc_ph = 0;  // bit a = phase of accumulator a
-    bool ok = true;
-    for (int item = blockIdx.x; ok && item < total; item += gridDim.x) {
-      const int sp = item / (tiles_mn * nbatch);
-      const int kb0 = sp * kb_per_split;
-      const int kb1 = min(kblocks_all, kb0 + kb_per_split);
-      if (!mbar_wait(&tempty[acc], ((acc_ph >> acc) & 1u) ^ 1u, ctx, FT_ERR_WAIT_TMEM_EMPTY)) break;
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(&full[s], ph, ctx, FT_ERR_WAIT_FULL)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_addr = smem_u32(sA + s * Cfg::A_BYTES);
-          const uint32_t b_addr = smem_u32(sB + s * Cfg::B_BYTES);
-#pragma unroll
-          for (int k = 0; k < G_BK / G_UMMA_K; ++k) {
-            umma_bf16(d_tmem, make_smem_desc(a_addr + k * a_adv, a_lbo, 1024),
-                      make_smem_desc(b_addr + k * b_adv, b_lbo, 1024), idesc,
-                      (kb > kb0 || k > 0) ? 1u : 0u);
-          }
-          umma_commit(&empty[s]);
-          if (kb == kb1 - 1) umma_commit(&tfull[acc]);
-        }
-        __syncwarp();
-        if (++s == Cfg::STAGES) {
-          s = 0;
-          ph ^= 1u;
-        }
-      }
-      if (kb1 <= kb0 && lane == 0) umma_commit(&tfull[acc]);  // empty split: nothing to wait for
-      __syncwarp();
-      acc_ph ^= (1u << acc);
-      acc ^= 1;
-    }
-  } else {
-    // ------------------------------------------------------------ epilogue (8 warps)
-    const int ew = warp - 2;
-    const int q = warp & 3;               // TMEM lane quarter this warp may read
-    const int half = ew >> 2;             // which half of the tile's columns
-    const int row_in_tile = q * 32 + lane;
-    constexpr int CHUNKS = BN / 32;
-    constexpr int C_HALF = (CHUNKS + 1) / 2;
-    const int c_begin = half == 0 ? 0 : C_HALF;
-    const int c_end = half == 0 ? C_HALF : CHUNKS;
-    int acc = 0;
-    uint32_t acc_ph = 0;
-    for (int item = blockIdx.x; item < total; item += gridDim.x) {
-      const int sp = item / (tiles_mn * nbatch);
-      const int rem = item - sp * (tiles_mn * nbatch);
-      const int l = rem / tiles_mn;
-      const int t = rem - l * tiles_mn;
-      const int m_t = t % tiles_m, n_t = t / tiles_m;
-      const int l0 = l % p.L0, l1 = l / p.L0;
-      const bool empty_split = (sp * kb_per_split >= kblocks_all);
-      if (!mbar_wait(&tfull[acc], (acc_ph >> acc) & 1u, ctx, FT_ERR_WAIT_TMEM_FULL)) break;
-      tc_fence_after();
-      const long long row = (long long)m_t * G_BM + row_in_tile;
-      const long long d_off = l0 * p.d_s0 + l1 * p.d_s1 + row * p.ldd;
-      const long long r_off = l0 * p.r_s0 + l1 * p.r_s1 + row * p.ldr;
-      const bool need_r = p.resid != nullptr;
-#pragma unroll 1
-      for (int ci = c_begin; ci < c_end; ++ci) {
-        const int c0 = ci * 32;
-        uint32_t r[32];
-        tmem_ld32(tmem_base + acc * Cfg::ACC_STRIDE + c0 + ((uint32_t)(q * 32) << 16), r);
-        tmem_ld_wait();
-        const int n0 = n_t * BN + c0;
-        if (row < p.M && n0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = empty_split ? 0.f : __uint_as_float(r[i]) * p.alpha;
-          const bool full_chunk = (n0 + 32 <= p.N);
-          if (p.splits > 1) {
-            // raw partial tile -> workspace [split][batch][M][N] (fp32)
-            float* wp = p.ws + (((long long)sp * nbatch + l) * p.M + row) * p.N + n0;
-            if (full_chunk && ((reinterpret_cast<uintptr_t>(wp) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                reinterpret_cast<float4*>(wp)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else {
-              for (int i = 0; i < 32; ++i)
-                if (n0 + i < p.N) wp[i] = v[i];
-            }
-            continue;
-          }
-          if (p.bias) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (full_chunk || n0 + i < p.N) v[i] += __bfloat162float(__ldg(p.bias + n0 + i));
-          }
-          if (p.aux) {
-            __nv_bfloat16* ap = p.aux + d_off + n0;
-            if (full_chunk && ((reinterpret_cast<uintptr_t>(ap) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint4 o;
-                o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
-                o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
-                o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
-                o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
-                reinterpret_cast<uint4*>(ap)[i] = o;
-              }
-            } else {
-              for (int i = 0; i < 32; ++i)
-                if (n0 + i < p.N) ap[i] = __float2bfloat16(v[i]);
-            }
-          }
-          float rr[32];
-          if (need_r) {
-            const __nv_bfloat16* rp = p.resid + r_off + n0;
-            if (full_chunk && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint4 u = __ldg(reinterpret_cast<const uint4*>(rp) + i);
-                float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
-                       f3 = unpack_bf16(u.w);
-                rr[8 * i + 0] = f0.x; rr[8 * i + 1] = f0.y; rr[8 * i + 2] = f1.x;
-                rr[8 * i + 3] = f1.y; rr[8 * i + 4] = f2.x; rr[8 * i + 5] = f2.y;
-                rr[8 * i + 6] = f3.x; rr[8 * i + 7] = f3.y;
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                rr[i] = (n0 + i < p.N) ? __bfloat162float(rp[i]) : 0.f;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) rr[i] = 0.f;
-          }
-          const bool r_is_operand = (p.epi >= FTK_EPI_MUL_DGELU_TANH);
-          if (p.epi != FTK_EPI_NONE) apply_epi32(v, rr, p.epi);
-          if (need_r && !r_is_operand) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += rr[i];
-          }
-          if (p.out_fp32) {
-            float* dp = reinterpret_cast<float*>(p.D) + d_off + n0;
-            if (full_chunk && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                if (p.accumulate) {
-                  float4 old = reinterpret_cast<float4*>(dp)[i];
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                reinterpret_cast<float4*>(dp)[i] = o;
-              }
-            } else {
-              for (int i = 0; i < 32; ++i)
-                if (n0 + i < p.N) dp[i] = p.accumulate ? dp[i] + v[i] : v[i];
-            }
-          } else {
-            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + d_off + n0;
-            if (full_chunk && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                if (p.accumulate) {
-                  uint4 u = reinterpret_cast<uint4*>(dp)[i];
-                  float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
-                         f3 = unpack_bf16(u.w);
-                  v[8 * i + 0] += f0.x; v[8 * i + 1] += f0.y; v[8 * i + 2] += f1.x;
-                  v[8 * i + 3] += f1.y; v[8 * i + 4] += f2.x; v[8 * i + 5] += f2.y;
-                  v[8 * i + 6] += f3.x; v[8 * i + 7] += f3.y;
-                }
-                uint4 o;
-                o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
-                o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
-                o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
-                o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
-                reinterpret_cast<uint4*>(dp)[i] = o;
-              }
-            } else {
-              for (int i = 0; i < 32; ++i)
-                if (n0 + i < p.N)
-                  dp[i] = __float2bfloat16(p.accumulate ? __bfloat162float(dp[i]) + v[i] : v[i]);
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
-      acc_ph ^= (1u << acc);
-      acc ^= 1;
-    }
-  }
-
-  // ---------------------------------------------------------------- teardown
-  if (*abort_f) {
-    // give copies and MMAs still in flight time to land before smem/TMEM go away
-    for (int i = 0; i < 100; ++i) __nanosleep(10000);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-}
 
 // D (+)= sum over splits (ascending) of ws[split]; 4 outputs per thread.
 __global__ void __launch_bounds__(256)
@@ -453,6 +60,8 @@ splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ D, long lo
     }
   }
 }
+
+__global__ void tick_i32_kernel(int* w) { *w += 1; }
 
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -512,7 +121,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   using Cfg = GemmCfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100_kernel<BN>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100_kernel<BN, 0>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
@@ -520,13 +129,51 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   long long items = (long long)((a.M + G_BM - 1) / G_BM) * ((a.N + BN - 1) / BN) * a.L0 * a.L1 * a.splits;
   int grid = (int)(items < max_ctas ? items : max_ctas);
   if (grid <= 0) return 0;
-  gemm_bf16_sm100_kernel<BN><<<grid, G_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, a);
+  CommArgs none;
+  memset(&none, 0, sizeof(none));
+  gemm_bf16_sm100_kernel<BN, 0><<<grid, G_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, a, none);
   return (int)cudaGetLastError();
+}
+
+static int make_operand_maps(const FtkGemmDesc* g, int L0, int L1, int bn, CUtensorMap* tmA,
+                             CUtensorMap* tmB) {
+  int rc;
+  if (!g->a_mn)
+    rc = ftk_make_tmap_bf16(tmA, g->A, g->K, g->M, L0, L1, g->lda, g->a_s0, g->a_s1, G_BK, G_BM);
+  else
+    rc = ftk_make_tmap_bf16(tmA, g->A, g->M, g->K, L0, L1, g->lda, g->a_s0, g->a_s1, 64, G_BK);
+  if (rc) return 1000 + rc;
+  if (!g->b_mn)
+    rc = ftk_make_tmap_bf16(tmB, g->B, g->K, g->N, L0, L1, g->ldb, g->b_s0, g->b_s1, G_BK, bn);
+  else
+    rc = ftk_make_tmap_bf16(tmB, g->B, g->N, g->K, L0, L1, g->ldb, g->b_s0, g->b_s1, 64, G_BK);
+  if (rc) return 2000 + rc;
+  return 0;
+}
+
+static void fill_gemm_args(GemmArgs& a, const FtkGemmDesc* g, int L0, int L1) {
+  a.M = g->M; a.N = g->N; a.K = g->K; a.L0 = L0; a.L1 = L1;
+  a.a_mn = g->a_mn ? 1 : 0; a.b_mn = g->b_mn ? 1 : 0;
+  a.D = g->D; a.ldd = g->ldd; a.d_s0 = g->d_s0; a.d_s1 = g->d_s1;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(g->bias);
+  a.resid = reinterpret_cast<const __nv_bfloat16*>(g->resid);
+  a.ldr = g->ldr; a.r_s0 = g->r_s0; a.r_s1 = g->r_s1;
+  a.aux = reinterpret_cast<__nv_bfloat16*>(g->aux);
+  a.alpha = g->alpha; a.epi = g->epi; a.out_fp32 = g->out_fp32; a.accumulate = g->accumulate;
+  a.splits = 1;
+  a.ws = reinterpret_cast<float*>(g->workspace);
+  a.status = ftk_status_word();
 }
 
 }  // namespace ftk
 
 using namespace ftk;
+
+extern "C" int ftk_tick_i32(int* word, void* stream_v) {
+  if (!word) return -2;
+  tick_i32_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(word);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
@@ -580,30 +227,12 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   if (bn != 128 && bn != 192 && bn != 256) return -5;
 
   CUtensorMap tmA, tmB;
-  int rc;
-  if (!g->a_mn)
-    rc = ftk_make_tmap_bf16(&tmA, g->A, g->K, g->M, L0, L1, g->lda, g->a_s0, g->a_s1, G_BK, G_BM);
-  else
-    rc = ftk_make_tmap_bf16(&tmA, g->A, g->M, g->K, L0, L1, g->lda, g->a_s0, g->a_s1, 64, G_BK);
-  if (rc) return 1000 + rc;
-  if (!g->b_mn)
-    rc = ftk_make_tmap_bf16(&tmB, g->B, g->K, g->N, L0, L1, g->ldb, g->b_s0, g->b_s1, G_BK, bn);
-  else
-    rc = ftk_make_tmap_bf16(&tmB, g->B, g->N, g->K, L0, L1, g->ldb, g->b_s0, g->b_s1, 64, G_BK);
-  if (rc) return 2000 + rc;
+  int rc = make_operand_maps(g, L0, L1, bn, &tmA, &tmB);
+  if (rc) return rc;
 
   GemmArgs a;
-  a.M = g->M; a.N = g->N; a.K = g->K; a.L0 = L0; a.L1 = L1;
-  a.a_mn = g->a_mn ? 1 : 0; a.b_mn = g->b_mn ? 1 : 0;
-  a.D = g->D; a.ldd = g->ldd; a.d_s0 = g->d_s0; a.d_s1 = g->d_s1;
-  a.bias = reinterpret_cast<const __nv_bfloat16*>(g->bias);
-  a.resid = reinterpret_cast<const __nv_bfloat16*>(g->resid);
-  a.ldr = g->ldr; a.r_s0 = g->r_s0; a.r_s1 = g->r_s1;
-  a.aux = reinterpret_cast<__nv_bfloat16*>(g->aux);
-  a.alpha = g->alpha; a.epi = g->epi; a.out_fp32 = g->out_fp32; a.accumulate = g->accumulate;
+  fill_gemm_args(a, g, L0, L1);
   a.splits = splits;
-  a.ws = reinterpret_cast<float*>(g->workspace);
-  a.status = ftk_status_word();
   if (!a.status) return -6;
   rc = bn == 256 ? launch_gemm<256>(tmA, tmB, a, sms, stream)
                  : (bn == 192 ? launch_gemm<192>(tmA, tmB, a, sms, stream)
@@ -614,5 +243,77 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   if (blocks > 148 * 8) blocks = 148 * 8;
   splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(a.ws, g->D, g->M, g->N, g->ldd, splits,
                                                             g->out_fp32, g->accumulate);
+  return (int)cudaGetLastError();
+}
+
+// GEMM fused with all-gather of an operand or reduce-scatter of the output (see ftk_api.h).
+extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (!g || !cd || g->M <= 0 || g->N <= 0 || g->K <= 0) return -2;
+  if (cd->world < 1 || cd->world > FTK_MAX_RANKS || cd->rank < 0 || cd->rank >= cd->world) return -2;
+  if (cd->mode < FTK_COMM_GATHER_A || cd->mode > FTK_COMM_SCATTER_D || !cd->epoch) return -2;
+  if ((g->L0 > 1) || (g->L1 > 1)) return -2;
+  if ((reinterpret_cast<uintptr_t>(g->A) & 15) || (reinterpret_cast<uintptr_t>(g->B) & 15)) return -3;
+  if ((g->lda % 8) || (g->ldb % 8)) return -4;
+  if (cd->chunk_rows <= 0 || cd->chunk_rows % G_BM) return -7;
+  constexpr int BN = 256;
+  const long long rows_total = (long long)cd->chunk_rows * cd->world;
+
+  CommArgs c;
+  memset(&c, 0, sizeof(c));
+  c.mode = cd->mode; c.rank = cd->rank; c.world = cd->world; c.chunk_rows = cd->chunk_rows;
+  c.epoch = cd->epoch;
+  const int sms = g->max_ctas > 0 ? g->max_ctas : num_sms();
+  c.comm_ctas = cd->comm_ctas > 0 ? cd->comm_ctas : 16;
+  if (c.comm_ctas >= sms) return -7;
+
+  if (cd->mode == FTK_COMM_SCATTER_D) {
+    if (rows_total != g->M || (g->N % 8) || (g->ldd % 8) || (g->resid && (g->ldr % 8))) return -7;
+    if (g->epi != FTK_EPI_NONE || g->aux) return -7;
+    for (int r = 0; r < cd->world; ++r) {
+      if (!cd->inbox[r] || !cd->arrive[r]) return -2;
+      c.inbox[r] = reinterpret_cast<__nv_bfloat16*>(cd->inbox[r]);
+      c.arrive[r] = cd->arrive[r];
+    }
+  } else {
+    const bool ga = cd->mode == FTK_COMM_GATHER_A;
+    // the staged operand must be contiguous [rows, K] so that a subtile is one byte range
+    if (ga ? (g->a_mn || g->lda != g->K || rows_total != g->M)
+           : (g->b_mn || g->ldb != g->K || rows_total != g->N))
+      return -7;
+    c.sub_bytes = (long long)G_BM * g->K * 2;
+    if (c.sub_bytes > G_COPY_SLOT ? (c.sub_bytes % G_COPY_SLOT) : (c.sub_bytes % 16)) return -7;
+    if (!cd->sub_flags) return -2;
+    c.full = reinterpret_cast<uint8_t*>(const_cast<void*>(ga ? g->A : g->B));
+    c.sub_flags = cd->sub_flags;
+    c.ready_local = cd->ready_local;
+    for (int r = 0; r < cd->world; ++r) {
+      if (!cd->src[r] || (reinterpret_cast<uintptr_t>(cd->src[r]) & 15)) return -3;
+      c.src[r] = reinterpret_cast<const uint8_t*>(cd->src[r]);
+      c.ready_peer[r] = cd->ready_peer[r];
+      if (cd->ready_local && r != cd->rank && !cd->ready_peer[r]) return -2;
+    }
+  }
+
+  CUtensorMap tmA, tmB;
+  int rc = make_operand_maps(g, 1, 1, BN, &tmA, &tmB);
+  if (rc) return rc;
+  GemmArgs a;
+  fill_gemm_args(a, g, 1, 1);
+  if (!a.status) return -6;
+
+  using Cfg = GemmCfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100_kernel<BN, 1>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const long long items = (long long)((a.M + G_BM - 1) / G_BM) * ((a.N + BN - 1) / BN);
+  long long n_compute = sms - c.comm_ctas;
+  if (items < n_compute) n_compute = items;
+  const int grid = (int)n_compute + c.comm_ctas;   // all CTAs resident: one per SM
+  gemm_bf16_sm100_kernel<BN, 1><<<grid, G_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, a, c);
   return (int)cudaGetLastError();
 }
