@@ -189,7 +189,7 @@ template <int BN, int COMM>
 __device__ __forceinline__ TileCoord decode_item(int item, const GemmArgs& p, const CommArgs& c,
                                                  int tiles_m, int tiles_n, int nbatch) {
   TileCoord t;
-  if (!COMM || c.mode == FTK_COMM_NONE) {
+  if (!COMM || c.mode == FTK_COMM_NONE || (c.mode == FTK_COMM_GATHER_B && p.b_mn)) {
     const int tiles_mn = tiles_m * tiles_n;
     t.sp = item / (tiles_mn * nbatch);
     const int rem = item - t.sp * (tiles_mn * nbatch);
@@ -455,13 +455,15 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
+    int k_ready = 0;
     for (int item = blockIdx.x; ok && item < total; item += n_compute) {
       const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
       const int m_t = t.m_t, n_t = t.n_t;
       const int l0 = t.l % p.L0, l1 = t.l / p.L0;
       const int kb0 = t.sp * kb_per_split;
       const int kb1 = min(kblocks_all, kb0 + kb_per_split);
-      if (COMM && (c.mode == FTK_COMM_GATHER_A || c.mode == FTK_COMM_GATHER_B)) {
+      const bool k_sharded = COMM && c.mode == FTK_COMM_GATHER_B && p.b_mn;
+      if (COMM && !k_sharded && (c.mode == FTK_COMM_GATHER_A || c.mode == FTK_COMM_GATHER_B)) {
         // the staged subtiles this tile reads must have landed
         int f0, f1;
         if (c.mode == FTK_COMM_GATHER_A) {
@@ -479,6 +481,21 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         if (!good) break;
       }
       for (int kb = kb0; kb < kb1; ++kb) {
+        if (k_sharded) {
+          // B is sharded along K: rows [0, k_ready * 128) of the staged operand are known final
+          const int need = (min(p.K, kb * G_BK + G_BK) - 1) / G_BM + 1;
+          while (ok && k_ready < need) {
+            int good = 1;
+            if (lane == 0) {
+              good = flag_wait<false>(c.sub_flags + k_ready, epoch, ctx) ? 1 : 0;
+              fence_proxy_async_all();
+            }
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (!good) ok = false;
+            ++k_ready;
+          }
+          if (!ok) break;
+        }
         if (!mbar_wait(&empty[s], ph ^ 1u, ctx, FT_ERR_WAIT_EMPTY)) {
           ok = false;
           break;

@@ -278,10 +278,12 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   } else {
     const bool ga = cd->mode == FTK_COMM_GATHER_A;
     // the staged operand must be contiguous [rows, K] so that a subtile is one byte range
+    // (B given MN-major, i.e. [K, N] row-major, is sharded along K: dgrad with a sharded weight)
+    const bool bk = !ga && g->b_mn;
     if (ga ? (g->a_mn || g->lda != g->K || rows_total != g->M)
-           : (g->b_mn || g->ldb != g->K || rows_total != g->N))
+           : (bk ? (g->ldb != g->N || rows_total != g->K) : (g->ldb != g->K || rows_total != g->N)))
       return -7;
-    c.sub_bytes = (long long)G_BM * g->K * 2;
+    c.sub_bytes = (long long)G_BM * (bk ? g->N : g->K) * 2;
     if (c.sub_bytes > G_COPY_SLOT ? (c.sub_bytes % G_COPY_SLOT) : (c.sub_bytes % 16)) return -7;
     if (!cd->sub_flags) return -2;
     c.full = reinterpret_cast<uint8_t*>(const_cast<void*>(ga ? g->A : g->B));

@@ -50,6 +50,23 @@ class FtkAttnDesc(C.Structure):
     ]
 
 
+FTK_MAX_RANKS = 8
+COMM_GATHER_A, COMM_GATHER_B, COMM_SCATTER_D = 1, 2, 3
+
+
+class FtkCommDesc(C.Structure):
+    _fields_ = [
+        ("mode", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("comm_ctas", C.c_int),
+        ("chunk_rows", C.c_int),
+        ("src", C.c_void_p * FTK_MAX_RANKS),
+        ("sub_flags", C.c_void_p), ("ready_local", C.c_void_p),
+        ("ready_peer", C.c_void_p * FTK_MAX_RANKS),
+        ("inbox", C.c_void_p * FTK_MAX_RANKS),
+        ("arrive", C.c_void_p * FTK_MAX_RANKS),
+        ("epoch", C.c_void_p),
+    ]
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 
@@ -70,6 +87,8 @@ def load(build_if_missing: bool = True):
     lib.ftk_status_word.restype = C.c_void_p
     lib.ftk_read_status.argtypes = [C.c_int]
     lib.ftk_gemm_bf16.argtypes = [C.POINTER(FtkGemmDesc), C.c_void_p]
+    lib.ftk_gemm_comm_bf16.argtypes = [C.POINTER(FtkGemmDesc), C.POINTER(FtkCommDesc), C.c_void_p]
+    lib.ftk_tick_i32.argtypes = [C.c_void_p, C.c_void_p]
     lib.ftk_attn_fwd.argtypes = [C.POINTER(FtkAttnDesc), C.c_void_p]
     lib.ftk_attn_bwd.argtypes = [C.POINTER(FtkAttnDesc), C.c_void_p]
     vp, i, f, ll, ull = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_ulonglong

@@ -1,0 +1,205 @@
+"""GEMMs fused with their collective over NVLink peer memory (one kernel per op).
+
+Three forms of the tcgen05 GEMM kernel (``csrc/gemm_kernel.cuh``), each one launch in which a
+few CTAs move data between GPUs while the rest multiply:
+
+* :meth:`FusedCollectives.allgather_a_gemm`  - all-gather of row-sharded activations feeding
+  the A operand (tensor-parallel column-parallel Linear with sequence parallelism);
+* :meth:`FusedCollectives.allgather_b_gemm`  - all-gather of a row-sharded weight feeding the
+  B operand (ZeRO-3 parameter gather fused into the first GEMM that consumes it), forward
+  (``x W^T``) and dgrad (``dy W``, weight sharded along the reduction dimension);
+* :meth:`FusedCollectives.gemm_reduce_scatter` - the epilogue stores bf16 partial tiles into the
+  owning rank's inbox and the owner adds them in ascending rank order (row-parallel Linear,
+  ZeRO-3 weight-gradient reduce-scatter).
+
+The reference has no distributed layer at all (FEATURE_PARITY.md:176); the Linear math is
+ft-nn/src/lib.rs:1076-1100 and ft-kernel-cpu/src/lib.rs:17162-17302.
+
+Protocol state: every flag word stores the *epoch* (use count) of the call that set it, so
+flag arrays are never cleared and can be shared by calls of different shapes.  The epoch lives
+in device memory and is advanced by a one-thread kernel before each launch, which keeps the
+sequence replayable inside a CUDA graph.  Shard buffers and inboxes that change between calls
+must alternate between two slots: a rank can run at most one collective ahead of its slowest
+peer, because every collective needs a contribution of every rank.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops import kernels as K
+from ..ops._lib import (COMM_GATHER_A, COMM_GATHER_B, COMM_SCATTER_D, FtkCommDesc, FtkGemmDesc)
+from .symm import SymmetricBuffer
+
+TILE_M = 128
+TILE_N = 256
+
+
+class SymmTensor:
+    """A tensor inside a :class:`SymmetricBuffer` together with its address on every rank."""
+
+    def __init__(self, buf: SymmetricBuffer, shape: Sequence[int], dtype: torch.dtype, byte_offset: int = 0):
+        n = 1
+        for s in shape:
+            n *= int(s)
+        self.buf = buf
+        self.t = buf.tensor(dtype, n, byte_offset).view(*shape)
+        self.peer_ptrs: List[int] = [p + byte_offset for p in buf.peer_ptrs]
+
+    @staticmethod
+    def alloc(shape: Sequence[int], dtype: torch.dtype, group, device) -> "SymmTensor":
+        n = 1
+        for s in shape:
+            n *= int(s)
+        buf = SymmetricBuffer(n * torch.empty((), dtype=dtype).element_size(), group, device)
+        return SymmTensor(buf, shape, dtype)
+
+
+class FusedCollectives:
+    """Flag storage, inboxes and launch helpers for the collective-fused GEMMs of one group."""
+
+    def __init__(self, group: Optional[dist.ProcessGroup], device: torch.device, *,
+                 max_gather_rows: int = 1 << 17, max_inbox_elems: int = 0, max_chunk_tiles: int = 4096,
+                 comm_ctas: int = 16):
+        self.group, self.device = group, device
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.comm_ctas = comm_ctas
+        self.lib = _lib.load()
+        # local words: [0] epoch, then one flag per 128-row subtile of a gathered operand
+        self.local = torch.zeros(64 + max_gather_rows // TILE_M, dtype=torch.int32, device=device)
+        self.epoch = self.local[0:1]
+        self.sub_flags = self.local[64:]
+        # symmetric words: ready[world] | arrive[2][max_chunk_tiles][world]
+        self.max_chunk_tiles = max_chunk_tiles
+        words = 64 + 2 * max_chunk_tiles * self.world
+        self.flags = SymmetricBuffer(words * 4, group, device)
+        self.flags.bytes.zero_()
+        self.max_inbox_elems = max_inbox_elems
+        self.inbox = None
+        if max_inbox_elems:
+            # two slots of [world][chunk_rows][N] bf16
+            self.inbox = SymmetricBuffer(2 * max_inbox_elems * 2, group, device)
+        self._slot = 0
+        torch.cuda.synchronize(device)
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    # ------------------------------------------------------------------ helpers
+    def _tick(self) -> None:
+        K._chk(self.lib.ftk_tick_i32(self.epoch.data_ptr(), K._stream()), "ftk_tick_i32")
+
+    def _comm(self, mode: int, chunk_rows: int) -> FtkCommDesc:
+        c = FtkCommDesc()
+        c.mode, c.rank, c.world = mode, self.rank, self.world
+        c.comm_ctas, c.chunk_rows = self.comm_ctas, chunk_rows
+        c.epoch = self.epoch.data_ptr()
+        return c
+
+    @staticmethod
+    def _gemm_desc(a, b, out, *, a_mn=False, b_mn=False, bias=None, resid=None, aux=None, epi=K.EPI_NONE,
+                   alpha=1.0, accumulate=False, M=None, N=None, K_=None) -> FtkGemmDesc:
+        g = FtkGemmDesc()
+        g.M, g.N, g.K, g.L0, g.L1 = M, N, K_, 1, 1
+        g.a_mn, g.b_mn = int(a_mn), int(b_mn)
+        g.A, g.lda = a.data_ptr(), a.stride(0)
+        g.B, g.ldb = b.data_ptr(), b.stride(0)
+        g.D, g.ldd = out.data_ptr(), out.stride(0)
+        g.bias = None if bias is None else bias.data_ptr()
+        if resid is not None:
+            g.resid, g.ldr = resid.data_ptr(), resid.stride(0)
+        if aux is not None:
+            g.aux = aux.data_ptr()
+        g.alpha, g.epi = float(alpha), int(epi)
+        g.out_fp32 = 1 if out.dtype == torch.float32 else 0
+        g.accumulate = int(accumulate)
+        return g
+
+    def _gather(self, c: FtkCommDesc, shard: SymmTensor, handshake: bool) -> None:
+        for r in range(self.world):
+            c.src[r] = shard.peer_ptrs[r]
+        n_sub = c.chunk_rows // TILE_M * self.world
+        if n_sub > self.sub_flags.numel():
+            raise K.KernelError("gathered operand has more 128-row subtiles than flag words")
+        c.sub_flags = self.sub_flags.data_ptr()
+        if handshake and self.world > 1:
+            c.ready_local = self.flags.local_ptr
+            for r in range(self.world):
+                c.ready_peer[r] = self.flags.peer_ptrs[r] + 4 * self.rank
+
+    # ------------------------------------------------------------------ all-gather -> GEMM (A)
+    def allgather_a_gemm(self, x_shard: SymmTensor, w: torch.Tensor, x_full: torch.Tensor, *,
+                         b_mn: bool = False, bias=None, epi=K.EPI_NONE, resid=None, aux=None, out=None,
+                         handshake: bool = True) -> torch.Tensor:
+        """``out = epi(allgather(x_shard) @ op(w) + bias)``; ``x_full`` receives the gathered rows.
+
+        ``x_shard.t`` is ``[rows / world, K]`` in symmetric memory, ``x_full`` ``[rows, K]`` local
+        scratch (contiguous); ``w`` is ``[N, K]`` or, with ``b_mn``, ``[K, N]``.
+        """
+        ms, k = x_shard.t.shape
+        m = ms * self.world
+        n = w.shape[1] if b_mn else w.shape[0]
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
+        g = self._gemm_desc(x_full, w, out, b_mn=b_mn, bias=bias, resid=resid, aux=aux, epi=epi, M=m, N=n, K_=k)
+        c = self._comm(COMM_GATHER_A, ms)
+        self._gather(c, x_shard, handshake)
+        self._tick()
+        K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(gather A)")
+        return out
+
+    # ------------------------------------------------------------------ all-gather -> GEMM (B)
+    def allgather_b_gemm(self, x: torch.Tensor, w_shard: SymmTensor, w_full: torch.Tensor, *,
+                         dgrad: bool = False, bias=None, epi=K.EPI_NONE, resid=None, aux=None, out=None,
+                         handshake: bool = False) -> torch.Tensor:
+        """Forward ``x @ W^T`` or (``dgrad``) ``x @ W`` with ``W = allgather(w_shard)`` ``[out, in]``.
+
+        The weight is sharded by output rows.  ``w_full`` ``[out, in]`` is local scratch that holds
+        the gathered weight afterwards (a later GEMM of the same layer may reuse it).
+        """
+        rows_s, cols = w_shard.t.shape
+        rows = rows_s * self.world
+        m = x.shape[0]
+        n, k = (cols, rows) if dgrad else (rows, cols)
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
+        g = self._gemm_desc(x, w_full, out, b_mn=dgrad, bias=bias, resid=resid, aux=aux, epi=epi, M=m, N=n, K_=k)
+        c = self._comm(COMM_GATHER_B, rows_s)
+        self._gather(c, w_shard, handshake)
+        self._tick()
+        K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(gather B)")
+        return out
+
+    # ------------------------------------------------------------------ GEMM -> reduce-scatter
+    def gemm_reduce_scatter(self, a: torch.Tensor, b: torch.Tensor, out_shard: torch.Tensor, *,
+                            a_mn: bool = False, b_mn: bool = False, bias=None, resid=None,
+                            accumulate: bool = False, alpha: float = 1.0) -> torch.Tensor:
+        """``out_shard = rows[rank] of sum_over_ranks(a @ op(b)) (+ bias) (+ resid) (+ out_shard)``.
+
+        The full product is ``[M, N]`` with ``M = world * out_shard.shape[0]``; partial tiles cross
+        NVLink as bf16 and are added in ascending rank order in fp32.
+        """
+        m = a.shape[1] if a_mn else a.shape[0]
+        k = a.shape[0] if a_mn else a.shape[1]
+        n = b.shape[1] if b_mn else b.shape[0]
+        ms = out_shard.shape[0]
+        if ms * self.world != m or out_shard.shape[1] != n:
+            raise K.KernelError(f"reduce-scatter output {tuple(out_shard.shape)} does not match [{m}/{self.world}, {n}]")
+        tiles = (ms // TILE_M) * ((n + TILE_N - 1) // TILE_N)
+        if self.inbox is None or self.world * ms * n > self.max_inbox_elems or tiles > self.max_chunk_tiles:
+            raise K.KernelError("inbox / flag storage too small for this reduce-scatter")
+        g = self._gemm_desc(a, b, out_shard, a_mn=a_mn, b_mn=b_mn, bias=bias, resid=resid, alpha=alpha,
+                            accumulate=accumulate, M=m, N=n, K_=k)
+        c = self._comm(COMM_SCATTER_D, ms)
+        slot = self._slot
+        self._slot ^= 1
+        for r in range(self.world):
+            c.inbox[r] = self.inbox.peer_ptrs[r] + slot * self.max_inbox_elems * 2
+            c.arrive[r] = self.flags.peer_ptrs[r] + 4 * (64 + slot * self.max_chunk_tiles * self.world)
+        self._tick()
+        K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(scatter)")
+        return out_shard

@@ -18,6 +18,16 @@ def _run_workers(script, nproc, port, timeout=300):
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
 
 
+def test_collective_fused_gemms(cuda_device):
+    """all-gather -> GEMM (A and B operand) and GEMM -> reduce-scatter against fp32 references."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    nproc = 2 if n < 4 else 4
+    p = _run_workers("_comm_worker.py", nproc, 29633)
+    assert p.returncode == 0 and "COMM_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
 def test_fused_data_parallel_matches_nccl_and_replays(cuda_device):
     n = torch.cuda.device_count()
     if n < 2:
