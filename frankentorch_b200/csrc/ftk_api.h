@@ -89,6 +89,33 @@ typedef struct FtkCommDesc {
 int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* c, void* stream);
 int ftk_tick_i32(int* word, void* stream);    // *word += 1 on the stream
 
+// ---- mixture of experts: top-2 routing and expert-parallel all-to-alls over peer memory ---
+// Expert e lives on rank e / (E / world).  A rank sends at most `capacity` rows to each expert;
+// receive buffers are [E / world][world][capacity][d] bf16 on every rank (symmetric).
+typedef struct FtkMoeDesc {
+  int T, d, E, capacity, rank, world;
+  const int* idx;      // [T, 2] chosen experts
+  const int* slot;     // [T, 2] slot inside (this rank, expert), -1 = dropped
+  const int* counts;   // [E] rows this rank sends to each expert
+  int* ticket;         // local scratch word, zero between launches
+  const int* epoch;    // device word: use count of the flag arrays (advance before each call)
+} FtkMoeDesc;
+// logits fp32 [T, ld] (first E columns used); d_logits bf16 [T, ld] (columns >= E zeroed)
+int ftk_moe_route(const float* logits, float* probs, int* idx, float* gate, int T, int E, int ld,
+                  void* stream);
+int ftk_moe_route_bwd(const float* probs, const int* idx, const float* d_gate, void* d_logits, int T,
+                      int E, int ld, void* stream);
+int ftk_moe_gate_grad(const void* g, const void* rows, float* d_gate, int T, int d, void* stream);
+int ftk_moe_slots(const int* idx, int* slot, int* counts, int T, int E, int capacity, void* stream);
+// rows of x (scaled by scale[t,k] when given) -> recv[expert rank]; waits for all sources and
+// zeroes the unused rows of this rank's own buffer.  arrive[r]: [world] words on rank r.
+int ftk_moe_dispatch(const FtkMoeDesc* m, const void* x, const float* scale, void* const* recv,
+                     int* const* recv_counts, int* const* arrive, void* stream);
+// out[t] = gate[t,0] * y[e0][slot0] + gate[t,1] * y[e1][slot1] (+ resid[t]); optionally keeps the
+// pulled rows ([T, 2, d]) for the gate gradient.  ready[r]: [world] words on rank r.
+int ftk_moe_combine(const FtkMoeDesc* m, void* const* y, int* const* ready, const float* gate, void* out,
+                    const void* resid, void* rows, void* stream);
+
 // ---- attention (causal / full), packed QKV layout ---------------------------------------
 // q/k/v: bf16 element (b, s, h, e) at base[b*bs + s*ss + h*hs + e]; head_dim in {64, 128}.
 // o: same addressing with its own strides.  lse: fp32 [B, H, S], log2 domain.

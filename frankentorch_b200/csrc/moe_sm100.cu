@@ -47,13 +47,14 @@ __device__ __forceinline__ bool moe_wait(const int* p, int want, int* status) {
 }
 
 // ------------------------------------------------------------------ route
-// One thread per token.  probs [T, E] fp32, idx [T, 2] int32, gate [T, 2] fp32.
+// One thread per token.  logits [T, ld] fp32 (first E columns), probs [T, E] fp32, idx [T, 2]
+// int32, gate [T, 2] fp32.
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, float* __restrict__ probs, int* __restrict__ idx,
-                 float* __restrict__ gate, int T, int E) {
+                 float* __restrict__ gate, int T, int E, int ld) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
-  const float* lp = logits + (long long)t * E;
+  const float* lp = logits + (long long)t * ld;
   float mx = -INFINITY;
   for (int e = 0; e < E; ++e) mx = fmaxf(mx, lp[e]);
   if (!(mx > -INFINITY && mx < INFINITY)) mx = 0.f;     // non-finite guard
@@ -80,10 +81,12 @@ moe_route_kernel(const float* __restrict__ logits, float* __restrict__ probs, in
   gate[2 * t + 1] = s > 0.f ? p1 / s : 0.5f;
 }
 
-// d_logits from d_gate: g_k = p_k / (p_a + p_b), p = softmax(logits).
+// d_logits (bf16 [T, ld], columns >= E zeroed) from d_gate: g_k = p_k / (p_a + p_b),
+// p = softmax(logits).
 __global__ void __launch_bounds__(256)
 moe_route_bwd_kernel(const float* __restrict__ probs, const int* __restrict__ idx,
-                     const float* __restrict__ d_gate, float* __restrict__ d_logits, int T, int E) {
+                     const float* __restrict__ d_gate, __nv_bfloat16* __restrict__ d_logits, int T, int E,
+                     int ld) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   const float* pp = probs + (long long)t * E;
@@ -99,8 +102,9 @@ moe_route_bwd_kernel(const float* __restrict__ probs, const int* __restrict__ id
   const float dot = pa * dpa + pb * dpb;
   for (int e = 0; e < E; ++e) {
     const float dp = e == a ? dpa : (e == b ? dpb : 0.f);
-    d_logits[(long long)t * E + e] = pp[e] * (dp - dot);
+    d_logits[(long long)t * ld + e] = __float2bfloat16(pp[e] * (dp - dot));
   }
+  for (int e = E; e < ld; ++e) d_logits[(long long)t * ld + e] = __float2bfloat16(0.f);
 }
 
 // ------------------------------------------------------------------ slots
@@ -230,8 +234,6 @@ struct MoeCombineArgs {
   __nv_bfloat16* out;                      // [T, d]
   const __nv_bfloat16* resid;              // [T, d] or null, added last
   __nv_bfloat16* rows;                     // [T, 2, d] or null: the pulled rows, kept for backward
-  const __nv_bfloat16* dots_with;          // [T, d] or null: d_gate[t,k] = <dots_with[t], row k>
-  float* d_gate;                           // [T, 2]
   const int* epoch;
   int T, d, e_local, capacity, rank, world;
   int* status;
@@ -269,7 +271,6 @@ moe_combine_kernel(const MoeCombineArgs a) {
                            a.y[src] + ((((long long)el * a.world + a.rank) * a.capacity + sl) * a.d));
       w[k] = a.gate ? a.gate[2 * t + k] : 1.f;
     }
-    float dot0 = 0.f, dot1 = 0.f;
     for (int v = lane; v < vec; v += 32) {
       const uint4 z = make_uint4(0u, 0u, 0u, 0u);
       const uint4 u0 = rp[0] ? __ldcg(rp[0] + v) : z;
@@ -280,11 +281,9 @@ moe_combine_kernel(const MoeCombineArgs a) {
       }
       const uint32_t* p0 = &u0.x;
       const uint32_t* p1 = &u1.x;
-      uint4 rs = z, dw = z;
+      uint4 rs = z;
       if (a.resid) rs = reinterpret_cast<const uint4*>(a.resid + t * a.d)[v];
-      if (a.dots_with) dw = reinterpret_cast<const uint4*>(a.dots_with + t * a.d)[v];
       const uint32_t* pr = &rs.x;
-      const uint32_t* pd = &dw.x;
       uint32_t o[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -293,25 +292,40 @@ moe_combine_kernel(const MoeCombineArgs a) {
         const float x0 = (w[0] * f0.x + w[1] * f1.x) + fr.x;
         const float x1 = (w[0] * f0.y + w[1] * f1.y) + fr.y;
         o[i] = pack_bf16(x0, x1);
-        if (a.dots_with) {
-          const float2 fd = unpack_bf16(pd[i]);
-          dot0 += fd.x * f0.x + fd.y * f0.y;
-          dot1 += fd.x * f1.x + fd.y * f1.y;
-        }
       }
       if (a.out) reinterpret_cast<uint4*>(a.out + t * a.d)[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    if (a.dots_with) {
+  }
+}
+
+// d_gate[t, k] = <g[t, :], rows[t, k, :]>; one warp per token.
+__global__ void __launch_bounds__(256)
+moe_gate_grad_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ rows,
+                     float* __restrict__ d_gate, int T, int d) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float dot0 = 0.f, dot1 = 0.f;
+  for (int v = lane; v < (d >> 3); v += 32) {
+    const uint4 ug = reinterpret_cast<const uint4*>(g + t * d)[v];
+    const uint4 u0 = reinterpret_cast<const uint4*>(rows + (2 * t) * d)[v];
+    const uint4 u1 = reinterpret_cast<const uint4*>(rows + (2 * t + 1) * d)[v];
+    const uint32_t *pg = &ug.x, *p0 = &u0.x, *p1 = &u1.x;
 #pragma unroll
-      for (int dlt = 16; dlt > 0; dlt >>= 1) {
-        dot0 += __shfl_xor_sync(0xffffffffu, dot0, dlt);
-        dot1 += __shfl_xor_sync(0xffffffffu, dot1, dlt);
-      }
-      if (lane == 0) {
-        a.d_gate[2 * t] = dot0;
-        a.d_gate[2 * t + 1] = dot1;
-      }
+    for (int i = 0; i < 4; ++i) {
+      const float2 fg = unpack_bf16(pg[i]), f0 = unpack_bf16(p0[i]), f1 = unpack_bf16(p1[i]);
+      dot0 += fg.x * f0.x + fg.y * f0.y;
+      dot1 += fg.x * f1.x + fg.y * f1.y;
     }
+  }
+#pragma unroll
+  for (int dlt = 16; dlt > 0; dlt >>= 1) {
+    dot0 += __shfl_xor_sync(0xffffffffu, dot0, dlt);
+    dot1 += __shfl_xor_sync(0xffffffffu, dot1, dlt);
+  }
+  if (lane == 0) {
+    d_gate[2 * t] = dot0;
+    d_gate[2 * t + 1] = dot1;
   }
 }
 
@@ -320,18 +334,18 @@ moe_combine_kernel(const MoeCombineArgs a) {
 using namespace ftk;
 
 extern "C" int ftk_moe_route(const float* logits, float* probs, int* idx, float* gate, int T, int E,
-                             void* stream) {
-  if (T <= 0 || E < 2 || E > MOE_MAX_E) return -2;
+                             int ld, void* stream) {
+  if (T <= 0 || E < 2 || E > MOE_MAX_E || ld < E) return -2;
   moe_route_kernel<<<(T + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, probs, idx,
-                                                                                       gate, T, E);
+                                                                                       gate, T, E, ld);
   return (int)cudaGetLastError();
 }
 
-extern "C" int ftk_moe_route_bwd(const float* probs, const int* idx, const float* d_gate, float* d_logits,
-                                 int T, int E, void* stream) {
-  if (T <= 0 || E < 2 || E > MOE_MAX_E) return -2;
+extern "C" int ftk_moe_route_bwd(const float* probs, const int* idx, const float* d_gate, void* d_logits,
+                                 int T, int E, int ld, void* stream) {
+  if (T <= 0 || E < 2 || E > MOE_MAX_E || ld < E) return -2;
   moe_route_bwd_kernel<<<(T + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      probs, idx, d_gate, d_logits, T, E);
+      probs, idx, d_gate, reinterpret_cast<__nv_bfloat16*>(d_logits), T, E, ld);
   return (int)cudaGetLastError();
 }
 
@@ -367,10 +381,8 @@ extern "C" int ftk_moe_dispatch(const FtkMoeDesc* m, const void* x, const float*
 }
 
 extern "C" int ftk_moe_combine(const FtkMoeDesc* m, void* const* y, int* const* ready, const float* gate,
-                               void* out, const void* resid, void* rows, const void* dots_with,
-                               float* d_gate, void* stream) {
+                               void* out, const void* resid, void* rows, void* stream) {
   if (!m || m->world < 1 || m->world > FTK_MAX_RANKS || (m->d % 8) || m->E % m->world) return -2;
-  if (dots_with && !d_gate) return -2;
   MoeCombineArgs a;
   for (int r = 0; r < m->world; ++r) {
     a.y[r] = reinterpret_cast<const __nv_bfloat16*>(y[r]);
@@ -380,8 +392,6 @@ extern "C" int ftk_moe_combine(const FtkMoeDesc* m, void* const* y, int* const* 
   a.out = reinterpret_cast<__nv_bfloat16*>(out);
   a.resid = reinterpret_cast<const __nv_bfloat16*>(resid);
   a.rows = reinterpret_cast<__nv_bfloat16*>(rows);
-  a.dots_with = reinterpret_cast<const __nv_bfloat16*>(dots_with);
-  a.d_gate = d_gate;
   a.epoch = m->epoch;
   a.T = m->T; a.d = m->d; a.e_local = m->E / m->world; a.capacity = m->capacity;
   a.rank = m->rank; a.world = m->world;
@@ -391,5 +401,12 @@ extern "C" int ftk_moe_combine(const FtkMoeDesc* m, void* const* y, int* const* 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   moe_combine_kernel<<<4 * sms, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ftk_moe_gate_grad(const void* g, const void* rows, float* d_gate, int T, int d, void* stream) {
+  if (T <= 0 || (d % 8)) return -2;
+  moe_gate_grad_kernel<<<(T + 7) / 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(g), reinterpret_cast<const __nv_bfloat16*>(rows), d_gate, T, d);
   return (int)cudaGetLastError();
 }

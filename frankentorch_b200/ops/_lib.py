@@ -67,6 +67,15 @@ class FtkCommDesc(C.Structure):
     ]
 
 
+class FtkMoeDesc(C.Structure):
+    _fields_ = [
+        ("T", C.c_int), ("d", C.c_int), ("E", C.c_int), ("capacity", C.c_int), ("rank", C.c_int),
+        ("world", C.c_int),
+        ("idx", C.c_void_p), ("slot", C.c_void_p), ("counts", C.c_void_p), ("ticket", C.c_void_p),
+        ("epoch", C.c_void_p),
+    ]
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 
@@ -92,7 +101,14 @@ def load(build_if_missing: bool = True):
     lib.ftk_attn_fwd.argtypes = [C.POINTER(FtkAttnDesc), C.c_void_p]
     lib.ftk_attn_bwd.argtypes = [C.POINTER(FtkAttnDesc), C.c_void_p]
     vp, i, f, ll, ull = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_ulonglong
+    pm, pv = C.POINTER(FtkMoeDesc), C.POINTER(C.c_void_p)
     sigs = {
+        "ftk_moe_route": [vp, vp, vp, vp, i, i, i, vp],
+        "ftk_moe_route_bwd": [vp, vp, vp, vp, i, i, i, vp],
+        "ftk_moe_gate_grad": [vp, vp, vp, i, i, vp],
+        "ftk_moe_slots": [vp, vp, vp, i, i, i, vp],
+        "ftk_moe_dispatch": [pm, vp, vp, pv, pv, pv, vp],
+        "ftk_moe_combine": [pm, pv, pv, vp, vp, vp, vp, vp],
         "ftk_layernorm_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, i, i, f, vp],
         "ftk_layernorm_bwd_blocks": [i],
         "ftk_layernorm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp],

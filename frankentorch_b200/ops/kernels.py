@@ -216,10 +216,10 @@ def attention_bwd(q, k, v, o, lse, d_o, *, causal=True, scale=None, dq=None, dk=
 
 
 # --------------------------------------------------------------------------------------- norms
-def layernorm_fwd(x, gamma, beta, eps=1e-5, resid=None):
+def layernorm_fwd(x, gamma, beta, eps=1e-5, resid=None, out=None):
     """Returns ``(y, mean, rstd, x_sum)``; ``x_sum`` is ``x + resid`` when ``resid`` is given."""
     rows, cols = x.shape
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if out is None else out
     mean = torch.empty(rows, dtype=torch.float32, device=x.device)
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
     xs = torch.empty_like(x) if resid is not None else None
@@ -229,10 +229,11 @@ def layernorm_fwd(x, gamma, beta, eps=1e-5, resid=None):
     return y, mean, rstd, (xs if resid is not None else x)
 
 
-def layernorm_bwd(dy, x, gamma, mean, rstd, *, dx_add=None, dgamma=None, dbeta=None, accumulate=False):
+def layernorm_bwd(dy, x, gamma, mean, rstd, *, dx_add=None, dgamma=None, dbeta=None, accumulate=False,
+                  out=None):
     rows, cols = x.shape
     lib = _lib.load()
-    dx = torch.empty_like(x)
+    dx = torch.empty_like(x) if out is None else out
     if dgamma is None:
         dgamma = torch.empty(cols, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(cols, dtype=torch.float32, device=x.device)

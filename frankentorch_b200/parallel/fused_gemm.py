@@ -74,22 +74,41 @@ class FusedCollectives:
         self.local = torch.zeros(64 + max_gather_rows // TILE_M, dtype=torch.int32, device=device)
         self.epoch = self.local[0:1]
         self.sub_flags = self.local[64:]
-        # symmetric words: ready[world] | arrive[2][max_chunk_tiles][world]
+        # symmetric words: ready[world] | arrive[3][max_chunk_tiles][world]
         self.max_chunk_tiles = max_chunk_tiles
-        words = 64 + 2 * max_chunk_tiles * self.world
+        words = 64 + 3 * max_chunk_tiles * self.world
         self.flags = SymmetricBuffer(words * 4, group, device)
         self.flags.bytes.zero_()
         self.max_inbox_elems = max_inbox_elems
         self.inbox = None
         if max_inbox_elems:
-            # two slots of [world][chunk_rows][N] bf16
-            self.inbox = SymmetricBuffer(2 * max_inbox_elems * 2, group, device)
+            # three slots of [world][chunk_rows][N] bf16, see begin_step()
+            self.inbox = SymmetricBuffer(3 * max_inbox_elems * 2, group, device)
         self._slot = 0
+        self._first = True
         torch.cuda.synchronize(device)
         if self.world > 1:
             dist.barrier(group=group)
 
     # ------------------------------------------------------------------ helpers
+    def begin_step(self) -> None:
+        """Call at the start of every training step (also while a CUDA graph is being captured).
+
+        Consecutive reduce-scatters must not share an inbox slot.  The first one of a step takes
+        slot 2 and the rest alternate between 0 and 1, so the rule also holds across the step
+        boundary when one captured step is replayed, whatever the number of calls per step.
+        """
+        self._first = True
+        self._slot = 0
+
+    def _next_slot(self) -> int:
+        if self._first:
+            self._first = False
+            return 2
+        s = self._slot
+        self._slot ^= 1
+        return s
+
     def _tick(self) -> None:
         K._chk(self.lib.ftk_tick_i32(self.epoch.data_ptr(), K._stream()), "ftk_tick_i32")
 
@@ -195,8 +214,7 @@ class FusedCollectives:
         g = self._gemm_desc(a, b, out_shard, a_mn=a_mn, b_mn=b_mn, bias=bias, resid=resid, alpha=alpha,
                             accumulate=accumulate, M=m, N=n, K_=k)
         c = self._comm(COMM_SCATTER_D, ms)
-        slot = self._slot
-        self._slot ^= 1
+        slot = self._next_slot()
         for r in range(self.world):
             c.inbox[r] = self.inbox.peer_ptrs[r] + slot * self.max_inbox_elems * 2
             c.arrive[r] = self.flags.peer_ptrs[r] + 4 * (64 + slot * self.max_chunk_tiles * self.world)

@@ -28,6 +28,16 @@ def test_collective_fused_gemms(cuda_device):
     assert p.returncode == 0 and "COMM_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
 
 
+def test_expert_parallel_moe(cuda_device):
+    """Dispatch / combine all-to-alls over peer memory with experts split over the ranks."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    nproc = 2 if n < 4 else 4
+    p = _run_workers("_moe_worker.py", nproc, 29635)
+    assert p.returncode == 0 and "MOE_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
 def test_fused_data_parallel_matches_nccl_and_replays(cuda_device):
     n = torch.cuda.device_count()
     if n < 2:
