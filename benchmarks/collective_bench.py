@@ -56,7 +56,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--comm-ctas", type=int, default=16)
+    ap.add_argument("--comm-ctas", type=int, default=0, help="0 = the launcher's default")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -80,8 +80,7 @@ def main():
 
     ms = 8192
     m = ms * world
-    fc = FusedCollectives(g, dev, max_gather_rows=max(m, 8192), max_inbox_elems=world * ms * 2048,
-                          comm_ctas=args.comm_ctas)
+    fc = FusedCollectives(g, dev, max_inbox_elems=world * ms * 2048, comm_ctas=args.comm_ctas)
 
     # ---- K12: all-gather(x) -> GEMM (column-parallel fc1 slice of the 1.3B model)
     d, n = 2048, 8192 // 8

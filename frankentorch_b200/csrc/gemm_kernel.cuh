@@ -179,6 +179,10 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 
 // Work item -> output tile.  Plain GEMMs walk m fastest; the collective forms walk the row
 // chunks of the sharded dimension in rank-rotated order.
@@ -218,16 +222,28 @@ __device__ __forceinline__ TileCoord decode_item(int item, const GemmArgs& p, co
 }
 
 // ------------------------------------------------------------------ comm CTAs: gather
-// Thread 0 loads shard pieces into an smem ring, thread 32 stores them to the local staging
-// buffer and publishes a flag per completed 128-row subtile.
+// The gathered operand is cut into pieces of at most G_COPY_SLOT bytes.  Pieces are visited in
+// rank-rotated order and dealt round robin to the comm CTAs, so the data of the first tiles is
+// fetched by many CTAs at once.  In each comm CTA one thread drives an smem ring: bulk loads
+// (from the peer's shard, or from this rank's own shard) run four pieces ahead of the bulk
+// stores into the local staging buffer; a flag word per piece is published once its store has
+// landed.  With `own_last` the own chunk is copied after the remote ones: the GEMM reads
+// own-shard tiles straight from the shard (second tensor map), the staged copy only serves
+// later consumers of the gathered operand.
 __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const CommArgs& c,
-                                            int epoch, int cta, const WaitCtx& ctx) {
+                                            int epoch, int cta, bool own_last, const WaitCtx& ctx) {
   uint64_t* full = bars;
-  uint64_t* empty = bars + G_COPY_SLOTS;
+  // progress word shared by the driver (thread 0) and the publisher (thread 32): number of this
+  // CTA's pieces whose stores have landed; -1 after a failure
+  int* progress = reinterpret_cast<int*>(bars + 2 * G_COPY_SLOTS);
   const int spc = c.chunk_rows / G_BM;                 // subtiles per chunk
-  const int n_sub = spc * c.world;
   const uint32_t piece = c.sub_bytes < G_COPY_SLOT ? (uint32_t)c.sub_bytes : (uint32_t)G_COPY_SLOT;
   const int pps = (int)(c.sub_bytes / piece);          // pieces per subtile
+  const int ppc = spc * pps;                           // pieces per chunk
+  const int n_pieces = ppc * c.world;
+  const int shift = own_last ? ppc : 0;                // visit v -> rotated piece (v + shift) % n
+  const int mine = cta < n_pieces ? (n_pieces - cta + c.comm_ctas - 1) / c.comm_ctas : 0;
+  auto rotated = [&](int i) { return (int)(((long long)cta + (long long)i * c.comm_ctas + shift) % n_pieces); };
   if (threadIdx.x == 0) {
     // announce that this rank's shard is final for this epoch
     if (cta == 0 && c.ready_local) {
@@ -235,134 +251,159 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
       for (int r = 0; r < c.world; ++r)
         if (r != c.rank) st_rel_sys(c.ready_peer[r], epoch);
     }
-    long long n = 0;
+    int issued = 0, stored = 0;
     int ready_seen = 1 << c.rank;
-    for (int q = cta; q < n_sub; q += c.comm_ctas) {
-      const int chunk = (c.rank + q / spc) % c.world;
-      const int sidx = q % spc;
-      if (c.ready_local && !((ready_seen >> chunk) & 1)) {
-        if (!flag_wait<true>(c.ready_local + chunk, epoch, ctx)) return;
-        ready_seen |= 1 << chunk;
-      }
-      const uint8_t* s = c.src[chunk] + (long long)sidx * c.sub_bytes;
-      for (int pc = 0; pc < pps; ++pc, ++n) {
-        const int slot = (int)(n % G_COPY_SLOTS);
-        const uint32_t ph = (uint32_t)((n / G_COPY_SLOTS) & 1);
-        if (!mbar_wait(&empty[slot], ph ^ 1u, ctx, FT_ERR_WAIT_EMPTY)) return;
+    bool ok = true;
+    while (ok && stored < mine) {
+      while (issued < mine && issued < stored + G_COPY_SLOTS - 2) {
+        const int q = rotated(issued);
+        const int chunk = (c.rank + q / ppc) % c.world;
+        if (c.ready_local && !((ready_seen >> chunk) & 1)) {
+          if (!flag_wait<true>(c.ready_local + chunk, epoch, ctx)) {
+            ok = false;
+            break;
+          }
+          ready_seen |= 1 << chunk;
+        }
+        const int slot = issued % G_COPY_SLOTS;
         mbar_arrive_expect_tx(&full[slot], piece);
-        bulk_load(smem + slot * G_COPY_SLOT, s + (long long)pc * piece, piece, &full[slot]);
+        bulk_load(smem + slot * G_COPY_SLOT, c.src[chunk] + (long long)(q % ppc) * piece, piece, &full[slot]);
+        ++issued;
       }
-    }
-  } else if (threadIdx.x == 32) {
-    long long n = 0, freed = 0;
-    int q_pub = cta;                                   // next subtile of this CTA to publish
-    auto retire = [&](long long done) {                // pieces [freed, done) are fully stored
-      for (; freed < done; ++freed) {
-        mbar_arrive(&empty[freed % G_COPY_SLOTS]);
-        if ((freed + 1) % pps == 0) {
-          const int chunk = (c.rank + q_pub / spc) % c.world;
-          fence_proxy_async_all();
-          __threadfence();
-          st_rel_gpu(c.sub_flags + chunk * spc + q_pub % spc, epoch);
-          q_pub += c.comm_ctas;
-        }
+      if (!ok) break;
+      const int slot = stored % G_COPY_SLOTS;
+      if (!mbar_wait(&full[slot], (uint32_t)((stored / G_COPY_SLOTS) & 1), ctx, FT_ERR_WAIT_FULL)) {
+        ok = false;
+        break;
       }
-    };
-    for (int q = cta; q < n_sub; q += c.comm_ctas) {
-      const int chunk = (c.rank + q / spc) % c.world;
-      uint8_t* d = c.full + ((long long)chunk * spc + q % spc) * c.sub_bytes;
-      for (int pc = 0; pc < pps; ++pc, ++n) {
-        const int slot = (int)(n % G_COPY_SLOTS);
-        const uint32_t ph = (uint32_t)((n / G_COPY_SLOTS) & 1);
-        if (!mbar_wait(&full[slot], ph, ctx, FT_ERR_WAIT_FULL)) {
-          bulk_wait_group<0>();
-          return;
-        }
-        bulk_store(d + (long long)pc * piece, smem + slot * G_COPY_SLOT, piece);
-        bulk_wait_group<2>();                          // all but the newest two stores landed
-        retire(n + 1 - 2 > 0 ? n + 1 - 2 : 0);
-      }
+      const int q = rotated(stored);
+      bulk_store(c.full + ((long long)((c.rank + q / ppc) % c.world) * ppc + q % ppc) * piece,
+                 smem + slot * G_COPY_SLOT, piece);
+      bulk_wait_group_read<1>();                       // the slot of the previous store is free
+      ++stored;
+      bulk_wait_group<3>();                            // all but the newest three stores landed
+      if (stored > 3) asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(progress)), "r"(stored - 3) : "memory");
     }
     bulk_wait_group<0>();
-    retire(n);
+    asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(progress)), "r"(ok ? stored : -1) : "memory");
+  } else if (threadIdx.x == 32) {
+    // publisher: turns the driver's progress into per-piece flags.  It owns no copies in flight,
+    // so its release stores never wait behind the ring.
+    int published = 0;
+    const long long t0 = clock64();
+    while (published < mine) {
+      int done;
+      asm volatile("ld.acquire.cta.shared.s32 %0, [%1];" : "=r"(done) : "r"(smem_u32(progress)) : "memory");
+      if (done < 0) return;
+      if (done == published) {
+        __nanosleep(100);
+        if (clock64() - t0 > 2 * G_PEER_WAIT_CYCLES) return;   // the driver's own waits are bounded
+        continue;
+      }
+      for (; published < done; ++published) {
+        const int q = rotated(published);
+        st_rel_gpu(c.sub_flags + ((c.rank + q / ppc) % c.world) * ppc + q % ppc, epoch);
+      }
+    }
   }
 }
 
-// ------------------------------------------------------------------ comm CTAs: ordered reduce
+// ------------------------------------------------------------------ ordered reduce
 // Tile (n_t, m_in) of this rank's chunk: out = sum over source ranks (ascending) of the bf16
-// partials in the local inbox, + bias, + residual, (+ previous output).
+// partials in the local inbox, + bias, + residual, (+ previous output).  Run by `nthr` threads
+// of a CTA (thread index `tid`), which synchronise on named barrier 1; tiles are dealt round
+// robin over `n_ctas` CTAs.  Every compute CTA calls this after its last GEMM tile, so the
+// whole GPU's bandwidth drains the inbox.
 template <int BN>
 __device__ __forceinline__ void comm_reduce(const GemmArgs& p, const CommArgs& c, int epoch, int cta,
-                                            const WaitCtx& ctx) {
+                                            int n_ctas, int tid, int nthr, const WaitCtx& ctx) {
   const int tpc = c.chunk_rows / G_BM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int n_tiles = tpc * tiles_n;
   const __nv_bfloat16* inbox = c.inbox[c.rank];
   const long long src_stride = (long long)c.chunk_rows * p.N;
-  for (int t = cta; t < n_tiles; t += c.comm_ctas) {
-    if ((int)threadIdx.x < c.world) {
-      if (!flag_wait<true>(c.arrive[c.rank] + t * c.world + threadIdx.x, epoch, ctx)) {
-        // fall through to the barrier; everyone sees the abort flag below
-      }
-    }
-    __syncthreads();
+  constexpr int U = 4;                                  // vectors in flight per thread and source
+  for (int t = cta; t < n_tiles; t += n_ctas) {
+    if (tid < c.world) flag_wait<true>(c.arrive[c.rank] + t * c.world + tid, epoch, ctx);
+    asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
     if (aborted(ctx)) return;
     const int n_t = t / tpc, m_in = t % tpc;
     const int n_base = n_t * BN;
     const int cols = min(BN, p.N - n_base);            // multiple of 8
     const int vec_per_row = cols >> 3;
-    for (int v = threadIdx.x; v < G_BM * vec_per_row; v += G_THREADS) {
-      const int row = m_in * G_BM + v / vec_per_row;   // row inside this rank's chunk
-      const int col = n_base + ((v % vec_per_row) << 3);
-      float acc[8];
+    const int n_vec = G_BM * vec_per_row;
+    for (int v0 = tid; v0 < n_vec; v0 += nthr * U) {
+      float acc[U][8];
+      long long off[U];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      const __nv_bfloat16* ip = inbox + (long long)row * p.N + col;
-#pragma unroll 4
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * nthr;
+        const int row = m_in * G_BM + v / vec_per_row;  // row inside this rank's chunk
+        const int col = n_base + ((v % vec_per_row) << 3);
+        off[u] = v < n_vec ? (long long)row * p.N + col : -1;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+      }
+#pragma unroll 2
       for (int s = 0; s < c.world; ++s) {
-        const uint4 u = __ldcg(reinterpret_cast<const uint4*>(ip + s * src_stride));
-        const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
-                     f3 = unpack_bf16(u.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
-      if (p.bias) {
+        uint4 w[U];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(__ldg(p.bias + col + i));
-      }
-      if (p.resid) {
-        const uint4 u = *reinterpret_cast<const uint4*>(p.resid + (long long)row * p.ldr + col);
-        const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
-                     f3 = unpack_bf16(u.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
-      if (p.out_fp32) {
-        float* dp = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col;
-        float4 a = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        float4 b = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        if (p.accumulate) {
-          const float4 oa = reinterpret_cast<float4*>(dp)[0], ob = reinterpret_cast<float4*>(dp)[1];
-          a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
-          b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
+        for (int u = 0; u < U; ++u)
+          w[u] = off[u] >= 0 ? __ldcg(reinterpret_cast<const uint4*>(inbox + s * src_stride + off[u]))
+                             : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float2 f0 = unpack_bf16(w[u].x), f1 = unpack_bf16(w[u].y), f2 = unpack_bf16(w[u].z),
+                       f3 = unpack_bf16(w[u].w);
+          acc[u][0] += f0.x; acc[u][1] += f0.y; acc[u][2] += f1.x; acc[u][3] += f1.y;
+          acc[u][4] += f2.x; acc[u][5] += f2.y; acc[u][6] += f3.x; acc[u][7] += f3.y;
         }
-        reinterpret_cast<float4*>(dp)[0] = a;
-        reinterpret_cast<float4*>(dp)[1] = b;
-      } else {
-        __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col;
-        if (p.accumulate) {
-          const uint4 u = *reinterpret_cast<const uint4*>(dp);
-          const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z),
-                       f3 = unpack_bf16(u.w);
-          acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-          acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (off[u] < 0) continue;
+        const int v = v0 + u * nthr;
+        const int row = m_in * G_BM + v / vec_per_row;
+        const int col = n_base + ((v % vec_per_row) << 3);
+        float* a8 = acc[u];
+        if (p.bias) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a8[i] += __bfloat162float(__ldg(p.bias + col + i));
         }
-        uint4 o;
-        o.x = pack_bf16(acc[0], acc[1]);
-        o.y = pack_bf16(acc[2], acc[3]);
-        o.z = pack_bf16(acc[4], acc[5]);
-        o.w = pack_bf16(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(dp) = o;
+        if (p.resid) {
+          const uint4 r4 = *reinterpret_cast<const uint4*>(p.resid + (long long)row * p.ldr + col);
+          const float2 f0 = unpack_bf16(r4.x), f1 = unpack_bf16(r4.y), f2 = unpack_bf16(r4.z),
+                       f3 = unpack_bf16(r4.w);
+          a8[0] += f0.x; a8[1] += f0.y; a8[2] += f1.x; a8[3] += f1.y;
+          a8[4] += f2.x; a8[5] += f2.y; a8[6] += f3.x; a8[7] += f3.y;
+        }
+        if (p.out_fp32) {
+          float* dp = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col;
+          float4 x = make_float4(a8[0], a8[1], a8[2], a8[3]);
+          float4 y = make_float4(a8[4], a8[5], a8[6], a8[7]);
+          if (p.accumulate) {
+            const float4 ox = reinterpret_cast<float4*>(dp)[0], oy = reinterpret_cast<float4*>(dp)[1];
+            x.x += ox.x; x.y += ox.y; x.z += ox.z; x.w += ox.w;
+            y.x += oy.x; y.y += oy.y; y.z += oy.z; y.w += oy.w;
+          }
+          reinterpret_cast<float4*>(dp)[0] = x;
+          reinterpret_cast<float4*>(dp)[1] = y;
+        } else {
+          __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col;
+          if (p.accumulate) {
+            const uint4 o4 = *reinterpret_cast<const uint4*>(dp);
+            const float2 f0 = unpack_bf16(o4.x), f1 = unpack_bf16(o4.y), f2 = unpack_bf16(o4.z),
+                         f3 = unpack_bf16(o4.w);
+            a8[0] += f0.x; a8[1] += f0.y; a8[2] += f1.x; a8[3] += f1.y;
+            a8[4] += f2.x; a8[5] += f2.y; a8[6] += f3.x; a8[7] += f3.y;
+          }
+          uint4 o;
+          o.x = pack_bf16(a8[0], a8[1]);
+          o.y = pack_bf16(a8[2], a8[3]);
+          o.z = pack_bf16(a8[4], a8[5]);
+          o.w = pack_bf16(a8[6], a8[7]);
+          *reinterpret_cast<uint4*>(dp) = o;
+        }
       }
     }
   }
@@ -372,7 +413,8 @@ __device__ __forceinline__ void comm_reduce(const GemmArgs& p, const CommArgs& c
 template <int BN, int COMM>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
-                       const __grid_constant__ CUtensorMap tmB, const GemmArgs p, const CommArgs c) {
+                       const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmOwn, const GemmArgs p, const CommArgs c) {
   using Cfg = GemmCfg<BN>;
   static_assert(!COMM || G_COPY_SLOTS * G_COPY_SLOT <= Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES),
                 "gather ring must fit the operand ring");
@@ -404,6 +446,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         mbar_init(&bars[i], 1);
         mbar_init(&bars[G_COPY_SLOTS + i], 1);
       }
+      *reinterpret_cast<int*>(bars + 2 * G_COPY_SLOTS) = 0;   // gather progress word
     } else {
       for (int i = 0; i < Cfg::STAGES; ++i) {
         mbar_init(&full[i], 1);
@@ -429,9 +472,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     if (COMM) {
       const int cta = (int)blockIdx.x - n_compute;
       if (c.mode == FTK_COMM_SCATTER_D)
-        comm_reduce<BN>(p, c, epoch, cta, ctx);
+        comm_reduce<BN>(p, c, epoch, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, G_THREADS, ctx);
       else
-        comm_gather(smem, bars, c, epoch, cta, ctx);
+        comm_gather(smem, bars, c, epoch, cta,
+                    /*own_last=*/c.mode == FTK_COMM_GATHER_A, ctx);
     }
     __syncthreads();
     return;
@@ -456,6 +500,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t ph = 0;
     bool ok = true;
     int k_ready = 0;
+    // flag words per 128-row subtile of a gathered operand (one per copied piece)
+    const int pps = !COMM ? 1 : (c.sub_bytes > G_COPY_SLOT ? (int)(c.sub_bytes / G_COPY_SLOT) : 1);
     for (int item = blockIdx.x; ok && item < total; item += n_compute) {
       const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
       const int m_t = t.m_t, n_t = t.n_t;
@@ -463,7 +509,26 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       const int kb0 = t.sp * kb_per_split;
       const int kb1 = min(kblocks_all, kb0 + kb_per_split);
       const bool k_sharded = COMM && c.mode == FTK_COMM_GATHER_B && p.b_mn;
-      if (COMM && !k_sharded && (c.mode == FTK_COMM_GATHER_A || c.mode == FTK_COMM_GATHER_B)) {
+      // operand tiles that lie wholly inside this rank's own shard are read from the shard itself
+      const CUtensorMap* mapA = &tmA;
+      const CUtensorMap* mapB = &tmB;
+      int a_row = m_t * G_BM, b_row = n_t * BN;
+      bool own = false;
+      if (COMM && !k_sharded && c.mode == FTK_COMM_GATHER_A) {
+        own = (a_row / c.chunk_rows == c.rank);
+        if (own) {
+          mapA = &tmOwn;
+          a_row -= c.rank * c.chunk_rows;
+        }
+      } else if (COMM && !k_sharded && c.mode == FTK_COMM_GATHER_B) {
+        own = c.chunk_rows >= BN && b_row >= c.rank * c.chunk_rows &&
+              min(p.N, b_row + BN) <= (c.rank + 1) * c.chunk_rows;
+        if (own) {
+          mapB = &tmOwn;
+          b_row -= c.rank * c.chunk_rows;
+        }
+      }
+      if (COMM && !k_sharded && !own && (c.mode == FTK_COMM_GATHER_A || c.mode == FTK_COMM_GATHER_B)) {
         // the staged subtiles this tile reads must have landed
         int f0, f1;
         if (c.mode == FTK_COMM_GATHER_A) {
@@ -472,13 +537,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
           f0 = (n_t * BN) / G_BM;
           f1 = (min(p.N, n_t * BN + BN) - 1) / G_BM;
         }
+        // one flag per piece; the lanes poll the pieces of subtiles f0..f1 in parallel
         int good = 1;
-        if (lane == 0) {
-          for (int f = f0; f <= f1 && good; ++f) good = flag_wait<false>(c.sub_flags + f, epoch, ctx) ? 1 : 0;
-          fence_proxy_async_all();
-        }
-        good = __shfl_sync(0xffffffffu, good, 0);
-        if (!good) break;
+        for (int pc = f0 * pps + lane; pc < (f1 + 1) * pps && good; pc += 32)
+          good = flag_wait<false>(c.sub_flags + pc, epoch, ctx) ? 1 : 0;
+        fence_proxy_async_all();
+        if (!__all_sync(0xffffffffu, good)) break;
       }
       for (int kb = kb0; kb < kb1; ++kb) {
         if (k_sharded) {
@@ -486,12 +550,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
           const int need = (min(p.K, kb * G_BK + G_BK) - 1) / G_BM + 1;
           while (ok && k_ready < need) {
             int good = 1;
-            if (lane == 0) {
-              good = flag_wait<false>(c.sub_flags + k_ready, epoch, ctx) ? 1 : 0;
-              fence_proxy_async_all();
-            }
-            good = __shfl_sync(0xffffffffu, good, 0);
-            if (!good) ok = false;
+            for (int pc = k_ready * pps + lane; pc < (k_ready + 1) * pps && good; pc += 32)
+              good = flag_wait<false>(c.sub_flags + pc, epoch, ctx) ? 1 : 0;
+            fence_proxy_async_all();
+            if (!__all_sync(0xffffffffu, good)) ok = false;
             ++k_ready;
           }
           if (!ok) break;
@@ -505,7 +567,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
           uint8_t* a_dst = sA + s * Cfg::A_BYTES;
           uint8_t* b_dst = sB + s * Cfg::B_BYTES;
           if (!p.a_mn) {
-            tma_load_4d(a_dst, &tmA, &full[s], kb * G_BK, m_t * G_BM, l0, l1);
+            tma_load_4d(a_dst, mapA, &full[s], kb * G_BK, a_row, l0, l1);
           } else {
 #pragma unroll
             for (int cc = 0; cc < G_BM / 64; ++cc)
@@ -513,7 +575,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
                           l0, l1);
           }
           if (!p.b_mn) {
-            tma_load_4d(b_dst, &tmB, &full[s], kb * G_BK, n_t * BN, l0, l1);
+            tma_load_4d(b_dst, mapB, &full[s], kb * G_BK, b_row, l0, l1);
           } else {
 #pragma unroll
             for (int cc = 0; cc < BN / 64; ++cc)
@@ -598,34 +660,46 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         // partial tile -> inbox of the owning rank, slot of this rank; then one flag per tile
         const int tpc = c.chunk_rows / G_BM;
         const int owner = m_t / tpc;
-        const long long row_in_chunk = row - (long long)owner * c.chunk_rows;
-        __nv_bfloat16* ob = c.inbox[owner] + ((long long)c.rank * c.chunk_rows + row_in_chunk) * p.N;
+        // first row of this warp's 32-row slab inside the owner's chunk, in this rank's inbox slot
+        const long long slab_row = (long long)m_t * G_BM + q * 32 - (long long)owner * c.chunk_rows;
+        __nv_bfloat16* ob = c.inbox[owner] + ((long long)c.rank * c.chunk_rows + slab_row) * p.N;
+        // Peer stores want long contiguous runs: two 32-column chunks are packed to bf16,
+        // transposed through a per-warp smem tile (32 rows x 128 B, XOR-swizzled 16-byte
+        // segments) and written so that 8 consecutive lanes cover 128 contiguous bytes of a row.
+        uint8_t* stage = smem + Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES) + 256 + ew * 4096;
 #pragma unroll 1
-        for (int ci = c_begin; ci < c_end; ++ci) {
+        for (int ci = c_begin; ci < c_end; ci += 2) {
           const int c0 = ci * 32;
-          uint32_t r[32];
+          uint32_t r[64];
           tmem_ld32(tmem_base + acc * Cfg::ACC_STRIDE + c0 + ((uint32_t)(q * 32) << 16), r);
+          tmem_ld32(tmem_base + acc * Cfg::ACC_STRIDE + c0 + 32 + ((uint32_t)(q * 32) << 16), r + 32);
           tmem_ld_wait();
-          const int n0 = n_t * BN + c0;
-          if (row < p.M && n0 < p.N) {
-            const int nv = min(4, (p.N - n0) >> 3);       // N is a multiple of 8
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              if (i < nv) {
-                uint4 o;
-                o.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * p.alpha, __uint_as_float(r[8 * i + 1]) * p.alpha);
-                o.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * p.alpha, __uint_as_float(r[8 * i + 3]) * p.alpha);
-                o.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * p.alpha, __uint_as_float(r[8 * i + 5]) * p.alpha);
-                o.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * p.alpha, __uint_as_float(r[8 * i + 7]) * p.alpha);
-                reinterpret_cast<uint4*>(ob + n0)[i] = o;
-              }
-            }
+          for (int j = 0; j < 8; ++j) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(r[8 * j + 0]) * p.alpha, __uint_as_float(r[8 * j + 1]) * p.alpha);
+            o.y = pack_bf16(__uint_as_float(r[8 * j + 2]) * p.alpha, __uint_as_float(r[8 * j + 3]) * p.alpha);
+            o.z = pack_bf16(__uint_as_float(r[8 * j + 4]) * p.alpha, __uint_as_float(r[8 * j + 5]) * p.alpha);
+            o.w = pack_bf16(__uint_as_float(r[8 * j + 6]) * p.alpha, __uint_as_float(r[8 * j + 7]) * p.alpha);
+            *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
           }
+          __syncwarp();
+          const int n0 = n_t * BN + c0;
+          const int seg = lane & 7;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + (lane >> 3);
+            const uint4 o = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((seg ^ (rr & 7)) << 4));
+            if ((long long)m_t * G_BM + q * 32 + rr < p.M && n0 + seg * 8 < p.N)
+              *reinterpret_cast<uint4*>(ob + (long long)rr * p.N + n0 + seg * 8) = o;
+          }
+          __syncwarp();
         }
+        // the accumulator is drained: release it before waiting for the peer stores to land
         tc_fence_before();
-        __threadfence_system();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
+        __threadfence_system();
         asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
         if (ew == 0 && lane == 0) {
           const int t_local = n_t * tpc + (m_t - owner * tpc);
@@ -763,6 +837,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       acc_ph ^= (1u << acc);
       acc ^= 1;
     }
+    // reduce-scatter: with the GEMM tiles done, the epilogue warps of every CTA drain the inbox
+    if (COMM && c.mode == FTK_COMM_SCATTER_D)
+      comm_reduce<BN>(p, c, epoch, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x - 64,
+                      32 * G_EPI_WARPS, ctx);
   }
 
   // ---------------------------------------------------------------- teardown

@@ -131,7 +131,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   if (grid <= 0) return 0;
   CommArgs none;
   memset(&none, 0, sizeof(none));
-  gemm_bf16_sm100_kernel<BN, 0><<<grid, G_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, a, none);
+  gemm_bf16_sm100_kernel<BN, 0><<<grid, G_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, tmA, a, none);
   return (int)cudaGetLastError();
 }
 
@@ -264,7 +264,9 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   c.mode = cd->mode; c.rank = cd->rank; c.world = cd->world; c.chunk_rows = cd->chunk_rows;
   c.epoch = cd->epoch;
   const int sms = g->max_ctas > 0 ? g->max_ctas : num_sms();
-  c.comm_ctas = cd->comm_ctas > 0 ? cd->comm_ctas : 16;
+  // gathers: CTAs that only move data (default 20); reduce-scatter: every CTA reduces after its
+  // GEMM tiles, dedicated CTAs are optional (default none)
+  c.comm_ctas = cd->comm_ctas > 0 ? cd->comm_ctas : (cd->mode == FTK_COMM_SCATTER_D ? 0 : 20);
   if (c.comm_ctas >= sms) return -7;
 
   if (cd->mode == FTK_COMM_SCATTER_D) {
@@ -305,10 +307,11 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   if (!a.status) return -6;
 
   using Cfg = GemmCfg<BN>;
+  constexpr int COMM_SMEM = Cfg::SMEM + G_EPI_WARPS * 4096;   // + per-warp store staging tiles
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100_kernel<BN, 1>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, COMM_SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
@@ -316,6 +319,13 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   long long n_compute = sms - c.comm_ctas;
   if (items < n_compute) n_compute = items;
   const int grid = (int)n_compute + c.comm_ctas;   // all CTAs resident: one per SM
-  gemm_bf16_sm100_kernel<BN, 1><<<grid, G_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, a, c);
+  // tiles inside this rank's own shard are read from the shard, not from the staging buffer
+  CUtensorMap tmOwn = tmA;
+  if (cd->mode == FTK_COMM_GATHER_A)
+    rc = ftk_make_tmap_bf16(&tmOwn, cd->src[cd->rank], g->K, cd->chunk_rows, 1, 1, g->K, 0, 0, G_BK, G_BM);
+  else if (cd->mode == FTK_COMM_GATHER_B && !g->b_mn && cd->chunk_rows >= BN)
+    rc = ftk_make_tmap_bf16(&tmOwn, cd->src[cd->rank], g->K, cd->chunk_rows, 1, 1, g->K, 0, 0, G_BK, BN);
+  if (rc) return 3000 + rc;
+  gemm_bf16_sm100_kernel<BN, 1><<<grid, G_THREADS, COMM_SMEM, stream>>>(tmA, tmB, tmOwn, a, c);
   return (int)cudaGetLastError();
 }

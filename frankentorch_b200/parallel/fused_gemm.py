@@ -63,15 +63,15 @@ class FusedCollectives:
     """Flag storage, inboxes and launch helpers for the collective-fused GEMMs of one group."""
 
     def __init__(self, group: Optional[dist.ProcessGroup], device: torch.device, *,
-                 max_gather_rows: int = 1 << 17, max_inbox_elems: int = 0, max_chunk_tiles: int = 4096,
-                 comm_ctas: int = 16):
+                 max_gather_bytes: int = 1 << 30, max_inbox_elems: int = 0, max_chunk_tiles: int = 4096,
+                 comm_ctas: int = 0):
         self.group, self.device = group, device
         self.rank = dist.get_rank(group) if group is not None else 0
         self.world = dist.get_world_size(group) if group is not None else 1
         self.comm_ctas = comm_ctas
         self.lib = _lib.load()
-        # local words: [0] epoch, then one flag per 128-row subtile of a gathered operand
-        self.local = torch.zeros(64 + max_gather_rows // TILE_M, dtype=torch.int32, device=device)
+        # local words: [0] epoch, then one flag per 32 KiB piece of a gathered operand
+        self.local = torch.zeros(64 + max_gather_bytes // 32768 + 1024, dtype=torch.int32, device=device)
         self.epoch = self.local[0:1]
         self.sub_flags = self.local[64:]
         # symmetric words: ready[world] | arrive[3][max_chunk_tiles][world]
@@ -141,9 +141,12 @@ class FusedCollectives:
     def _gather(self, c: FtkCommDesc, shard: SymmTensor, handshake: bool) -> None:
         for r in range(self.world):
             c.src[r] = shard.peer_ptrs[r]
-        n_sub = c.chunk_rows // TILE_M * self.world
-        if n_sub > self.sub_flags.numel():
-            raise K.KernelError("gathered operand has more 128-row subtiles than flag words")
+        # one flag word per copied piece (at most 32 KiB) of the gathered operand
+        row_bytes = shard.t.shape[1] * 2
+        sub = TILE_M * row_bytes
+        n_flags = c.chunk_rows // TILE_M * self.world * max(1, sub // 32768)
+        if n_flags > self.sub_flags.numel():
+            raise K.KernelError("gathered operand needs more flag words than were allocated")
         c.sub_flags = self.sub_flags.data_ptr()
         if handshake and self.world > 1:
             c.ready_local = self.flags.local_ptr
