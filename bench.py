@@ -35,11 +35,13 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
 MODELS = {
-    # name: (preset, micro_batch_per_gpu, seq_len)
-    "gpt2-small": ("gpt2-small", 8, 1024),
-    "gpt2-medium": ("gpt2-medium", 4, 2048),
-    "gpt-1.3b": ("gpt-1.3b", 4, 2048),
-    "gpt-tiny": ("gpt-tiny", 4, 128),
+    # name: (preset, micro_batch_per_gpu, seq_len, default parallelism)
+    "gpt2-small": ("gpt2-small", 8, 1024, "dp"),       # data parallel, fused reduce-scatter + AdamW
+    "gpt2-medium": ("gpt2-medium", 4, 2048, "zero3"),  # block weights sharded, gathers fused into GEMMs
+    "gpt-1.3b": ("gpt-1.3b", 4, 2048, "tp"),           # tensor + sequence parallel over all GPUs
+    "moe-12l": ("moe-12l", 4, 2048, "ep"),             # 8 experts top-2, expert parallel
+    "gpt-tiny": ("gpt-tiny", 4, 128, "dp"),
+    "moe-tiny": ("moe-tiny", 4, 128, "ep"),
 }
 
 
@@ -54,6 +56,8 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--parallelism", default="", choices=["", "dp", "tp", "zero3", "ep"],
+                    help="default: the one the named config asks for")
     ap.add_argument("--dp-impl", default="fused", choices=["fused", "nccl"],
                     help="multi-GPU gradient path: in-kernel NVLink reduce-scatter+AdamW+all-gather, or NCCL all-reduce")
     return ap.parse_args()
@@ -147,14 +151,30 @@ def main():
     from frankentorch_b200.ops import kernels as K
     from frankentorch_b200.training.engine import OptimConfig, TrainEngine
 
-    preset, mb, seq = MODELS[args.model]
+    preset, mb, seq, par = MODELS[args.model]
+    par = args.parallelism or par
     mb = args.micro_batch or mb
     seq = args.seq_len or seq
-    cfg = GPTConfig.preset(preset)
-    cfg.max_seq = max(seq, 1) if seq < cfg.max_seq else cfg.max_seq
+    group = dist.group.WORLD if world > 1 else None
     tape = TensorTape(grad_dtype=None)
     tape.accumulate_fn = lambda a, b: K.add(a, b) if (a.dtype == torch.bfloat16 and a.is_cuda) else a + b
-    model = GPT(cfg, tape, device=dev, seed=1234, group=dist.group.WORLD if world > 1 else None)
+    if par == "ep":
+        from frankentorch_b200.models.gpt_moe import MoEConfig, MoEGPT
+        cfg = MoEConfig.gpt_preset(preset)
+        cfg.max_seq = max(seq, 1) if seq < cfg.max_seq else cfg.max_seq
+        model = MoEGPT(cfg, MoEConfig(), tape, dev, group=group, micro_batch=mb, seq_len=seq, seed=1234)
+    else:
+        cfg = GPTConfig.preset(preset)
+        cfg.max_seq = max(seq, 1) if seq < cfg.max_seq else cfg.max_seq
+        if par == "tp":
+            from frankentorch_b200.models.gpt_tp import TensorParallelGPT
+            model = TensorParallelGPT(cfg, tape, dev, group=group, micro_batch=mb, seq_len=seq, seed=1234)
+        elif par == "zero3":
+            from frankentorch_b200.models.gpt_zero3 import Zero3GPT
+            model = Zero3GPT(cfg, tape, dev, group=group, seed=1234)
+        else:
+            model = GPT(cfg, tape, device=dev, seed=1234, group=group)
+    n_params = model.param_count() if hasattr(model, "param_count") else cfg.param_count()
     dp = None
     if world > 1:
         from frankentorch_b200.parallel.data_parallel import FusedDataParallel, NcclDataParallel
@@ -231,12 +251,13 @@ def main():
         "impl": "ours",
         "config": {
             "model": cfg.name, "n_layer": cfg.n_layer, "d_model": cfg.d_model, "n_head": cfg.n_head,
-            "vocab": cfg.vocab_size, "params": cfg.param_count(),
+            "vocab": cfg.vocab_size, "params": n_params,
             "micro_batch_per_gpu": mb, "global_batch": mb * world, "seq_len": seq,
-            "parallelism": f"dp{world}" if world > 1 else "single",
+            "parallelism": ({"dp": "dp", "tp": "tp+sp", "zero3": "zero3-dp", "ep": "ep+dp"}[par] + str(world))
+            if world > 1 else f"single ({par} code path)",
             "dp_impl": (args.dp_impl if world > 1 else None),
             "optimizer": "AdamW fp32 master + bf16 compute copy, grad clip 1.0",
-            "cuda_graph": not args.no_graph,
+            "cuda_graph": engine.use_graph,
             "l2": "no flush: one step streams >3 GB of activations, weights and optimizer state (L2 is 126 MB)",
         },
         "clocks": clocks,

@@ -48,6 +48,11 @@ class TrainEngine:
         self.hyper = torch.tensor([self.opt.lr, 1.0, 1.0, 1.0], dtype=torch.float32, device=dev)
         self.lr_host = torch.tensor([self.opt.lr], dtype=torch.float32).pin_memory()
         self.step_dev = torch.zeros((), dtype=torch.int64, device=dev)
+        # rank-local parameter shards (tensor / expert parallel models) use their own hyper vector:
+        # the same step and clip factor with the model's gradient scale folded in
+        self.local_arenas = list(getattr(model, "local_arenas", []))
+        self.local_grad_scale = float(getattr(model, "local_grad_scale", 1.0))
+        self.hyper_local = self.hyper.clone()
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         # library collectives (the NCCL baseline path) stay out of graph capture
@@ -63,15 +68,25 @@ class TrainEngine:
         K.adamw_tick(self.step_dev, self.hyper, o.beta1, o.beta2)
         if self.dp is not None:
             self.dp.reduce_and_update(a, self.hyper, o, self.sumsq, self.grad_norm, self.step_dev)
-            return
-        if o.grad_clip is not None:
-            K.sumsq(a.grads, out=self.sumsq)
-            K.clip_scale(self.sumsq, o.grad_clip, self.hyper, self.grad_norm)
-        K.adamw_dev(a.master, a.params, a.grads, a.m, a.v, self.hyper,
-                    beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay)
+        else:
+            if o.grad_clip is not None:
+                K.sumsq(a.grads, out=self.sumsq)
+                K.clip_scale(self.sumsq, o.grad_clip, self.hyper, self.grad_norm)
+            K.adamw_dev(a.master, a.params, a.grads, a.m, a.v, self.hyper,
+                        beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay)
+        if self.local_arenas:
+            # (the clip factor is the one derived from the replicated parameters' global norm)
+            self.hyper_local.copy_(self.hyper)
+            if self.local_grad_scale != 1.0:
+                self.hyper_local[3:4].mul_(self.local_grad_scale)
+            for la in self.local_arenas:
+                K.adamw_dev(la.master, la.params, la.grads, la.m, la.v, self.hyper_local,
+                            beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay)
 
     def _step_body(self) -> None:
         n0 = K.launch_count()
+        if hasattr(self.model, "begin_step"):
+            self.model.begin_step()
         self.model.reset_grads()
         loss_id = self.model.forward(self.ids, self.targets)
         self.last_report = self.tape.backward(loss_id, BackwardOptions())
@@ -89,6 +104,7 @@ class TrainEngine:
         own = self.dp if (self.dp is not None and a.master is None) else a   # who holds master/m/v
         snap = (own.master.clone(), own.m.clone(), own.v.clone(), self.step_dev.clone(), self.hyper.clone(),
                 a.params.clone())
+        snap_local = [(la.master.clone(), la.m.clone(), la.v.clone(), la.params.clone()) for la in self.local_arenas]
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -99,6 +115,8 @@ class TrainEngine:
         own.master.copy_(snap[0]); own.m.copy_(snap[1]); own.v.copy_(snap[2])
         self.hyper.copy_(snap[4])
         a.params.copy_(snap[5])
+        for la, sl in zip(self.local_arenas, snap_local):
+            la.master.copy_(sl[0]); la.m.copy_(sl[1]); la.v.copy_(sl[2]); la.params.copy_(sl[3])
         self.step_dev.copy_(snap[3])   # (the multi-GPU path keeps its own, never-rewinding sequence)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):

@@ -38,6 +38,24 @@ def test_expert_parallel_moe(cuda_device):
     assert p.returncode == 0 and "MOE_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
 
 
+def test_tensor_parallel_gpt_follows_unsharded_model(cuda_device):
+    """Tensor + sequence parallel GPT (fused all-gather->GEMM / GEMM->reduce-scatter blocks)."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    p = _run_workers("_tp_worker.py", 2, 29637)
+    assert p.returncode == 0 and "TP_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_zero3_gpt_follows_unsharded_model(cuda_device):
+    """Block weights sharded by rows: gather fused into fwd / dgrad GEMMs, wgrad reduce-scattered."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    p = _run_workers("_zero3_worker.py", 2, 29639)
+    assert p.returncode == 0 and "ZERO3_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
 def test_fused_data_parallel_matches_nccl_and_replays(cuda_device):
     n = torch.cuda.device_count()
     if n < 2:
