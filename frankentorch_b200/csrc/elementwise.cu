@@ -440,3 +440,35 @@ extern "C" int ftk_fill_f32(float* x, long long n, float v, void* stream) {
   fill_f32_kernel<<<ew_grid(n, 256), 256, 0, STREAM(stream)>>>(x, n, v);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Bounded-wait self test: one thread waits for *flag >= want with a cycle budget and, when the
+// budget runs out, records FT_ERR_WAIT_PEER in the status word and returns - the same protocol
+// every peer wait of the multi-GPU kernels follows.  The host test points it at a flag that
+// nothing sets and checks that the status word reports the timeout while the context stays usable.
+__global__ void wait_probe_kernel(const int* flag, int want, long long budget_cycles, int* status,
+                                  long long* waited_cycles) {
+  const long long t0 = clock64();
+  int v;
+  bool ok = true;
+  while (true) {
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= want) break;
+    __nanosleep(256);
+    if (clock64() - t0 > budget_cycles) {
+      atomicCAS(status, 0, ftk::FT_ERR_WAIT_PEER | (int(blockIdx.x) << 8));
+      ok = false;
+      break;
+    }
+  }
+  if (waited_cycles) *waited_cycles = ok ? 0 : clock64() - t0;
+}
+
+extern "C" int ftk_wait_probe(const int* flag, int want, long long budget_cycles, long long* waited_cycles,
+                              void* stream) {
+  int* status = ftk_status_word();
+  if (!status || !flag || budget_cycles <= 0 || budget_cycles > 4000000000ll) return -2;
+  wait_probe_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, want, budget_cycles, status,
+                                                                         waited_cycles);
+  return (int)cudaGetLastError();
+}

@@ -217,6 +217,10 @@ int ftk_present_rgba8(const unsigned char* src, void* dst, int width, int height
 // 1-D convolution-over-time gather X[t_in, cin] -> Y[t_out, cin*k] with zero padding.
 int ftk_im2col_1d(const float* x, float* y, int t_in, int cin, int k, int stride, int pad,
                   int t_out, void* stream);
+// Bounded-wait self test: waits up to budget_cycles (<= 4e9) for *flag >= want; on timeout the
+// status word gets FT_ERR_WAIT_PEER and *waited_cycles the cycles spent.  Never blocks longer.
+int ftk_wait_probe(const int* flag, int want, long long budget_cycles, long long* waited_cycles,
+                   void* stream);
 
 #ifdef __cplusplus
 }

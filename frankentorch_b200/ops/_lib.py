@@ -137,6 +137,7 @@ def load(build_if_missing: bool = True):
         "ftk_fill_f32": [vp, ll, f, vp],
         "ftk_present_rgba8": [vp, vp, i, i, ll, i, vp],
         "ftk_im2col_1d": [vp, vp, i, i, i, i, i, i, vp],
+        "ftk_wait_probe": [vp, i, ll, vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
