@@ -30,31 +30,36 @@ constexpr int BW_WARP_TMA = 16;
 constexpr int BW_WARP_MMA = 17;
 
 // =============================================================================== delta
-// delta[b,h,s] = sum_e dO * O ; one warp per (b, s, h) row.
+// delta[b,h,s] = sum_e dO * O.  LPR = hd / 8 lanes share one (b, s, h) row (16 bytes each), so
+// a warp covers 32 / LPR rows and every lane loads.
+template <int LPR>
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                  float* __restrict__ delta, int B, int H, int S, int hd, long long bs,
-                  long long ss, long long hs) {
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+                  float* __restrict__ delta, int B, int H, int S, long long bs, long long ss,
+                  long long hs) {
+  constexpr int RPW = 32 / LPR;                       // rows per warp
   const int lane = threadIdx.x & 31;
-  if (w >= (long long)B * S * H) return;
-  const int h = (int)(w % H);
-  const long long t = w / H;
-  const int s = (int)(t % S);
-  const int b = (int)(t / S);
-  const long long off = (long long)b * bs + (long long)s * ss + (long long)h * hs;
+  const long long w = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
+  const int sub = lane % LPR;
   float acc = 0.f;
-  if (lane * 8 < hd) {
-    uint4 a = *reinterpret_cast<const uint4*>(o + off + lane * 8);
-    uint4 g = *reinterpret_cast<const uint4*>(d_o + off + lane * 8);
+  const bool live = w < (long long)B * S * H;
+  int h = 0, s = 0, b = 0;
+  if (live) {
+    h = (int)(w % H);
+    const long long t = w / H;
+    s = (int)(t % S);
+    b = (int)(t / S);
+    const long long off = (long long)b * bs + (long long)s * ss + (long long)h * hs + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + off);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + off);
     float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), a2 = unpack_bf16(a.z), a3 = unpack_bf16(a.w);
     float2 g0 = unpack_bf16(g.x), g1 = unpack_bf16(g.y), g2 = unpack_bf16(g.z), g3 = unpack_bf16(g.w);
     acc = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y + a2.x * g2.x + a2.y * g2.y +
           a3.x * g3.x + a3.y * g3.y;
   }
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
-  if (lane == 0) delta[((long long)b * H + h) * S + s] = acc;
+  for (int d = LPR / 2; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  if (live && sub == 0) delta[((long long)b * H + h) * S + s] = acc;
 }
 
 // Store 32 packed-bf16 columns (16 words) of one tile row into the swizzled K-major tile.
@@ -518,9 +523,10 @@ static int attn_bwd_launch(const FtkAttnDesc* a, cudaStream_t s) {
     attr = true;
   }
   const long long nrows = (long long)a->B * a->S * a->H;
-  attn_delta_kernel<<<(unsigned)((nrows + 7) / 8), 256, 0, s>>>(
+  constexpr int LPR = HD / 8, ROWS_PER_CTA = 8 * (32 / LPR);
+  attn_delta_kernel<LPR><<<(unsigned)((nrows + ROWS_PER_CTA - 1) / ROWS_PER_CTA), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(a->o), reinterpret_cast<const __nv_bfloat16*>(a->d_o),
-      a->delta, a->B, a->H, a->S, a->hd, a->o_bs, a->o_ss, a->o_hs);
+      a->delta, a->B, a->H, a->S, a->o_bs, a->o_ss, a->o_hs);
   dim3 grid((a->S + AT_T - 1) / AT_T, a->H, a->B);
   attn_bwd_dkv_kernel<HD><<<grid, BW_THREADS, DkvCfg<HD>::SMEM, s>>>(tq, tk, tv, tdo, p);
   attn_bwd_dq_kernel<HD><<<grid, BW_THREADS, DqCfg<HD>::SMEM, s>>>(tq, tk, tv, tdo, p);

@@ -21,7 +21,7 @@
 // the mainloop of tile i+1.  The device code, including the collective-fused forms
 // (all-gather -> GEMM, GEMM -> reduce-scatter), lives in gemm_kernel.cuh; this file holds
 // the split-K reduction and the host launchers.
-#include "gemm_kernel.cuh"
+#include "gemm2_kernel.cuh"
 
 namespace ftk {
 
@@ -135,6 +135,28 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return (int)cudaGetLastError();
 }
 
+// CTA-pair kernel: grid = 2 CTAs per cluster, at most sms / 2 clusters.
+#ifndef FTK_PAIR_TILE_COST
+#define FTK_PAIR_TILE_COST 9.0   /* not chosen by the heuristic until measured; force_bn = 512 selects it */
+#endif
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& a, int max_ctas,
+                            cudaStream_t stream) {
+  using Cfg = Gemm2Cfg;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const long long items = (long long)((a.M + 255) / 256) * ((a.N + 255) / 256) * a.L0 * a.L1 * a.splits;
+  long long pairs = max_ctas / 2;
+  if (items < pairs) pairs = items;
+  if (pairs <= 0) return 0;
+  gemm2_bf16_sm100_kernel<<<(unsigned)(2 * pairs), G_THREADS, Cfg::SMEM, stream>>>(tmA, tmB, a);
+  return (int)cudaGetLastError();
+}
+
 static int make_operand_maps(const FtkGemmDesc* g, int L0, int L1, int bn, CUtensorMap* tmA,
                              CUtensorMap* tmB) {
   int rc;
@@ -194,7 +216,14 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   const int kblocks = (g->K + G_BK - 1) / G_BK;
   const bool splittable = g->epi == FTK_EPI_NONE && !g->bias && !g->resid && !g->aux && g->workspace &&
                           (g->N % 4 == 0) && (g->ldd % 4 == 0) && L0 * L1 == 1;
+  // Option 512 is the CTA-pair kernel: 256 x 256 tiles on sms / 2 clusters; per SM it does the
+  // work of a 128 x 256 tile with a third less operand traffic (FTK_PAIR_TILE_COST, measured).
   auto cost = [&](int bn, int s) {
+    if (bn == 512) {
+      const long long tiles = ((g->M + 255) / 256) * ((g->N + 255) / 256) * L0 * L1;
+      const long long waves = (tiles * s + sms / 2 - 1) / (sms / 2);
+      return (double)waves * FTK_PAIR_TILE_COST / s + (s > 1 ? 0.08 + 0.01 * s : 0.0);
+    }
     const long long tiles = tiles_m * ((g->N + bn - 1) / bn) * L0 * L1;
     const long long waves = (tiles * s + sms - 1) / sms;
     const double w = bn == 256 ? 1.0 : (bn == 192 ? 0.80 : 0.86);
@@ -205,11 +234,12 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
     if (!splittable || g->split_k == 1 || kblocks / s < 8) return false;
     return (long long)s * g->M * g->N * 4 <= g->workspace_bytes;
   };
-  static const int bn_opts[3] = {256, 192, 128};
+  static const int bn_opts[4] = {512, 256, 192, 128};
   static const int s_opts[8] = {1, 2, 3, 4, 6, 8, 12, 16};
   int bn = g->force_bn, splits = 1;
   double best = 1e30;
-  for (int bi = 0; bi < 3; ++bi) {
+  for (int bi = 0; bi < 4; ++bi) {
+    if (bn_opts[bi] == 512 && (sms < 2 || g->M < 256)) continue;
     if (g->force_bn && bn_opts[bi] != g->force_bn) continue;
     for (int si = 0; si < 8; ++si) {
       const int s = s_opts[si];
@@ -224,19 +254,20 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
     }
   }
   if (g->split_k > 1 && split_ok(g->split_k)) splits = g->split_k;
-  if (bn != 128 && bn != 192 && bn != 256) return -5;
+  if (bn != 128 && bn != 192 && bn != 256 && bn != 512) return -5;
 
   CUtensorMap tmA, tmB;
-  int rc = make_operand_maps(g, L0, L1, bn, &tmA, &tmB);
+  int rc = make_operand_maps(g, L0, L1, bn == 512 ? 128 : bn, &tmA, &tmB);   // a pair stages 128 B rows per CTA
   if (rc) return rc;
 
   GemmArgs a;
   fill_gemm_args(a, g, L0, L1);
   a.splits = splits;
   if (!a.status) return -6;
-  rc = bn == 256 ? launch_gemm<256>(tmA, tmB, a, sms, stream)
-                 : (bn == 192 ? launch_gemm<192>(tmA, tmB, a, sms, stream)
-                              : launch_gemm<128>(tmA, tmB, a, sms, stream));
+  rc = bn == 512 ? launch_gemm_pair(tmA, tmB, a, sms, stream)
+       : bn == 256 ? launch_gemm<256>(tmA, tmB, a, sms, stream)
+                   : (bn == 192 ? launch_gemm<192>(tmA, tmB, a, sms, stream)
+                                : launch_gemm<128>(tmA, tmB, a, sms, stream));
   if (rc || splits == 1) return rc;
   const long long total4 = ((long long)g->M * g->N) >> 2;
   long long blocks = (total4 + 255) / 256;

@@ -166,6 +166,147 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// ----------------------------------------------------------------------------- LayerNorm bwd, one pass
+// dx and the per-block column partials of dgamma / dbeta from a single read of dy and x.
+// A CTA of 8 warps owns LNB_ROWS consecutive rows; warp w takes rows w, w + 8, ... in ascending
+// order, keeps the row in registers (packed bf16), and adds dy*xhat / dy into per-lane column
+// accumulators.  The 8 warps then add their accumulators into shared memory one after the
+// other (fixed order) and the CTA writes partial[blk][c].  NV = 16-byte vectors per lane.
+constexpr int LNB_ROWS = 32;
+template <int NV>
+__global__ void __launch_bounds__(ROW_WARPS * 32, 2)
+ln_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                    const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                    const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dx_add,
+                    __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int cols,
+                    int nblk) {
+  __shared__ float sg[NV * 256], sb[NV * 256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;
+  const uint4* gv = reinterpret_cast<const uint4*>(gamma);
+  uint4 gp[NV];
+  float dg[NV][8], db[NV][8];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int v = lane + 32 * j;
+    gp[j] = v < nvec ? __ldg(gv + v) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dg[j][i] = db[j][i] = 0.f;
+  }
+  for (int rr = 0; rr < LNB_ROWS / ROW_WARPS; ++rr) {
+    const int row = blockIdx.x * LNB_ROWS + rr * ROW_WARPS + warp;
+    if (row >= rows) break;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
+    const uint4* dr = reinterpret_cast<const uint4*>(dy + (size_t)row * cols);
+    uint4 xp[NV], dp[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      xp[j] = v < nvec ? xr[v] : make_uint4(0u, 0u, 0u, 0u);
+      dp[j] = v < nvec ? dr[v] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (lane + 32 * j < nvec) {
+        float fx[8], fd[8], g[8];
+        unpack8(xp[j], fx);
+        unpack8(dp[j], fd);
+        unpack8(gp[j], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float gd = g[i] * fd[i];
+          const float xh = (fx[i] - mean) * rstd;
+          s1 += gd;
+          s2 += gd * xh;
+          dg[j][i] += fd[i] * xh;
+          db[j][i] += fd[i];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / cols;
+    s2 = warp_sum(s2) / cols;
+    const uint4* av = dx_add ? reinterpret_cast<const uint4*>(dx_add + (size_t)row * cols) : nullptr;
+    uint4* ov = reinterpret_cast<uint4*>(dx + (size_t)row * cols);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nvec) {
+        float fx[8], fd[8], g[8], a[8];
+        unpack8(xp[j], fx);
+        unpack8(dp[j], fd);
+        unpack8(gp[j], g);
+        if (av) unpack8(av[v], a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xh = (fx[i] - mean) * rstd;
+          const float r = rstd * (g[i] * fd[i] - s1 - xh * s2);
+          fx[i] = av ? r + a[i] : r;
+        }
+        ov[v] = pack8(fx);
+      }
+    }
+  }
+  // warps add their column accumulators in warp order
+  for (int w = 0; w < ROW_WARPS; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int v = lane + 32 * j;
+        if (v < nvec) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = v * 8 + i;
+            sg[c] = w == 0 ? dg[j][i] : sg[c] + dg[j][i];
+            sb[c] = w == 0 ? db[j][i] : sb[c] + db[j][i];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* pg = partial + (size_t)blockIdx.x * cols;
+  float* pb = partial + ((size_t)nblk + blockIdx.x) * cols;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    pg[c] = sg[c];
+    pb[c] = sb[c];
+  }
+}
+
+// Fixed-order sum over many block partials, parallel over 8 interleaved groups of blocks:
+// thread (g, c) adds partial[b][c] for b = g, g + 8, ... ascending, then the 8 group sums are
+// added in group order.  `two` arrays per launch (dgamma and dbeta).
+__global__ void __launch_bounds__(256)
+col_final_wide_kernel(const float* __restrict__ partial, float* __restrict__ out,
+                      const float* __restrict__ partial2, float* __restrict__ out2, int cols, int nblk,
+                      int accumulate) {
+  __shared__ float sm[2][8][32];
+  const int cl = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
+  float s = 0.f, t = 0.f;
+  if (c < cols) {
+#pragma unroll 4
+    for (int b = g; b < nblk; b += 8) {
+      s += partial[(size_t)b * cols + c];
+      if (partial2) t += partial2[(size_t)b * cols + c];
+    }
+  }
+  sm[0][g][cl] = s;
+  sm[1][g][cl] = t;
+  __syncthreads();
+  if (g == 0 && c < cols) {
+    float a = 0.f, b2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      a += sm[0][k][cl];
+      b2 += sm[1][k][cl];
+    }
+    out[c] = accumulate ? out[c] + a : a;
+    if (partial2) out2[c] = accumulate ? out2[c] + b2 : b2;
+  }
+}
+
 // Column partials: partial[blk][c] = sum over this block's rows of dy*xhat, and of dy.
 // MODE 0: LayerNorm (two outputs), 1: RMSNorm (dgamma only), 2: plain column sum of dy.
 // A CTA covers 64 columns x COL_ROWS_PER_BLK rows with 8 row groups of 32 column pairs:
@@ -433,10 +574,9 @@ extern "C" int ftk_rmsnorm_fwd(const void* x, const void* gamma, void* y, float*
       BF(x), nullptr, nullptr, BF(gamma), nullptr, BFW(y), nullptr, rstd, rows, cols, eps);
   return (int)cudaGetLastError();
 }
-extern "C" int ftk_layernorm_bwd_blocks(int rows) {
-  return (rows + COL_ROWS_PER_BLK - 1) / COL_ROWS_PER_BLK;
-}
-extern "C" int ftk_colsum_blocks(int rows) { return ftk_layernorm_bwd_blocks(rows); }
+// number of partial blocks the caller must provide room for (2 * blocks * cols floats)
+extern "C" int ftk_layernorm_bwd_blocks(int rows) { return (rows + LNB_ROWS - 1) / LNB_ROWS; }
+extern "C" int ftk_colsum_blocks(int rows) { return (rows + COL_ROWS_PER_BLK - 1) / COL_ROWS_PER_BLK; }
 
 extern "C" int ftk_layernorm_bwd(const void* dy, const void* x, const void* gamma,
                                  const float* mean, const float* rstd, const void* dx_add, void* dx,
@@ -444,10 +584,20 @@ extern "C" int ftk_layernorm_bwd(const void* dy, const void* x, const void* gamm
                                  int accumulate, void* stream) {
   if (cols % 8 || rows <= 0) return -2;
   cudaStream_t s = STREAM(stream);
+  if (dgamma && cols <= 768) {
+    // one pass: dx + column partials, then the fixed-order sum over blocks (wider rows would
+    // spill the per-lane column accumulators and take the three-kernel path below)
+    const int nblk = ftk_layernorm_bwd_blocks(rows);
+    ln_bwd_fused_kernel<3><<<nblk, ROW_WARPS * 32, 0, s>>>(BF(dy), BF(x), BF(gamma), mean, rstd, BF(dx_add),
+                                                          BFW(dx), partial, rows, cols, nblk);
+    col_final_wide_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, dgamma, partial + (size_t)nblk * cols, dbeta,
+                                                           cols, nblk, accumulate);
+    return (int)cudaGetLastError();
+  }
   norm_bwd_dx_kernel<false><<<(rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, s>>>(
       BF(dy), BF(x), BF(gamma), mean, rstd, BF(dx_add), BFW(dx), rows, cols);
   if (dgamma) {
-    const int nblk = ftk_layernorm_bwd_blocks(rows);
+    const int nblk = ftk_colsum_blocks(rows);
     dim3 g((cols / 2 + 31) / 32, nblk);
     col_partial_kernel<0><<<g, 256, 0, s>>>(BF(dy), BF(x), mean, rstd, partial, rows, cols, cols, nblk);
     col_final_kernel<<<(cols + 127) / 128, 128, 0, s>>>(partial, dgamma, partial + (size_t)nblk * cols,
@@ -463,11 +613,11 @@ extern "C" int ftk_rmsnorm_bwd(const void* dy, const void* x, const void* gamma,
   norm_bwd_dx_kernel<true><<<(rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, s>>>(
       BF(dy), BF(x), BF(gamma), nullptr, rstd, nullptr, BFW(dx), rows, cols);
   if (dgamma) {
-    const int nblk = ftk_layernorm_bwd_blocks(rows);
+    const int nblk = ftk_colsum_blocks(rows);
     dim3 g((cols / 2 + 31) / 32, nblk);
     col_partial_kernel<1><<<g, 256, 0, s>>>(BF(dy), BF(x), nullptr, rstd, partial, rows, cols, cols, nblk);
-    col_final_kernel<<<(cols + 127) / 128, 128, 0, s>>>(partial, dgamma, nullptr, nullptr, cols, nblk,
-                                                         accumulate);
+    col_final_wide_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, dgamma, nullptr, nullptr, cols, nblk,
+                                                           accumulate);
   }
   return (int)cudaGetLastError();
 }
@@ -478,7 +628,7 @@ extern "C" int ftk_colsum_bf16(const void* x, float* out, float* partial, int ro
   const int nblk = ftk_colsum_blocks(rows);
   dim3 g((cols / 2 + 31) / 32, nblk);
   col_partial_kernel<2><<<g, 256, 0, s>>>(BF(x), nullptr, nullptr, nullptr, partial, rows, cols, ld, nblk);
-  col_final_kernel<<<(cols + 127) / 128, 128, 0, s>>>(partial, out, nullptr, nullptr, cols, nblk, accumulate);
+  col_final_wide_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, out, nullptr, nullptr, cols, nblk, accumulate);
   return (int)cudaGetLastError();
 }
 

@@ -141,3 +141,47 @@ def test_gemm_batched(cuda_device):
     k.check_status()
     ref = 0.5 * torch.einsum("xymk,xynk->xymn", a.float(), b.float())
     _check(out, ref, 2e-2, "batched")
+
+
+# ------------------------------------------------------------------ CTA-pair kernel (force_bn = 512)
+@pytest.mark.parametrize("M,N,K", [
+    (256, 256, 64),           # one pair tile, one k-block
+    (256, 256, 512),          # k loop over the 6-stage ring
+    (512, 768, 320),          # several tiles, ragged K
+    (520, 264, 200),          # ragged M / N: the peer CTA's rows and columns run off the edge
+    (4096, 2304, 768),        # more tiles than clusters: persistent loop + accumulator ping-pong
+])
+def test_gemm_pair_kmajor(cuda_device, M, N, K):
+    k = _ops()
+    a = _rand((M, K), cuda_device, seed=11)
+    b = _rand((N, K), cuda_device, seed=12)
+    out = k.gemm(a, b, force_bn=512)
+    k.check_status()
+    _check(out, a.float() @ b.float().t(), 2e-2, f"pair gemm {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+def test_gemm_pair_mn_major_and_epilogues(cuda_device, a_mn, b_mn):
+    k = _ops()
+    M, N, K = 512, 640, 384
+    a = _rand((K, M) if a_mn else (M, K), cuda_device, seed=13)
+    b = _rand((K, N) if b_mn else (N, K), cuda_device, seed=14)
+    bias = _rand((N,), cuda_device, seed=15)
+    resid = _rand((M, N), cuda_device, seed=16)
+    out = k.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, resid=resid, force_bn=512)
+    k.check_status()
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    _check(out, af @ bf + bias.float() + resid.float(), 2e-2, f"pair gemm a_mn={a_mn} b_mn={b_mn}")
+
+
+def test_gemm_pair_split_k_and_determinism(cuda_device):
+    k = _ops()
+    a = _rand((4096, 768), cuda_device, seed=17)       # wgrad shape: dW = dy^T x
+    b = _rand((4096, 768), cuda_device, seed=18)
+    ref = a.float().t() @ b.float()
+    o1 = k.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32, force_bn=512, split_k=4)
+    o2 = k.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32, force_bn=512, split_k=4, max_ctas=36)
+    k.check_status()
+    _check(o1, ref, 2e-2, "pair split-k")
+    assert torch.equal(o1, o2), "the pair kernel's result must not depend on the grid"
