@@ -24,7 +24,8 @@ struct Gemm2Cfg {
   static constexpr int STAGES = 6;
   static constexpr int ACC_STRIDE = 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/ +
+                              G_EPI_WARPS * 4096 /*output staging tiles*/;
 };
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G_THREADS, 1)
@@ -209,6 +210,10 @@ gemm2_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       const long long d_off = l0 * p.d_s0 + l1 * p.d_s1 + row * p.ldd;
       const long long r_off = l0 * p.r_s0 + l1 * p.r_s1 + row * p.ldr;
       const bool need_r = p.resid != nullptr;
+      // bf16 outputs leave through a per-warp transposing smem tile (see OutStager)
+      OutStager stager(smem + Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES) + 256 + ew * 4096, p,
+                       reinterpret_cast<__nv_bfloat16*>(p.D) + l0 * p.d_s0 + l1 * p.d_s1,
+                       (long long)m_t * G_BM + q * 32, lane);
 #pragma unroll 1
       for (int ci = c_begin; ci < c_end; ++ci) {
         const int c0 = ci * 32;
@@ -216,6 +221,8 @@ gemm2_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         tmem_ld32(tmem_base + acc * Cfg::ACC_STRIDE + c0 + ((uint32_t)(q * 32) << 16), r);
         tmem_ld_wait();
         const int n0 = n_t * BN + c0;
+        const bool stage_this = stager.usable && n0 + 32 <= p.N;     // warp-uniform
+        if (!stage_this) stager.flush();
         if (row < p.M && n0 < p.N) {
           float v[32];
 #pragma unroll
@@ -299,6 +306,8 @@ gemm2_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
               for (int i = 0; i < 32; ++i)
                 if (n0 + i < p.N) dp[i] = p.accumulate ? dp[i] + v[i] : v[i];
             }
+          } else if (stage_this) {
+            stager.put(v);
           } else {
             __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + d_off + n0;
             if (full_chunk && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
@@ -326,7 +335,9 @@ gemm2_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
             }
           }
         }
+        if (stage_this) stager.chunk_done(n0);     // every lane of the warp, also rows past M
       }
+      stager.flush();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&tempty[acc]);   // the MMA warp lives in the leader CTA

@@ -67,10 +67,11 @@ template <int BN>
 struct GemmCfg {
   static constexpr int A_BYTES = G_BM * G_BK * 2;
   static constexpr int B_BYTES = BN * G_BK * 2;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 5 : 6);
+  static constexpr int STAGES = (BN == 128) ? 6 : 4;
   static constexpr int ACC_STRIDE = (BN == 192) ? 256 : BN;  // TMEM columns between accumulators
   static constexpr int TMEM_COLS = (BN == 128) ? 256 : 512;  // power of two
-  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*align*/ + 256 /*barriers*/ +
+                              G_EPI_WARPS * 4096 /*output staging tiles*/;
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -121,6 +122,62 @@ __device__ __forceinline__ void apply_epi32(float* v, const float* rr, int epi) 
       break;
   }
 }
+
+// ------------------------------------------------------------------ coalescing bf16 output stores
+// One warp's staging tile: 32 rows x 128 B in shared memory, 16-byte segments XOR-swizzled by
+// the row.  A thread `put`s the packed bf16 of its row for one 32-column chunk; after two chunks
+// (or at the end of the tile) `flush` reads the tile transposed so that 8 consecutive lanes
+// write 128 contiguous bytes (4 lanes / 64 bytes when only one chunk is staged) of one row.
+struct OutStager {
+  uint8_t* tile;
+  __nv_bfloat16* d_base;       // row 0 of the output (of this batch entry)
+  long long row0, ldd;         // first output row of this warp's slab, leading dimension
+  int M, lane, staged, n_start;
+  bool usable;
+  __device__ __forceinline__ OutStager(uint8_t* t, const GemmArgs& p, __nv_bfloat16* d, long long r0, int ln)
+      : tile(t), d_base(d), row0(r0), ldd(p.ldd), M(p.M), lane(ln), staged(0), n_start(0) {
+    usable = !p.out_fp32 && !p.accumulate && p.splits == 1 && (p.ldd % 8 == 0) &&
+             ((reinterpret_cast<uintptr_t>(d) & 15) == 0);
+  }
+  __device__ __forceinline__ void put(const float* v) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 o;
+      o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
+      o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+      o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+      o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+      *reinterpret_cast<uint4*>(tile + lane * 128 + (((staged * 4 + i) ^ (lane & 7)) << 4)) = o;
+    }
+  }
+  __device__ __forceinline__ void chunk_done(int n0) {
+    if (staged == 0) n_start = n0;
+    if (++staged == 2) flush();
+  }
+  __device__ __forceinline__ void flush() {
+    if (staged == 0) return;
+    __syncwarp();
+    if (staged == 2) {
+      const int seg = lane & 7;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + (lane >> 3);
+        const uint4 o = *reinterpret_cast<const uint4*>(tile + rr * 128 + ((seg ^ (rr & 7)) << 4));
+        if (row0 + rr < M) *reinterpret_cast<uint4*>(d_base + (row0 + rr) * ldd + n_start + seg * 8) = o;
+      }
+    } else {
+      const int seg = lane & 3;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = 8 * i + (lane >> 2);
+        const uint4 o = *reinterpret_cast<const uint4*>(tile + rr * 128 + ((seg ^ (rr & 7)) << 4));
+        if (row0 + rr < M) *reinterpret_cast<uint4*>(d_base + (row0 + rr) * ldd + n_start + seg * 8) = o;
+      }
+    }
+    __syncwarp();
+    staged = 0;
+  }
+};
 
 // ------------------------------------------------------------------ flags between CTAs / ranks
 __device__ __forceinline__ int ld_acq_gpu(const int* p) {
@@ -712,6 +769,13 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       const long long d_off = l0 * p.d_s0 + l1 * p.d_s1 + row * p.ldd;
       const long long r_off = l0 * p.r_s0 + l1 * p.r_s1 + row * p.ldr;
       const bool need_r = p.resid != nullptr;
+      // bf16 outputs leave through a per-warp smem tile (32 rows x 128 B, XOR-swizzled 16-byte
+      // segments): a thread owns one row of the accumulator, so direct stores would touch 32
+      // rows per instruction with 16 bytes each; after the transpose 8 consecutive lanes write
+      // 128 contiguous bytes of one row.
+      OutStager stager(smem + Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES) + 256 + ew * 4096, p,
+                       reinterpret_cast<__nv_bfloat16*>(p.D) + l0 * p.d_s0 + l1 * p.d_s1,
+                       (long long)m_t * G_BM + q * 32, lane);
 #pragma unroll 1
       for (int ci = c_begin; ci < c_end; ++ci) {
         const int c0 = ci * 32;
@@ -719,6 +783,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         tmem_ld32(tmem_base + acc * Cfg::ACC_STRIDE + c0 + ((uint32_t)(q * 32) << 16), r);
         tmem_ld_wait();
         const int n0 = n_t * BN + c0;
+        const bool stage_this = stager.usable && n0 + 32 <= p.N;     // warp-uniform
+        if (!stage_this) stager.flush();
         if (row < p.M && n0 < p.N) {
           float v[32];
 #pragma unroll
@@ -803,6 +869,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
               for (int i = 0; i < 32; ++i)
                 if (n0 + i < p.N) dp[i] = p.accumulate ? dp[i] + v[i] : v[i];
             }
+          } else if (stage_this) {
+            stager.put(v);
           } else {
             __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + d_off + n0;
             if (full_chunk && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
@@ -830,7 +898,9 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
             }
           }
         }
+        if (stage_this) stager.chunk_done(n0);     // every lane of the warp, also rows past M
       }
+      stager.flush();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);

@@ -136,9 +136,16 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
 }
 
 // CTA-pair kernel: grid = 2 CTAs per cluster, at most sms / 2 clusters.
-#ifndef FTK_PAIR_TILE_COST
-#define FTK_PAIR_TILE_COST 9.0   /* not chosen by the heuristic until measured; force_bn = 512 selects it */
-#endif
+// Relative cost of a pair tile in the tile-choice model (a lone 128 x 256 tile = 1.0); the
+// environment variable FT_GEMM_PAIR_COST overrides it (a large value disables the pair kernel).
+static double pair_tile_cost() {
+  static double c = -1.0;
+  if (c < 0.0) {
+    const char* e = getenv("FT_GEMM_PAIR_COST");
+    c = (e && atof(e) > 0.0) ? atof(e) : 0.92;
+  }
+  return c;
+}
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& a, int max_ctas,
                             cudaStream_t stream) {
   using Cfg = Gemm2Cfg;
@@ -217,12 +224,12 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   const bool splittable = g->epi == FTK_EPI_NONE && !g->bias && !g->resid && !g->aux && g->workspace &&
                           (g->N % 4 == 0) && (g->ldd % 4 == 0) && L0 * L1 == 1;
   // Option 512 is the CTA-pair kernel: 256 x 256 tiles on sms / 2 clusters; per SM it does the
-  // work of a 128 x 256 tile with a third less operand traffic (FTK_PAIR_TILE_COST, measured).
+  // work of a 128 x 256 tile with a third less operand traffic.
   auto cost = [&](int bn, int s) {
     if (bn == 512) {
       const long long tiles = ((g->M + 255) / 256) * ((g->N + 255) / 256) * L0 * L1;
       const long long waves = (tiles * s + sms / 2 - 1) / (sms / 2);
-      return (double)waves * FTK_PAIR_TILE_COST / s + (s > 1 ? 0.08 + 0.01 * s : 0.0);
+      return (double)waves * pair_tile_cost() / s + (s > 1 ? 0.08 + 0.01 * s : 0.0);
     }
     const long long tiles = tiles_m * ((g->N + bn - 1) / bn) * L0 * L1;
     const long long waves = (tiles * s + sms - 1) / sms;
@@ -338,7 +345,7 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   if (!a.status) return -6;
 
   using Cfg = GemmCfg<BN>;
-  constexpr int COMM_SMEM = Cfg::SMEM + G_EPI_WARPS * 4096;   // + per-warp store staging tiles
+  constexpr int COMM_SMEM = Cfg::SMEM;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100_kernel<BN, 1>,
