@@ -25,7 +25,7 @@
 namespace ftk {
 
 constexpr int BW_THREADS = 576;
-constexpr int BW_MATH = 512;        // threads that arrive on the math barriers
+constexpr int BW_MATH = 16;         // one arrival per math warp on the math barriers
 constexpr int BW_WARP_TMA = 16;
 constexpr int BW_WARP_MMA = 17;
 
@@ -116,8 +116,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* qdo_full = bars + 1;    // [2]
   uint64_t* qdo_empty = bars + 3;   // [2]
   uint64_t* st_full = bars + 5;     // S^T and dP^T in TMEM
-  uint64_t* st_free = bars + 6;     // both copied to registers (512 arrivals)
-  uint64_t* pds_ready = bars + 7;   // [2] P^T and dS^T written to smem (512 arrivals)
+  uint64_t* st_free = bars + 6;     // both copied to registers (one arrival per warp)
+  uint64_t* pds_ready = bars + 7;   // [2] P^T and dS^T written to smem (one arrival per warp)
   uint64_t* acc_done = bars + 9;    // [2] dV/dK MMAs that read the buffer finished
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
@@ -247,7 +247,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_ld32(tmem_base + C::TM_DPT + c0 + lane_sel, rd);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(st_free);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(st_free);      // one arrival per warp
       const float4* sl4 = reinterpret_cast<const float4*>(stat + st * 256 + c0);
       const float4* dl4 = reinterpret_cast<const float4*>(stat + st * 256 + 128 + c0);
       const bool need_mask = (q0 + AT_T > p.S) || (k0 + AT_T > p.S) || (p.causal && q0 < k0 + AT_T - 1);
@@ -278,7 +279,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       store_row32_packed(smem + C::OFF_PT + buf * 2 * AT_REGION, row, c0, pw);
       store_row32_packed(smem + C::OFF_DST + buf * 2 * AT_REGION, row, c0, dw);
       fence_proxy_async_smem();
-      mbar_arrive(&pds_ready[buf]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pds_ready[buf]);      // one arrival per warp
     }
     if (ok && nit > 0)
       ok = mbar_wait(&acc_done[(nit - 1) % C::NBUF], ((nit - 1) / C::NBUF) & 1, ctx, FT_ERR_WAIT_TMEM_FULL);
@@ -342,8 +344,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* kv_full = bars + 1;    // [3]
   uint64_t* kv_empty = bars + 4;   // [3]
   uint64_t* s_full = bars + 7;     // S and dP in TMEM
-  uint64_t* s_free = bars + 8;     // both copied to registers (512 arrivals)
-  uint64_t* ds_ready = bars + 9;   // [2] dS written to smem (512 arrivals)
+  uint64_t* s_free = bars + 8;     // both copied to registers (one arrival per warp)
+  uint64_t* ds_ready = bars + 9;   // [2] dS written to smem (one arrival per warp)
   uint64_t* acc_done = bars + 11;  // [2] dQ MMA that read the buffer finished
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
@@ -460,7 +462,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tmem_ld32(tmem_base + C::TM_DP + c0 + lane_sel, rd);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(s_free);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);      // one arrival per warp
       const int k0 = j * AT_T;
       const bool need_mask = (k0 + AT_T > p.S) || (q0 + AT_T > p.S) || (p.causal && k0 + AT_T - 1 > q0);
       uint32_t dw[16];
@@ -479,7 +482,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           !mbar_wait(&acc_done[buf], ((j / C::NBUF) - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       store_row32_packed(smem + C::OFF_DS + buf * 2 * AT_REGION, row, c0, dw);
       fence_proxy_async_smem();
-      mbar_arrive(&ds_ready[buf]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_ready[buf]);      // one arrival per warp
     }
     if (ok && nkv > 0)
       ok = mbar_wait(&acc_done[(nkv - 1) % C::NBUF], ((nkv - 1) / C::NBUF) & 1, ctx, FT_ERR_WAIT_TMEM_FULL);

@@ -59,8 +59,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* kv_full = bars + 1;        // [8]
   uint64_t* kv_empty = bars + 9;       // [8]
   uint64_t* s_full = bars + 17;        // [2] per tile: scores in TMEM
-  uint64_t* s_free = bars + 19;        // [2] per tile: scores copied to registers (128 arrivals)
-  uint64_t* p_ready = bars + 21;       // [2] per tile: probabilities in smem (128 arrivals)
+  uint64_t* s_free = bars + 19;        // [2] per tile: scores copied to registers (one arrival per warp)
+  uint64_t* p_ready = bars + 21;       // [2] per tile: probabilities in smem (one arrival per warp)
   uint64_t* pv_done = bars + 23;       // [2] per tile: PV finished (P tile free, O tile settled)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
   int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
@@ -79,8 +79,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 128);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&s_free[i], 4);      // one arrival per warp of the group
+      mbar_init(&p_ready[i], 4);
       mbar_init(&pv_done[i], 1);
     }
     *abort_f = 0;
@@ -207,7 +207,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld32(s_tmem + 96, r + 96);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&s_free[t]);               // the next QK^T may overwrite the score tile now
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[t]);   // the next QK^T may overwrite the score tile now
       const int k0 = j * AT_T;
       const bool need_mask = (k0 + AT_T > p.S) || (p.causal && k0 + AT_T - 1 > q0 + t * AT_T);
       if (need_mask) {
@@ -271,7 +272,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         *reinterpret_cast<uint4*>(sP + (c16 >> 3) * AT_REGION + (((c16 & 7) ^ (row & 7)) << 4)) = u;
       }
       fence_proxy_async_smem();
-      mbar_arrive(&p_ready[t]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[t]);
     }
     if (ok && n_my > 0) ok = mbar_wait(&pv_done[t], (n_my - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL);
     if (ok && n_my > 0) {
