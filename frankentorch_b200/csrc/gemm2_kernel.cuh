@@ -94,41 +94,6 @@ gemm2_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    // L2 prefetch cursor: walks the same (item, k-block) sequence G_L2_AHEAD steps ahead of the
-    // shared-memory ring, so operand tiles that come from HBM are in L2 when the ring asks
-    int pf_item = pair, pf_k = 0;
-    auto prefetch_step = [&]() {
-      if (pf_item >= total) return;
-      const int sp = pf_item / (tiles_mn * nbatch);
-      const int rem = pf_item - sp * (tiles_mn * nbatch);
-      const int l = rem / tiles_mn;
-      const int t = rem - l * tiles_mn;
-      const int a_row = (2 * (t % tiles_m2) + rank) * G_BM;
-      const int b_row = (t / tiles_m2) * BN + rank * 128;
-      const int kb0 = sp * kb_per_split;
-      const int kb1 = min(kblocks_all, kb0 + kb_per_split);
-      const int kb = kb0 + pf_k;
-      if (kb < kb1 && lane == 0) {
-        const int l0 = l % p.L0, l1 = l / p.L0;
-        if (!p.a_mn) {
-          tma_prefetch_l2_4d(&tmA, kb * G_BK, a_row, l0, l1);
-        } else {
-          tma_prefetch_l2_4d(&tmA, a_row, kb * G_BK, l0, l1);
-          tma_prefetch_l2_4d(&tmA, a_row + 64, kb * G_BK, l0, l1);
-        }
-        if (!p.b_mn) {
-          tma_prefetch_l2_4d(&tmB, kb * G_BK, b_row, l0, l1);
-        } else {
-          tma_prefetch_l2_4d(&tmB, b_row, kb * G_BK, l0, l1);
-          tma_prefetch_l2_4d(&tmB, b_row + 64, kb * G_BK, l0, l1);
-        }
-      }
-      if (++pf_k >= kb1 - kb0) {
-        pf_k = 0;
-        pf_item += n_pairs;
-      }
-    };
-    for (int i = 0; i < G_L2_AHEAD; ++i) prefetch_step();
     for (int item = pair; ok && item < total; item += n_pairs) {
       const int sp = item / (tiles_mn * nbatch);
       const int rem = item - sp * (tiles_mn * nbatch);
@@ -140,7 +105,6 @@ gemm2_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(kblocks_all, kb0 + kb_per_split);
       for (int kb = kb0; kb < kb1; ++kb) {
-        prefetch_step();
         if (!mbar_wait(&empty[s], ph ^ 1u, ctx, FT_ERR_WAIT_EMPTY)) {
           ok = false;
           break;

@@ -25,7 +25,6 @@ constexpr int G_BK = 64;
 constexpr int G_UMMA_K = 16;
 constexpr int G_EPI_WARPS = 8;
 constexpr int G_THREADS = 64 + 32 * G_EPI_WARPS;
-constexpr int G_L2_AHEAD = 8;        // k-blocks the L2 prefetch cursor runs ahead of the smem ring
 constexpr int G_MAX_RANKS = 8;
 constexpr int G_COPY_SLOT = 32768;   // bytes per bulk copy of the gather ring
 constexpr int G_COPY_SLOTS = 6;
@@ -560,40 +559,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     int k_ready = 0;
     // flag words per 128-row subtile of a gathered operand (one per copied piece)
     const int pps = !COMM ? 1 : (c.sub_bytes > G_COPY_SLOT ? (int)(c.sub_bytes / G_COPY_SLOT) : 1);
-    // L2 prefetch cursor (plain GEMMs only): walks the same (item, k-block) sequence
-    // G_L2_AHEAD steps ahead of the shared-memory ring, so that operand tiles which come from
-    // HBM are already in L2 when the ring asks for them
-    int pf_item = blockIdx.x, pf_k = 0;
-    auto prefetch_step = [&]() {
-      if (COMM || pf_item >= total) return;
-      const TileCoord t = decode_item<BN, COMM>(pf_item, p, c, tiles_m, tiles_n, nbatch);
-      const int kb0 = t.sp * kb_per_split;
-      const int kb1 = min(kblocks_all, kb0 + kb_per_split);
-      const int kb = kb0 + pf_k;
-      if (kb < kb1 && lane == 0) {
-        const int l0 = t.l % p.L0, l1 = t.l / p.L0;
-        if (!p.a_mn) {
-          tma_prefetch_l2_4d(&tmA, kb * G_BK, t.m_t * G_BM, l0, l1);
-        } else {
-#pragma unroll
-          for (int cc = 0; cc < G_BM / 64; ++cc)
-            tma_prefetch_l2_4d(&tmA, t.m_t * G_BM + cc * 64, kb * G_BK, l0, l1);
-        }
-        if (!p.b_mn) {
-          tma_prefetch_l2_4d(&tmB, kb * G_BK, t.n_t * BN, l0, l1);
-        } else {
-#pragma unroll
-          for (int cc = 0; cc < BN / 64; ++cc)
-            tma_prefetch_l2_4d(&tmB, t.n_t * BN + cc * 64, kb * G_BK, l0, l1);
-        }
-      }
-      if (++pf_k >= kb1 - kb0) {
-        pf_k = 0;
-        pf_item += n_compute;
-      }
-    };
-    if (!COMM)
-      for (int i = 0; i < G_L2_AHEAD; ++i) prefetch_step();
+    // (An L2 prefetch cursor running 8 k-blocks ahead of the ring was measured and removed: the
+    // extra TMA requests slowed the mainloop by 1.7x.)
     for (int item = blockIdx.x; ok && item < total; item += n_compute) {
       const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
       const int m_t = t.m_t, n_t = t.n_t;
@@ -637,7 +604,6 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         if (!__all_sync(0xffffffffu, good)) break;
       }
       for (int kb = kb0; kb < kb1; ++kb) {
-        prefetch_step();
         if (k_sharded) {
           // B is sharded along K: rows [0, k_ready * 128) of the staged operand are known final
           const int need = (min(p.K, kb * G_BK + G_BK) - 1) / G_BM + 1;
