@@ -224,6 +224,9 @@ class TensorTape:
         # its hooks still run); the GPU training path skips such nodes instead of launching fills.
         self.materialize_zero_grads = grad_dtype is not None
         self.accumulate_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor] = lambda a, b: a + b
+        # optional profiler hook: a callable returning a context manager, entered around every
+        # backward rule (NVTX ranges per tape node, see utils/profiling.py)
+        self.range_fn: Optional[Callable[[str], object]] = None
         self.last_plan_cache: Dict[Tuple[int, int], Tuple] = {}
 
     def __del__(self):
@@ -413,7 +416,11 @@ class TensorTape:
             if not node.requires_grad or node.vjp is None:
                 continue
             steps.append(TensorBackwardStep(nid, incoming.numel(), node.rule))
-            contribs = node.vjp(incoming, GradTargets(self, node, grads))
+            if self.range_fn is not None:
+                with self.range_fn("bwd:%s#%d" % (node.rule, nid)):
+                    contribs = node.vjp(incoming, GradTargets(self, node, grads))
+            else:
+                contribs = node.vjp(incoming, GradTargets(self, node, grads))
             if len(contribs) != len(node.inputs):
                 raise TensorGradientShapeMismatch(
                     f"rule '{node.rule}' returned {len(contribs)} gradients for {len(node.inputs)} inputs")

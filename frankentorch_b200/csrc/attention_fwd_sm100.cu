@@ -39,6 +39,17 @@ struct Fwd2Cfg {
   static constexpr int TM_O = 256;                          // O tile t at TM_O + HD t
 };
 
+#ifdef FT_ATTN_TRACE
+// Optional timeline of one CTA (development builds only): [role][iteration][point] clock64 values.
+__device__ long long g_attn_trace[4 * 16 * 8 + 3 * 4096];
+#define FT_TRACE(role, it, pt)                                                        \
+  do {                                                                                \
+    if (trace_cta && lane == 0 && (it) < 16) g_attn_trace[((role) * 16 + (it)) * 8 + (pt)] = clock64(); \
+  } while (0)
+#else
+#define FT_TRACE(role, it, pt) do { } while (0)
+#endif
+
 template <int REGS>
 __device__ __forceinline__ void reg_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
@@ -66,6 +77,18 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx ctx{p.status, abort_f};
+#ifdef FT_ATTN_TRACE
+  const bool trace_cta = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (threadIdx.x == 0 && cta_lin < 4096) {
+    unsigned long long t0;
+    unsigned smid;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    g_attn_trace[512 + cta_lin * 3 + 0] = (long long)t0;
+    g_attn_trace[512 + cta_lin * 3 + 2] = smid;
+  }
+#endif
 
   if ((smem_u32(smem) & 1023u) != 0u) {
     if (threadIdx.x == 0) atomicCAS(p.status, 0, FT_ERR_BAD_ARG);
@@ -161,14 +184,18 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       };
       if (ok && nkv > 0) ok = issue_scores(0);
       for (int j = 0; ok && j < nkv; ++j) {
+        FT_TRACE(2, j, 0);
         if (j + 1 < nkv) ok = issue_scores(j + 1);     // runs under the softmax of block j
         if (!ok) break;
+        FT_TRACE(2, j, 1);
         const int n = 2 * j + 1, slot = n % C::NSLOT;
         if (!mbar_wait(&kv_full[slot], (n / C::NSLOT) & 1, ctx, FT_ERR_WAIT_FULL)) break;
+        FT_TRACE(2, j, 2);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j >= nb[t]) continue;
           if (!mbar_wait(&p_ready[t], j & 1, ctx, FT_ERR_WAIT_SOFTMAX)) { ok = false; break; }
+          FT_TRACE(2, j, 3 + t);
           tc_fence_after();
           if (lane == 0) {
             mma_p_times_rows(tmem_base + C::TM_O + HD * t, p_addr + t * 2 * AT_REGION,
@@ -198,7 +225,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_my; ++j) {
+      FT_TRACE(t, j, 0);
       if (!mbar_wait(&s_full[t], j & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      FT_TRACE(t, j, 1);
       tc_fence_after();
       uint32_t r[128];
       tmem_ld32(s_tmem + 0, r + 0);
@@ -206,6 +235,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld32(s_tmem + 64, r + 64);
       tmem_ld32(s_tmem + 96, r + 96);
       tmem_ld_wait();
+      FT_TRACE(t, j, 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[t]);   // the next QK^T may overwrite the score tile now
@@ -227,6 +257,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
       }
       const float bm2 = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.sl2;   // sl2 > 0
+      FT_TRACE(t, j, 3);
       // lazy reference maximum: move it only when this block exceeds the headroom
       float alpha = 1.f;
       const bool move = (bm2 > m2 + F2_LAZY) || (m2 == -INFINITY && bm2 > -INFINITY);
@@ -247,6 +278,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         r[(i >> 1) + 1] = pack_bf16(e2, e3);
       }
       l = l * alpha + (rs0 + rs1) + (rs2 + rs3);
+      FT_TRACE(t, j, 4);
       if (j > 0) {
         // PV of the previous block must be finished before P is overwritten and before the
         // accumulator may be rescaled
@@ -266,6 +298,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_fence_before();
         }
       }
+      FT_TRACE(t, j, 5);
 #pragma unroll
       for (int c16 = 0; c16 < 16; ++c16) {     // 16 chunks of 8 bf16 (16 bytes)
         const uint4 u = make_uint4(r[4 * c16], r[4 * c16 + 1], r[4 * c16 + 2], r[4 * c16 + 3]);
@@ -274,6 +307,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t]);
+      FT_TRACE(t, j, 6);
     }
     if (ok && n_my > 0) ok = mbar_wait(&pv_done[t], (n_my - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL);
     if (ok && n_my > 0) {
@@ -309,6 +343,13 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 9) tmem_dealloc(tmem_base, C::TMEM_COLS);
+#ifdef FT_ATTN_TRACE
+  if (threadIdx.x == 0 && cta_lin < 4096) {
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    g_attn_trace[512 + cta_lin * 3 + 1] = (long long)t1;
+  }
+#endif
 }
 
 template <int HD>
@@ -334,6 +375,12 @@ static int attn_fwd2_launch(const FtkAttnDesc* a, cudaStream_t s) {
 }  // namespace ftk
 
 using namespace ftk;
+
+#ifdef FT_ATTN_TRACE
+extern "C" int ftk_attn_trace_read(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(long long) * n);
+}
+#endif
 
 extern "C" int ftk_attn_fwd(const FtkAttnDesc* a, void* stream) {
   if (!a || a->B <= 0 || a->H <= 0 || a->S <= 0) return -2;

@@ -24,6 +24,8 @@ peer, because every collective needs a contribution of every rank.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from typing import List, Optional, Sequence
 
@@ -68,6 +70,9 @@ class FusedCollectives:
         self.group, self.device = group, device
         self.rank = dist.get_rank(group) if group is not None else 0
         self.world = dist.get_world_size(group) if group is not None else 1
+        if comm_ctas == 0 and "FT_COMM_CTAS" in os.environ:
+            from ..utils.config import env_flag
+            comm_ctas = int(env_flag("FT_COMM_CTAS"))
         self.comm_ctas = comm_ctas
         self.lib = _lib.load()
         # local words: [0] epoch, then one flag per 32 KiB piece of a gathered operand

@@ -101,8 +101,11 @@ class FunctionCtx:
 
 
 class FrankenTorchSession:
-    def __init__(self, mode: ExecutionMode = ExecutionMode.Strict, device: str = "cpu", seed: int = DEFAULT_SEED,
+    def __init__(self, mode: Optional[ExecutionMode] = None, device: str = "cpu", seed: int = DEFAULT_SEED,
                  default_dtype: Optional[DType] = None, ledger_dispatch: bool = True):
+        if mode is None:   # the FT_MODE switch picks the mode of sessions that do not name one
+            from .utils.config import env_flag
+            mode = env_flag("FT_MODE")
         self.runtime = RuntimeContext(ExecutionMode.parse(mode))
         self.device = torch.device(device)
         self.is_cuda = self.device.type == "cuda"
