@@ -58,7 +58,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--parallelism", default="", choices=["", "dp", "tp", "zero3", "ep"],
                     help="default: the one the named config asks for")
-    ap.add_argument("--dp-impl", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--dp-impl", default=os.environ.get("FT_DP_IMPL", "fused"), choices=["fused", "nccl"],
                     help="multi-GPU gradient path: in-kernel NVLink reduce-scatter+AdamW+all-gather, or NCCL all-reduce")
     return ap.parse_args()
 
@@ -150,6 +150,7 @@ def main():
     from frankentorch_b200.models.gpt import GPT, GPTConfig
     from frankentorch_b200.ops import kernels as K
     from frankentorch_b200.training.engine import OptimConfig, TrainEngine
+    from frankentorch_b200.utils.metrics import percentile_nearest_rank
 
     preset, mb, seq, par = MODELS[args.model]
     par = args.parallelism or par
@@ -207,12 +208,17 @@ def main():
     sampler.start()
     sync_all()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps - 1)]
     ev0.record()
     for i in range(args.steps):
         engine.step_device(read_loss=False)
+        if i + 1 < args.steps:
+            marks[i].record()          # step boundaries for the p50 / p99 figures (no synchronisation)
     ev1.record()
     sync_all()
     dev_ms = ev0.elapsed_time(ev1)
+    edges = [ev0] + marks + [ev1]
+    step_ms = [edges[i].elapsed_time(edges[i + 1]) for i in range(args.steps)]
 
     # ---------------- end-to-end region: public API, H2D inputs + D2H loss every step
     e2e_ms = None
@@ -243,6 +249,8 @@ def main():
         "steps": args.steps,
         "warmup": max(args.warmup, 3),
         "ms_per_step": dev_ms / args.steps,
+        "step_ms_p50": percentile_nearest_rank(step_ms, 50),
+        "step_ms_p99": percentile_nearest_rank(step_ms, 99),
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,

@@ -20,6 +20,7 @@ import torch
 
 from ..autograd.tape import BackwardOptions
 from ..ops import kernels as K
+from ..utils.profiling import install_tape_ranges
 
 
 @dataclass
@@ -37,6 +38,7 @@ class TrainEngine:
                  use_cuda_graph: bool = True, dp=None):
         self.model = model
         self.tape = model.tape
+        install_tape_ranges(self.tape)       # NVTX range per backward rule when FT_NVTX=1
         self.B, self.S = micro_batch, seq_len
         self.opt = optim or OptimConfig()
         self.dp = dp
