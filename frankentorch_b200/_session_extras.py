@@ -1,0 +1,193 @@
+"""Session methods layered on the rule tables: the reference's un-prefixed / ``functional_*``
+spellings, multi-output factorisations, dtype shorthands, complex helpers and the index-valued
+vision / point-cloud utilities.
+
+The reference's session exposes several names for one operation (``cross_entropy_loss`` and
+``functional_cross_entropy``, ``tensor_scaled_dot_product_attention``; see the method list
+reconstructed from crates/ft-conformance/src/lib.rs:4839-5000, crates/ft-nn/src/lib.rs:5178-5184
+and crates/ft-api/tests/grad_fd_audit.rs:315).  Every alias below binds to the same tape
+operator as its ``tensor_*`` spelling, so evidence, rule strings and gradients are identical.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .autograd import functions_extra as FX
+from .core.dtype import DType
+
+# alias -> existing session method
+_ALIASES = {
+    # losses
+    "mse_loss": "tensor_mse_loss", "l1_loss": "tensor_l1_loss", "cross_entropy_loss": "tensor_cross_entropy",
+    "nll_loss": "tensor_nll_loss", "bce_loss": "tensor_bce_loss",
+    "bce_with_logits_loss": "tensor_bce_with_logits_loss", "smooth_l1_loss": "tensor_smooth_l1_loss",
+    "huber_loss": "tensor_huber_loss", "kl_div": "tensor_kl_div",
+    "cosine_embedding_loss": "tensor_cosine_embedding_loss", "focal_loss": "tensor_focal_loss",
+    "triplet_margin_loss": "tensor_triplet_margin_loss", "multi_margin_loss": "tensor_multi_margin_loss",
+    "ctc_loss": "tensor_ctc_loss", "gaussian_nll_loss": "tensor_gaussian_nll_loss",
+    "poisson_nll_loss": "tensor_poisson_nll_loss", "dice_loss": "tensor_dice_loss",
+    "iou_loss": "tensor_iou_loss", "giou_loss": "tensor_giou_loss",
+    "hinge_embedding_loss": "tensor_hinge_embedding_loss", "soft_margin_loss": "tensor_soft_margin_loss",
+    "margin_ranking_loss": "tensor_margin_ranking_loss",
+    # nn functional
+    "functional_linear": "tensor_linear", "functional_layer_norm": "tensor_layer_norm",
+    "functional_rms_norm": "tensor_rms_norm", "functional_group_norm": "tensor_group_norm",
+    "tensor_scaled_dot_product_attention": "tensor_sdpa", "apply_rotary_pos_emb": "tensor_rotary_pos_emb",
+    "tensor_dropout": "functional_dropout",
+    # random, in place
+    "normal_": "tensor_normal_", "uniform_": "tensor_uniform_",
+}
+
+
+def _alias(target: str, name: str):
+    def method(self, *a, **kw):
+        return getattr(self, target)(*a, **kw)
+    method.__name__ = name
+    method.__doc__ = f"Alias of :meth:`{target}`."
+    return method
+
+
+# ------------------------------------------------------------------------------- dtype shorthands
+def tensor_half(self, a):
+    return self.tensor_to_dtype(a, DType.F16)
+
+
+def tensor_float(self, a):
+    return self.tensor_to_dtype(a, DType.F32)
+
+
+def tensor_double(self, a):
+    return self.tensor_to_dtype(a, DType.F64)
+
+
+def tensor_bfloat16(self, a):
+    return self.tensor_to_dtype(a, DType.BF16)
+
+
+# ------------------------------------------------------------------------------- losses / nn
+def functional_cross_entropy(self, logits, target, reduction: str = "mean"):
+    """``cross_entropy(logits, target, reduction)`` (crates/ft-conformance/tests/e2e_training.rs:289)."""
+    return self.tensor_cross_entropy(logits, target, reduction=reduction)
+
+
+def _functional_batch_norm(self, x, running_mean=None, running_var=None, weight=None, bias=None,
+                           training: bool = True, momentum: float = 0.1, eps: float = 1e-5):
+    """Batch norm over ``[N, C, *]``.  Training mode normalises with the batch statistics and
+    updates the running statistics (node ids) in place with the unbiased variance; evaluation
+    mode normalises with the running statistics."""
+    if not training and running_mean is not None:
+        return self.tensor_batch_norm_eval(x, running_mean, running_var, weight, bias, eps=eps)
+    if running_mean is not None:
+        xv = self.tensor(x).detach()
+        dims = [0] + list(range(2, xv.dim()))
+        n = xv.numel() / xv.shape[1]
+        rm, rv = self.tensor(running_mean), self.tensor(running_var)
+        with torch.no_grad():
+            rm.mul_(1 - momentum).add_(xv.mean(dims).to(rm.dtype), alpha=momentum)
+            rv.mul_(1 - momentum).add_(xv.var(dims, unbiased=False).to(rv.dtype) * (n / max(n - 1.0, 1.0)),
+                                       alpha=momentum)
+        self.tensor_tape.bump_version(running_mean)
+        self.tensor_tape.bump_version(running_var)
+    return self.tensor_batch_norm(x, weight, bias, eps=eps)
+
+
+def _bn_rank(rank: int):
+    def method(self, x, running_mean=None, running_var=None, weight=None, bias=None, training=True,
+               momentum=0.1, eps=1e-5):
+        nd = self.tensor(x).dim()
+        ok = (nd in (2, 3)) if rank == 1 else (nd == rank + 2)
+        if not ok:
+            raise ValueError(f"functional_batch_norm{rank}d: unexpected input rank {nd}")
+        return _functional_batch_norm(self, x, running_mean, running_var, weight, bias, training, momentum, eps)
+    method.__name__ = f"functional_batch_norm{rank}d"
+    return method
+
+
+def multi_head_attention_forward(self, query, key, value, num_heads: int, q_w, k_w, v_w, out_w,
+                                 q_b=None, k_b=None, v_b=None, out_b=None, attn_mask=None,
+                                 is_causal: bool = False):
+    """Separate q/k/v/out projections, heads split ``[N,S,E] -> [N,H,S,hd]``, one SDPA call,
+    inverse permute and the output projection (crates/ft-nn/src/lib.rs:5145-5184)."""
+    N, S, E = self.tensor(query).shape
+    T = self.tensor(key).shape[1]
+    hd = E // num_heads
+
+    def proj(x, w, b, L):
+        y = self.tensor_linear(self.tensor_reshape(x, [N * L, E]), w, b)
+        return self.tensor_permute(self.tensor_reshape(y, [N, L, num_heads, hd]), [0, 2, 1, 3])
+    q, k, v = proj(query, q_w, q_b, S), proj(key, k_w, k_b, T), proj(value, v_w, v_b, T)
+    o = self.tensor_sdpa(q, k, v, attn_mask, is_causal=is_causal)
+    o = self.tensor_reshape(self.tensor_contiguous(self.tensor_permute(o, [0, 2, 1, 3])), [N * S, E])
+    return self.tensor_reshape(self.tensor_linear(o, out_w, out_b), [N, S, E])
+
+
+# ------------------------------------------------------------------------------- factorisations
+def tensor_linalg_svd(self, a) -> Tuple[int, int, int]:
+    """Reduced SVD ``(U, S, Vh)``; each factor is its own tape node with its own gradient rule."""
+    return self.tensor_linalg_svd_u(a), self.tensor_linalg_svdvals(a), self.tensor_linalg_svd_vh(a)
+
+
+def tensor_linalg_qr(self, a) -> Tuple[int, int]:
+    return self.tensor_linalg_qr_q(a), self.tensor_linalg_qr_r(a)
+
+
+def tensor_linalg_eigh(self, a) -> Tuple[int, int]:
+    return self.tensor_linalg_eigh_values(a), self.tensor_linalg_eigh_vectors(a)
+
+
+def tensor_linalg_eig(self, a) -> Tuple[int, int]:
+    """Eigenvalues and eigenvectors of a general matrix in the ``[..., 2]`` complex layout."""
+    return self.tensor_linalg_eig_values(a), self.tensor_linalg_eig_vectors(a)
+
+
+def tensor_linalg_slogdet(self, a) -> Tuple[int, int]:
+    return self.tensor_linalg_slogdet_sign(a), self.tensor_linalg_slogdet_logabs(a)
+
+
+def tensor_linalg_lu(self, a) -> Tuple[int, int, int]:
+    return self.tensor_linalg_lu_p(a), self.tensor_linalg_lu_l(a), self.tensor_linalg_lu_u(a)
+
+
+# ------------------------------------------------------------------------------- index-valued utilities
+def _leaf_index(self, t: torch.Tensor) -> int:
+    # index results follow the session convention for index tensors: f64-valued, no gradient
+    return self.tensor_tape.leaf(t.to(torch.float64).to(self.device), False)
+
+
+def nms(self, boxes, scores, iou_threshold: float) -> int:
+    """Indices (f64-valued) of the boxes kept by greedy non-maximum suppression, best first."""
+    return _leaf_index(self, FX.nms_indices(self.tensor(boxes), self.tensor(scores), float(iou_threshold)))
+
+
+def batched_nms(self, boxes, scores, classes, iou_threshold: float) -> int:
+    b, c = self.tensor(boxes), self.tensor(classes)
+    span = (b.max() - b.min()).abs() + 1
+    shifted = b + (c.to(b.dtype) * span)[:, None]
+    return _leaf_index(self, FX.nms_indices(shifted, self.tensor(scores), float(iou_threshold)))
+
+
+def ball_query(self, xyz, centers, radius: float, k: int) -> int:
+    return _leaf_index(self, FX.ball_query_indices(self.tensor(xyz), self.tensor(centers), float(radius), int(k)))
+
+
+def farthest_point_sampling(self, xyz, m: int, start: int = 0) -> int:
+    return _leaf_index(self, FX.farthest_point_sampling_indices(self.tensor(xyz), int(m), int(start)))
+
+
+def roi_pool(self, feat, rois, output_size=(2, 2), spatial_scale: float = 1.0) -> int:
+    return self.tensor_roi_pool(feat, rois, output_size=output_size, spatial_scale=spatial_scale)
+
+
+def install(cls) -> None:
+    for name, target in _ALIASES.items():
+        if hasattr(cls, target) and not hasattr(cls, name):
+            setattr(cls, name, _alias(target, name))
+    for fn in (tensor_half, tensor_float, tensor_double, tensor_bfloat16, functional_cross_entropy,
+               multi_head_attention_forward, tensor_linalg_svd, tensor_linalg_qr, tensor_linalg_eigh,
+               tensor_linalg_eig, tensor_linalg_slogdet, tensor_linalg_lu, nms, batched_nms, ball_query,
+               farthest_point_sampling, roi_pool):
+        setattr(cls, fn.__name__, fn)
+    for rank in (1, 2, 3):
+        setattr(cls, f"functional_batch_norm{rank}d", _bn_rank(rank))

@@ -89,19 +89,26 @@ __device__ __forceinline__ void store_out32(__nv_bfloat16* dst, const uint32_t* 
 template <int HD>
 struct DkvCfg {
   static constexpr int TILE = (HD / 64) * AT_REGION;
-  static constexpr int STAGES = (HD == 64) ? 2 : 1;          // Q / dO ring
-  static constexpr int NBUF = (HD == 64) ? 2 : 1;            // P^T / dS^T buffers
+  // head_dim 64 leaves 128 TMEM columns free: P^T and dS^T (packed bf16, 64 columns each) are
+  // written there by the threads that own their rows, and the dV / dK products read their A
+  // operand from tensor memory, so neither tile crosses shared memory (which a 128-row CTA tile
+  // already saturates with its B operands).  head_dim 128 fills all 512 columns with
+  // accumulators and stages both tiles in shared memory.
+  static constexpr bool TS = (HD == 64);
+  static constexpr int STAGES = (HD == 64) ? 3 : 1;          // Q / dO ring
+  static constexpr int NBUF = 1;                             // P^T / dS^T buffers
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = TILE;
   static constexpr int OFF_Q = 2 * TILE;                     // [STAGES]
   static constexpr int OFF_DO = OFF_Q + STAGES * TILE;       // [STAGES]
   static constexpr int OFF_PT = OFF_DO + STAGES * TILE;      // [NBUF] P^T  [keys x queries]
-  static constexpr int OFF_DST = OFF_PT + NBUF * 2 * AT_REGION;   // [NBUF] dS^T
-  static constexpr int OFF_STAT = OFF_DST + NBUF * 2 * AT_REGION; // [STAGES][2][128] floats
+  static constexpr int OFF_DST = OFF_PT + (TS ? 0 : NBUF * 2 * AT_REGION);   // [NBUF] dS^T
+  static constexpr int OFF_STAT = OFF_DST + (TS ? 0 : NBUF * 2 * AT_REGION); // [STAGES][2][128] floats
   static constexpr int OFF_BAR = OFF_STAT + STAGES * 2 * 128 * 4;
   static constexpr int SMEM = OFF_BAR + 512;
   static constexpr int TMEM_COLS = 512;
   static constexpr int TM_ST = 0, TM_DPT = 128, TM_DV = 256, TM_DK = 256 + HD;
+  static constexpr int TM_PT = 256 + 2 * HD, TM_DST = 256 + 2 * HD + 64;   // TS only
 };
 
 template <int HD>
@@ -113,13 +120,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;    // [2]
-  uint64_t* qdo_empty = bars + 3;   // [2]
-  uint64_t* st_full = bars + 5;     // S^T and dP^T in TMEM
-  uint64_t* st_free = bars + 6;     // both copied to registers (one arrival per warp)
-  uint64_t* pds_ready = bars + 7;   // [2] P^T and dS^T written to smem (one arrival per warp)
-  uint64_t* acc_done = bars + 9;    // [2] dV/dK MMAs that read the buffer finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* qdo_full = bars + 1;    // [4]
+  uint64_t* qdo_empty = bars + 5;   // [4]
+  uint64_t* st_full = bars + 9;     // S^T and dP^T in TMEM
+  uint64_t* st_free = bars + 10;    // both copied to registers (one arrival per warp)
+  uint64_t* pds_ready = bars + 11;  // [2] P^T and dS^T handed to the tensor core (one arrival per warp)
+  uint64_t* acc_done = bars + 13;   // [2] dV/dK MMAs that read the buffer finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx ctx{p.status, abort_f};
@@ -130,9 +137,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&pds_ready[i], BW_MATH);
       mbar_init(&acc_done[i], 1);
     }
@@ -150,7 +159,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int kb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // linear grid, key blocks with the most query blocks (the early ones under a causal mask) first
+  const int n_hb = p.H * p.B;
+  const int kb = (int)blockIdx.x / n_hb;
+  const int hb = (int)blockIdx.x % n_hb;
+  const int h = hb % p.H, b = hb / p.H;
   const int k0 = kb * AT_T;
   const int nq_all = (p.S + AT_T - 1) / AT_T;
   const int qb_first = p.causal ? kb : 0;
@@ -217,10 +230,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!mbar_wait(&pds_ready[buf], (it / C::NBUF) & 1, ctx, FT_ERR_WAIT_SOFTMAX)) break;
       tc_fence_after();
       if (lane == 0) {
-        mma_p_times_rows(tmem_base + C::TM_DV, pt_addr + buf * 2 * AT_REGION, do_addr + st * C::TILE,
-                         idesc_acc, it > 0);
-        mma_p_times_rows(tmem_base + C::TM_DK, dst_addr + buf * 2 * AT_REGION, q_addr + st * C::TILE,
-                         idesc_acc, it > 0);
+        if constexpr (C::TS) {
+          mma_ptmem_times_rows(tmem_base + C::TM_DV, tmem_base + C::TM_PT, do_addr + st * C::TILE,
+                               idesc_acc, it > 0);
+          mma_ptmem_times_rows(tmem_base + C::TM_DK, tmem_base + C::TM_DST, q_addr + st * C::TILE,
+                               idesc_acc, it > 0);
+        } else {
+          mma_p_times_rows(tmem_base + C::TM_DV, pt_addr + buf * 2 * AT_REGION, do_addr + st * C::TILE,
+                           idesc_acc, it > 0);
+          mma_p_times_rows(tmem_base + C::TM_DK, dst_addr + buf * 2 * AT_REGION, q_addr + st * C::TILE,
+                           idesc_acc, it > 0);
+        }
         umma_commit(&acc_done[buf]);
         umma_commit(&qdo_empty[st]);
       }
@@ -276,9 +296,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // the buffer's previous reader (dV/dK of iteration it - NBUF) must have finished
       if (it >= C::NBUF &&
           !mbar_wait(&acc_done[buf], ((it / C::NBUF) - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-      store_row32_packed(smem + C::OFF_PT + buf * 2 * AT_REGION, row, c0, pw);
-      store_row32_packed(smem + C::OFF_DST + buf * 2 * AT_REGION, row, c0, dw);
-      fence_proxy_async_smem();
+      if constexpr (C::TS) {
+        // this thread's 32 queries of its key row: 16 packed columns of each operand tile
+        tc_fence_after();
+        tmem_st16(tmem_base + C::TM_PT + 16 * g + lane_sel, pw);
+        tmem_st16(tmem_base + C::TM_DST + 16 * g + lane_sel, dw);
+        tmem_st_wait();
+        tc_fence_before();
+      } else {
+        store_row32_packed(smem + C::OFF_PT + buf * 2 * AT_REGION, row, c0, pw);
+        store_row32_packed(smem + C::OFF_DST + buf * 2 * AT_REGION, row, c0, dw);
+        fence_proxy_async_smem();
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_ready[buf]);      // one arrival per warp
     }
@@ -319,17 +348,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 template <int HD>
 struct DqCfg {
   static constexpr int TILE = (HD / 64) * AT_REGION;
-  static constexpr int STAGES = (HD == 64) ? 3 : 2;      // K / V ring
+  static constexpr bool TS = (HD == 64);                 // dS in tensor memory (see DkvCfg)
+  static constexpr int STAGES = (HD == 64) ? 4 : 2;      // K / V ring
   static constexpr int NBUF = (HD == 64) ? 2 : 1;        // dS buffers
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_DO = TILE;
   static constexpr int OFF_K = 2 * TILE;                 // [STAGES]
   static constexpr int OFF_V = OFF_K + STAGES * TILE;    // [STAGES]
   static constexpr int OFF_DS = OFF_V + STAGES * TILE;   // [NBUF] dS [queries x keys]
-  static constexpr int OFF_BAR = OFF_DS + NBUF * 2 * AT_REGION;
+  static constexpr int OFF_BAR = OFF_DS + (TS ? 0 : NBUF * 2 * AT_REGION);
   static constexpr int SMEM = OFF_BAR + 512;
   static constexpr int TMEM_COLS = 512;
   static constexpr int TM_S = 0, TM_DP = 128, TM_DQ = 256;
+  static constexpr int TM_DS = 384;                      // TS: dS buffer i at TM_DS + 64 i
 };
 
 template <int HD>
@@ -341,13 +372,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* qdo_full = bars;
-  uint64_t* kv_full = bars + 1;    // [3]
-  uint64_t* kv_empty = bars + 4;   // [3]
-  uint64_t* s_full = bars + 7;     // S and dP in TMEM
-  uint64_t* s_free = bars + 8;     // both copied to registers (one arrival per warp)
-  uint64_t* ds_ready = bars + 9;   // [2] dS written to smem (one arrival per warp)
-  uint64_t* acc_done = bars + 11;  // [2] dQ MMA that read the buffer finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* kv_full = bars + 1;    // [4]
+  uint64_t* kv_empty = bars + 5;   // [4]
+  uint64_t* s_full = bars + 9;     // S and dP in TMEM
+  uint64_t* s_free = bars + 10;    // both copied to registers (one arrival per warp)
+  uint64_t* ds_ready = bars + 11;  // [2] dS handed to the tensor core (one arrival per warp)
+  uint64_t* acc_done = bars + 13;  // [2] dQ MMA that read the buffer finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx ctx{p.status, abort_f};
@@ -358,7 +389,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int i = 0; i < 3; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
@@ -380,8 +411,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // linear grid, query blocks with the most key blocks (the late ones under a causal mask) first
+  const int n_hb = p.H * p.B;
+  const int qb = (int)gridDim.x / n_hb - 1 - (int)blockIdx.x / n_hb;
+  const int hb = (int)blockIdx.x % n_hb;
+  const int h = hb % p.H, b = hb / p.H;
   const int q0 = qb * AT_T;
   const int nkv_all = (p.S + AT_T - 1) / AT_T;
   const int nkv = p.causal ? min(qb + 1, nkv_all) : nkv_all;
@@ -435,8 +469,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!mbar_wait(&ds_ready[buf], (j / C::NBUF) & 1, ctx, FT_ERR_WAIT_SOFTMAX)) break;
       tc_fence_after();
       if (lane == 0) {
-        mma_p_times_rows(tmem_base + C::TM_DQ, ds_addr + buf * 2 * AT_REGION, k_addr + st * C::TILE,
-                         idesc_acc, j > 0);
+        if constexpr (C::TS)
+          mma_ptmem_times_rows(tmem_base + C::TM_DQ, tmem_base + C::TM_DS + 64 * buf, k_addr + st * C::TILE,
+                               idesc_acc, j > 0);
+        else
+          mma_p_times_rows(tmem_base + C::TM_DQ, ds_addr + buf * 2 * AT_REGION, k_addr + st * C::TILE,
+                           idesc_acc, j > 0);
         umma_commit(&acc_done[buf]);
         umma_commit(&kv_empty[st]);
       }
@@ -480,8 +518,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       if (j >= C::NBUF &&
           !mbar_wait(&acc_done[buf], ((j / C::NBUF) - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-      store_row32_packed(smem + C::OFF_DS + buf * 2 * AT_REGION, row, c0, dw);
-      fence_proxy_async_smem();
+      if constexpr (C::TS) {
+        tc_fence_after();
+        tmem_st16(tmem_base + C::TM_DS + 64 * buf + 16 * g + lane_sel, dw);
+        tmem_st_wait();
+        tc_fence_before();
+      } else {
+        store_row32_packed(smem + C::OFF_DS + buf * 2 * AT_REGION, row, c0, dw);
+        fence_proxy_async_smem();
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_ready[buf]);      // one arrival per warp
     }
@@ -531,7 +576,7 @@ static int attn_bwd_launch(const FtkAttnDesc* a, cudaStream_t s) {
   attn_delta_kernel<LPR><<<(unsigned)((nrows + ROWS_PER_CTA - 1) / ROWS_PER_CTA), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(a->o), reinterpret_cast<const __nv_bfloat16*>(a->d_o),
       a->delta, a->B, a->H, a->S, a->o_bs, a->o_ss, a->o_hs);
-  dim3 grid((a->S + AT_T - 1) / AT_T, a->H, a->B);
+  dim3 grid((unsigned)(((a->S + AT_T - 1) / AT_T) * a->H * a->B));
   attn_bwd_dkv_kernel<HD><<<grid, BW_THREADS, DkvCfg<HD>::SMEM, s>>>(tq, tk, tv, tdo, p);
   attn_bwd_dq_kernel<HD><<<grid, BW_THREADS, DqCfg<HD>::SMEM, s>>>(tq, tk, tv, tdo, p);
   return (int)cudaGetLastError();

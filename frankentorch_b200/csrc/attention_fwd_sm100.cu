@@ -16,8 +16,10 @@
 //              registers to the softmax groups (setmaxnreg).
 // The output accumulates in TMEM across all key blocks.  The running maximum is lazy: a row
 // keeps its reference maximum until a block exceeds it by more than 2^8, and only then is the
-// TMEM accumulator rescaled (tcgen05.ld / mul / tcgen05.st, voted per warp).  Probabilities
-// reach the tensor core through a 128B-swizzled bf16 tile in shared memory.
+// TMEM accumulator rescaled (tcgen05.ld / mul / tcgen05.st, voted per warp).  With head_dim 64
+// the probabilities stay in tensor memory (tcgen05.st of packed bf16 pairs by the row's thread)
+// and P V is issued with its A operand in TMEM; with head_dim 128 all 512 columns are taken by
+// S and O, and P reaches the tensor core through a 128B-swizzled bf16 tile in shared memory.
 #include "attn_common.cuh"
 
 namespace ftk {
@@ -28,16 +30,28 @@ constexpr float F2_LAZY = 8.0f;       // log2 headroom before the accumulator is
 template <int HD>
 struct Fwd2Cfg {
   static constexpr int TILE = (HD / 64) * AT_REGION;        // one [128 x HD] bf16 tile
-  static constexpr int NSLOT = (HD == 64) ? 6 : 3;          // K/V ring
+  // head_dim 64 leaves 128 TMEM columns free: the probabilities go there (packed bf16, 64 columns
+  // per tile) and P V reads its A operand from tensor memory.  A 128-row CTA tile keeps the
+  // tensor core fed from shared memory at 128 B/clk, which is all the SM has: taking the P tile
+  // out of shared memory (64 KB written + 64 KB read per key block) roughly halves that traffic.
+  static constexpr bool TS = (HD == 64);
+  static constexpr int NSLOT = (HD == 64) ? 8 : 3;          // K/V ring
   static constexpr int OFF_Q = 0;                           // 2 tiles
   static constexpr int OFF_KV = 2 * TILE;                   // [NSLOT]
-  static constexpr int OFF_P = OFF_KV + NSLOT * TILE;       // 2 tiles of [128 x 128] bf16
-  static constexpr int OFF_BAR = OFF_P + 2 * 2 * AT_REGION;
+  static constexpr int OFF_P = OFF_KV + NSLOT * TILE;       // 2 tiles of [128 x 128] bf16 (not TS)
+  static constexpr int OFF_BAR = OFF_P + (TS ? 0 : 2 * 2 * AT_REGION);
   static constexpr int SMEM = OFF_BAR + 1024;
   static constexpr int TMEM_COLS = 512;
   static constexpr int TM_S = 0;                            // S tile t at TM_S + 128 t
   static constexpr int TM_O = 256;                          // O tile t at TM_O + HD t
+  static constexpr int TM_P = 256 + 2 * HD;                 // TS: P tile t at TM_P + 64 t
 };
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 
 #ifdef FT_ATTN_TRACE
 // Optional timeline of one CTA (development builds only): [role][iteration][point] clock64 values.
@@ -78,8 +92,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx ctx{p.status, abort_f};
 #ifdef FT_ATTN_TRACE
-  const bool trace_cta = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const bool trace_cta = blockIdx.x == 0;
+  const int cta_lin = blockIdx.x;
   if (threadIdx.x == 0 && cta_lin < 4096) {
     unsigned long long t0;
     unsigned smid;
@@ -118,9 +132,14 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // heavy (late) query blocks first
-  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Linear grid, heavy (late) query blocks first over the whole launch: every CTA of the block
+  // with the most key blocks is scheduled before any lighter one (longest-first keeps the tail
+  // of the launch short when the work per CTA varies 4:1 under a causal mask).
+  const int n_hb = p.H * p.B;
+  const int n_qb = (int)gridDim.x / n_hb;
+  const int qb = n_qb - 1 - (int)blockIdx.x / n_hb;
+  const int hb = (int)blockIdx.x % n_hb;
+  const int h = hb % p.H, b = hb / p.H;
   const int q0 = qb * 2 * AT_T;
   const int nkv_all = (p.S + AT_T - 1) / AT_T;
   int nb[2];                                  // key blocks each tile needs
@@ -198,8 +217,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           FT_TRACE(2, j, 3 + t);
           tc_fence_after();
           if (lane == 0) {
-            mma_p_times_rows(tmem_base + C::TM_O + HD * t, p_addr + t * 2 * AT_REGION,
-                             kv_addr + slot * C::TILE, idesc_pv, j > 0);
+            if constexpr (C::TS)
+              mma_ptmem_times_rows(tmem_base + C::TM_O + HD * t, tmem_base + C::TM_P + 64 * t,
+                                   kv_addr + slot * C::TILE, idesc_pv, j > 0);
+            else
+              mma_p_times_rows(tmem_base + C::TM_O + HD * t, p_addr + t * 2 * AT_REGION,
+                               kv_addr + slot * C::TILE, idesc_pv, j > 0);
             umma_commit(&pv_done[t]);
           }
           __syncwarp();
@@ -219,7 +242,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t lane_sel = (uint32_t)(qd * 32) << 16;
     const uint32_t s_tmem = tmem_base + C::TM_S + 128 * t + lane_sel;
     const uint32_t o_tmem = tmem_base + C::TM_O + HD * t + lane_sel;
-    uint8_t* sP = smem + C::OFF_P + t * 2 * AT_REGION + row * 128;
+    uint8_t* sP = smem + C::OFF_P + t * 2 * AT_REGION + row * 128;   // not TS
+    const uint32_t p_tmem = tmem_base + C::TM_P + 64 * t + lane_sel;   // TS
     const int n_my = nb[t];
     float m2 = -INFINITY;                    // reference maximum, already times sl2
     float l = 0.f;
@@ -250,11 +274,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 128; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(r[i]));
-        mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+      for (int i = 0; i < 128; i += 8) {
+        mx0 = max3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        mx2 = max3(mx2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+        mx3 = max3(mx3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
       }
       const float bm2 = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.sl2;   // sl2 > 0
       FT_TRACE(t, j, 3);
@@ -267,22 +291,24 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       const float moff = (m2 == -INFINITY) ? 0.f : m2;
       float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+      // exponentials of elements [i0, i0 + 64): packed probabilities reuse the low registers
+      auto exp_half = [&](int i0) {
 #pragma unroll
-      for (int i = 0; i < 128; i += 4) {
-        const float e0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.sl2, -moff));
-        const float e1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.sl2, -moff));
-        const float e2 = fast_exp2(fmaf(__uint_as_float(r[i + 2]), p.sl2, -moff));
-        const float e3 = fast_exp2(fmaf(__uint_as_float(r[i + 3]), p.sl2, -moff));
-        rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
-        r[i >> 1] = pack_bf16(e0, e1);          // packed probabilities reuse the low registers
-        r[(i >> 1) + 1] = pack_bf16(e2, e3);
-      }
-      l = l * alpha + (rs0 + rs1) + (rs2 + rs3);
-      FT_TRACE(t, j, 4);
-      if (j > 0) {
-        // PV of the previous block must be finished before P is overwritten and before the
-        // accumulator may be rescaled
-        if (!mbar_wait(&pv_done[t], (j - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        for (int i = i0; i < i0 + 64; i += 4) {
+          const float e0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.sl2, -moff));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.sl2, -moff));
+          const float e2 = fast_exp2(fmaf(__uint_as_float(r[i + 2]), p.sl2, -moff));
+          const float e3 = fast_exp2(fmaf(__uint_as_float(r[i + 3]), p.sl2, -moff));
+          rs0 += e0; rs1 += e1; rs2 += e2; rs3 += e3;
+          r[i >> 1] = pack_bf16(e0, e1);
+          r[(i >> 1) + 1] = pack_bf16(e2, e3);
+        }
+      };
+      // PV of the previous block must be finished before P is overwritten and before the
+      // accumulator may be rescaled
+      auto settle_previous = [&]() -> bool {
+        if (j == 0) return true;
+        if (!mbar_wait(&pv_done[t], (j - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) return false;
         if (__any_sync(0xffffffffu, move)) {
           tc_fence_after();
 #pragma unroll
@@ -297,14 +323,35 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
           tc_fence_before();
         }
-      }
-      FT_TRACE(t, j, 5);
+        return true;
+      };
+      if constexpr (C::TS) {
+        // probabilities go to tensor memory, each half as soon as it is computed
+        if (!settle_previous()) { ok = false; break; }
+        FT_TRACE(t, j, 4);
+        tc_fence_after();
+        exp_half(0);
+        tmem_st32(p_tmem, r);
+        exp_half(64);
+        tmem_st32(p_tmem + 32, r + 32);
+        l = l * alpha + (rs0 + rs1) + (rs2 + rs3);
+        FT_TRACE(t, j, 5);
+        tmem_st_wait();
+        tc_fence_before();
+      } else {
+        exp_half(0);
+        exp_half(64);
+        l = l * alpha + (rs0 + rs1) + (rs2 + rs3);
+        FT_TRACE(t, j, 4);
+        if (!settle_previous()) { ok = false; break; }
+        FT_TRACE(t, j, 5);
 #pragma unroll
-      for (int c16 = 0; c16 < 16; ++c16) {     // 16 chunks of 8 bf16 (16 bytes)
-        const uint4 u = make_uint4(r[4 * c16], r[4 * c16 + 1], r[4 * c16 + 2], r[4 * c16 + 3]);
-        *reinterpret_cast<uint4*>(sP + (c16 >> 3) * AT_REGION + (((c16 & 7) ^ (row & 7)) << 4)) = u;
+        for (int c16 = 0; c16 < 16; ++c16) {     // 16 chunks of 8 bf16 (16 bytes)
+          const uint4 u = make_uint4(r[4 * c16], r[4 * c16 + 1], r[4 * c16 + 2], r[4 * c16 + 3]);
+          *reinterpret_cast<uint4*>(sP + (c16 >> 3) * AT_REGION + (((c16 & 7) ^ (row & 7)) << 4)) = u;
+        }
+        fence_proxy_async_smem();
       }
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t]);
       FT_TRACE(t, j, 6);
@@ -367,7 +414,7 @@ static int attn_fwd2_launch(const FtkAttnDesc* a, cudaStream_t s) {
     if ((rc = set_smem(attn_fwd2_kernel<HD>, Fwd2Cfg<HD>::SMEM))) return rc;
     attr = true;
   }
-  dim3 grid((a->S + 2 * AT_T - 1) / (2 * AT_T), a->H, a->B);
+  dim3 grid((unsigned)(((a->S + 2 * AT_T - 1) / (2 * AT_T)) * a->H * a->B));
   attn_fwd2_kernel<HD><<<grid, F2_THREADS, Fwd2Cfg<HD>::SMEM, s>>>(tq, tk, tv, p);
   return (int)cudaGetLastError();
 }

@@ -58,6 +58,16 @@ __device__ __forceinline__ void mma_p_times_rows(uint32_t d_tmem, uint32_t p_bas
               (accumulate || kk != 0) ? 1u : 0u);
   }
 }
+// Same product with A = probabilities held in tensor memory: 128 lanes (rows) x 64 columns of
+// packed bf16 pairs (K = 128), written by the row-owning threads with tcgen05.st.
+__device__ __forceinline__ void mma_ptmem_times_rows(uint32_t d_tmem, uint32_t p_tmem, uint32_t b_base,
+                                                     uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < AT_T / 16; ++kk) {
+    umma_bf16_ts(d_tmem, p_tmem + kk * 8, make_smem_desc(b_base + kk * 2048, AT_REGION, 1024), idesc,
+                 (accumulate || kk != 0) ? 1u : 0u);
+  }
+}
 // Write 32 fp32 values of one tile row as bf16 into the swizzled K-major tile.
 __device__ __forceinline__ void store_row32_swizzled(uint8_t* tile, int row, int col0,
                                                      const float* v) {

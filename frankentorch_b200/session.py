@@ -30,6 +30,7 @@ import torch
 from .autograd import functions as _f1  # noqa: F401  (populate the rule table)
 from .autograd import functions_nn as _f3  # noqa: F401
 from .autograd import functions_shape as _f2  # noqa: F401
+from .autograd import functions_extra as _f4  # noqa: F401
 from .autograd.functions import OPS, OpDef
 from .autograd.scalar_tape import BackwardReport, Tape
 from .autograd.tape import (BackwardOptions, BorrowedInputVersionMismatch, TensorBackwardReport, TensorHookHandle,
@@ -294,3 +295,7 @@ from . import _session_factories as _fac_install  # noqa: E402
 
 _ops_install.install(FrankenTorchSession)
 _fac_install.install(FrankenTorchSession)
+
+from . import _session_extras as _extra_install  # noqa: E402
+
+_extra_install.install(FrankenTorchSession)
