@@ -24,10 +24,11 @@
 
 namespace ftk {
 
-constexpr int BW_THREADS = 576;
+constexpr int BW_THREADS = 608;
 constexpr int BW_MATH = 16;         // one arrival per math warp on the math barriers
 constexpr int BW_WARP_TMA = 16;
-constexpr int BW_WARP_MMA = 17;
+constexpr int BW_WARP_MMA = 17;      // issues the score products, owns TMEM
+constexpr int BW_WARP_MMA2 = 18;     // issues the accumulating products
 
 // =============================================================================== delta
 // delta[b,h,s] = sum_e dO * O.  LPR = hd / 8 lanes share one (b, s, h) row (16 bytes each), so
@@ -86,6 +87,19 @@ __device__ __forceinline__ void store_out32(__nv_bfloat16* dst, const uint32_t* 
 }
 
 // =============================================================================== backward: dK, dV
+#ifdef FT_ATTN_TRACE
+// Optional timeline of CTA 0 of each backward kernel (development builds only):
+// [kernel][role][iteration][point] clock64 values.
+__device__ long long g_attn_bwd_trace[2 * 3 * 16 * 8];
+#define FT_BTRACE(kern, role, it, pt)                                                              \
+  do {                                                                                             \
+    if (blockIdx.x == 0 && lane == 0 && (it) < 16)                                                 \
+      g_attn_bwd_trace[(((kern) * 3 + (role)) * 16 + (it)) * 8 + (pt)] = clock64();                \
+  } while (0)
+#else
+#define FT_BTRACE(kern, role, it, pt) do { } while (0)
+#endif
+
 template <int HD>
 struct DkvCfg {
   static constexpr int TILE = (HD / 64) * AT_REGION;
@@ -202,16 +216,20 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       __syncwarp();
     }
   } else if (warp == BW_WARP_MMA) {
+    // ---------------------------------------------------------- issuer 1: S^T = K Q^T, dP^T = V dO^T
+    // (two issuing warps: the issuing thread runs in step with the tensor pipe, so the waits and
+    // descriptor steps of one product would otherwise idle the pipe for the other)
     const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-    const uint32_t idesc_acc = make_idesc_bf16(128, HD, 0, 1);
     const uint32_t k_addr = smem_u32(smem + C::OFF_K), v_addr = smem_u32(smem + C::OFF_V);
     const uint32_t q_addr = smem_u32(smem + C::OFF_Q), do_addr = smem_u32(smem + C::OFF_DO);
-    const uint32_t pt_addr = smem_u32(smem + C::OFF_PT), dst_addr = smem_u32(smem + C::OFF_DST);
-    // S^T and dP^T of iteration i: needs Q_i / dO_i and the score tiles drained of i - 1
-    auto issue_scores = [&](int i) -> bool {
+    bool ok = mbar_wait(kv_full, 0, ctx, FT_ERR_WAIT_FULL);
+    for (int i = 0; ok && i < nit; ++i) {
       const int st = i % C::STAGES;
-      if (!mbar_wait(&qdo_full[st], (i / C::STAGES) & 1, ctx, FT_ERR_WAIT_FULL)) return false;
-      if (i > 0 && !mbar_wait(st_free, (i - 1) & 1, ctx, FT_ERR_WAIT_TMEM_EMPTY)) return false;
+      FT_BTRACE(0, 2, i, 0);
+      // needs Q_i / dO_i and the score tiles of iteration i - 1 copied to registers
+      if (!mbar_wait(&qdo_full[st], (i / C::STAGES) & 1, ctx, FT_ERR_WAIT_FULL)) break;
+      if (i > 0 && !mbar_wait(st_free, (i - 1) & 1, ctx, FT_ERR_WAIT_TMEM_EMPTY)) break;
+      FT_BTRACE(0, 2, i, 1);
       tc_fence_after();
       if (lane == 0) {
         mma_kmajor<HD>(tmem_base + C::TM_ST, k_addr, q_addr + st * C::TILE, idesc_s);
@@ -219,15 +237,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         umma_commit(st_full);
       }
       __syncwarp();
-      return true;
-    };
-    bool ok = mbar_wait(kv_full, 0, ctx, FT_ERR_WAIT_FULL);
-    if (ok && nit > 0) ok = issue_scores(0);
-    for (int it = 0; ok && it < nit; ++it) {
+      FT_BTRACE(0, 2, i, 2);
+    }
+  } else if (warp == BW_WARP_MMA2) {
+    // ---------------------------------------------------------- issuer 2: dV += P^T dO, dK += dS^T Q
+    const uint32_t idesc_acc = make_idesc_bf16(128, HD, 0, 1);
+    const uint32_t q_addr = smem_u32(smem + C::OFF_Q), do_addr = smem_u32(smem + C::OFF_DO);
+    const uint32_t pt_addr = smem_u32(smem + C::OFF_PT), dst_addr = smem_u32(smem + C::OFF_DST);
+    for (int it = 0; it < nit; ++it) {
       const int st = it % C::STAGES, buf = it % C::NBUF;
-      if (C::STAGES > 1 && it + 1 < nit) ok = issue_scores(it + 1);
-      if (!ok) break;
+      if (!mbar_wait(&qdo_full[st], (it / C::STAGES) & 1, ctx, FT_ERR_WAIT_FULL)) break;
+      FT_BTRACE(0, 2, it, 3);
       if (!mbar_wait(&pds_ready[buf], (it / C::NBUF) & 1, ctx, FT_ERR_WAIT_SOFTMAX)) break;
+      FT_BTRACE(0, 2, it, 4);
       tc_fence_after();
       if (lane == 0) {
         if constexpr (C::TS) {
@@ -242,12 +264,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                            idesc_acc, it > 0);
         }
         umma_commit(&acc_done[buf]);
-        umma_commit(&qdo_empty[st]);
+        umma_commit(&qdo_empty[st]);     // S^T / dP^T of this stage finished before the math ran
       }
       __syncwarp();
-      if (C::STAGES == 1 && it + 1 < nit) ok = issue_scores(it + 1);
+      FT_BTRACE(0, 2, it, 5);
     }
-  } else {
+  } else if (warp < BW_MATH) {
     const int g = warp >> 2;               // column group: queries [32 g, 32 g + 32) of the block
     const int qd = warp & 3;
     const int row = qd * 32 + lane;        // key row of this thread
@@ -259,13 +281,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int st = it % C::STAGES, buf = it % C::NBUF;
       const int q0 = (qb_first + it) * AT_T;
       // statistics were written by the producer before its arrive on qdo_full
+      FT_BTRACE(0, warp == 0 ? 0 : 1, it, 0);
       if (!mbar_wait(&qdo_full[st], (it / C::STAGES) & 1, ctx, FT_ERR_WAIT_FULL)) { ok = false; break; }
       if (!mbar_wait(st_full, it & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      FT_BTRACE(0, warp == 0 ? 0 : 1, it, 1);
       tc_fence_after();
       uint32_t rs[32], rd[32];
       tmem_ld32(tmem_base + C::TM_ST + c0 + lane_sel, rs);
       tmem_ld32(tmem_base + C::TM_DPT + c0 + lane_sel, rd);
       tmem_ld_wait();
+      FT_BTRACE(0, warp == 0 ? 0 : 1, it, 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(st_free);      // one arrival per warp
@@ -273,6 +298,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const float4* dl4 = reinterpret_cast<const float4*>(stat + st * 256 + 128 + c0);
       const bool need_mask = (q0 + AT_T > p.S) || (k0 + AT_T > p.S) || (p.causal && q0 < k0 + AT_T - 1);
       uint32_t pw[16], dw[16];
+      // masked scores become -inf in a pass of their own (diagonal and ragged blocks only), so
+      // the main loop carries no per-element predicates
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int gq = q0 + c0 + i;
+          if (gq >= p.S || gk >= p.S || (p.causal && gk > gq)) rs[i] = __float_as_uint(-INFINITY);
+        }
+      }
 #pragma unroll
       for (int i4 = 0; i4 < 8; ++i4) {
         const float4 nl = sl4[i4], dl = dl4[i4];
@@ -282,10 +316,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int u = 0; u < 4; ++u) {
           const int i = 4 * i4 + u;
           e[u] = fast_exp2(fmaf(__uint_as_float(rs[i]), p.sl2, nls[u]));
-          if (need_mask) {
-            const int gq = q0 + c0 + i;
-            if (gq >= p.S || gk >= p.S || (p.causal && gk > gq)) e[u] = 0.f;
-          }
           d[u] = e[u] * (__uint_as_float(rd[i]) - dls[u]);
         }
         pw[2 * i4] = pack_bf16(e[0], e[1]);
@@ -293,9 +323,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         dw[2 * i4] = pack_bf16(d[0], d[1]);
         dw[2 * i4 + 1] = pack_bf16(d[2], d[3]);
       }
+      FT_BTRACE(0, warp == 0 ? 0 : 1, it, 3);
       // the buffer's previous reader (dV/dK of iteration it - NBUF) must have finished
       if (it >= C::NBUF &&
           !mbar_wait(&acc_done[buf], ((it / C::NBUF) - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      FT_BTRACE(0, warp == 0 ? 0 : 1, it, 4);
       if constexpr (C::TS) {
         // this thread's 32 queries of its key row: 16 packed columns of each operand tile
         tc_fence_after();
@@ -310,6 +342,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&pds_ready[buf]);      // one arrival per warp
+      FT_BTRACE(0, warp == 0 ? 0 : 1, it, 5);
     }
     if (ok && nit > 0)
       ok = mbar_wait(&acc_done[(nit - 1) % C::NBUF], ((nit - 1) / C::NBUF) & 1, ctx, FT_ERR_WAIT_TMEM_FULL);
@@ -442,15 +475,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       __syncwarp();
     }
   } else if (warp == BW_WARP_MMA) {
+    // ---------------------------------------------------------- issuer 1: S = Q K^T, dP = dO V^T
     const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-    const uint32_t idesc_acc = make_idesc_bf16(128, HD, 0, 1);
     const uint32_t q_addr = smem_u32(smem + C::OFF_Q), do_addr = smem_u32(smem + C::OFF_DO);
     const uint32_t k_addr = smem_u32(smem + C::OFF_K), v_addr = smem_u32(smem + C::OFF_V);
-    const uint32_t ds_addr = smem_u32(smem + C::OFF_DS);
-    auto issue_scores = [&](int jj) -> bool {
+    bool ok = mbar_wait(qdo_full, 0, ctx, FT_ERR_WAIT_FULL);
+    for (int jj = 0; ok && jj < nkv; ++jj) {
       const int st = jj % C::STAGES;
-      if (!mbar_wait(&kv_full[st], (jj / C::STAGES) & 1, ctx, FT_ERR_WAIT_FULL)) return false;
-      if (jj > 0 && !mbar_wait(s_free, (jj - 1) & 1, ctx, FT_ERR_WAIT_TMEM_EMPTY)) return false;
+      FT_BTRACE(1, 2, jj, 0);
+      if (!mbar_wait(&kv_full[st], (jj / C::STAGES) & 1, ctx, FT_ERR_WAIT_FULL)) break;
+      if (jj > 0 && !mbar_wait(s_free, (jj - 1) & 1, ctx, FT_ERR_WAIT_TMEM_EMPTY)) break;
+      FT_BTRACE(1, 2, jj, 1);
       tc_fence_after();
       if (lane == 0) {
         mma_kmajor<HD>(tmem_base + C::TM_S, q_addr, k_addr + st * C::TILE, idesc_s);
@@ -458,15 +493,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         umma_commit(s_full);
       }
       __syncwarp();
-      return true;
-    };
-    bool ok = mbar_wait(qdo_full, 0, ctx, FT_ERR_WAIT_FULL);
-    if (ok && nkv > 0) ok = issue_scores(0);
-    for (int j = 0; ok && j < nkv; ++j) {
+      FT_BTRACE(1, 2, jj, 2);
+    }
+  } else if (warp == BW_WARP_MMA2) {
+    // ---------------------------------------------------------- issuer 2: dQ += dS K
+    const uint32_t idesc_acc = make_idesc_bf16(128, HD, 0, 1);
+    const uint32_t k_addr = smem_u32(smem + C::OFF_K);
+    const uint32_t ds_addr = smem_u32(smem + C::OFF_DS);
+    for (int j = 0; j < nkv; ++j) {
       const int st = j % C::STAGES, buf = j % C::NBUF;
-      if (j + 1 < nkv) ok = issue_scores(j + 1);
-      if (!ok) break;
+      if (!mbar_wait(&kv_full[st], (j / C::STAGES) & 1, ctx, FT_ERR_WAIT_FULL)) break;
+      FT_BTRACE(1, 2, j, 3);
       if (!mbar_wait(&ds_ready[buf], (j / C::NBUF) & 1, ctx, FT_ERR_WAIT_SOFTMAX)) break;
+      FT_BTRACE(1, 2, j, 4);
       tc_fence_after();
       if (lane == 0) {
         if constexpr (C::TS)
@@ -476,11 +515,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           mma_p_times_rows(tmem_base + C::TM_DQ, ds_addr + buf * 2 * AT_REGION, k_addr + st * C::TILE,
                            idesc_acc, j > 0);
         umma_commit(&acc_done[buf]);
-        umma_commit(&kv_empty[st]);
+        umma_commit(&kv_empty[st]);      // S / dP of this stage finished before the math ran
       }
       __syncwarp();
+      FT_BTRACE(1, 2, j, 5);
     }
-  } else {
+  } else if (warp < BW_MATH) {
     const int g = warp >> 2;               // column group: keys [32 g, 32 g + 32) of the block
     const int qd = warp & 3;
     const int row = qd * 32 + lane;
@@ -493,31 +533,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     bool ok = true;
     for (int j = 0; j < nkv; ++j) {
       const int buf = j % C::NBUF;
+      FT_BTRACE(1, warp == 0 ? 0 : 1, j, 0);
       if (!mbar_wait(s_full, j & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      FT_BTRACE(1, warp == 0 ? 0 : 1, j, 1);
       tc_fence_after();
       uint32_t rs[32], rd[32];
       tmem_ld32(tmem_base + C::TM_S + c0 + lane_sel, rs);
       tmem_ld32(tmem_base + C::TM_DP + c0 + lane_sel, rd);
       tmem_ld_wait();
+      FT_BTRACE(1, warp == 0 ? 0 : 1, j, 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);      // one arrival per warp
       const int k0 = j * AT_T;
       const bool need_mask = (k0 + AT_T > p.S) || (q0 + AT_T > p.S) || (p.causal && k0 + AT_T - 1 > q0);
       uint32_t dw[16];
+      if (need_mask) {      // masked scores become -inf in a pass of their own
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kc = k0 + c0 + i;
+          if (kc >= p.S || grow >= p.S || (p.causal && kc > grow)) rs[i] = __float_as_uint(-INFINITY);
+        }
+      }
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), p.sl2, nlse));
-        float e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), p.sl2, nlse));
-        if (need_mask) {
-          const int kc = k0 + c0 + i;
-          if (kc >= p.S || grow >= p.S || (p.causal && kc > grow)) e0 = 0.f;
-          if (kc + 1 >= p.S || grow >= p.S || (p.causal && kc + 1 > grow)) e1 = 0.f;
-        }
+        const float e0 = fast_exp2(fmaf(__uint_as_float(rs[i]), p.sl2, nlse));
+        const float e1 = fast_exp2(fmaf(__uint_as_float(rs[i + 1]), p.sl2, nlse));
         dw[i >> 1] = pack_bf16(e0 * (__uint_as_float(rd[i]) - dl), e1 * (__uint_as_float(rd[i + 1]) - dl));
       }
+      FT_BTRACE(1, warp == 0 ? 0 : 1, j, 3);
       if (j >= C::NBUF &&
           !mbar_wait(&acc_done[buf], ((j / C::NBUF) - 1) & 1, ctx, FT_ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      FT_BTRACE(1, warp == 0 ? 0 : 1, j, 4);
       if constexpr (C::TS) {
         tc_fence_after();
         tmem_st16(tmem_base + C::TM_DS + 64 * buf + 16 * g + lane_sel, dw);
@@ -529,6 +576,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_ready[buf]);      // one arrival per warp
+      FT_BTRACE(1, warp == 0 ? 0 : 1, j, 5);
     }
     if (ok && nkv > 0)
       ok = mbar_wait(&acc_done[(nkv - 1) % C::NBUF], ((nkv - 1) / C::NBUF) & 1, ctx, FT_ERR_WAIT_TMEM_FULL);
@@ -585,6 +633,12 @@ static int attn_bwd_launch(const FtkAttnDesc* a, cudaStream_t s) {
 }  // namespace ftk
 
 using namespace ftk;
+
+#ifdef FT_ATTN_TRACE
+extern "C" int ftk_attn_bwd_trace_read(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_attn_bwd_trace, sizeof(long long) * n);
+}
+#endif
 
 extern "C" int ftk_attn_bwd(const FtkAttnDesc* a, void* stream) {
   if (!a || a->B <= 0 || a->H <= 0 || a->S <= 0 || !a->delta || !a->lse) return -2;

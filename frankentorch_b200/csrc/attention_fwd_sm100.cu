@@ -12,8 +12,8 @@
 //              query row reads its whole 128-wide score row into registers with tcgen05.ld and
 //              releases the TMEM score tile at once, so QK^T of the next block runs under the
 //              exponentials of this one and the two groups alternate on the tensor core;
-//   warp 8     TMA producer;  warp 9  MMA issuer (owns TMEM);  warps 10-11 only hand their
-//              registers to the softmax groups (setmaxnreg).
+//   warp 8     TMA producer;  warp 9  issues S = Q K^T (owns TMEM);  warp 10 issues O += P V;
+//              warp 11 only hands its registers to the softmax groups (setmaxnreg).
 // The output accumulates in TMEM across all key blocks.  The running maximum is lazy: a row
 // keeps its reference maximum until a block exceeds it by more than 2^8, and only then is the
 // TMEM accumulator rescaled (tcgen05.ld / mul / tcgen05.st, voted per warp).  With head_dim 64
@@ -174,21 +174,26 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncwarp();
       }
     } else if (warp == 9) {
-      // ------------------------------------------------------------ MMA issuer
+      // ------------------------------------------------------------ MMA issuer 1: S = Q K^T
+      // The issuing thread runs in step with the tensor pipe (an MMA is accepted when the one
+      // before the previous has finished), so every wait, fence and descriptor step between
+      // two MMAs is time the pipe idles.  Two issuers, one per product, overlap that overhead:
+      // this warp owns the K slots, warp 10 the V slots (each slot has one releasing commit).
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-      const uint32_t idesc_pv = make_idesc_bf16(128, HD, 0, 1);
       const uint32_t q_addr = smem_u32(smem + C::OFF_Q);
-      const uint32_t p_addr = smem_u32(smem + C::OFF_P);
       const uint32_t kv_addr = smem_u32(smem + C::OFF_KV);
       bool ok = mbar_wait(q_full, 0, ctx, FT_ERR_WAIT_FULL);
-      // S of block jj for both tiles: needs K_jj and the score tiles drained of block jj-1
-      auto issue_scores = [&](int jj) -> bool {
+      for (int jj = 0; ok && jj < nkv; ++jj) {
+        FT_TRACE(2, jj, 0);
         const int n = 2 * jj, slot = n % C::NSLOT;
-        if (!mbar_wait(&kv_full[slot], (n / C::NSLOT) & 1, ctx, FT_ERR_WAIT_FULL)) return false;
+        if (!mbar_wait(&kv_full[slot], (n / C::NSLOT) & 1, ctx, FT_ERR_WAIT_FULL)) break;
+        FT_TRACE(2, jj, 1);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (jj >= nb[t]) continue;
-          if (jj > 0 && !mbar_wait(&s_free[t], (jj - 1) & 1, ctx, FT_ERR_WAIT_TMEM_EMPTY)) return false;
+          // the score tile must have been copied to registers (block jj - 1)
+          if (jj > 0 && !mbar_wait(&s_free[t], (jj - 1) & 1, ctx, FT_ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          FT_TRACE(2, jj, 2 + t);
           tc_fence_after();
           if (lane == 0) {
             mma_kmajor<HD>(tmem_base + C::TM_S + 128 * t, q_addr + t * C::TILE,
@@ -197,24 +202,26 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
           __syncwarp();
         }
+        if (!ok) break;
         if (lane == 0) umma_commit(&kv_empty[slot]);
         __syncwarp();
-        return true;
-      };
-      if (ok && nkv > 0) ok = issue_scores(0);
+        FT_TRACE(2, jj, 4);
+      }
+    } else if (warp == 10) {
+      // ------------------------------------------------------------ MMA issuer 2: O += P V
+      const uint32_t idesc_pv = make_idesc_bf16(128, HD, 0, 1);
+      const uint32_t p_addr = smem_u32(smem + C::OFF_P);
+      const uint32_t kv_addr = smem_u32(smem + C::OFF_KV);
+      bool ok = true;
       for (int j = 0; ok && j < nkv; ++j) {
-        FT_TRACE(2, j, 0);
-        if (j + 1 < nkv) ok = issue_scores(j + 1);     // runs under the softmax of block j
-        if (!ok) break;
-        FT_TRACE(2, j, 1);
+        FT_TRACE(3, j, 0);
         const int n = 2 * j + 1, slot = n % C::NSLOT;
         if (!mbar_wait(&kv_full[slot], (n / C::NSLOT) & 1, ctx, FT_ERR_WAIT_FULL)) break;
-        FT_TRACE(2, j, 2);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j >= nb[t]) continue;
           if (!mbar_wait(&p_ready[t], j & 1, ctx, FT_ERR_WAIT_SOFTMAX)) { ok = false; break; }
-          FT_TRACE(2, j, 3 + t);
+          FT_TRACE(3, j, 1 + 2 * t);
           tc_fence_after();
           if (lane == 0) {
             if constexpr (C::TS)
@@ -226,6 +233,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             umma_commit(&pv_done[t]);
           }
           __syncwarp();
+          FT_TRACE(3, j, 2 + 2 * t);
         }
         if (!ok) break;
         if (lane == 0) umma_commit(&kv_empty[slot]);

@@ -35,37 +35,38 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// A (K-major) x B (K-major)^T with K = HD, operands stored as HD/64 regions.
+// A (K-major) x B (K-major)^T with K = HD, operands stored as HD/64 regions.  The descriptors'
+// low words are built once per call and stepped by constants (see desc_lo).
 template <int HD>
 __device__ __forceinline__ void mma_kmajor(uint32_t d_tmem, uint32_t a_base, uint32_t b_base,
                                            uint32_t idesc) {
+  const uint32_t a_lo = desc_lo(a_base, 16), b_lo = desc_lo(b_base, 16);
 #pragma unroll
   for (int kk = 0; kk < HD / 16; ++kk) {
-    const uint32_t off = (kk >> 2) * AT_REGION + (kk & 3) * 32;
-    umma_bf16(d_tmem, make_smem_desc(a_base + off, 16, 1024), make_smem_desc(b_base + off, 16, 1024),
-              idesc, kk != 0 ? 1u : 0u);
+    const uint32_t off = (uint32_t)(((kk >> 2) * AT_REGION + (kk & 3) * 32) >> 4);
+    umma_bf16_lo(d_tmem, a_lo + off, b_lo + off, idesc, kk != 0 ? 1u : 0u);
   }
 }
 // A = probabilities [128 x 128] K-major in two regions; B = [128 k-rows x HD] stored
 // row-major per 64-column region (MN-major operand), K = 128.
 __device__ __forceinline__ void mma_p_times_rows(uint32_t d_tmem, uint32_t p_base, uint32_t b_base,
                                                  uint32_t idesc, bool accumulate) {
+  const uint32_t a_lo = desc_lo(p_base, 16), b_lo = desc_lo(b_base, AT_REGION);
 #pragma unroll
   for (int kk = 0; kk < AT_T / 16; ++kk) {
-    const uint32_t a_off = (kk >> 2) * AT_REGION + (kk & 3) * 32;
-    umma_bf16(d_tmem, make_smem_desc(p_base + a_off, 16, 1024),
-              make_smem_desc(b_base + kk * 2048, AT_REGION, 1024), idesc,
-              (accumulate || kk != 0) ? 1u : 0u);
+    const uint32_t a_off = (uint32_t)(((kk >> 2) * AT_REGION + (kk & 3) * 32) >> 4);
+    umma_bf16_lo(d_tmem, a_lo + a_off, b_lo + (uint32_t)(kk * 128), idesc, (accumulate || kk != 0) ? 1u : 0u);
   }
 }
 // Same product with A = probabilities held in tensor memory: 128 lanes (rows) x 64 columns of
 // packed bf16 pairs (K = 128), written by the row-owning threads with tcgen05.st.
 __device__ __forceinline__ void mma_ptmem_times_rows(uint32_t d_tmem, uint32_t p_tmem, uint32_t b_base,
                                                      uint32_t idesc, bool accumulate) {
+  const uint32_t b_lo = desc_lo(b_base, AT_REGION);
 #pragma unroll
   for (int kk = 0; kk < AT_T / 16; ++kk) {
-    umma_bf16_ts(d_tmem, p_tmem + kk * 8, make_smem_desc(b_base + kk * 2048, AT_REGION, 1024), idesc,
-                 (accumulate || kk != 0) ? 1u : 0u);
+    umma_bf16_ts_lo(d_tmem, p_tmem + kk * 8, b_lo + (uint32_t)(kk * 128), idesc,
+                    (accumulate || kk != 0) ? 1u : 0u);
   }
 }
 // Write 32 fp32 values of one tile row as bf16 into the swizzled K-major tile.

@@ -142,6 +142,8 @@ gemm2_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint32_t idesc = make_idesc_bf16(2 * G_BM, BN, p.a_mn, p.b_mn);
       const uint32_t a_lbo = p.a_mn ? G_BK * 128 : 16, a_adv = p.a_mn ? G_UMMA_K * 128 : G_UMMA_K * 2;
       const uint32_t b_lbo = p.b_mn ? G_BK * 128 : 16, b_adv = p.b_mn ? G_UMMA_K * 128 : G_UMMA_K * 2;
+      const uint32_t a_lo0 = desc_lo(smem_u32(sA), a_lbo), b_lo0 = desc_lo(smem_u32(sB), b_lbo);
+      const uint32_t a_adv16 = a_adv >> 4, b_adv16 = b_adv >> 4;
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -161,14 +163,12 @@ gemm2_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           tc_fence_after();
           if (lane == 0) {
-            const uint32_t a_addr = smem_u32(sA + s * Cfg::A_BYTES);
-            const uint32_t b_addr = smem_u32(sB + s * Cfg::B_BYTES);
+            const uint32_t a_lo = a_lo0 + (uint32_t)s * (Cfg::A_BYTES >> 4);
+            const uint32_t b_lo = b_lo0 + (uint32_t)s * (Cfg::B_BYTES >> 4);
+            umma_bf16_pair_lo(d_tmem, a_lo, b_lo, idesc, kb > kb0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < G_BK / G_UMMA_K; ++k) {
-              umma_bf16_pair(d_tmem, make_smem_desc(a_addr + k * a_adv, a_lbo, 1024),
-                             make_smem_desc(b_addr + k * b_adv, b_lbo, 1024), idesc,
-                             (kb > kb0 || k > 0) ? 1u : 0u);
-            }
+            for (int k = 1; k < G_BK / G_UMMA_K; ++k)
+              umma_bf16_pair_lo(d_tmem, a_lo + k * a_adv16, b_lo + k * b_adv16, idesc, 1u);
             umma_commit_pair(&empty[s], 3);                       // the stage is free in both CTAs
             if (kb == kb1 - 1) umma_commit_pair(&tfull[acc], 3);  // both epilogues may drain
           }
