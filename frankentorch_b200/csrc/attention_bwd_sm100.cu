@@ -8,14 +8,15 @@
 // Layout: Q/K/V/O/dO are addressed in place inside the packed [B*S, 3*d] / [B*S, d]
 // activations through 4-D TMA maps {head_dim, S, H, B}; no head split/merge copies.
 //
-// Two kernels, each 18 warps: warps 0-15 do the elementwise math, warp 16 is the TMA
-// producer, warp 17 issues the MMAs and owns TMEM.  The 16 math warps split every
-// 128 x 128 score tile by columns (four groups of 32 columns; a thread owns one tile row
-// inside its group's columns), so one tcgen05.ld per operand brings a thread's whole share
-// into registers, the TMEM score tiles are released at once and the tensor core computes the
-// next block's scores under the exponentials of this one.  P^T / dS^T (or dS) go back to the
-// tensor core through 128B-swizzled bf16 tiles in shared memory, double-buffered where
-// shared memory allows.
+// Two kernels, each 19 warps: warps 0-15 do the elementwise math, warp 16 is the TMA
+// producer, warp 17 issues the score products (and owns TMEM), warp 18 the accumulating
+// products.  The 16 math warps split every 128 x 128 score tile by columns (four groups of 32
+// columns; a thread owns one tile row inside its group's columns), so one tcgen05.ld per
+// operand brings a thread's whole share into registers, the TMEM score tiles are released at
+// once and the tensor core computes the next block's scores under the exponentials of this
+// one.  With head_dim 64, P^T / dS^T (or dS) go back to the tensor core through tensor memory
+// (tcgen05.st by the row's thread, MMA with its A operand in TMEM); with head_dim 128 all 512
+// columns hold accumulators and they go through 128B-swizzled bf16 tiles in shared memory.
 //
 // Determinism: dK/dV are accumulated in TMEM by the CTA that owns the key block, dQ by the
 // CTA that owns the query block (second kernel), both in ascending block order; there are
@@ -109,7 +110,7 @@ struct DkvCfg {
   // already saturates with its B operands).  head_dim 128 fills all 512 columns with
   // accumulators and stages both tiles in shared memory.
   static constexpr bool TS = (HD == 64);
-  static constexpr int STAGES = (HD == 64) ? 3 : 1;          // Q / dO ring
+  static constexpr int STAGES = (HD == 64) ? 4 : 1;          // Q / dO ring
   static constexpr int NBUF = 1;                             // P^T / dS^T buffers
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = TILE;
@@ -194,18 +195,31 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       load_tile<HD>(smem + C::OFF_K, &tmK, kv_full, k0, h, b);
       load_tile<HD>(smem + C::OFF_V, &tmV, kv_full, k0, h, b);
     }
+    // Per-query statistics (-lse and delta) of a block travel with its Q / dO tiles: they are
+    // fetched into registers one iteration ahead, so their global-memory latency is spent while
+    // this warp waits for the stage, not between the stage becoming free and its TMA loads.
+    const long long sbase = ((long long)b * p.H + h) * p.S;
+    float nl_r[4], dl_r[4];
+    auto fetch_stats = [&](int it) {
+      const int q0 = (qb_first + it) * AT_T;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int gq = q0 + lane + 32 * u;
+        nl_r[u] = gq < p.S ? -p.lse[sbase + gq] : -INFINITY;
+        dl_r[u] = gq < p.S ? p.delta[sbase + gq] : 0.f;
+      }
+    };
+    if (nit > 0) fetch_stats(0);
     for (int it = 0; it < nit; ++it) {
       const int st = it % C::STAGES;
       const uint32_t ph = (it / C::STAGES) & 1;
       if (!mbar_wait(&qdo_empty[st], ph ^ 1u, ctx, FT_ERR_WAIT_EMPTY)) break;
       const int q0 = (qb_first + it) * AT_T;
-      // per-query statistics of this block: -lse and delta (published by the arrive below)
-      float* sl = stat + st * 256;
-      const long long sbase = ((long long)b * p.H + h) * p.S;
-      for (int i = lane; i < AT_T; i += 32) {
-        const int gq = q0 + i;
-        sl[i] = gq < p.S ? -p.lse[sbase + gq] : -INFINITY;
-        sl[128 + i] = gq < p.S ? p.delta[sbase + gq] : 0.f;
+      float* sl = stat + st * 256;          // published by the arrive below
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        sl[lane + 32 * u] = nl_r[u];
+        sl[128 + lane + 32 * u] = dl_r[u];
       }
       __syncwarp();
       if (lane == 0) {
@@ -214,6 +228,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         load_tile<HD>(smem + C::OFF_DO + st * C::TILE, &tmDO, &qdo_full[st], q0, h, b);
       }
       __syncwarp();
+      if (it + 1 < nit) fetch_stats(it + 1);
     }
   } else if (warp == BW_WARP_MMA) {
     // ---------------------------------------------------------- issuer 1: S^T = K Q^T, dP^T = V dO^T
