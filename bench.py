@@ -70,12 +70,56 @@ class ClockSampler:
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, uuid: str = ""):
         self.gpu = gpu_index
+        self.uuid = uuid
         self.proc = None
         self.path = None
+        self.thread = None
+        self.stop_flag = None
+        self.rows = []
+
+    def _start_nvml(self) -> bool:
+        """Preferred sampler: NVML in a thread of this process, one reading every 20 ms (a
+        spawned nvidia-smi needs longer to enumerate eight GPUs than a short timed region lasts).
+        Read-only queries; nothing on the GPU is changed."""
+        try:
+            import threading
+
+            import pynvml as nv
+            nv.nvmlInit()
+            h = None
+            if self.uuid:
+                for cand in (self.uuid, self.uuid.encode()):
+                    try:
+                        h = nv.nvmlDeviceGetHandleByUUID(cand)
+                        break
+                    except Exception:
+                        h = None
+            if h is None:
+                h = nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+            mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.stop_flag = threading.Event()
+
+            def loop():
+                while not self.stop_flag.is_set():
+                    try:
+                        self.rows.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), mx, int(reasons_fn(h))))
+                    except Exception:
+                        pass
+                    self.stop_flag.wait(0.02)
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return True
+        except Exception:
+            self.thread = None
+            return False
 
     def start(self):
+        if self._start_nvml():
+            return
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -87,6 +131,20 @@ class ClockSampler:
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            if self.rows:
+                # NVML clocks-event-reason bits
+                bits = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                        0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+                seen = 0
+                for _, _, r in self.rows:
+                    seen |= r
+                out.update(sm_mhz=statistics.median(r[0] for r in self.rows), sm_max_mhz=self.rows[0][1],
+                           samples=len(self.rows), reasons=sorted(n for b, n in bits.items() if seen & b),
+                           source="nvml")
+            return out
         if self.proc is None:
             return out
         try:
@@ -204,7 +262,7 @@ def main():
     K.check_status()
 
     # ---------------- device-timed region: K steps, CUDA events, inputs resident on the device
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, "GPU-" + str(getattr(torch.cuda.get_device_properties(dev), "uuid", "")))
     sampler.start()
     sync_all()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -305,6 +305,21 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   // gathers: CTAs that only move data (default 20); reduce-scatter: every CTA reduces after its
   // GEMM tiles, dedicated CTAs are optional (default none)
   c.comm_ctas = cd->comm_ctas > 0 ? cd->comm_ctas : (cd->mode == FTK_COMM_SCATTER_D ? 0 : 20);
+  if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D) {
+    // Split the SMs between copying and computing in proportion to the work: a copy CTA keeps
+    // 128 KB of peer loads in flight, which at NVLink latency under load is ~13 GB/s (measured
+    // at 2 and 8 ranks), a compute CTA delivers its share of the sustained GEMM rate.
+    const bool bk = cd->mode == FTK_COMM_GATHER_B && g->b_mn;
+    const double row_bytes = 2.0 * (double)(bk ? g->N : g->K);
+    const double remote = (double)(cd->world - 1) * (double)cd->chunk_rows * row_bytes;
+    const double comm_work = remote / 13e9;
+    const double gemm_work = 2.0 * (double)g->M * (double)g->N * (double)g->K / (1.4e15 / (double)sms);
+    int cc = (int)(sms * comm_work / (comm_work + gemm_work) + 0.5);
+    if (cc < 12) cc = 12;
+    if (cc > 64) cc = 64;
+    if (cd->world == 1) cc = 8;
+    c.comm_ctas = cc;
+  }
   if (c.comm_ctas >= sms) return -7;
 
   if (cd->mode == FTK_COMM_SCATTER_D) {
