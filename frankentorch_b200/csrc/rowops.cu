@@ -473,14 +473,30 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* 
   const int nvec = ld >> 3;
   const long long tgt = targets[row];
   float m = -INFINITY;
-  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
-    uint4 u = xv[v];
-    if (use_smem) ce_smem[v] = u;
-    float f[8];
-    unpack8(u, f);
+  // four 16-byte loads in flight per thread: a 100 KB row is otherwise fetched 8 KB at a time and
+  // the kernel sits at memory latency instead of bandwidth
+  for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * CE_THREADS) {
+    uint4 u[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (v * 8 + i < vocab) m = fmaxf(m, f[i]);
+    for (int k = 0; k < 4; ++k) {
+      const int v = v0 + k * CE_THREADS;
+      u[k] = v < nvec ? xv[v] : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int v = v0 + k * CE_THREADS;
+      if (v >= nvec) break;
+      if (use_smem) ce_smem[v] = u[k];
+      float f[8];
+      unpack8(u[k], f);
+      if (v * 8 + 8 <= vocab) {
+        m = fmaxf(m, fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7]))));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (v * 8 + i < vocab) m = fmaxf(m, f[i]);
+      }
+    }
   }
   m = block_reduce(m, red, true);
   const uint4* src = use_smem ? ce_smem : xv;
@@ -488,9 +504,14 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* 
   for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
     float f[8];
     unpack8(src[v], f);
+    if (v * 8 + 8 <= vocab) {       // whole vector inside the vocabulary: no per-element guard
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (v * 8 + i < vocab) s += __expf(f[i] - m);
+      for (int i = 0; i < 8; ++i) s += __expf(f[i] - m);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (v * 8 + i < vocab) s += __expf(f[i] - m);
+    }
   }
   s = block_reduce(s, red, false);
   const float lse = m + __logf(s);
@@ -503,15 +524,21 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* 
     const float inv = 1.f / s;
     const bool ignore = !(tgt >= 0 && tgt < vocab);
     uint4* ov = reinterpret_cast<uint4*>(dlogits + row * ld);
+    const int vt = ignore ? -1 : (int)(tgt >> 3);     // the vector that holds the target column
     for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
       float f[8];
       unpack8(src[v], f);
+      if (!ignore && v != vt && v * 8 + 8 <= vocab) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int c = v * 8 + i;
-        float g = 0.f;
-        if (c < vocab && !ignore) g = (__expf(f[i] - m) * inv - (c == tgt ? 1.f : 0.f)) * grad_scale;
-        f[i] = g;
+        for (int i = 0; i < 8; ++i) f[i] = (__expf(f[i] - m) * inv - 0.f) * grad_scale;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = v * 8 + i;
+          float g = 0.f;
+          if (c < vocab && !ignore) g = (__expf(f[i] - m) * inv - (c == tgt ? 1.f : 0.f)) * grad_scale;
+          f[i] = g;
+        }
       }
       ov[v] = pack8(f);
     }
