@@ -290,7 +290,7 @@ __device__ __forceinline__ TileCoord decode_item(int item, const GemmArgs& p, co
 __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const CommArgs& c,
                                             int epoch, int cta, bool own_last, const WaitCtx& ctx) {
   uint64_t* full = bars;
-  // progress word shared by the driver (thread 0) and the publisher (thread 32): number of this
+  // progress word shared by the storer (thread 64) and the publisher (thread 32): number of this
   // CTA's pieces whose stores have landed; -1 after a failure
   int* progress = reinterpret_cast<int*>(bars + 2 * G_COPY_SLOTS);
   const int spc = c.chunk_rows / G_BM;                 // subtiles per chunk
@@ -301,33 +301,38 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
   const int shift = own_last ? ppc : 0;                // visit v -> rotated piece (v + shift) % n
   const int mine = cta < n_pieces ? (n_pieces - cta + c.comm_ctas - 1) / c.comm_ctas : 0;
   auto rotated = [&](int i) { return (int)(((long long)cta + (long long)i * c.comm_ctas + shift) % n_pieces); };
+  uint64_t* empty = bars + G_COPY_SLOTS;
   if (threadIdx.x == 0) {
-    // announce that this rank's shard is final for this epoch
+    // loader: peer (or own) memory -> ring slot.  It never waits for a store to land, only for
+    // the slot's previous contents to have been read out, so up to G_COPY_SLOTS loads are in
+    // flight per CTA.
     if (cta == 0 && c.ready_local) {
+      // announce that this rank's shard is final for this epoch
       __threadfence_system();
       for (int r = 0; r < c.world; ++r)
         if (r != c.rank) st_rel_sys(c.ready_peer[r], epoch);
     }
-    int issued = 0, stored = 0;
     int ready_seen = 1 << c.rank;
-    bool ok = true;
-    while (ok && stored < mine) {
-      while (issued < mine && issued < stored + G_COPY_SLOTS - 2) {
-        const int q = rotated(issued);
-        const int chunk = (c.rank + q / ppc) % c.world;
-        if (c.ready_local && !((ready_seen >> chunk) & 1)) {
-          if (!flag_wait<true>(c.ready_local + chunk, epoch, ctx)) {
-            ok = false;
-            break;
-          }
-          ready_seen |= 1 << chunk;
-        }
-        const int slot = issued % G_COPY_SLOTS;
-        mbar_arrive_expect_tx(&full[slot], piece);
-        bulk_load(smem + slot * G_COPY_SLOT, c.src[chunk] + (long long)(q % ppc) * piece, piece, &full[slot]);
-        ++issued;
+    for (int i = 0; i < mine; ++i) {
+      const int slot = i % G_COPY_SLOTS;
+      if (i >= G_COPY_SLOTS &&
+          !mbar_wait(&empty[slot], (uint32_t)(((i / G_COPY_SLOTS) - 1) & 1), ctx, FT_ERR_WAIT_EMPTY))
+        break;
+      const int q = rotated(i);
+      const int chunk = (c.rank + q / ppc) % c.world;
+      if (c.ready_local && !((ready_seen >> chunk) & 1)) {
+        if (!flag_wait<true>(c.ready_local + chunk, epoch, ctx)) break;
+        ready_seen |= 1 << chunk;
       }
-      if (!ok) break;
+      mbar_arrive_expect_tx(&full[slot], piece);
+      bulk_load(smem + slot * G_COPY_SLOT, c.src[chunk] + (long long)(q % ppc) * piece, piece, &full[slot]);
+    }
+  } else if (threadIdx.x == 64) {
+    // storer: ring slot -> the gathered operand in this GPU's memory; frees a slot once its store
+    // has read it and advances the progress word once stores have landed
+    int stored = 0;
+    bool ok = true;
+    while (stored < mine) {
       const int slot = stored % G_COPY_SLOTS;
       if (!mbar_wait(&full[slot], (uint32_t)((stored / G_COPY_SLOTS) & 1), ctx, FT_ERR_WAIT_FULL)) {
         ok = false;
@@ -336,7 +341,8 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
       const int q = rotated(stored);
       bulk_store(c.full + ((long long)((c.rank + q / ppc) % c.world) * ppc + q % ppc) * piece,
                  smem + slot * G_COPY_SLOT, piece);
-      bulk_wait_group_read<1>();                       // the slot of the previous store is free
+      bulk_wait_group_read<1>();                       // the previous store has read its slot
+      if (stored > 0) mbar_arrive(&empty[(stored - 1) % G_COPY_SLOTS]);
       ++stored;
       bulk_wait_group<3>();                            // all but the newest three stores landed
       if (stored > 3) asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(progress)), "r"(stored - 3) : "memory");
