@@ -1,0 +1,2 @@
+
+from .encoder import EncoderGpu, EncoderLayerWeights  # noqa: E402,F401
