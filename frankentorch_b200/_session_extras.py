@@ -15,6 +15,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from .autograd import functions_extra as FX
+from .autograd import functions_sparse as FS
 from .core.dtype import DType
 
 # alias -> existing session method
@@ -180,7 +181,84 @@ def roi_pool(self, feat, rois, output_size=(2, 2), spatial_scale: float = 1.0) -
     return self.tensor_roi_pool(feat, rois, output_size=output_size, spatial_scale=spatial_scale)
 
 
+# ------------------------------------------------------------------------------- sparse COO / CSR
+class SparseCOO:
+    """Handle of a sparse COO tensor on the session's tape: two dense nodes and a static shape
+    (``indices[nnz, ndim]`` f64-valued, ``values[nnz]``)."""
+
+    __slots__ = ("indices", "values", "shape", "coalesced")
+
+    def __init__(self, indices: int, values: int, shape: Sequence[int], coalesced: bool = False):
+        self.indices, self.values, self.shape, self.coalesced = indices, values, tuple(int(s) for s in shape), coalesced
+
+
+def sparse_coo_tensor(self, indices, values, shape, requires_grad: bool = False) -> SparseCOO:
+    """``indices``: ``[nnz][ndim]`` integers, ``values``: ``[nnz]`` floats (lists or tensors)."""
+    it = torch.as_tensor(indices, dtype=torch.float64).reshape(-1, len(shape))
+    vt = torch.as_tensor(values, dtype=torch.float64).reshape(-1)
+    if it.shape[0] != vt.shape[0]:
+        raise ValueError("indices and values disagree on nnz")
+    FS.linear_index(it, shape)     # range check
+    return SparseCOO(self.tensor_tape.leaf(it.to(self.device), False),
+                     self.tensor_tape.leaf(vt.to(self.device), requires_grad), shape)
+
+
+def sparse_coalesce(self, sp: SparseCOO) -> SparseCOO:
+    if sp.coalesced:
+        return sp
+    idx = self.tensor_sparse_coo_coalesce_indices(sp.indices, sp.values, shape=sp.shape)
+    val = self.tensor_sparse_coo_coalesce_values(sp.indices, sp.values, shape=sp.shape)
+    return SparseCOO(idx, val, sp.shape, True)
+
+
+def sparse_to_dense(self, sp: SparseCOO) -> int:
+    return self.tensor_sparse_coo_to_dense(sp.indices, sp.values, shape=sp.shape)
+
+
+def sparse_matmul(self, sp: SparseCOO, dense: int) -> int:
+    if len(sp.shape) != 2:
+        raise ValueError("sparse_matmul needs a 2-D sparse operand")
+    return self.tensor_sparse_coo_matmul_dense(sp.indices, sp.values, dense, shape=sp.shape)
+
+
+def sparse_add(self, a: SparseCOO, b: SparseCOO) -> SparseCOO:
+    if a.shape != b.shape:
+        raise ValueError("sparse_add needs equal shapes")
+    idx = self.tensor_cat([a.indices, b.indices], 0)
+    val = self.tensor_cat([a.values, b.values], 0)
+    return sparse_coalesce(self, SparseCOO(idx, val, a.shape))
+
+
+def sparse_to_csr(self, sp: SparseCOO) -> Tuple[List[int], List[int], List[float]]:
+    crow, col, val = FS.csr_from_coo(self.tensor(sp.indices), self.tensor(sp.values), sp.shape)
+    return crow.tolist(), col.tolist(), val.tolist()
+
+
+def sparse_nnz(self, sp: SparseCOO) -> int:
+    return int(self.tensor(sp.values).shape[0])
+
+
+# ------------------------------------------------------------------------------- low rank / counting
+def tensor_svd_lowrank(self, a, q: int = 6, niter: int = 2, seed: int = 0x4654) -> Tuple[int, int, int]:
+    kw = dict(q=q, niter=niter, seed=seed)
+    return (self.tensor_svd_lowrank_u(a, **kw), self.tensor_svd_lowrank_s(a, **kw), self.tensor_svd_lowrank_v(a, **kw))
+
+
+def tensor_pca_lowrank(self, a, q: int = 6, center: bool = True, niter: int = 2, seed: int = 0x4654):
+    kw = dict(q=q, center=center, niter=niter, seed=seed)
+    return (self.tensor_pca_lowrank_u(a, **kw), self.tensor_pca_lowrank_s(a, **kw), self.tensor_pca_lowrank_v(a, **kw))
+
+
+def tensor_unique_with_counts(self, a) -> Tuple[int, int, int]:
+    """``(values, inverse, counts)`` of the sorted unique elements."""
+    return self.tensor_unique(a), self.tensor_unique_inverse(a), self.tensor_unique_counts(a)
+
+
 def install(cls) -> None:
+    for fn in (sparse_coo_tensor, sparse_coalesce, sparse_to_dense, sparse_matmul, sparse_add, sparse_to_csr,
+               sparse_nnz, tensor_svd_lowrank, tensor_pca_lowrank, tensor_unique_with_counts):
+        setattr(cls, fn.__name__, fn)
+    cls.supcon_loss = _alias("tensor_supcon_loss", "supcon_loss")
     for name, target in _ALIASES.items():
         if hasattr(cls, target) and not hasattr(cls, name):
             setattr(cls, name, _alias(target, name))

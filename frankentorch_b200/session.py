@@ -31,6 +31,7 @@ from .autograd import functions as _f1  # noqa: F401  (populate the rule table)
 from .autograd import functions_nn as _f3  # noqa: F401
 from .autograd import functions_shape as _f2  # noqa: F401
 from .autograd import functions_extra as _f4  # noqa: F401
+from .autograd import functions_sparse as _f5  # noqa: F401
 from .autograd.functions import OPS, OpDef
 from .autograd.scalar_tape import BackwardReport, Tape
 from .autograd.tape import (BackwardOptions, BorrowedInputVersionMismatch, TensorBackwardReport, TensorHookHandle,
