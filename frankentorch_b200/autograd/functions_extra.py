@@ -320,3 +320,9 @@ def _fractional_max_pool2d(x, kernel_size=2, output_size=None, output_ratio=None
 
 
 _generic("fractional_max_pool2d", _fractional_max_pool2d, "max pool over pseudo-random windows: gradient to the arg-max")
+_nograd("max_pool2d_indices", lambda x, kernel_size=2, stride=None, padding=0:
+        torch.nn.functional.max_pool2d(x, kernel_size, stride, padding, return_indices=True)[1].to(torch.float64),
+        "flat arg-max positions of max_pool2d; no gradient")
+_generic("max_unpool2d", lambda x, indices, kernel_size=2, stride=None, padding=0, output_size=None:
+         torch.nn.functional.max_unpool2d(x, indices.long(), kernel_size, stride, padding, output_size),
+         "d(max_unpool)/dx = gather of g at the indices")

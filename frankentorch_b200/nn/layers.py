@@ -63,9 +63,10 @@ class LazyLinear(Module):
 
     def forward(self, session, x):
         if self._inner is None:
-            self._inner = Linear(session, session.tensor_shape(x)[-1], self.out_features, self._bias)
-            self.register_parameter("weight", self._inner.weight)
-            self.register_parameter("bias", self._inner.bias)
+            # bypass child registration: the parameters are registered on this module itself
+            object.__setattr__(self, "_inner", Linear(session, session.tensor_shape(x)[-1], self.out_features, self._bias))
+            self.register_parameter("weight", self._inner._parameters["weight"])
+            self.register_parameter("bias", self._inner._parameters["bias"])
         return session.tensor_linear(x, self._parameters["weight"], self._parameters["bias"])
 
 
