@@ -92,3 +92,57 @@ def load_training_state(engine, stem: str) -> None:
     else:
         a.sync_shadow()
     torch.cuda.synchronize()
+
+
+# --------------------------------------------------------------------------- job state sidecar
+def job_state(*, scheduler=None, session=None, loader=None, step: int = 0, extra: Dict = None) -> Dict:
+    """Host-side state that, with the tensors above, makes a resumed job replay the original one:
+    learning-rate scheduler (``SchedulerState``: last_epoch / last_lrs / extra, ft-optim
+    ``:2301``), the session's xoshiro256++ stream (four 64-bit words), and the data loader's
+    position (LCG state, cursor, current shuffled order).  Plain JSON-able values."""
+    out: Dict = {"schema": "ft-job-state-v1", "step": int(step), "extra": dict(extra or {})}
+    if scheduler is not None:
+        st = scheduler.state()
+        out["scheduler"] = {"last_epoch": int(st.last_epoch), "last_lrs": [float(x) for x in st.last_lrs],
+                            "extra": {k: float(v) for k, v in st.extra.items()}}
+    if session is not None:
+        out["prng"] = [int(session.rng.state[i]) for i in range(4)]
+    if loader is not None:
+        out["loader"] = {"rng_state": int(loader._rng.state), "cursor": int(loader._cursor),
+                         "order": None if loader._order is None else [int(i) for i in loader._order]}
+    return out
+
+
+def restore_job_state(state: Dict, *, scheduler=None, session=None, loader=None) -> int:
+    """Inverse of :func:`job_state`; returns the saved step.  Unknown schemas are rejected."""
+    if state.get("schema") != "ft-job-state-v1":
+        raise ValueError(f"unknown job-state schema {state.get('schema')!r}")
+    if scheduler is not None and "scheduler" in state:
+        from ..optim.schedulers import SchedulerState
+        s = state["scheduler"]
+        scheduler.load_state(SchedulerState(int(s["last_epoch"]), list(s["last_lrs"]), dict(s["extra"])))
+    if session is not None and "prng" in state:
+        words = state["prng"]
+        if len(words) != 4:
+            raise ValueError("the PRNG state has four 64-bit words")
+        for i, w in enumerate(words):
+            session.rng.state[i] = int(w) & ((1 << 64) - 1)
+    if loader is not None and "loader" in state:
+        ld = state["loader"]
+        loader._rng.state = int(ld["rng_state"])
+        loader._cursor = int(ld["cursor"])
+        loader._order = None if ld["order"] is None else [int(i) for i in ld["order"]]
+    return int(state.get("step", 0))
+
+
+def save_job_state(path: str, **kw) -> str:
+    import json
+    with open(path, "w") as f:
+        json.dump(job_state(**kw), f, sort_keys=True, separators=(",", ":"))
+    return path
+
+
+def load_job_state(path: str, **kw) -> int:
+    import json
+    with open(path) as f:
+        return restore_job_state(json.load(f), **kw)
