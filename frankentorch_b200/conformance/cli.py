@@ -266,9 +266,10 @@ def main(argv=None) -> int:
     p.add_argument("artifact")
     p.add_argument("--repair-symbols", type=int, default=4)
     p.set_defaults(fn=emit_packet_sidecar)
-    p = sub.add_parser("validate_artifacts")
-    p.add_argument("root")
-    p.set_defaults(fn=validate_artifacts)
+    for name in ("validate_artifacts", "validate_phase2c_artifacts"):   # the reference's binary carries the longer name
+        p = sub.add_parser(name)
+        p.add_argument("root", nargs="?", default=".")
+        p.set_defaults(fn=validate_artifacts)
     p = sub.add_parser("run_perf_slos")
     p.add_argument("--profile", default="smoke", choices=["smoke", "full"])
     p.add_argument("--iterations", type=int, default=10)
