@@ -10,8 +10,12 @@ the same math with bf16 ``torch.nn.functional`` ops (cuBLAS + flash SDPA).
 """
 import argparse
 import json
+import pathlib
+import sys
 
 import torch
+
+sys.path.insert(0, str(pathlib.Path(__file__).resolve().parent.parent))
 
 from frankentorch_b200.models.encoder import EncoderGpu, EncoderLayerWeights, LN_EPS
 

@@ -284,9 +284,10 @@ __device__ __forceinline__ TileCoord decode_item(int item, const GemmArgs& p, co
 // fetched by many CTAs at once.  In each comm CTA one thread drives an smem ring: bulk loads
 // (from the peer's shard, or from this rank's own shard) run four pieces ahead of the bulk
 // stores into the local staging buffer; a flag word per piece is published once its store has
-// landed.  With `own_last` the own chunk is copied after the remote ones: the GEMM reads
-// own-shard tiles straight from the shard (second tensor map), the staged copy only serves
-// later consumers of the gathered operand.
+// landed.  With `own_aside` (activation gathers) the ring moves the remote chunks only: the GEMM
+// reads own-shard tiles straight from the shard (second tensor map), and the staged copy of the
+// own chunk, which only serves later consumers of the gathered operand, is made by the other
+// warps of the copy CTAs with plain 16-byte loads and stores while the ring runs.
 __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const CommArgs& c,
                                             int epoch, int cta, bool own_last, const WaitCtx& ctx) {
   uint64_t* full = bars;
@@ -297,10 +298,34 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
   const uint32_t piece = c.sub_bytes < G_COPY_SLOT ? (uint32_t)c.sub_bytes : (uint32_t)G_COPY_SLOT;
   const int pps = (int)(c.sub_bytes / piece);          // pieces per subtile
   const int ppc = spc * pps;                           // pieces per chunk
-  const int n_pieces = ppc * c.world;
-  const int shift = own_last ? ppc : 0;                // visit v -> rotated piece (v + shift) % n
+  const bool own_aside = own_last;
+  // pieces are numbered by distance from this rank: [0, ppc) is the own chunk
+  const int first = own_aside ? ppc : 0;
+  const int n_pieces = ppc * c.world - first;
   const int mine = cta < n_pieces ? (n_pieces - cta + c.comm_ctas - 1) / c.comm_ctas : 0;
-  auto rotated = [&](int i) { return (int)(((long long)cta + (long long)i * c.comm_ctas + shift) % n_pieces); };
+  auto rotated = [&](int i) { return first + (int)(((long long)cta + (long long)i * c.comm_ctas) % n_pieces); };
+  if (own_aside && threadIdx.x >= 96) {
+    // own chunk: shard -> its place in the gathered operand, 8 vectors in flight per thread
+    const long long nvec = (long long)ppc * piece / 16;
+    const uint4* src = reinterpret_cast<const uint4*>(c.src[c.rank]);
+    uint4* dst = reinterpret_cast<uint4*>(c.full + (long long)c.rank * ppc * piece);
+    const long long nthr = (long long)c.comm_ctas * (blockDim.x - 96);
+    const long long t0 = (long long)cta * (blockDim.x - 96) + (threadIdx.x - 96);
+    for (long long v0 = t0; v0 < nvec; v0 += 8 * nthr) {
+      uint4 u[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const long long v = v0 + k * nthr;
+        if (v < nvec) u[k] = __ldg(src + v);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const long long v = v0 + k * nthr;
+        if (v < nvec) dst[v] = u[k];
+      }
+    }
+    return;
+  }
   uint64_t* empty = bars + G_COPY_SLOTS;
   if (threadIdx.x == 0) {
     // loader: peer (or own) memory -> ring slot.  It never waits for a store to land, only for

@@ -317,7 +317,7 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
     int cc = (int)(sms * comm_work / (comm_work + gemm_work) + 0.5);
     if (cc < 12) cc = 12;
     if (cc > 64) cc = 64;
-    if (cd->world == 1) cc = 8;
+    if (cd->world == 1) cc = 32;   // nothing to fetch: the copy CTAs only stage the own chunk
     c.comm_ctas = cc;
   }
   if (c.comm_ctas >= sms) return -7;
