@@ -28,6 +28,7 @@ constexpr int G_THREADS = 64 + 32 * G_EPI_WARPS;
 constexpr int G_MAX_RANKS = 8;
 constexpr int G_COPY_SLOT = 32768;   // bytes per bulk copy of the gather ring
 constexpr int G_COPY_SLOTS = 6;
+constexpr int G_SCATTER_BATCH = 8;   // reduce-scatter tiles per system-scope fence
 constexpr long long G_PEER_WAIT_CYCLES = 4000000000ll;
 
 struct GemmArgs {
@@ -739,6 +740,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     const int c_end = half == 0 ? C_HALF : CHUNKS;
     int acc = 0;
     uint32_t acc_ph = 0;
+    int pend_owner[G_SCATTER_BATCH], pend_tile[G_SCATTER_BATCH], n_pend = 0;   // scatter: unpublished tiles
     for (int item = blockIdx.x; item < total; item += n_compute) {
       const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
       const int sp = t.sp, l = t.l, m_t = t.m_t, n_t = t.n_t;
@@ -790,11 +792,18 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
-        __threadfence_system();
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
-        if (ew == 0 && lane == 0) {
-          const int t_local = n_t * tpc + (m_t - owner * tpc);
-          st_rel_sys(c.arrive[owner] + t_local * c.world + c.rank, epoch);
+        // A system-scope fence waits for every peer store of this thread to be acknowledged
+        // (tens of microseconds under load), so arrival flags are published in batches: one
+        // fence per G_SCATTER_BATCH tiles instead of one per tile.
+        pend_owner[n_pend] = owner;
+        pend_tile[n_pend] = n_t * tpc + (m_t - owner * tpc);
+        if (++n_pend == G_SCATTER_BATCH) {
+          __threadfence_system();
+          asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
+          if (ew == 0 && lane == 0)
+            for (int i = 0; i < n_pend; ++i)
+              st_rel_sys(c.arrive[pend_owner[i]] + pend_tile[i] * c.world + c.rank, epoch);
+          n_pend = 0;
         }
         acc_ph ^= (1u << acc);
         acc ^= 1;
@@ -940,6 +949,13 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       if (lane == 0) mbar_arrive(&tempty[acc]);
       acc_ph ^= (1u << acc);
       acc ^= 1;
+    }
+    if (COMM && c.mode == FTK_COMM_SCATTER_D && n_pend > 0) {      // the last, partial batch of arrival flags
+      __threadfence_system();
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
+      if (ew == 0 && lane == 0)
+        for (int i = 0; i < n_pend; ++i)
+          st_rel_sys(c.arrive[pend_owner[i]] + pend_tile[i] * c.world + c.rank, epoch);
     }
     // reduce-scatter: with the GEMM tiles done, the epilogue warps of every CTA drain the inbox
     if (COMM && c.mode == FTK_COMM_SCATTER_D)
