@@ -52,25 +52,45 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
   const uint4* rr = resid ? reinterpret_cast<const uint4*>(resid + (size_t)row * cols) : nullptr;
   uint4* so = sum_out ? reinterpret_cast<uint4*>(sum_out + (size_t)row * cols) : nullptr;
+  // The first ROW_CACHE vectors of a lane (2048 columns) live in registers: every loop over
+  // them is fully unrolled so the array never spills to local memory, and all loads of the row
+  // are issued before any arithmetic (a lane that loads and reduces one vector at a time sits at
+  // memory latency).  Columns beyond the cache are re-read.  Sums run in ascending vector order
+  // in both parts, so results do not depend on the split.
   uint4 cache[ROW_CACHE];
+  uint4 rcache[ROW_CACHE];
+#pragma unroll
+  for (int c = 0; c < ROW_CACHE; ++c) {
+    const int v = lane + 32 * c;
+    if (v < nvec) {
+      cache[c] = xr[v];
+      if (rr) rcache[c] = rr[v];
+    }
+  }
   float s = 0.f;
-  for (int c = 0, v = lane; v < nvec; ++c, v += 32) {
-    uint4 u = xr[v];
+  auto first_pass = [&](uint4 u, const uint4& r, int v) -> uint4 {
     float f[8];
     unpack8(u, f);
     if (rr) {
       float g[8];
-      unpack8(rr[v], g);
+      unpack8(r, g);
 #pragma unroll
       for (int i = 0; i < 8; ++i) f[i] += g[i];
       u = pack8(f);
       unpack8(u, f);  // statistics are taken on the rounded sum that downstream kernels will read
       if (so) so[v] = u;
     }
-    if (c < ROW_CACHE) cache[c] = u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) s += RMS ? f[i] * f[i] : f[i];
+    return u;
+  };
+#pragma unroll
+  for (int c = 0; c < ROW_CACHE; ++c) {
+    const int v = lane + 32 * c;
+    if (v < nvec) cache[c] = first_pass(cache[c], rcache[c], v);
   }
+  for (int v = lane + 32 * ROW_CACHE; v < nvec; v += 32)
+    first_pass(xr[v], rr ? rr[v] : make_uint4(0u, 0u, 0u, 0u), v);
   s = warp_sum(s);
   float mean = 0.f, rstd;
   const uint4* src = rr ? reinterpret_cast<const uint4*>(so) : xr;
@@ -79,8 +99,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   } else {
     mean = s / cols;
     float q = 0.f;
-    for (int c = 0, v = lane; v < nvec; ++c, v += 32) {
-      uint4 u = (c < ROW_CACHE) ? cache[c] : src[v];
+    auto second_pass = [&](const uint4& u) {
       float f[8];
       unpack8(u, f);
 #pragma unroll
@@ -88,7 +107,11 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
         float d = f[i] - mean;
         q += d * d;
       }
-    }
+    };
+#pragma unroll
+    for (int c = 0; c < ROW_CACHE; ++c)
+      if (lane + 32 * c < nvec) second_pass(cache[c]);
+    for (int v = lane + 32 * ROW_CACHE; v < nvec; v += 32) second_pass(src[v]);
     q = warp_sum(q);
     rstd = rsqrtf(q / cols + eps);
   }
@@ -99,8 +122,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   const uint4* gv = reinterpret_cast<const uint4*>(gamma);
   const uint4* bv = beta ? reinterpret_cast<const uint4*>(beta) : nullptr;
   uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * cols);
-  for (int c = 0, v = lane; v < nvec; ++c, v += 32) {
-    uint4 u = (c < ROW_CACHE) ? cache[c] : src[v];
+  auto write_out = [&](const uint4& u, int v) {
     float f[8], g[8], b[8];
     unpack8(u, f);
     unpack8(__ldg(gv + v), g);
@@ -111,7 +133,11 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
       f[i] = bv ? h + b[i] : h;
     }
     yr[v] = pack8(f);
-  }
+  };
+#pragma unroll
+  for (int c = 0; c < ROW_CACHE; ++c)
+    if (lane + 32 * c < nvec) write_out(cache[c], lane + 32 * c);
+  for (int v = lane + 32 * ROW_CACHE; v < nvec; v += 32) write_out(src[v], v);
 }
 
 // ----------------------------------------------------------------------------- LayerNorm bwd dx
