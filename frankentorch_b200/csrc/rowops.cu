@@ -38,8 +38,9 @@ constexpr int ROW_WARPS = 8;     // rows per CTA
 constexpr int ROW_CACHE = 8;     // 8 x (32 lanes x 8 elems) = 2048 columns kept in registers
 
 // ----------------------------------------------------------------------------- LayerNorm fwd
+constexpr int NF_CACHE = 4;      // forward: 4 x (32 lanes x 8 elems) = 1024 columns kept in registers
 template <bool RMS>
-__global__ void __launch_bounds__(ROW_WARPS * 32)
+__global__ void __launch_bounds__(ROW_WARPS * 32, 4)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ resid,
                 __nv_bfloat16* __restrict__ sum_out, const __nv_bfloat16* __restrict__ gamma,
                 const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
@@ -52,15 +53,15 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
   const uint4* rr = resid ? reinterpret_cast<const uint4*>(resid + (size_t)row * cols) : nullptr;
   uint4* so = sum_out ? reinterpret_cast<uint4*>(sum_out + (size_t)row * cols) : nullptr;
-  // The first ROW_CACHE vectors of a lane (2048 columns) live in registers: every loop over
+  // The first NF_CACHE vectors of a lane (1024 columns) live in registers: every loop over
   // them is fully unrolled so the array never spills to local memory, and all loads of the row
   // are issued before any arithmetic (a lane that loads and reduces one vector at a time sits at
   // memory latency).  Columns beyond the cache are re-read.  Sums run in ascending vector order
   // in both parts, so results do not depend on the split.
-  uint4 cache[ROW_CACHE];
-  uint4 rcache[ROW_CACHE];
+  uint4 cache[NF_CACHE];
+  uint4 rcache[NF_CACHE];
 #pragma unroll
-  for (int c = 0; c < ROW_CACHE; ++c) {
+  for (int c = 0; c < NF_CACHE; ++c) {
     const int v = lane + 32 * c;
     if (v < nvec) {
       cache[c] = xr[v];
@@ -85,11 +86,11 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     return u;
   };
 #pragma unroll
-  for (int c = 0; c < ROW_CACHE; ++c) {
+  for (int c = 0; c < NF_CACHE; ++c) {
     const int v = lane + 32 * c;
     if (v < nvec) cache[c] = first_pass(cache[c], rcache[c], v);
   }
-  for (int v = lane + 32 * ROW_CACHE; v < nvec; v += 32)
+  for (int v = lane + 32 * NF_CACHE; v < nvec; v += 32)
     first_pass(xr[v], rr ? rr[v] : make_uint4(0u, 0u, 0u, 0u), v);
   s = warp_sum(s);
   float mean = 0.f, rstd;
@@ -109,9 +110,9 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
       }
     };
 #pragma unroll
-    for (int c = 0; c < ROW_CACHE; ++c)
+    for (int c = 0; c < NF_CACHE; ++c)
       if (lane + 32 * c < nvec) second_pass(cache[c]);
-    for (int v = lane + 32 * ROW_CACHE; v < nvec; v += 32) second_pass(src[v]);
+    for (int v = lane + 32 * NF_CACHE; v < nvec; v += 32) second_pass(src[v]);
     q = warp_sum(q);
     rstd = rsqrtf(q / cols + eps);
   }
@@ -135,9 +136,9 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
     yr[v] = pack8(f);
   };
 #pragma unroll
-  for (int c = 0; c < ROW_CACHE; ++c)
+  for (int c = 0; c < NF_CACHE; ++c)
     if (lane + 32 * c < nvec) write_out(cache[c], lane + 32 * c);
-  for (int v = lane + 32 * ROW_CACHE; v < nvec; v += 32) write_out(src[v], v);
+  for (int v = lane + 32 * NF_CACHE; v < nvec; v += 32) write_out(src[v], v);
 }
 
 // ----------------------------------------------------------------------------- LayerNorm bwd dx
