@@ -27,6 +27,9 @@ def _ref(q, k, v, causal):
     (1, 200, 2, 64, True),      # ragged sequence
     (1, 256, 2, 128, True),
     (1, 384, 1, 128, False),
+    (1, 200, 2, 64, False),     # ragged, non-causal (encoder inference)
+    (1, 328, 1, 128, True),     # ragged, head_dim 128
+    (2, 1024, 2, 64, True),     # eight key blocks: every ring slot is reused
 ])
 def test_attention_fwd_bwd(cuda_device, B, S, H, hd, causal):
     from frankentorch_b200.ops import kernels as k
