@@ -41,6 +41,7 @@ ENV_FLAGS: Dict[str, EnvFlag] = {f.name: f for f in (
     EnvFlag("FT_DP_IMPL", "fused", str, "data-parallel gradient path: fused (peer memory) or nccl"),
     EnvFlag("FT_COMM_CTAS", 20, int, "copy CTAs of the gather-fused GEMMs"),
     EnvFlag("FT_MODE", "strict", str, "execution mode of new sessions: strict or hardened"),
+    EnvFlag("FT_ENC_CHUNK", 8, int, "encoder inference: layers per CUDA graph (models/encoder.py)"),
 )}
 
 _cache: Dict[str, Any] = {}
