@@ -56,6 +56,7 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--log-jsonl", default="", help="append a structured ft-conformance-log-v1 record of this run")
     ap.add_argument("--parallelism", default="", choices=["", "dp", "tp", "zero3", "ep"],
                     help="default: the one the named config asks for")
     ap.add_argument("--dp-impl", default=os.environ.get("FT_DP_IMPL", "fused"), choices=["fused", "nccl"],
@@ -341,6 +342,10 @@ def main():
         }
     if rank == 0:
         print(json.dumps(out))
+        if args.log_jsonl:
+            from frankentorch_b200.utils.metrics import training_log_record
+            with open(args.log_jsonl, "a") as f:
+                f.write(json.dumps(training_log_record(out), sort_keys=True) + "\n")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -107,3 +107,36 @@ def gpt_step_flops(n_layer: int, d: int, ff: int, vocab: int, seq: int, tokens: 
     per_tok = n_layer * (2 * d * 3 * d + 2 * d * d + 2 * 2 * d * ff) + 2 * d * vocab
     attn = n_layer * 2 * 2 * seq * d * (0.5 if causal else 1.0)
     return 3.0 * tokens * (per_tok + attn)
+
+
+def training_log_record(bench_line: Dict, *, mode: str = "strict", seed: int = 1234,
+                        roofline: Optional[Dict[str, float]] = None) -> Dict:
+    """One ``ft-conformance-log-v1`` record for a training benchmark: the 13 required fields of the
+    structured log contract (artifacts/phase2c/TEST_LOG_CONTRACT_V1.md) plus the training metrics
+    (tokens/s max over ranks, step-time p50 / p99, roofline fraction per fused path)."""
+    import time
+
+    from ..conformance.runner import LOG_SCHEMA, env_fingerprint
+    cfg = bench_line.get("config", {})
+    scenario = f"train/{mode}:{cfg.get('model', '?')}/{cfg.get('parallelism', '?')}"
+    n = int(bench_line.get("n_gpus", 1))
+    launch = "python bench.py" if n == 1 else (
+        f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {n} --master-addr 127.0.0.1 bench.py")
+    return {
+        "schema_version": LOG_SCHEMA, "ts_unix_ms": int(time.time() * 1000), "suite_id": "training",
+        "scenario_id": scenario, "fixture_id": "synthetic-uniform-tokens", "packet_id": "FT-B200-TRAIN",
+        "mode": mode, "seed": int(seed), "env_fingerprint": env_fingerprint(),
+        "artifact_refs": ["bench.py"],
+        "replay_command": f"{launch} --gpus {n} --model {cfg.get('model', 'gpt2-small')} "
+                          f"--steps {bench_line.get('steps', 20)} --warmup {bench_line.get('warmup', 5)}",
+        "outcome": "pass" if bench_line.get("value", 0) > 0 else "fail",
+        "reason_code": "ok" if bench_line.get("value", 0) > 0 else "no_throughput",
+        "metrics": {
+            "tokens_per_s_max_over_ranks": bench_line.get("value"),
+            "ms_per_step": bench_line.get("ms_per_step"),
+            "step_ms_p50": bench_line.get("step_ms_p50"), "step_ms_p99": bench_line.get("step_ms_p99"),
+            "e2e_tokens_per_s": (bench_line.get("e2e") or {}).get("value"),
+            "gpu_launches": bench_line.get("gpu_launches"), "n_gpus": n,
+            "clocks": bench_line.get("clocks"), "roofline_fraction": dict(roofline or {}),
+        },
+    }

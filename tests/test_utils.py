@@ -133,3 +133,18 @@ def test_stage_profile_on_cpu():
         pass
     out = prof.summary()
     assert out["a"]["n"] == 2 and out["a"]["ms"] >= 0.0
+
+
+def test_training_log_record_has_the_contract_fields():
+    line = {"value": 638000.0, "ms_per_step": 12.8, "step_ms_p50": 12.8, "step_ms_p99": 12.9, "n_gpus": 8, "steps": 20,
+            "warmup": 5, "gpu_launches": 5600, "e2e": {"value": 636000.0}, "clocks": {"sm_mhz": 1965.0},
+            "config": {"model": "gpt2-small", "parallelism": "dp8"}}
+    rec = metrics.training_log_record(line, roofline={"gemm_reduce_scatter": 0.5})
+    required = ["schema_version", "ts_unix_ms", "suite_id", "scenario_id", "fixture_id", "packet_id", "mode", "seed",
+                "env_fingerprint", "artifact_refs", "replay_command", "outcome", "reason_code"]
+    assert all(k in rec for k in required) and rec["artifact_refs"]
+    assert rec["schema_version"] == "ft-conformance-log-v1" and rec["outcome"] == "pass"
+    assert rec["scenario_id"] == "train/strict:gpt2-small/dp8"
+    assert "--nproc-per-node 8" in rec["replay_command"] and "--gpus 8" in rec["replay_command"]
+    assert rec["metrics"]["step_ms_p99"] == 12.9 and rec["metrics"]["roofline_fraction"] == {"gemm_reduce_scatter": 0.5}
+    assert metrics.training_log_record({"value": 0})["outcome"] == "fail"
