@@ -1,4 +1,4 @@
-"""Pipeline parallelism: a GPipe schedule over point-to-point sends between consecutive stages.
+"""Pipeline parallelism: GPipe and 1F1B schedules over point-to-point sends between consecutive stages.
 
 The reference has no pipeline parallelism; this module only adds the scheduling and the
 activation / gradient hand-off, every stage runs on the Deterministic Autograd Contract tape
@@ -70,46 +70,54 @@ class GPipeStage:
     def step(self, *, n_micro: int, micro_inputs: Optional[List[torch.Tensor]] = None,
              targets: Optional[List[torch.Tensor]] = None, in_shape: Optional[Sequence[int]] = None,
              out_shape: Optional[Sequence[int]] = None, dtype: torch.dtype = torch.float64,
-             device: str = "cpu") -> Optional[float]:
+             device: str = "cpu", schedule: str = "gpipe") -> Optional[float]:
         """Run forward and backward of ``n_micro`` micro-batches; returns the mean loss on the
-        last stage (None elsewhere).  Parameter gradients are left in the tape's accumulators."""
+        last stage (None elsewhere).  Parameter gradients are left in the tape's accumulators.
+
+        ``schedule``: ``"gpipe"`` runs every forward, then the backwards from the last micro-batch
+        to the first; ``"1f1b"`` runs ``world - 1 - rank`` warm-up forwards, then alternates one
+        forward with one backward (micro-batches in ascending order) and drains the remaining
+        backwards, so at most ``world - rank`` micro-batches are live on a stage.  Both orders are
+        fixed, hence replayable; they differ in the order parameter gradients are summed."""
+        if schedule not in ("gpipe", "1f1b"):
+            raise ValueError(f"unknown pipeline schedule {schedule!r}")
         tape, M = self.tape, n_micro
         prev, nxt = self._peer(self.rank - 1) if not self.first else None, \
             self._peer(self.rank + 1) if not self.last else None
-        # ---------------------------------------------------------------- forward
-        recv_bufs, recv_req = [], []
+        # every receive of the step is posted up front; tags separate micro-batches and directions
+        recv_bufs, recv_req, grad_bufs, grad_req = [], [], [], []
         if not self.first:
             for m in range(M):
                 buf = torch.empty(tuple(in_shape), dtype=dtype, device=device)
                 recv_bufs.append(buf)
                 recv_req.append(dist.irecv(buf, src=prev, group=self.group, tag=m))
-        x_ids, y_ids, loss_ids, send_req = [], [], [], []
-        for m in range(M):
+        if not self.last:
+            for m in range(M):
+                buf = torch.empty(tuple(out_shape), dtype=dtype, device=device)
+                grad_bufs.append(buf)
+                grad_req.append(dist.irecv(buf, src=nxt, group=self.group, tag=1000 + m))
+        x_ids, y_ids, loss_ids = [None] * M, [None] * M, [None] * M
+        pending = []
+        total = [0.0]
+        self.max_live = live = 0
+
+        def forward(m: int) -> None:
             if self.first:
                 x = tape.leaf(micro_inputs[m], requires_grad=False)
             else:
                 recv_req[m].wait()
                 x = tape.leaf(recv_bufs[m], requires_grad=True)
             y = self.stage_fn(tape, x, m)
-            x_ids.append(x)
-            y_ids.append(y)
+            x_ids[m], y_ids[m] = x, y
             if self.last:
-                loss_ids.append(self.loss_fn(tape, y, targets[m], m))
+                loss_ids[m] = self.loss_fn(tape, y, targets[m], m)
             else:
-                send_req.append(dist.isend(tape.value(y).detach().contiguous(), dst=nxt, group=self.group, tag=m))
-        # ---------------------------------------------------------------- backward
-        grad_bufs, grad_req = [], []
-        if not self.last:
-            for m in range(M):
-                buf = torch.empty(tuple(out_shape), dtype=dtype, device=device)
-                grad_bufs.append(buf)
-                grad_req.append(dist.irecv(buf, src=nxt, group=self.group, tag=1000 + m))
-        back_req = []
-        total = 0.0
-        for m in reversed(range(M)):
+                pending.append(dist.isend(tape.value(y).detach().contiguous(), dst=nxt, group=self.group, tag=m))
+
+        def backward(m: int) -> None:
             if self.last:
                 root = loss_ids[m]
-                total += float(tape.value(root))
+                total[0] += float(tape.value(root))
                 seed = torch.full_like(tape.value(root), 1.0 / M, dtype=tape.grad_dtype or tape.value(root).dtype)
             else:
                 grad_req[m].wait()
@@ -120,7 +128,25 @@ class GPipeStage:
             report = tape.backward(root, BackwardOptions(retain_graph=True), seed=seed)
             if not self.first:
                 gx = report.gradient(x_ids[m])
-                back_req.append(dist.isend(gx.to(dtype).contiguous(), dst=prev, group=self.group, tag=1000 + m))
-        for r in send_req + back_req:
+                pending.append(dist.isend(gx.to(dtype).contiguous(), dst=prev, group=self.group, tag=1000 + m))
+
+        if schedule == "gpipe":
+            order = [("f", m) for m in range(M)] + [("b", m) for m in reversed(range(M))]
+        else:
+            warm = min(self.world - 1 - self.rank, M)
+            order = [("f", m) for m in range(warm)]
+            for k in range(M - warm):
+                order += [("f", warm + k), ("b", k)]
+            order += [("b", m) for m in range(M - warm, M)]
+        self.last_order = order
+        for kind, m in order:
+            if kind == "f":
+                forward(m)
+                live += 1
+                self.max_live = max(self.max_live, live)
+            else:
+                backward(m)
+                live -= 1
+        for r in pending:
             r.wait()
-        return total / M if self.last else None
+        return total[0] / M if self.last else None
