@@ -284,6 +284,20 @@ class DataLoader:
         """Start a new epoch; a shuffling loader draws the next permutation on the next batch."""
         self._order, self._cursor = None, 0
 
+    def state_dict(self) -> Dict:
+        """Position of the loader: LCG state, cursor and the current epoch's order (plain values),
+        so a resumed job draws the same remaining batches and the same later permutations."""
+        return {"rng_state": int(self._rng.state), "cursor": int(self._cursor),
+                "order": None if self._order is None else [int(i) for i in self._order]}
+
+    def load_state_dict(self, sd: Dict) -> None:
+        order = sd.get("order")
+        if order is not None and sorted(order) != sorted(self._base):
+            raise DataError("the saved order does not index this loader's dataset")
+        self._rng.state = int(sd["rng_state"])
+        self._cursor = int(sd["cursor"])
+        self._order = None if order is None else [int(i) for i in order]
+
     def num_batches(self) -> int:
         bs, n = self.config.batch_size, len(self._base)
         if bs == 0:

@@ -108,8 +108,7 @@ def job_state(*, scheduler=None, session=None, loader=None, step: int = 0, extra
     if session is not None:
         out["prng"] = [int(session.rng.state[i]) for i in range(4)]
     if loader is not None:
-        out["loader"] = {"rng_state": int(loader._rng.state), "cursor": int(loader._cursor),
-                         "order": None if loader._order is None else [int(i) for i in loader._order]}
+        out["loader"] = loader.state_dict()
     return out
 
 
@@ -128,10 +127,7 @@ def restore_job_state(state: Dict, *, scheduler=None, session=None, loader=None)
         for i, w in enumerate(words):
             session.rng.state[i] = int(w) & ((1 << 64) - 1)
     if loader is not None and "loader" in state:
-        ld = state["loader"]
-        loader._rng.state = int(ld["rng_state"])
-        loader._cursor = int(ld["cursor"])
-        loader._order = None if ld["order"] is None else [int(i) for i in ld["order"]]
+        loader.load_state_dict(state["loader"])
     return int(state.get("step", 0))
 
 
