@@ -1,7 +1,9 @@
 """In-tree build of the native libraries.
 
 Two shared objects are produced next to the sources (they are git-ignored build
-artefacts):
+artefacts, together with ``lib/build_manifest.json``, which records the sha256 of the
+sources and flags each one was built from; a library is rebuilt when that differs from
+what is on disk now, whatever the modification times say):
 
 * ``lib/libftk_sm100.so``  - the hand-written sm_100a CUDA kernels (plain C ABI,
   no PyTorch dependency), compiled with ``nvcc -gencode arch=compute_100a,code=sm_100a``.
@@ -13,6 +15,9 @@ artefacts):
 """
 from __future__ import annotations
 
+import fcntl
+import hashlib
+import json
 import os
 import shutil
 import subprocess
@@ -39,11 +44,38 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found; set NVCC=/path/to/nvcc")
 
 
-def _newer(src_list, target: Path) -> bool:
-    if not target.exists():
-        return True
-    t = target.stat().st_mtime
-    return any(Path(s).stat().st_mtime > t for s in src_list)
+def _digest(paths, extra=()) -> str:
+    """sha256 over the contents of ``paths`` (in sorted order) and the strings in ``extra``."""
+    h = hashlib.sha256()
+    for x in extra:
+        h.update(str(x).encode())
+        h.update(b"\0")
+    for p in sorted(map(str, paths)):
+        h.update(os.path.basename(p).encode())
+        h.update(b"\0")
+        with open(p, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _manifest() -> dict:
+    try:
+        return json.loads((LIB / "build_manifest.json").read_text())
+    except Exception:
+        return {}
+
+
+def _save_manifest(m: dict) -> None:
+    (LIB / "build_manifest.json").write_text(json.dumps(m, indent=1, sort_keys=True))
+
+
+def _stale(key: str, digest: str, target: Path, manifest: dict) -> bool:
+    """A target is rebuilt when it is missing or was built from different source bytes or flags.
+
+    Modification times are not consulted: a binary that is newer than its sources but was built
+    from other sources (a checkout, a copied tree) would otherwise be used as is.
+    """
+    return (not target.exists()) or manifest.get(key) != digest
 
 
 def _run(cmd):
@@ -69,10 +101,23 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
     srcs = kernel_sources()
     nvcc = _nvcc()
+    man = _manifest()
+    digests = {(s.stem + ".o"): _digest([s] + headers, NVCC_FLAGS) for s in srcs}
+    so_digest = _digest([], sorted(digests.values()))
+    if not force and not _stale(out.name, so_digest, out, man):
+        return out          # the library on disk was built from exactly these sources and flags
+    with _Lock():
+        return _build_kernels_locked(force, verbose, out, srcs, nvcc, digests, so_digest)
+
+
+def _build_kernels_locked(force, verbose, out, srcs, nvcc, digests, so_digest) -> Path:
+    man = _manifest()
+    if not force and not _stale(out.name, so_digest, out, man):
+        return out          # another process built it while this one waited for the lock
     jobs = []
     for s in srcs:
         o = OBJ / (s.stem + ".o")
-        if force or _newer([s] + headers, o):
+        if force or _stale(o.name, digests[o.name], o, man):
             jobs.append([nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(s), "-o", str(o)])
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
@@ -80,8 +125,11 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
                 if verbose and log.strip():
                     print(log)
     objs = [OBJ / (s.stem + ".o") for s in srcs]
-    if force or jobs or _newer(objs, out):
-        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-lcudart"])
+    _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-lcudart"])
+    man = _manifest()
+    man.update(digests)
+    man[out.name] = so_digest
+    _save_manifest(man)
     return out
 
 
@@ -94,10 +142,42 @@ def build_core(force: bool = False) -> Path:
     headers = list((CSRC / "core").glob("*.h")) + list((CSRC / "core").glob("*.hpp"))
     if not srcs:
         return out
-    if force or _newer(srcs + headers, out):
-        cxx = os.environ.get("CXX", "g++")
-        _run([cxx, *CXX_FLAGS, "-shared", "-o", str(out), *map(str, srcs), "-lpthread"])
+    man = _manifest()
+    d = _digest(srcs + headers, CXX_FLAGS)
+    if force or _stale(out.name, d, out, man):
+        with _Lock():
+            if force or _stale(out.name, d, out, _manifest()):
+                cxx = os.environ.get("CXX", "g++")
+                _run([cxx, *CXX_FLAGS, "-shared", "-o", str(out), *map(str, srcs), "-lpthread"])
+                man = _manifest()
+                man[out.name] = d
+                _save_manifest(man)
     return out
+
+
+def is_current() -> bool:
+    """True when both libraries exist and were built from the sources now on disk."""
+    man = _manifest()
+    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    ds = sorted(_digest([s] + headers, NVCC_FLAGS) for s in kernel_sources())
+    k_ok = (LIB / "libftk_sm100.so").exists() and man.get("libftk_sm100.so") == _digest([], ds)
+    ch = list((CSRC / "core").glob("*.h")) + list((CSRC / "core").glob("*.hpp"))
+    c_ok = (LIB / "libftcore.so").exists() and man.get("libftcore.so") == _digest(core_sources() + ch, CXX_FLAGS)
+    return k_ok and c_ok
+
+
+class _Lock:
+    """Inter-process lock: the ranks of one job may all find a stale library at import time."""
+
+    def __enter__(self):
+        LIB.mkdir(exist_ok=True)
+        self.f = open(LIB / ".build.lock", "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
 
 
 def build_all(force: bool = False, verbose: bool = False):

@@ -178,7 +178,11 @@ class GradTargets:
         return n.grad_buffer, n.grad_buffer_filled
 
     def mark_accumulated(self, input_index: int) -> None:
-        self._tape.nodes[self._node.inputs[input_index]].grad_buffer_filled = True
+        nid = self._node.inputs[input_index]
+        self._tape.nodes[nid].grad_buffer_filled = True
+        fn = self._tape.leaf_grad_written_fn
+        if fn is not None:
+            fn(nid)
 
 
 class TensorNode:
@@ -227,6 +231,10 @@ class TensorTape:
         # optional profiler hook: a callable returning a context manager, entered around every
         # backward rule (NVTX ranges per tape node, see utils/profiling.py)
         self.range_fn: Optional[Callable[[str], object]] = None
+        # optional observer, called with the leaf id each time a rule has written that leaf's
+        # gradient in place (the kernel is already on the stream); the data-parallel engine uses it
+        # to start a bucket's reduction as soon as its last gradient is in
+        self.leaf_grad_written_fn: Optional[Callable[[int], None]] = None
         self.last_plan_cache: Dict[Tuple[int, int], Tuple] = {}
 
     def __del__(self):

@@ -12,6 +12,7 @@ namespace {
 
 constexpr int kRowsPerBlock = 64;   // rows summed by one thread before the cross-block pass
 constexpr int kMaxDevices = 64;
+constexpr long long kMaxGridY = 65535;
 
 // Scratch for the per-row-block partial sums.  In host code this name is only a stand-in
 // for the symbol; its device address comes from cudaGetSymbolAddress below.
@@ -75,27 +76,37 @@ extern "C" int ftk_colsum_bf16_noalloc(const void* x, float* out, int rows, int 
                                        int accumulate, void* stream) {
   if (!x || !out || rows <= 0 || cols <= 0 || (cols % 2) || (ld % 2) || ld < cols)
     return FTK_NOALLOC_ERR_BAD_ARG;
-  const long long nblk = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  // the kernel reads x as 32-bit bf16 pairs and out as fp32 words: a pointer that is not 4-byte
+  // aligned (a bf16 view that starts at an odd element) would fault on the device, so refuse it here
+  if ((reinterpret_cast<uintptr_t>(x) & 3u) || (reinterpret_cast<uintptr_t>(out) & 3u))
+    return FTK_NOALLOC_ERR_BAD_ARG;
+  const long long nblk = ((long long)rows + kRowsPerBlock - 1) / kRowsPerBlock;
   if (nblk * (long long)cols > (long long)FTK_COLSUM_NOALLOC_MAX_FLOATS)
     return FTK_NOALLOC_ERR_TOO_LARGE;
+  if (nblk > kMaxGridY) return FTK_NOALLOC_ERR_TOO_LARGE;   // row blocks ride on grid.y
   float* scratch = scratch_for_current_device();
   if (!scratch) return FTK_NOALLOC_ERR_SETUP;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  dim3 grid((cols / 2 + 127) / 128, (unsigned)nblk);
+  dim3 grid((unsigned)((cols / 2 + 127) / 128), (unsigned)nblk);
   colsum_partial_noalloc<<<grid, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), scratch, rows,
                                               cols, ld);
+  // a first launch that was refused must not be followed by a kernel that folds stale scratch into out
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return (int)e;
   colsum_final_noalloc<<<(cols + 255) / 256, 256, 0, s>>>(scratch, out, cols, (int)nblk, accumulate);
-  return (int)cudaGetLastError();
+  return (int)cudaPeekAtLastError();
 }
 
 extern "C" const char* ftk_noalloc_strerror(int code) {
   switch (code) {
     case FTK_NOALLOC_OK: return "ok";
     case FTK_NOALLOC_ERR_BAD_ARG:
-      return "ftk_colsum_bf16_noalloc: bad argument (null pointer, non-positive extent, odd cols or ld, ld < cols)";
+      return "ftk_colsum_bf16_noalloc: bad argument (null pointer, non-positive extent, odd cols or ld, ld < cols, "
+             "or x / out not 4-byte aligned)";
     case FTK_NOALLOC_ERR_TOO_LARGE:
       return "ftk_colsum_bf16_noalloc: ceil(rows/64)*cols exceeds the built-in scratch of 1048576 floats (4 MiB); "
-             "use ftk_colsum_bf16 with a caller-provided scratch buffer for larger problems";
+             "or ceil(rows/64) exceeds 65535 row blocks; use ftk_colsum_bf16 with a caller-provided scratch buffer "
+             "for larger problems";
     case FTK_NOALLOC_ERR_SETUP:
       return "ftk_colsum_bf16_noalloc: could not resolve the device address of the built-in scratch array";
     default: return "ftk_colsum_bf16_noalloc: CUDA error (see cudaGetErrorString)";

@@ -27,6 +27,7 @@ enum : int {
   FT_ERR_WAIT_PEER = 5,       // a flag owned by another rank never reached the expected value
   FT_ERR_WAIT_SOFTMAX = 6,    // attention: MMA issuer waited for probabilities that never arrived
   FT_ERR_BAD_ARG = 7,
+  FT_ERR_WAIT_WARPS = 8,      // a barrier among a CTA's warps was abandoned by one of them (abort elsewhere)
 };
 
 // One second at ~1.9 GHz; legitimate waits inside one kernel are far shorter.
@@ -112,6 +113,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       }
     }
   }
+}
+
+// Barrier among the warps that share `bar` (initialised with one arrival per warp), with the
+// same bounded wait as everything else: a warp that left through an abort never arrives, and the
+// others give up when they see the abort flag or run out of budget, where a named hardware
+// barrier (`bar.sync`) would keep them waiting for ever.  Release/acquire at CTA scope like
+// `bar.sync`; `phase` is the caller's running parity of this barrier.
+__device__ __forceinline__ bool warps_barrier(uint64_t* bar, uint32_t& phase, int lane, const WaitCtx& c) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+  const bool ok = mbar_wait(bar, phase, c, FT_ERR_WAIT_WARPS);
+  phase ^= 1u;
+  return ok;
 }
 
 // ----------------------------------------------------------------------------

@@ -55,6 +55,9 @@ typedef struct FtkGemmDesc {
 int* ftk_status_word(void);               // device pointer (allocated on first use, per device)
 int ftk_read_status(int reset);           // synchronises the device; returns the status word
 int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream);
+// Which kernel ftk_gemm_bf16 would launch: *bn = 128 / 192 / 256 (one CTA per 128 x bn tile) or
+// 512 (CTA-pair kernel, 256 x 256 tiles, cta_group::2); *splits = split-K factor.  No launch.
+int ftk_gemm_plan(const FtkGemmDesc* g, int* bn, int* splits);
 
 // ---- GEMM fused with a collective over NVLink peer memory --------------------------------
 // One kernel: `comm_ctas` CTAs move shards / reduce partials while the rest run the GEMM.
@@ -238,6 +241,50 @@ int ftk_adamw_dev(float* master, void* shadow_bf16, const float* grad, float* m,
                   const float* hyper, float beta1, float beta2, float eps, float weight_decay,
                   void* stream);
 int ftk_fill_f32(float* x, long long n, float v, void* stream);
+#ifdef __cplusplus
+}
+#endif
+
+// ---- bucketed data-parallel optimizer step over peer memory (dp_fused.cu) --------------------
+#ifdef __cplusplus
+extern "C" {
+#endif
+#define FTK_DP_MAX_RANKS 16
+#define FTK_DP_MAX_BUCKETS 64
+// One bucket of the flat parameter arena (all counts in elements).  `shard` (a multiple of 8) is
+// the number of elements of the bucket each rank owns: rank r owns [lo + r*shard, lo + (r+1)*shard)
+// clipped to hi.  `off` is where that shard starts in the rank-local shard arrays (fp32 master,
+// moments, reduced gradient); the bucket's W inbox slots start at world*off in the inbox.
+typedef struct {
+  long long lo, hi, shard, off;
+} FtkDpBucket;
+// This rank's view of the job.  inbox / params / flags / slots: `world` pointers each, entry r
+// being rank r's buffer mapped into this process (entry `rank` is the local buffer).
+//   flags : u64 [3][FTK_DP_MAX_BUCKETS][FTK_DP_MAX_RANKS], zero-initialised, never cleared
+//   slots : fp32 [FTK_DP_MAX_RANKS]
+//   inbox : wire type (bf16, or fp32 when wire_fp32) [world * sum of shards]
+// Local device memory: buckets (table of n_buckets entries), gshard fp32 [sum of shards],
+// partial fp32 [n_buckets * n_ctas], counters u32 [2 * FTK_DP_MAX_BUCKETS] (zero-initialised),
+// seq (step sequence number, advanced by ftk_dp_begin_step), ok_word (1 = step healthy).
+typedef struct {
+  void* const* inbox;
+  void* const* params;
+  void* const* flags;
+  void* const* slots;
+  const FtkDpBucket* buckets;
+  int rank, world, n_buckets, n_ctas, wire_fp32;
+  float* gshard;
+  float* partial;
+  unsigned int* counters;
+  long long* seq;
+  int* ok_word;
+} FtkDpComm;
+int ftk_dp_begin_step(const FtkDpComm* c, void* stream);
+int ftk_dp_bucket_reduce(const FtkDpComm* c, int bucket, const float* grads, void* stream);
+int ftk_dp_norm(const FtkDpComm* c, float max_norm, float* hyper, float* norm_out, void* stream);
+int ftk_dp_update(const FtkDpComm* c, int b0, int b1, float* master, float* m, float* v, const float* hyper,
+                  float beta1, float beta2, float eps, float weight_decay, int n_ctas, void* stream);
+int ftk_dp_wait_params(const FtkDpComm* c, int b0, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -23,7 +23,11 @@
 //     GPU that loads the library until the process exits;
 //     ceil(rows / 64) * cols must not exceed it, otherwise the call returns
 //     FTK_NOALLOC_ERR_TOO_LARGE and launches nothing
-//     (ftk_noalloc_strerror() gives the message);
+//     (ftk_noalloc_strerror() gives the message); ceil(rows / 64) itself must not exceed
+//     65535 (the row blocks are one grid dimension), same error;
+//   * x and out must be 4-byte aligned (x is read as pairs of bf16, out as fp32 words): a
+//     bf16 view that starts at an odd element is refused with FTK_NOALLOC_ERR_BAD_ARG
+//     before anything is launched, because on the device it would be a misaligned access;
 //   * the first call on each device looks up the scratch array's device address
 //     (cudaGetSymbolAddress) and caches it; make that first call before starting
 //     any stream capture on that device;
@@ -43,8 +47,8 @@ extern "C" {
 
 enum {
   FTK_NOALLOC_OK = 0,
-  FTK_NOALLOC_ERR_BAD_ARG = -2,      // null pointer, non-positive extent, odd cols/ld
-  FTK_NOALLOC_ERR_TOO_LARGE = -20,   // ceil(rows/64)*cols exceeds the scratch capacity
+  FTK_NOALLOC_ERR_BAD_ARG = -2,      // null pointer, non-positive extent, odd cols/ld, x/out not 4-byte aligned
+  FTK_NOALLOC_ERR_TOO_LARGE = -20,   // ceil(rows/64)*cols exceeds the scratch capacity, or > 65535 row blocks
   FTK_NOALLOC_ERR_SETUP = -21,       // the scratch symbol's address could not be resolved
 };
 

@@ -400,12 +400,13 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
 // ------------------------------------------------------------------ ordered reduce
 // Tile (n_t, m_in) of this rank's chunk: out = sum over source ranks (ascending) of the bf16
 // partials in the local inbox, + bias, + residual, (+ previous output).  Run by `nthr` threads
-// of a CTA (thread index `tid`), which synchronise on named barrier 1; tiles are dealt round
-// robin over `n_ctas` CTAs.  Every compute CTA calls this after its last GEMM tile, so the
+// of a CTA (thread index `tid`), which synchronise on the abort-aware warp barrier `wbar` (one
+// arrival per participating warp); tiles are dealt round robin over `n_ctas` CTAs.  Every compute CTA calls this after its last GEMM tile, so the
 // whole GPU's bandwidth drains the inbox.
 template <int BN>
 __device__ __forceinline__ void comm_reduce(const GemmArgs& p, const CommArgs& c, int epoch, int cta,
-                                            int n_ctas, int tid, int nthr, const WaitCtx& ctx) {
+                                            int n_ctas, int tid, int nthr, const WaitCtx& ctx,
+                                            uint64_t* wbar, uint32_t& wbar_ph) {
   const int tpc = c.chunk_rows / G_BM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int n_tiles = tpc * tiles_n;
@@ -414,8 +415,7 @@ __device__ __forceinline__ void comm_reduce(const GemmArgs& p, const CommArgs& c
   constexpr int U = 4;                                  // vectors in flight per thread and source
   for (int t = cta; t < n_tiles; t += n_ctas) {
     if (tid < c.world) flag_wait<true>(c.arrive[c.rank] + t * c.world + tid, epoch, ctx);
-    asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory");
-    if (aborted(ctx)) return;
+    if (!warps_barrier(wbar, wbar_ph, tid & 31, ctx) || aborted(ctx)) return;
     const int n_t = t / tpc, m_in = t % tpc;
     const int n_base = n_t * BN;
     const int cols = min(BN, p.N - n_base);            // multiple of 8
@@ -520,6 +520,9 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
+  uint64_t* wbar = tempty + 3;            // barrier among the epilogue warps (all warps of a reduce CTA)
+  static_assert((2 * Cfg::STAGES + 6) * 8 <= 256, "barrier space");
+  uint32_t wbar_ph = 0;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -546,6 +549,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         mbar_init(&tempty[i], G_EPI_WARPS);
       }
     }
+    mbar_init(wbar, comm_cta ? G_THREADS / 32 : G_EPI_WARPS);
     *abort_f = 0;
     fence_mbar_init();
   }
@@ -561,7 +565,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     if (COMM) {
       const int cta = (int)blockIdx.x - n_compute;
       if (c.mode == FTK_COMM_SCATTER_D)
-        comm_reduce<BN>(p, c, epoch, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, G_THREADS, ctx);
+        comm_reduce<BN>(p, c, epoch, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, G_THREADS, ctx, wbar,
+                        wbar_ph);
       else
         comm_gather(smem, bars, c, epoch, cta,
                     /*own_last=*/c.mode == FTK_COMM_GATHER_A, ctx);
@@ -741,12 +746,16 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     int acc = 0;
     uint32_t acc_ph = 0;
     int pend_owner[G_SCATTER_BATCH], pend_tile[G_SCATTER_BATCH], n_pend = 0;   // scatter: unpublished tiles
+    bool epi_ok = true;   // false once this warp gave up a wait: it then skips every later barrier
     for (int item = blockIdx.x; item < total; item += n_compute) {
       const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
       const int sp = t.sp, l = t.l, m_t = t.m_t, n_t = t.n_t;
       const int l0 = l % p.L0, l1 = l / p.L0;
       const bool empty_split = (sp * kb_per_split >= kblocks_all);
-      if (!mbar_wait(&tfull[acc], (acc_ph >> acc) & 1u, ctx, FT_ERR_WAIT_TMEM_FULL)) break;
+      if (!mbar_wait(&tfull[acc], (acc_ph >> acc) & 1u, ctx, FT_ERR_WAIT_TMEM_FULL)) {
+        epi_ok = false;
+        break;
+      }
       tc_fence_after();
       const long long row = (long long)m_t * G_BM + row_in_tile;
       if (COMM && c.mode == FTK_COMM_SCATTER_D) {
@@ -799,7 +808,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         pend_tile[n_pend] = n_t * tpc + (m_t - owner * tpc);
         if (++n_pend == G_SCATTER_BATCH) {
           __threadfence_system();
-          asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
+          if (!warps_barrier(wbar, wbar_ph, lane, ctx)) {
+            epi_ok = false;
+            break;
+          }
           if (ew == 0 && lane == 0)
             for (int i = 0; i < n_pend; ++i)
               st_rel_sys(c.arrive[pend_owner[i]] + pend_tile[i] * c.world + c.rank, epoch);
@@ -950,17 +962,19 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       acc_ph ^= (1u << acc);
       acc ^= 1;
     }
-    if (COMM && c.mode == FTK_COMM_SCATTER_D && n_pend > 0) {      // the last, partial batch of arrival flags
+    // A warp that gave up a wait (epi_ok false) goes straight to the teardown: its siblings are
+    // at, or will reach, a bounded warps_barrier and leave the same way once they see the abort flag.
+    if (COMM && c.mode == FTK_COMM_SCATTER_D && epi_ok && n_pend > 0) {   // the last, partial batch of flags
       __threadfence_system();
-      asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
-      if (ew == 0 && lane == 0)
+      if (!warps_barrier(wbar, wbar_ph, lane, ctx)) epi_ok = false;
+      if (epi_ok && ew == 0 && lane == 0)
         for (int i = 0; i < n_pend; ++i)
           st_rel_sys(c.arrive[pend_owner[i]] + pend_tile[i] * c.world + c.rank, epoch);
     }
     // reduce-scatter: with the GEMM tiles done, the epilogue warps of every CTA drain the inbox
-    if (COMM && c.mode == FTK_COMM_SCATTER_D)
+    if (COMM && c.mode == FTK_COMM_SCATTER_D && epi_ok && !aborted(ctx))
       comm_reduce<BN>(p, c, epoch, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x - 64,
-                      32 * G_EPI_WARPS, ctx);
+                      32 * G_EPI_WARPS, ctx, wbar, wbar_ph);
   }
 
   // ---------------------------------------------------------------- teardown

@@ -104,27 +104,39 @@ int ftk_make_tmap_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint6
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-static int g_num_sms = 0;
 static int num_sms() {
-  if (!g_num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (g_num_sms <= 0) g_num_sms = 148;
+  static int cache[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!cache[dev]) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cache[dev] = n > 0 ? n : 148;
   }
-  return g_num_sms;
+  return cache[dev];
 }
+
+// cudaFuncSetAttribute applies to the current device only: remember per device what was set.
+struct PerDeviceOnce {
+  bool done[64] = {false};
+  bool* slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    return &done[dev];
+  }
+};
 
 template <int BN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& a,
                        int max_ctas, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce once;
+  bool* attr_set_p = once.slot();
+  if (!*attr_set_p) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100_kernel<BN, 0>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    *attr_set_p = true;
   }
   long long items = (long long)((a.M + G_BM - 1) / G_BM) * ((a.N + BN - 1) / BN) * a.L0 * a.L1 * a.splits;
   int grid = (int)(items < max_ctas ? items : max_ctas);
@@ -149,12 +161,13 @@ static double pair_tile_cost() {
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& a, int max_ctas,
                             cudaStream_t stream) {
   using Cfg = Gemm2Cfg;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce once;
+  bool* attr_set_p = once.slot();
+  if (!*attr_set_p) {
     cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    *attr_set_p = true;
   }
   const long long items = (long long)((a.M + 255) / 256) * ((a.N + 255) / 256) * a.L0 * a.L1 * a.splits;
   long long pairs = max_ctas / 2;
@@ -204,8 +217,9 @@ extern "C" int ftk_tick_i32(int* word, void* stream_v) {
   return (int)cudaGetLastError();
 }
 
-extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+// Argument checks and tile choice shared by the launcher and the plan query.  Returns 0 and
+// (bn, splits), or a negative argument error.  bn == 512 stands for the CTA-pair kernel.
+static int plan_gemm(const FtkGemmDesc* g, int* bn_out, int* splits_out) {
   if (!g || g->M <= 0 || g->N <= 0 || g->K <= 0) return -2;
   const int L0 = g->L0 > 0 ? g->L0 : 1, L1 = g->L1 > 0 ? g->L1 : 1;
   // alignment rules of the tiled TMA copies: 16-byte base, 16-byte strides.
@@ -262,6 +276,25 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   }
   if (g->split_k > 1 && split_ok(g->split_k)) splits = g->split_k;
   if (bn != 128 && bn != 192 && bn != 256 && bn != 512) return -5;
+  *bn_out = bn;
+  *splits_out = splits;
+  return 0;
+}
+
+// Which kernel ftk_gemm_bf16 would launch for this problem: *bn = 128 / 192 / 256 (single-CTA tile
+// 128 x bn) or 512 (CTA-pair kernel, 256 x 256 tiles); *splits = split-K factor.  Launches nothing.
+extern "C" int ftk_gemm_plan(const FtkGemmDesc* g, int* bn, int* splits) {
+  if (!bn || !splits) return -2;
+  return plan_gemm(g, bn, splits);
+}
+
+extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  int bn = 0, splits = 1;
+  int prc = plan_gemm(g, &bn, &splits);
+  if (prc) return prc;
+  const int L0 = g->L0 > 0 ? g->L0 : 1, L1 = g->L1 > 0 ? g->L1 : 1;
+  const int sms = g->max_ctas > 0 ? g->max_ctas : num_sms();
 
   CUtensorMap tmA, tmB;
   int rc = make_operand_maps(g, L0, L1, bn == 512 ? 128 : bn, &tmA, &tmB);   // a pair stages 128 B rows per CTA
@@ -361,12 +394,13 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
 
   using Cfg = GemmCfg<BN>;
   constexpr int COMM_SMEM = Cfg::SMEM;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce once;
+  bool* attr_set_p = once.slot();
+  if (!*attr_set_p) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100_kernel<BN, 1>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, COMM_SMEM);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    *attr_set_p = true;
   }
   const long long items = (long long)((a.M + G_BM - 1) / G_BM) * ((a.N + BN - 1) / BN);
   long long n_compute = sms - c.comm_ctas;

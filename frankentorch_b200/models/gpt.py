@@ -67,7 +67,8 @@ class ParamArena:
 
     ALIGN = 128  # elements
 
-    def __init__(self, specs: List[Tuple[str, Tuple[int, ...]]], device, *, group=None, pad_multiple: int = 1024):
+    def __init__(self, specs: List[Tuple[str, Tuple[int, ...]]], device, *, group=None, pad_multiple: int = 1024,
+                 peer_visible: bool = False):
         self.specs = specs
         self.offsets: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
         off = 0
@@ -77,7 +78,7 @@ class ParamArena:
             off += (n + self.ALIGN - 1) // self.ALIGN * self.ALIGN
         off = (off + pad_multiple - 1) // pad_multiple * pad_multiple
         self.numel = off
-        self.symmetric = group is not None
+        self.symmetric = group is not None or peer_visible   # (a one-rank job can use the peer kernels too)
         if self.symmetric:
             from ..parallel.symm import SymmetricBuffer
             self.params_buf = SymmetricBuffer(off * 2, group, device)
@@ -87,9 +88,17 @@ class ParamArena:
         else:
             self.params = torch.zeros(off, dtype=torch.bfloat16, device=device)
             self.grads = torch.zeros(off, dtype=torch.float32, device=device)
+        # arena offsets where a data-parallel gradient bucket must end (see parallel/data_parallel.py)
+        self.bucket_cuts: List[int] = []
         self.master = torch.zeros(off, dtype=torch.float32, device=device)
         self.m = torch.zeros(off, dtype=torch.float32, device=device)
         self.v = torch.zeros(off, dtype=torch.float32, device=device)
+
+    def slot_end(self, name: str) -> int:
+        """One past the last arena element of the (128-aligned) slot of parameter ``name``."""
+        off, shape = self.offsets[name]
+        n = int(math.prod(shape))
+        return off + (n + self.ALIGN - 1) // self.ALIGN * self.ALIGN
 
     def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
         off, shape = self.offsets[name]
@@ -106,7 +115,8 @@ class ParamArena:
 class GPT:
     """GPT-2 style decoder; ``forward`` records the step on a :class:`TensorTape`."""
 
-    def __init__(self, cfg: GPTConfig, tape: TensorTape, device="cuda", seed: int = 1234, *, group=None):
+    def __init__(self, cfg: GPTConfig, tape: TensorTape, device="cuda", seed: int = 1234, *, group=None,
+                 peer_visible: bool = False):
         self.cfg = cfg
         self.tape = tape
         self.device = torch.device(device)
@@ -129,7 +139,11 @@ class GPT:
         if group is not None:
             import torch.distributed as dist
             world = dist.get_world_size(group)
-        self.arena = ParamArena(specs, self.device, group=group, pad_multiple=1024 * world)
+        self.arena = ParamArena(specs, self.device, group=group, pad_multiple=1024 * world,
+                                peer_visible=peer_visible)
+        # the embeddings' gradients are complete only when the backward pass ends (the token table is
+        # also the LM head): they form one bucket of their own
+        self.arena.bucket_cuts.append(self.arena.slot_end("wpe.weight"))
         self._init_weights(seed)
         # parameters are the lowest-index leaves of the tape; the per-step graph is truncated above
         self.leaf: Dict[str, int] = {}

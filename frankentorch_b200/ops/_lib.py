@@ -85,7 +85,8 @@ def load(build_if_missing: bool = True):
     global _LIB
     if _LIB is not None:
         return _LIB
-    if not _LIB_PATH.exists() and build_if_missing and os.environ.get("FT_NO_AUTOBUILD") != "1":
+    if build_if_missing and os.environ.get("FT_NO_AUTOBUILD") != "1":
+        # also rebuilds a library that was built from other sources than the ones on disk
         from .. import _build
         _build.build_kernels()
     if not _LIB_PATH.exists():

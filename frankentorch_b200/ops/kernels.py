@@ -23,6 +23,7 @@ _STATUS_NAMES = {
     3: "WAIT_TMEM_FULL (accumulator never completed)", 4: "WAIT_TMEM_EMPTY (accumulator never drained)",
     5: "WAIT_PEER (peer flag never arrived)", 6: "WAIT_SOFTMAX (probabilities never arrived)",
     7: "BAD_ARG (misaligned shared memory or invalid argument)",
+    8: "WAIT_WARPS (a warp barrier was abandoned after an abort elsewhere in the CTA)",
 }
 
 # launch counter: how many of this package's kernels launchers were called (bench reporting)

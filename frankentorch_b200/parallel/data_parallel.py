@@ -1,9 +1,16 @@
-"""Data parallelism (ZeRO-1 style) with the gradient reduce-scatter fused into the sharded
-AdamW update and the parameter all-gather, all through in-kernel NVLink peer accesses.
+"""Data parallelism (ZeRO-1 style): the gradient reduce-scatter is fused with the sharded AdamW
+update and the parameter all-gather, bucket by bucket, through in-kernel NVLink peer accesses,
+and runs under the backward pass.
 
-``FusedDataParallel`` owns the peer-visible gradient / parameter arenas and the flag blocks;
-``reduce_and_update`` launches the four kernels of ``csrc/dp_fused.cu`` on the current stream
-(capturable in a CUDA graph: the step number lives in device memory).
+``FusedDataParallel`` cuts the flat parameter arena into buckets at parameter boundaries.  The
+tape tells it whenever a rule has written a parameter gradient in place; when the last gradient
+of a bucket is in, that bucket's push + ordered reduce (``csrc/dp_fused.cu``) is launched on a
+communication stream behind an event, while the main stream continues with the backward pass.
+Gradients cross NVLink as bf16 and are summed in fp32 in ascending rank order, so results are
+bit-identical run to run (and between eager execution and CUDA-graph replay: the step number
+lives in device memory and the cross-stream dependencies are captured with the graph).  After
+the last bucket: global gradient norm (one scalar exchange), AdamW on the owned shards, peer
+stores of the updated bf16 parameters into every rank's arena.
 
 ``NcclDataParallel`` is the stock path - NCCL all-reduce of the flat gradient followed by the
 single-GPU fused AdamW - kept as the baseline and as the hardened-mode fallback.
@@ -15,7 +22,9 @@ ft-optim/src/lib.rs:800-1085.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -25,72 +34,292 @@ from ..ops import kernels as K
 from .symm import SymmetricBuffer
 
 DP_MAX_RANKS = 16
-REDUCE_CTAS = 296
+DP_MAX_BUCKETS = 64
+DEFAULT_BUCKET_ELEMS = 16 * 1024 * 1024      # ~32 MB of bf16 on the wire per bucket
+REDUCE_CTAS = 64                             # CTAs of the per-bucket push / reduce kernels
+UPDATE_CTAS = 296                            # CTAs of the AdamW + all-gather kernel
 
 
 def shard_multiple(world: int) -> int:
-    """The flat arena length must be a multiple of this so shards are float4-aligned."""
+    """The flat arena length is padded to a multiple of this (bucket ends stay 128-aligned)."""
     return 1024 * max(world, 1)
 
 
+@dataclass(frozen=True)
+class Bucket:
+    lo: int       # first arena element
+    hi: int       # one past the last
+    shard: int    # elements of the bucket owned by each rank (multiple of 8); the last ranks' may be cut by hi
+    off: int      # start of this bucket's shard in the rank-local shard arrays
+
+    def owned(self, rank: int) -> Tuple[int, int]:
+        """Arena range [a, b) of the bucket that ``rank`` owns (empty when a >= b)."""
+        a = self.lo + rank * self.shard
+        return a, max(a, min(a + self.shard, self.hi))
+
+
+def plan_buckets(param_ranges: Sequence[Tuple[int, int]], numel: int, world: int,
+                 target_elems: int = DEFAULT_BUCKET_ELEMS, max_buckets: int = DP_MAX_BUCKETS,
+                 forced_cuts: Sequence[int] = ()) -> List[Bucket]:
+    """Cut ``[0, numel)`` into buckets at parameter boundaries.
+
+    ``param_ranges`` are the arena slots ``(start, end)`` in arena order (ends are 128-aligned, so
+    every bucket boundary is).  Parameters are added to a bucket until it holds at least
+    ``target_elems``; the last bucket takes the arena's tail padding.  ``forced_cuts`` are arena
+    offsets where a boundary must fall (a model puts one behind the parameters whose gradients
+    arrive last, e.g. the embeddings, so that they do not hold back a bucket of early finishers);
+    a size cut that would fall less than half a target before a forced one is left to it.  The
+    boundaries depend only on the arena layout, the world size and the target: every rank computes
+    the same plan.
+    """
+    if numel % 8:
+        raise ValueError("the arena length must be a multiple of 8")
+    cuts, start, n_params = [], 0, len(param_ranges)
+    forced = sorted(set(int(c) for c in forced_cuts if 0 < c < numel))
+    for i, (a, b) in enumerate(param_ranges):
+        if i + 1 == n_params:
+            break
+        if b in forced:
+            cuts.append(b)
+            start = b
+        elif b - start >= target_elems and not any(b < c <= b + target_elems // 2 for c in forced):
+            cuts.append(b)
+            start = b
+    edges = [0] + cuts + [numel]
+    while len(edges) - 1 > max_buckets:             # merge the smallest neighbours until the table fits
+        sizes = [edges[i + 2] - edges[i] for i in range(len(edges) - 2)]
+        j = sizes.index(min(sizes))
+        del edges[j + 1]
+    out, off = [], 0
+    for lo, hi in zip(edges[:-1], edges[1:]):
+        if lo % 8 or hi % 8:
+            raise ValueError("bucket boundaries must be multiples of 8 elements")
+        shard = -(-(hi - lo) // world)
+        shard = -(-shard // 8) * 8
+        out.append(Bucket(lo, hi, shard, off))
+        off += shard
+    return out
+
+
+def scatter_shards_to_arena(buckets: Sequence[Bucket], shards: Sequence[torch.Tensor], numel: int) -> torch.Tensor:
+    """Rebuild a flat arena-ordered tensor from every rank's local shard array (``shards[r]``)."""
+    full = torch.zeros(numel, dtype=shards[0].dtype, device=shards[0].device)
+    for bk in buckets:
+        for r, s in enumerate(shards):
+            a, b = bk.owned(r)
+            if b > a:
+                full[a:b] = s[bk.off: bk.off + (b - a)]
+    return full
+
+
+def gather_arena_shard(buckets: Sequence[Bucket], full: torch.Tensor, rank: int, total: int) -> torch.Tensor:
+    """The rank-local shard array (length ``total``) cut out of a flat arena-ordered tensor."""
+    out = torch.zeros(total, dtype=full.dtype, device=full.device)
+    for bk in buckets:
+        a, b = bk.owned(rank)
+        if b > a:
+            out[bk.off: bk.off + (b - a)] = full[a:b]
+    return out
+
+
+class _Bucket(C.Structure):
+    _fields_ = [("lo", C.c_longlong), ("hi", C.c_longlong), ("shard", C.c_longlong), ("off", C.c_longlong)]
+
+
+class _Comm(C.Structure):
+    _fields_ = [("inbox", C.POINTER(C.c_void_p)), ("params", C.POINTER(C.c_void_p)),
+                ("flags", C.POINTER(C.c_void_p)), ("slots", C.POINTER(C.c_void_p)),
+                ("buckets", C.c_void_p),
+                ("rank", C.c_int), ("world", C.c_int), ("n_buckets", C.c_int), ("n_ctas", C.c_int),
+                ("wire_fp32", C.c_int),
+                ("gshard", C.c_void_p), ("partial", C.c_void_p), ("counters", C.c_void_p),
+                ("seq", C.c_void_p), ("ok_word", C.c_void_p)]
+
+
+def _bind(lib):
+    pc, vp, i, f = C.POINTER(_Comm), C.c_void_p, C.c_int, C.c_float
+    lib.ftk_dp_begin_step.argtypes = [pc, vp]
+    lib.ftk_dp_bucket_reduce.argtypes = [pc, i, vp, vp]
+    lib.ftk_dp_norm.argtypes = [pc, f, vp, vp, vp]
+    lib.ftk_dp_update.argtypes = [pc, i, i, vp, vp, vp, vp, f, f, f, f, i, vp]
+    lib.ftk_dp_wait_params.argtypes = [pc, i, vp]
+    for fn in (lib.ftk_dp_begin_step, lib.ftk_dp_bucket_reduce, lib.ftk_dp_norm, lib.ftk_dp_update,
+               lib.ftk_dp_wait_params):
+        fn.restype = C.c_int
+    return lib
+
+
 class FusedDataParallel:
-    def __init__(self, arena, group: dist.ProcessGroup, device: torch.device):
+    """Bucketed reduce-scatter + sharded AdamW + all-gather over peer memory.
+
+    ``overlap=True`` launches each bucket on ``comm_stream`` as soon as its gradients are complete
+    (needs :meth:`attach`); otherwise all buckets are launched after the backward pass.
+    ``wire`` is ``"bf16"`` (default) or ``"fp32"`` (twice the NVLink bytes, no rounding before the sum).
+    """
+
+    def __init__(self, arena, group: Optional[dist.ProcessGroup], device: torch.device, *,
+                 bucket_elems: Optional[int] = None, wire: Optional[str] = None, overlap: bool = True):
         self.group, self.device = group, device
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.world = dist.get_world_size(group) if group is not None else 1
         if self.world > DP_MAX_RANKS:
             raise ValueError(f"at most {DP_MAX_RANKS} ranks per data-parallel group")
-        n = arena.numel
-        if n % shard_multiple(self.world):
-            raise ValueError("arena length must be padded to shard_multiple(world)")
-        self.shard_len = n // self.world
         if not getattr(arena, "symmetric", False):
             raise ValueError("FusedDataParallel needs an arena allocated in symmetric memory")
         self.arena = arena
-        # flags: [3 phases][DP_MAX_RANKS] u64, then sumsq slots [DP_MAX_RANKS] fp32
-        self.ctrl = SymmetricBuffer(3 * DP_MAX_RANKS * 8 + DP_MAX_RANKS * 4, group, device)
-        self.slots_off = 3 * DP_MAX_RANKS * 8
-        lo, hi = self.rank * self.shard_len, (self.rank + 1) * self.shard_len
-        # optimizer state is kept for the owned shard only
-        self.master = arena.master[lo:hi].clone()
-        self.m = torch.zeros(self.shard_len, dtype=torch.float32, device=device)
-        self.v = torch.zeros(self.shard_len, dtype=torch.float32, device=device)
+        self.overlap = overlap and os.environ.get("FT_DP_OVERLAP", "1") != "0"
+        wire = wire or os.environ.get("FT_DP_WIRE", "bf16")
+        if wire not in ("bf16", "fp32"):
+            raise ValueError("wire must be 'bf16' or 'fp32'")
+        self.wire = wire
+        target = int(bucket_elems or float(os.environ.get("FT_DP_BUCKET_MB", "0")) * (1 << 19)
+                     or DEFAULT_BUCKET_ELEMS)
+        ranges = []
+        for name, _ in arena.specs:
+            off, shape = arena.offsets[name]
+            n = 1
+            for s in shape:
+                n *= int(s)
+            ranges.append((off, off + (n + arena.ALIGN - 1) // arena.ALIGN * arena.ALIGN))
+        self.buckets = plan_buckets(ranges, arena.numel, self.world, target,
+                                    forced_cuts=getattr(arena, "bucket_cuts", ()))
+        self.total_shard = sum(b.shard for b in self.buckets)
+        self.shard_len = self.total_shard
+        self.n_ctas = int(os.environ.get("FT_DP_CTAS", REDUCE_CTAS))
+        nb = len(self.buckets)
+        # peer-visible: inbox, flag block, sumsq slots
+        wsize = 2 if wire == "bf16" else 4
+        self.inbox = SymmetricBuffer(self.world * self.total_shard * wsize, group, device)
+        flag_bytes = 3 * DP_MAX_BUCKETS * DP_MAX_RANKS * 8
+        self.ctrl = SymmetricBuffer(flag_bytes + DP_MAX_RANKS * 4, group, device)
+        # rank-local optimizer state for the owned shards only
+        self.master = gather_arena_shard(self.buckets, arena.master, self.rank, self.total_shard)
+        self.m = torch.zeros(self.total_shard, dtype=torch.float32, device=device)
+        self.v = torch.zeros(self.total_shard, dtype=torch.float32, device=device)
         arena.drop_full_optimizer_state()
-        self.gshard = torch.empty(self.shard_len, dtype=torch.float32, device=device)
-        self.partial = torch.zeros(REDUCE_CTAS, dtype=torch.float32, device=device)
-        self.gate = torch.zeros(1, dtype=torch.int64, device=device)
-        # communication sequence number: grows by one per call, never rewinds (the flags compare
-        # against it), and lives on the device so a captured graph advances it on every replay
+        self.gshard = torch.zeros(self.total_shard, dtype=torch.float32, device=device)
+        self.partial = torch.zeros(nb * self.n_ctas, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(2 * DP_MAX_BUCKETS, dtype=torch.int32, device=device)
+        # step sequence number: grows by one per step, never rewinds (the flags compare against it),
+        # and lives on the device so a captured graph advances it on every replay
         self.seq_dev = torch.zeros((), dtype=torch.int64, device=device)
-        self._seq_scratch = torch.zeros(4, dtype=torch.float32, device=device)
-        lib = _lib.load()
-        self._fn = lib.ftk_dp_step
-        vpp = C.POINTER(C.c_void_p)
-        self._fn.argtypes = [vpp, vpp, vpp, vpp, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
-                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p,
-                             C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_void_p]
-        self._fn.restype = C.c_int
-        self._grads_tbl = arena.grads_buf.peer_table()
-        self._params_tbl = arena.params_buf.peer_table()
-        self._flags_tbl = self.ctrl.peer_table()
-        self._slots_tbl = self.ctrl.peer_table(self.slots_off)
-        dist.barrier(group=group)
+        self.ok_dev = torch.ones((), dtype=torch.int32, device=device)
+        tbl = (_Bucket * nb)(*[_Bucket(b.lo, b.hi, b.shard, b.off) for b in self.buckets])
+        self._bucket_host = torch.frombuffer(bytearray(bytes(tbl)), dtype=torch.int64).clone()
+        self.bucket_dev = self._bucket_host.to(device)
+        self._lib = _bind(_lib.load())
+        self._tables = (self.inbox.peer_table(), arena.params_buf.peer_table(), self.ctrl.peer_table(),
+                        self.ctrl.peer_table(flag_bytes))
+        pv = C.POINTER(C.c_void_p)
+        self._comm = _Comm(C.cast(self._tables[0], pv), C.cast(self._tables[1], pv), C.cast(self._tables[2], pv),
+                           C.cast(self._tables[3], pv),
+                           self.bucket_dev.data_ptr(), self.rank, self.world, nb, self.n_ctas,
+                           1 if wire == "fp32" else 0, self.gshard.data_ptr(), self.partial.data_ptr(),
+                           self.counters.data_ptr(), self.seq_dev.data_ptr(), self.ok_dev.data_ptr())
+        self.comm_stream = torch.cuda.Stream(device=device)
+        # bucket completion tracking (host side, drives the launches while a step is recorded)
+        self._leaf_bucket: Dict[int, int] = {}
+        self._writes_seen: Dict[int, int] = {}
+        self._expected: Optional[List[int]] = None
+        self._remaining: List[int] = []
+        self._launched: List[bool] = [False] * nb
+        self._events: List[torch.cuda.Event] = []
+        self.launch_order: List[int] = []          # bucket order of the last recorded step
+        if group is not None:
+            dist.barrier(group=group)
 
+    # ------------------------------------------------------------------ wiring to the tape
+    def attach(self, tape, leaf_ids: Dict[str, int]) -> None:
+        """Track in-place gradient writes of the arena's parameter leaves (``leaf_ids``: name -> tape id)."""
+        for name, nid in leaf_ids.items():
+            if name not in self.arena.offsets:
+                continue
+            off = self.arena.offsets[name][0]
+            for bi, bk in enumerate(self.buckets):
+                if bk.lo <= off < bk.hi:
+                    self._leaf_bucket[int(nid)] = bi
+                    break
+        tape.leaf_grad_written_fn = self._leaf_written
+
+    def _leaf_written(self, nid: int) -> None:
+        b = self._leaf_bucket.get(int(nid))
+        if b is None:
+            return
+        if self._expected is None:                  # first step: count the writes per bucket
+            self._writes_seen[b] = self._writes_seen.get(b, 0) + 1
+            return
+        self._remaining[b] -= 1
+        if self._remaining[b] == 0 and self.overlap and not self._launched[b]:
+            self._launch_bucket(b)
+
+    def begin_step(self) -> None:
+        """First thing of a step, on the main stream: advance the sequence number, arm the ok word."""
+        K._chk(self._lib.ftk_dp_begin_step(C.byref(self._comm), torch.cuda.current_stream().cuda_stream),
+               "ftk_dp_begin_step")
+        K._launches += 1
+        if self._expected is not None:
+            self._remaining = list(self._expected)
+        self._launched = [False] * len(self.buckets)
+        self._events = []
+        self.launch_order = []
+
+    def _launch_bucket(self, b: int) -> None:
+        """Push + reduce of bucket ``b`` on the communication stream, after everything the main stream
+        has been given so far (that includes the kernels that wrote the bucket's gradients)."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self.comm_stream.wait_event(ev)
+        self._events.append(ev)
+        K._chk(self._lib.ftk_dp_bucket_reduce(C.byref(self._comm), b, self.arena.grads.data_ptr(),
+                                              self.comm_stream.cuda_stream), "ftk_dp_bucket_reduce")
+        K._launches += 2
+        self._launched[b] = True
+        self.launch_order.append(b)
+
+    # ------------------------------------------------------------------ the optimizer step
     def reduce_and_update(self, arena, hyper, opt, sumsq, grad_norm, step_dev) -> None:
-        K.adamw_tick(self.seq_dev, self._seq_scratch, 0.5, 0.5)   # seq += 1 (reuses the counter kernel)
-        rc = self._fn(self._grads_tbl, self._params_tbl, self._flags_tbl, self._slots_tbl, self.rank, self.world,
-                      self.gshard.data_ptr(), self.partial.data_ptr(), REDUCE_CTAS, self.gate.data_ptr(),
-                      self.master.data_ptr(), self.m.data_ptr(), self.v.data_ptr(), self.shard_len,
-                      self.seq_dev.data_ptr(), hyper.data_ptr(), grad_norm.data_ptr(),
-                      float(opt.grad_clip or 0.0), float(opt.beta1), float(opt.beta2), float(opt.eps),
-                      float(opt.weight_decay), torch.cuda.current_stream().cuda_stream)
-        K._chk(rc, "ftk_dp_step")
-        K._launches += 3   # four kernels in one launcher call
+        if self._expected is None and self._writes_seen:
+            self._expected = [self._writes_seen.get(b, 0) for b in range(len(self.buckets))]
+        # buckets whose gradients were not all written in place (or the first, counting step)
+        for b in reversed(range(len(self.buckets))):
+            if not self._launched[b]:
+                self._launch_bucket(b)
+        cs = self.comm_stream.cuda_stream
+        c = C.byref(self._comm)
+        K._chk(self._lib.ftk_dp_norm(c, float(opt.grad_clip or 0.0), hyper.data_ptr(), grad_norm.data_ptr(), cs),
+               "ftk_dp_norm")
+        K._chk(self._lib.ftk_dp_update(c, 0, len(self.buckets), self.master.data_ptr(), self.m.data_ptr(),
+                                       self.v.data_ptr(), hyper.data_ptr(), float(opt.beta1), float(opt.beta2),
+                                       float(opt.eps), float(opt.weight_decay), UPDATE_CTAS, cs), "ftk_dp_update")
+        K._chk(self._lib.ftk_dp_wait_params(c, 0, cs), "ftk_dp_wait_params")
+        K._launches += 3
+        torch.cuda.current_stream().wait_stream(self.comm_stream)
 
+    # ------------------------------------------------------------------ state access
     def gather_master(self) -> torch.Tensor:
-        """Full fp32 master weights on every rank (checkpointing; not on the step path)."""
-        full = torch.empty(self.shard_len * self.world, dtype=torch.float32, device=self.device)
-        dist.all_gather_into_tensor(full, self.master, group=self.group)
-        return full
+        """Full fp32 master weights in arena order on every rank (checkpointing; not on the step path)."""
+        return self._gather(self.master)
+
+    def _gather(self, local: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            shards = [local]
+        else:
+            allv = torch.empty(self.world * self.total_shard, dtype=local.dtype, device=self.device)
+            dist.all_gather_into_tensor(allv, local.contiguous(), group=self.group)
+            shards = list(allv.view(self.world, self.total_shard))
+        return scatter_shards_to_arena(self.buckets, shards, self.arena.numel)
+
+    def gather_optimizer_state(self) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """(master, m, v) in arena order on every rank: what a replicated optimizer would hold."""
+        return self._gather(self.master), self._gather(self.m), self._gather(self.v)
+
+    def layout_tensor(self) -> torch.Tensor:
+        """The bucket table ``[n_buckets, 4]`` = (lo, hi, shard, off) as float64 (checkpoint metadata)."""
+        return self._bucket_host.view(-1, 4).to(torch.float64)
+
+    def step_ok(self) -> bool:
+        """Host read of the step's ok word (synchronises): False when a bounded wait ran out."""
+        return bool(int(self.ok_dev.item()) == 1)
 
 
 class NcclDataParallel:
@@ -98,13 +327,15 @@ class NcclDataParallel:
 
     eager_only = True   # the engine does not capture this path in a CUDA graph
 
-    def __init__(self, arena, group: dist.ProcessGroup, device: torch.device):
+    def __init__(self, arena, group: Optional[dist.ProcessGroup], device: torch.device):
         self.group, self.device = group, device
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.world = dist.get_world_size(group) if group is not None else 1
         self.arena = arena
 
     def reduce_and_update(self, arena, hyper, opt, sumsq, grad_norm, step_dev) -> None:
-        dist.all_reduce(arena.grads, op=dist.ReduceOp.AVG, group=self.group)
+        if self.world > 1:
+            dist.all_reduce(arena.grads, op=dist.ReduceOp.AVG, group=self.group)
         if opt.grad_clip is not None:
             K.sumsq(arena.grads, out=sumsq)
             K.clip_scale(sumsq, opt.grad_clip, hyper, grad_norm)

@@ -13,9 +13,10 @@ rebuild keeps that model:
 * device-side waits on peer flags are bounded (see ``csrc``); when one runs out the kernel
   records a code in the status word, which :func:`device_status_error` turns into
   :class:`DeviceWaitTimeout`.
-* ``HardenedDataParallel`` wraps the fused data-parallel step: in strict mode a failure is
-  raised to the caller, in hardened mode the wrapper switches to the NCCL all-reduce path for
-  the rest of the run and records the event in the evidence ledger.
+* ``HardenedTrainer`` wraps the training engine: between steps it reads the status word and lets
+  the ranks agree on it; in strict mode a failure is raised on every rank, in hardened mode the
+  engine is switched to the NCCL all-reduce path for the rest of the run and the event is
+  recorded in the evidence ledger.
 
 Nothing here faults, traps or hangs a GPU: failures are raised on the host, and tests inject them
 on the host (a rank that raises, exits or stops publishing).
@@ -98,7 +99,8 @@ class RankHealth:
 
 _STATUS_NAMES = {1: "TMA data never landed", 2: "pipeline stage never released", 3: "accumulator never completed",
                  4: "accumulator never drained", 5: "a flag owned by another rank never reached the expected value",
-                 6: "probabilities never arrived", 7: "bad argument"}
+                 6: "probabilities never arrived", 7: "bad argument",
+                 8: "a warp barrier was abandoned after an abort elsewhere in the CTA"}
 
 
 def device_status_error(status_word: int) -> Optional[DeviceWaitTimeout]:
@@ -109,49 +111,77 @@ def device_status_error(status_word: int) -> Optional[DeviceWaitTimeout]:
     return DeviceWaitTimeout(code, cta, _STATUS_NAMES.get(code, "unknown"))
 
 
-class HardenedDataParallel:
-    """Strict / hardened wrapper around a fused data-parallel step with a library fallback.
+class HardenedTrainer:
+    """Strict / hardened failure policy around a :class:`TrainEngine` whose optimizer step runs
+    through the fused peer-memory data-parallel kernels.
 
-    ``primary`` and ``fallback_factory()`` follow the ``reduce_and_update`` protocol of
-    :mod:`frankentorch_b200.parallel.data_parallel`.  ``read_status`` returns the device status
-    word (it synchronises, so it is polled every ``check_every`` steps, not every step).
+    The engine's step is a replayed CUDA graph, so nothing inside it can change course; the policy
+    therefore lives on the host, between steps:
+
+    * every ``check_every`` steps the device status word is read (``read_status``; it
+      synchronises) and the ranks agree on the outcome (``agree``: an integer MAX over a host-side
+      group, e.g. ``gloo`` - every rank must take the same branch, a rank that switched to a library
+      collective while its peers still spin on peer flags would only move the failure);
+    * a fused step whose bounded waits ran out has updated nothing: the kernels poison the norm
+      exchange so that every rank skips the AdamW update and the all-gather of that step
+      (``csrc/dp_fused.cu``), and the master weights, moments and parameters are those of the
+      last good step;
+    * strict mode raises :class:`DeviceWaitTimeout` on every rank; hardened mode records the event
+      (ledger kind ``durability``), rebuilds the full fp32 optimizer state from the shards, swaps
+      the engine's data-parallel object for ``fallback_factory()`` (the NCCL all-reduce path, run
+      eagerly), and re-runs the last step if it was one of the skipped ones.
     """
 
-    def __init__(self, primary, fallback_factory: Callable[[], object], *, mode: str = "strict",
-                 read_status: Optional[Callable[[], int]] = None, check_every: int = 16, ledger=None):
+    def __init__(self, engine, fallback_factory: Callable[[], object], *, mode: str = "strict",
+                 read_status: Optional[Callable[[], int]] = None, agree: Optional[Callable[[int], int]] = None,
+                 check_every: int = 16, ledger=None):
         if mode not in ("strict", "hardened"):
             raise ValueError("mode must be 'strict' or 'hardened'")
-        self.primary, self.fallback_factory, self.mode = primary, fallback_factory, mode
-        self.read_status, self.check_every, self.ledger = read_status, max(1, check_every), ledger
-        self.active = primary
+        self.engine, self.fallback_factory, self.mode = engine, fallback_factory, mode
+        self.read_status, self.agree = read_status, agree or (lambda v: v)
+        self.check_every, self.ledger = max(1, check_every), ledger
         self.fell_back = False
         self.events: List[dict] = []
         self._n = 0
 
-    @property
-    def eager_only(self) -> bool:
-        return getattr(self.active, "eager_only", False)
+    def step(self, ids_host, targets_host, *, read_loss: bool = True):
+        loss = self.engine.step(ids_host, targets_host, read_loss=read_loss)
+        self._n += 1
+        if not self.fell_back and self.read_status is not None and self._n % self.check_every == 0:
+            redo = self.poll()
+            if redo:
+                loss = self.engine.step_device(read_loss=read_loss)
+        return loss
 
-    def __getattr__(self, name):
-        return getattr(self.active, name)
-
-    def poll(self) -> None:
-        if self.read_status is None or self.fell_back:
-            return
-        err = device_status_error(int(self.read_status()))
-        if err is None:
-            return
-        ev = {"event": "dp_device_wait_timeout", "code": err.code, "cta": err.cta, "mode": self.mode, "step": self._n}
+    def poll(self) -> bool:
+        """Read and agree on the status; returns True when the caller should re-run the last step."""
+        local = int(self.read_status())
+        agreed = int(self.agree(local))
+        if agreed == 0:
+            return False
+        err = device_status_error(local if local else agreed)
+        ev = {"event": "dp_device_wait_timeout", "code": err.code, "cta": err.cta, "mode": self.mode,
+              "step": self._n, "local_status": local, "agreed_status": agreed}
         self.events.append(ev)
         if self.ledger is not None:
             self.ledger.record("durability", "fused data-parallel step failed: " + str(err), ev)
         if self.mode == "strict":
             raise err
-        self.active = self.fallback_factory()
+        dp = self.engine.dp
+        last_skipped = bool(hasattr(dp, "step_ok") and not dp.step_ok())
+        self.engine.switch_data_parallel(self.fallback_factory)
         self.fell_back = True
+        ev["last_step_rerun"] = last_skipped
+        return last_skipped
 
-    def reduce_and_update(self, *args, **kw) -> None:
-        self._n += 1
-        if self._n % self.check_every == 0:
-            self.poll()
-        self.active.reduce_and_update(*args, **kw)
+
+def gloo_max_agreement(group) -> Callable[[int], int]:
+    """``agree`` callable for :class:`HardenedTrainer`: integer MAX over a host-side process group."""
+    import torch
+    import torch.distributed as dist
+
+    def agree(v: int) -> int:
+        t = torch.tensor([int(v)], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return int(t.item())
+    return agree

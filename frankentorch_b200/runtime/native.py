@@ -13,9 +13,10 @@ def load():
     global _LIB
     if _LIB is not None:
         return _LIB
-    if not _PATH.exists():
+    import os
+    if os.environ.get("FT_NO_AUTOBUILD") != "1":
         from .. import _build
-        _build.build_core()
+        _build.build_core()     # no-op when the library was built from the sources on disk
     lib = C.CDLL(str(_PATH))
     vp, i64, u64, i32, dbl = C.c_void_p, C.c_int64, C.c_uint64, C.c_int, C.c_double
     P = C.POINTER

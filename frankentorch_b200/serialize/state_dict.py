@@ -142,12 +142,22 @@ def save_sharded(sd: Dict[str, torch.Tensor], stem: str, rank: int) -> str:
 
 
 def consolidate_shards(stem: str, world: int, out_path: Optional[str] = None) -> Dict[str, torch.Tensor]:
-    """Merge per-rank shards (disjoint key sets, or row-sharded tensors named ``key@shard{r}``)."""
+    """Merge per-rank shards: disjoint key sets, row-sharded tensors named ``key@shard{r}``
+    (concatenated in rank order), and bucket-sharded flat tensors named ``key@bshard{r}`` with
+    their bucket table ``key@layout`` (rows ``lo, hi, shard, off``: rank ``r`` holds elements
+    ``[lo + r*shard, min(lo + (r+1)*shard, hi))`` of every bucket at ``off`` of its piece)."""
     merged: Dict[str, torch.Tensor] = {}
     parts: Dict[str, List[Tuple[int, torch.Tensor]]] = {}
+    bparts: Dict[str, Dict[int, torch.Tensor]] = {}
+    layouts: Dict[str, torch.Tensor] = {}
     for r in range(world):
         for k, t in load_state_dict(f"{stem}.rank{r}.ftsv").items():
-            if "@shard" in k:
+            if k.endswith("@layout"):
+                layouts[k[: -len("@layout")]] = t
+            elif "@bshard" in k:
+                base, idx = k.rsplit("@bshard", 1)
+                bparts.setdefault(base, {})[int(idx)] = t
+            elif "@shard" in k:
                 base, idx = k.rsplit("@shard", 1)
                 parts.setdefault(base, []).append((int(idx), t))
             elif k in merged:
@@ -157,6 +167,19 @@ def consolidate_shards(stem: str, world: int, out_path: Optional[str] = None) ->
                 merged[k] = t
     for base, lst in parts.items():
         merged[base] = torch.cat([t for _, t in sorted(lst, key=lambda x: x[0])], 0)
+    for base, by_rank in bparts.items():
+        if base not in layouts or sorted(by_rank) != list(range(world)):
+            raise SerializeError("ShardLayout", f"'{base}': bucket table or a rank's piece is missing")
+        table = layouts[base].to(torch.int64).reshape(-1, 4).tolist()
+        numel = max(hi for _, hi, _, _ in table)
+        full = torch.zeros(numel, dtype=by_rank[0].dtype)
+        for lo, hi, shard, off in table:
+            for r in range(world):
+                a = lo + r * shard
+                b = max(a, min(a + shard, hi))
+                if b > a:
+                    full[a:b] = by_rank[r].reshape(-1)[off: off + (b - a)]
+        merged[base] = full
     if out_path:
         save_state_dict(merged, out_path)
     return merged

@@ -5,8 +5,8 @@ sorted keys, shape, dtype tag, raw little-endian data - no pickle):
 
 * ``optim.master`` / ``optim.m`` / ``optim.v``: fp32 master weights and AdamW moments of the
   replicated arena - the whole arena on a single GPU, this rank's shard under
-  ``FusedDataParallel`` (keys end in ``@shard{rank}`` so ``consolidate_shards`` can rebuild the
-  unsharded tensors);
+  ``FusedDataParallel`` (keys end in ``@bshard{rank}`` and come with the bucket table
+  ``<key>@layout``, so ``consolidate_shards`` can rebuild the unsharded, arena-ordered tensors);
 * ``local{i}.master`` / ``.m`` / ``.v``: rank-local arenas (tensor-parallel shards, ZeRO-3 weight
   shards, this rank's experts);
 * ``step`` (AdamW step counter) and ``hyper`` (learning rate, bias corrections, clip factor).
@@ -39,12 +39,16 @@ def training_state_dict(engine) -> Dict[str, torch.Tensor]:
     a = engine.model.arena
     sharded = engine.dp is not None and a.master is None
     own = engine.dp if sharded else a
-    suffix = f"@shard{rank}" if sharded else ""
+    suffix = f"@bshard{rank}" if sharded else ""
     sd = {
         "optim.master" + suffix: own.master, "optim.m" + suffix: own.m, "optim.v" + suffix: own.v,
         f"rank{rank}.step": engine.step_dev.reshape(1).to(torch.float64),
         f"rank{rank}.hyper": engine.hyper,
     }
+    if sharded:
+        # the bucket table (lo, hi, shard, off per bucket) lets consolidate_shards put the pieces back
+        for k in ("optim.master", "optim.m", "optim.v"):
+            sd[k + "@layout"] = engine.dp.layout_tensor()
     for i, la in enumerate(engine.local_arenas):
         sd[f"rank{rank}.local{i}.master"] = la.master
         sd[f"rank{rank}.local{i}.m"] = la.m
@@ -66,7 +70,7 @@ def load_training_state(engine, stem: str) -> None:
     a = engine.model.arena
     sharded = engine.dp is not None and a.master is None
     own = engine.dp if sharded else a
-    suffix = f"@shard{rank}" if sharded else ""
+    suffix = f"@bshard{rank}" if sharded else ""
     dev = engine.step_dev.device
 
     def put(dst: torch.Tensor, key: str) -> None:

@@ -42,6 +42,8 @@ class TrainEngine:
         self.B, self.S = micro_batch, seq_len
         self.opt = optim or OptimConfig()
         self.dp = dp
+        if dp is not None and hasattr(dp, "attach"):
+            dp.attach(self.tape, getattr(model, "leaf", {}))
         dev = model.device
         self.ids = torch.zeros((micro_batch, seq_len), dtype=torch.int64, device=dev)
         self.targets = torch.zeros((micro_batch, seq_len), dtype=torch.int64, device=dev)
@@ -58,6 +60,7 @@ class TrainEngine:
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         # library collectives (the NCCL baseline path) stay out of graph capture
+        self._graph_requested = use_cuda_graph
         self.use_graph = use_cuda_graph and not getattr(dp, "eager_only", False)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.launches_per_step = 0
@@ -87,6 +90,8 @@ class TrainEngine:
 
     def _step_body(self) -> None:
         n0 = K.launch_count()
+        if self.dp is not None and hasattr(self.dp, "begin_step"):
+            self.dp.begin_step()
         if hasattr(self.model, "begin_step"):
             self.model.begin_step()
         self.model.reset_grads()
@@ -123,6 +128,24 @@ class TrainEngine:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._step_body()
+
+    def switch_data_parallel(self, factory) -> None:
+        """Replace the data-parallel object between steps (the hardened-mode fallback).
+
+        A sharded optimizer (fp32 master / moments held per rank) is first gathered back into
+        the arena, so that the replacement - built by ``factory()`` afterwards - finds the full
+        state a replicated optimizer needs; the captured graph is dropped and rebuilt (or not
+        used at all when the replacement runs library collectives)."""
+        torch.cuda.synchronize()
+        a, old = self.model.arena, self.dp
+        if old is not None and a.master is None and hasattr(old, "gather_optimizer_state"):
+            a.master, a.m, a.v = old.gather_optimizer_state()
+        self.tape.leaf_grad_written_fn = None
+        self.dp = factory()
+        if self.dp is not None and hasattr(self.dp, "attach"):
+            self.dp.attach(self.tape, getattr(self.model, "leaf", {}))
+        self.use_graph = self._graph_requested and not getattr(self.dp, "eager_only", False)
+        self.graph = None
 
     # ------------------------------------------------------------------ public API
     def set_lr(self, lr: float) -> None:

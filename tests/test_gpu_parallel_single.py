@@ -96,3 +96,88 @@ def test_training_state_checkpoint_resumes_bit_identically(cuda_device, tmp_path
     tail = [resumed.step(*b) for b in batches[3:]]
     assert head == ref[:3]
     assert tail == ref[3:], (tail, ref[3:])
+
+
+from frankentorch_b200.ops import kernels as K  # noqa: E402
+
+
+def _dp_engine(cuda_device, seed, *, graph, clip, wire="fp32", bucket_elems=None, overlap=True, dp=True):
+    from frankentorch_b200.models.gpt import GPT, GPTConfig
+    from frankentorch_b200.parallel.data_parallel import FusedDataParallel
+    from frankentorch_b200.training.engine import OptimConfig, TrainEngine
+    cfg = GPTConfig.preset("gpt-tiny")
+    model = GPT(cfg, _tape(), device=cuda_device, seed=seed, peer_visible=dp)
+    d = FusedDataParallel(model.arena, None, cuda_device, wire=wire, bucket_elems=bucket_elems,
+                          overlap=overlap) if dp else None
+    eng = TrainEngine(model, 2, 128, OptimConfig(lr=1e-3, grad_clip=clip), use_cuda_graph=graph, dp=d)
+    return cfg, model, eng, d
+
+
+def test_bucketed_data_parallel_on_one_rank_matches_plain_engine(cuda_device):
+    """The peer-memory path with a world of one (every "peer" is this GPU) against the single-GPU
+    optimizer: with fp32 on the wire and no clipping the two are the same arithmetic, bit for bit,
+    whatever the bucket size and whether or not buckets start under the backward pass."""
+    from frankentorch_b200.models.gpt import GPTConfig
+    cfg = GPTConfig.preset("gpt-tiny")
+    batches = [_batch(cfg, 2, 128, seed=200 + i) for i in range(4)]
+    _, m0, e0, _ = _dp_engine(cuda_device, 5, graph=False, clip=None, dp=False)
+    ref_losses = [e0.step(*b) for b in batches]
+    ref = m0.arena.params.clone()
+    for graph, bucket_elems, overlap in ((False, None, True), (True, 40_000, True), (True, 40_000, False)):
+        _, m, e, d = _dp_engine(cuda_device, 5, graph=graph, clip=None, bucket_elems=bucket_elems, overlap=overlap)
+        losses = [e.step(*b) for b in batches]
+        K.check_status()
+        assert d.step_ok()
+        assert losses == ref_losses, (graph, bucket_elems, losses, ref_losses)
+        assert torch.equal(m.arena.params, ref)
+        if bucket_elems:
+            assert len(d.buckets) > 3
+            if overlap:
+                # the last layers' bucket goes first, the embeddings' bucket (arena start) last
+                assert set(d.launch_order[-2:]) == {0, 1} and d.launch_order[0] == len(d.buckets) - 1, d.launch_order
+        assert torch.equal(d.gather_master()[: ref.numel()].to(torch.bfloat16), ref)
+
+
+def test_bucketed_data_parallel_bf16_wire_and_clip_replay(cuda_device):
+    """bf16 on the wire + global-norm clipping: close to the single-GPU path, and bit-identical
+    between eager execution and CUDA-graph replay and between bucket sizes (sums are per element;
+    only the norm's partial sums depend on the buckets, so that part is compared with clipping off)."""
+    from frankentorch_b200.models.gpt import GPTConfig
+    cfg = GPTConfig.preset("gpt-tiny")
+    batches = [_batch(cfg, 2, 128, seed=300 + i) for i in range(5)]
+    _, m0, e0, _ = _dp_engine(cuda_device, 9, graph=True, clip=1.0, dp=False)
+    for b in batches:
+        e0.step(*b)
+    outs = {}
+    for key, graph, be, clip in (("eager", False, 40_000, 1.0), ("graph", True, 40_000, 1.0),
+                                 ("nc_small", True, 40_000, None), ("nc_big", True, None, None)):
+        _, m, e, d = _dp_engine(cuda_device, 9, graph=graph, clip=clip, wire="bf16", bucket_elems=be)
+        for b in batches:
+            e.step(*b)
+        K.check_status()
+        outs[key] = m.arena.params.clone()
+    assert torch.equal(outs["eager"], outs["graph"])
+    assert torch.equal(outs["nc_small"], outs["nc_big"])
+    diff = (outs["graph"].float() - m0.arena.params.float()).abs().max().item()
+    assert diff < 2e-2, diff
+
+
+def test_sharded_checkpoint_of_bucketed_optimizer_state_resumes(cuda_device, tmp_path):
+    from frankentorch_b200.models.gpt import GPTConfig
+    from frankentorch_b200.serialize.state_dict import consolidate_shards
+    from frankentorch_b200.training.checkpoint import load_training_state, save_training_state
+    cfg = GPTConfig.preset("gpt-tiny")
+    batches = [_batch(cfg, 2, 128, seed=400 + i) for i in range(6)]
+    _, _, full, _ = _dp_engine(cuda_device, 3, graph=True, clip=1.0, wire="bf16", bucket_elems=40_000)
+    ref = [full.step(*b) for b in batches]
+    _, _, first, d1 = _dp_engine(cuda_device, 3, graph=True, clip=1.0, wire="bf16", bucket_elems=40_000)
+    head = [first.step(*b) for b in batches[:3]]
+    stem = str(tmp_path / "ck")
+    save_training_state(first, stem)
+    merged = consolidate_shards(stem, 1)
+    assert torch.equal(merged["optim.master"], d1.gather_master().cpu())
+    _, _, resumed, _ = _dp_engine(cuda_device, 77, graph=True, clip=1.0, wire="bf16", bucket_elems=40_000)
+    resumed.step(*batches[0])
+    load_training_state(resumed, stem)
+    tail = [resumed.step(*b) for b in batches[3:]]
+    assert head + tail == ref

@@ -11,8 +11,8 @@ import pytest
 import torch
 import torch.distributed as dist
 
-from frankentorch_b200.parallel.health import (DeviceWaitTimeout, HardenedDataParallel, PeerFailure, RankHealth,
-                                               device_status_error)
+from frankentorch_b200.parallel.health import (DeviceWaitTimeout, HardenedTrainer, PeerFailure, RankHealth,
+                                               device_status_error, gloo_max_agreement)
 
 
 def test_heartbeat_timeout_and_announced_failure():
@@ -44,42 +44,140 @@ def test_status_word_decoding():
 
 
 class _FakeDP:
-    def __init__(self, name):
-        self.name, self.calls = name, 0
+    def __init__(self, name, ok=True):
+        self.name, self.ok = name, ok
 
-    def reduce_and_update(self, *a, **k):
-        self.calls += 1
+    def step_ok(self):
+        return self.ok
+
+
+class _FakeEngine:
+    """The two things the policy needs from an engine: run a step, swap the data-parallel object."""
+
+    def __init__(self, dp):
+        self.dp, self.steps, self.device_steps, self.switched = dp, 0, 0, 0
+
+    def step(self, ids, targets, read_loss=True):
+        self.steps += 1
+        return float(self.steps)
+
+    def step_device(self, read_loss=False):
+        self.device_steps += 1
+        return -1.0
+
+    def switch_data_parallel(self, factory):
+        self.dp = factory()
+        self.switched += 1
+
+
+class _Ledger:
+    def __init__(self):
+        self.rows = []
+
+    def record(self, kind, summary, detail):
+        self.rows.append((kind, summary, detail))
 
 
 def test_strict_raises_and_hardened_falls_back():
     status = [0]
-    strict = HardenedDataParallel(_FakeDP("fused"), lambda: _FakeDP("nccl"), mode="strict",
-                                  read_status=lambda: status[0], check_every=2)
-    strict.reduce_and_update()
-    strict.reduce_and_update()
+    strict = HardenedTrainer(_FakeEngine(_FakeDP("fused")), lambda: _FakeDP("nccl"), mode="strict",
+                             read_status=lambda: status[0], check_every=2)
+    strict.step(None, None)
+    strict.step(None, None)
     status[0] = 5 | (3 << 8)
-    strict.reduce_and_update()
+    strict.step(None, None)                       # odd step: not polled
     with pytest.raises(DeviceWaitTimeout):
-        strict.reduce_and_update()
+        strict.step(None, None)
 
-    class Ledger:
-        def __init__(self):
-            self.rows = []
-
-        def record(self, kind, summary, detail):
-            self.rows.append((kind, summary, detail))
-    led = Ledger()
+    led = _Ledger()
     status[0] = 0
-    hard = HardenedDataParallel(_FakeDP("fused"), lambda: _FakeDP("nccl"), mode="hardened",
-                                read_status=lambda: status[0], check_every=1, ledger=led)
-    hard.reduce_and_update()
-    assert hard.active.name == "fused" and not hard.fell_back
+    eng = _FakeEngine(_FakeDP("fused", ok=False))
+    hard = HardenedTrainer(eng, lambda: _FakeDP("nccl"), mode="hardened", read_status=lambda: status[0],
+                           check_every=1, ledger=led)
+    assert hard.step(None, None) == 1.0 and eng.dp.name == "fused" and not hard.fell_back
     status[0] = 5
-    hard.reduce_and_update()
-    assert hard.fell_back and hard.active.name == "nccl" and hard.active.calls == 1
+    # the failed step updated nothing (step_ok() is False): it is run again on the fallback path
+    assert hard.step(None, None) == -1.0
+    assert hard.fell_back and eng.dp.name == "nccl" and eng.switched == 1 and eng.device_steps == 1
     assert led.rows and led.rows[0][0] == "durability" and hard.events[0]["code"] == 5
-    hard.reduce_and_update()           # no more polling after the fallback
-    assert hard.active.calls == 2
+    assert hard.events[0]["last_step_rerun"] is True
+    hard.step(None, None)                         # no more polling after the fallback
+    assert eng.switched == 1 and eng.device_steps == 1
+
+
+def _agree_main(rank, world, port, q):
+    """gloo ranks: only rank 1's device reports a timeout; both must take the fallback branch."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=__import__("datetime").timedelta(seconds=60))
+    eng = _FakeEngine(_FakeDP("fused", ok=True))
+    status = [0]
+    tr = HardenedTrainer(eng, lambda: _FakeDP("nccl"), mode="hardened", read_status=lambda: status[0],
+                         agree=gloo_max_agreement(dist.group.WORLD), check_every=1)
+    tr.step(None, None)
+    if rank == 1:
+        status[0] = 5 | (9 << 8)
+    tr.step(None, None)
+    q.put((rank, tr.fell_back, eng.dp.name, tr.events[0]["local_status"], tr.events[0]["agreed_status"]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_agree_on_the_fallback_over_a_host_group():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29950 + os.getpid() % 40
+    procs = [ctx.Process(target=_agree_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        item = q.get(timeout=90)
+        res[item[0]] = item
+    for p in procs:
+        p.join(timeout=30)
+        assert not p.is_alive()
+    assert res[0][1:] == (True, "nccl", 0, 5 | (9 << 8))
+    assert res[1][1:] == (True, "nccl", 5 | (9 << 8), 5 | (9 << 8))
+
+
+@pytest.mark.gpu
+def test_hardened_fallback_through_the_real_engine(cuda_device):
+    """World of one on a real GPU: a reported timeout (injected through the status reader, no kernel
+    is made to wait) makes the engine leave its captured graph, gather the sharded optimizer state
+    back into the arena and continue on the library path; training goes on from the same state."""
+    from frankentorch_b200.autograd.tape import TensorTape
+    from frankentorch_b200.models.gpt import GPT, GPTConfig
+    from frankentorch_b200.ops import kernels as K
+    from frankentorch_b200.parallel.data_parallel import FusedDataParallel, NcclDataParallel
+    from frankentorch_b200.training.engine import OptimConfig, TrainEngine
+    cfg = GPTConfig.preset("gpt-tiny")
+
+    def make(peer):
+        tape = TensorTape(grad_dtype=None)
+        tape.accumulate_fn = lambda a, b: K.add(a, b) if (a.dtype == torch.bfloat16 and a.is_cuda) else a + b
+        model = GPT(cfg, tape, device=cuda_device, seed=3, peer_visible=peer)
+        dp = FusedDataParallel(model.arena, None, cuda_device, wire="fp32", bucket_elems=40_000) if peer else None
+        return model, TrainEngine(model, 2, 128, OptimConfig(lr=1e-3, grad_clip=None), use_cuda_graph=True, dp=dp)
+    g = torch.Generator().manual_seed(5)
+    tok = torch.randint(0, cfg.vocab_size, (2, 129), generator=g)
+    ids, tgt = tok[:, :-1].contiguous().pin_memory(), tok[:, 1:].contiguous().pin_memory()
+    m_ref, e_ref = make(False)
+    ref = [e_ref.step(ids, tgt) for _ in range(6)]
+    model, eng = make(True)
+    status = [0]
+    led = _Ledger()
+    tr = HardenedTrainer(eng, lambda: NcclDataParallel(model.arena, None, cuda_device), mode="hardened",
+                         read_status=lambda: status[0], check_every=1, ledger=led)
+    got = [tr.step(ids, tgt) for _ in range(3)]
+    status[0] = 5
+    got += [tr.step(ids, tgt) for _ in range(3)]
+    K.check_status()
+    assert tr.fell_back and isinstance(eng.dp, NcclDataParallel) and not eng.use_graph
+    assert model.arena.master is not None and model.arena.m is not None
+    assert led.rows and tr.events[0]["last_step_rerun"] is False
+    assert got == ref, (got, ref)
+    assert torch.equal(model.arena.params, m_ref.arena.params)
 
 
 def _rank_main(rank, world, port, q):

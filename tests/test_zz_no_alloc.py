@@ -61,3 +61,19 @@ def test_noalloc_colsum_rejects_oversized_problem(cuda_device):
     assert rc == -20
     assert b"exceeds the built-in scratch" in lib.ftk_noalloc_strerror(rc)
     assert lib.ftk_colsum_bf16_noalloc(None, out.data_ptr(), 8, 8, 8, 0, None) == -2
+
+
+def test_noalloc_colsum_rejects_misaligned_pointers_and_too_many_row_blocks(cuda_device):
+    """Host-side rejections only: nothing may reach the device for these arguments."""
+    lib = _lib()
+    x = torch.zeros(16, 16, dtype=torch.bfloat16, device=cuda_device)
+    out = torch.zeros(16, dtype=torch.float32, device=cuda_device)
+    # a bf16 view that starts at an odd element is 2-byte but not 4-byte aligned
+    assert lib.ftk_colsum_bf16_noalloc(x.data_ptr() + 2, out.data_ptr(), 8, 8, 16, 0, None) == -2
+    assert lib.ftk_colsum_bf16_noalloc(x.data_ptr(), out.data_ptr() + 2, 8, 8, 16, 0, None) == -2
+    # 5,000,000 rows of 2 columns fit the scratch (78,125 * 2 floats) but need 78,125 row blocks
+    assert lib.ftk_colsum_bf16_noalloc(x.data_ptr(), out.data_ptr(), 5_000_000, 2, 2, 1, None) == -20
+    # rows near INT_MAX must not overflow the block count
+    assert lib.ftk_colsum_bf16_noalloc(x.data_ptr(), out.data_ptr(), 2**31 - 1, 2, 2, 0, None) == -20
+    torch.cuda.synchronize()
+    assert float(out.abs().sum()) == 0.0
