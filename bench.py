@@ -11,6 +11,14 @@ sequence length 1024 (GPT-2 small, data parallel) by default; ``--model`` select
 named configs.  Data is synthetic (tokens uniform over the vocabulary), weights are
 random-init.
 
+``vs_torch`` is a head-to-head with stock PyTorch (``benchmarks/torch_baseline.py``: DDP for the
+data-parallel config, FSDP for the ZeRO-3 one) sampled in the same invocation, the two arms
+interleaved in a balanced-square slot order, each arm's first-half / second-half null checked,
+the incumbent's version reported by the arm itself.  On more than one GPU ``multi_gpu_check``
+holds the fused gradient reduction against an NCCL all-reduce of the same gradients and against
+its own replay (a failure makes the exit code non-zero), and ``exposed_comm_ms_per_step`` is the
+time the compute stream waited for communication in the last step (GPU timer marks).
+
 Two numbers are reported.  ``value`` times K optimizer steps with CUDA events on the
 launching stream (inputs already on the device).  ``e2e`` times K calls of the public
 ``TrainEngine.step(ids, targets)`` API, which every step copies that step's tokens and
@@ -56,6 +64,9 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-torch-arm", action="store_true",
+                    help="skip the interleaved stock-PyTorch arm (DDP for dp, FSDP for zero3) that fills vs_torch")
+    ap.add_argument("--h2h-steps", type=int, default=5, help="optimizer steps per head-to-head sample")
     ap.add_argument("--log-jsonl", default="", help="append a structured ft-conformance-log-v1 record of this run")
     ap.add_argument("--parallelism", default="", choices=["", "dp", "tp", "zero3", "ep"],
                     help="default: the one the named config asks for")
@@ -176,6 +187,33 @@ class ClockSampler:
         return out
 
 
+def multi_gpu_check(engine, dp, dist, torch):
+    """Outside the timed region, on the gradients of one more step: the fused reduce-scatter against an
+    NCCL all-reduce of the same gradients, and a second run of the reduction against the first, bit for bit."""
+    from frankentorch_b200.ops import kernels as K
+    engine.step_device(read_loss=False)
+    torch.cuda.synchronize()
+    a = engine.model.arena
+    fused = dp._gather(dp.gshard)                        # reduced gradients, arena order, fp32
+    ref = a.grads.detach().clone()
+    dist.all_reduce(ref, op=dist.ReduceOp.AVG)
+    scale = float(ref.abs().max().clamp_min(1e-30))
+    diff = float((fused[: ref.numel()] - ref).abs().max()) / scale
+    first = dp.gshard.clone()
+    dp.begin_step()                                      # applies the pending update, advances the sequence
+    for b in reversed(range(len(dp.buckets))):
+        dp._launch_bucket(b)
+    torch.cuda.current_stream().wait_stream(dp.comm_stream)
+    torch.cuda.synchronize()
+    K.check_status()
+    same = torch.tensor([1 if torch.equal(first, dp.gshard) else 0], device=first.device)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    tol = 8e-3 if dp.wire == "bf16" else 1e-5
+    return {"reduced_grad_max_abs_diff_over_max": diff, "tolerance": tol, "wire": dp.wire,
+            "bit_identical_replay": bool(int(same)), "buckets": len(dp.buckets),
+            "ok": bool(diff <= tol and int(same) == 1)}
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -239,6 +277,8 @@ def main():
     if world > 1:
         from frankentorch_b200.parallel.data_parallel import FusedDataParallel, NcclDataParallel
         dp = (NcclDataParallel if args.dp_impl == "nccl" else FusedDataParallel)(model.arena, dist.group.WORLD, dev)
+    if dp is not None and hasattr(dp, "record_stamps"):
+        dp.record_stamps = True      # four one-thread time-mark kernels per step: the exposed-communication figure
     engine = TrainEngine(model, mb, seq, OptimConfig(lr=3e-4, grad_clip=1.0), use_cuda_graph=not args.no_graph, dp=dp)
 
     # synthetic data: tokens uniform over the vocabulary, a fresh pinned batch per step
@@ -289,8 +329,61 @@ def main():
             losses.append(engine.step(ids, tg, read_loss=True))
         sync_all()
         e2e_ms = (time.perf_counter() - t0) * 1e3
-    clocks = sampler.stop()
+    clocks = sampler.stop()          # the clock record covers the two timed regions above, nothing else
+    exposed_ms = dp.exposed_ms() if (dp is not None and hasattr(dp, "exposed_ms")) else None
+    if hasattr(engine, "sync_parameters"):
+        engine.sync_parameters()
     K.check_status()
+
+    # ---------------- head to head with stock PyTorch, interleaved in the balanced-square slot order
+    vs_torch = None
+    if not args.no_torch_arm and par in ("dp", "zero3") and preset in ("gpt2-small", "gpt2-medium", "gpt-tiny"):
+        from benchmarks.torch_baseline import TorchArm
+        from frankentorch_b200 import harness as H
+        try:
+            arm = TorchArm(preset, dev, world, rank, parallel="fsdp" if par == "zero3" else "ddp",
+                           micro_batch=mb, seq_len=seq)
+            version = H.require_reported_version(arm.version_line())     # the arm reports it; no ratio without it
+            for _ in range(3):
+                arm.step()
+            hs = max(1, args.h2h_steps)
+            h2h_sampler = ClockSampler(local_rank, "GPU-" + str(getattr(torch.cuda.get_device_properties(dev), "uuid", "")))
+            h2h_sampler.start()
+
+            def _max_ms(ms):
+                t = torch.tensor([ms], dtype=torch.float64, device=dev)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                return float(t) / hs
+
+            def ours_sample():
+                sync_all()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(hs):
+                    engine.step_device(read_loss=False)
+                b.record()
+                torch.cuda.synchronize()
+                return _max_ms(a.elapsed_time(b))
+
+            def torch_sample():
+                sync_all()
+                return _max_ms(arm.timed_block(hs))
+            res = H.run_balanced_square(ours_sample, torch_sample, rounds=2,
+                                        ours_steps=("forward", "backward", "clip", "optimizer"),
+                                        incumbent_steps=H.parse_timed_steps(arm.timed_steps_line()) or ())
+            vs_torch = dict(res.as_dict(), impl=arm.impl, steps_per_sample=hs, clocks=h2h_sampler.stop(),
+                            **H.incumbent_provenance_block(version))
+            arm.release()
+            if hasattr(engine, "sync_parameters"):
+                engine.sync_parameters()
+        except H.MissingIncumbentVersion as e:
+            vs_torch = {"refused": str(e)}
+    K.check_status()
+
+    mgc = None
+    if world > 1 and dp is not None and hasattr(dp, "gshard"):
+        mgc = multi_gpu_check(engine, dp, dist, torch)
 
     times = torch.tensor([dev_ms, e2e_ms if e2e_ms is not None else 0.0], dtype=torch.float64, device=dev)
     if world > 1:
@@ -331,7 +424,12 @@ def main():
         "gpu_launches": engine.launches_per_step * args.steps,
         "gpu_launches_per_step": engine.launches_per_step,
         "final_loss": losses[-1] if losses and losses[-1] is not None else None,
+        "vs_torch": vs_torch,
     }
+    if exposed_ms is not None:
+        out["exposed_comm_ms_per_step"] = exposed_ms
+    if mgc is not None:
+        out["multi_gpu_check"] = mgc
     if e2e_ms is not None:
         out["e2e"] = {
             "value": tokens_per_step * args.steps / (e2e_max / 1e3),
@@ -349,6 +447,8 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if mgc is not None and not mgc["ok"]:
+        return 3
     return 0
 
 

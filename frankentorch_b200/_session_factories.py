@@ -222,6 +222,16 @@ def functional_dropout(self, nid, p=0.5, training=True):
         return nid
     if not (0.0 <= p < 1.0):
         raise ValueError("dropout p must be in [0, 1)")
+    x = self.tensor(nid)
+    if self.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous():
+        # GPU backend: counter-based Philox mask (seed = the session seed, offset = elements drawn so far),
+        # regenerated by the backward pass instead of being stored
+        from .ops import fused as F
+        off = self._dropout_calls
+        self._dropout_calls += x.numel()
+        rg = self.tensor_tape.grad_enabled and self.tensor_tape.nodes[nid].requires_grad
+        self._record_dispatch("dropout", rg, launched="ftk::dropout_kernel<philox>")
+        return F.dropout(self.tensor_tape, nid, float(p), int(self._seed), off)
     mask = (self.rng.uniform(self.tensor_numel(nid)).reshape(self.tensor_shape(nid)) > p).to(torch.float64) / (1.0 - p)
     m = _new(self, mask, False, self.tensor_dtype(nid))
     return self.tensor_mul(nid, m)
@@ -337,7 +347,10 @@ def tensor_to_f64(self, a):
 
 
 def tensor_contiguous(self, a):
-    return self.tensor_reshape(a, shape=tuple(self.tensor_shape(a)))
+    """A dense row-major copy when ``a`` is a strided view, ``a`` itself otherwise."""
+    if self.tensor(a).is_contiguous():
+        return a
+    return self._apply("contiguous", [a])
 
 
 def tensor_split(self, a, split_size, dim=0):

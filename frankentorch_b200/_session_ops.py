@@ -2,8 +2,11 @@
 
 The tensor operators are generated from the VJP rule table: ``tensor_<op>(ids..., **params)``
 runs the forward, records a dispatch decision in the ledger and appends a tape node whose
-backward is the table's rule.  On the CUDA device the hot operators route to the fused
-sm_100a kernels instead (``ops/fused.py``).
+backward is the table's rule.  On the CPU device forward and backward are PyTorch CPU operators
+(f64).  On the CUDA device the entry point first asks the sm_100a kernel registry
+(``dispatch/sm100.py``): a registered operator with qualifying operands runs the hand-written
+kernels of ``ops/fused.py``; an operator without a kernel is an error in strict mode and a
+ledger-recorded PyTorch fallback in hardened mode.
 """
 from __future__ import annotations
 
@@ -37,7 +40,23 @@ def _apply(self, name: str, inputs: Sequence[int], **kw) -> int:
         cast_back = vals[0].dtype
         vals = [v.to(self._autocast.to_torch()) if v.is_floating_point() else v for v in vals]
     rg = tape.grad_enabled and any(tape.nodes[i].requires_grad for i in inputs)
-    self._record_dispatch(name, rg)
+    if self.is_cuda:
+        from .dispatch import sm100
+        route = sm100.ROUTES.get(name)
+        if route is not None and self._autocast is None:
+            res = route(self, list(inputs), vals, kw)
+            if res is not None:
+                self._record_dispatch(name, rg, launched=res[1])
+                return res[0]
+        if name in sm100.LAYOUT_OPS:
+            self._record_dispatch(name, rg, launched=f"layout::{name}")
+        else:
+            why = "no route" if route is None else "operands do not qualify (dtype / layout / extents)"
+            if self.runtime.mode.value != "hardened" or not sm100.fallback_allowed("hardened"):
+                raise sm100.NoKernelForBackend(name, why)
+            self._record_dispatch(name, rg, launched=f"torch::{name}", deviation=sm100.DEVIATION_ID)
+    else:
+        self._record_dispatch(name, rg)
     out = op.fwd(*vals, **kw)
     if cast_back is not None:
         out = out.to(cast_back)

@@ -129,6 +129,7 @@ OPS["cumprod"] = OpDef("cumprod", lambda x, dim=0: torch.cumprod(x, dim),
 # ---------------------------------------------------------------------------------- shape
 _reg("reshape", lambda x, shape=(): x.reshape(tuple(shape)), lambda g, i, o, kw: [g.reshape(i[0].shape)],
      "d(shape_op(x))/dx=identity")
+_reg("contiguous", lambda x: x.contiguous(), lambda g, i, o, kw: [g], "d(shape_op(x))/dx=identity")
 _reg("view", lambda x, shape=(): x.reshape(tuple(shape)), lambda g, i, o, kw: [g.reshape(i[0].shape)],
      "d(shape_op(x))/dx=identity")
 _reg("squeeze", lambda x, dim=None: x.squeeze() if dim is None else x.squeeze(dim),

@@ -313,6 +313,22 @@ class TensorTape:
     def clear_graph(self) -> None:
         self.truncate_graph_to(0)
 
+    def release_values(self, lo: int, hi: int) -> int:
+        """Drop the values, rules and saved tensors of the computed (non-leaf, non-retained) nodes with
+        ``lo <= id < hi`` whose backward has run, keeping the nodes themselves: ids stay valid for
+        bookkeeping, but the nodes can no longer be read or differentiated through.  Frees the
+        activations of one micro-batch while other graphs on the same tape are still needed.
+        Returns the number of nodes released."""
+        n = 0
+        for node in self.nodes[max(0, lo): max(0, min(hi, len(self.nodes)))]:
+            if node.is_leaf or node.retain_grad or node.value is None:
+                continue
+            node.value = None
+            node.vjp = None
+            node.saved = None
+            n += 1
+        return n
+
     # ------------------------------------------------------------------ hooks
     def register_tensor_hook(self, nid: int, fn: Callable[[torch.Tensor], Optional[torch.Tensor]]) -> TensorHookHandle:
         n = self._node(nid)

@@ -24,8 +24,16 @@
 //   dp_update      AdamW on the fp32 master shards of buckets [b0, b1) (math of
 //                  ft-optim/src/lib.rs:1040-1054) and peer stores of the updated bf16 values
 //                  into every rank's parameter arena; the last CTA publishes "parameters of
-//                  [b0, b1) from rank r are written".  Does nothing when the step was poisoned.
+//                  [b0, b1) from rank r are written".  The arithmetic is skipped when no update
+//                  is pending (first step, or a poisoned step); the flag is published regardless,
+//                  so the waits of a step never depend on whether the previous one was healthy.
 //   dp_wait_params waits until every peer has published the parameters of a bucket range.
+//
+// The update may be deferred: dp_norm, which ends a step, stores the hyper-parameters of that
+// step (learning rate, bias corrections, clip factor) next to a `pending` word, and the host
+// launches dp_update for each bucket at the start of the NEXT step on the communication stream,
+// in forward order, while the forward pass waits bucket by bucket (an event for the local part,
+// dp_wait_params for the peers' parts).  The all-gather then runs under the forward pass.
 //
 // Waiting kernels only ever wait for kernels that were launched earlier on the same stream or
 // that run on other GPUs, never for a later launch on this GPU.  Flags hold the sequence number
@@ -172,7 +180,7 @@ dp_push_kernel(DpPeers P, int b, const float* __restrict__ grads, unsigned int* 
 template <typename WireT>
 __global__ void __launch_bounds__(256)
 dp_reduce_kernel(DpPeers P, int b, float* __restrict__ gshard, float* __restrict__ partial_sumsq,
-                 const long long* __restrict__ seq_ptr, int* ok_word, int* status) {
+                 int partial_stride, const long long* __restrict__ seq_ptr, int* ok_word, int* status) {
   __shared__ float red[32];
   const FtkDpBucket bk = P.buckets[b];
   const unsigned long long seq = (unsigned long long)*seq_ptr;
@@ -214,8 +222,13 @@ dp_reduce_kernel(DpPeers P, int b, float* __restrict__ gshard, float* __restrict
     float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (threadIdx.x == 0) partial_sumsq[(long long)b * gridDim.x + blockIdx.x] = t;
+    if (threadIdx.x == 0) partial_sumsq[(long long)b * partial_stride + blockIdx.x] = t;
   }
+  // the bucket's row of partials has room for the largest grid; entries beyond this launch's grid
+  // must read as zero whatever an earlier, wider launch left there
+  if (blockIdx.x == 0)
+    for (int i = gridDim.x + threadIdx.x; i < partial_stride; i += blockDim.x)
+      partial_sumsq[(long long)b * partial_stride + i] = 0.f;
 }
 
 // ----------------------------------------------------------------------------------- norm
@@ -224,7 +237,8 @@ dp_reduce_kernel(DpPeers P, int b, float* __restrict__ gshard, float* __restrict
 __global__ void __launch_bounds__(32)
 dp_norm_kernel(DpPeers P, const float* __restrict__ partial_sumsq, int n_partial, float max_norm,
                float* __restrict__ hyper, float* __restrict__ norm_out,
-               const long long* __restrict__ seq_ptr, int* ok_word, int* status) {
+               const long long* __restrict__ seq_ptr, int* ok_word, int* status, int* pending,
+               float* __restrict__ hyper_pending) {
   const unsigned long long seq = (unsigned long long)*seq_ptr;
   float s = 0.f;
   if (threadIdx.x == 0) {
@@ -260,6 +274,12 @@ dp_norm_kernel(DpPeers P, const float* __restrict__ partial_sumsq, int n_partial
     }
     hyper[3] = ok ? c : 0.f;
     *ok_word = ok ? 1 : 0;
+    // what the (possibly deferred) update of this step's gradients will use
+    hyper_pending[0] = hyper[0];
+    hyper_pending[1] = hyper[1];
+    hyper_pending[2] = hyper[2];
+    hyper_pending[3] = ok ? c : 0.f;
+    *pending = ok ? 1 : 0;
   }
 }
 
@@ -268,14 +288,14 @@ __global__ void __launch_bounds__(256)
 dp_update_kernel(DpPeers P, int b0, int b1, float* __restrict__ master, float* __restrict__ m,
                  float* __restrict__ v, const float* __restrict__ gshard, const float* __restrict__ hyper,
                  float b1c, float b2c, float eps, float wd, unsigned int* counters,
-                 const long long* __restrict__ seq_ptr, const int* __restrict__ ok_word) {
-  // a poisoned step leaves master, moments and parameters exactly as they were (and publishes
-  // nothing: the peers' bounded waits then report the failure too)
-  if (*ok_word == 0) return;
+                 const long long* __restrict__ seq_ptr, const int* __restrict__ pending) {
+  // with nothing pending (first step, or a poisoned step) master, moments and parameters stay
+  // exactly as they were; the flag below is published all the same
+  const bool live = *pending != 0;
   const unsigned long long seq = (unsigned long long)*seq_ptr;
   const float lr = hyper[0], bc1 = hyper[1], bc2 = hyper[2], gscale = hyper[3];
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (int b = b0; b < b1; ++b) {
+  for (int b = b0; live && b < b1; ++b) {
     const FtkDpBucket bk = P.buckets[b];
     const long long mine = bk.lo + (long long)P.rank * bk.shard;
     long long n_valid = bk.hi - mine;
@@ -327,6 +347,7 @@ __global__ void dp_begin_step_kernel(long long* seq, int* ok_word) {
   *seq += 1;
   *ok_word = 1;
 }
+__global__ void dp_clear_pending_kernel(int* pending) { *pending = 0; }
 
 }  // namespace ftk
 
@@ -386,21 +407,22 @@ extern "C" int ftk_dp_begin_step(const FtkDpComm* c, void* stream) {
 }
 
 // Push this rank's gradients of bucket b to the owners and reduce the shard this rank owns.
-extern "C" int ftk_dp_bucket_reduce(const FtkDpComm* c, int b, const float* grads, void* stream) {
+extern "C" int ftk_dp_bucket_reduce(const FtkDpComm* c, int b, const float* grads, int n_ctas, void* stream) {
   DpPeers P;
   int rc = fill_peers(c, &P);
   if (rc) return rc;
-  if (b < 0 || b >= c->n_buckets || !grads) return -2;
+  if (b < 0 || b >= c->n_buckets || !grads || n_ctas < 1 || n_ctas > c->n_ctas) return -2;
   int* status = ftk_status_word();
   if (!status) return -6;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (c->wire_fp32) {
-    dp_push_kernel<float><<<c->n_ctas, 256, 0, s>>>(P, b, grads, c->counters, c->seq);
-    dp_reduce_kernel<float><<<c->n_ctas, 256, 0, s>>>(P, b, c->gshard, c->partial, c->seq, c->ok_word, status);
+    dp_push_kernel<float><<<n_ctas, 256, 0, s>>>(P, b, grads, c->counters, c->seq);
+    dp_reduce_kernel<float><<<n_ctas, 256, 0, s>>>(P, b, c->gshard, c->partial, c->n_ctas, c->seq, c->ok_word,
+                                                   status);
   } else {
-    dp_push_kernel<__nv_bfloat16><<<c->n_ctas, 256, 0, s>>>(P, b, grads, c->counters, c->seq);
-    dp_reduce_kernel<__nv_bfloat16><<<c->n_ctas, 256, 0, s>>>(P, b, c->gshard, c->partial, c->seq, c->ok_word,
-                                                            status);
+    dp_push_kernel<__nv_bfloat16><<<n_ctas, 256, 0, s>>>(P, b, grads, c->counters, c->seq);
+    dp_reduce_kernel<__nv_bfloat16><<<n_ctas, 256, 0, s>>>(P, b, c->gshard, c->partial, c->n_ctas, c->seq,
+                                                           c->ok_word, status);
   }
   return (int)cudaPeekAtLastError();
 }
@@ -411,20 +433,29 @@ extern "C" int ftk_dp_norm(const FtkDpComm* c, float max_norm, float* hyper, flo
   if (rc) return rc;
   int* status = ftk_status_word();
   if (!status) return -6;
+  if (!c->pending || !c->hyper_pending) return -2;
   dp_norm_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      P, c->partial, c->n_buckets * c->n_ctas, max_norm, hyper, norm_out, c->seq, c->ok_word, status);
+      P, c->partial, c->n_buckets * c->n_ctas, max_norm, hyper, norm_out, c->seq, c->ok_word, status, c->pending,
+      c->hyper_pending);
   return (int)cudaPeekAtLastError();
 }
 
+// Applies the pending update (hyper-parameters stored by the last ftk_dp_norm) to buckets [b0, b1).
 extern "C" int ftk_dp_update(const FtkDpComm* c, int b0, int b1, float* master, float* m, float* v,
-                             const float* hyper, float beta1, float beta2, float eps, float wd, int n_ctas,
-                             void* stream) {
+                             float beta1, float beta2, float eps, float wd, int n_ctas, void* stream) {
   DpPeers P;
   int rc = fill_peers(c, &P);
   if (rc) return rc;
-  if (b0 < 0 || b1 > c->n_buckets || b0 >= b1 || n_ctas < 1) return -2;
+  if (b0 < 0 || b1 > c->n_buckets || b0 >= b1 || n_ctas < 1 || !c->pending || !c->hyper_pending) return -2;
   dp_update_kernel<<<n_ctas, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      P, b0, b1, master, m, v, c->gshard, hyper, beta1, beta2, eps, wd, c->counters, c->seq, c->ok_word);
+      P, b0, b1, master, m, v, c->gshard, c->hyper_pending, beta1, beta2, eps, wd, c->counters, c->seq,
+      c->pending);
+  return (int)cudaPeekAtLastError();
+}
+
+extern "C" int ftk_dp_clear_pending(const FtkDpComm* c, void* stream) {
+  if (!c || !c->pending) return -2;
+  dp_clear_pending_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(c->pending);
   return (int)cudaPeekAtLastError();
 }
 

@@ -435,6 +435,18 @@ extern "C" int ftk_adamw_dev(float* master, void* shadow, const float* grad, flo
                                                                       hyper, b1, b2, eps, wd);
   return (int)cudaGetLastError();
 }
+// One thread stores the GPU's nanosecond timer: a time mark inside a stream (or a captured graph),
+// for measuring how long a stream sat between two points without a host round trip.
+__global__ void timestamp_kernel(unsigned long long* out) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  *out = t;
+}
+extern "C" int ftk_timestamp(unsigned long long* out, void* stream) {
+  if (!out) return -2;
+  timestamp_kernel<<<1, 1, 0, STREAM(stream)>>>(out);
+  return (int)cudaGetLastError();
+}
 extern "C" int ftk_fill_f32(float* x, long long n, float v, void* stream) {
   if (n <= 0) return -2;
   fill_f32_kernel<<<ew_grid(n, 256), 256, 0, STREAM(stream)>>>(x, n, v);

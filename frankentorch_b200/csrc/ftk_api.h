@@ -241,6 +241,8 @@ int ftk_adamw_dev(float* master, void* shadow_bf16, const float* grad, float* m,
                   const float* hyper, float beta1, float beta2, float eps, float weight_decay,
                   void* stream);
 int ftk_fill_f32(float* x, long long n, float v, void* stream);
+// *out = %globaltimer (ns) when the stream reaches this point (capturable in a CUDA graph).
+int ftk_timestamp(unsigned long long* out, void* stream);
 #ifdef __cplusplus
 }
 #endif
@@ -264,8 +266,10 @@ typedef struct {
 //   slots : fp32 [FTK_DP_MAX_RANKS]
 //   inbox : wire type (bf16, or fp32 when wire_fp32) [world * sum of shards]
 // Local device memory: buckets (table of n_buckets entries), gshard fp32 [sum of shards],
-// partial fp32 [n_buckets * n_ctas], counters u32 [2 * FTK_DP_MAX_BUCKETS] (zero-initialised),
-// seq (step sequence number, advanced by ftk_dp_begin_step), ok_word (1 = step healthy).
+// partial fp32 [n_buckets * n_ctas] (n_ctas = the widest grid any bucket is launched with),
+// counters u32 [2 * FTK_DP_MAX_BUCKETS] (zero-initialised), seq (step sequence number, advanced
+// by ftk_dp_begin_step), ok_word (1 = step healthy), pending (1 = reduced gradients wait for their
+// update), hyper_pending fp32[4] (the hyper-parameters that update will use).
 typedef struct {
   void* const* inbox;
   void* const* params;
@@ -278,12 +282,15 @@ typedef struct {
   unsigned int* counters;
   long long* seq;
   int* ok_word;
+  int* pending;
+  float* hyper_pending;
 } FtkDpComm;
 int ftk_dp_begin_step(const FtkDpComm* c, void* stream);
-int ftk_dp_bucket_reduce(const FtkDpComm* c, int bucket, const float* grads, void* stream);
+int ftk_dp_bucket_reduce(const FtkDpComm* c, int bucket, const float* grads, int n_ctas, void* stream);
 int ftk_dp_norm(const FtkDpComm* c, float max_norm, float* hyper, float* norm_out, void* stream);
-int ftk_dp_update(const FtkDpComm* c, int b0, int b1, float* master, float* m, float* v, const float* hyper,
+int ftk_dp_update(const FtkDpComm* c, int b0, int b1, float* master, float* m, float* v,
                   float beta1, float beta2, float eps, float weight_decay, int n_ctas, void* stream);
+int ftk_dp_clear_pending(const FtkDpComm* c, void* stream);
 int ftk_dp_wait_params(const FtkDpComm* c, int b0, void* stream);
 #ifdef __cplusplus
 }

@@ -157,20 +157,28 @@ class DispatchDecision:
     backend_key: DispatchKey
     keyset_bits: int
     fallback_used: bool
+    deviation: Optional[str] = None      # allow-list id of the hardened-mode deviation that fired, if any
 
     def summary(self) -> str:
-        return (f"op={self.op} mode={self.mode.value} kernel={self.kernel} dispatch_key={self.selected_key.name} "
-                f"backend_key={self.backend_key.name} keyset_bits=0x{self.keyset_bits:x} "
-                f"fallback_path={str(self.fallback_used).lower()}")
+        s = (f"op={self.op} mode={self.mode.value} kernel={self.kernel} dispatch_key={self.selected_key.name} "
+             f"backend_key={self.backend_key.name} keyset_bits=0x{self.keyset_bits:x} "
+             f"fallback_path={str(self.fallback_used).lower()}")
+        return s + (f" deviation={self.deviation}" if self.deviation else "")
 
 
 _KERNEL_NS = {DispatchKey.AutogradCPU: "autograd_cpu", DispatchKey.CPU: "cpu",
               DispatchKey.AutogradSM100: "autograd_sm100", DispatchKey.SM100: "sm100"}
 
 
-def decide(op: str, mode: ExecutionMode, keyset: DispatchKeySet, kernel_suffix: str) -> DispatchDecision:
+def decide(op: str, mode: ExecutionMode, keyset: DispatchKeySet, kernel_suffix: str, *,
+           kernel: Optional[str] = None, deviation: Optional[str] = None) -> DispatchDecision:
+    """Resolve the key set and name the kernel.  ``kernel`` (a full name such as
+    ``ftk::norm_fwd_kernel<layer_norm>``) replaces the default ``<namespace>::<suffix>`` string when the
+    caller knows which kernel it launched; ``deviation`` marks a hardened-mode fallback."""
     selected, backend, effective, fallback = resolve(mode, keyset)
-    return DispatchDecision(op, mode, f"{_KERNEL_NS[effective]}::{kernel_suffix}", selected, backend, keyset.bits, fallback)
+    name = kernel if kernel is not None else f"{_KERNEL_NS[effective]}::{kernel_suffix}"
+    return DispatchDecision(op, mode, name, selected, backend, keyset.bits, fallback or deviation is not None,
+                            deviation)
 
 
 def ensure_meta_compatible(lhs_dtype: DType, rhs_dtype: DType, lhs_device: Device, rhs_device: Device) -> None:

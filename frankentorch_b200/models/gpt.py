@@ -152,6 +152,9 @@ class GPT:
             tape.bind_grad_buffer(nid, self.arena.view(self.arena.grads, name))
             self.leaf[name] = nid
         self.param_boundary = len(tape)
+        # set by the training engine: called with a parameter name before the forward pass reads that
+        # parameter (and everything before it in the arena), see FusedDataParallel.gate_param
+        self.param_gate = None
 
     def _init_weights(self, seed: int) -> None:
         cfg, a = self.cfg, self.arena
@@ -218,9 +221,14 @@ class GPT:
         """Record one training forward; returns the tape id of the scalar mean loss."""
         cfg, tape, P = self.cfg, self.tape, self.leaf
         B, S = ids.shape
+        gate = self.param_gate
+        if gate is not None:
+            gate("wpe.weight")
         x = F.embedding(tape, ids, P["wte.weight"], P["wpe.weight"], S)
         for l in range(cfg.n_layer):
             p = f"blocks.{l}."
+            if gate is not None:
+                gate(p + "mlp.fc2.bias")
             h = F.layernorm(tape, x, P[p + "ln1.weight"], P[p + "ln1.bias"], cfg.ln_eps)
             qkv = F.linear(tape, h, P[p + "attn.qkv_proj.weight"], P[p + "attn.qkv_proj.bias"])
             a = F.attention_packed(tape, qkv, cfg.n_head, causal=True)
@@ -228,6 +236,8 @@ class GPT:
             h = F.layernorm(tape, x, P[p + "ln2.weight"], P[p + "ln2.bias"], cfg.ln_eps)
             x = F.mlp_up_down(tape, h, P[p + "mlp.fc1.weight"], P[p + "mlp.fc1.bias"],
                               P[p + "mlp.fc2.weight"], P[p + "mlp.fc2.bias"], x, act=cfg.act)
+        if gate is not None:
+            gate("ln_f.bias")
         h = F.layernorm(tape, x, P["ln_f.weight"], P["ln_f.bias"], cfg.ln_eps)
         head = P["wte.weight"] if cfg.tie_lm_head else P["lm_head.weight"]
         return F.lm_head_cross_entropy(tape, h, head, targets, cfg.vocab_size)

@@ -136,6 +136,7 @@ def load(build_if_missing: bool = True):
         "ftk_clip_scale": [vp, f, vp, vp, vp],
         "ftk_adamw_dev": [vp, vp, vp, vp, vp, ll, vp, f, f, f, f, vp],
         "ftk_fill_f32": [vp, ll, f, vp],
+        "ftk_timestamp": [vp, vp],
         "ftk_present_rgba8": [vp, vp, i, i, ll, i, vp],
         "ftk_im2col_1d": [vp, vp, i, i, i, i, i, i, vp],
         "ftk_wait_probe": [vp, i, ll, vp, vp],

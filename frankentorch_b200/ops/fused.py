@@ -237,3 +237,135 @@ def lm_head_cross_entropy(tape: TensorTape, x: int, w: int, targets_ids: torch.T
 
     return tape.record("lm_head_ce", [x, w], loss.reshape(()), vjp,
                        RULE_LINEAR + " [+softmax-cross-entropy, mean]")
+
+
+# ----------------------------------------------------------------------------------------------
+# Single operators of the session surface (one kernel forward, one or two backward).  The composite
+# rules above are what the GPT models use; these give every hot session operator an sm_100a route.
+def matmul(tape: TensorTape, a: int, b: int) -> int:
+    """``a[M,K] @ b[K,N]`` (ft-autograd MatMul arm, ft-autograd/src/lib.rs:11953)."""
+    av, bv = tape.value(a), tape.value(b)
+    y = K.gemm(av, bv, b_mn=True)
+    a_needs, b_needs = tape.nodes[a].requires_grad, tape.nodes[b].requires_grad
+
+    def vjp(g, targets):
+        da = K.gemm(g, bv) if a_needs else None                         # dOut @ B^T
+        db = K.gemm(av, g, a_mn=True, b_mn=True) if b_needs else None   # A^T @ dOut
+        return [da, db]
+
+    return tape.record("matmul", [a, b], y, vjp, RULE_LINEAR)
+
+
+def bmm(tape: TensorTape, a: int, b: int) -> int:
+    """Batched ``a[L,M,K] @ b[L,K,N]`` on the strided-batched GEMM."""
+    av, bv = tape.value(a), tape.value(b)
+    L, M, Kd = av.shape
+    N = bv.shape[2]
+
+    def run(x, y, m, n, k, x_mn, y_mn):
+        out = torch.empty((L, m, n), dtype=torch.bfloat16, device=x.device)
+        K.gemm_batched(x, y, out, M=m, N=n, K=k, L0=L, L1=1, a_strides=(x.stride(1), x.stride(0), 0),
+                       b_strides=(y.stride(1), y.stride(0), 0), d_strides=(n, m * n, 0), a_mn=x_mn, b_mn=y_mn)
+        return out
+    y = run(av, bv, M, N, Kd, False, True)
+
+    def vjp(g, targets):
+        g = g.contiguous()
+        da = run(g, bv, M, Kd, N, False, False)      # dOut @ B^T  (B given as [K, N] = [n_out, k] row-major)
+        db = run(av, g, Kd, N, M, True, True)        # A^T @ dOut
+        return [da, db]
+
+    return tape.record("bmm", [a, b], y, vjp, "d(bmm(A,B))/dA=dOut@B^T; d(bmm(A,B))/dB=A^T@dOut (batched)")
+
+
+def gelu(tape: TensorTape, x: int, *, tanh_form: bool = False) -> int:
+    xv = tape.value(x)
+    y = K.gelu_fwd(xv, tanh_form=tanh_form)
+
+    def vjp(g, targets):
+        return [K.gelu_bwd(xv, g.contiguous(), tanh_form=tanh_form)]
+
+    return tape.record("gelu_tanh" if tanh_form else "gelu", [x], y, vjp, "d(gelu(x))/dx")
+
+
+def softmax_lastdim(tape: TensorTape, x: int) -> int:
+    """Row softmax over the last dimension (ft-kernel-cpu/src/lib.rs:18350; guards of fused.rs:321)."""
+    xv = tape.value(x)
+    y = K.softmax_rows(xv.reshape(-1, xv.shape[-1])).reshape(xv.shape)
+
+    def vjp(g, targets):
+        return [K.softmax_bwd(y, g.contiguous()).reshape(xv.shape)]
+
+    return tape.record("softmax", [x], y, vjp, "d(softmax(x))/dx_i=s_i*(grad_i-sum(grad*s))")
+
+
+def add_same_shape(tape: TensorTape, a: int, b: int) -> int:
+    y = K.add(tape.value(a), tape.value(b))
+    return tape.record("add", [a, b], y, lambda g, targets: [g, g], "d(a+b)/da=1; d(a+b)/db=1")
+
+
+def embedding_lookup(tape: TensorTape, w: int, ids: torch.Tensor) -> int:
+    """``w[ids]`` for an id tensor of any shape; backward is the deterministic sorted scatter-add."""
+    wv = tape.value(w)
+    flat = ids.reshape(-1).to(torch.int64)
+    out = K.embedding_fwd(flat, wv, None, flat.numel()).view(*ids.shape, wv.shape[1])
+
+    def vjp(go, targets):
+        dw = torch.zeros(wv.shape, dtype=torch.float32, device=wv.device)
+        K.embedding_bwd(flat, go.reshape(-1, go.shape[-1]).contiguous(), dw, None, flat.numel())
+        return [dw]
+
+    return tape.record("embedding", [w], out, vjp, "d(index_select(x))/dx=scatter_add_grad")
+
+
+def sdpa(tape: TensorTape, q: int, k: int, v: int, *, causal: bool, scale: Optional[float] = None) -> int:
+    """Flash attention on ``[..., S, hd]`` operands (``[N*H, S, hd]`` or ``[N, H, S, hd]``,
+    ft-nn/src/lib.rs:5145-5184); the kernels read them as ``[B, S, H, hd]`` views, no copies."""
+    qv, kv, vv = tape.value(q), tape.value(k), tape.value(v)
+
+    def as_bshd(t):
+        if t.dim() == 3:
+            return t.unsqueeze(2)                 # [L, S, 1, hd]
+        return t.transpose(1, 2)                  # [N, H, S, hd] -> [N, S, H, hd] view
+    q4, k4, v4 = as_bshd(qv), as_bshd(kv), as_bshd(vv)
+    o_store = torch.empty_like(qv)
+    o, lse = K.attention_fwd(q4, k4, v4, causal=causal, scale=scale, out=as_bshd(o_store))
+
+    def vjp(go, targets):
+        go_c = go.contiguous()
+        dq, dk, dv = torch.empty_like(qv), torch.empty_like(kv), torch.empty_like(vv)
+        K.attention_bwd(q4, k4, v4, o, lse, as_bshd(go_c), causal=causal, scale=scale,
+                        dq=as_bshd(dq), dk=as_bshd(dk), dv=as_bshd(dv))
+        return [dq, dk, dv]
+
+    return tape.record("sdpa", [q, k, v], o_store, vjp, "d(sdpa(q,k,v))/dq,dk,dv [flash, recompute P]")
+
+
+def cross_entropy_mean(tape: TensorTape, logits: int, targets_ids: torch.Tensor) -> int:
+    """``mean(cross_entropy(logits, targets))``; the logits node keeps its value (the gradient is
+    written to a second buffer), ft-kernel-cpu/src/lib.rs:6649/6679."""
+    lv = tape.value(logits)
+    rows, vocab = lv.shape
+    losses, dlogits = K.cross_entropy_fwd_bwd(lv, targets_ids.reshape(-1).to(torch.int64), vocab, 1.0 / rows,
+                                              inplace=False)
+    loss = K.reduce_mean(losses)
+
+    def vjp(g, targets):
+        if g.numel() == 1 and getattr(g, "_ft_unit_seed", False):
+            return [dlogits]
+        return [(dlogits.float() * g.reshape(()).float()).to(torch.bfloat16)]
+
+    return tape.record("cross_entropy", [logits], loss.reshape(()), vjp,
+                       "d(cross_entropy)/dlogits=g*(softmax-onehot)")
+
+
+def dropout(tape: TensorTape, x: int, p: float, seed: int, offset: int = 0) -> int:
+    """Philox dropout: the mask is a function of (seed, offset, element index), so backward
+    regenerates it by running the same kernel on the incoming gradient (ft-nn/src/lib.rs:2357-2373)."""
+    xv = tape.value(x)
+    y = K.dropout(xv, p, seed, offset)
+
+    def vjp(g, targets):
+        return [K.dropout(g.contiguous(), p, seed, offset)]
+
+    return tape.record("dropout", [x], y, vjp, "d(dropout(x))/dx=mask/(1-p)")

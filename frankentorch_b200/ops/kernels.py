@@ -443,6 +443,12 @@ def fill_f32(x, value=0.0):
     _chk(_lib.load().ftk_fill_f32(x.data_ptr(), x.numel(), float(value), _stream()), "ftk_fill_f32")
 
 
+def timestamp(out: torch.Tensor, index: int = 0, stream: Optional[int] = None) -> None:
+    """Store the GPU nanosecond timer into ``out[index]`` (int64) when the stream gets here."""
+    _chk(_lib.load().ftk_timestamp(out.data_ptr() + 8 * index, _stream() if stream is None else stream),
+         "ftk_timestamp")
+
+
 # --------------------------------------------------------------------------------------- misc
 def present_rgba8(src, width, height, row_bytes, half=False):
     dst = torch.empty((height, width, 4), dtype=torch.float16 if half else torch.float32, device=src.device)

@@ -3,9 +3,16 @@
 The reference has no pipeline parallelism; this module only adds the scheduling and the
 activation / gradient hand-off, every stage runs on the Deterministic Autograd Contract tape
 like any other model code.  Transfers are ``torch.distributed`` point-to-point operations
-(NCCL on GPUs, gloo on CPU) posted asynchronously: all receives of a phase are posted up front
-and a send is only waited for when its buffer is needed again, so communication overlaps the
-compute of the neighbouring micro-batches.
+(NCCL on GPUs, gloo on CPU).  A library such as NCCL runs all transfers between one pair of
+ranks on one stream in the order they were posted and ignores tags, so the order of posting is
+the protocol: every transfer is posted when the schedule reaches it (a send right after the
+compute that produced it, a receive right before the compute that needs it), and when a send is
+directly followed by a receive from the same neighbour - the steady state of 1F1B, where two
+stages would otherwise both be sending first - the two are posted as one group
+(``batch_isend_irecv``).  Before anything is posted, :func:`check_pair_orders` replays the
+posting orders of a stage and its neighbours on the host and refuses a schedule in which two
+ranks would wait for each other.  Sends are only waited for at the end of the step, so they
+overlap the compute of the following micro-batches.
 
 Schedule of one step with ``M`` micro-batches on stage ``r`` of ``W``:
 
@@ -20,7 +27,7 @@ last stage is the mean over micro-batches; every micro-batch's backward is seede
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence
+from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -48,8 +55,82 @@ def tape_op(tape: TensorTape, name: str, inputs: Sequence[int], **kw) -> int:
     return tape.record(name, list(inputs), out, vjp, op.rule)
 
 
+def stage_order(rank: int, world: int, n_micro: int, schedule: str) -> List[Tuple[str, int]]:
+    """The fixed sequence of ``("f", m)`` / ``("b", m)`` items stage ``rank`` runs in one step."""
+    M = n_micro
+    if schedule == "gpipe":
+        return [("f", m) for m in range(M)] + [("b", m) for m in reversed(range(M))]
+    if schedule == "1f1b":
+        warm = min(world - 1 - rank, M)
+        order = [("f", m) for m in range(warm)]
+        for k in range(M - warm):
+            order += [("f", warm + k), ("b", k)]
+        return order + [("b", m) for m in range(M - warm, M)]
+    raise ValueError(f"unknown pipeline schedule {schedule!r}")
+
+
+def comm_groups(rank: int, world: int, n_micro: int, schedule: str) -> List[List[Tuple[str, int, str, int]]]:
+    """Posting order of stage ``rank``: a list of groups of ``(kind, peer, what, m)`` with ``kind`` in
+    ``{"send", "recv"}``, ``what`` in ``{"act", "grad"}``.  Transfers in one group are posted together;
+    groups are posted in list order.  A send joins the following receive's group when both go to
+    the same neighbour and nothing is computed in between."""
+    first, last = rank == 0, rank == world - 1
+    groups: List[List[Tuple[str, int, str, int]]] = []
+    carry: Optional[Tuple[str, int, str, int]] = None      # a send waiting to see what comes next
+    for kind, m in stage_order(rank, world, n_micro, schedule):
+        recv = None
+        if kind == "f" and not first:
+            recv = ("recv", rank - 1, "act", m)
+        if kind == "b" and not last:
+            recv = ("recv", rank + 1, "grad", m)
+        if carry is not None:
+            if recv is not None and recv[1] == carry[1]:
+                groups.append([carry, recv])
+                recv = None
+            else:
+                groups.append([carry])
+            carry = None
+        if recv is not None:
+            groups.append([recv])
+        if kind == "f" and not last:
+            carry = ("send", rank + 1, "act", m)
+        if kind == "b" and not first:
+            carry = ("send", rank - 1, "grad", m)
+    if carry is not None:
+        groups.append([carry])
+    return groups
+
+
+def check_pair_orders(rank: int, world: int, n_micro: int, schedule: str) -> None:
+    """Replay, on the host, the transfers between stage ``rank`` and each neighbour the way an in-order
+    point-to-point stream executes them: the head groups of the two sides run concurrently, a send
+    completes with the matching receive, a group retires when all of its transfers have.  Raises
+    ``RuntimeError`` if neither head can make progress (the ranks would wait for each other)."""
+    for peer in (rank - 1, rank + 1):
+        if peer < 0 or peer >= world:
+            continue
+        mine = [[t for t in g if t[1] == peer] for g in comm_groups(rank, world, n_micro, schedule)]
+        theirs = [[t for t in g if t[1] == rank] for g in comm_groups(peer, world, n_micro, schedule)]
+        a = [set((k, w, m) for k, _, w, m in g) for g in mine if g]
+        b = [set((k, w, m) for k, _, w, m in g) for g in theirs if g]
+        while a and b:
+            matched = [(k, w, m) for (k, w, m) in a[0] if (("recv" if k == "send" else "send"), w, m) in b[0]]
+            if not matched:
+                raise RuntimeError(f"pipeline schedule '{schedule}' would deadlock between stages {rank} and {peer}: "
+                                   f"{sorted(a[0])} faces {sorted(b[0])}")
+            for k, w, m in matched:
+                a[0].discard((k, w, m))
+                b[0].discard((("recv" if k == "send" else "send"), w, m))
+            if not a[0]:
+                a.pop(0)
+            if b and not b[0]:
+                b.pop(0)
+        if a or b:
+            raise RuntimeError(f"pipeline schedule '{schedule}': unmatched transfers between stages {rank} and {peer}")
+
+
 class GPipeStage:
-    """One stage of a GPipe pipeline.
+    """One stage of a pipeline (GPipe or 1F1B order).
 
     ``stage_fn(tape, x_id, m)`` maps the tape id of the stage input of micro-batch ``m`` to the
     id of the stage output.  On the last stage ``loss_fn(tape, y_id, target, m)`` returns the id
@@ -77,42 +158,74 @@ class GPipeStage:
         ``schedule``: ``"gpipe"`` runs every forward, then the backwards from the last micro-batch
         to the first; ``"1f1b"`` runs ``world - 1 - rank`` warm-up forwards, then alternates one
         forward with one backward (micro-batches in ascending order) and drains the remaining
-        backwards, so at most ``world - rank`` micro-batches are live on a stage.  Both orders are
-        fixed, hence replayable; they differ in the order parameter gradients are summed."""
-        if schedule not in ("gpipe", "1f1b"):
-            raise ValueError(f"unknown pipeline schedule {schedule!r}")
+        backwards, so at most ``world - rank`` micro-batches are live on a stage: the values and
+        saved tensors of a micro-batch's nodes are dropped as soon as its backward has run
+        (``max_live`` counts micro-batches whose activations are held).  Both orders are fixed, hence
+        replayable; they differ in the order parameter gradients are summed."""
         tape, M = self.tape, n_micro
-        prev, nxt = self._peer(self.rank - 1) if not self.first else None, \
-            self._peer(self.rank + 1) if not self.last else None
-        # every receive of the step is posted up front; tags separate micro-batches and directions
-        recv_bufs, recv_req, grad_bufs, grad_req = [], [], [], []
-        if not self.first:
-            for m in range(M):
-                buf = torch.empty(tuple(in_shape), dtype=dtype, device=device)
-                recv_bufs.append(buf)
-                recv_req.append(dist.irecv(buf, src=prev, group=self.group, tag=m))
-        if not self.last:
-            for m in range(M):
-                buf = torch.empty(tuple(out_shape), dtype=dtype, device=device)
-                grad_bufs.append(buf)
-                grad_req.append(dist.irecv(buf, src=nxt, group=self.group, tag=1000 + m))
+        check_pair_orders(self.rank, self.world, M, schedule)      # refuse an order that would hang, before posting
+        groups = comm_groups(self.rank, self.world, M, schedule)
+        order = stage_order(self.rank, self.world, M, schedule)
+        self.last_order = order
+        gi = [0]                                                    # next group to post
+        bufs, works, posted, payloads, pending = {}, {}, set(), {}, []
         x_ids, y_ids, loss_ids = [None] * M, [None] * M, [None] * M
-        pending = []
+        node_span = [None] * M
         total = [0.0]
         self.max_live = live = 0
 
+        def post_next() -> None:
+            """Post the next group of the schedule: one transfer, or a send and a receive together."""
+            g = groups[gi[0]]
+            gi[0] += 1
+            ops, keys = [], []
+            for kind, peer, what, m in g:
+                key = (kind, what, m)
+                tag = m if what == "act" else 1000 + m            # honoured by gloo, ignored by NCCL
+                if kind == "recv":
+                    bufs[key] = torch.empty(tuple(in_shape if what == "act" else out_shape), dtype=dtype, device=device)
+                    ops.append(dist.P2POp(dist.irecv, bufs[key], self._peer(peer), self.group, tag))
+                else:
+                    ops.append(dist.P2POp(dist.isend, payloads.pop(key), self._peer(peer), self.group, tag))
+                keys.append(key)
+            if len(ops) == 1:
+                o = ops[0]
+                ws = [o.op(o.tensor, o.peer, o.group, o.tag)]
+            else:
+                ws = dist.batch_isend_irecv(ops)
+            for n, key in enumerate(keys):
+                works[key] = [ws[n]] if len(ws) == len(keys) else list(ws)   # a coalesced group has one handle
+                posted.add(key)
+                if key[0] == "send":
+                    pending.extend(works[key])
+
+        def wait_recv(key) -> torch.Tensor:
+            while key not in posted:
+                post_next()
+            for w in works[key]:
+                w.wait()
+            return bufs.pop(key)
+
+        def send(key, tensor: torch.Tensor) -> None:
+            """Hand a payload to the schedule.  A send that stands alone in its group is posted at once;
+            one grouped with the next receive from the same neighbour is posted when that receive is."""
+            payloads[key] = tensor
+            while gi[0] < len(groups) and all(k == "send" and (k, w, m) in payloads for k, _, w, m in groups[gi[0]]):
+                post_next()
+
         def forward(m: int) -> None:
+            lo = len(tape)
             if self.first:
                 x = tape.leaf(micro_inputs[m], requires_grad=False)
             else:
-                recv_req[m].wait()
-                x = tape.leaf(recv_bufs[m], requires_grad=True)
+                x = tape.leaf(wait_recv(("recv", "act", m)), requires_grad=True)
             y = self.stage_fn(tape, x, m)
             x_ids[m], y_ids[m] = x, y
             if self.last:
                 loss_ids[m] = self.loss_fn(tape, y, targets[m], m)
             else:
-                pending.append(dist.isend(tape.value(y).detach().contiguous(), dst=nxt, group=self.group, tag=m))
+                send(("send", "act", m), tape.value(y).detach().contiguous())
+            node_span[m] = (lo, len(tape))
 
         def backward(m: int) -> None:
             if self.last:
@@ -120,25 +233,17 @@ class GPipeStage:
                 total[0] += float(tape.value(root))
                 seed = torch.full_like(tape.value(root), 1.0 / M, dtype=tape.grad_dtype or tape.value(root).dtype)
             else:
-                grad_req[m].wait()
+                g = wait_recv(("recv", "grad", m))
                 root = y_ids[m]
-                seed = grad_bufs[m].to(tape.grad_dtype) if tape.grad_dtype is not None else grad_bufs[m]
-            # the micro-batch graphs share the parameter leaves: keep them until the caller
-            # truncates the tape after the step
+                seed = g.to(tape.grad_dtype) if tape.grad_dtype is not None else g
+            # the micro-batch graphs share the parameter leaves: the graph stays on the tape until the
+            # caller truncates it after the step, but this micro-batch's activations are released below
             report = tape.backward(root, BackwardOptions(retain_graph=True), seed=seed)
             if not self.first:
                 gx = report.gradient(x_ids[m])
-                pending.append(dist.isend(gx.to(dtype).contiguous(), dst=prev, group=self.group, tag=1000 + m))
+                send(("send", "grad", m), gx.to(dtype).contiguous())
+            tape.release_values(*node_span[m])
 
-        if schedule == "gpipe":
-            order = [("f", m) for m in range(M)] + [("b", m) for m in reversed(range(M))]
-        else:
-            warm = min(self.world - 1 - self.rank, M)
-            order = [("f", m) for m in range(warm)]
-            for k in range(M - warm):
-                order += [("f", warm + k), ("b", k)]
-            order += [("b", m) for m in range(M - warm, M)]
-        self.last_order = order
         for kind, m in order:
             if kind == "f":
                 forward(m)
@@ -147,6 +252,8 @@ class GPipeStage:
             else:
                 backward(m)
                 live -= 1
+        if gi[0] != len(groups) or payloads:
+            raise RuntimeError("pipeline step ended with transfers of the schedule not posted")
         for r in pending:
             r.wait()
         return total[0] / M if self.last else None

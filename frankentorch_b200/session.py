@@ -14,9 +14,13 @@ ft-nn / ft-optim / ft-data / ft-conformance): ``tensor_variable``, ``tensor_valu
 ``variable/value/add/sub/mul/div/backward/gradient``.  Index and label tensors may be passed
 as float-valued tensors (ft-conformance/tests/e2e_training.rs:289).
 
-``device="cpu"`` (default) is the f64 reference path; ``device="cuda"`` runs the sm_100a
-backend, where hot operators (linear, layer_norm, attention, cross-entropy ...) are the
-fused kernels of :mod:`frankentorch_b200.ops.fused`.
+``device="cpu"`` (default) is the f64 reference path on PyTorch CPU operators.  ``device="cuda"``
+is the sm_100a backend: the operator entry point looks each call up in the kernel registry
+(:mod:`frankentorch_b200.dispatch.sm100`).  linear / matmul / bmm / layer_norm / rms_norm / softmax /
+gelu / add / embedding / sdpa / cross_entropy / dropout on bf16 operands run the hand-written
+kernels and the ledger names the kernel that was launched; layout operators are recorded as such;
+any other operator is refused in strict mode and runs the PyTorch CUDA operator in hardened mode,
+recorded with ``fallback_path=true`` and an allow-listed deviation id.
 """
 from __future__ import annotations
 
@@ -119,9 +123,12 @@ class FrankenTorchSession:
             self.tensor_tape.accumulate_fn = lambda a, b: K.add(a, b) if a.dtype == torch.bfloat16 else a + b
         self.tape = Tape(self.runtime.mode)
         self.rng = Xoshiro256pp(seed)
+        self._seed = int(seed)
         self._no_grad_depth = 0
         self._autocast: Optional[DType] = None
         self._ledger_dispatch = ledger_dispatch
+        self.last_decision: Optional[DispatchDecision] = None
+        self._dropout_calls = 0          # Philox offset of the next dropout on the GPU backend
         self._device_enum = Device.Cuda if self.is_cuda else Device.Cpu
         self.runtime.ledger.record(EvidenceKind.Policy,
                                    f"session device={self.device} default_dtype={self.default_dtype.value} seed={seed}")
@@ -138,10 +145,15 @@ class FrankenTorchSession:
     def evidence(self) -> List[EvidenceEntry]:
         return self.runtime.evidence()
 
-    def _record_dispatch(self, op: str, requires_grad: bool, kernel: Optional[str] = None) -> DispatchDecision:
-        decision = decide(op, self.runtime.mode, keyset_for(self._device_enum, requires_grad), kernel or op)
+    def _record_dispatch(self, op: str, requires_grad: bool, kernel: Optional[str] = None, *,
+                         launched: Optional[str] = None, deviation: Optional[str] = None) -> DispatchDecision:
+        """One Dispatch entry per operator call.  ``launched`` is the full name of the kernel that ran
+        (sm_100a routes); ``deviation`` the allow-list id of a hardened-mode fallback."""
+        decision = decide(op, self.runtime.mode, keyset_for(self._device_enum, requires_grad), kernel or op,
+                          kernel=launched, deviation=deviation)
         if self._ledger_dispatch:
             self.runtime.ledger.record(EvidenceKind.Dispatch, decision.summary())
+        self.last_decision = decision
         return decision
 
     # ------------------------------------------------------------------ scalar DAC

@@ -36,6 +36,8 @@ def _rank_world(engine):
 def training_state_dict(engine) -> Dict[str, torch.Tensor]:
     """Tensors that define the optimizer trajectory of ``engine`` on this rank (CPU copies)."""
     rank, world = _rank_world(engine)
+    if hasattr(engine, "sync_parameters"):
+        engine.sync_parameters()          # a deferred optimizer update belongs to the state that is saved
     a = engine.model.arena
     sharded = engine.dp is not None and a.master is None
     own = engine.dp if sharded else a
@@ -79,6 +81,8 @@ def load_training_state(engine, stem: str) -> None:
             raise ValueError(f"{key}: checkpoint has {src.numel()} elements, the engine expects {dst.numel()}")
         dst.copy_(src.to(dev).reshape(dst.shape))
 
+    if sharded and hasattr(engine.dp, "discard_pending"):
+        engine.dp.discard_pending()       # gradients reduced before the load belong to the old trajectory
     put(own.master, "optim.master" + suffix)
     put(own.m, "optim.m" + suffix)
     put(own.v, "optim.v" + suffix)

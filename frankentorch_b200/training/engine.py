@@ -44,6 +44,7 @@ class TrainEngine:
         self.dp = dp
         if dp is not None and hasattr(dp, "attach"):
             dp.attach(self.tape, getattr(model, "leaf", {}))
+        self._wire_param_gates()
         dev = model.device
         self.ids = torch.zeros((micro_batch, seq_len), dtype=torch.int64, device=dev)
         self.targets = torch.zeros((micro_batch, seq_len), dtype=torch.int64, device=dev)
@@ -66,6 +67,23 @@ class TrainEngine:
         self.launches_per_step = 0
         self.last_report = None
         self.steps_done = 0
+
+    def _wire_param_gates(self) -> None:
+        """A model with a ``param_gate`` slot tells the data-parallel object which parameters its
+        forward pass is about to read, so a deferred all-gather can run under the forward pass."""
+        dp = self.dp
+        if hasattr(self.model, "param_gate"):
+            gated = dp is not None and hasattr(dp, "gate_param")
+            self.model.param_gate = dp.gate_param if gated else None
+            if gated:
+                dp.uses_gates = True
+
+    def sync_parameters(self) -> None:
+        """Make the parameter arena current on every rank (applies a deferred optimizer update).
+        Call before reading weights: evaluation, export, checkpoints, the end of training."""
+        if self.dp is not None and hasattr(self.dp, "flush"):
+            self.dp.flush()
+        torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ one step, eager
     def _optimizer(self) -> None:
@@ -125,6 +143,8 @@ class TrainEngine:
         for la, sl in zip(self.local_arenas, snap_local):
             la.master.copy_(sl[0]); la.m.copy_(sl[1]); la.v.copy_(sl[2]); la.params.copy_(sl[3])
         self.step_dev.copy_(snap[3])   # (the multi-GPU path keeps its own, never-rewinding sequence)
+        if self.dp is not None and hasattr(self.dp, "discard_pending"):
+            self.dp.discard_pending()  # the warm-up step's reduced gradients must not be applied
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._step_body()
@@ -144,6 +164,7 @@ class TrainEngine:
         self.dp = factory()
         if self.dp is not None and hasattr(self.dp, "attach"):
             self.dp.attach(self.tape, getattr(self.model, "leaf", {}))
+        self._wire_param_gates()
         self.use_graph = self._graph_requested and not getattr(self.dp, "eager_only", False)
         self.graph = None
 

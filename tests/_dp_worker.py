@@ -36,7 +36,8 @@ def main():
     small = dict(bucket_elems=40_000)
     runs = (("nccl", False, {}), ("fused", False, small), ("fused", True, small),
             ("fused1", True, dict(bucket_elems=1 << 40, overlap=False)),
-            ("fused32", True, dict(bucket_elems=40_000, wire="fp32")))
+            ("fused32", True, dict(bucket_elems=40_000, wire="fp32")),
+            ("fused_now", True, dict(bucket_elems=40_000, defer_update=False)))
     for impl, graph, kw in runs:
         cfg, model, eng = build(dev, dist.group.WORLD, "fused" if impl.startswith("fused") else impl, graph, **kw)
         g = torch.Generator().manual_seed(100 + rank)          # different data per rank
@@ -45,6 +46,7 @@ def main():
         ids, tgt = tok[:, :-1].contiguous().pin_memory(), tok[:, 1:].contiguous().pin_memory()
         for _ in range(6):
             losses.append(eng.step(ids, tgt))
+        eng.sync_parameters()
         K.check_status()
         if impl.startswith("fused"):
             assert eng.dp.step_ok()
@@ -64,8 +66,11 @@ def main():
     # fp32 on the wire differs from the NCCL all-reduce only by summation order
     d32 = (results[("fused32", True)][0] - base).abs().max().item()
     assert d32 <= (results[("fused", True)][0] - base).abs().max().item() + 1e-6, d32
-    # eager and graph replays of the fused path are bit-identical (fixed rank-order reduction)
+    # eager and graph replays of the fused path are bit-identical (fixed rank-order reduction), and so
+    # are the deferred (under the next forward pass) and the immediate update
     assert torch.equal(results[("fused", False)][0], results[("fused", True)][0])
+    assert torch.equal(results[("fused_now", True)][0], results[("fused", True)][0])
+    assert results[("fused_now", True)][1] == results[("fused", True)][1]
     assert results[("fused", True)][1][-1] < results[("fused", True)][1][0]
     if rank == 0:
         print("DP_WORKER_OK", world, results[("fused", True)][1])

@@ -101,14 +101,15 @@ def test_training_state_checkpoint_resumes_bit_identically(cuda_device, tmp_path
 from frankentorch_b200.ops import kernels as K  # noqa: E402
 
 
-def _dp_engine(cuda_device, seed, *, graph, clip, wire="fp32", bucket_elems=None, overlap=True, dp=True):
+def _dp_engine(cuda_device, seed, *, graph, clip, wire="fp32", bucket_elems=None, overlap=True, dp=True,
+               defer=None):
     from frankentorch_b200.models.gpt import GPT, GPTConfig
     from frankentorch_b200.parallel.data_parallel import FusedDataParallel
     from frankentorch_b200.training.engine import OptimConfig, TrainEngine
     cfg = GPTConfig.preset("gpt-tiny")
     model = GPT(cfg, _tape(), device=cuda_device, seed=seed, peer_visible=dp)
     d = FusedDataParallel(model.arena, None, cuda_device, wire=wire, bucket_elems=bucket_elems,
-                          overlap=overlap) if dp else None
+                          overlap=overlap, defer_update=defer) if dp else None
     eng = TrainEngine(model, 2, 128, OptimConfig(lr=1e-3, grad_clip=clip), use_cuda_graph=graph, dp=d)
     return cfg, model, eng, d
 
@@ -123,9 +124,13 @@ def test_bucketed_data_parallel_on_one_rank_matches_plain_engine(cuda_device):
     _, m0, e0, _ = _dp_engine(cuda_device, 5, graph=False, clip=None, dp=False)
     ref_losses = [e0.step(*b) for b in batches]
     ref = m0.arena.params.clone()
-    for graph, bucket_elems, overlap in ((False, None, True), (True, 40_000, True), (True, 40_000, False)):
-        _, m, e, d = _dp_engine(cuda_device, 5, graph=graph, clip=None, bucket_elems=bucket_elems, overlap=overlap)
+    for graph, bucket_elems, overlap, defer in ((False, None, True, True), (True, 40_000, True, True),
+                                                (True, 40_000, False, True), (True, 40_000, True, False),
+                                                (False, 40_000, True, False)):
+        _, m, e, d = _dp_engine(cuda_device, 5, graph=graph, clip=None, bucket_elems=bucket_elems, overlap=overlap,
+                                defer=defer)
         losses = [e.step(*b) for b in batches]
+        e.sync_parameters()
         K.check_status()
         assert d.step_ok()
         assert losses == ref_losses, (graph, bucket_elems, losses, ref_losses)
@@ -149,14 +154,17 @@ def test_bucketed_data_parallel_bf16_wire_and_clip_replay(cuda_device):
     for b in batches:
         e0.step(*b)
     outs = {}
-    for key, graph, be, clip in (("eager", False, 40_000, 1.0), ("graph", True, 40_000, 1.0),
-                                 ("nc_small", True, 40_000, None), ("nc_big", True, None, None)):
-        _, m, e, d = _dp_engine(cuda_device, 9, graph=graph, clip=clip, wire="bf16", bucket_elems=be)
+    for key, graph, be, clip, defer in (("eager", False, 40_000, 1.0, True), ("graph", True, 40_000, 1.0, True),
+                                        ("now", True, 40_000, 1.0, False),
+                                        ("nc_small", True, 40_000, None, True), ("nc_big", True, None, None, False)):
+        _, m, e, d = _dp_engine(cuda_device, 9, graph=graph, clip=clip, wire="bf16", bucket_elems=be, defer=defer)
         for b in batches:
             e.step(*b)
+        e.sync_parameters()
         K.check_status()
         outs[key] = m.arena.params.clone()
     assert torch.equal(outs["eager"], outs["graph"])
+    assert torch.equal(outs["now"], outs["graph"])        # deferring the update does not change it
     assert torch.equal(outs["nc_small"], outs["nc_big"])
     diff = (outs["graph"].float() - m0.arena.params.float()).abs().max().item()
     assert diff < 2e-2, diff

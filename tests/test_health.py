@@ -172,6 +172,7 @@ def test_hardened_fallback_through_the_real_engine(cuda_device):
     got = [tr.step(ids, tgt) for _ in range(3)]
     status[0] = 5
     got += [tr.step(ids, tgt) for _ in range(3)]
+    eng.sync_parameters()
     K.check_status()
     assert tr.fell_back and isinstance(eng.dp, NcclDataParallel) and not eng.use_graph
     assert model.arena.master is not None and model.arena.m is not None

@@ -92,3 +92,45 @@ def test_one_f_one_b_matches_single_process_and_bounds_live_micro_batches():
     max_live, order = res[0][0]
     # stage 0 of 2: one warm-up forward, then forward / backward pairs, then the last backward
     assert order == [("f", 0), ("f", 1), ("b", 0), ("f", 2), ("b", 1), ("b", 2)] and max_live == 2
+
+
+def test_posting_orders_pair_up_for_every_stage_and_schedule():
+    """The host-side replay of the per-pair posting orders (what an in-order point-to-point stream
+    would execute) finds no two ranks waiting for each other, for both schedules and several shapes;
+    and it does flag an order in which both neighbours send first."""
+    from frankentorch_b200.parallel import pipeline as P
+    for schedule in ("gpipe", "1f1b"):
+        for world in (2, 3, 4, 8):
+            for M in (1, 2, 3, 4, 8, 16):
+                for r in range(world):
+                    P.check_pair_orders(r, world, M, schedule)
+    # 1F1B steady state: a stage's send of the next activation and its receive of a gradient form one group
+    g = P.comm_groups(0, 2, 3, "1f1b")
+    assert [("send", 1, "act", 1), ("recv", 1, "grad", 0)] in g
+    assert P.comm_groups(1, 2, 3, "1f1b")[1] == [("send", 0, "grad", 0), ("recv", 0, "act", 1)]
+    # without grouping, the same schedule has both stages sending first: the replay must refuse it
+    real = P.comm_groups
+
+    def ungrouped(rank, world, n_micro, schedule):
+        return [[t] for grp in real(rank, world, n_micro, schedule) for t in grp]
+    P.comm_groups = ungrouped
+    try:
+        import pytest
+        with pytest.raises(RuntimeError, match="deadlock"):
+            P.check_pair_orders(0, 2, 3, "1f1b")
+    finally:
+        P.comm_groups = real
+
+
+def test_release_values_frees_a_micro_batch_but_keeps_ids():
+    from frankentorch_b200.autograd.tape import TensorTape
+    from frankentorch_b200.parallel.pipeline import tape_op
+    tape = TensorTape(grad_dtype=torch.float64)
+    w = tape.leaf(torch.ones(3, 3, dtype=torch.float64), requires_grad=True)
+    lo = len(tape)
+    x = tape.leaf(torch.ones(2, 3, dtype=torch.float64), requires_grad=False)
+    y = tape_op(tape, "relu", [tape_op(tape, "linear", [x, w])])
+    hi = len(tape)
+    assert tape.release_values(lo, hi) == 2
+    assert tape.value(y) is None and tape.value(w) is not None and tape.value(x) is not None
+    assert len(tape) == hi
