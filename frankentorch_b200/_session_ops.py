@@ -72,7 +72,11 @@ def _apply(self, name: str, inputs: Sequence[int], **kw) -> int:
             else:
                 ins, o = _vals, _out
             return list(_op.vjp(g, ins, o, _kw))
-    return tape.record(name, list(inputs), out, vjp, op.rule)
+    cg = None
+    if vjp is not None and not self.is_cuda:
+        from .autograd.double_backward import op_cg
+        cg = op_cg(tape, op, kw, inputs)
+    return tape.record(name, list(inputs), out, vjp, op.rule, cg=cg)
 
 
 _BUILTIN_BINARY = {"max", "min", "atan2", "fmod", "remainder", "pow_tensor", "matmul", "bmm", "dot", "outer", "kron",
@@ -183,38 +187,94 @@ def tensor_retain_grad(self, nid: int) -> None:
     self.tensor_tape.retain_grad(nid)
 
 
-def tensor_autograd_grad(self, outputs: int, inputs: Sequence[int], retain_graph: bool = True):
-    """Gradients of ``outputs`` w.r.t. ``inputs`` without touching the accumulated ``.grad`` slots."""
+def tensor_autograd_grad(self, outputs: int, inputs: Sequence[int], retain_graph: bool = True,
+                         create_graph: bool = False):
+    """Gradients of ``outputs`` w.r.t. ``inputs`` without touching the accumulated ``.grad`` slots.
+
+    Returns tensors; with ``create_graph=True`` returns the tape ids of the gradient nodes instead
+    (``None`` for an input the output does not depend on), which can be differentiated again."""
     tape = self.tensor_tape
-    saved = {i: (tape.nodes[i].grad, tape.nodes[i].grad_buffer_filled) for i in range(len(tape.nodes))}
+    n_before = len(tape.nodes)
+    saved = {i: (tape.nodes[i].grad, tape.nodes[i].grad_buffer_filled) for i in range(n_before)}
     opts = BackwardOptions.for_mode(self.runtime.mode)
-    opts.retain_graph = retain_graph
+    opts.retain_graph = retain_graph or create_graph
+    opts.create_graph = create_graph
     rep = tape.backward(outputs, opts)
     for i, (g, f) in saved.items():
         tape.nodes[i].grad, tape.nodes[i].grad_buffer_filled = g, f
+    if create_graph:
+        return [rep.gradient_node(i) for i in inputs]
     return [rep.gradient(i) for i in inputs]
 
 
-def tensor_functional_hessian(self, fn: Callable[[torch.Tensor], torch.Tensor], x: int) -> torch.Tensor:
-    """Dense Hessian of a scalar function of one tensor by central differences of its DAC gradient."""
-    x0 = self.tensor(x).detach().to(torch.float64)
-    n = x0.numel()
-
-    def grad_at(v):
-        leaf = self.tensor_tape.leaf(v.reshape(x0.shape).to(self.tensor(x).dtype), True)
-        mark = len(self.tensor_tape)
-        out = fn(self, leaf)
-        g = self.tensor_autograd_grad(out, [leaf])[0].reshape(-1).to(torch.float64).clone()
-        return g
-
+def tensor_functional_hessian(self, y, x: int) -> torch.Tensor:
+    """Dense Hessian ``d2 y / dx dx`` of a scalar node ``y`` w.r.t. the tensor node ``x`` by double
+    backward: one graph-building backward gives the gradient as a tape node, then one ordinary
+    backward per gradient element (seeded with a unit vector) gives a row
+    (ft-api tests/*_double_backward_parity.rs call it as ``tensor_functional_hessian(out, x)``).
+    ``y`` may also be a callable ``fn(session, x_id) -> scalar node id``; it is evaluated once."""
+    tape = self.tensor_tape
+    if callable(y):
+        y = y(self, x)
+    if self.tensor(y).numel() != 1:
+        raise ValueError("tensor_functional_hessian needs a scalar output")
+    (g_id,) = self.tensor_autograd_grad(y, [x], create_graph=True)
+    xv = self.tensor(x)
+    n = xv.numel()
     H = torch.zeros(n, n, dtype=torch.float64)
-    eps = 1e-5
-    flat = x0.reshape(-1)
+    if g_id is None:
+        return H
+    gdt = tape.grad_dtype or self.tensor(g_id).dtype
+    saved = {i: tape.nodes[i].grad for i in range(len(tape.nodes))}
     for j in range(n):
-        e = torch.zeros(n, dtype=torch.float64)
-        e[j] = eps
-        H[:, j] = (grad_at(flat + e) - grad_at(flat - e)) / (2 * eps)
-    return 0.5 * (H + H.t())
+        if not tape.nodes[g_id].requires_grad:
+            break                                   # the gradient is constant in x: the Hessian is zero
+        seed = torch.zeros(n, dtype=gdt, device=xv.device)
+        seed[j] = 1.0
+        rep = tape.backward(g_id, BackwardOptions(retain_graph=True), seed=seed.reshape(self.tensor(g_id).shape))
+        row = rep.gradient(x)
+        if row is not None:
+            H[j] = row.reshape(-1).to("cpu", torch.float64)
+    for i, g in saved.items():
+        tape.nodes[i].grad = g
+    return H
+
+
+def tensor_apply_function_with_create_graph(self, inputs: Sequence[int], forward_fn, backward_fn) -> int:
+    """Custom autograd function whose backward is written in session operators, so it can be
+    differentiated again (ft-autograd/src/lib.rs:8951, :1520-1533).
+
+    ``forward_fn(ctx, tensors) -> tensor`` as in :func:`tensor_apply_function`;
+    ``backward_fn(session, ctx, grad_id, input_ids) -> list of node ids (or None)`` builds the
+    input gradients out of ``tensor_*`` calls.  An ordinary backward evaluates it without recording."""
+    from .session import FunctionCtx
+    tape = self.tensor_tape
+    inputs = list(inputs)
+    vals = [tape.value(i) for i in inputs]
+    ctx = FunctionCtx([tape.nodes[i].requires_grad for i in inputs])
+    out = forward_fn(ctx, vals)
+    self._record_dispatch("custom_function", any(ctx.needs_input_grad), "custom_function")
+
+    def vjp(g, targets):
+        mark = len(tape)
+        prev, tape.grad_enabled = tape.grad_enabled, False
+        try:
+            gid = tape.leaf(g, requires_grad=False)
+            ids = backward_fn(self, ctx, gid, inputs)
+            res = [None if i is None else tape.value(i) for i in ids]
+        finally:
+            tape.grad_enabled = prev
+        tape.truncate_graph_to(mark)
+        return res
+
+    def cg(g_id):
+        prev, tape.grad_enabled = tape.grad_enabled, True
+        try:
+            return list(backward_fn(self, ctx, g_id, inputs))
+        finally:
+            tape.grad_enabled = prev
+
+    return tape.record("custom_function", inputs, out, vjp, "custom autograd function backward", cg=cg)
 
 
 def truncate_autograd_graph(self, boundary: int) -> None:
@@ -361,7 +421,7 @@ def install(cls) -> None:
                tensor_accumulated_gradient_tensor, tensor_accumulated_gradient_len, tensor_set_accumulated_gradient,
                tensor_zero_grad, tensor_zero_grads, tensor_retain_grad, tensor_autograd_grad, tensor_functional_hessian,
                truncate_autograd_graph, autograd_graph_len, register_tensor_hook, remove_tensor_hook,
-               tensor_apply_function, checkpoint, tensor_add_, tensor_sub_, tensor_mul_, tensor_div_, tensor_neg_,
+               tensor_apply_function, tensor_apply_function_with_create_graph, checkpoint, tensor_add_, tensor_sub_, tensor_mul_, tensor_div_, tensor_neg_,
                tensor_zero_, tensor_fill_, tensor_clamp_, tensor_update_param_values, tensor_update_param_values_f64_with,
                tensor_update_param_values_f64_with_accumulated_gradient):
         setattr(cls, fn.__name__, fn)

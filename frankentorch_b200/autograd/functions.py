@@ -51,11 +51,19 @@ def unbroadcast(g: torch.Tensor, shape) -> torch.Tensor:
 def local_vjp(fwd):
     """VJP of one node by differentiating a re-run of its forward on detached inputs."""
     def vjp(g, inputs, out, kw):
-        xs = [x.detach().clone().requires_grad_(x.is_floating_point() or x.is_complex()) for x in inputs]
+        # Inside a graph-building backward the rule is itself being differentiated: its arguments carry
+        # torch's grad tracking and the result must stay connected to them (see double_backward.py).
+        higher = torch.is_grad_enabled() and (g.requires_grad or any(
+            isinstance(x, torch.Tensor) and x.requires_grad for x in inputs))
+        if higher:
+            xs = [x if (x.requires_grad or not (x.is_floating_point() or x.is_complex()))
+                  else x.detach().requires_grad_(True) for x in inputs]
+        else:
+            xs = [x.detach().clone().requires_grad_(x.is_floating_point() or x.is_complex()) for x in inputs]
         with torch.enable_grad():
             y = fwd(*xs, **kw)
-        need = [x for x in xs if x.requires_grad]
-        grads = torch.autograd.grad(y, need, g.to(y.dtype), allow_unused=True) if need else ()
+            need = [x for x in xs if x.requires_grad]
+            grads = torch.autograd.grad(y, need, g.to(y.dtype), allow_unused=True, create_graph=higher) if need else ()
         it = iter(grads)
         return [next(it) if x.requires_grad else None for x in xs]
     return vjp

@@ -139,9 +139,14 @@ class TensorBackwardReport:
     gradients: Dict[int, torch.Tensor]
     steps: List[TensorBackwardStep]
     telemetry: TensorSchedulerTelemetry
+    # create_graph=True only: tape id of the node that holds each gradient (differentiable further)
+    gradient_nodes: Dict[int, int] = field(default_factory=dict)
 
     def gradient(self, node: int) -> Optional[torch.Tensor]:
         return self.gradients.get(int(node))
+
+    def gradient_node(self, node: int) -> Optional[int]:
+        return self.gradient_nodes.get(int(node))
 
 
 # Marker a VJP rule returns for an input whose gradient it already accumulated in place into
@@ -187,7 +192,7 @@ class GradTargets:
 
 class TensorNode:
     __slots__ = ("id", "op", "inputs", "value", "requires_grad", "is_leaf", "vjp", "rule", "retain_grad",
-                 "hooks", "grad", "grad_buffer", "grad_buffer_filled", "version", "saved", "name")
+                 "hooks", "grad", "grad_buffer", "grad_buffer_filled", "version", "saved", "name", "cg")
 
     def __init__(self, nid, op, inputs, value, requires_grad, is_leaf, vjp, rule):
         self.id = nid
@@ -206,6 +211,7 @@ class TensorNode:
         self.version = 0
         self.saved = None
         self.name = None
+        self.cg = None      # graph-building backward: (grad node id) -> per-input contribution node ids
 
 
 @dataclass(frozen=True)
@@ -265,14 +271,17 @@ class TensorTape:
         return nid
 
     def record(self, op: str, inputs: Sequence[int], value: torch.Tensor,
-               vjp: Optional[Callable], rule: str, saved: Any = None) -> int:
-        """Append a computed node.  ``vjp(grad_out, targets) -> sequence of per-input grads``."""
+               vjp: Optional[Callable], rule: str, saved: Any = None, cg: Optional[Callable] = None) -> int:
+        """Append a computed node.  ``vjp(grad_out, targets) -> sequence of per-input grads``;
+        ``cg(grad_node_id) -> sequence of per-input contribution node ids`` is the graph-building
+        form of the same rule, used by ``backward(..., create_graph=True)``."""
         for i in inputs:
             if i < 0 or i >= len(self.nodes):
                 raise UnknownTensorNode(f"node {i}")
         rg = self.grad_enabled and any(self.nodes[i].requires_grad for i in inputs) and vjp is not None
         nid = self._append(op, tuple(inputs), value, rg, False, vjp if rg else None, rule)
         self.nodes[nid].saved = saved if rg else None
+        self.nodes[nid].cg = cg if rg else None
         return nid
 
     def value(self, nid: int) -> torch.Tensor:
@@ -403,6 +412,9 @@ class TensorTape:
             guard = fallback = True
         depth = min(opts.current_reentrant_depth, opts.max_reentrant_depth)
         order, deps, (pushes, pops, max_len) = self.schedule(root)
+        if opts.create_graph:
+            return self._backward_create_graph(root, opts, seed, order, deps, (pushes, pops, max_len), depth, guard,
+                                               fallback)
 
         rootn = self.nodes[root]
         if seed is None:
@@ -490,3 +502,66 @@ class TensorTape:
             self._lib.ftc_tape_mark_consumed(self._h)
         telemetry = TensorSchedulerTelemetry(order, pushes, pops, max_len, deps, depth, guard, fallback)
         return TensorBackwardReport(grads, steps, telemetry)
+
+    # ------------------------------------------------------------------ graph-building backward
+    def _backward_create_graph(self, root, opts, seed, order, deps, stats, depth, guard, fallback):
+        """The same scheduler order as ``backward``, but every gradient is a tape node: a rule's
+        contributions are appended as nodes (``node.cg``), accumulation is an ``add`` node, and the
+        report maps each reached node to the id of its gradient node.  The graph is never consumed
+        (``create_graph`` implies ``retain_graph``, ft-autograd/src/lib.rs:15755)."""
+        pushes, pops, max_len = stats
+        nodes = self.nodes
+        rootn = nodes[root]
+        if seed is None:
+            seed = torch.ones_like(rootn.value, dtype=self.grad_dtype or rootn.value.dtype)
+        gnode: Dict[int, int] = {root: self.leaf(seed, requires_grad=False)}
+        steps: List[TensorBackwardStep] = []
+        for nid in list(order):
+            node = nodes[nid]
+            gi = gnode.get(nid)
+            if gi is None:
+                continue
+            gval = nodes[gi].value
+            for _, hook in node.hooks:
+                res = hook(gval)
+                if res is not None:
+                    if tuple(res.shape) != tuple(gval.shape):
+                        raise TensorGradientShapeMismatch(
+                            f"hook on node {nid} changed the gradient shape {tuple(gval.shape)} -> {tuple(res.shape)}")
+                    gi = self.leaf(res, requires_grad=False)      # a replaced gradient is a constant of the new graph
+                    gval = res
+                    gnode[nid] = gi
+            if node.is_leaf:
+                if node.requires_grad:
+                    steps.append(TensorBackwardStep(nid, gval.numel(), "leaf"))
+                continue
+            if not node.requires_grad:
+                continue
+            if node.cg is None:
+                raise AutogradError(f"rule '{node.rule}' (node {nid}) has no graph-building backward; "
+                                    "create_graph needs apply_function_with_create_graph for custom functions")
+            steps.append(TensorBackwardStep(nid, gval.numel(), node.rule))
+            contribs = node.cg(gi)
+            if len(contribs) != len(node.inputs):
+                raise TensorGradientShapeMismatch(
+                    f"rule '{node.rule}' returned {len(contribs)} gradient nodes for {len(node.inputs)} inputs")
+            for inp, c in zip(node.inputs, contribs):
+                if c is None or not nodes[inp].requires_grad:
+                    continue
+                prev = gnode.get(inp)
+                gnode[inp] = c if prev is None else self._cg_add(prev, c)
+        grads = {nid: nodes[g].value for nid, g in gnode.items()}
+        for nid in order:
+            node = nodes[nid]
+            if not node.requires_grad or not (node.is_leaf or node.retain_grad) or nid not in grads:
+                continue
+            g = self._cast_grad(grads[nid])
+            node.grad = g.clone() if node.grad is None else node.grad + g
+        telemetry = TensorSchedulerTelemetry(order, pushes, pops, max_len, deps, depth, guard, fallback)
+        return TensorBackwardReport(grads, steps, telemetry, dict(gnode))
+
+    def _cg_add(self, a: int, b: int) -> int:
+        """Accumulation of two gradient nodes as a node of its own (contributions are added in rule order)."""
+        va, vb = self.nodes[a].value, self.nodes[b].value
+        return self.record("add", [a, b], self.accumulate_fn(va, vb), lambda g, targets: [g, g],
+                           "d(a+b)/da=1; d(a+b)/db=1", cg=lambda g_id: [g_id, g_id])
