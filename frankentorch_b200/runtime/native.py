@@ -47,6 +47,13 @@ def load():
         "ftc_adamw_f64": ([vp, vp, vp, vp, i64, dbl, dbl, dbl, dbl, dbl, i64], None),
         "ftc_gelu_tanh_clamped_f32": ([vp, vp, i64], None),
         "ftc_softmax_guarded_f32": ([vp, vp, i64, i64], None),
+        "ftc_pool_configure": ([C.c_char_p, P(i32)], i32), "ftc_pool_width": ([], i32),
+        "ftc_pool_physical_cores": ([], i32), "ftc_pool_auto_width": ([], i32),
+        "ftc_pool_reset_for_tests": ([], None), "ftc_pool_set_min_work": ([i64], i64),
+        "ftc_pairwise_sum_par": ([vp, i64], dbl),
+        "ftc_linear_f64_par": ([vp, vp, vp, vp, i64, i64, i64], None),
+        "ftc_layer_norm_f64_par": ([vp, vp, vp, vp, i64, i64, dbl], None),
+        "ftc_adamw_f64_par": ([vp, vp, vp, vp, i64, dbl, dbl, dbl, dbl, dbl, i64], None),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

@@ -14,11 +14,14 @@ u8 has_grad, u64 grad bits`` (:506-529) into a 64-bit hasher.  The reference's h
 uses FNV-1a-64 over the same byte feed, so envelopes written here verify here, while the
 reference's golden digest (``det64:4950f922ab2dbd30``) does not reproduce.
 
-Sidecar: systematic XOR fountain code over fixed-size symbols with a seeded, replayable
-neighbour selection - the role RaptorQ plays in the reference (:175-373): symbol size 32 / 64 /
-128 / 256 by payload length (:553-560), seed ``0x46545f5241505451``, repair count
-``max(requested, 1) + 8``, a manifest of repair symbols and a decode proof showing the payload
-is recoverable after dropping source symbols.
+Sidecar: a systematic random linear fountain code over GF(2^8) with seeded, replayable
+coefficients (``code = "rlf256-systematic-v1"``) in the role RaptorQ plays in the reference
+(:175-373), with the reference's parameters: symbol size 32 / 64 / 128 / 256 by payload length
+(:553-560), seed ``0x46545f5241505451``, repair count ``max(requested, 1) + 8`` with the 1024 /
+65,536 limits, a manifest of repair symbols and a decode proof found by dropping source symbols
+in several mixes until a decode returns the payload.  Any ``m`` lost source symbols are recovered
+from ``m`` repair symbols unless their coefficient matrix happens to be singular (probability
+about 1/255, vanishing with every surplus symbol).
 """
 from __future__ import annotations
 
@@ -36,6 +39,7 @@ MAX_PAYLOAD_BYTES = 1 << 20
 SIDECAR_SEED = 0x46545F5241505451
 OBJECT_ID = (0x46545F434B50545F, 0x4455524142494C45)
 MAX_REPAIR_SYMBOLS = 1024
+MAX_SOURCE_SYMBOLS = 65536
 
 
 class SerializeError(ValueError):
@@ -149,6 +153,47 @@ def decode_checkpoint(text: str, mode: ExecutionMode = ExecutionMode.Strict, run
 
 
 # -------------------------------------------------------------------------------------- sidecar
+# The erasure code is a systematic random linear fountain code over GF(2^8) ("rlf256"): repair
+# symbol e is sum_i c(e, i) * source_i with coefficients drawn from a generator seeded by
+# (seed, e), every c non-zero.  Any m lost source symbols are recovered from any m' >= m repair
+# symbols whose m x m' coefficient matrix has rank m - for random coefficients that fails with
+# probability about 1/255 per exactly-sufficient set and vanishes with each extra symbol - by
+# Gauss-Jordan elimination over GF(2^8).  It is NOT RaptorQ (RFC 6330's pre-code and degree tables
+# are not reproduced here); it plays RaptorQ's role with the reference's parameters.
+CODE_NAME = "rlf256-systematic-v1"
+_GF_POLY = 0x11D
+
+
+def _gf_tables():
+    import numpy as np
+    exp = np.zeros(512, dtype=np.int32)
+    log = np.zeros(256, dtype=np.int32)
+    x = 1
+    for i in range(255):
+        exp[i] = x
+        log[x] = i
+        x <<= 1
+        if x & 0x100:
+            x ^= _GF_POLY
+    exp[255:510] = exp[0:255]
+    mul = np.zeros((256, 256), dtype=np.uint8)
+    a = np.arange(1, 256)
+    mul[1:, 1:] = exp[(log[a][:, None] + log[a][None, :])].astype(np.uint8)
+    inv = np.zeros(256, dtype=np.uint8)
+    inv[1:] = exp[255 - log[a]].astype(np.uint8)
+    return mul, inv
+
+
+_GF = None
+
+
+def _gf():
+    global _GF
+    if _GF is None:
+        _GF = _gf_tables()
+    return _GF
+
+
 @dataclass
 class RepairSymbol:
     esi: int
@@ -157,7 +202,9 @@ class RepairSymbol:
 
 
 @dataclass
-class RaptorQSidecar:
+class RepairSidecar:
+    """Repair symbols stored next to an artifact (field set of the reference's sidecar record,
+    ft-serialize/src/lib.rs:69-101, plus ``code``, which names the erasure code actually used)."""
     schema_version: int
     source_hash: str
     symbol_size: int
@@ -167,9 +214,15 @@ class RaptorQSidecar:
     object_id: Tuple[int, int]
     repair_symbols: int
     repair_manifest: List[RepairSymbol] = field(default_factory=list)
+    code: str = CODE_NAME
 
     def to_json(self) -> str:
         return json.dumps(asdict(self), separators=(",", ":"))
+
+
+# Name under which the reference exposes this record.  The record's ``code`` field says which
+# erasure code produced the symbols: this implementation's is rlf256, not RaptorQ.
+RaptorQSidecar = RepairSidecar
 
 
 @dataclass
@@ -201,101 +254,125 @@ class _Lcg:
         return (self.s >> 33) % bound
 
 
-def _neighbours(esi: int, k: int, seed: int, count: int) -> List[int]:
-    """Source symbols XOR-ed into repair symbol ``esi``.
-
-    The ``count`` repair symbols form two interleaved families of residue classes (mod R1 and
-    mod R2, each rotated by a seeded offset): every source symbol is covered once per family,
-    so any single loss and any two losses that differ in at least one family are recoverable.
-    """
-    j = esi - k
-    r1 = (count + 1) // 2
-    r2 = max(1, count - r1)
-    rot = _Lcg(seed).next(1 << 16)
-    if j < r1:
-        cls = [i for i in range(k) if (i + rot) % r1 == j]
-    else:
-        cls = [i for i in range(k) if (i * 7 + rot) % r2 == (j - r1) % r2]
-    return cls or [j % k]
+def _coefficients(esi: int, k: int, seed: int):
+    """The k non-zero GF(2^8) coefficients of repair symbol ``esi`` (replayable from seed and esi)."""
+    import numpy as np
+    g = _Lcg(seed ^ ((esi + 1) * 0x9E3779B97F4A7C15))
+    return np.fromiter((1 + g.next(255) for _ in range(k)), dtype=np.uint8, count=k)
 
 
-def _symbols(payload: bytes, size: int) -> List[bytearray]:
+def _symbols(payload: bytes, size: int):
+    import numpy as np
     k = max(1, (len(payload) + size - 1) // size)
     padded = payload + bytes(k * size - len(payload))
-    return [bytearray(padded[i * size:(i + 1) * size]) for i in range(k)]
+    return np.frombuffer(padded, dtype=np.uint8).reshape(k, size).copy()
 
 
-def _xor(a: bytearray, b) -> None:
-    for i in range(len(a)):
-        a[i] ^= b[i]
+def repair_symbol_count(requested: int, k: int) -> int:
+    """``max(requested, 1) + 8`` (ft-serialize/src/lib.rs:205-221; the systematic code needs no
+    padding symbols, so the reference's ``k' - k`` term is zero).  More than 1024 requested repair
+    symbols, or a block of more than 65,536 source symbols, is an error (:27, :37, :186)."""
+    if requested > MAX_REPAIR_SYMBOLS:
+        raise SerializeError("RepairSymbolLimit", f"repair_symbols {requested} exceeds {MAX_REPAIR_SYMBOLS}")
+    if k > MAX_SOURCE_SYMBOLS:
+        raise SerializeError("SourceSymbolLimit", f"{k} source symbols exceed {MAX_SOURCE_SYMBOLS}")
+    return max(requested, 1) + 8
 
 
-def generate_raptorq_sidecar(payload: bytes, repair_symbols: int = 0) -> Tuple[RaptorQSidecar, DecodeProofArtifact]:
+def generate_repair_sidecar(payload: bytes, repair_symbols: int = 0) -> Tuple[RepairSidecar, DecodeProofArtifact]:
+    """Repair symbols for ``payload`` and a proof that it is recoverable from them.
+
+    The proof is found the way the reference does it (:223-373): source symbols are dropped in
+    several mixes (the first ones, evenly spread ones, seeded random ones, as many as there are repair
+    symbols and then fewer) until a decode from the remaining symbols plus the sidecar returns the
+    payload; ``recovered`` is False - never assumed - if none of the mixes decodes."""
+    import numpy as np
+    mul, _ = _gf()
     size = symbol_size_for(len(payload))
     src = _symbols(payload, size)
-    k = len(src)
-    count = min(MAX_REPAIR_SYMBOLS, max(repair_symbols, 1) + 8)
+    k = src.shape[0]
+    count = repair_symbol_count(repair_symbols, k)
     manifest = []
     for j in range(count):
         esi = k + j
-        nb = _neighbours(esi, k, SIDECAR_SEED, count)
-        sym = bytearray(size)
-        for n in nb:
-            _xor(sym, src[n])
-        manifest.append(RepairSymbol(esi, len(nb), bytes(sym).hex()))
-    side = RaptorQSidecar(1, hash_bytes(payload), size, k, len(payload), SIDECAR_SEED, OBJECT_ID, count, manifest)
-    # decode proof: drop source symbols (several mixes) until a drop set is found that the repair
-    # symbols recover exactly
+        c = _coefficients(esi, k, SIDECAR_SEED)
+        sym = np.bitwise_xor.reduce(mul[c[:, None], src], axis=0)
+        manifest.append(RepairSymbol(esi, k, sym.tobytes().hex()))
+    side = RepairSidecar(1, hash_bytes(payload), size, k, len(payload), SIDECAR_SEED, OBJECT_ID, count, manifest)
+    rows = [src[i].tobytes() for i in range(k)]
+    rng = _Lcg(SIDECAR_SEED ^ k)
     proof = None
-    for ndrop in (min(k, 3), min(k, 2), 1):
-        dropped = [(i * 7 + 1) % k for i in range(ndrop)]
-        dropped = sorted(set(dropped))
-        rec = decode_with_sidecar([None if i in dropped else bytes(s) for i, s in enumerate(src)], side)
-        ok = rec is not None and rec == payload
-        if ok:
-            used = [m.esi for m in manifest if any(n in dropped for n in _neighbours(m.esi, k, SIDECAR_SEED, count))]
-            ph = hash_bytes(json.dumps([side.source_hash, dropped, used]).encode())
-            proof = DecodeProofArtifact(1, side.source_hash, dropped, used, True, ph)
+    for ndrop in sorted({min(k, count), min(k, max(1, count // 2)), min(k, 3), 1}, reverse=True):
+        mixes = [list(range(ndrop)), sorted({(i * k) // ndrop for i in range(ndrop)}),
+                 sorted({rng.next(k) for _ in range(ndrop)})]
+        for dropped in mixes:
+            rec = decode_with_sidecar([None if i in set(dropped) else r for i, r in enumerate(rows)], side)
+            if rec is not None and rec == payload:
+                used = [m.esi for m in manifest[: len(dropped)]]
+                ph = hash_bytes(json.dumps([side.source_hash, dropped, used]).encode())
+                proof = DecodeProofArtifact(1, side.source_hash, dropped, used, True, ph)
+                break
+        if proof is not None:
             break
     if proof is None:
-        proof = DecodeProofArtifact(1, side.source_hash, [], [], True, hash_bytes(side.source_hash.encode()))
+        proof = DecodeProofArtifact(1, side.source_hash, [], [], False, hash_bytes(side.source_hash.encode()))
     return side, proof
 
 
-def decode_with_sidecar(received: Sequence[Optional[bytes]], side: RaptorQSidecar) -> Optional[bytes]:
+# The reference's name for this entry point (ft-serialize/src/lib.rs:175).
+generate_raptorq_sidecar = generate_repair_sidecar
+
+
+def decode_with_sidecar(received: Sequence[Optional[bytes]], side: RepairSidecar) -> Optional[bytes]:
     """Recover the payload from source symbols (``None`` = lost) plus the sidecar's repair symbols
-    by Gaussian elimination over GF(2).  Returns ``None`` if the losses are not recoverable."""
+    by Gauss-Jordan elimination over GF(2^8).  Returns ``None`` if the losses are not recoverable
+    (more losses than repair symbols, a rank-deficient system, or a hash mismatch afterwards)."""
+    import numpy as np
+    mul, inv = _gf()
     k, size = side.k, side.symbol_size
+    if len(received) != k:
+        return None
     missing = [i for i, s in enumerate(received) if s is None]
     if not missing:
-        return b"".join(received)[: side.payload_len]
-    col = {m: j for j, m in enumerate(missing)}
-    rows = []
-    for rs in side.repair_manifest:
-        nb = _neighbours(rs.esi, k, side.seed, side.repair_symbols)
-        val = bytearray(bytes.fromhex(rs.bytes))
-        mask = 0
-        for n in nb:
-            if received[n] is None:
-                mask |= 1 << col[n]
-            else:
-                _xor(val, received[n])
-        if mask:
-            rows.append([mask, val])
-    # Gauss-Jordan over GF(2): one pivot row per missing symbol, eliminated from every other row
-    solved: Dict[int, list] = {}
-    for j in range(len(missing)):
-        piv = next((r for r in rows if (r[0] >> j) & 1), None)
-        if piv is None:
-            return None
-        rows.remove(piv)
-        for r in rows + list(solved.values()):
-            if (r[0] >> j) & 1:
-                r[0] ^= piv[0]
-                _xor(r[1], piv[1])
-        solved[j] = piv
-    if any(solved[j][0] != (1 << j) for j in solved):
+        data = b"".join(received)[: side.payload_len]
+        return data if hash_bytes(data) == side.source_hash else None
+    m = len(missing)
+    if m > len(side.repair_manifest):
         return None
-    out = [bytes(solved[col[i]][1]) if s is None else s for i, s in enumerate(received)]
+    have = [i for i in range(k) if received[i] is not None]
+    have_arr = np.frombuffer(b"".join(received[i] for i in have), dtype=np.uint8).reshape(len(have), size) \
+        if have else np.zeros((0, size), dtype=np.uint8)
+    A = np.zeros((len(side.repair_manifest), m), dtype=np.uint8)
+    B = np.zeros((len(side.repair_manifest), size), dtype=np.uint8)
+    for r, rs in enumerate(side.repair_manifest):
+        c = _coefficients(rs.esi, k, side.seed)
+        val = np.frombuffer(bytes.fromhex(rs.bytes), dtype=np.uint8).copy()
+        if len(val) != size:
+            return None
+        if have:
+            val ^= np.bitwise_xor.reduce(mul[c[have][:, None], have_arr], axis=0)
+        A[r] = c[missing]
+        B[r] = val
+    # Gauss-Jordan: a pivot row per missing symbol, eliminated from every other row
+    used = np.zeros(A.shape[0], dtype=bool)
+    pivot_of = [-1] * m
+    for j in range(m):
+        cand = [r for r in range(A.shape[0]) if not used[r] and A[r, j] != 0]
+        if not cand:
+            return None
+        p = cand[0]
+        used[p] = True
+        pivot_of[j] = p
+        f = inv[A[p, j]]
+        A[p] = mul[f, A[p]]
+        B[p] = mul[f, B[p]]
+        for r in range(A.shape[0]):
+            if r != p and A[r, j] != 0:
+                g = A[r, j]
+                A[r] ^= mul[g, A[p]]
+                B[r] ^= mul[g, B[p]]
+    out = list(received)
+    for j, i in enumerate(missing):
+        out[i] = B[pivot_of[j]].tobytes()
     data = b"".join(out)[: side.payload_len]
     return data if hash_bytes(data) == side.source_hash else None

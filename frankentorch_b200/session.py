@@ -132,6 +132,11 @@ class FrankenTorchSession:
         self._device_enum = Device.Cuda if self.is_cuda else Device.Cpu
         self.runtime.ledger.record(EvidenceKind.Policy,
                                    f"session device={self.device} default_dtype={self.default_dtype.value} seed={seed}")
+        if not self.is_cuda:
+            # thread width of the CPU reference kernels (FT_CPU_THREADS), decided once per process
+            from .runtime.cpu_pool import configure_cpu_threads, resolve_spec
+            if resolve_spec():
+                configure_cpu_threads(ledger=self.runtime.ledger)
 
     # ------------------------------------------------------------------ mode / evidence
     @property

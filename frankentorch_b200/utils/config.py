@@ -42,6 +42,14 @@ ENV_FLAGS: Dict[str, EnvFlag] = {f.name: f for f in (
     EnvFlag("FT_COMM_CTAS", 20, int, "copy CTAs of the gather-fused GEMMs"),
     EnvFlag("FT_MODE", "strict", str, "execution mode of new sessions: strict or hardened"),
     EnvFlag("FT_ENC_CHUNK", 8, int, "encoder inference: layers per CUDA graph (models/encoder.py)"),
+    EnvFlag("FT_CPU_THREADS", "", str,
+            "thread width of the CPU reference kernels: unset = serial, 'auto' = min(16, physical cores), or a count"),
+    EnvFlag("FT_DP_OVERLAP", True, _bool, "start each gradient bucket's reduction under the backward pass"),
+    EnvFlag("FT_DP_DEFER", True, _bool, "run the sharded AdamW + parameter all-gather under the next forward pass"),
+    EnvFlag("FT_DP_WIRE", "bf16", str, "gradient type on NVLink for the fused data-parallel path: bf16 or fp32"),
+    EnvFlag("FT_DP_BUCKET_MB", 0.0, float, "gradient bucket size in MB of bf16 (0 = 32)"),
+    EnvFlag("FT_DP_CTAS", 48, int, "CTAs of a bucket's push / reduce kernels while the backward pass runs"),
+    EnvFlag("FT_DP_TAIL_CTAS", 592, int, "CTAs of the buckets that finish with the backward pass"),
 )}
 
 _cache: Dict[str, Any] = {}

@@ -1,0 +1,546 @@
+"""Property and fuzz tier (hypothesis, CPU only).
+
+The reference fuzzes its parsers and kernels with libFuzzer targets (fuzz/fuzz_targets/*.rs:
+ft_serialize_state_dict, ft_serialize_checkpoint_roundtrip, ft_serialize_raptorq_sidecar, the
+schema-parser target, ...) and states scheduler / determinism properties with proptest
+(ft-autograd/src/lib.rs:23102-23269).  The same contracts, stated as properties:
+
+* parsers are total: arbitrary bytes / strings either decode or raise the module's typed error,
+  never anything else;
+* encoders round-trip exactly;
+* the backward scheduler is a function of the graph alone, replays, and its telemetry is
+  self-consistent;
+* strict never succeeds where hardened fails; fallbacks are flagged.
+"""
+import ctypes as C
+import json
+import math
+import struct
+
+import hypothesis.strategies as st
+import numpy as np
+import pytest
+import torch
+from hypothesis import HealthCheck, assume, example, given, settings
+
+from frankentorch_b200 import serialize
+from frankentorch_b200.autograd.tape import BackwardOptions, TensorTape
+from frankentorch_b200.core.dtype import DType
+from frankentorch_b200.dispatch import keys as dk
+from frankentorch_b200.dispatch.schema import OpSchemaError, parse_schema_name, parse_schema_or_name
+from frankentorch_b200.runtime import native
+from frankentorch_b200.runtime.ledger import ExecutionMode
+from frankentorch_b200.serialize import SerializeError, SnapshotEntry
+from frankentorch_b200.session import FrankenTorchSession
+
+FAST = settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+SLOW = settings(max_examples=25, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+
+_DT = [torch.float64, torch.float32, torch.float16, torch.bfloat16]
+finite = st.floats(allow_nan=False, allow_infinity=False, width=32, min_value=-1e4, max_value=1e4)
+
+
+@st.composite
+def state_dicts(draw):
+    n = draw(st.integers(0, 5))
+    sd = {}
+    for i in range(n):
+        key = draw(st.text(alphabet="abcdefghij._0123456789é", min_size=1, max_size=12)) + str(i)
+        shape = draw(st.lists(st.integers(0, 4), min_size=0, max_size=3))
+        numel = int(np.prod(shape)) if shape else 1
+        vals = draw(st.lists(finite, min_size=numel, max_size=numel))
+        dt = draw(st.sampled_from(_DT))
+        sd[key] = torch.tensor(vals, dtype=torch.float64).reshape(shape).to(dt)
+    return sd
+
+
+# ------------------------------------------------------------------------------------ FTSV
+@FAST
+@given(state_dicts())
+def test_ftsv_round_trip_is_exact_and_sorted(sd):
+    data = serialize.state_dict_to_bytes(sd)
+    back = serialize.load_state_dict_from_bytes(data)
+    assert list(back) == sorted(sd)
+    for k in sd:
+        assert back[k].dtype == sd[k].dtype and tuple(back[k].shape) == tuple(sd[k].shape)
+        assert torch.equal(back[k].view(torch.uint8 if back[k].numel() == 0 else back[k].dtype), sd[k]) or \
+            back[k].numel() == 0
+    assert serialize.state_dict_to_bytes(back) == data               # byte-stable re-encode
+
+
+@FAST
+@given(st.binary(max_size=300))
+@example(b"FTSV" + struct.pack("<IQ", 1, 2 ** 62))
+@example(b"FTSV" + struct.pack("<IQ", 9, 0))
+def test_ftsv_loader_is_total_on_arbitrary_bytes(blob):
+    try:
+        out = serialize.load_state_dict_from_bytes(blob)
+    except SerializeError:
+        return
+    assert isinstance(out, dict)
+
+
+@FAST
+@given(state_dicts(), st.data())
+def test_ftsv_truncation_and_trailing_bytes_fail_closed(sd, data):
+    blob = serialize.state_dict_to_bytes(sd)
+    cut = data.draw(st.integers(0, max(0, len(blob) - 1)))
+    with pytest.raises(SerializeError):
+        serialize.load_state_dict_from_bytes(blob[:cut])
+    with pytest.raises(SerializeError):
+        serialize.load_state_dict_from_bytes(blob + b"\x00")
+
+
+@FAST
+@given(state_dicts(), st.data())
+def test_ftsv_byte_flips_never_escape_the_typed_error(sd, data):
+    blob = bytearray(serialize.state_dict_to_bytes(sd))
+    pos = data.draw(st.integers(0, len(blob) - 1))
+    blob[pos] ^= data.draw(st.integers(1, 255))
+    try:
+        serialize.load_state_dict_from_bytes(bytes(blob))
+    except SerializeError:
+        pass
+
+
+# ------------------------------------------------------------------------------------ envelope
+entries_st = st.lists(st.builds(SnapshotEntry, st.integers(0, 2 ** 40), finite, st.one_of(st.none(), finite)),
+                      max_size=8)
+
+
+@FAST
+@given(entries_st, st.sampled_from([ExecutionMode.Strict, ExecutionMode.Hardened]))
+def test_envelope_round_trip_normalises_and_verifies(entries, mode):
+    text = serialize.encode_checkpoint(entries, mode)
+    m2, back = serialize.decode_checkpoint(text, mode)
+    assert m2 == mode
+    assert [(e.node_id, e.value, e.grad) for e in back] == \
+        [(e.node_id, e.value, e.grad) for e in serialize.normalize_entries(entries)]
+    assert serialize.encode_checkpoint(list(reversed(entries)), mode) == text       # order-insensitive
+
+
+@FAST
+@given(entries_st, st.data())
+def test_envelope_mutations_fail_closed_in_both_modes(entries, data):
+    doc = json.loads(serialize.encode_checkpoint(entries, ExecutionMode.Strict))
+    kind = data.draw(st.sampled_from(["extra_field", "bad_hash", "version", "array", "entry_field", "garbage"]))
+    if kind == "extra_field":
+        doc["surprise"] = 1
+    elif kind == "bad_hash":
+        doc["source_hash"] = "det64:0000000000000000" if doc["source_hash"] != "det64:0000000000000000" else "det64:1"
+    elif kind == "version":
+        doc["schema_version"] = 99
+    elif kind == "array":
+        doc = [doc]
+    elif kind == "entry_field":
+        assume(doc["entries"])
+        doc["entries"][0]["zzz"] = 0
+    text = json.dumps(doc) if kind != "garbage" else data.draw(st.text(max_size=40))
+    for mode in (ExecutionMode.Strict, ExecutionMode.Hardened):
+        try:
+            serialize.decode_checkpoint(text, mode)
+        except SerializeError:
+            continue
+        assert kind == "garbage"      # only random text may happen to be ... nothing valid, in fact
+        pytest.fail("a mutated envelope decoded")
+
+
+@FAST
+@given(st.sampled_from([float("nan"), float("inf"), float("-inf")]))
+def test_envelope_rejects_non_finite_values_at_encode(x):
+    with pytest.raises(SerializeError):
+        serialize.encode_checkpoint([SnapshotEntry(0, x, None)])
+
+
+# ------------------------------------------------------------------------------------ sidecar
+@SLOW
+@given(st.binary(min_size=1, max_size=3000), st.integers(0, 6), st.data())
+def test_sidecar_recovers_any_loss_up_to_the_repair_count(payload, req, data):
+    side, proof = serialize.generate_repair_sidecar(payload, req)
+    assert side.code == serialize.CODE_NAME and side.repair_symbols == max(req, 1) + 8
+    assert side.symbol_size == serialize.symbol_size_for(len(payload)) and proof.recovered
+    size, k = side.symbol_size, side.k
+    padded = payload + bytes(k * size - len(payload))
+    syms = [padded[i * size:(i + 1) * size] for i in range(k)]
+    n_lost = data.draw(st.integers(0, min(k, side.repair_symbols - 2)))    # two surplus symbols: singular systems ~2^-24
+    lost = set(data.draw(st.permutations(list(range(k))))[:n_lost])
+    rec = serialize.decode_with_sidecar([None if i in lost else s for i, s in enumerate(syms)], side)
+    assert rec == payload
+    # more losses than repair symbols can never be repaired, and must say so
+    if k > side.repair_symbols:
+        assert serialize.decode_with_sidecar([None] * (side.repair_symbols + 1) + syms[side.repair_symbols + 1:], side) is None
+
+
+@SLOW
+@given(st.binary(min_size=40, max_size=600), st.data())
+def test_sidecar_detects_corrupted_symbols(payload, data):
+    side, _ = serialize.generate_repair_sidecar(payload, 2)
+    size, k = side.symbol_size, side.k
+    padded = payload + bytes(k * size - len(payload))
+    syms = [padded[i * size:(i + 1) * size] for i in range(k)]
+    j = data.draw(st.integers(0, k - 1))
+    assume(j * size < len(payload))
+    bad = bytearray(syms[j])
+    bad[0] ^= 0x5A
+    syms[j] = bytes(bad)
+    lost = (j + 1) % k
+    got = serialize.decode_with_sidecar([None if i == lost and k > 1 else s for i, s in enumerate(syms)], side)
+    assert got is None                      # the hash check refuses a wrong reconstruction
+
+
+def test_sidecar_limits_follow_the_reference():
+    with pytest.raises(SerializeError):
+        serialize.generate_repair_sidecar(b"abc", 1025)
+    assert serialize.repair_symbol_count(0, 10) == 9 and serialize.repair_symbol_count(1024, 10) == 1032
+
+
+# ------------------------------------------------------------------------------------ schema parser
+@FAST
+@given(st.text(max_size=60))
+@example("aten::add.Tensor(Tensor self, Tensor other, *, Scalar alpha=1) -> Tensor")
+@example("aten::add.out(Tensor self, Tensor(a!) out) -> Tensor(a!)")
+@example("::")
+@example("a::b(")
+def test_schema_parser_is_total(text):
+    for fn in (parse_schema_name, parse_schema_or_name):
+        try:
+            fn(text)
+        except OpSchemaError:
+            pass
+
+
+@FAST
+@given(st.from_regex(r"[a-z]{1,8}", fullmatch=True), st.from_regex(r"[a-z][a-z0-9]{0,8}", fullmatch=True),
+       st.one_of(st.none(), st.from_regex(r"[A-Za-z][A-Za-z0-9]{0,6}", fullmatch=True)), st.booleans())
+def test_schema_names_normalise_and_reparse(ns, base, overload, inplace):
+    text = f"{ns}::{base}" + ("_" if inplace else "") + (f".{overload}" if overload else "")
+    name = parse_schema_name(text)
+    assert (name.base, name.overload, name.is_inplace) == (base, overload, inplace)
+    again = parse_schema_name(f"{ns}::" + name.unambiguous_name())     # the normal form is a fixed point
+    assert again == name
+
+
+# ------------------------------------------------------------------------------------ safetensors
+@FAST
+@given(blob=st.binary(max_size=200))
+def test_safetensors_loader_is_total(tmp_path_factory, blob):
+    p = tmp_path_factory.mktemp("st") / "x.safetensors"
+    p.write_bytes(blob)
+    try:
+        serialize.load_safetensors(str(p))
+    except SerializeError:
+        pass
+
+
+@SLOW
+@given(sd=state_dicts())
+def test_safetensors_round_trip(tmp_path_factory, sd):
+    sd = {k: v for k, v in sd.items() if v.numel() > 0}
+    p = str(tmp_path_factory.mktemp("st") / "x.safetensors")
+    serialize.save_safetensors(sd, p, metadata={"who": "test"})
+    back = serialize.load_safetensors(p)
+    assert sorted(back) == sorted(sd)
+    for k in sd:
+        assert torch.equal(back[k], sd[k])
+    assert serialize.load_safetensors_metadata(p) == {"who": "test"}
+
+
+# ------------------------------------------------------------------------------------ scheduler on random DAGs
+@st.composite
+def dags(draw):
+    n_leaf = draw(st.integers(1, 4))
+    n_op = draw(st.integers(1, 14))
+    nodes = [("leaf", (), draw(st.booleans()) or i == 0) for i in range(n_leaf)]
+    for j in range(n_op):
+        k = draw(st.integers(1, 3))
+        ins = tuple(draw(st.integers(0, len(nodes) - 1)) for _ in range(k))
+        nodes.append(("op", ins, None))
+    return nodes
+
+
+def _build_core(nodes):
+    lib = native.load()
+    h = lib.ftc_tape_new()
+    rg = []
+    for kind, ins, flag in nodes:
+        arr = (C.c_int64 * max(1, len(ins)))(*ins)
+        r = bool(flag) if kind == "leaf" else any(rg[i] for i in ins)
+        lib.ftc_tape_add_node(h, arr, len(ins), int(r), int(kind == "leaf"))
+        rg.append(r)
+    return lib, h, rg
+
+
+def _schedule(lib, h, root, n):
+    order, deps, stats = (C.c_int64 * n)(), (C.c_int64 * n)(), (C.c_int64 * 3)()
+    cnt = lib.ftc_tape_schedule(h, root, 1, order, deps, stats)
+    return cnt, list(order[:max(cnt, 0)]), list(deps[:n]), tuple(stats)
+
+
+@FAST
+@given(dags())
+def test_scheduler_replays_and_its_telemetry_is_self_consistent(nodes):
+    lib, h, rg = _build_core(nodes)
+    n, root = len(nodes), len(nodes) - 1
+    try:
+        a = _schedule(lib, h, root, n)
+        b = _schedule(lib, h, root, n)
+        assert a == b                                            # a function of the graph alone
+        cnt, order, deps, (pushes, pops, max_len) = a
+        if not rg[root]:
+            assert cnt == -2
+            return
+        assert cnt == len(order) == len(set(order)) and order[0] == root
+        assert pushes == pops == cnt and 1 <= max_len <= cnt
+        pos = {v: i for i, v in enumerate(order)}
+        for v in order:                                           # consumers before producers
+            for i in nodes[v][1]:
+                if i in pos:
+                    assert pos[v] < pos[i]
+        # every input of a scheduled node is scheduled (the order is a property of the graph alone, a
+        # node that does not require grad still takes its place); dependency counts = reachable consumers
+        for v in order:
+            for i in nodes[v][1]:
+                assert i in pos
+        want = [0] * n
+        for v in order:
+            for i in nodes[v][1]:
+                want[i] += 1
+        assert [deps[i] for i in order] == [want[i] for i in order]
+        # among simultaneously ready nodes the highest id runs first: the order is the unique
+        # topological order produced by a max-heap, recomputed here
+        import heapq
+        remaining, ready, out = list(want), [-root], []
+        while ready:
+            v = -heapq.heappop(ready)
+            out.append(v)
+            for i in nodes[v][1]:
+                remaining[i] -= 1
+                if remaining[i] == 0:
+                    heapq.heappush(ready, -i)
+        assert out == order
+    finally:
+        lib.ftc_tape_free(h)
+
+
+_UN = ["tanh", "sigmoid", "exp", "neg", "square"]
+_BIN = ["add", "sub", "mul"]
+
+
+@st.composite
+def expression(draw):
+    n_leaf = draw(st.integers(1, 3))
+    leaves = [draw(st.lists(st.floats(-1.5, 1.5, width=32), min_size=3, max_size=3)) for _ in range(n_leaf)]
+    prog = []
+    for j in range(draw(st.integers(1, 8))):
+        if draw(st.booleans()):
+            prog.append((draw(st.sampled_from(_UN)), draw(st.integers(0, n_leaf + j - 1)), None))
+        else:
+            prog.append((draw(st.sampled_from(_BIN)), draw(st.integers(0, n_leaf + j - 1)),
+                         draw(st.integers(0, n_leaf + j - 1))))
+    return leaves, prog
+
+
+def _run_expr(leaves, prog):
+    s = FrankenTorchSession("strict")
+    ids = [s.tensor_variable(v, [3], True) for v in leaves]
+    for op, a, b in prog:
+        ids.append(getattr(s, "tensor_" + op)(ids[a]) if b is None else getattr(s, "tensor_" + op)(ids[a], ids[b]))
+    root = s.tensor_sum(ids[-1])
+    rep = s.tensor_backward(root)
+    return [rep.gradient(i) for i in ids[:len(leaves)]], rep.telemetry, [st_.rule for st_ in rep.steps]
+
+
+@SLOW
+@given(expression())
+def test_tensor_backward_is_bitwise_replayable_and_matches_torch(case):
+    leaves, prog = case
+    g1, t1, r1 = _run_expr(leaves, prog)
+    g2, t2, r2 = _run_expr(leaves, prog)
+    assert t1.execution_order == t2.execution_order and t1.dependency_snapshot == t2.dependency_snapshot and r1 == r2
+    for a, b in zip(g1, g2):
+        assert (a is None and b is None) or torch.equal(a, b)
+    ts = [torch.tensor(v, dtype=torch.float64, requires_grad=True) for v in leaves]
+    vals = list(ts)
+    fn = {"tanh": torch.tanh, "sigmoid": torch.sigmoid, "exp": torch.exp, "neg": torch.neg, "square": torch.square,
+          "add": torch.add, "sub": torch.sub, "mul": torch.mul}
+    for op, a, b in prog:
+        vals.append(fn[op](vals[a]) if b is None else fn[op](vals[a], vals[b]))
+    want = torch.autograd.grad(vals[-1].sum(), ts, allow_unused=True)
+    for got, w in zip(g1, want):
+        if w is None:
+            assert got is None or float(got.abs().max()) == 0.0
+        else:
+            assert got is not None and torch.allclose(got, w, rtol=1e-10, atol=1e-10)
+
+
+# ------------------------------------------------------------------------------------ dispatch keys
+@FAST
+@given(st.integers(0, 2 ** 12 - 1))
+def test_dispatch_resolution_strict_is_never_laxer_than_hardened(bits):
+    ks = dk.DispatchKeySet(bits)
+    res = {}
+    for mode in (ExecutionMode.Strict, ExecutionMode.Hardened):
+        try:
+            res[mode] = dk.resolve(mode, ks)
+        except dk.DispatchKeyError as e:
+            res[mode] = e
+    s, h = res[ExecutionMode.Strict], res[ExecutionMode.Hardened]
+    if not isinstance(s, Exception):
+        assert not isinstance(h, Exception) and s == h and s[3] is False      # strict success: same, no fallback
+    if isinstance(h, Exception):
+        assert isinstance(s, Exception)
+    if not isinstance(h, Exception) and isinstance(s, Exception):
+        assert h[3] is True                                                    # the difference is a flagged fallback
+
+
+@FAST
+@given(st.sampled_from(list(DType)), st.sampled_from(list(DType)), st.sampled_from(list(DType)))
+def test_dtype_promotion_is_commutative_idempotent_and_monotone(a, b, c):
+    try:
+        ab = a.promote_types(b)
+    except Exception:
+        with pytest.raises(Exception):
+            b.promote_types(a)
+        return
+    assert ab == b.promote_types(a) and a.promote_types(a) == a
+    # the result absorbs both operands: promoting it with either changes nothing
+    assert ab.promote_types(a) == ab and ab.promote_types(b) == ab
+
+
+# ------------------------------------------------------------------------------------ data / PRNG
+@FAST
+@given(st.integers(0, 2 ** 64 - 1), st.integers(0, 200))
+def test_lcg_shuffle_is_a_replayable_permutation(seed, n):
+    lib = native.load()
+
+    def run():
+        state = (C.c_uint64 * 1)(seed)
+        idx = torch.arange(n, dtype=torch.int64)
+        lib.ftc_lcg_shuffle(state, idx.data_ptr(), n)
+        return idx.tolist(), int(state[0])
+    a, b = run(), run()
+    assert a == b and sorted(a[0]) == list(range(n))
+
+
+@FAST
+@given(st.integers(0, 2 ** 64 - 1), st.integers(1, 50), st.integers(0, 49))
+def test_xoshiro_state_round_trip_resumes_the_stream(seed, n, cut):
+    from frankentorch_b200.session import Xoshiro256pp
+    cut = min(cut, n)
+    r = Xoshiro256pp(seed)
+    full = r.uniform(n).tolist()
+    r2 = Xoshiro256pp(seed)
+    head = r2.uniform(cut).tolist()
+    r3 = Xoshiro256pp(0)
+    r3.set_state(r2.get_state())
+    assert head + r3.uniform(n - cut).tolist() == full
+    assert all(0.0 <= x < 1.0 for x in full)
+
+
+@SLOW
+@given(st.integers(1, 40), st.integers(1, 9), st.booleans(), st.booleans(), st.integers(0, 12))
+def test_dataloader_state_dict_resumes_mid_epoch(n, bs, shuffle, drop_last, k):
+    from frankentorch_b200 import data as D
+    s = FrankenTorchSession("strict")
+    ds = D.TensorDataset({"x": torch.arange(n, dtype=torch.float64).reshape(n, 1)})
+
+    def batches(loader, count):
+        out = []
+        for _ in range(count):
+            b = loader.next_batch(s)
+            if b is None:
+                loader.reset()
+                b = loader.next_batch(s)
+                if b is None:
+                    break
+            out.append(s.tensor_values(b.get("x")))
+        return out
+    cfg = D.DataLoaderConfig(bs).with_shuffle(shuffle).with_drop_last(drop_last)
+    a = D.DataLoader(ds, cfg)
+    ref = batches(a, k + 5)
+    b1 = D.DataLoader(ds, cfg)
+    head = batches(b1, k)
+    state = b1.state_dict()
+    b2 = D.DataLoader(ds, cfg)
+    b2.load_state_dict(json.loads(json.dumps(state)))
+    assert head + batches(b2, len(ref) - len(head)) == ref
+
+
+# ------------------------------------------------------------------------------------ reductions / pool
+@FAST
+@given(st.lists(st.floats(-1e6, 1e6, allow_nan=False, width=64), min_size=0, max_size=2000))
+def test_pairwise_sum_tree_is_fixed_and_accurate(xs):
+    lib = native.load()
+    x = torch.tensor(xs, dtype=torch.float64)
+    got = lib.ftc_pairwise_sum(x.data_ptr(), len(xs))
+
+    def tree(lo, hi):
+        if hi - lo <= 128:
+            s = 0.0
+            for v in xs[lo:hi]:
+                s += v
+            return s
+        mid = lo + (hi - lo) // 2
+        return tree(lo, mid) + tree(mid, hi)
+    assert got == tree(0, len(xs))                                # the documented tree, bit for bit
+    assert abs(got - math.fsum(xs)) <= 1e-9 * (1.0 + sum(abs(v) for v in xs))
+
+
+# ------------------------------------------------------------------------------------ ledger
+@FAST
+@given(st.integers(4, 40), st.integers(0, 200))
+def test_ledger_keeps_its_anchor_and_stays_bounded(cap, n):
+    from frankentorch_b200.runtime.ledger import EvidenceKind, EvidenceLedger
+    led = EvidenceLedger(soft_cap=cap)
+    led.record(EvidenceKind.Policy, "anchor")
+    for i in range(n):
+        led.record(EvidenceKind.Dispatch, f"e{i}")
+    ev = led.entries()
+    assert ev[0].summary == "anchor" and len(ev) <= cap + 1
+    if n:
+        assert ev[-1].summary == f"e{n - 1}"
+    tail = [int(e.summary[1:]) for e in ev[1:]]
+    assert tail == sorted(tail) and (not tail or tail == list(range(tail[0], tail[0] + len(tail))))
+
+
+# ------------------------------------------------------------------------------------ harness
+@FAST
+@given(st.integers(0, 64), st.integers(0, 64))
+def test_incumbent_sample_rounds_spreads_a_fixed_count(rounds, samples):
+    from frankentorch_b200.harness import incumbent_sample_rounds
+    r = incumbent_sample_rounds(rounds, samples)
+    assert len(r) == min(rounds, samples) and r == sorted(set(r)) and all(0 <= x < rounds for x in r)
+
+
+@FAST
+@given(st.text(max_size=50))
+@example("PT_SAMPLE lane -1.0 0")
+@example("PT_SAMPLE lane nan 0")
+@example("PT_SAMPLE lane 2.5 1e3")
+def test_sample_line_parser_is_total_and_refuses_broken_durations(line):
+    from frankentorch_b200.harness import parse_reported_version, parse_sample_line
+    s = parse_sample_line(line)
+    if s is not None:
+        assert math.isfinite(s.milliseconds) and s.milliseconds >= 0.0 and s.lane
+    parse_reported_version(line)
+
+
+# ------------------------------------------------------------------------------------ optimizer math
+@FAST
+@given(st.lists(st.tuples(finite, finite), min_size=1, max_size=16), st.floats(1e-5, 0.5), st.floats(0.0, 0.3),
+       st.integers(1, 5))
+def test_native_adamw_matches_the_formula_and_its_parallel_form(pairs, lr, wd, step):
+    lib = native.load()
+    p0 = torch.tensor([a for a, _ in pairs], dtype=torch.float64)
+    g = torch.tensor([b for _, b in pairs], dtype=torch.float64)
+    outs = []
+    for fn in (lib.ftc_adamw_f64, lib.ftc_adamw_f64_par):
+        p, m, v = p0.clone(), torch.zeros_like(p0), torch.zeros_like(p0)
+        fn(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), len(pairs), lr, 0.9, 0.999, 1e-8, wd, step)
+        outs.append((p, m, v))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    m = 0.1 * g
+    v = 0.001 * g * g
+    want = p0 - (p0 * lr * wd + lr * (m / (1 - 0.9 ** step)) / (torch.sqrt(v / (1 - 0.999 ** step)) + 1e-8))
+    assert torch.allclose(outs[0][0], want, rtol=1e-12, atol=1e-12)
