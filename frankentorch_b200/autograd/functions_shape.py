@@ -259,6 +259,14 @@ def _topk_vjp(g, i, o, kw):
 
 _reg("topk", lambda x, k=1, dim=-1, largest=True: torch.topk(x, k, dim=dim, largest=largest, sorted=True).values,
      _topk_vjp, "d(topk(x))/dx=scatter_grad_to_topk_positions")
+def _index_select_sparse_vjp(g, i, o, kw):
+    from .tape import RowSparseGradient
+    return [RowSparseGradient.from_indexed(i[1], g, i[0].shape), None]
+
+
+# the same gather as `embedding`; its table gradient is row-sparse (ft-autograd/src/lib.rs:582-587, :8204)
+_reg("index_select_sparse", lambda w, ids: w[ids], _index_select_sparse_vjp,
+     "d(index_select(x))/dx=scatter_add_grad [row-sparse]")
 _reg("embedding", lambda w, ids: w[ids],
      lambda g, i, o, kw: [torch.zeros_like(i[0], dtype=g.dtype).index_add_(0, i[1].reshape(-1), g.reshape(-1, i[0].shape[1])), None],
      "d(index_select(x))/dx=scatter_add_grad")

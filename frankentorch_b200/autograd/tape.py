@@ -141,12 +141,58 @@ class TensorBackwardReport:
     telemetry: TensorSchedulerTelemetry
     # create_graph=True only: tape id of the node that holds each gradient (differentiable further)
     gradient_nodes: Dict[int, int] = field(default_factory=dict)
+    # leaves whose whole gradient of this backward arrived row-sparse (index_select_sparse)
+    sparse_gradients: Dict[int, "RowSparseGradient"] = field(default_factory=dict)
 
     def gradient(self, node: int) -> Optional[torch.Tensor]:
-        return self.gradients.get(int(node))
+        g = self.gradients.get(int(node))
+        if g is None and int(node) in self.sparse_gradients:
+            return self.sparse_gradients[int(node)].to_dense()
+        return g
+
+    def sparse_gradient(self, node: int):
+        """The row-sparse gradient of ``node`` as a ``SparseCOOTensor`` (None if it was not sparse)."""
+        g = self.sparse_gradients.get(int(node))
+        return None if g is None else g.to_coo()
 
     def gradient_node(self, node: int) -> Optional[int]:
         return self.gradient_nodes.get(int(node))
+
+
+class RowSparseGradient:
+    """Gradient of a 2-D (or higher) table that is zero outside ``rows``: ``values[i]`` is the
+    gradient of row ``rows[i]``; rows are unique and ascending, duplicates having been summed in
+    source order (so the sum's bits do not depend on how the work was split).  What
+    ``index_select_sparse`` hands to ``SparseAdam`` (ft-autograd/src/lib.rs:8204, :15680-15750)."""
+
+    __slots__ = ("rows", "values", "shape")
+
+    def __init__(self, rows: torch.Tensor, values: torch.Tensor, shape):
+        self.rows, self.values, self.shape = rows, values, tuple(shape)
+
+    @staticmethod
+    def from_indexed(ids: torch.Tensor, g: torch.Tensor, shape) -> "RowSparseGradient":
+        """Sum the rows of ``g`` (one per entry of ``ids``) that hit the same table row."""
+        flat = ids.reshape(-1).to(torch.int64)
+        g2 = g.reshape(flat.numel(), -1)
+        rows, inverse = torch.unique(flat, sorted=True, return_inverse=True)
+        values = torch.zeros((rows.numel(), g2.shape[1]), dtype=g2.dtype, device=g2.device)
+        values.index_add_(0, inverse, g2)            # (CPU index_add_ adds in source order)
+        return RowSparseGradient(rows, values.reshape((rows.numel(),) + tuple(shape[1:])), shape)
+
+    def add(self, other: "RowSparseGradient") -> "RowSparseGradient":
+        ids = torch.cat([self.rows, other.rows])
+        vals = torch.cat([self.values, other.values])
+        return RowSparseGradient.from_indexed(ids, vals, self.shape)
+
+    def to_dense(self) -> torch.Tensor:
+        out = torch.zeros(self.shape, dtype=self.values.dtype, device=self.values.device)
+        out.index_add_(0, self.rows, self.values)
+        return out
+
+    def to_coo(self):
+        from ..core.tensor import SparseCOOTensor
+        return SparseCOOTensor(self.rows.reshape(1, -1), self.values, self.shape)
 
 
 # Marker a VJP rule returns for an input whose gradient it already accumulated in place into
@@ -192,7 +238,8 @@ class GradTargets:
 
 class TensorNode:
     __slots__ = ("id", "op", "inputs", "value", "requires_grad", "is_leaf", "vjp", "rule", "retain_grad",
-                 "hooks", "grad", "grad_buffer", "grad_buffer_filled", "version", "saved", "name", "cg")
+                 "hooks", "grad", "grad_buffer", "grad_buffer_filled", "version", "saved", "name", "cg",
+                 "sparse_grad")
 
     def __init__(self, nid, op, inputs, value, requires_grad, is_leaf, vjp, rule):
         self.id = nid
@@ -212,6 +259,7 @@ class TensorNode:
         self.saved = None
         self.name = None
         self.cg = None      # graph-building backward: (grad node id) -> per-input contribution node ids
+        self.sparse_grad = None   # accumulated row-sparse gradient (leaves fed through index_select_sparse)
 
 
 @dataclass(frozen=True)
@@ -357,7 +405,15 @@ class TensorTape:
         n = self._node(nid)
         if n.grad_buffer is not None:
             return n.grad_buffer if n.grad_buffer_filled else None
+        if n.sparse_grad is not None:
+            dense = n.sparse_grad.to_dense()
+            return dense if n.grad is None else n.grad + dense
         return n.grad
+
+    def accumulated_sparse_gradient(self, nid: int) -> Optional["RowSparseGradient"]:
+        """The accumulated gradient in row-sparse form, when all of it arrived that way."""
+        n = self._node(nid)
+        return n.sparse_grad if n.grad is None else None
 
     def set_accumulated_gradient(self, nid: int, grad: Optional[torch.Tensor]) -> None:
         n = self._node(nid)
@@ -370,6 +426,7 @@ class TensorTape:
     def zero_accumulated_gradient(self, nid: int) -> None:
         n = self._node(nid)
         n.grad = None
+        n.sparse_grad = None
         n.grad_buffer_filled = False
 
     def bind_grad_buffer(self, nid: int, buf: torch.Tensor) -> None:
@@ -421,11 +478,15 @@ class TensorTape:
             seed = torch.ones_like(rootn.value, dtype=self.grad_dtype or rootn.value.dtype)
             seed._ft_unit_seed = True   # lets fused loss rules skip a multiply by one
         grads: Dict[int, torch.Tensor] = {root: seed}
+        sparse: Dict[int, RowSparseGradient] = {}
         steps: List[TensorBackwardStep] = []
         nodes = self.nodes
         for nid in order:
             node = nodes[nid]
             incoming = grads.get(nid)
+            if incoming is None and nid in sparse:
+                steps.append(TensorBackwardStep(nid, int(node.value.numel()), "leaf"))
+                continue
             if incoming is None:
                 # No gradient reached this node: either it does not require grad, or every rule
                 # that feeds it accumulated in place (bound gradient buffers).  A zero gradient
@@ -465,6 +526,15 @@ class TensorTape:
                     continue
                 if not nodes[inp].requires_grad:
                     continue
+                if isinstance(g, RowSparseGradient):
+                    tgt = nodes[inp]
+                    if tgt.is_leaf and not tgt.hooks and tgt.grad_buffer is None and inp not in grads:
+                        prev_s = sparse.get(inp)
+                        sparse[inp] = g if prev_s is None else prev_s.add(g)
+                        continue
+                    g = g.to_dense()          # a consumer that needs the dense form (hooks, non-leaf, mixed)
+                if inp in sparse:             # a dense contribution joins an earlier sparse one: go dense
+                    g = self.accumulate_fn(sparse.pop(inp).to_dense(), self._cast_grad(g))
                 g = self._cast_grad(g)
                 prev = grads.get(inp)
                 if prev is None:
@@ -495,13 +565,24 @@ class TensorTape:
                     node.grad_buffer_filled = True
             elif node.grad is None:
                 node.grad = g.clone() if g is seed else g
+                if node.sparse_grad is not None:          # earlier sparse history folds into the dense slot
+                    node.grad = node.grad + node.sparse_grad.to_dense()
+                    node.sparse_grad = None
             else:
                 node.grad = node.grad + g
 
+        for nid, sg in sparse.items():
+            node = nodes[nid]
+            sg = RowSparseGradient(sg.rows, self._cast_grad(sg.values), sg.shape)
+            sparse[nid] = sg
+            if node.grad is not None:                     # mixed history: keep accumulating densely
+                node.grad = node.grad + sg.to_dense()
+            else:
+                node.sparse_grad = sg if node.sparse_grad is None else node.sparse_grad.add(sg)
         if not (opts.retain_graph or opts.create_graph):
             self._lib.ftc_tape_mark_consumed(self._h)
         telemetry = TensorSchedulerTelemetry(order, pushes, pops, max_len, deps, depth, guard, fallback)
-        return TensorBackwardReport(grads, steps, telemetry)
+        return TensorBackwardReport(grads, steps, telemetry, sparse_gradients=sparse)
 
     # ------------------------------------------------------------------ graph-building backward
     def _backward_create_graph(self, root, opts, seed, order, deps, stats, depth, guard, fallback):

@@ -17,6 +17,11 @@ the number of graph launches per forward to ``ceil(layers / chunk)``.
 
 As in the reference the key projection has no bias (Whisper-style encoder), the GELU is the
 clamped tanh form and the output is the stack output before any final LayerNorm.
+
+``attach_stem`` + ``forward_from_mel`` run the encoder front as well (fused.rs:1060-1132): two
+1-D convolutions over time (kernel 3, padding 1; stride 1, then stride 2) as im2col + GEMM with
+the bias and the GELU in the epilogue, the positional embedding added as the second GEMM's
+residual, then the layer stack.
 """
 from __future__ import annotations
 
@@ -86,6 +91,43 @@ def reference_forward(layers: Sequence[EncoderLayerWeights], x: torch.Tensor, n_
     return x
 
 
+@dataclass
+class StemWeights:
+    """Conv stem in the reference's upload layout (fused.rs:1064-1081): ``conv*_wt`` is
+    ``[cin * 3, d_model]`` with row index ``ci * 3 + kk``; ``pos_emb`` is ``[n_ctx_cap, d_model]``."""
+    conv1_wt: torch.Tensor
+    conv1_b: torch.Tensor
+    conv2_wt: torch.Tensor
+    conv2_b: torch.Tensor
+    pos_emb: torch.Tensor
+
+    @staticmethod
+    def random(n_mels: int, d_model: int, n_ctx_cap: int, gen: torch.Generator) -> "StemWeights":
+        r = lambda *sh, s=1.0: torch.randn(*sh, generator=gen) * s
+        return StemWeights(r(n_mels * 3, d_model, s=(n_mels * 3) ** -0.5), r(d_model, s=0.02),
+                           r(d_model * 3, d_model, s=(d_model * 3) ** -0.5), r(d_model, s=0.02),
+                           r(n_ctx_cap, d_model, s=0.1))
+
+
+def stem_out_rows(t_in: int) -> int:
+    """Rows after conv1 (k3, s1, p1: unchanged) and conv2 (k3, s2, p1: halved, rounded up)."""
+    t1 = (t_in + 2 - 3) + 1
+    return (t1 + 2 - 3) // 2 + 1
+
+
+def reference_stem(stem: StemWeights, mel: torch.Tensor) -> torch.Tensor:
+    """conv1 + GELU -> conv2 + GELU -> + pos_emb in plain torch (oracle); ``mel`` is ``[t_in, n_mels]``."""
+    d = stem.conv1_b.shape[0]
+
+    def conv(x, wt, b, stride):
+        cin = x.shape[1]
+        w = wt.to(x).T.reshape(d, cin, 3)                                  # [out, cin, k]
+        y = torch.nn.functional.conv1d(x.T.unsqueeze(0), w, b.to(x), stride=stride, padding=1)
+        return _gelu_tanh_clamped(y.squeeze(0).T)
+    h = conv(conv(mel, stem.conv1_wt, stem.conv1_b, 1), stem.conv2_wt, stem.conv2_b, 2)
+    return h + stem.pos_emb.to(mel)[: h.shape[0]]
+
+
 class _GpuLayer:
     def __init__(self, l: EncoderLayerWeights, dev):
         bf = lambda t: t.to(dev, torch.bfloat16).contiguous()
@@ -117,6 +159,54 @@ class EncoderGpu:
         self.layers = [_GpuLayer(l, self.device) for l in layers]
         self._graphs: Dict[int, Tuple[list, torch.Tensor, torch.Tensor]] = {}
         self.launches_per_layer = 7
+        self.stem = None
+
+    # ------------------------------------------------------------------ conv stem
+    def attach_stem(self, stem: StemWeights, n_mels: int, n_ctx_cap: int) -> None:
+        """Upload the conv stem and the positional embedding (bf16, resident)."""
+        d = self.d_model
+        if tuple(stem.conv1_wt.shape) != (n_mels * 3, d) or tuple(stem.conv2_wt.shape) != (d * 3, d):
+            raise ValueError("conv weights must be [cin * 3, d_model]")
+        if tuple(stem.pos_emb.shape) != (n_ctx_cap, d):
+            raise ValueError("pos_emb must be [n_ctx_cap, d_model]")
+        if (n_mels * 3) % 8:
+            raise ValueError("n_mels * 3 must be a multiple of 8 (16-byte operand rows)")
+        bf = lambda t: t.to(self.device, torch.bfloat16).contiguous()
+        self.stem = dict(n_mels=n_mels, n_ctx_cap=n_ctx_cap, conv1_wt=bf(stem.conv1_wt), conv1_b=bf(stem.conv1_b),
+                         conv2_wt=bf(stem.conv2_wt), conv2_b=bf(stem.conv2_b), pos_emb=bf(stem.pos_emb))
+
+    def has_stem(self) -> bool:
+        return self.stem is not None
+
+    def _run_stem(self, mel_dev: torch.Tensor) -> torch.Tensor:
+        """``mel_dev``: fp32 ``[t_in, n_mels]`` on the device -> bf16 ``[t2, d_model]``; 8 launches."""
+        from ..ops import kernels as K
+        st = self.stem
+        c1 = K.cast_f32_to_bf16(K.im2col_1d(mel_dev, 3, 1, 1))
+        g1 = K.gemm(c1, st["conv1_wt"], b_mn=True, bias=st["conv1_b"], epi=K.EPI_GELU_TANH)
+        c2 = K.cast_f32_to_bf16(K.im2col_1d(K.cast_bf16_to_f32(g1), 3, 2, 1))
+        t2 = c2.shape[0]
+        return K.gemm(c2, st["conv2_wt"], b_mn=True, bias=st["conv2_b"], epi=K.EPI_GELU_TANH,
+                      resid=st["pos_emb"][:t2])
+
+    def forward_from_mel(self, mel: torch.Tensor, t_in: Optional[int] = None):
+        """The whole encoder front from the mel spectrogram ``[t_in, n_mels]`` (host or device floats):
+        conv1 (k3, s1, p1) + GELU -> conv2 (k3, s2, p1) + GELU -> + pos_emb -> layer stack.
+        Returns ``(activations before any final LayerNorm as fp32 on the host, rows)``."""
+        from ..ops import kernels as K
+        if self.stem is None:
+            raise RuntimeError("no conv stem attached (attach_stem)")
+        n_mels = self.stem["n_mels"]
+        t_in = int(mel.numel() // n_mels) if t_in is None else int(t_in)
+        if t_in == 0 or mel.numel() != t_in * n_mels:
+            raise ValueError(f"forward_from_mel input {mel.numel()} != {t_in}x{n_mels}")
+        t2 = stem_out_rows(t_in)
+        if t2 > self.stem["n_ctx_cap"]:
+            raise ValueError(f"forward_from_mel: conv output {t2} rows > positional capacity {self.stem['n_ctx_cap']}")
+        m = mel.reshape(t_in, n_mels).to(self.device, torch.float32, non_blocking=True).contiguous()
+        x = self._run_stem(m)
+        K.check_status()
+        return self.forward_stack(x).to("cpu", torch.float32), t2
 
     # ------------------------------------------------------------------ one chunk, eager
     def _run_layers(self, x: torch.Tensor, layers: List[_GpuLayer]) -> torch.Tensor:

@@ -330,9 +330,11 @@ class AlphaDropout(Dropout):
 
 # -------------------------------------------------------------------------------------- embeddings
 class Embedding(Module):
-    def __init__(self, session, num_embeddings: int, embedding_dim: int, padding_idx: Optional[int] = None):
+    def __init__(self, session, num_embeddings: int, embedding_dim: int, padding_idx: Optional[int] = None,
+                 sparse: bool = False):
         super().__init__()
         self.padding_idx = padding_idx
+        self.sparse = sparse        # row-sparse weight gradient for SparseAdam (ft-nn/src/lib.rs:2873 "+sparse")
         w = _param(session, (num_embeddings, embedding_dim), "normal", std=1.0)
         if padding_idx is not None:
             with session.no_grad():
@@ -340,7 +342,10 @@ class Embedding(Module):
         self.register_parameter("weight", w)
 
     def forward(self, session, ids):
-        out = session.tensor_embedding(self._parameters["weight"], ids)
+        if self.sparse:
+            out = session.tensor_index_select_sparse(self._parameters["weight"], ids)
+        else:
+            out = session.tensor_embedding(self._parameters["weight"], ids)
         if self.padding_idx is not None:
             h = session.register_tensor_hook  # gradient of the padding row is forced to zero
             pid, wid = self.padding_idx, self._parameters["weight"]

@@ -373,20 +373,42 @@ class SparseAdam(Optimizer):
         super().__init__(params, lr)
         self._betas, self._eps = tuple(betas), eps
 
-    def _update(self, p, w, g, t):
+    def step(self, session, report=None) -> None:
+        """Rows come from the tape's row-sparse accumulated gradient when the parameter was read
+        through ``index_select_sparse`` / ``Embedding(sparse=True)`` (no dense gradient is ever
+        formed, ft-optim/src/lib.rs:5519); a dense gradient is scanned for its non-zero rows."""
+        tape = session.tensor_tape
+        for p in self.params:
+            sg = tape.accumulated_sparse_gradient(p)
+            if sg is None:
+                g = self._grad(session, p)
+                if g is None:
+                    continue
+                g = g.to(torch.float64) if not g.is_cuda else g.to(torch.float32)
+                rows = torch.nonzero(g.reshape(g.shape[0], -1).abs().sum(1) != 0).reshape(-1)
+                vals = g[rows]
+            else:
+                rows = sg.rows
+                vals = sg.values.to(torch.float64) if not sg.values.is_cuda else sg.values.to(torch.float32)
+                if self._maximize:
+                    vals = -vals
+            self.steps[p] += 1
+            self._update_rows(p, session.tensor(p), rows, vals, self.steps[p])
+            tape.bump_version(p)
+
+    def _update_rows(self, p, w, rows, gm, t):
         b1, b2 = self._betas
-        g2 = g.reshape(g.shape[0], -1)
-        rows = torch.nonzero(g2.abs().sum(1) != 0).reshape(-1)
         if rows.numel() == 0:
             return
-        m, v = self._st(p, "m", g), self._st(p, "v", g)
-        gm = g[rows]
+        st = self.state[p]
+        if "m" not in st:
+            st["m"] = torch.zeros(w.shape, dtype=gm.dtype, device=w.device)
+            st["v"] = torch.zeros(w.shape, dtype=gm.dtype, device=w.device)
+        m, v = st["m"], st["v"]
         m[rows] = b1 * m[rows] + (1 - b1) * gm
         v[rows] = b2 * v[rows] + (1 - b2) * gm * gm
         upd = (m[rows] / (1 - b1 ** t)) / ((v[rows] / (1 - b2 ** t)).sqrt() + self._eps)
-        wf = w.to(g.dtype)
-        wf[rows] -= self.lr * upd
-        _apply(w, wf)
+        w[rows] = (w[rows].to(gm.dtype) - self.lr * upd).to(w.dtype)      # only the touched rows are rewritten
 
 
 class Muon(Optimizer):

@@ -50,3 +50,54 @@ def test_encoder_gpu_matches_the_fp32_oracle(seq, d, heads, n_layers, chunk):
     eager = EncoderGpu(layers, heads, chunk=1, use_cuda_graph=False).forward(x, seq)
     assert torch.equal(got, eager)                    # chunking and graphs do not change the bits
     assert len(enc.chunks()) == -(-n_layers // chunk)
+
+
+def test_reference_stem_is_two_strided_convolutions_plus_positions():
+    from frankentorch_b200.models.encoder import StemWeights, reference_stem, stem_out_rows
+    g = torch.Generator().manual_seed(4)
+    n_mels, d, t_in = 8, 16, 11
+    stem = StemWeights.random(n_mels, d, 32, g)
+    mel = torch.randn(t_in, n_mels, generator=g, dtype=torch.float64)
+    got = reference_stem(stem, mel)
+    assert got.shape == (stem_out_rows(t_in), d) and stem_out_rows(t_in) == 6 and stem_out_rows(12) == 6
+    # the gather the GPU path uses (column index ci * 3 + kk, zero padding) times the [cin*3, d] weight
+    def im2col(x, stride):
+        t, c = x.shape
+        t_out = (t + 2 - 3) // stride + 1
+        y = torch.zeros(t_out, c * 3, dtype=x.dtype)
+        for o in range(t_out):
+            for ci in range(c):
+                for kk in range(3):
+                    p = o * stride + kk - 1
+                    if 0 <= p < t:
+                        y[o, ci * 3 + kk] = x[p, ci]
+        return y
+    from frankentorch_b200.models.encoder import _gelu_tanh_clamped
+    h1 = _gelu_tanh_clamped(im2col(mel, 1) @ stem.conv1_wt.double() + stem.conv1_b.double())
+    h2 = _gelu_tanh_clamped(im2col(h1, 2) @ stem.conv2_wt.double() + stem.conv2_b.double())
+    assert torch.allclose(got, h2 + stem.pos_emb.double()[: h2.shape[0]], atol=1e-10)
+
+
+@pytest.mark.gpu
+def test_forward_from_mel_matches_the_fp32_oracle():
+    from frankentorch_b200.models.encoder import StemWeights, reference_stem, stem_out_rows
+    d, heads, n_mels, t_in = 256, 4, 80, 301
+    layers = _layers(2, d, 4 * d, seed=5)
+    g = torch.Generator().manual_seed(6)
+    stem = StemWeights.random(n_mels, d, 1500, g)
+    mel = torch.randn(t_in, n_mels, generator=g)
+    enc = EncoderGpu(layers, heads, chunk=8)
+    with pytest.raises(RuntimeError):
+        enc.forward_from_mel(mel)
+    enc.attach_stem(stem, n_mels, 1500)
+    assert enc.has_stem()
+    got, rows = enc.forward_from_mel(mel, t_in)
+    assert rows == stem_out_rows(t_in) == 151 and got.shape == (151, d)
+    x0 = reference_stem(stem, mel.to("cuda", torch.float32))
+    want = reference_forward(layers, x0, heads).cpu()
+    err = (got - want).abs().max() / want.abs().max()
+    assert err < 4e-2, float(err)
+    again, _ = enc.forward_from_mel(mel, t_in)
+    assert torch.equal(got, again)
+    with pytest.raises(ValueError):
+        enc.forward_from_mel(torch.randn(4000, n_mels))          # more rows than positional embeddings
