@@ -50,6 +50,11 @@ typedef struct FtkGemmDesc {
   void* workspace;       // NULL disables split-K
   long long workspace_bytes;
   int split_k;           // 0 = heuristic, 1 = off, >1 = forced
+  // Stream for the split-K reduction kernel (NULL = the GEMM's stream).  With another stream the
+  // launcher orders the reduction behind the GEMM through an event and the caller joins that
+  // stream before it reads D or reuses the workspace; the next kernel on the GEMM's stream then
+  // overlaps the reduction.
+  void* reduce_stream;
 } FtkGemmDesc;
 
 int* ftk_status_word(void);               // device pointer (allocated on first use, per device)

@@ -312,8 +312,22 @@ extern "C" int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream_v) {
   const long long total4 = ((long long)g->M * g->N) >> 2;
   long long blocks = (total4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(a.ws, g->D, g->M, g->N, g->ldd, splits,
-                                                            g->out_fp32, g->accumulate);
+  cudaStream_t rs = g->reduce_stream ? reinterpret_cast<cudaStream_t>(g->reduce_stream) : stream;
+  if (rs != stream) {
+    // reduction on its own stream, ordered behind the GEMM (one event per device, re-recorded per call)
+    static cudaEvent_t ev[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!ev[dev]) {
+      cudaError_t e = cudaEventCreateWithFlags(&ev[dev], cudaEventDisableTiming);
+      if (e != cudaSuccess) return (int)e;
+    }
+    cudaError_t e = cudaEventRecord(ev[dev], stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(rs, ev[dev], 0);
+    if (e != cudaSuccess) return (int)e;
+  }
+  splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, rs>>>(a.ws, g->D, g->M, g->N, g->ldd, splits,
+                                                         g->out_fp32, g->accumulate);
   return (int)cudaGetLastError();
 }
 

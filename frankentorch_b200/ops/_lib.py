@@ -31,6 +31,7 @@ class FtkGemmDesc(C.Structure):
         ("alpha", C.c_float), ("epi", C.c_int), ("out_fp32", C.c_int), ("accumulate", C.c_int),
         ("force_bn", C.c_int), ("max_ctas", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_longlong), ("split_k", C.c_int),
+        ("reduce_stream", C.c_void_p),
     ]
 
 
@@ -97,6 +98,8 @@ def load(build_if_missing: bool = True):
     lib.ftk_status_word.restype = C.c_void_p
     lib.ftk_read_status.argtypes = [C.c_int]
     lib.ftk_gemm_bf16.argtypes = [C.POINTER(FtkGemmDesc), C.c_void_p]
+    lib.ftk_gemm_plan.argtypes = [C.POINTER(FtkGemmDesc), C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    lib.ftk_gemm_plan.restype = C.c_int
     lib.ftk_gemm_comm_bf16.argtypes = [C.POINTER(FtkGemmDesc), C.POINTER(FtkCommDesc), C.c_void_p]
     lib.ftk_tick_i32.argtypes = [C.c_void_p, C.c_void_p]
     lib.ftk_attn_fwd.argtypes = [C.POINTER(FtkAttnDesc), C.c_void_p]

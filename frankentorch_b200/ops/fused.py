@@ -11,6 +11,7 @@ buffer already holds a contribution), so no temporary dW tensor is materialised.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -21,25 +22,92 @@ from . import kernels as K
 RULE_LINEAR = "d(A@B)/dA=dOut@B^T; d(A@B)/dB=A^T@dOut"
 
 
-def _wgrad_into(targets, idx, dy2d, x2d):
+class SideWork:
+    """Small memory-bound kernels of a backward rule (bias column sums, split-K reductions) run on a
+    second stream next to the rule's GEMMs and are joined before the rule returns.
+
+    Entering makes the side stream wait for everything the main stream holds (the incoming gradient
+    is complete); leaving makes the main stream wait for the side stream, and only then tells the
+    tape's observer which parameter gradients were written (a data-parallel bucket must not start
+    before the split-K reduction that finishes its last gradient).  Nothing about the arithmetic
+    changes: the same kernels see the same data.  Works eagerly and under CUDA-graph capture (the
+    fork and the join are captured as parallel branches).  ``FT_SIDE_STREAM=0`` keeps everything on
+    one stream."""
+
+    _streams = {}
+    enabled = os.environ.get("FT_SIDE_STREAM", "1") != "0"
+
+    def __init__(self, tape: TensorTape, device: torch.device):
+        self.tape, self.device = tape, device
+        self.on = SideWork.enabled and device.type == "cuda"
+        self._marks = []
+        self._saved_fn = None
+
+    @classmethod
+    def stream_for(cls, device: torch.device) -> torch.cuda.Stream:
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        if key not in cls._streams:
+            cls._streams[key] = torch.cuda.Stream(device=device)
+        return cls._streams[key]
+
+    def __enter__(self):
+        if self.on:
+            self.main = torch.cuda.current_stream(self.device)
+            self.side = SideWork.stream_for(self.device)
+            ev = torch.cuda.Event()
+            ev.record(self.main)
+            self.side.wait_event(ev)
+            self._saved_fn = self.tape.leaf_grad_written_fn
+            if self._saved_fn is not None:
+                self.tape.leaf_grad_written_fn = self._marks.append      # held back until the join
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+            self.main.wait_event(ev)
+            K.workspace_idle(self.device)
+            self.tape.leaf_grad_written_fn = self._saved_fn
+            if self._saved_fn is not None and exc[0] is None:
+                for nid in self._marks:
+                    self._saved_fn(nid)
+        return False
+
+    def wgrad(self, dy2d, x2d, out=None, accumulate=False):
+        """Weight gradient GEMM on the main stream; its split-K reduction (if any) on the side stream."""
+        if not self.on:
+            return K.linear_wgrad(dy2d, x2d, out=out, accumulate=accumulate)
+        return K.linear_wgrad(dy2d, x2d, out=out, accumulate=accumulate, reduce_stream=self.side.cuda_stream)
+
+    def colsum(self, dy2d, out=None, accumulate=False):
+        if not self.on:
+            return K.colsum(dy2d, out=out, accumulate=accumulate)
+        with torch.cuda.stream(self.side):
+            return K.colsum(dy2d, out=out, accumulate=accumulate)
+
+
+def _wgrad_into(targets, idx, dy2d, x2d, side: Optional["SideWork"] = None):
     """dW (+)= dy^T x, written into the bound gradient buffer when there is one."""
+    run = side.wgrad if side is not None else K.linear_wgrad
     tgt = targets.leaf_target(idx)
     if tgt is not None:
         buf, filled = tgt
-        K.linear_wgrad(dy2d, x2d, out=buf, accumulate=filled)
+        run(dy2d, x2d, out=buf, accumulate=filled)
         targets.mark_accumulated(idx)
         return ACCUMULATED
-    return K.linear_wgrad(dy2d, x2d)
+    return run(dy2d, x2d)
 
 
-def _bgrad_into(targets, idx, dy2d):
+def _bgrad_into(targets, idx, dy2d, side: Optional["SideWork"] = None):
+    run = side.colsum if side is not None else K.colsum
     tgt = targets.leaf_target(idx)
     if tgt is not None:
         buf, filled = tgt
-        K.colsum(dy2d, out=buf, accumulate=filled)
+        run(dy2d, out=buf, accumulate=filled)
         targets.mark_accumulated(idx)
         return ACCUMULATED
-    return K.colsum(dy2d)
+    return run(dy2d)
 
 
 def linear(tape: TensorTape, x: int, w: int, b: Optional[int] = None, *, act: Optional[str] = None,
@@ -71,11 +139,14 @@ def linear(tape: TensorTape, x: int, w: int, b: Optional[int] = None, *, act: Op
             g2 = K.gelu_bwd(aux, g2, tanh_form=(act == "gelu_tanh")) if act != "relu" else \
                 (g2 * (aux > 0)).to(torch.bfloat16)
         out = []
-        dx = K.linear_dgrad(g2, wv).reshape(xv.shape) if x_needs else None
+        with SideWork(tape, g2.device) as side:
+            db = _bgrad_into(targets, 2, g2, side) if has_b else None      # column sums next to the GEMMs
+            dw = _wgrad_into(targets, 1, g2, x2, side)
+            dx = K.linear_dgrad(g2, wv).reshape(xv.shape) if x_needs else None
         out.append(dx)
-        out.append(_wgrad_into(targets, 1, g2, x2))
+        out.append(dw)
         if has_b:
-            out.append(_bgrad_into(targets, 2, g2))
+            out.append(db)
         if has_r:
             out.append(gy)
         return out
@@ -102,12 +173,18 @@ def mlp_up_down(tape: TensorTape, x: int, w1: int, b1: int, w2: int, b2: int, re
 
     def vjp(gy, targets):
         g2 = gy.reshape(-1, gy.shape[-1])
-        dw2 = _wgrad_into(targets, 3, g2, h)
-        db2 = _bgrad_into(targets, 4, g2)
-        du = K.linear_dgrad(g2, w2v, epi=depi, resid=u)      # (dY @ w2) * act'(U)
-        dw1 = _wgrad_into(targets, 1, du, x2)
-        db1 = _bgrad_into(targets, 2, du)
-        dx = K.linear_dgrad(du, w1v).reshape(xv.shape)
+        with SideWork(tape, g2.device) as side:
+            db2 = _bgrad_into(targets, 4, g2, side)
+            dw2 = _wgrad_into(targets, 3, g2, h, side)
+            du = K.linear_dgrad(g2, w2v, epi=depi, resid=u)      # (dY @ w2) * act'(U)
+            # du is produced on the main stream: the side stream must see it before it sums its columns
+            if side.on:
+                ev = torch.cuda.Event()
+                ev.record(side.main)
+                side.side.wait_event(ev)
+            db1 = _bgrad_into(targets, 2, du, side)
+            dw1 = _wgrad_into(targets, 1, du, x2, side)
+            dx = K.linear_dgrad(du, w1v).reshape(xv.shape)
         return [dx, dw1, db1, dw2, db2, gy]
 
     return tape.record("mlp", [x, w1, b1, w2, b2, resid], y, vjp,
@@ -231,8 +308,9 @@ def lm_head_cross_entropy(tape: TensorTape, x: int, w: int, targets_ids: torch.T
         dl = dlogits
         if not (g.numel() == 1 and g.dtype == torch.float32 and getattr(g, "_ft_unit_seed", False)):
             dl = (dlogits.float() * g.reshape(()).float()).to(torch.bfloat16)
-        dw = _wgrad_into(targets, 1, dl, x2)
-        dx = K.linear_dgrad(dl, wv).reshape(xv.shape)
+        with SideWork(tape, dl.device) as side:
+            dw = _wgrad_into(targets, 1, dl, x2, side)
+            dx = K.linear_dgrad(dl, wv).reshape(xv.shape)
         return [dx, dw]
 
     return tape.record("lm_head_ce", [x, w], loss.reshape(()), vjp,

@@ -76,11 +76,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          bias: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
          aux: Optional[torch.Tensor] = None, epi: int = EPI_NONE, alpha: float = 1.0,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-         accumulate: bool = False, force_bn: int = 0, max_ctas: int = 0, split_k: int = 0) -> torch.Tensor:
+         accumulate: bool = False, force_bn: int = 0, max_ctas: int = 0, split_k: int = 0,
+         reduce_stream: Optional[int] = None) -> torch.Tensor:
     """``D = epi(alpha * A @ B^T + bias) (+ resid) (+ D)`` on the tcgen05 GEMM.
 
     ``a`` is ``[M, K]`` (``a_mn=False``) or ``[K, M]`` (``a_mn=True``); ``b`` is
     ``[N, K]`` or ``[K, N]`` likewise.  Both must be bf16 with unit inner stride.
+    ``reduce_stream`` (a raw stream handle) moves a split-K reduction off the launching stream;
+    the caller joins that stream before reading the output or launching the next split-K GEMM.
     """
     _bf16(a, "a"), _bf16(b, "b")
     if a.dim() != 2 or b.dim() != 2 or a.stride(1) != 1 or b.stride(1) != 1:
@@ -114,15 +117,42 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         raise KernelError("gemm output must be bf16 or fp32")
     g.accumulate, g.force_bn, g.max_ctas = int(accumulate), int(force_bn), int(max_ctas)
     g.split_k = int(split_k)
+    g.reduce_stream = reduce_stream
+    lib = _lib.load()
+    dev_key = a.device.index if a.device.index is not None else torch.cuda.current_device()
     if split_k != 1 and bias is None and resid is None and aux is None and epi == EPI_NONE:
         ws = _gemm_workspace(a.device)
         g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel() * 4
-    _chk(_lib.load().ftk_gemm_bf16(C.byref(g), _stream()), "ftk_gemm_bf16")
+        busy = _WS_BUSY.get(dev_key)
+        if busy is not None or reduce_stream is not None:
+            bn, sp = C.c_int(0), C.c_int(1)
+            lib.ftk_gemm_plan(C.byref(g), C.byref(bn), C.byref(sp))
+            if sp.value > 1:
+                if busy is not None:
+                    # a reduction on another stream still reads the split-K workspace this GEMM will write
+                    torch.cuda.current_stream(a.device).wait_event(busy)
+                    _WS_BUSY.pop(dev_key, None)
+            else:
+                g.reduce_stream = reduce_stream = None
+    _chk(lib.ftk_gemm_bf16(C.byref(g), _stream()), "ftk_gemm_bf16")
+    if reduce_stream is not None and g.workspace:
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.ExternalStream(reduce_stream, device=a.device))
+        _WS_BUSY[dev_key] = ev
     return out
 
 
 _WORKSPACES = {}
 GEMM_WORKSPACE_BYTES = 64 << 20
+# per device: event recorded behind a split-K reduction that runs on a stream other than its GEMM's;
+# the next split-K GEMM waits for it, and whoever joins that stream calls workspace_idle()
+_WS_BUSY = {}
+
+
+def workspace_idle(device) -> None:
+    """The caller has joined the stream that ran split-K reductions: the workspace is free again."""
+    key = device.index if getattr(device, "index", None) is not None else torch.cuda.current_device()
+    _WS_BUSY.pop(key, None)
 
 
 def _gemm_workspace(device) -> torch.Tensor:
@@ -164,9 +194,10 @@ def linear_dgrad(dy, w, *, epi=EPI_NONE, resid=None, out=None):
     return gemm(dy, w, b_mn=True, epi=epi, resid=resid, out=out)
 
 
-def linear_wgrad(dy, x, *, out=None, accumulate=False):
+def linear_wgrad(dy, x, *, out=None, accumulate=False, reduce_stream=None):
     """``dw[out, in] (+)= dy^T @ x`` in fp32; both operands are consumed MN-major."""
-    return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=torch.float32, accumulate=accumulate)
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, out_dtype=torch.float32, accumulate=accumulate,
+                reduce_stream=reduce_stream)
 
 
 # --------------------------------------------------------------------------------------- attention

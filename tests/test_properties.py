@@ -396,6 +396,9 @@ def test_dispatch_resolution_strict_is_never_laxer_than_hardened(bits):
 @FAST
 @given(st.sampled_from(list(DType)), st.sampled_from(list(DType)), st.sampled_from(list(DType)))
 def test_dtype_promotion_is_commutative_idempotent_and_monotone(a, b, c):
+    # QInt8 and QUInt8 share a rank and the tie goes to the left operand, in the reference as well
+    # (ft-core/src/lib.rs:135-170): that one pair is order-dependent by construction
+    assume({a, b} != {DType.QInt8, DType.QUInt8})
     try:
         ab = a.promote_types(b)
     except Exception:
