@@ -630,7 +630,7 @@ extern "C" int ftk_rmsnorm_fwd(const void* x, const void* gamma, void* y, float*
 }
 // number of partial blocks the caller must provide room for (2 * blocks * cols floats)
 extern "C" int ftk_layernorm_bwd_blocks(int rows) { return (rows + LNB_ROWS - 1) / LNB_ROWS; }
-extern "C" int ftk_colsum_blocks(int rows) { return (rows + COL_ROWS_PER_BLK - 1) / COL_ROWS_PER_BLK; }
+static int norm_col_blocks(int rows) { return (rows + COL_ROWS_PER_BLK - 1) / COL_ROWS_PER_BLK; }
 
 extern "C" int ftk_layernorm_bwd(const void* dy, const void* x, const void* gamma,
                                  const float* mean, const float* rstd, const void* dx_add, void* dx,
@@ -651,7 +651,7 @@ extern "C" int ftk_layernorm_bwd(const void* dy, const void* x, const void* gamm
   norm_bwd_dx_kernel<false><<<(rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, s>>>(
       BF(dy), BF(x), BF(gamma), mean, rstd, BF(dx_add), BFW(dx), rows, cols);
   if (dgamma) {
-    const int nblk = ftk_colsum_blocks(rows);
+    const int nblk = norm_col_blocks(rows);
     dim3 g((cols / 2 + 31) / 32, nblk);
     col_partial_kernel<0><<<g, 256, 0, s>>>(BF(dy), BF(x), mean, rstd, partial, rows, cols, cols, nblk);
     col_final_kernel<<<(cols + 127) / 128, 128, 0, s>>>(partial, dgamma, partial + (size_t)nblk * cols,
@@ -667,7 +667,7 @@ extern "C" int ftk_rmsnorm_bwd(const void* dy, const void* x, const void* gamma,
   norm_bwd_dx_kernel<true><<<(rows + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, s>>>(
       BF(dy), BF(x), BF(gamma), nullptr, rstd, nullptr, BFW(dx), rows, cols);
   if (dgamma) {
-    const int nblk = ftk_colsum_blocks(rows);
+    const int nblk = norm_col_blocks(rows);
     dim3 g((cols / 2 + 31) / 32, nblk);
     col_partial_kernel<1><<<g, 256, 0, s>>>(BF(dy), BF(x), nullptr, rstd, partial, rows, cols, cols, nblk);
     col_final_wide_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, dgamma, nullptr, nullptr, cols, nblk,
@@ -675,13 +675,81 @@ extern "C" int ftk_rmsnorm_bwd(const void* dy, const void* x, const void* gamma,
   }
   return (int)cudaGetLastError();
 }
+// Plain column sums with 16-byte loads: a CTA covers 256 columns x CSW_ROWS rows as 8 row groups of
+// 32 lanes x 8 columns.  Each thread adds its rows (r0 + group, + 8, ...) in ascending order with four
+// row loads in flight, then group 0 adds the 8 group sums in group order: a fixed tree again.
+constexpr int CSW_ROWS = 64;
+__global__ void __launch_bounds__(256)
+colsum_wide_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ partial, int rows, int cols,
+                   long long ld) {
+  __shared__ float sm[COL_GROUPS][32][9];
+  const int lane = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * 8;
+  const int blk = blockIdx.y;
+  const int r0 = blk * CSW_ROWS;
+  const int r1 = min(rows, r0 + CSW_ROWS);
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (c < cols) {
+    int r = r0 + rg;
+    for (; r + 3 * COL_GROUPS < r1; r += 4 * COL_GROUPS) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        v[u] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(r + u * COL_GROUPS) * ld + c));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 f0 = unpack_bf16(v[u].x), f1 = unpack_bf16(v[u].y), f2 = unpack_bf16(v[u].z),
+                     f3 = unpack_bf16(v[u].w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+    }
+    for (; r < r1; r += COL_GROUPS) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4*>(x + (size_t)r * ld + c));
+      const float2 f0 = unpack_bf16(w.x), f1 = unpack_bf16(w.y), f2 = unpack_bf16(w.z), f3 = unpack_bf16(w.w);
+      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+      acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sm[rg][lane][i] = acc[i];
+  __syncthreads();
+  if (rg == 0 && c < cols) {
+    float t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = 0.f;
+#pragma unroll
+    for (int k = 0; k < COL_GROUPS; ++k)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) t[i] += sm[k][lane][i];
+    float* dst = partial + (size_t)blk * cols + c;
+    reinterpret_cast<float4*>(dst)[0] = make_float4(t[0], t[1], t[2], t[3]);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(t[4], t[5], t[6], t[7]);
+  }
+}
+
+// Number of row blocks (= rows of the partial buffer the caller provides) for `rows` input rows.
+extern "C" int ftk_colsum_blocks(int rows) { return (rows + CSW_ROWS - 1) / CSW_ROWS; }
+
 extern "C" int ftk_colsum_bf16(const void* x, float* out, float* partial, int rows, int cols,
                                long long ld, int accumulate, void* stream) {
   if (cols % 2 || ld % 2 || rows <= 0) return -2;
   cudaStream_t s = STREAM(stream);
-  const int nblk = ftk_colsum_blocks(rows);
-  dim3 g((cols / 2 + 31) / 32, nblk);
-  col_partial_kernel<2><<<g, 256, 0, s>>>(BF(x), nullptr, nullptr, nullptr, partial, rows, cols, ld, nblk);
+  const bool wide = (cols % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(partial) & 15) == 0);
+  int nblk;
+  if (wide) {
+    nblk = ftk_colsum_blocks(rows);
+    dim3 g((cols / 8 + 31) / 32, nblk);
+    colsum_wide_kernel<<<g, 256, 0, s>>>(BF(x), partial, rows, cols, ld);
+  } else {
+    // odd extents / alignments: two columns per thread; needs fewer row blocks than were provided for
+    nblk = (rows + COL_ROWS_PER_BLK - 1) / COL_ROWS_PER_BLK;
+    dim3 g((cols / 2 + 31) / 32, nblk);
+    col_partial_kernel<2><<<g, 256, 0, s>>>(BF(x), nullptr, nullptr, nullptr, partial, rows, cols, ld, nblk);
+  }
   col_final_wide_kernel<<<(cols + 31) / 32, 256, 0, s>>>(partial, out, nullptr, nullptr, cols, nblk, accumulate);
   return (int)cudaGetLastError();
 }

@@ -123,6 +123,18 @@ def test_elementwise_and_colsum(cuda_device):
     m = _bf(torch.randn(300, 770), cuda_device)
     cs = k.colsum(m)
     assert (cs - m.float().sum(0)).abs().max().item() < 1e-2
+    # wide path (16-byte loads): ragged row counts, a strided view, accumulate mode, run-twice identity;
+    # narrow path: an extent that is not a multiple of 8
+    for rows, cols, ld in ((8192, 768, 768), (1000, 3072, 3072), (257, 264, 512), (33, 10, 16), (5, 8, 8)):
+        base = (torch.randn(rows, ld) * 2).to(torch.bfloat16).to(cuda_device)
+        v = base[:, :cols]
+        want = v.float().sum(0)
+        got = k.colsum(v)
+        assert (got - want).abs().max().item() < 2e-2 * max(1.0, rows / 1000), (rows, cols)
+        assert torch.equal(got, k.colsum(v))
+        acc = got.clone()
+        k.colsum(v, out=acc, accumulate=True)
+        assert torch.allclose(acc, 2 * got)
     # dropout: replayable, right keep rate, right scale
     big = _bf(torch.ones(1 << 16), cuda_device)
     d1, d2 = k.dropout(big, 0.25, seed=7, offset=3), k.dropout(big, 0.25, seed=7, offset=3)
