@@ -428,6 +428,9 @@ def main():
     }
     if exposed_ms is not None:
         out["exposed_comm_ms_per_step"] = exposed_ms
+        parts = getattr(dp, "exposed_parts_ms", None)
+        if parts:
+            out["exposed_comm_parts_ms"] = {"before_first_parameters": parts[0], "after_backward": parts[1]}
     if mgc is not None:
         out["multi_gpu_check"] = mgc
     if e2e_ms is not None:

@@ -4,6 +4,7 @@
     python benchmarks/kernel_bench.py gemm --m 8192 --n 2304 --k 768 [--mode fwd|dgrad|wgrad]
     python benchmarks/kernel_bench.py attn --b 8 --s 1024 --h 12 --hd 64 [--bwd]
     python benchmarks/kernel_bench.py sweep            # the shapes of the five training configs
+    python benchmarks/kernel_bench.py rows --case all  # row / elementwise / optimizer / comm kernels (world = 1)
 
 Each line reports the achieved TFLOP/s (or GB/s) and the fraction of the measured peak read from
 MEASURED_PEAKS.json at the repository root (fallback 1590 TFLOP/s, 6650 GB/s), next to the same
@@ -112,9 +113,144 @@ def bench_attn(B, S, H, hd, bwd, iters, warm, ref=True):
     ops.check_status()
 
 
+class Clocks:
+    """SM clock and throttle reasons sampled with NVML while the cases run (read-only queries)."""
+
+    def __init__(self):
+        self.rows, self.stop_flag, self.thread = [], None, None
+
+    def __enter__(self):
+        try:
+            import threading
+
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+            reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+            self.mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self.stop_flag = threading.Event()
+
+            def loop():
+                while not self.stop_flag.is_set():
+                    try:
+                        self.rows.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), int(reasons(h))))
+                    except Exception:
+                        pass
+                    self.stop_flag.wait(0.02)
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.thread = None
+        return self
+
+    def __exit__(self, *exc):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            if self.rows:
+                import statistics
+                bits = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                        0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+                seen = 0
+                for _, r in self.rows:
+                    seen |= r
+                out = {"sm_mhz": statistics.median(r[0] for r in self.rows), "sm_max_mhz": self.mx,
+                       "reasons": sorted(n for b, n in bits.items() if seen & b), "samples": len(self.rows)}
+        print(json.dumps({"clocks": out}), flush=True)
+        return False
+
+
+def _row_cases(rows, cols):
+    """name -> (callable, algorithmic bytes moved per call).  Inputs exceed L2 only for the big cases; the
+    timing loop flushes L2 between iterations either way."""
+    f32 = lambda *sh: torch.randn(*sh, device="cuda")
+    x, dy = bf(rows, cols, scale=1.0), bf(rows, cols, scale=1.0)
+    g, b = bf(cols, scale=1.0), bf(cols)
+    n = rows * cols
+    y, mean, rstd, _ = ops.layernorm_fwd(x, g, b)
+    yr, rr = ops.rmsnorm_fwd(x, g)
+    sm = ops.softmax_rows(x)
+    V, d, T = 50304, cols, rows
+    ids = torch.randint(0, 50257, (T,), device="cuda")
+    wte, wpe = bf(V, d), bf(1024, d)
+    dwte, dwpe = torch.zeros(V, d, device="cuda"), torch.zeros(1024, d, device="cuda")
+    N = 32 << 20
+    master, gr, m, v = f32(N), f32(N), torch.zeros(N, device="cuda"), torch.zeros(N, device="cuda")
+    shadow = torch.empty(N, dtype=torch.bfloat16, device="cuda")
+    hyper = torch.tensor([1e-3, 0.1, 0.001, 1.0], device="cuda")
+    ss, nrm = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    xf = f32(rows, cols)
+    cases = {
+        "layernorm_fwd": (lambda: ops.layernorm_fwd(x, g, b), 4 * n),
+        "layernorm_bwd": (lambda: ops.layernorm_bwd(dy, x, g, mean, rstd, dx_add=dy), 8 * n),
+        "rmsnorm_fwd": (lambda: ops.rmsnorm_fwd(x, g), 4 * n),
+        "rmsnorm_bwd": (lambda: ops.rmsnorm_bwd(dy, x, g, rr), 6 * n + 4 * n),
+        "softmax_rows": (lambda: ops.softmax_rows(x), 4 * n),
+        "softmax_bwd": (lambda: ops.softmax_bwd(sm, dy), 6 * n),
+        "gelu_fwd": (lambda: ops.gelu_fwd(x), 4 * n),
+        "gelu_bwd": (lambda: ops.gelu_bwd(x, dy), 6 * n),
+        "add": (lambda: ops.add(x, dy), 6 * n),
+        "dropout": (lambda: ops.dropout(x, 0.1, 7), 4 * n),
+        "cast_f32_bf16": (lambda: ops.cast_f32_to_bf16(xf), 6 * n),
+        "colsum": (lambda: ops.colsum(dy), 2 * n),
+        "embedding_fwd": (lambda: ops.embedding_fwd(ids, wte, wpe, 1024), 4 * T * d + 2 * T * d),
+        "embedding_bwd": (lambda: ops.embedding_bwd(ids, dy, dwte, dwpe, 1024), 2 * T * d + 8 * T * d),
+        "adamw_dev": (lambda: ops.adamw_dev(master, shadow, gr, m, v, hyper, beta1=0.9, beta2=0.999, eps=1e-8,
+                                            weight_decay=0.01), 30 * N),
+        "sumsq": (lambda: ops.sumsq(gr, out=ss), 4 * N),
+        "clip_scale": (lambda: ops.clip_scale(ss, 1.0, hyper, nrm), 16),
+    }
+    return cases
+
+
+def bench_rows(case, rows, cols, iters, warm):
+    pk = peaks()
+    cases = _row_cases(rows, cols)
+    names = list(cases) if case == "all" else [case]
+    for name in names:
+        fn, nbytes = cases[name]
+        t = timeit(fn, iters, warm)
+        gbs = nbytes / t / 1e6
+        print(f"{name:14s} rows {rows} cols {cols}: {t*1e3:8.1f} us {gbs:8.1f} GB/s "
+              f"({gbs / pk['hbm_gbs']:.2f} of {pk['src']} copy bandwidth)", flush=True)
+    ops.check_status()
+
+
+def bench_dp_world1(n_params, iters, warm):
+    """The bucketed data-parallel kernels with this GPU as the only rank (push, reduce, norm, update)."""
+    import types
+
+    from frankentorch_b200.models.gpt import ParamArena
+    from frankentorch_b200.parallel.data_parallel import FusedDataParallel
+    pk = peaks()
+    arena = ParamArena([("w", (n_params,))], torch.device("cuda"), peer_visible=True)
+    arena.master.normal_()
+    arena.grads.normal_()
+    dp = FusedDataParallel(arena, None, torch.device("cuda"), bucket_elems=n_params // 4, overlap=False,
+                           defer_update=False)
+    opt = types.SimpleNamespace(beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, grad_clip=1.0)
+    hyper = torch.tensor([1e-3, 0.1, 0.001, 1.0], device="cuda")
+    nrm, ss = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+
+    def step():
+        dp.begin_step()
+        dp.reduce_and_update(arena, hyper, opt, ss, nrm, None)
+    t = timeit(step, iters, warm)
+    nbytes = n_params * (4 + 2 + 2 + 4 + 4 + 24 + 2)       # push r/w, reduce r/w, update r/w master+m+v, params
+    print(f"dp_world1 {n_params} params: {t*1e3:8.1f} us {nbytes / t / 1e6:8.1f} GB/s "
+          f"({nbytes / t / 1e6 / pk['hbm_gbs']:.2f} of {pk['src']} copy bandwidth)", flush=True)
+    ops.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "sweep"])
+    ap.add_argument("what", choices=["gemm", "attn", "sweep", "rows", "dp"])
+    ap.add_argument("--case", default="all")
+    ap.add_argument("--rows", type=int, default=8192)
+    ap.add_argument("--cols", type=int, default=768)
+    ap.add_argument("--params", type=int, default=32 << 20)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=2304)
     ap.add_argument("--k", type=int, default=768)
@@ -129,10 +265,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-ref", action="store_true")
     a = ap.parse_args()
+    with Clocks():
+        _dispatch(a)
+
+
+def _dispatch(a):
     if a.what == "gemm":
         bench_gemm(a.m, a.n, a.k, a.mode, a.iters, a.warmup, not a.no_ref, a.force_bn)
     elif a.what == "attn":
         bench_attn(a.b, a.s, a.h, a.hd, a.bwd, a.iters, a.warmup, not a.no_ref)
+    elif a.what == "rows":
+        bench_rows(a.case, a.rows, a.cols, a.iters, a.warmup)
+    elif a.what == "dp":
+        bench_dp_world1(a.params, a.iters, a.warmup)
     else:
         for (N, Kd) in [(2304, 768), (768, 768), (3072, 768), (768, 3072), (50304, 768),
                         (3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (8192, 8192)]:

@@ -238,11 +238,14 @@ __global__ void __launch_bounds__(32)
 dp_norm_kernel(DpPeers P, const float* __restrict__ partial_sumsq, int n_partial, float max_norm,
                float* __restrict__ hyper, float* __restrict__ norm_out,
                const long long* __restrict__ seq_ptr, int* ok_word, int* status, int* pending,
-               float* __restrict__ hyper_pending) {
+               float* __restrict__ hyper_pending, const float* __restrict__ extra_sumsq) {
   const unsigned long long seq = (unsigned long long)*seq_ptr;
   float s = 0.f;
   if (threadIdx.x == 0) {
     for (int i = 0; i < n_partial; ++i) s += partial_sumsq[i];   // index order
+    // squared norm of this rank's own (not replicated) gradients, e.g. tensor-parallel shards or
+    // local experts: the global norm covers every parameter of the job, wherever it lives
+    if (extra_sumsq) s += *extra_sumsq;
     if (*ok_word == 0) s = DP_POISON;
   }
   s = __shfl_sync(0xffffffffu, s, 0);
@@ -427,7 +430,8 @@ extern "C" int ftk_dp_bucket_reduce(const FtkDpComm* c, int b, const float* grad
   return (int)cudaPeekAtLastError();
 }
 
-extern "C" int ftk_dp_norm(const FtkDpComm* c, float max_norm, float* hyper, float* norm_out, void* stream) {
+extern "C" int ftk_dp_norm(const FtkDpComm* c, float max_norm, float* hyper, float* norm_out,
+                           const float* extra_sumsq, void* stream) {
   DpPeers P;
   int rc = fill_peers(c, &P);
   if (rc) return rc;
@@ -436,7 +440,7 @@ extern "C" int ftk_dp_norm(const FtkDpComm* c, float max_norm, float* hyper, flo
   if (!c->pending || !c->hyper_pending) return -2;
   dp_norm_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       P, c->partial, c->n_buckets * c->n_ctas, max_norm, hyper, norm_out, c->seq, c->ok_word, status, c->pending,
-      c->hyper_pending);
+      c->hyper_pending, extra_sumsq);
   return (int)cudaPeekAtLastError();
 }
 

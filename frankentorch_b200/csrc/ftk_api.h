@@ -292,7 +292,10 @@ typedef struct {
 } FtkDpComm;
 int ftk_dp_begin_step(const FtkDpComm* c, void* stream);
 int ftk_dp_bucket_reduce(const FtkDpComm* c, int bucket, const float* grads, int n_ctas, void* stream);
-int ftk_dp_norm(const FtkDpComm* c, float max_norm, float* hyper, float* norm_out, void* stream);
+// extra_sumsq (device, may be NULL): squared norm of gradients only this rank holds; it is added to
+// the rank's share before the exchange, so the clip factor comes from the norm of ALL gradients.
+int ftk_dp_norm(const FtkDpComm* c, float max_norm, float* hyper, float* norm_out, const float* extra_sumsq,
+                void* stream);
 int ftk_dp_update(const FtkDpComm* c, int b0, int b1, float* master, float* m, float* v,
                   float beta1, float beta2, float eps, float weight_decay, int n_ctas, void* stream);
 int ftk_dp_clear_pending(const FtkDpComm* c, void* stream);

@@ -39,7 +39,8 @@ DP_MAX_BUCKETS = 64
 DEFAULT_BUCKET_ELEMS = 16 * 1024 * 1024      # ~32 MB of bf16 on the wire per bucket
 REDUCE_CTAS = 48                             # CTAs of a bucket's push / reduce kernels under the backward pass
 TAIL_CTAS = 592                              # ... and of the buckets that finish with the backward pass
-UPDATE_CTAS = 296                            # CTAs of the AdamW + all-gather kernel
+UPDATE_CTAS = 296                            # CTAs of the AdamW + all-gather kernel when nothing else runs
+UPDATE_OVERLAP_CTAS = 64                     # ... and of the per-bucket updates that run under the forward pass
 
 
 def shard_multiple(world: int) -> int:
@@ -143,7 +144,7 @@ def _bind(lib):
     pc, vp, i, f = C.POINTER(_Comm), C.c_void_p, C.c_int, C.c_float
     lib.ftk_dp_begin_step.argtypes = [pc, vp]
     lib.ftk_dp_bucket_reduce.argtypes = [pc, i, vp, i, vp]
-    lib.ftk_dp_norm.argtypes = [pc, f, vp, vp, vp]
+    lib.ftk_dp_norm.argtypes = [pc, f, vp, vp, vp, vp]
     lib.ftk_dp_update.argtypes = [pc, i, i, vp, vp, vp, f, f, f, f, i, vp]
     lib.ftk_dp_clear_pending.argtypes = [pc, vp]
     lib.ftk_dp_wait_params.argtypes = [pc, i, vp]
@@ -206,6 +207,7 @@ class FusedDataParallel:
         # grids: narrow while the backward pass needs the SMs, wide for buckets that finish last
         self.ctas_overlap = int(os.environ.get("FT_DP_CTAS", REDUCE_CTAS))
         self.ctas_tail = max(self.ctas_overlap, int(os.environ.get("FT_DP_TAIL_CTAS", TAIL_CTAS)))
+        self.ctas_update_overlap = int(os.environ.get("FT_DP_UPDATE_CTAS", UPDATE_OVERLAP_CTAS))
         nb = len(self.buckets)
         # peer-visible: inbox, flag block, sumsq slots
         wsize = 2 if wire == "bf16" else 4
@@ -326,8 +328,10 @@ class FusedDataParallel:
         nb = len(self.buckets)
         spans = [(b, b + 1) for b in range(nb)] if per_bucket else [(0, nb)]
         for lo, hi in spans:
+            # the first bucket gates the forward pass and gets the whole GPU; the others run under it
+            ctas = UPDATE_CTAS if (lo == 0 or not per_bucket) else self.ctas_update_overlap
             K._chk(self._lib.ftk_dp_update(c, lo, hi, self.master.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
-                                           b1, b2, eps, wd, UPDATE_CTAS, cs), "ftk_dp_update")
+                                           b1, b2, eps, wd, ctas, cs), "ftk_dp_update")
             if per_bucket:
                 e = torch.cuda.Event()
                 e.record(self.comm_stream)
@@ -373,7 +377,9 @@ class FusedDataParallel:
         self._launched[b] = True
         self.launch_order.append(b)
 
-    def reduce_and_update(self, arena, hyper, opt, sumsq, grad_norm, step_dev) -> None:
+    def reduce_and_update(self, arena, hyper, opt, sumsq, grad_norm, step_dev, extra_sumsq=None) -> None:
+        """``extra_sumsq``: device scalar with the squared norm of the gradients that only this rank
+        holds (rank-local arenas); it enters the global norm that sets the clip factor."""
         nb = len(self.buckets)
         if self._expected is None and self._writes_seen:
             self._expected = [self._writes_seen.get(b, 0) for b in range(nb)]
@@ -388,8 +394,13 @@ class FusedDataParallel:
             if not self._launched[b]:
                 self._launch_bucket(b)
         cs, c = self.comm_stream.cuda_stream, C.byref(self._comm)
-        K._chk(self._lib.ftk_dp_norm(c, float(opt.grad_clip or 0.0), hyper.data_ptr(), grad_norm.data_ptr(), cs),
-               "ftk_dp_norm")
+        if extra_sumsq is not None:                 # computed on the main stream just before this call
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self.comm_stream.wait_event(ev)
+            self._events.append(ev)
+        K._chk(self._lib.ftk_dp_norm(c, float(opt.grad_clip or 0.0), hyper.data_ptr(), grad_norm.data_ptr(),
+                                     None if extra_sumsq is None else extra_sumsq.data_ptr(), cs), "ftk_dp_norm")
         main = torch.cuda.current_stream()
         if self.record_stamps:
             if not self._stamped_first_gate:
@@ -411,6 +422,7 @@ class FusedDataParallel:
         if not self.record_stamps:
             return None
         t = [int(x) for x in self.stamps.tolist()]
+        self.exposed_parts_ms = ((t[1] - t[0]) / 1e6, (t[3] - t[2]) / 1e6)    # (start of step, end of step)
         return ((t[1] - t[0]) + (t[3] - t[2])) / 1e6
 
     def flush(self) -> None:
@@ -468,11 +480,16 @@ class NcclDataParallel:
         self.world = dist.get_world_size(group) if group is not None else 1
         self.arena = arena
 
-    def reduce_and_update(self, arena, hyper, opt, sumsq, grad_norm, step_dev) -> None:
+    def reduce_and_update(self, arena, hyper, opt, sumsq, grad_norm, step_dev, extra_sumsq=None) -> None:
         if self.world > 1:
             dist.all_reduce(arena.grads, op=dist.ReduceOp.AVG, group=self.group)
         if opt.grad_clip is not None:
             K.sumsq(arena.grads, out=sumsq)
+            if extra_sumsq is not None:            # rank-local gradients: summed over the ranks, then added
+                ex = extra_sumsq.clone()
+                if self.world > 1:
+                    dist.all_reduce(ex, group=self.group)
+                sumsq.add_(ex)
             K.clip_scale(sumsq, opt.grad_clip, hyper, grad_norm)
         K.adamw_dev(arena.master, arena.params, arena.grads, arena.m, arena.v, hyper,
                     beta1=opt.beta1, beta2=opt.beta2, eps=opt.eps, weight_decay=opt.weight_decay)

@@ -59,6 +59,7 @@ class TrainEngine:
         self.local_grad_scale = float(getattr(model, "local_grad_scale", 1.0))
         self.hyper_local = self.hyper.clone()
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.local_sumsq = torch.zeros(1, dtype=torch.float32, device=dev)   # squared norm of rank-local gradients
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         # library collectives (the NCCL baseline path) stay out of graph capture
         self._graph_requested = use_cuda_graph
@@ -89,16 +90,31 @@ class TrainEngine:
     def _optimizer(self) -> None:
         o, a = self.opt, self.model.arena
         K.adamw_tick(self.step_dev, self.hyper, o.beta1, o.beta2)
+        # The clip factor comes from the norm of every gradient of the job: the replicated arena's
+        # (reduced over the ranks) and the rank-local arenas' (tensor-parallel / ZeRO-3 shards, local
+        # experts), the latter with the model's gradient scale, summed over the ranks.
+        extra = None
+        if self.local_arenas and o.grad_clip is not None:
+            for i, la in enumerate(self.local_arenas):
+                K.sumsq(la.grads, out=self.local_sumsq, accumulate=i > 0)
+            if self.local_grad_scale != 1.0:
+                self.local_sumsq.mul_(self.local_grad_scale ** 2)
+            extra = self.local_sumsq
         if self.dp is not None:
-            self.dp.reduce_and_update(a, self.hyper, o, self.sumsq, self.grad_norm, self.step_dev)
+            if extra is not None:
+                self.dp.reduce_and_update(a, self.hyper, o, self.sumsq, self.grad_norm, self.step_dev,
+                                          extra_sumsq=extra)
+            else:
+                self.dp.reduce_and_update(a, self.hyper, o, self.sumsq, self.grad_norm, self.step_dev)
         else:
             if o.grad_clip is not None:
                 K.sumsq(a.grads, out=self.sumsq)
+                if extra is not None:
+                    self.sumsq.add_(extra)
                 K.clip_scale(self.sumsq, o.grad_clip, self.hyper, self.grad_norm)
             K.adamw_dev(a.master, a.params, a.grads, a.m, a.v, self.hyper,
                         beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay)
         if self.local_arenas:
-            # (the clip factor is the one derived from the replicated parameters' global norm)
             self.hyper_local.copy_(self.hyper)
             if self.local_grad_scale != 1.0:
                 self.hyper_local[3:4].mul_(self.local_grad_scale)

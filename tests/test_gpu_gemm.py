@@ -15,10 +15,26 @@ def _rand(shape, dev, scale=1.0, seed=0):
     return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(dev)
 
 
+def _tile_rel_err(out, ref, tile=128):
+    """Max over ``tile x tile`` output tiles of (max abs error in the tile) / (max abs reference in the
+    tile): one wrong tile of small values cannot hide behind large values elsewhere in the matrix."""
+    import torch.nn.functional as F
+    g, w = out.float().reshape(-1, out.shape[-1]), ref.float().reshape(-1, ref.shape[-1])
+    R, C = g.shape
+    pr, pc = (-R) % tile, (-C) % tile
+    g, w = F.pad(g, (0, pc, 0, pr)), F.pad(w, (0, pc, 0, pr))
+    e = (g - w).abs().view((R + pr) // tile, tile, (C + pc) // tile, tile).amax((1, 3))
+    m = w.abs().view((R + pr) // tile, tile, (C + pc) // tile, tile).amax((1, 3))
+    return (e / m.clamp_min(w.abs().max() * 1e-3)).max().item()
+
+
 def _check(out, ref, tol, what):
     err = (out.float() - ref).abs().max().item()
     denom = ref.abs().max().item() + 1e-6
     assert err / denom < tol, f"{what}: max abs err {err:.4g} vs ref max {denom:.4g}"
+    if out.dim() >= 2:
+        t = _tile_rel_err(out, ref)
+        assert t < 3 * tol, f"{what}: worst 128x128 tile is off by {t:.3g} of its own magnitude"
 
 
 @pytest.mark.parametrize("M,N,K,bn", [

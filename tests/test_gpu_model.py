@@ -99,3 +99,57 @@ def test_engine_trains(cuda_device, graph):
     assert abs(losses[0] - math.log(cfg.vocab_size)) < 0.5
     assert losses[-1] < losses[0] - 0.3, losses
     assert int(eng.step_dev.item()) == 8
+
+
+def _tile_rel_err(got, want, tile=128):
+    """Max over ``tile x tile`` tiles of (max abs error in the tile) / (max abs reference in the tile):
+    a wrong low-magnitude tile cannot hide behind large values elsewhere in the matrix."""
+    g, w = got.float(), want.float()
+    if g.dim() == 1:
+        g, w = g[None], w[None]
+    R, Cc = g.shape
+    pr, pc = (-R) % tile, (-Cc) % tile
+    g, w = F.pad(g, (0, pc, 0, pr)), F.pad(w, (0, pc, 0, pr))
+    e = (g - w).abs().view((R + pr) // tile, tile, (Cc + pc) // tile, tile).amax((1, 3))
+    m = w.abs().view((R + pr) // tile, tile, (Cc + pc) // tile, tile).amax((1, 3))
+    floor = w.abs().max() * 1e-3                       # tiles that are all (near) zero in the reference
+    return float((e / m.clamp_min(floor)).max())
+
+
+def test_full_shape_gpt2_small_step_against_fp32_torch(cuda_device):
+    """One forward + backward of the real GPT-2 small shape (12 layers, d = 768, vocab 50257 padded to
+    50304, S = 1024: pair tiles, split-K weight gradients, eight key blocks of attention) against the
+    same model in fp32 PyTorch: loss, every parameter's gradient (norm-relative), and a per-tile check
+    of the big matrices."""
+    from frankentorch_b200.autograd.tape import TensorTape
+    from frankentorch_b200.models.gpt import GPT, GPTConfig
+    from frankentorch_b200.ops import kernels as K
+    cfg = GPTConfig.preset("gpt2-small")
+    tape = TensorTape(grad_dtype=None)
+    tape.accumulate_fn = lambda a, b: K.add(a, b) if a.dtype == torch.bfloat16 else a + b
+    model = GPT(cfg, tape, device=cuda_device, seed=21)
+    g = torch.Generator().manual_seed(8)
+    tok = torch.randint(0, cfg.vocab_size, (2, 1025), generator=g).to(cuda_device)
+    ids, tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    loss_id = model.forward(ids, tgt)
+    tape.backward(loss_id)
+    K.check_status()
+    params = {n: t[: cfg.vocab_size] if n == "wte.weight" else t for n, t in model.named_parameters()}
+    ref_loss, ref_grads = _torch_reference(cfg, params, ids, tgt)
+    assert abs(tape.value(loss_id).item() - ref_loss) < 2e-2
+    worst = ("", 0.0)
+    for name, _ in model.arena.specs:
+        got = model.arena.view(model.arena.grads, name)
+        if name == "wte.weight":
+            assert float(got[cfg.vocab_size:].abs().max()) == 0.0          # padding rows get no gradient
+            got = got[: cfg.vocab_size]
+        want = ref_grads[name]
+        rel = (got - want).norm().item() / (want.norm().item() + 1e-12)
+        if rel > worst[1]:
+            worst = (name, rel)
+        assert rel < 3e-2, f"{name}: relative gradient error {rel:.3g}"
+    for name in ("blocks.0.attn.qkv_proj.weight", "blocks.6.mlp.fc1.weight", "blocks.11.mlp.fc2.weight",
+                 "blocks.11.attn.out_proj.weight", "wpe.weight"):
+        t = _tile_rel_err(model.arena.view(model.arena.grads, name), ref_grads[name])
+        assert t < 0.15, f"{name}: worst 128x128 tile is off by {t:.3g} of its own magnitude"
+    print("worst parameter", worst)

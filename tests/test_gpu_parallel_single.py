@@ -50,6 +50,37 @@ def test_sharded_gpt_on_one_rank_matches_plain_gpt(cuda_device, kind):
         assert losses[-1] < losses[0]
 
 
+@pytest.mark.parametrize("kind", ["tp", "zero3"])
+def test_clip_norm_of_a_sharded_model_covers_every_parameter(cuda_device, kind):
+    """The clip factor of the sharded models comes from the norm of ALL gradients (replicated arena +
+    rank-local shards): with clipping active the reported norm and the trajectory follow the plain model."""
+    from frankentorch_b200.models.gpt import GPT, GPTConfig
+    from frankentorch_b200.models.gpt_tp import TensorParallelGPT
+    from frankentorch_b200.models.gpt_zero3 import Zero3GPT
+    from frankentorch_b200.training.engine import OptimConfig, TrainEngine
+    cfg = GPTConfig(n_layer=2, d_model=256, n_head=4, d_ff=1024, vocab_size=1000, max_seq=128, name="gpt-test")
+    bs, S = 2, 128
+    ids, tgt = _batch(cfg, bs, S)
+    opt = OptimConfig(lr=1e-3, grad_clip=0.05)                 # far below the gradient norm: always active
+    ref = GPT(cfg, _tape(), device=cuda_device, seed=3)
+    sd = ref.state_dict()
+    eng_ref = TrainEngine(ref, bs, S, opt, use_cuda_graph=False)
+    ref_losses, ref_norms = [], []
+    for _ in range(3):
+        ref_losses.append(eng_ref.step(ids, tgt))
+        ref_norms.append(float(eng_ref.grad_norm))
+    assert ref_norms[0] > 0.5                                  # the clip really bites
+    m = (TensorParallelGPT(cfg, _tape(), cuda_device, group=None, micro_batch=bs, seq_len=S, seed=3) if kind == "tp"
+         else Zero3GPT(cfg, _tape(), cuda_device, group=None, seed=3))
+    m.load_full_state_dict(sd)
+    eng = TrainEngine(m, bs, S, opt, use_cuda_graph=True)
+    for step in range(3):
+        loss = eng.step(ids, tgt)
+        assert abs(float(eng.grad_norm) - ref_norms[step]) < 2e-2 * ref_norms[step], (kind, step, float(eng.grad_norm), ref_norms)
+        assert abs(loss - ref_losses[step]) < 3e-2 * max(1.0, abs(ref_losses[step]))
+    K.check_status()
+
+
 def test_moe_gpt_trains_on_one_rank(cuda_device):
     from frankentorch_b200.models.gpt_moe import MoEConfig, MoEGPT
     from frankentorch_b200.ops import kernels as K
