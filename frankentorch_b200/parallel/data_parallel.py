@@ -37,10 +37,15 @@ from .symm import SymmetricBuffer
 DP_MAX_RANKS = 16
 DP_MAX_BUCKETS = 64
 DEFAULT_BUCKET_ELEMS = 16 * 1024 * 1024      # ~32 MB of bf16 on the wire per bucket
-REDUCE_CTAS = 48                             # CTAs of a bucket's push / reduce kernels under the backward pass
-TAIL_CTAS = 592                              # ... and of the buckets that finish with the backward pass
-UPDATE_CTAS = 296                            # CTAs of the AdamW + all-gather kernel when nothing else runs
-UPDATE_OVERLAP_CTAS = 64                     # ... and of the per-bucket updates that run under the forward pass
+# Grid sizes.  The GEMMs of the backward pass fill every SM's shared memory, so a communication kernel
+# that becomes ready while one runs is not co-resident with it: it takes the SMs between two compute
+# kernels (or next to the row kernels).  What it costs the step is therefore its own duration, and wide
+# grids that finish quickly beat narrow ones that "stay out of the way" (measured at 2 GPUs, GPT-2
+# small: 12 / 48 / 148 / 296 CTAs per bucket kernel -> 14.50 / 13.23 / 13.02 / 13.00 ms per step).
+REDUCE_CTAS = 296                            # CTAs of a bucket's push / reduce kernels
+TAIL_CTAS = 592                              # ... of the buckets that finish with the backward pass
+UPDATE_CTAS = 592                            # CTAs of the AdamW + all-gather kernel
+UPDATE_OVERLAP_CTAS = 592                    # ... also for the per-bucket updates under the forward pass
 
 
 def shard_multiple(world: int) -> int:

@@ -48,7 +48,9 @@ ENV_FLAGS: Dict[str, EnvFlag] = {f.name: f for f in (
     EnvFlag("FT_DP_DEFER", True, _bool, "run the sharded AdamW + parameter all-gather under the next forward pass"),
     EnvFlag("FT_DP_WIRE", "bf16", str, "gradient type on NVLink for the fused data-parallel path: bf16 or fp32"),
     EnvFlag("FT_DP_BUCKET_MB", 0.0, float, "gradient bucket size in MB of bf16 (0 = 32)"),
-    EnvFlag("FT_DP_CTAS", 48, int, "CTAs of a bucket's push / reduce kernels while the backward pass runs"),
+    EnvFlag("FT_DP_CTAS", 296, int, "CTAs of a bucket's push / reduce kernels while the backward pass runs"),
+    EnvFlag("FT_DP_UPDATE_CTAS", 592, int, "CTAs of the per-bucket AdamW + all-gather kernels under the forward pass"),
+    EnvFlag("FT_SIDE_STREAM", True, _bool, "bias column sums and split-K reductions of a backward rule on a second stream"),
     EnvFlag("FT_DP_TAIL_CTAS", 592, int, "CTAs of the buckets that finish with the backward pass"),
 )}
 
