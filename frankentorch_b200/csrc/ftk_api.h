@@ -55,6 +55,12 @@ typedef struct FtkGemmDesc {
   // stream before it reads D or reuses the workspace; the next kernel on the GEMM's stream then
   // overlaps the reduction.
   void* reduce_stream;
+  // Ragged rows: the M rows (of every batch) are segments of seg_rows rows, of which only the first
+  // seg_counts[batch * ceil(M / seg_rows) + segment] (device, int32) are in use.  128-row tiles
+  // without a row in use are skipped entirely: their part of D is left untouched.  NULL = dense.
+  // Single-CTA tiles only (no CTA pairs, no split-K).
+  const int* seg_counts;
+  int seg_rows;
 } FtkGemmDesc;
 
 int* ftk_status_word(void);               // device pointer (allocated on first use, per device)

@@ -47,7 +47,25 @@ struct GemmArgs {
   int splits;          // >1: split-K, partial tiles go to `ws` as fp32 [split][M][N]
   float* ws;
   int* status;
+  // Ragged rows (expert batches): the M rows of batch l are segments of `seg_rows` rows of which
+  // only the first seg_counts[l * segs + s] are in use; a 128-row tile without a used row is
+  // skipped by every role (no loads, no MMAs, no stores).  NULL = all rows in use.
+  const int* seg_counts;
+  int seg_rows;
 };
+
+// True when rows [m_t * 128, m_t * 128 + 128) of batch l hold at least one row in use.  Every role of a
+// CTA evaluates this for the same items, so the pipelines stay in step.
+__device__ __forceinline__ bool tile_has_rows(const GemmArgs& p, int l, int m_t) {
+  if (!p.seg_counts) return true;
+  const int row0 = m_t * 128, row1 = min(p.M, row0 + 128);
+  const int segs = (p.M + p.seg_rows - 1) / p.seg_rows;
+  for (int sg = row0 / p.seg_rows; sg <= (row1 - 1) / p.seg_rows; ++sg) {
+    const int lo = sg * p.seg_rows, hi = lo + __ldg(p.seg_counts + l * segs + sg);
+    if (max(row0, lo) < min(row1, hi)) return true;
+  }
+  return false;
+}
 
 struct CommArgs {
   int mode;                      // FTK_COMM_*
@@ -600,6 +618,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     // extra TMA requests slowed the mainloop by 1.7x.)
     for (int item = blockIdx.x; ok && item < total; item += n_compute) {
       const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
+      if (!tile_has_rows(p, t.l, t.m_t)) continue;
       const int m_t = t.m_t, n_t = t.n_t;
       const int l0 = t.l % p.L0, l1 = t.l / p.L0;
       const int kb0 = t.sp * kb_per_split;
@@ -699,6 +718,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t acc_ph = 0;  // bit a = phase of accumulator a
     bool ok = true;
     for (int item = blockIdx.x; ok && item < total; item += n_compute) {
+      if (p.seg_counts) {
+        const TileCoord tc = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
+        if (!tile_has_rows(p, tc.l, tc.m_t)) continue;
+      }
       const int sp = (COMM && c.mode != FTK_COMM_NONE) ? 0 : item / (tiles_mn * nbatch);
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(kblocks_all, kb0 + kb_per_split);
@@ -749,6 +772,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     bool epi_ok = true;   // false once this warp gave up a wait: it then skips every later barrier
     for (int item = blockIdx.x; item < total; item += n_compute) {
       const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
+      if (!tile_has_rows(p, t.l, t.m_t)) continue;
       const int sp = t.sp, l = t.l, m_t = t.m_t, n_t = t.n_t;
       const int l0 = l % p.L0, l1 = l / p.L0;
       const bool empty_split = (sp * kb_per_split >= kblocks_all);

@@ -205,6 +205,8 @@ static void fill_gemm_args(GemmArgs& a, const FtkGemmDesc* g, int L0, int L1) {
   a.splits = 1;
   a.ws = reinterpret_cast<float*>(g->workspace);
   a.status = ftk_status_word();
+  a.seg_counts = g->seg_counts;
+  a.seg_rows = g->seg_rows;
 }
 
 }  // namespace ftk
@@ -235,8 +237,9 @@ static int plan_gemm(const FtkGemmDesc* g, int* bn_out, int* splits_out) {
   // Split-K (weight-gradient shapes: few output tiles, long reduction) is considered when the
   // epilogue is a plain store and the caller supplied a workspace.
   const int kblocks = (g->K + G_BK - 1) / G_BK;
+  if (g->seg_counts && g->seg_rows <= 0) return -2;
   const bool splittable = g->epi == FTK_EPI_NONE && !g->bias && !g->resid && !g->aux && g->workspace &&
-                          (g->N % 4 == 0) && (g->ldd % 4 == 0) && L0 * L1 == 1;
+                          (g->N % 4 == 0) && (g->ldd % 4 == 0) && L0 * L1 == 1 && !g->seg_counts;
   // Option 512 is the CTA-pair kernel: 256 x 256 tiles on sms / 2 clusters; per SM it does the
   // work of a 128 x 256 tile with a third less operand traffic.
   auto cost = [&](int bn, int s) {
@@ -260,7 +263,7 @@ static int plan_gemm(const FtkGemmDesc* g, int* bn_out, int* splits_out) {
   int bn = g->force_bn, splits = 1;
   double best = 1e30;
   for (int bi = 0; bi < 4; ++bi) {
-    if (bn_opts[bi] == 512 && (sms < 2 || g->M < 256)) continue;
+    if (bn_opts[bi] == 512 && (sms < 2 || g->M < 256 || g->seg_counts)) continue;
     if (g->force_bn && bn_opts[bi] != g->force_bn) continue;
     for (int si = 0; si < 8; ++si) {
       const int s = s_opts[si];

@@ -32,6 +32,7 @@ class FtkGemmDesc(C.Structure):
         ("force_bn", C.c_int), ("max_ctas", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_longlong), ("split_k", C.c_int),
         ("reduce_stream", C.c_void_p),
+        ("seg_counts", C.c_void_p), ("seg_rows", C.c_int),
     ]
 
 

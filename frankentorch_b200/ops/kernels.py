@@ -77,13 +77,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          aux: Optional[torch.Tensor] = None, epi: int = EPI_NONE, alpha: float = 1.0,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          accumulate: bool = False, force_bn: int = 0, max_ctas: int = 0, split_k: int = 0,
-         reduce_stream: Optional[int] = None) -> torch.Tensor:
+         reduce_stream: Optional[int] = None, seg_counts: Optional[torch.Tensor] = None,
+         seg_rows: int = 0) -> torch.Tensor:
     """``D = epi(alpha * A @ B^T + bias) (+ resid) (+ D)`` on the tcgen05 GEMM.
 
     ``a`` is ``[M, K]`` (``a_mn=False``) or ``[K, M]`` (``a_mn=True``); ``b`` is
     ``[N, K]`` or ``[K, N]`` likewise.  Both must be bf16 with unit inner stride.
     ``reduce_stream`` (a raw stream handle) moves a split-K reduction off the launching stream;
     the caller joins that stream before reading the output or launching the next split-K GEMM.
+    ``seg_counts`` (int32, device) with ``seg_rows``: the rows are segments of ``seg_rows`` rows of which
+    only the first ``seg_counts[s]`` are in use; 128-row tiles without a used row are skipped and
+    their output rows are left as they were (expert batches with capacity padding).
     """
     _bf16(a, "a"), _bf16(b, "b")
     if a.dim() != 2 or b.dim() != 2 or a.stride(1) != 1 or b.stride(1) != 1:
@@ -118,6 +122,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.accumulate, g.force_bn, g.max_ctas = int(accumulate), int(force_bn), int(max_ctas)
     g.split_k = int(split_k)
     g.reduce_stream = reduce_stream
+    if seg_counts is not None:
+        if seg_counts.dtype != torch.int32 or not seg_counts.is_cuda or seg_rows <= 0:
+            raise KernelError("seg_counts must be a CUDA int32 tensor and seg_rows positive")
+        if a_mn or seg_counts.numel() < -(-M // seg_rows):
+            raise KernelError("seg_counts needs one entry per segment of rows of a row-major A operand")
+        g.seg_counts, g.seg_rows = seg_counts.data_ptr(), int(seg_rows)
     lib = _lib.load()
     dev_key = a.device.index if a.device.index is not None else torch.cuda.current_device()
     if split_k != 1 and bias is None and resid is None and aux is None and epi == EPI_NONE:
@@ -184,14 +194,14 @@ def gemm_batched(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int,
     return out
 
 
-def linear_fwd(x, w, bias=None, *, epi=EPI_NONE, resid=None, aux=None, out=None):
+def linear_fwd(x, w, bias=None, *, epi=EPI_NONE, resid=None, aux=None, out=None, seg_counts=None, seg_rows=0):
     """``y = epi(x @ w^T + bias) (+ resid)`` with ``w`` stored ``[out, in]``."""
-    return gemm(x, w, bias=bias, epi=epi, resid=resid, aux=aux, out=out)
+    return gemm(x, w, bias=bias, epi=epi, resid=resid, aux=aux, out=out, seg_counts=seg_counts, seg_rows=seg_rows)
 
 
-def linear_dgrad(dy, w, *, epi=EPI_NONE, resid=None, out=None):
+def linear_dgrad(dy, w, *, epi=EPI_NONE, resid=None, out=None, seg_counts=None, seg_rows=0):
     """``dx = dy @ w`` (``w`` is ``[out, in]``; consumed as an MN-major operand)."""
-    return gemm(dy, w, b_mn=True, epi=epi, resid=resid, out=out)
+    return gemm(dy, w, b_mn=True, epi=epi, resid=resid, out=out, seg_counts=seg_counts, seg_rows=seg_rows)
 
 
 def linear_wgrad(dy, x, *, out=None, accumulate=False, reduce_stream=None):

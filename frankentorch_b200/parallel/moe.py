@@ -51,6 +51,18 @@ class MoEBuffers:
         self.recv_dy = SymmTensor(self.buf, shape, torch.bfloat16, 2 * n)
         self.dxe = SymmTensor(self.buf, shape, torch.bfloat16, 3 * n)
         self.counts = SymmTensor(self.buf, (ep.e_local * ep.world,), torch.int32, 4 * n)
+        self._ep = ep
+        self._act = {}
+
+    def activations(self, ff: int):
+        """Pre-activation, activation and their gradient, ``[E_local, world * C, ff]`` each, allocated
+        once and zero-filled: the ragged GEMMs never write the rows of skipped tiles, and what they
+        leave there must stay finite (the weight gradients multiply those rows by exact zeros)."""
+        if ff not in self._act:
+            ep = self._ep
+            shape = (ep.e_local, ep.world * ep.capacity, ff)
+            self._act[ff] = tuple(torch.zeros(shape, dtype=torch.bfloat16, device=ep.device) for _ in range(3))
+        return self._act[ff]
 
 
 class ExpertParallel:
@@ -154,11 +166,17 @@ def moe_ffn(tape: TensorTape, x: int, wr: int, w1: int, b1: int, w2: int, b2: in
     X = bufs.recv_x.t.view(el_n, rows_e, d)
     Y = bufs.y.t.view(el_n, rows_e, d)
     ff = w1v.shape[1]
-    u = torch.empty((el_n, rows_e, ff), dtype=torch.bfloat16, device=xv.device)
-    h = torch.empty_like(u)
+    # Rows of an expert's batch: `world` segments of `capacity` slots, of which the first
+    # recv_counts[e][src] hold tokens.  The GEMMs skip every 128-row tile that holds none (their outputs
+    # are never read: combine only fetches slots below the count), so the capacity padding costs nothing.
+    # The activation buffers live with the layer, start zeroed and only ever hold finite values in
+    # skipped rows, which the weight gradients multiply by the zero rows of the dispatched gradient.
+    u, h, du_all = bufs.activations(ff)
+    seg = bufs.counts.t.view(el_n, ep.world)
+    cap = ep.capacity
     for e in range(el_n):
-        K.linear_fwd(X[e], w1v[e], b1v[e], epi=epi, aux=u[e], out=h[e])
-        K.linear_fwd(h[e], w2v[e], b2v[e], out=Y[e])
+        K.linear_fwd(X[e], w1v[e], b1v[e], epi=epi, aux=u[e], out=h[e], seg_counts=seg[e], seg_rows=cap)
+        K.linear_fwd(h[e], w2v[e], b2v[e], out=Y[e], seg_counts=seg[e], seg_rows=cap)
     out, rows = ep.combine(bufs.y, idx, slot, counts, gate,
                            resid=None if rv is None else rv.reshape(T, d), keep_rows=True)
 
@@ -188,14 +206,15 @@ def moe_ffn(tape: TensorTape, x: int, wr: int, w1: int, b1: int, w2: int, b2: in
             r = into(targets, 5, e, lambda out, accumulate: K.colsum(DY[e], out=out, accumulate=accumulate))
             if r is None:
                 loose[5].append(K.colsum(DY[e]))
-            du = K.linear_dgrad(DY[e], w2v[e], epi=depi, resid=u[e])
+            du = du_all[e]
+            K.linear_dgrad(DY[e], w2v[e], epi=depi, resid=u[e], out=du, seg_counts=seg[e], seg_rows=cap)
             r = into(targets, 2, e, lambda out, accumulate: K.linear_wgrad(du, X[e], out=out, accumulate=accumulate))
             if r is None:
                 loose[2].append(K.linear_wgrad(du, X[e]))
             r = into(targets, 3, e, lambda out, accumulate: K.colsum(du, out=out, accumulate=accumulate))
             if r is None:
                 loose[3].append(K.colsum(du))
-            K.linear_dgrad(du, w1v[e], out=DX[e])
+            K.linear_dgrad(du, w1v[e], out=DX[e], seg_counts=seg[e], seg_rows=cap)
         grads = {}
         for i in (2, 3, 4, 5):
             if loose[i]:

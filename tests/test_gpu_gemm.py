@@ -201,3 +201,26 @@ def test_gemm_pair_split_k_and_determinism(cuda_device):
     k.check_status()
     _check(o1, ref, 2e-2, "pair split-k")
     assert torch.equal(o1, o2), "the pair kernel's result must not depend on the grid"
+
+
+def test_gemm_skips_tiles_without_rows_in_use(cuda_device):
+    """Ragged rows (expert batches): rows come in segments of which only a prefix is in use; tiles of
+    128 rows that hold no row in use are skipped (their output is left alone), every other row is exact."""
+    k = _ops()
+    seg_rows, segs, N, K = 640, 3, 256, 192          # 5 tiles per segment
+    counts = torch.tensor([200, 0, 513], dtype=torch.int32, device=cuda_device)
+    a = _rand((seg_rows * segs, K), cuda_device, seed=7)
+    w = _rand((N, K), cuda_device, 0.2, 8)
+    bias = _rand((N,), cuda_device, 0.5, 9)
+    out = torch.full((seg_rows * segs, N), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    k.gemm(a, w, bias=bias, out=out, seg_counts=counts, seg_rows=seg_rows)
+    k.check_status()
+    ref = a.float() @ w.float().t() + bias.float()
+    for s, c in enumerate(counts.tolist()):
+        lo = s * seg_rows
+        used_hi = lo + -(-c // 128) * 128                      # rows of tiles that hold a used row are computed
+        if c:
+            _check(out[lo:lo + c], ref[lo:lo + c], 2e-2, f"segment {s} rows in use")
+        assert torch.all(out[used_hi:lo + seg_rows].float() == 7.0), f"segment {s}: a skipped tile was written"
+    dense = k.gemm(a, w, bias=bias)
+    assert torch.equal(dense[:200], out[:200])                 # the same kernel arithmetic, bit for bit
