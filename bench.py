@@ -50,6 +50,8 @@ MODELS = {
     "moe-12l": ("moe-12l", 4, 2048, "ep"),             # 8 experts top-2, expert parallel
     "gpt-tiny": ("gpt-tiny", 4, 128, "dp"),
     "moe-tiny": ("moe-tiny", 4, 128, "ep"),
+    # CPU single-process MLP 784-256-128-10 (f32, ReLU, cross-entropy, AdamW 1e-3, batch 64): no GPU involved
+    "mlp-cpu": ("mlp-cpu", 64, 784, "cpu"),
 }
 
 
@@ -214,6 +216,104 @@ def multi_gpu_check(engine, dp, dist, torch):
             "ok": bool(diff <= tol and int(same) == 1)}
 
 
+def run_mlp_cpu(args):
+    """Config 1: the public session API end to end on the CPU reference path, with deterministic-replay and
+    state-dict round-trip checks, and the stock-PyTorch arm as an interleaved co-process."""
+    import tempfile as _tmp
+
+    import torch
+
+    from frankentorch_b200 import harness as H
+    from frankentorch_b200 import nn, optim, serialize
+    from frankentorch_b200.core.dtype import DType
+    from frankentorch_b200.session import FrankenTorchSession
+    dims, batch = (784, 256, 128, 10), 64
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+
+    class MLP(nn.Module):
+        def __init__(self, s):
+            super().__init__()
+            self.l1, self.l2, self.l3 = (nn.Linear(s, dims[i], dims[i + 1]) for i in range(3))
+
+        def forward(self, s, x):
+            return self.l3(s, s.tensor_relu(self.l2(s, s.tensor_relu(self.l1(s, x)))))
+
+    def build():
+        s = FrankenTorchSession(default_dtype=DType.F32)
+        m = MLP(s)
+        for _, p in m.named_parameters():
+            s.tensor(p).data = s.tensor(p).to(torch.float32)
+        return s, m, optim.AdamW(m.parameters(), 1e-3), s.autograd_graph_len()
+
+    def train(state, n):
+        s, m, opt, boundary = state
+        losses, orders = [], []
+        for _ in range(n):
+            x = s.tensor_variable_from_storage(s.tensor(s.randn([batch, dims[0]])).to(torch.float32))
+            y = s.randint(0, dims[-1], [batch])
+            loss = s.tensor_cross_entropy(m(s, x), y)
+            opt.zero_grad(s)
+            rep = s.tensor_backward(loss)
+            opt.step(s, rep)
+            losses.append(s.tensor_item(loss))
+            orders.append(tuple(rep.telemetry.execution_order))
+            s.truncate_autograd_graph(boundary)
+        return losses, orders
+    # replay: two sessions from the same seed give the same loss bits and execution orders for 100 steps
+    a, b = build(), build()
+    la, oa = train(a, 100)
+    lb, ob = train(b, 100)
+    replay_ok = la == lb and oa == ob
+    with _tmp.TemporaryDirectory() as td:
+        path = os.path.join(td, "mlp.ftsv")
+        serialize.save_state_dict(a[1].state_dict(a[0]), path)
+        c = build()
+        c[1].load_state_dict(c[0], serialize.load_state_dict(path), strict=True)
+        probe = torch.randn(4, dims[0])
+        pa = a[0].tensor(a[1](a[0], a[0].tensor_variable_from_storage(probe)))
+        pc = c[0].tensor(c[1](c[0], c[0].tensor_variable_from_storage(probe)))
+        round_trip_ok = bool(torch.equal(pa, pc))
+    # timed: K steps after W warm-up steps (wall clock: everything is host work)
+    st = build()
+    train(st, warmup)
+    t0 = time.perf_counter()
+    train(st, steps)
+    ms = (time.perf_counter() - t0) * 1e3
+    # head to head: the incumbent as a co-process, interleaved in the balanced-square order
+    hs = max(1, args.h2h_steps * 2)
+    vs = None
+    if not args.no_torch_arm:
+        try:
+            arm = H.CoProcessArm([sys.executable, os.path.join(REPO, "benchmarks", "torch_mlp_arm.py"),
+                                  "--steps", str(hs)])
+            try:
+                def ours():
+                    t = time.perf_counter()
+                    train(st, hs)
+                    return (time.perf_counter() - t) * 1e3 / hs
+                res = H.run_balanced_square(ours, lambda: arm.sample("mlp").milliseconds / hs, rounds=2,
+                                            ours_steps=("batch", "forward", "loss", "backward", "optimizer"),
+                                            incumbent_steps=arm.timed_steps or ())
+                vs = dict(res.as_dict(), impl="stock pytorch CPU (nn.Sequential, AdamW), co-process",
+                          steps_per_sample=hs, **H.incumbent_provenance_block(arm.version, torch.get_num_threads()))
+            finally:
+                arm.close()
+        except H.MissingIncumbentVersion as e:
+            vs = {"refused": str(e)}
+    out = {"metric": "train steps/sec (CPU, single process)", "value": steps / (ms / 1e3), "unit": "steps/s",
+           "n_gpus": 0, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
+           "scaling": "none", "vs_baseline": None, "dtype": "f32 (f64 gradient space)",
+           "data": "synthetic (inputs N(0,1), labels uniform in [0,10), session PRNG)", "impl": "ours",
+           "config": {"model": "mlp 784-256-128-10", "batch": batch, "optimizer": "AdamW lr 1e-3",
+                      "api": "FrankenTorchSession + ft.nn + ft.optim on the CPU reference path"},
+           "deterministic_replay_100_steps": replay_ok, "state_dict_round_trip_exact": round_trip_ok,
+           "final_loss": la[-1], "gpu_launches": 0, "vs_torch": vs,
+           "e2e": {"value": steps / (ms / 1e3), "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                   "note": "host-only workload: the timed region is already the public API end to end"}}
+    print(json.dumps(out))
+    return 0 if (replay_ok and round_trip_ok) else 3
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -228,6 +328,8 @@ def main():
     args = parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.model == "mlp-cpu":
+        return run_mlp_cpu(args)
 
     import torch
     import torch.distributed as dist

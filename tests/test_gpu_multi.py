@@ -63,3 +63,13 @@ def test_fused_data_parallel_matches_nccl_and_replays(cuda_device):
     nproc = 2 if n < 4 else 4
     p = _run_workers("_dp_worker.py", nproc, 29631)
     assert p.returncode == 0 and "DP_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_pipeline_stages_over_nccl_match_a_single_process_run(cuda_device):
+    """GPipe and 1F1B on two GPUs over NCCL send / recv (NVLS off, 60 s process-group timeout): the
+    posting order that the host-side replay accepted really completes, gradients and loss match."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    p = _run_workers("_pp_worker.py", 2, 29641, timeout=240)
+    assert p.returncode == 0 and "PP_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
