@@ -225,10 +225,11 @@ def bench_dp_world1(n_params, iters, warm):
     from frankentorch_b200.models.gpt import ParamArena
     from frankentorch_b200.parallel.data_parallel import FusedDataParallel
     pk = peaks()
-    arena = ParamArena([("w", (n_params,))], torch.device("cuda"), peer_visible=True)
+    dev = torch.device("cuda", 0)
+    arena = ParamArena([("w", (n_params,))], dev, peer_visible=True)
     arena.master.normal_()
     arena.grads.normal_()
-    dp = FusedDataParallel(arena, None, torch.device("cuda"), bucket_elems=n_params // 4, overlap=False,
+    dp = FusedDataParallel(arena, None, dev, bucket_elems=n_params // 4, overlap=False,
                            defer_update=False)
     opt = types.SimpleNamespace(beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, grad_clip=1.0)
     hyper = torch.tensor([1e-3, 0.1, 0.001, 1.0], device="cuda")

@@ -327,6 +327,7 @@ def matmul(tape: TensorTape, a: int, b: int) -> int:
     a_needs, b_needs = tape.nodes[a].requires_grad, tape.nodes[b].requires_grad
 
     def vjp(g, targets):
+        g = g.contiguous()          # an expanded gradient (from a sum) has zero strides
         da = K.gemm(g, bv) if a_needs else None                         # dOut @ B^T
         db = K.gemm(av, g, a_mn=True, b_mn=True) if b_needs else None   # A^T @ dOut
         return [da, db]
