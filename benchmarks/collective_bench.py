@@ -10,6 +10,7 @@ with an L2 flush between iterations.  The roofline of a fused op is the slower o
 FLOPs / measured GEMM peak and NVLink bytes / 770 GB/s (measured peer copy per direction).
 """
 import argparse
+import contextlib
 import json
 import os
 import sys
@@ -18,6 +19,7 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 LINK_GBS = 770.0
 
@@ -57,6 +59,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--comm-ctas", type=int, default=0, help="0 = the launcher's default")
+    ap.add_argument("--nvls-ctas", type=int, default=148)
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -66,6 +69,9 @@ def main():
     from frankentorch_b200.parallel.fused_gemm import FusedCollectives, SymmTensor
     from frankentorch_b200.parallel.moe import ExpertParallel
 
+    from kernel_bench import Clocks
+    clk = Clocks() if rank == 0 else contextlib.nullcontext()
+    clk.__enter__()
     peak, src = peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     g = dist.group.WORLD
@@ -98,6 +104,21 @@ def main():
     t_b = timeit(base_ag, args.iters, args.warmup, flush)
     report(f"allgather->gemm  x[{ms}x{d}]*{world} @ W[{n}x{d}]", t_f, t_b, 2.0 * m * n * d,
            (world - 1) * ms * d * 2)
+    # push form: two alternating symmetric staging buffers, the shards stored by their owners
+    stg = fc.staging((m, d))
+    turn = [0]
+
+    def push_ag():
+        turn[0] ^= 1
+        fc.allgather_a_gemm(xs, w, stg[turn[0]], out=out)
+    t_p = timeit(push_ag, args.iters, args.warmup, flush)
+    K.check_status()
+    want = torch.matmul(x_full, w.t())
+    assert torch.equal(stg[turn[0]].t, x_full), "push gather staged other rows than the NCCL all-gather"
+    assert float((out.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
+    report(f"allgather->gemm (push)  x[{ms}x{d}]*{world} @ W[{n}x{d}]", t_p, t_b, 2.0 * m * n * d,
+           (world - 1) * ms * d * 2)
+    del stg
 
     # ---- K13: GEMM -> reduce-scatter (row-parallel fc2 slice)
     kk, n2 = 8192 // 8, 2048
@@ -133,6 +154,16 @@ def main():
     t_b = timeit(base_agw, args.iters, args.warmup, flush)
     report(f"allgather(W)->gemm  x[8192x{d3}] @ W[{n3}x{d3}]", t_f, t_b, 2.0 * 8192 * n3 * d3,
            (world - 1) * (n3 // world) * d3 * 2)
+    wstg = fc.staging((n3, d3))
+
+    def push_agw():
+        turn[0] ^= 1
+        fc.allgather_b_gemm(x3, ws, wstg[turn[0]], out=out3)
+    t_p = timeit(push_agw, args.iters, args.warmup, flush)
+    K.check_status()
+    assert torch.equal(wstg[turn[0]].t, w_full), "push gather staged other weights than the NCCL all-gather"
+    report(f"allgather(W)->gemm (push)  x[8192x{d3}] @ W[{n3}x{d3}]", t_p, t_b, 2.0 * 8192 * n3 * d3,
+           (world - 1) * (n3 // world) * d3 * 2)
 
     # ---- K14 / K16: MoE dispatch and combine (8 experts, top-2, capacity 1.25, d = 1024)
     T, dm, E = 8192, 1024, 8
@@ -165,9 +196,34 @@ def main():
         t_b = timeit(base_comb, args.iters, args.warmup, flush)
         report(f"moe combine  T={T} d={dm}", t_f, t_b, 0.0, remote * dm * 2)
 
+    # ---- NVLS: multimem.st all-gather and multimem.ld_reduce all-reduce against NCCL
+    try:
+        from frankentorch_b200.parallel.nvls import MulticastBuffer, NvlsCollectives, NvlsUnavailable
+        nel = 8 << 20                                            # 32 MiB of fp32 per rank
+        mb = MulticastBuffer(world * nel * 4 + nel * 4, None, dev)
+        coll = NvlsCollectives(mb, n_ctas=args.nvls_ctas)
+        srcv = torch.randn(nel, device=dev)
+        gathered = torch.empty(world * nel, device=dev)
+        t_f = timeit(lambda: coll.all_gather(srcv, 0), args.iters, args.warmup, flush)
+        t_b = timeit(lambda: dist.all_gather_into_tensor(gathered, srcv), args.iters, args.warmup, flush)
+        K.check_status()
+        assert torch.equal(mb.tensor(torch.float32, world * nel, 0), gathered)
+        report(f"nvls all-gather  {nel * 4 >> 20} MiB per rank (multimem.st)", t_f, t_b, 0.0, (world - 1) * nel * 4)
+        red = torch.randn(nel, device=dev)
+        off = world * nel * 4
+        t_f = timeit(lambda: coll.all_reduce_(off, nel, torch.float32), args.iters, args.warmup, flush)
+        t_b = timeit(lambda: dist.all_reduce(red), args.iters, args.warmup, flush)
+        K.check_status()
+        report(f"nvls all-reduce  {nel * 4 >> 20} MiB fp32 (multimem.ld_reduce + st)", t_f, t_b, 0.0,
+               2 * (world - 1) * nel * 4 // world)
+    except Exception as e:          # no multicast object on this system: say so, keep the other rows
+        if rank == 0:
+            print(json.dumps({"nvls": "unavailable", "why": repr(e)[:200]}))
+
+    clk.__exit__(None, None, None)
     if rank == 0:
         print(json.dumps({"world": world, "gemm_peak_tflops": peak, "peak_source": src, "link_gbs": LINK_GBS,
-                          "results": rows}, indent=1))
+                          "iters": args.iters, "results": rows}, indent=1))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -99,6 +99,12 @@ typedef struct FtkCommDesc {
   void* inbox[FTK_MAX_RANKS];          // scatter: inbox of every rank
   int* arrive[FTK_MAX_RANKS];          // scatter: [chunk tiles][world] words on every rank
   const int* epoch;
+  // gather, push form (push != 0): every rank stores its own shard into the staging buffer of every
+  // peer and sets the flags there; the GEMM's staged operand (A or B) must be full_peer[rank] and
+  // sub_flags must be flags_peer[rank].  Consecutive calls must alternate two staging buffers.
+  int push;
+  void* full_peer[FTK_MAX_RANKS];
+  int* flags_peer[FTK_MAX_RANKS];
 } FtkCommDesc;
 int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* c, void* stream);
 int ftk_tick_i32(int* word, void* stream);    // *word += 1 on the stream
@@ -306,6 +312,31 @@ int ftk_dp_update(const FtkDpComm* c, int b0, int b1, float* master, float* m, f
                   float beta1, float beta2, float eps, float weight_decay, int n_ctas, void* stream);
 int ftk_dp_clear_pending(const FtkDpComm* c, void* stream);
 int ftk_dp_wait_params(const FtkDpComm* c, int b0, void* stream);
+#ifdef __cplusplus
+}
+#endif
+
+// ---- collectives through the NVSwitch multicast object (nvls.cu) -----------------------------
+#ifdef __cplusplus
+extern "C" {
+#endif
+#define FTK_NVLS_MAX_RANKS 16
+// One symmetric allocation bound to a multicast object.  mc: its multicast address; local: this
+// rank's own mapping; flags[r]: rank r's flag block (u64 [4][FTK_NVLS_MAX_RANKS], zero-initialised,
+// inside the allocation, addressed through the ordinary peer mapping); counter: a zeroed local
+// device word.  `seq` of a call must be larger than that of every earlier call on the same
+// allocation and equal on all ranks.
+typedef struct {
+  void* mc;
+  void* local;
+  void* flags[FTK_NVLS_MAX_RANKS];
+  unsigned int* counter;
+  int rank, world;
+} FtkNvlsComm;
+int ftk_nvls_allgather(const FtkNvlsComm* c, const void* src, long long dst_off, long long chunk_bytes,
+                       unsigned long long seq, int n_ctas, void* stream);
+int ftk_nvls_allreduce(const FtkNvlsComm* c, long long off, long long n_bytes, int dtype, unsigned long long seq,
+                       int n_ctas, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -77,6 +77,9 @@ struct CommArgs {
   int* sub_flags;                // gather: one word per 128-row subtile, holds the epoch
   int* ready_local;              // gather: [world] words written by the peers (may be null)
   int* ready_peer[G_MAX_RANKS];  // gather: word `rank` of peer r's ready_local
+  int push;                      // gather: 1 = every rank stores its own shard into the peers' staging
+  uint8_t* full_peer[G_MAX_RANKS];   // push gather: staging buffer of rank r (entry `rank` == full)
+  int* flags_peer[G_MAX_RANKS];      // push gather: sub_flags of rank r (entry `rank` == sub_flags)
   __nv_bfloat16* inbox[G_MAX_RANKS];  // scatter: inbox of rank r, [world][chunk_rows][N]
   int* arrive[G_MAX_RANKS];      // scatter: flags of rank r, [tiles of one chunk][world]
   const int* epoch;              // device word: use count (>= 1) of the flag arrays
@@ -415,6 +418,54 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
   }
 }
 
+// ------------------------------------------------------------------ comm CTAs: gather, push form
+// Every rank stores its own shard into every peer's staging buffer with plain 16-byte peer
+// stores and publishes one flag per piece AT THE CONSUMER, so that consumers only ever poll
+// their own memory.  The work list is destination-major in the order the consumers need their
+// chunks: rank P's data is the first remote chunk of rank P-1, the second of P-2, ...; at any
+// time each GPU sends one chunk to one peer and receives one chunk from one peer at the full
+// link rate, and a consumer's next chunk is complete after 1/(W-1) of the whole exchange.
+// Pieces are dealt round robin to all warps of the copy CTAs (CTA index fastest); a warp keeps
+// 8 x 512 bytes in flight.  The copy into this rank's own staging buffer comes first for weight
+// gathers (tiles that straddle two chunks wait for its flags) and last for activation gathers
+// (the GEMM reads own tiles from the shard; the staged copy only serves later kernels).
+// The caller alternates two staging buffers between consecutive calls: a rank can be at most
+// one collective ahead of a peer, so the buffer it writes is never the one that peer still reads.
+__device__ __forceinline__ void comm_gather_push(const CommArgs& c, int epoch, int cta, bool own_last) {
+  const int spc = c.chunk_rows / G_BM;
+  const uint32_t piece = c.sub_bytes < G_COPY_SLOT ? (uint32_t)c.sub_bytes : (uint32_t)G_COPY_SLOT;
+  const int pps = (int)(c.sub_bytes / piece);
+  const int ppc = spc * pps;
+  const int lane = threadIdx.x & 31;
+  const int n_warps = c.comm_ctas * (int)(blockDim.x >> 5);
+  const int gw = (int)(threadIdx.x >> 5) * c.comm_ctas + cta;
+  const int nv = (int)(piece >> 4);
+  const long long total = (long long)ppc * c.world;
+  for (long long j = gw; j < total; j += n_warps) {
+    const int d = (int)(j / ppc), q = (int)(j % ppc);
+    int dest;
+    if (own_last)
+      dest = d == c.world - 1 ? c.rank : (c.rank - 1 - d + 2 * c.world) % c.world;
+    else
+      dest = (c.rank - d + c.world) % c.world;
+    const uint4* src = reinterpret_cast<const uint4*>(c.src[c.rank] + (long long)q * piece);
+    uint4* dst = reinterpret_cast<uint4*>(c.full_peer[dest] + ((long long)c.rank * ppc + q) * piece);
+    for (int v0 = lane; v0 < nv; v0 += 32 * 8) {
+      uint4 u[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (v0 + k * 32 < nv) u[k] = __ldg(src + v0 + k * 32);
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (v0 + k * 32 < nv) dst[v0 + k * 32] = u[k];
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) st_rel_sys(c.flags_peer[dest] + c.rank * ppc + q, epoch);
+    __syncwarp();
+  }
+}
+
 // ------------------------------------------------------------------ ordered reduce
 // Tile (n_t, m_in) of this rank's chunk: out = sum over source ranks (ascending) of the bf16
 // partials in the local inbox, + bias, + residual, (+ previous output).  Run by `nthr` threads
@@ -585,6 +636,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       if (c.mode == FTK_COMM_SCATTER_D)
         comm_reduce<BN>(p, c, epoch, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, G_THREADS, ctx, wbar,
                         wbar_ph);
+      else if (c.push)
+        comm_gather_push(c, epoch, cta, /*own_last=*/c.mode == FTK_COMM_GATHER_A);
       else
         comm_gather(smem, bars, c, epoch, cta,
                     /*own_last=*/c.mode == FTK_COMM_GATHER_A, ctx);
@@ -655,7 +708,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
         // one flag per piece; the lanes poll the pieces of subtiles f0..f1 in parallel
         int good = 1;
         for (int pc = f0 * pps + lane; pc < (f1 + 1) * pps && good; pc += 32)
-          good = flag_wait<false>(c.sub_flags + pc, epoch, ctx) ? 1 : 0;
+          good = (c.push ? flag_wait<true>(c.sub_flags + pc, epoch, ctx)
+                         : flag_wait<false>(c.sub_flags + pc, epoch, ctx)) ? 1 : 0;
         fence_proxy_async_all();
         if (!__all_sync(0xffffffffu, good)) break;
       }
@@ -666,7 +720,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
           while (ok && k_ready < need) {
             int good = 1;
             for (int pc = k_ready * pps + lane; pc < (k_ready + 1) * pps && good; pc += 32)
-              good = flag_wait<false>(c.sub_flags + pc, epoch, ctx) ? 1 : 0;
+              good = (c.push ? flag_wait<true>(c.sub_flags + pc, epoch, ctx)
+                             : flag_wait<false>(c.sub_flags + pc, epoch, ctx)) ? 1 : 0;
             fence_proxy_async_all();
             if (!__all_sync(0xffffffffu, good)) ok = false;
             ++k_ready;

@@ -355,7 +355,9 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   // gathers: CTAs that only move data (default 20); reduce-scatter: every CTA reduces after its
   // GEMM tiles, dedicated CTAs are optional (default none)
   c.comm_ctas = cd->comm_ctas > 0 ? cd->comm_ctas : (cd->mode == FTK_COMM_SCATTER_D ? 0 : 20);
-  if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D) {
+  if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D && cd->push) {
+    c.comm_ctas = 16;   // stores are posted: a few CTAs keep the link full
+  } else if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D) {
     // Split the SMs between copying and computing in proportion to the work: a copy CTA keeps
     // 128 KB of peer loads in flight, which at NVLink latency under load is ~13 GB/s (measured
     // at 2 and 8 ranks), a compute CTA delivers its share of the sustained GEMM rate.
@@ -393,13 +395,22 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
     if (!cd->sub_flags) return -2;
     c.full = reinterpret_cast<uint8_t*>(const_cast<void*>(ga ? g->A : g->B));
     c.sub_flags = cd->sub_flags;
-    c.ready_local = cd->ready_local;
+    c.ready_local = cd->push ? nullptr : cd->ready_local;
+    c.push = cd->push ? 1 : 0;
     for (int r = 0; r < cd->world; ++r) {
+      if (cd->push) {
+        // only the own shard is read; peers' staging buffers and flag arrays are written
+        if (!cd->full_peer[r] || !cd->flags_peer[r] || (reinterpret_cast<uintptr_t>(cd->full_peer[r]) & 15)) return -2;
+        c.full_peer[r] = reinterpret_cast<uint8_t*>(cd->full_peer[r]);
+        c.flags_peer[r] = cd->flags_peer[r];
+        if (r != cd->rank) continue;
+      }
       if (!cd->src[r] || (reinterpret_cast<uintptr_t>(cd->src[r]) & 15)) return -3;
       c.src[r] = reinterpret_cast<const uint8_t*>(cd->src[r]);
       c.ready_peer[r] = cd->ready_peer[r];
-      if (cd->ready_local && r != cd->rank && !cd->ready_peer[r]) return -2;
+      if (!cd->push && cd->ready_local && r != cd->rank && !cd->ready_peer[r]) return -2;
     }
+    if (cd->push && (c.full_peer[cd->rank] != c.full || c.flags_peer[cd->rank] != c.sub_flags)) return -2;
   }
 
   CUtensorMap tmA, tmB;

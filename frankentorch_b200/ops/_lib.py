@@ -66,6 +66,9 @@ class FtkCommDesc(C.Structure):
         ("inbox", C.c_void_p * FTK_MAX_RANKS),
         ("arrive", C.c_void_p * FTK_MAX_RANKS),
         ("epoch", C.c_void_p),
+        ("push", C.c_int),
+        ("full_peer", C.c_void_p * FTK_MAX_RANKS),
+        ("flags_peer", C.c_void_p * FTK_MAX_RANKS),
     ]
 
 

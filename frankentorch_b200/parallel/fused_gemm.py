@@ -8,6 +8,10 @@ few CTAs move data between GPUs while the rest multiply:
 * :meth:`FusedCollectives.allgather_b_gemm`  - all-gather of a row-sharded weight feeding the
   B operand (ZeRO-3 parameter gather fused into the first GEMM that consumes it), forward
   (``x W^T``) and dgrad (``dy W``, weight sharded along the reduction dimension);
+  Both gathers have two forms: the *pull* form (staging buffer in ordinary local memory; copy CTAs
+  fetch the peers' shards) and the *push* form (staging buffer in symmetric memory, passed as a
+  :class:`SymmTensor`: every rank stores its own shard into all peers' staging buffers in the
+  order the consumers need them, and consumers poll flags in their own memory only);
 * :meth:`FusedCollectives.gemm_reduce_scatter` - the epilogue stores bf16 partial tiles into the
   owning rank's inbox and the owner adds them in ascending rank order (row-parallel Linear,
   ZeRO-3 weight-gradient reduce-scatter).
@@ -20,7 +24,10 @@ flag arrays are never cleared and can be shared by calls of different shapes.  T
 in device memory and is advanced by a one-thread kernel before each launch, which keeps the
 sequence replayable inside a CUDA graph.  Shard buffers and inboxes that change between calls
 must alternate between two slots: a rank can run at most one collective ahead of its slowest
-peer, because every collective needs a contribution of every rank.
+peer, because every collective needs a contribution of every rank.  The same rule covers the
+push form's staging buffers (:meth:`FusedCollectives.staging` hands out such pairs): a peer
+writes into this rank's buffer, so the buffer a call receives into must not be read by the
+call before it nor by anything launched after that call.
 """
 from __future__ import annotations
 
@@ -84,6 +91,9 @@ class FusedCollectives:
         words = 64 + 3 * max_chunk_tiles * self.world
         self.flags = SymmetricBuffer(words * 4, group, device)
         self.flags.bytes.zero_()
+        # push-form gathers: the per-piece flags are written by the peers
+        self.gflags = SymmetricBuffer(self.sub_flags.numel() * 4, group, device)
+        self.gflags.bytes.zero_()
         self.max_inbox_elems = max_inbox_elems
         self.inbox = None
         if max_inbox_elems:
@@ -143,9 +153,24 @@ class FusedCollectives:
         g.accumulate = int(accumulate)
         return g
 
-    def _gather(self, c: FtkCommDesc, shard: SymmTensor, handshake: bool) -> None:
+    def staging(self, shape: Sequence[int], slots: int = 2) -> List[SymmTensor]:
+        """``slots`` symmetric bf16 staging buffers for the push-form gathers (alternate them call by call)."""
+        return [SymmTensor.alloc(shape, torch.bfloat16, self.group, self.device) for _ in range(slots)]
+
+    def _gather(self, c: FtkCommDesc, shard: SymmTensor, handshake: bool, full=None) -> None:
         for r in range(self.world):
             c.src[r] = shard.peer_ptrs[r]
+        if isinstance(full, SymmTensor):
+            row_bytes = shard.t.shape[1] * 2
+            n_flags = c.chunk_rows // TILE_M * self.world * max(1, TILE_M * row_bytes // 32768)
+            if n_flags > self.sub_flags.numel():
+                raise K.KernelError("gathered operand needs more flag words than were allocated")
+            c.push = 1
+            c.sub_flags = self.gflags.local_ptr
+            for r in range(self.world):
+                c.full_peer[r] = full.peer_ptrs[r]
+                c.flags_peer[r] = self.gflags.peer_ptrs[r]
+            return
         # one flag word per copied piece (at most 32 KiB) of the gathered operand
         row_bytes = shard.t.shape[1] * 2
         sub = TILE_M * row_bytes
@@ -165,8 +190,12 @@ class FusedCollectives:
         """``out = epi(allgather(x_shard) @ op(w) + bias)``; ``x_full`` receives the gathered rows.
 
         ``x_shard.t`` is ``[rows / world, K]`` in symmetric memory, ``x_full`` ``[rows, K]`` local
-        scratch (contiguous); ``w`` is ``[N, K]`` or, with ``b_mn``, ``[K, N]``.
+        scratch (contiguous) or, for the push form, a :class:`SymmTensor` of that shape; ``w`` is
+        ``[N, K]`` or, with ``b_mn``, ``[K, N]``.
         """
+        full_sym = x_full if isinstance(x_full, SymmTensor) else None
+        if full_sym is not None:
+            x_full = full_sym.t
         ms, k = x_shard.t.shape
         m = ms * self.world
         n = w.shape[1] if b_mn else w.shape[0]
@@ -174,7 +203,7 @@ class FusedCollectives:
             out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
         g = self._gemm_desc(x_full, w, out, b_mn=b_mn, bias=bias, resid=resid, aux=aux, epi=epi, M=m, N=n, K_=k)
         c = self._comm(COMM_GATHER_A, ms)
-        self._gather(c, x_shard, handshake)
+        self._gather(c, x_shard, handshake, full_sym)
         self._tick()
         K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(gather A)")
         return out
@@ -188,6 +217,9 @@ class FusedCollectives:
         The weight is sharded by output rows.  ``w_full`` ``[out, in]`` is local scratch that holds
         the gathered weight afterwards (a later GEMM of the same layer may reuse it).
         """
+        full_sym = w_full if isinstance(w_full, SymmTensor) else None
+        if full_sym is not None:
+            w_full = full_sym.t
         rows_s, cols = w_shard.t.shape
         rows = rows_s * self.world
         m = x.shape[0]
@@ -196,7 +228,7 @@ class FusedCollectives:
             out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
         g = self._gemm_desc(x, w_full, out, b_mn=dgrad, bias=bias, resid=resid, aux=aux, epi=epi, M=m, N=n, K_=k)
         c = self._comm(COMM_GATHER_B, rows_s)
-        self._gather(c, w_shard, handshake)
+        self._gather(c, w_shard, handshake, full_sym)
         self._tick()
         K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(gather B)")
         return out

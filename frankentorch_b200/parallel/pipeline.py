@@ -9,10 +9,16 @@ the protocol: every transfer is posted when the schedule reaches it (a send righ
 compute that produced it, a receive right before the compute that needs it), and when a send is
 directly followed by a receive from the same neighbour - the steady state of 1F1B, where two
 stages would otherwise both be sending first - the two are posted as one group
-(``batch_isend_irecv``).  Before anything is posted, :func:`check_pair_orders` replays the
-posting orders of a stage and its neighbours on the host and refuses a schedule in which two
-ranks would wait for each other.  Sends are only waited for at the end of the step, so they
-overlap the compute of the following micro-batches.
+(``batch_isend_irecv``).  EVERY transfer goes through ``batch_isend_irecv``, a lone one as a
+group of one: ProcessGroupNCCL runs grouped point-to-point operations on the group-wide
+communicator and ungrouped ones on a two-rank communicator of their own, and a send on one
+communicator never meets a receive on the other (a step that mixed the two forms ended in the
+process group's timeout).  On the group-wide communicator all of a rank's transfers, to either
+neighbour, run on one stream in posting order; before anything is posted,
+:func:`check_pair_orders` (each pair on its own) and :func:`check_fifo_orders` (one queue per
+rank over all its neighbours) replay the posting orders on the host and refuse a schedule in
+which ranks would wait for each other.  Sends are only waited for at the end of the step, so
+they overlap the compute of the following micro-batches.
 
 Schedule of one step with ``M`` micro-batches on stage ``r`` of ``W``:
 
@@ -129,6 +135,33 @@ def check_pair_orders(rank: int, world: int, n_micro: int, schedule: str) -> Non
             raise RuntimeError(f"pipeline schedule '{schedule}': unmatched transfers between stages {rank} and {peer}")
 
 
+def check_fifo_orders(world: int, n_micro: int, schedule: str) -> None:
+    """Replay the whole pipeline with ONE in-order queue of groups per rank (all neighbours together,
+    the way grouped point-to-point operations run on a group-wide NCCL communicator): the head groups
+    of all ranks are in flight, a transfer completes when the peer's head group holds its counterpart,
+    a group retires when all of its transfers have.  Raises ``RuntimeError`` when no head can progress."""
+    queues = [[set((k, p, w, m) for k, p, w, m in g) for g in comm_groups(r, world, n_micro, schedule)]
+              for r in range(world)]
+    while any(queues):
+        progress = False
+        for r in range(world):
+            if not queues[r]:
+                continue
+            for k, p, w, m in sorted(queues[r][0]):
+                other = ("recv" if k == "send" else "send", r, w, m)
+                if queues[p] and other in queues[p][0]:
+                    queues[r][0].discard((k, p, w, m))
+                    queues[p][0].discard(other)
+                    progress = True
+        for r in range(world):
+            while queues[r] and not queues[r][0]:
+                queues[r].pop(0)
+                progress = True
+        if not progress:
+            heads = {r: sorted(q[0]) for r, q in enumerate(queues) if q}
+            raise RuntimeError(f"pipeline schedule '{schedule}' would deadlock on in-order queues: heads {heads}")
+
+
 class GPipeStage:
     """One stage of a pipeline (GPipe or 1F1B order).
 
@@ -164,6 +197,7 @@ class GPipeStage:
         replayable; they differ in the order parameter gradients are summed."""
         tape, M = self.tape, n_micro
         check_pair_orders(self.rank, self.world, M, schedule)      # refuse an order that would hang, before posting
+        check_fifo_orders(self.world, M, schedule)
         groups = comm_groups(self.rank, self.world, M, schedule)
         order = stage_order(self.rank, self.world, M, schedule)
         self.last_order = order
@@ -188,11 +222,9 @@ class GPipeStage:
                 else:
                     ops.append(dist.P2POp(dist.isend, payloads.pop(key), self._peer(peer), self.group, tag))
                 keys.append(key)
-            if len(ops) == 1:
-                o = ops[0]
-                ws = [o.op(o.tensor, o.peer, o.group, o.tag)]
-            else:
-                ws = dist.batch_isend_irecv(ops)
+            # always as a group, also a lone transfer: grouped and ungrouped NCCL point-to-point
+            # operations use different communicators and never match each other
+            ws = dist.batch_isend_irecv(ops)
             for n, key in enumerate(keys):
                 works[key] = [ws[n]] if len(ws) == len(keys) else list(ws)   # a coalesced group has one handle
                 posted.add(key)

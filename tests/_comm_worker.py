@@ -39,6 +39,8 @@ def main():
     w_sh = SymmTensor.alloc((n // world, kdim), torch.bfloat16, dist.group.WORLD, dev)
     x_full = torch.empty((m, kdim), dtype=torch.bfloat16, device=dev)
     w_full = torch.empty((n, kdim), dtype=torch.bfloat16, device=dev)
+    x_stage = fc.staging((m, kdim))        # push form: peers store into these
+    w_stage = fc.staging((n, kdim))
 
     for it in range(3):                    # several epochs over the same flag arrays
         base = 1000 * it
@@ -53,6 +55,11 @@ def main():
         ref = torch.cat(xs).float() @ w.float().t() + bias.float()
         close(out, ref, f"gather-A epoch {it}", rank)
         assert torch.equal(x_full, torch.cat(xs)), "gathered activations differ"
+        # push form of the same op (the owners store their shards into every staging buffer)
+        out_p = fc.allgather_a_gemm(sh, w, x_stage[it & 1], bias=bias)
+        K.check_status()
+        assert torch.equal(out_p, out), "push and pull gathers give different products"
+        assert torch.equal(x_stage[it & 1].t, torch.cat(xs)), "pushed activations differ"
 
         # ---- all-gather(B) -> GEMM forward and dgrad, weight sharded by output rows
         ws = [rnd((n // world, kdim), base + 200 + r, dev) for r in range(world)]
@@ -69,6 +76,13 @@ def main():
         out = fc.allgather_b_gemm(dy, w_sh, w_full, dgrad=True)
         K.check_status()
         close(out, dy.float() @ wf, f"gather-B dgrad epoch {it}", rank)
+        out_p = fc.allgather_b_gemm(x, w_sh, w_stage[0])
+        K.check_status()
+        close(out_p, x.float() @ wf.t(), f"gather-B fwd (push) epoch {it}", rank)
+        assert torch.equal(w_stage[0].t, torch.cat(ws)), "pushed weights differ"
+        out_p = fc.allgather_b_gemm(dy, w_sh, w_stage[1], dgrad=True)
+        K.check_status()
+        assert torch.equal(out_p, out), "push and pull dgrad differ"
 
         # ---- GEMM -> reduce-scatter with bias and residual, bf16 and fp32-accumulate outputs
         a_all = [rnd((m, kdim), base + 500 + r, dev) for r in range(world)]

@@ -73,3 +73,16 @@ def test_pipeline_stages_over_nccl_match_a_single_process_run(cuda_device):
         pytest.skip("needs at least 2 GPUs")
     p = _run_workers("_pp_worker.py", 2, 29641, timeout=240)
     assert p.returncode == 0 and "PP_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]
+
+
+def test_multicast_collectives_match_nccl(cuda_device):
+    """multimem.st all-gather (bit-exact) and multimem.ld_reduce all-reduce (tolerance, same bits on every
+    rank and run) over a symmetric allocation bound to an NVSwitch multicast object."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    nproc = 2 if n < 4 else 4
+    p = _run_workers("_nvls_worker.py", nproc, 29643, timeout=240)
+    if "NVLS_WORKER_SKIP" in p.stdout:
+        pytest.skip("no multicast support on this system")
+    assert p.returncode == 0 and "NVLS_WORKER_OK" in p.stdout, p.stdout[-3000:] + p.stderr[-3000:]

@@ -134,3 +134,23 @@ def test_release_values_frees_a_micro_batch_but_keeps_ids():
     assert tape.release_values(lo, hi) == 2
     assert tape.value(y) is None and tape.value(w) is not None and tape.value(x) is not None
     assert len(tape) == hi
+
+
+def test_posting_orders_complete_on_one_in_order_queue_per_rank():
+    """Grouped NCCL transfers of a rank share one stream whatever the neighbour: the replay with one queue
+    per rank must drain for every schedule, and a hand-made bad order must be refused."""
+    from frankentorch_b200.parallel import pipeline as pp
+    for world in (2, 3, 4, 5):
+        for m in (1, 2, 4, 7):
+            for schedule in ("gpipe", "1f1b"):
+                pp.check_fifo_orders(world, m, schedule)
+    real = pp.comm_groups
+
+    def both_send_first(rank, world, n_micro, schedule):
+        return [[("send", 1 - rank, "act", 0)], [("recv", 1 - rank, "act", 0)]]
+    pp.comm_groups = both_send_first
+    try:
+        with pytest.raises(RuntimeError, match="deadlock"):
+            pp.check_fifo_orders(2, 1, "gpipe")
+    finally:
+        pp.comm_groups = real
