@@ -3,6 +3,7 @@ import datetime
 import multiprocessing as mp
 import os
 
+import pytest
 import torch
 import torch.distributed as dist
 
