@@ -2,7 +2,8 @@
 reference survey: ``run_e2e_matrix``, ``run_differential_report``, ``triage_forensics_failures``,
 ``build_failure_forensics_index``, ``check_reliability_budgets``, ``run_raptorq_durability_pipeline``,
 ``validate_phase2c_artifacts``, ``run_perf_slos``, ``check_perf_slos``, ``check_benchmark_regression``,
-``emit_packet_sidecar``).
+``emit_packet_sidecar``), plus ``emit_packet_contracts`` (per-packet contract table, fixture manifest and
+parity report, the counterpart of artifacts/phase2c/FT-P2C-00X/ in the reference).
 
     python -m frankentorch_b200.conformance.cli run_e2e_matrix --mode both --output e2e.jsonl
     python -m frankentorch_b200.conformance.cli run_differential_report --output diff.json
@@ -196,8 +197,22 @@ def validate_artifacts(args) -> int:
                 side = json.load(open(os.path.join(dirpath, f)))
                 if not os.path.exists(art) or hash_bytes(open(art, "rb").read()) != side["source_hash"]:
                     bad.append(art)
-    print(json.dumps({"passed": not bad, "stale_or_missing": bad}, indent=2))
-    return 0 if not bad else 1
+    from . import packets
+    contract_problems = packets.validate(args.root)
+    for sub in ("artifacts/phase2c", "phase2c"):
+        if os.path.isdir(os.path.join(args.root, sub)):
+            contract_problems += packets.validate(os.path.join(args.root, sub))
+    ok = not bad and not contract_problems
+    print(json.dumps({"passed": ok, "stale_or_missing": bad, "packet_contract_problems": contract_problems}, indent=2))
+    return 0 if ok else 1
+
+
+def emit_packet_contracts(args) -> int:
+    """Write the per-packet contract table, fixture manifest and parity report (both modes are run now)."""
+    from . import packets
+    written = packets.emit(args.output)
+    print(json.dumps({"written": len(written), "root": args.output, "problems": packets.validate(args.output)}, indent=2))
+    return 0
 
 
 def run_perf_slos_cmd(args) -> int:
@@ -270,6 +285,9 @@ def main(argv=None) -> int:
         p = sub.add_parser(name)
         p.add_argument("root", nargs="?", default=".")
         p.set_defaults(fn=validate_artifacts)
+    p = sub.add_parser("emit_packet_contracts")
+    p.add_argument("--output", default="artifacts/phase2c")
+    p.set_defaults(fn=emit_packet_contracts)
     p = sub.add_parser("run_perf_slos")
     p.add_argument("--profile", default="smoke", choices=["smoke", "full"])
     p.add_argument("--iterations", type=int, default=10)

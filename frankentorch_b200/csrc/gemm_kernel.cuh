@@ -310,6 +310,20 @@ __device__ __forceinline__ TileCoord decode_item(int item, const GemmArgs& p, co
 // reads own-shard tiles straight from the shard (second tensor map), and the staged copy of the
 // own chunk, which only serves later consumers of the gathered operand, is made by the other
 // warps of the copy CTAs with plain 16-byte loads and stores while the ring runs.
+//
+// Push form (c.push): the same ring, with the roles of the two sides exchanged.  Every rank stores
+// its OWN shard into every rank's staging buffer (bulk loads from local memory, bulk stores to the
+// peer's memory: stores are posted, so the ring is not bound by NVLink round trips the way peer
+// loads are) and publishes the piece's flag AT THE CONSUMER with a system-scope release, so that
+// consumers only ever poll their own memory.  The work list is destination-major in the order the
+// consumers need their chunks: rank P's data is the first remote chunk of rank P-1, the second of
+// P-2, ...; at any time each GPU sends one chunk to one peer and receives one chunk from one peer
+// at the full link rate, and a consumer's next chunk is complete after 1/(W-1) of the exchange.
+// The copy into this rank's own staging buffer comes first for weight gathers (tiles that
+// straddle two chunks wait for its flags) and last for activation gathers (the GEMM reads own
+// tiles from the shard; the staged copy only serves later kernels).  The caller alternates two
+// staging buffers between consecutive calls: a rank can be at most one collective ahead of a
+// peer, so the buffer it writes is never the one that peer still reads.
 __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const CommArgs& c,
                                             int epoch, int cta, bool own_last, const WaitCtx& ctx) {
   uint64_t* full = bars;
@@ -320,12 +334,21 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
   const uint32_t piece = c.sub_bytes < G_COPY_SLOT ? (uint32_t)c.sub_bytes : (uint32_t)G_COPY_SLOT;
   const int pps = (int)(c.sub_bytes / piece);          // pieces per subtile
   const int ppc = spc * pps;                           // pieces per chunk
-  const bool own_aside = own_last;
-  // pieces are numbered by distance from this rank: [0, ppc) is the own chunk
+  const bool push = c.push != 0;
+  const bool own_aside = own_last && !push;
+  // pieces are numbered by distance from this rank: [0, ppc) is the own chunk (pull), or by
+  // destination in the order the consumers need them (push)
   const int first = own_aside ? ppc : 0;
   const int n_pieces = ppc * c.world - first;
   const int mine = cta < n_pieces ? (n_pieces - cta + c.comm_ctas - 1) / c.comm_ctas : 0;
   auto rotated = [&](int i) { return first + (int)(((long long)cta + (long long)i * c.comm_ctas) % n_pieces); };
+  // piece number -> the rank whose memory is read (pull) / written (push)
+  auto other = [&](int q) {
+    const int dd = q / ppc;
+    if (!push) return (c.rank + dd) % c.world;
+    if (own_last) return dd == c.world - 1 ? c.rank : (c.rank - 1 - dd + 2 * c.world) % c.world;
+    return (c.rank - dd + c.world) % c.world;
+  };
   if (own_aside && threadIdx.x >= 96) {
     // own chunk: shard -> its place in the gathered operand, 8 vectors in flight per thread
     const long long nvec = (long long)ppc * piece / 16;
@@ -366,7 +389,7 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
           !mbar_wait(&empty[slot], (uint32_t)(((i / G_COPY_SLOTS) - 1) & 1), ctx, FT_ERR_WAIT_EMPTY))
         break;
       const int q = rotated(i);
-      const int chunk = (c.rank + q / ppc) % c.world;
+      const int chunk = push ? c.rank : other(q);
       if (c.ready_local && !((ready_seen >> chunk) & 1)) {
         if (!flag_wait<true>(c.ready_local + chunk, epoch, ctx)) break;
         ready_seen |= 1 << chunk;
@@ -386,15 +409,20 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
         break;
       }
       const int q = rotated(stored);
-      bulk_store(c.full + ((long long)((c.rank + q / ppc) % c.world) * ppc + q % ppc) * piece,
-                 smem + slot * G_COPY_SLOT, piece);
+      if (push)
+        bulk_store(c.full_peer[other(q)] + ((long long)c.rank * ppc + q % ppc) * piece, smem + slot * G_COPY_SLOT,
+                   piece);
+      else
+        bulk_store(c.full + ((long long)other(q) * ppc + q % ppc) * piece, smem + slot * G_COPY_SLOT, piece);
       bulk_wait_group_read<1>();                       // the previous store has read its slot
       if (stored > 0) mbar_arrive(&empty[(stored - 1) % G_COPY_SLOTS]);
       ++stored;
       bulk_wait_group<3>();                            // all but the newest three stores landed
+      if (push) fence_proxy_async_all();               // peer writes of the async proxy before the flag's release
       if (stored > 3) asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(progress)), "r"(stored - 3) : "memory");
     }
     bulk_wait_group<0>();
+    if (push) fence_proxy_async_all();
     asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(progress)), "r"(ok ? stored : -1) : "memory");
   } else if (threadIdx.x == 32) {
     // publisher: turns the driver's progress into per-piece flags.  It owns no copies in flight,
@@ -412,57 +440,12 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
       }
       for (; published < done; ++published) {
         const int q = rotated(published);
-        st_rel_gpu(c.sub_flags + ((c.rank + q / ppc) % c.world) * ppc + q % ppc, epoch);
+        if (push)
+          st_rel_sys(c.flags_peer[other(q)] + c.rank * ppc + q % ppc, epoch);
+        else
+          st_rel_gpu(c.sub_flags + other(q) * ppc + q % ppc, epoch);
       }
     }
-  }
-}
-
-// ------------------------------------------------------------------ comm CTAs: gather, push form
-// Every rank stores its own shard into every peer's staging buffer with plain 16-byte peer
-// stores and publishes one flag per piece AT THE CONSUMER, so that consumers only ever poll
-// their own memory.  The work list is destination-major in the order the consumers need their
-// chunks: rank P's data is the first remote chunk of rank P-1, the second of P-2, ...; at any
-// time each GPU sends one chunk to one peer and receives one chunk from one peer at the full
-// link rate, and a consumer's next chunk is complete after 1/(W-1) of the whole exchange.
-// Pieces are dealt round robin to all warps of the copy CTAs (CTA index fastest); a warp keeps
-// 8 x 512 bytes in flight.  The copy into this rank's own staging buffer comes first for weight
-// gathers (tiles that straddle two chunks wait for its flags) and last for activation gathers
-// (the GEMM reads own tiles from the shard; the staged copy only serves later kernels).
-// The caller alternates two staging buffers between consecutive calls: a rank can be at most
-// one collective ahead of a peer, so the buffer it writes is never the one that peer still reads.
-__device__ __forceinline__ void comm_gather_push(const CommArgs& c, int epoch, int cta, bool own_last) {
-  const int spc = c.chunk_rows / G_BM;
-  const uint32_t piece = c.sub_bytes < G_COPY_SLOT ? (uint32_t)c.sub_bytes : (uint32_t)G_COPY_SLOT;
-  const int pps = (int)(c.sub_bytes / piece);
-  const int ppc = spc * pps;
-  const int lane = threadIdx.x & 31;
-  const int n_warps = c.comm_ctas * (int)(blockDim.x >> 5);
-  const int gw = (int)(threadIdx.x >> 5) * c.comm_ctas + cta;
-  const int nv = (int)(piece >> 4);
-  const long long total = (long long)ppc * c.world;
-  for (long long j = gw; j < total; j += n_warps) {
-    const int d = (int)(j / ppc), q = (int)(j % ppc);
-    int dest;
-    if (own_last)
-      dest = d == c.world - 1 ? c.rank : (c.rank - 1 - d + 2 * c.world) % c.world;
-    else
-      dest = (c.rank - d + c.world) % c.world;
-    const uint4* src = reinterpret_cast<const uint4*>(c.src[c.rank] + (long long)q * piece);
-    uint4* dst = reinterpret_cast<uint4*>(c.full_peer[dest] + ((long long)c.rank * ppc + q) * piece);
-    for (int v0 = lane; v0 < nv; v0 += 32 * 8) {
-      uint4 u[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k)
-        if (v0 + k * 32 < nv) u[k] = __ldg(src + v0 + k * 32);
-#pragma unroll
-      for (int k = 0; k < 8; ++k)
-        if (v0 + k * 32 < nv) dst[v0 + k * 32] = u[k];
-    }
-    __threadfence_system();
-    __syncwarp();
-    if (lane == 0) st_rel_sys(c.flags_peer[dest] + c.rank * ppc + q, epoch);
-    __syncwarp();
   }
 }
 
@@ -636,8 +619,6 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       if (c.mode == FTK_COMM_SCATTER_D)
         comm_reduce<BN>(p, c, epoch, (int)blockIdx.x, (int)gridDim.x, (int)threadIdx.x, G_THREADS, ctx, wbar,
                         wbar_ph);
-      else if (c.push)
-        comm_gather_push(c, epoch, cta, /*own_last=*/c.mode == FTK_COMM_GATHER_A);
       else
         comm_gather(smem, bars, c, epoch, cta,
                     /*own_last=*/c.mode == FTK_COMM_GATHER_A, ctx);

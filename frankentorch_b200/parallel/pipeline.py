@@ -20,6 +20,15 @@ rank over all its neighbours) replay the posting orders on the host and refuse a
 which ranks would wait for each other.  Sends are only waited for at the end of the step, so
 they overlap the compute of the following micro-batches.
 
+NCCL sets up the connection of a (peer, direction) pair the first time a group uses it, with a
+HOST-side handshake that returns only when the peer's host sets up its end.  A schedule group
+such as "send activation 3 + receive gradient 3" would then hold back the send until the peer
+posts its first gradient send, which the peer reaches only after that very activation has
+arrived: the step would end in the process group's timeout.  So before its first step every
+stage exchanges one small tensor with each neighbour in both directions, all four transfers in
+one group that every rank posts at the same point (:func:`connect_neighbours`); afterwards no
+group waits for a connection.
+
 Schedule of one step with ``M`` micro-batches on stage ``r`` of ``W``:
 
   forward   m = 0..M-1 : recv activation (r > 0) -> stage_fn -> send activation (r < W-1)
@@ -162,6 +171,29 @@ def check_fifo_orders(world: int, n_micro: int, schedule: str) -> None:
             raise RuntimeError(f"pipeline schedule '{schedule}' would deadlock on in-order queues: heads {heads}")
 
 
+_CONNECTED = set()
+
+
+def connect_neighbours(rank: int, world: int, group: Optional[dist.ProcessGroup], device) -> None:
+    """Once per (group, device): a symmetric exchange of one element with the previous and the next stage,
+    both directions in one group, so that every point-to-point connection the schedules use exists
+    before a schedule group depends on it.  Collective over the stages (all call it at the same point)."""
+    key = (id(group) if group is not None else 0, str(device))
+    if key in _CONNECTED or world < 2 or dist.get_backend(group) == "gloo":
+        return
+    peer = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
+    keep, ops = [], []
+    for nb in (rank + 1, rank - 1):
+        if 0 <= nb < world:
+            out, inp = torch.zeros(1, device=device), torch.empty(1, device=device)
+            keep += [out, inp]
+            ops += [dist.P2POp(dist.isend, out, peer(nb), group), dist.P2POp(dist.irecv, inp, peer(nb), group)]
+    for w in dist.batch_isend_irecv(ops):
+        w.wait()
+    torch.cuda.synchronize(device)
+    _CONNECTED.add(key)
+
+
 class GPipeStage:
     """One stage of a pipeline (GPipe or 1F1B order).
 
@@ -198,6 +230,7 @@ class GPipeStage:
         tape, M = self.tape, n_micro
         check_pair_orders(self.rank, self.world, M, schedule)      # refuse an order that would hang, before posting
         check_fifo_orders(self.world, M, schedule)
+        connect_neighbours(self.rank, self.world, self.group, device)
         groups = comm_groups(self.rank, self.world, M, schedule)
         order = stage_order(self.rank, self.world, M, schedule)
         self.last_order = order

@@ -59,3 +59,29 @@ def test_durability_pipeline_and_validator(tmp_path):
     assert cli.main(["validate_artifacts", str(root)]) == 0
     (root / "golden.json").write_text("tampered")
     assert cli.main(["validate_artifacts", str(root)]) == 1
+
+
+def test_packet_contract_artifacts_are_emitted_and_validated(tmp_path):
+    """Each packet gets a contract table, a manifest pinning its golden cases and an all-pass parity report; the
+    validator notices a stale manifest and a missing contract row."""
+    import json
+
+    from frankentorch_b200.conformance import packets
+    root = str(tmp_path / "phase2c")
+    written = packets.emit(root)
+    assert len(written) == 3 * len(packets.CONTRACTS)
+    assert packets.validate(root) == []
+    rep = json.load(open(f"{root}/FT-P2C-004/parity_report.json"))
+    assert rep["passed"] and rep["modes"]["strict"]["cases"] == rep["modes"]["strict"]["passed"] > 0
+    man_path = f"{root}/FT-P2C-001/fixture_manifest.json"
+    man = json.load(open(man_path))
+    man["fixtures"][0]["sha256"] = "0" * 64
+    json.dump(man, open(man_path, "w"))
+    table = f"{root}/FT-P2C-009/contract_table.md"
+    open(table, "w").write(open(table).read().replace("`OPTIM-002`", "`OPTIM-00X`"))
+    problems = packets.validate(root)
+    assert any("FT-P2C-001" in p and "changed" in p for p in problems)
+    assert any("FT-P2C-009" in p and "OPTIM-002" in p for p in problems)
+    # the committed artifacts are current
+    here = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+    assert packets.validate(__import__("os").path.join(here, "artifacts", "phase2c")) == []
