@@ -67,7 +67,8 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-torch-arm", action="store_true",
-                    help="skip the interleaved stock-PyTorch arm (DDP for dp, FSDP for zero3) that fills vs_torch")
+                    help="skip the interleaved stock-PyTorch arm (DDP for dp, FSDP for zero3, Megatron-style TP for tp, "
+                         "all_to_all + bmm experts for ep) that fills vs_torch")
     ap.add_argument("--h2h-steps", type=int, default=5, help="optimizer steps per head-to-head sample")
     ap.add_argument("--log-jsonl", default="", help="append a structured ft-conformance-log-v1 record of this run")
     ap.add_argument("--parallelism", default="", choices=["", "dp", "tp", "zero3", "ep"],
@@ -439,12 +440,12 @@ def main():
 
     # ---------------- head to head with stock PyTorch, interleaved in the balanced-square slot order
     vs_torch = None
-    if not args.no_torch_arm and par in ("dp", "zero3") and preset in ("gpt2-small", "gpt2-medium", "gpt-tiny"):
+    if not args.no_torch_arm and preset in ("gpt2-small", "gpt2-medium", "gpt-1.3b", "gpt-tiny", "moe-12l", "moe-tiny"):
         from benchmarks.torch_baseline import TorchArm
         from frankentorch_b200 import harness as H
         try:
-            arm = TorchArm(preset, dev, world, rank, parallel="fsdp" if par == "zero3" else "ddp",
-                           micro_batch=mb, seq_len=seq)
+            arm = TorchArm(preset, dev, world, rank, micro_batch=mb, seq_len=seq,
+                           parallel={"dp": "ddp", "zero3": "fsdp", "tp": "tp", "ep": "ep"}[par])
             version = H.require_reported_version(arm.version_line())     # the arm reports it; no ratio without it
             for _ in range(3):
                 arm.step()
@@ -518,6 +519,8 @@ def main():
             "parallelism": ({"dp": "dp", "tp": "tp+sp", "zero3": "zero3-dp", "ep": "ep+dp"}[par] + str(world))
             if world > 1 else f"single ({par} code path)",
             "dp_impl": (args.dp_impl if world > 1 else None),
+            "dp_param_allgather": (("multimem stores through NVSwitch" if getattr(dp, "nvls_params", False)
+                                    else "peer stores") if dp is not None else None),
             "optimizer": "AdamW fp32 master + bf16 compute copy, grad clip 1.0",
             "cuda_graph": engine.use_graph,
             "l2": "no flush: one step streams >3 GB of activations, weights and optimizer state (L2 is 126 MB)",

@@ -104,20 +104,23 @@ def main():
     t_b = timeit(base_ag, args.iters, args.warmup, flush)
     report(f"allgather->gemm  x[{ms}x{d}]*{world} @ W[{n}x{d}]", t_f, t_b, 2.0 * m * n * d,
            (world - 1) * ms * d * 2)
-    # push form: two alternating symmetric staging buffers, the shards stored by their owners
+    # push form: two alternating symmetric staging buffers, the shards delivered by their owners, through
+    # the copy engines (deliveries queued on a second stream) or by copy CTAs inside the GEMM kernel
     stg = fc.staging((m, d))
     turn = [0]
 
     def push_ag():
         turn[0] ^= 1
         fc.allgather_a_gemm(xs, w, stg[turn[0]], out=out)
-    t_p = timeit(push_ag, args.iters, args.warmup, flush)
-    K.check_status()
     want = torch.matmul(x_full, w.t())
-    assert torch.equal(stg[turn[0]].t, x_full), "push gather staged other rows than the NCCL all-gather"
-    assert float((out.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
-    report(f"allgather->gemm (push)  x[{ms}x{d}]*{world} @ W[{n}x{d}]", t_p, t_b, 2.0 * m * n * d,
-           (world - 1) * ms * d * 2)
+    for transport, label in (("ce", "push, copy engines"), ("sm", "push, copy CTAs")):
+        fc.transport = transport
+        t_p = timeit(push_ag, args.iters, args.warmup, flush)
+        K.check_status()
+        assert torch.equal(stg[turn[0]].t, x_full), "push gather staged other rows than the NCCL all-gather"
+        assert float((out.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
+        report(f"allgather->gemm ({label})  x[{ms}x{d}]*{world} @ W[{n}x{d}]", t_p, t_b, 2.0 * m * n * d,
+               (world - 1) * ms * d * 2)
     del stg
 
     # ---- K13: GEMM -> reduce-scatter (row-parallel fc2 slice)
@@ -159,11 +162,13 @@ def main():
     def push_agw():
         turn[0] ^= 1
         fc.allgather_b_gemm(x3, ws, wstg[turn[0]], out=out3)
-    t_p = timeit(push_agw, args.iters, args.warmup, flush)
-    K.check_status()
-    assert torch.equal(wstg[turn[0]].t, w_full), "push gather staged other weights than the NCCL all-gather"
-    report(f"allgather(W)->gemm (push)  x[8192x{d3}] @ W[{n3}x{d3}]", t_p, t_b, 2.0 * 8192 * n3 * d3,
-           (world - 1) * (n3 // world) * d3 * 2)
+    for transport, label in (("ce", "push, copy engines"), ("sm", "push, copy CTAs")):
+        fc.transport = transport
+        t_p = timeit(push_agw, args.iters, args.warmup, flush)
+        K.check_status()
+        assert torch.equal(wstg[turn[0]].t, w_full), "push gather staged other weights than the NCCL all-gather"
+        report(f"allgather(W)->gemm ({label})  x[8192x{d3}] @ W[{n3}x{d3}]", t_p, t_b, 2.0 * 8192 * n3 * d3,
+               (world - 1) * (n3 // world) * d3 * 2)
 
     # ---- K14 / K16: MoE dispatch and combine (8 experts, top-2, capacity 1.25, d = 1024)
     T, dm, E = 8192, 1024, 8

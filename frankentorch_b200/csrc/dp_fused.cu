@@ -41,8 +41,11 @@
 // graph replays correctly) and are never cleared.  Every wait on a peer flag is bounded: when
 // the budget runs out the kernel records FT_ERR_WAIT_PEER in the status word, clears the step's
 // `ok` word and returns; the host raises (strict mode) or falls back to NCCL (hardened mode).
-// Plain acquire loads on peer-visible memory; no multimem / NVLS object is bound, so a peer
-// that exits between steps cannot fault the other GPUs.
+// Plain acquire loads on peer-visible memory.  Optionally (params_mc) the parameter arenas are
+// bound to one NVSwitch multicast address and dp_update broadcasts each updated bf16 value with a
+// single multimem.st (egress bytes per rank: its shard once, not W-1 times); everything else,
+// flags included, stays on ordinary peer stores.  Jobs that must survive a rank's exit run
+// without it: a process that dies bound to a multicast object can fault its peers' GPUs.
 //
 // The reference has no distributed training (docs/planning/FEATURE_PARITY.md:176); the sums'
 // fixed order carries its determinism contract (ft-autograd/src/lib.rs:20794-20819) across GPUs.
@@ -65,6 +68,7 @@ struct DpPeers {
   unsigned long long* flags[DP_MAX_RANKS]; // each rank's flag block: [3][DP_MAX_BUCKETS][DP_MAX_RANKS] u64
   float* slots[DP_MAX_RANKS];              // each rank's sumsq slots: [DP_MAX_RANKS] fp32
   const FtkDpBucket* buckets;              // local device table
+  __nv_bfloat16* params_mc;                // multicast address of the parameter arenas (NVLS), or null
   int rank, world, n_buckets;
 };
 
@@ -326,9 +330,17 @@ dp_update_kernel(DpPeers P, int b0, int b1, float* __restrict__ master, float* _
       uint2 o;
       o.x = pack_bf16(pp[0], pp[1]);
       o.y = pack_bf16(pp[2], pp[3]);
-      for (int j = 0; j < P.world; ++j) {   // all-gather: store into every rank's parameter arena
-        const int r = (P.rank + j) % P.world;
-        reinterpret_cast<uint2*>(P.params[r] + mine)[i] = o;
+      if (P.params_mc) {
+        // all-gather through the switch: one multimem store lands in every rank's parameter arena
+        asm volatile("multimem.st.relaxed.sys.global.v2.bf16x2 [%0], {%1, %2};" ::"l"(
+                         reinterpret_cast<uint2*>(P.params_mc + mine) + i),
+                     "r"(o.x), "r"(o.y)
+                     : "memory");
+      } else {
+        for (int j = 0; j < P.world; ++j) {   // all-gather: store into every rank's parameter arena
+          const int r = (P.rank + j) % P.world;
+          reinterpret_cast<uint2*>(P.params[r] + mine)[i] = o;
+        }
       }
     }
   }
@@ -397,6 +409,7 @@ static int fill_peers(const FtkDpComm* c, DpPeers* P) {
     P->slots[r] = reinterpret_cast<float*>(c->slots[r]);
   }
   P->buckets = c->buckets;
+  P->params_mc = reinterpret_cast<__nv_bfloat16*>(c->params_mc);
   P->rank = c->rank;
   P->world = c->world;
   P->n_buckets = c->n_buckets;

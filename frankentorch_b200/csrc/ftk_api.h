@@ -102,12 +102,16 @@ typedef struct FtkCommDesc {
   // gather, push form (push != 0): every rank stores its own shard into the staging buffer of every
   // peer and sets the flags there; the GEMM's staged operand (A or B) must be full_peer[rank] and
   // sub_flags must be flags_peer[rank].  Consecutive calls must alternate two staging buffers.
+  // push == 2: the shards are delivered from outside the kernel (ftk_copy_async + ftk_set_flags_sys on
+  // another stream, i.e. by the copy engines); the kernel has no copy CTAs and only polls the flags.
   int push;
   void* full_peer[FTK_MAX_RANKS];
   int* flags_peer[FTK_MAX_RANKS];
 } FtkCommDesc;
 int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* c, void* stream);
 int ftk_tick_i32(int* word, void* stream);    // *word += 1 on the stream
+int ftk_set_flags_sys(int* flags, int n, const int* epoch, void* stream);   // flags[0..n) = *epoch, release.sys
+int ftk_copy_async(void* dst, const void* src, long long bytes, void* stream);   // copy-engine D2D copy
 
 // ---- mixture of experts: top-2 routing and expert-parallel all-to-alls over peer memory ---
 // Expert e lives on rank e / (E / world).  A rank sends at most `capacity` rows to each expert;
@@ -301,6 +305,7 @@ typedef struct {
   int* ok_word;
   int* pending;
   float* hyper_pending;
+  void* params_mc;   // multicast address covering every rank's parameter arena (NVLS), or NULL
 } FtkDpComm;
 int ftk_dp_begin_step(const FtkDpComm* c, void* stream);
 int ftk_dp_bucket_reduce(const FtkDpComm* c, int bucket, const float* grads, int n_ctas, void* stream);

@@ -311,11 +311,12 @@ __device__ __forceinline__ TileCoord decode_item(int item, const GemmArgs& p, co
 // own chunk, which only serves later consumers of the gathered operand, is made by the other
 // warps of the copy CTAs with plain 16-byte loads and stores while the ring runs.
 //
-// Push form (c.push): the same ring, with the roles of the two sides exchanged.  Every rank stores
-// its OWN shard into every rank's staging buffer (bulk loads from local memory, bulk stores to the
-// peer's memory: stores are posted, so the ring is not bound by NVLink round trips the way peer
-// loads are) and publishes the piece's flag AT THE CONSUMER with a system-scope release, so that
-// consumers only ever poll their own memory.  The work list is destination-major in the order the
+// Push form (c.push): the roles of the two sides are exchanged.  Every rank stores its OWN shard
+// into every rank's staging buffer and publishes the piece's flag AT THE CONSUMER with a
+// system-scope release, so that consumers only ever poll their own memory.  The loader thread
+// fills the ring from local memory with bulk loads; one storer warp per slot drains it with plain
+// 16-byte peer stores, which are posted and so are not bound by NVLink round trips the way peer
+// loads are (bulk stores to a peer were measured at a quarter of the rate of these).  The work list is destination-major in the order the
 // consumers need their chunks: rank P's data is the first remote chunk of rank P-1, the second of
 // P-2, ...; at any time each GPU sends one chunk to one peer and receives one chunk from one peer
 // at the full link rate, and a consumer's next chunk is complete after 1/(W-1) of the exchange.
@@ -372,6 +373,47 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
     return;
   }
   uint64_t* empty = bars + G_COPY_SLOTS;
+  if (push && threadIdx.x >= 96) {
+    // push form, storer warps: one warp per ring slot (a warp that served several slots could meet a
+    // slot's barrier a whole phase early and take its parity for "complete").  Warp sw copies the pieces
+    // i = sw, sw + slots, ... from slot sw to the consumer's staging buffer with 16-byte peer stores
+    // (posted: no round trip), frees the slot and publishes the piece's flag at the consumer.
+    const int lane = threadIdx.x & 31, sw = (int)(threadIdx.x >> 5) - 3;
+    static_assert(G_THREADS / 32 - 3 >= G_COPY_SLOTS, "one storer warp per ring slot");
+    if (sw >= G_COPY_SLOTS) return;
+    const int nv = (int)(piece >> 4);
+    // A system-scope fence waits until the peer has acknowledged every store of the thread (microseconds
+    // over NVLink), so a slot is freed as soon as its bytes are in registers / on their way, and the
+    // flags of PUSH_BATCH pieces are published behind one fence.
+    constexpr int PUSH_BATCH = 4;
+    int* pend[PUSH_BATCH];
+    int n_pend = 0;
+    for (int i = sw; i < mine; i += G_COPY_SLOTS) {
+      const int slot = sw;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(&full[slot], (uint32_t)((i / G_COPY_SLOTS) & 1), ctx, FT_ERR_WAIT_FULL) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      __syncwarp();
+      if (!ok) return;
+      const int q = rotated(i);
+      const int dest = other(q);
+      const uint4* s4 = reinterpret_cast<const uint4*>(smem + slot * G_COPY_SLOT);
+      uint4* d4 = reinterpret_cast<uint4*>(c.full_peer[dest] + ((long long)c.rank * ppc + q % ppc) * piece);
+#pragma unroll 8
+      for (int v = lane; v < nv; v += 32) d4[v] = s4[v];
+      __syncwarp();                                   // every lane has read its part of the slot
+      if (lane == 0) mbar_arrive(&empty[slot]);
+      pend[n_pend++] = c.flags_peer[dest] + c.rank * ppc + q % ppc;
+      if (n_pend == PUSH_BATCH || i + G_COPY_SLOTS >= mine) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0)
+          for (int k = 0; k < n_pend; ++k) st_rel_sys(pend[k], epoch);
+        n_pend = 0;
+      }
+    }
+    return;
+  }
   if (threadIdx.x == 0) {
     // loader: peer (or own) memory -> ring slot.  It never waits for a store to land, only for
     // the slot's previous contents to have been read out, so up to G_COPY_SLOTS loads are in
@@ -397,7 +439,7 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
       mbar_arrive_expect_tx(&full[slot], piece);
       bulk_load(smem + slot * G_COPY_SLOT, c.src[chunk] + (long long)(q % ppc) * piece, piece, &full[slot]);
     }
-  } else if (threadIdx.x == 64) {
+  } else if (!push && threadIdx.x == 64) {
     // storer: ring slot -> the gathered operand in this GPU's memory; frees a slot once its store
     // has read it and advances the progress word once stores have landed
     int stored = 0;
@@ -409,22 +451,16 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
         break;
       }
       const int q = rotated(stored);
-      if (push)
-        bulk_store(c.full_peer[other(q)] + ((long long)c.rank * ppc + q % ppc) * piece, smem + slot * G_COPY_SLOT,
-                   piece);
-      else
-        bulk_store(c.full + ((long long)other(q) * ppc + q % ppc) * piece, smem + slot * G_COPY_SLOT, piece);
+      bulk_store(c.full + ((long long)other(q) * ppc + q % ppc) * piece, smem + slot * G_COPY_SLOT, piece);
       bulk_wait_group_read<1>();                       // the previous store has read its slot
       if (stored > 0) mbar_arrive(&empty[(stored - 1) % G_COPY_SLOTS]);
       ++stored;
       bulk_wait_group<3>();                            // all but the newest three stores landed
-      if (push) fence_proxy_async_all();               // peer writes of the async proxy before the flag's release
       if (stored > 3) asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(progress)), "r"(stored - 3) : "memory");
     }
     bulk_wait_group<0>();
-    if (push) fence_proxy_async_all();
     asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(progress)), "r"(ok ? stored : -1) : "memory");
-  } else if (threadIdx.x == 32) {
+  } else if (!push && threadIdx.x == 32) {
     // publisher: turns the driver's progress into per-piece flags.  It owns no copies in flight,
     // so its release stores never wait behind the ring.
     int published = 0;
@@ -440,10 +476,7 @@ __device__ __forceinline__ void comm_gather(uint8_t* smem, uint64_t* bars, const
       }
       for (; published < done; ++published) {
         const int q = rotated(published);
-        if (push)
-          st_rel_sys(c.flags_peer[other(q)] + c.rank * ppc + q % ppc, epoch);
-        else
-          st_rel_gpu(c.sub_flags + other(q) * ppc + q % ppc, epoch);
+        st_rel_gpu(c.sub_flags + other(q) * ppc + q % ppc, epoch);
       }
     }
   }

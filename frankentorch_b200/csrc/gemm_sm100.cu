@@ -32,10 +32,24 @@ splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ D, long lo
   const long long total4 = (M * N) >> 2;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += stride) {
-    float4 s = reinterpret_cast<const float4*>(ws)[i];
-    for (int k = 1; k < splits; ++k) {
-      const float4 t = reinterpret_cast<const float4*>(ws + (long long)k * M * N)[i];
-      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    // all partials of the element are requested before the first add (one memory latency, not `splits`);
+    // the adds stay in ascending split order
+    constexpr int U = 8;
+    float4 t[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k)
+      if (k < splits) t[k] = __ldcg(reinterpret_cast<const float4*>(ws + (long long)k * M * N) + i);
+    float4 s = t[0];
+#pragma unroll
+    for (int k = 1; k < U; ++k)
+      if (k < splits) { s.x += t[k].x; s.y += t[k].y; s.z += t[k].z; s.w += t[k].w; }
+    for (int k0 = U; k0 < splits; k0 += U) {
+#pragma unroll
+      for (int k = 0; k < U; ++k)
+        if (k0 + k < splits) t[k] = __ldcg(reinterpret_cast<const float4*>(ws + (long long)(k0 + k) * M * N) + i);
+#pragma unroll
+      for (int k = 0; k < U; ++k)
+        if (k0 + k < splits) { s.x += t[k].x; s.y += t[k].y; s.z += t[k].z; s.w += t[k].w; }
     }
     const long long e = i << 2;
     const long long r = e / N, c = e - r * N;
@@ -213,6 +227,27 @@ static void fill_gemm_args(GemmArgs& a, const FtkGemmDesc* g, int L0, int L1) {
 
 using namespace ftk;
 
+// flags[0..n) = *epoch with system-scope release stores (the flags may live on another GPU); launched
+// behind the copy whose arrival they announce, on the same stream.
+__global__ void set_flags_sys_kernel(int* flags, int n, const int* __restrict__ epoch) {
+  const int e = *epoch;
+  __threadfence_system();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags + i), "r"(e) : "memory");
+}
+extern "C" int ftk_set_flags_sys(int* flags, int n, const int* epoch, void* stream_v) {
+  if (!flags || !epoch || n <= 0) return -2;
+  // one warp: it must find room on an SM beside a resident GEMM CTA (the consumer that waits for these flags)
+  set_flags_sys_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(flags, n, epoch);
+  return (int)cudaGetLastError();
+}
+// One device-to-device copy on a stream (local or peer destination): the copy engines move it, no SM is used.
+extern "C" int ftk_copy_async(void* dst, const void* src, long long bytes, void* stream_v) {
+  if (!dst || !src || bytes <= 0) return -2;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice,
+                              reinterpret_cast<cudaStream_t>(stream_v));
+}
+
 extern "C" int ftk_tick_i32(int* word, void* stream_v) {
   if (!word) return -2;
   tick_i32_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(word);
@@ -355,8 +390,10 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   // gathers: CTAs that only move data (default 20); reduce-scatter: every CTA reduces after its
   // GEMM tiles, dedicated CTAs are optional (default none)
   c.comm_ctas = cd->comm_ctas > 0 ? cd->comm_ctas : (cd->mode == FTK_COMM_SCATTER_D ? 0 : 20);
-  if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D && cd->push) {
-    c.comm_ctas = 16;   // stores are posted: a few CTAs keep the link full
+  if (cd->mode != FTK_COMM_SCATTER_D && cd->push == 2) {
+    c.comm_ctas = 0;    // the shards arrive by copy engine: every CTA multiplies, the producers poll the flags
+  } else if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D && cd->push) {
+    c.comm_ctas = 16;
   } else if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D) {
     // Split the SMs between copying and computing in proportion to the work: a copy CTA keeps
     // 128 KB of peer loads in flight, which at NVLink latency under load is ~13 GB/s (measured

@@ -136,8 +136,16 @@ __global__ void __launch_bounds__(256) nvls_allgather_kernel(NvlsArgs a, const u
   if (ok) {
     char* dst = a.mc + dst_off + (long long)a.rank * n16 * 16;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride)
-      mm_st16(dst + i * 16, src[i]);
+    constexpr int U = 8;                              // loads in flight per thread
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n16; i0 += U * stride) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < n16) v[u] = __ldcs(src + i0 + u * stride);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < n16) mm_st16(dst + (i0 + u * stride) * 16, v[u]);
+    }
   }
   nv_leave(a, 1, seq);
 }
@@ -152,9 +160,19 @@ __global__ void __launch_bounds__(256) nvls_allreduce_kernel(NvlsArgs a, long lo
     const long long hi = lo + per < n16 ? lo + per : n16;
     char* p = a.mc + off;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += stride) {
-      const uint4 v = kBf16 ? mm_ld_reduce_bf16x8(p + i * 16) : mm_ld_reduce_f32x4(p + i * 16);
-      mm_st16(p + i * 16, v);
+    constexpr int U = 4;                              // switch-side reductions in flight per thread
+    for (long long i0 = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < hi; i0 += U * stride) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < hi) v[u] = kBf16 ? mm_ld_reduce_bf16x8(p + i * 16) : mm_ld_reduce_f32x4(p + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < hi) mm_st16(p + i * 16, v[u]);
+      }
     }
   }
   nv_leave(a, 3, seq);

@@ -196,9 +196,11 @@ norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 // ----------------------------------------------------------------------------- LayerNorm bwd, one pass
 // dx and the per-block column partials of dgamma / dbeta from a single read of dy and x.
 // A CTA of 8 warps owns LNB_ROWS consecutive rows; warp w takes rows w, w + 8, ... in ascending
-// order, keeps the row in registers (packed bf16), and adds dy*xhat / dy into per-lane column
-// accumulators.  The 8 warps then add their accumulators into shared memory one after the
-// other (fixed order) and the CTA writes partial[blk][c].  NV = 16-byte vectors per lane.
+// order.  The loads of a warp's next row are issued before the arithmetic of the current one
+// (register double buffer), so a warp always has a row in flight; gamma is read from shared
+// memory.  Per-lane column accumulators of dy*xhat / dy are added over the 8 warps in warp order
+// through one shared-memory pass per quantity (layout [warp][i][vector]: conflict-free both ways)
+// and the CTA writes partial[blk][c].  NV = 16-byte vectors per lane.
 constexpr int LNB_ROWS = 32;
 template <int NV>
 __global__ void __launch_bounds__(ROW_WARPS * 32, 2)
@@ -207,32 +209,45 @@ ln_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dx_add,
                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int cols,
                     int nblk) {
-  __shared__ float sg[NV * 256], sb[NV * 256];
+  constexpr int VEC = NV * 32;                      // vectors of a (padded) row
+  __shared__ float red[ROW_WARPS][8 * VEC];
+  __shared__ uint4 sgam[VEC];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = cols >> 3;
-  const uint4* gv = reinterpret_cast<const uint4*>(gamma);
-  uint4 gp[NV];
+  for (int v = threadIdx.x; v < VEC; v += blockDim.x)
+    sgam[v] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(gamma) + v) : make_uint4(0u, 0u, 0u, 0u);
   float dg[NV][8], db[NV][8];
 #pragma unroll
-  for (int j = 0; j < NV; ++j) {
-    const int v = lane + 32 * j;
-    gp[j] = v < nvec ? __ldg(gv + v) : make_uint4(0u, 0u, 0u, 0u);
+  for (int j = 0; j < NV; ++j)
 #pragma unroll
     for (int i = 0; i < 8; ++i) dg[j][i] = db[j][i] = 0.f;
-  }
-  for (int rr = 0; rr < LNB_ROWS / ROW_WARPS; ++rr) {
-    const int row = blockIdx.x * LNB_ROWS + rr * ROW_WARPS + warp;
-    if (row >= rows) break;
+  const int row0 = blockIdx.x * LNB_ROWS + warp;
+  const int row_end = min(rows, (int)(blockIdx.x + 1) * LNB_ROWS);
+  uint4 xn[NV], dn[NV];
+  float mean_n = 0.f, rstd_n = 0.f;
+  auto fetch = [&](int row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * cols);
     const uint4* dr = reinterpret_cast<const uint4*>(dy + (size_t)row * cols);
-    uint4 xp[NV], dp[NV];
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int v = lane + 32 * j;
-      xp[j] = v < nvec ? xr[v] : make_uint4(0u, 0u, 0u, 0u);
-      dp[j] = v < nvec ? dr[v] : make_uint4(0u, 0u, 0u, 0u);
+      xn[j] = v < nvec ? __ldcs(xr + v) : make_uint4(0u, 0u, 0u, 0u);
+      dn[j] = v < nvec ? __ldcs(dr + v) : make_uint4(0u, 0u, 0u, 0u);
     }
-    const float mean = mean_in[row], rstd = rstd_in[row];
+    mean_n = __ldg(mean_in + row);
+    rstd_n = __ldg(rstd_in + row);
+  };
+  if (row0 < row_end) fetch(row0);
+  __syncthreads();                                  // gamma is in shared memory
+  for (int row = row0; row < row_end; row += ROW_WARPS) {
+    uint4 xp[NV], dp[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      xp[j] = xn[j];
+      dp[j] = dn[j];
+    }
+    const float mean = mean_n, rstd = rstd_n;
+    if (row + ROW_WARPS < row_end) fetch(row + ROW_WARPS);     // in flight during this row's arithmetic
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -240,7 +255,7 @@ ln_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
         float fx[8], fd[8], g[8];
         unpack8(xp[j], fx);
         unpack8(dp[j], fd);
-        unpack8(gp[j], g);
+        unpack8(sgam[lane + 32 * j], g);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float gd = g[i] * fd[i];
@@ -263,7 +278,7 @@ ln_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
         float fx[8], fd[8], g[8], a[8];
         unpack8(xp[j], fx);
         unpack8(dp[j], fd);
-        unpack8(gp[j], g);
+        unpack8(sgam[v], g);
         if (av) unpack8(av[v], a);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -275,29 +290,26 @@ ln_bwd_fused_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
       }
     }
   }
-  // warps add their column accumulators in warp order
-  for (int w = 0; w < ROW_WARPS; ++w) {
-    if (warp == w) {
-#pragma unroll
-      for (int j = 0; j < NV; ++j) {
-        const int v = lane + 32 * j;
-        if (v < nvec) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int c = v * 8 + i;
-            sg[c] = w == 0 ? dg[j][i] : sg[c] + dg[j][i];
-            sb[c] = w == 0 ? db[j][i] : sb[c] + db[j][i];
-          }
-        }
-      }
-    }
-    __syncthreads();
-  }
+  // the 8 warps' column accumulators, added in warp order: dgamma first, then dbeta
   float* pg = partial + (size_t)blockIdx.x * cols;
   float* pb = partial + ((size_t)nblk + blockIdx.x) * cols;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    pg[c] = sg[c];
-    pb[c] = sb[c];
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    if (pass) __syncthreads();                      // the sums of pass 0 have been read
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) red[warp][i * VEC + lane + 32 * j] = pass ? db[j][i] : dg[j][i];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 8 * VEC; idx += blockDim.x) {
+      const int i = idx / VEC, v = idx - i * VEC;
+      if (v < nvec) {
+        float t = red[0][idx];
+#pragma unroll
+        for (int w = 1; w < ROW_WARPS; ++w) t += red[w][idx];
+        (pass ? pb : pg)[v * 8 + i] = t;
+      }
+    }
   }
 }
 

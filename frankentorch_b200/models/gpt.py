@@ -68,7 +68,7 @@ class ParamArena:
     ALIGN = 128  # elements
 
     def __init__(self, specs: List[Tuple[str, Tuple[int, ...]]], device, *, group=None, pad_multiple: int = 1024,
-                 peer_visible: bool = False):
+                 peer_visible: bool = False, multicast_params: bool = False):
         self.specs = specs
         self.offsets: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
         off = 0
@@ -81,7 +81,8 @@ class ParamArena:
         self.symmetric = group is not None or peer_visible   # (a one-rank job can use the peer kernels too)
         if self.symmetric:
             from ..parallel.symm import SymmetricBuffer
-            self.params_buf = SymmetricBuffer(off * 2, group, device)
+            self.params_buf = (self._multicast_params(off * 2, group, device) if multicast_params else None) or \
+                SymmetricBuffer(off * 2, group, device)
             self.grads_buf = SymmetricBuffer(off * 4, group, device)
             self.params = self.params_buf.tensor(torch.bfloat16, off)
             self.grads = self.grads_buf.tensor(torch.float32, off)
@@ -93,6 +94,29 @@ class ParamArena:
         self.master = torch.zeros(off, dtype=torch.float32, device=device)
         self.m = torch.zeros(off, dtype=torch.float32, device=device)
         self.v = torch.zeros(off, dtype=torch.float32, device=device)
+
+    @staticmethod
+    def _multicast_params(nbytes: int, group, device):
+        """The parameter arena as a multicast (NVLS) buffer when ``FT_DP_NVLS`` asks for it (``1``, or ``auto`` =
+        jobs of four or more ranks) and the system offers a multicast address; None otherwise.  The
+        data-parallel update then broadcasts the new bf16 parameters with one multimem store per value."""
+        import os
+        want = os.environ.get("FT_DP_NVLS", "auto")
+        if group is None or want == "0":
+            return None
+        import torch.distributed as dist
+        world = dist.get_world_size(group)
+        if world < 2 or (want == "auto" and world < 4) or torch.device(device).type != "cuda":
+            return None
+        try:
+            from ..parallel.nvls import MulticastBuffer
+            buf = MulticastBuffer(nbytes, group, device)
+        except Exception:       # no symmetric-memory support in this build / on this system: peer stores
+            buf = None
+        # every rank takes the same path: one that could not bind the object sends all back to peer stores
+        ok = torch.tensor([1 if (buf is not None and buf.has_multicast) else 0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        return buf if int(ok) == 1 else None
 
     def slot_end(self, name: str) -> int:
         """One past the last arena element of the (128-aligned) slot of parameter ``name``."""
@@ -140,7 +164,7 @@ class GPT:
             import torch.distributed as dist
             world = dist.get_world_size(group)
         self.arena = ParamArena(specs, self.device, group=group, pad_multiple=1024 * world,
-                                peer_visible=peer_visible)
+                                peer_visible=peer_visible, multicast_params=True)
         # the embeddings' gradients are complete only when the backward pass ends (the token table is
         # also the LM head): they form one bucket of their own
         self.arena.bucket_cuts.append(self.arena.slot_end("wpe.weight"))

@@ -106,6 +106,9 @@ def load(build_if_missing: bool = True):
     lib.ftk_gemm_plan.restype = C.c_int
     lib.ftk_gemm_comm_bf16.argtypes = [C.POINTER(FtkGemmDesc), C.POINTER(FtkCommDesc), C.c_void_p]
     lib.ftk_tick_i32.argtypes = [C.c_void_p, C.c_void_p]
+    lib.ftk_set_flags_sys.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    lib.ftk_copy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]
+    lib.ftk_set_flags_sys.restype = lib.ftk_copy_async.restype = C.c_int
     lib.ftk_attn_fwd.argtypes = [C.POINTER(FtkAttnDesc), C.c_void_p]
     lib.ftk_attn_bwd.argtypes = [C.POINTER(FtkAttnDesc), C.c_void_p]
     vp, i, f, ll, ull = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_ulonglong

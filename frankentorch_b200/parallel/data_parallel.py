@@ -142,7 +142,7 @@ class _Comm(C.Structure):
                 ("wire_fp32", C.c_int),
                 ("gshard", C.c_void_p), ("partial", C.c_void_p), ("counters", C.c_void_p),
                 ("seq", C.c_void_p), ("ok_word", C.c_void_p), ("pending", C.c_void_p),
-                ("hyper_pending", C.c_void_p)]
+                ("hyper_pending", C.c_void_p), ("params_mc", C.c_void_p)]
 
 
 def _bind(lib):
@@ -245,7 +245,10 @@ class FusedDataParallel:
                            self.bucket_dev.data_ptr(), self.rank, self.world, nb, self.ctas_tail,
                            1 if wire == "fp32" else 0, self.gshard.data_ptr(), self.partial.data_ptr(),
                            self.counters.data_ptr(), self.seq_dev.data_ptr(), self.ok_dev.data_ptr(),
-                           self.pending_dev.data_ptr(), self.hyper_pending.data_ptr())
+                           self.pending_dev.data_ptr(), self.hyper_pending.data_ptr(),
+                           int(getattr(arena.params_buf, "mc_ptr", 0) or 0) or None)
+        # True when the updated parameters are broadcast with multimem stores through NVSwitch
+        self.nvls_params = bool(getattr(arena.params_buf, "mc_ptr", 0))
         self.comm_stream = torch.cuda.Stream(device=device)
         self._opt: Optional[Tuple[float, float, float, float]] = None   # (beta1, beta2, eps, weight_decay)
         # bucket completion tracking (host side, drives the launches while a step is recorded)

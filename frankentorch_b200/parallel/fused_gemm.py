@@ -10,8 +10,13 @@ few CTAs move data between GPUs while the rest multiply:
   (``x W^T``) and dgrad (``dy W``, weight sharded along the reduction dimension);
   Both gathers have two forms: the *pull* form (staging buffer in ordinary local memory; copy CTAs
   fetch the peers' shards) and the *push* form (staging buffer in symmetric memory, passed as a
-  :class:`SymmTensor`: every rank stores its own shard into all peers' staging buffers in the
-  order the consumers need them, and consumers poll flags in their own memory only);
+  :class:`SymmTensor`: every rank delivers its own shard into all peers' staging buffers in the
+  order the consumers need them, and consumers poll flags in their own memory only).  The push
+  form has two transports (``FT_GATHER_TRANSPORT``): ``ce`` (default) enqueues the deliveries as
+  device-to-device copies on a second stream, each followed by a one-block kernel that sets the
+  arrival flags at the consumer, so the copy engines move the bytes at the full NVLink rate and
+  all SMs multiply; ``sm`` moves them with copy CTAs inside the GEMM kernel (a handful of SMs
+  cannot keep NVLink full: 8-17 GB/s per copy CTA measured, whatever the instruction mix);
 * :meth:`FusedCollectives.gemm_reduce_scatter` - the epilogue stores bf16 partial tiles into the
   owning rank's inbox and the owner adds them in ascending rank order (row-parallel Linear,
   ZeRO-3 weight-gradient reduce-scatter).
@@ -101,6 +106,9 @@ class FusedCollectives:
             self.inbox = SymmetricBuffer(3 * max_inbox_elems * 2, group, device)
         self._slot = 0
         self._first = True
+        self.transport = os.environ.get("FT_GATHER_TRANSPORT", "ce")
+        self.ce_parts = max(1, int(os.environ.get("FT_GATHER_CE_PARTS", "4")))   # copies per (chunk, destination)
+        self.comm_stream = torch.cuda.Stream(device=device)
         torch.cuda.synchronize(device)
         if self.world > 1:
             dist.barrier(group=group)
@@ -165,7 +173,7 @@ class FusedCollectives:
             n_flags = c.chunk_rows // TILE_M * self.world * max(1, TILE_M * row_bytes // 32768)
             if n_flags > self.sub_flags.numel():
                 raise K.KernelError("gathered operand needs more flag words than were allocated")
-            c.push = 1
+            c.push = 2 if self.transport == "ce" else 1
             c.sub_flags = self.gflags.local_ptr
             for r in range(self.world):
                 c.full_peer[r] = full.peer_ptrs[r]
@@ -182,6 +190,40 @@ class FusedCollectives:
             c.ready_local = self.flags.local_ptr
             for r in range(self.world):
                 c.ready_peer[r] = self.flags.peer_ptrs[r] + 4 * self.rank
+
+    def _ce_deliver(self, shard: SymmTensor, full: SymmTensor, own_last: bool):
+        """Copy-engine transport of the push form: on the communication stream, behind everything the launching
+        stream has queued so far (the shard is final, the epoch is ticked), copy this rank's shard into every
+        rank's staging buffer - destinations in the order they will need it, each chunk in ``ce_parts`` copies -
+        and set the arrival flags of each part at its consumer.  Returns the event the launching stream must
+        wait for after the GEMM (the shard may then be rewritten, the own staged copy is complete)."""
+        main, cs = torch.cuda.current_stream(self.device), self.comm_stream
+        ev = torch.cuda.Event()
+        ev.record(main)
+        cs.wait_event(ev)
+        rows, cols = shard.t.shape
+        row_bytes = cols * 2
+        piece = min(TILE_M * row_bytes, 32768)
+        chunk_bytes = rows * row_bytes
+        ppc = chunk_bytes // piece
+        W, r = self.world, self.rank
+        if own_last:
+            dests = [(r - 1 - d) % W for d in range(W - 1)] + [r]
+        else:
+            dests = [r] + [(r - d) % W for d in range(1, W)]
+        parts = min(self.ce_parts, ppc)
+        bounds = [ppc * k // parts for k in range(parts + 1)]
+        src, lib, raw = shard.peer_ptrs[r], self.lib, C.c_void_p(cs.cuda_stream)
+        for dest in dests:
+            for k in range(parts):
+                p0, p1 = bounds[k], bounds[k + 1]
+                K._chk(lib.ftk_copy_async(full.peer_ptrs[dest] + r * chunk_bytes + p0 * piece, src + p0 * piece,
+                                          (p1 - p0) * piece, raw), "ftk_copy_async")
+                K._chk(lib.ftk_set_flags_sys(self.gflags.peer_ptrs[dest] + 4 * (r * ppc + p0), p1 - p0,
+                                             self.epoch.data_ptr(), raw), "ftk_set_flags_sys")
+        done = torch.cuda.Event()
+        done.record(cs)
+        return done
 
     # ------------------------------------------------------------------ all-gather -> GEMM (A)
     def allgather_a_gemm(self, x_shard: SymmTensor, w: torch.Tensor, x_full: torch.Tensor, *,
@@ -205,7 +247,10 @@ class FusedCollectives:
         c = self._comm(COMM_GATHER_A, ms)
         self._gather(c, x_shard, handshake, full_sym)
         self._tick()
+        done = self._ce_deliver(x_shard, full_sym, own_last=True) if c.push == 2 else None
         K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(gather A)")
+        if done is not None:
+            torch.cuda.current_stream(self.device).wait_event(done)
         return out
 
     # ------------------------------------------------------------------ all-gather -> GEMM (B)
@@ -230,7 +275,10 @@ class FusedCollectives:
         c = self._comm(COMM_GATHER_B, rows_s)
         self._gather(c, w_shard, handshake, full_sym)
         self._tick()
+        done = self._ce_deliver(w_shard, full_sym, own_last=False) if c.push == 2 else None
         K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(gather B)")
+        if done is not None:
+            torch.cuda.current_stream(self.device).wait_event(done)
         return out
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter

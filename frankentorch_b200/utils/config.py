@@ -46,6 +46,8 @@ ENV_FLAGS: Dict[str, EnvFlag] = {f.name: f for f in (
             "thread width of the CPU reference kernels: unset = serial, 'auto' = min(16, physical cores), or a count"),
     EnvFlag("FT_DP_OVERLAP", True, _bool, "start each gradient bucket's reduction under the backward pass"),
     EnvFlag("FT_DP_DEFER", True, _bool, "run the sharded AdamW + parameter all-gather under the next forward pass"),
+    EnvFlag("FT_DP_NVLS", "auto", str, "data-parallel parameter all-gather through NVSwitch multimem stores: 0, 1, or "
+            "auto (jobs of four or more ranks, where the system offers a multicast object)"),
     EnvFlag("FT_DP_WIRE", "bf16", str, "gradient type on NVLink for the fused data-parallel path: bf16 or fp32"),
     EnvFlag("FT_DP_BUCKET_MB", 0.0, float, "gradient bucket size in MB of bf16 (0 = 32)"),
     EnvFlag("FT_DP_CTAS", 296, int, "CTAs of a bucket's push / reduce kernels while the backward pass runs"),

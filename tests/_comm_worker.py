@@ -44,6 +44,8 @@ def main():
 
     for it in range(3):                    # several epochs over the same flag arrays
         base = 1000 * it
+        # push form: copy-engine deliveries in epochs 0 and 2, copy CTAs inside the kernel in epoch 1
+        fc.transport = "sm" if it == 1 else "ce"
         # ---- all-gather(A) -> GEMM, ranks hold different weights (column-parallel)
         xs = [rnd((ms, kdim), base + r, dev) for r in range(world)]
         w = rnd((n, kdim), base + 100 + rank, dev)
@@ -103,6 +105,24 @@ def main():
         fc.gemm_reduce_scatter(a_all[rank], b_all[rank], out2, resid=resid)
         K.check_status()
         assert torch.equal(out, out2), "reduce-scatter is not bit-reproducible"
+
+    # one copy CTA: its ring of six slots wraps (every slot is reused, phases flip) in both forms
+    fc1 = FusedCollectives(dist.group.WORLD, dev, comm_ctas=1)
+    fc1.transport = "sm"
+    stage1 = fc1.staging((m, kdim))
+    for it in range(2):
+        xs = [rnd((ms, kdim), 9000 + 10 * it + r, dev) for r in range(world)]
+        w = rnd((n, kdim), 9100 + it, dev)
+        sh = x_sh[it & 1]
+        sh.t.copy_(xs[rank])
+        ref = torch.cat(xs).float() @ w.float().t()
+        out = fc1.allgather_a_gemm(sh, w, x_full)
+        K.check_status()
+        close(out, ref, f"gather-A one copy CTA (pull) {it}", rank)
+        out = fc1.allgather_a_gemm(sh, w, stage1[it & 1])
+        K.check_status()
+        close(out, ref, f"gather-A one copy CTA (push) {it}", rank)
+        assert torch.equal(stage1[it & 1].t, torch.cat(xs)), "pushed activations differ (one copy CTA)"
 
     torch.cuda.synchronize()
     dist.barrier()

@@ -37,8 +37,12 @@ def main():
     runs = (("nccl", False, {}), ("fused", False, small), ("fused", True, small),
             ("fused1", True, dict(bucket_elems=1 << 40, overlap=False)),
             ("fused32", True, dict(bucket_elems=40_000, wire="fp32")),
-            ("fused_now", True, dict(bucket_elems=40_000, defer_update=False)))
+            ("fused_now", True, dict(bucket_elems=40_000, defer_update=False)),
+            ("fused_nvls", True, small))
+    nvls_used = False
     for impl, graph, kw in runs:
+        # the parameter all-gather through NVSwitch multimem stores only in the run that names it
+        os.environ["FT_DP_NVLS"] = "1" if impl == "fused_nvls" else "0"
         cfg, model, eng = build(dev, dist.group.WORLD, "fused" if impl.startswith("fused") else impl, graph, **kw)
         g = torch.Generator().manual_seed(100 + rank)          # different data per rank
         losses = []
@@ -50,6 +54,8 @@ def main():
         K.check_status()
         if impl.startswith("fused"):
             assert eng.dp.step_ok()
+            assert eng.dp.nvls_params == (impl == "fused_nvls" and eng.dp.nvls_params)
+            nvls_used = nvls_used or eng.dp.nvls_params
             if impl == "fused":
                 assert len(eng.dp.buckets) > 3 and eng.dp.launch_order[0] == len(eng.dp.buckets) - 1
         params = model.arena.params.float().clone()
@@ -71,9 +77,12 @@ def main():
     assert torch.equal(results[("fused", False)][0], results[("fused", True)][0])
     assert torch.equal(results[("fused_now", True)][0], results[("fused", True)][0])
     assert results[("fused_now", True)][1] == results[("fused", True)][1]
+    # the multimem broadcast moves the same bits as the peer stores
+    assert torch.equal(results[("fused_nvls", True)][0], results[("fused", True)][0])
+    assert results[("fused_nvls", True)][1] == results[("fused", True)][1]
     assert results[("fused", True)][1][-1] < results[("fused", True)][1][0]
     if rank == 0:
-        print("DP_WORKER_OK", world, results[("fused", True)][1])
+        print("DP_WORKER_OK", world, "nvls_params" if nvls_used else "peer_stores_only", results[("fused", True)][1])
     dist.barrier()
     dist.destroy_process_group()
 
