@@ -60,6 +60,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--comm-ctas", type=int, default=0, help="0 = the launcher's default")
     ap.add_argument("--nvls-ctas", type=int, default=148)
+    ap.add_argument("--gathers-only", action="store_true", help="only the all-gather -> GEMM rows")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -123,21 +124,22 @@ def main():
                (world - 1) * ms * d * 2)
     del stg
 
-    # ---- K13: GEMM -> reduce-scatter (row-parallel fc2 slice)
-    kk, n2 = 8192 // 8, 2048
-    a = bf(m, kk)
-    w2 = bf(n2, kk)
-    shard = torch.empty((ms, n2), dtype=torch.bfloat16, device=dev)
-    full = torch.empty((m, n2), dtype=torch.bfloat16, device=dev)
-    t_f = timeit(lambda: fc.gemm_reduce_scatter(a, w2, shard), args.iters, args.warmup, flush)
-    K.check_status()
+    if not args.gathers_only:
+        # ---- K13: GEMM -> reduce-scatter (row-parallel fc2 slice)
+        kk, n2 = 8192 // 8, 2048
+        a = bf(m, kk)
+        w2 = bf(n2, kk)
+        shard = torch.empty((ms, n2), dtype=torch.bfloat16, device=dev)
+        full = torch.empty((m, n2), dtype=torch.bfloat16, device=dev)
+        t_f = timeit(lambda: fc.gemm_reduce_scatter(a, w2, shard), args.iters, args.warmup, flush)
+        K.check_status()
 
-    def base_rs():
-        torch.matmul(a, w2.t(), out=full)
-        dist.reduce_scatter_tensor(shard, full)
-    t_b = timeit(base_rs, args.iters, args.warmup, flush)
-    report(f"gemm->reduce-scatter  A[{m}x{kk}] @ W[{n2}x{kk}]", t_f, t_b, 2.0 * m * n2 * kk,
-           (world - 1) * ms * n2 * 2)
+        def base_rs():
+            torch.matmul(a, w2.t(), out=full)
+            dist.reduce_scatter_tensor(shard, full)
+        t_b = timeit(base_rs, args.iters, args.warmup, flush)
+        report(f"gemm->reduce-scatter  A[{m}x{kk}] @ W[{n2}x{kk}]", t_f, t_b, 2.0 * m * n2 * kk,
+               (world - 1) * ms * n2 * 2)
 
     # ---- K11: all-gather(W shards) -> GEMM (ZeRO-3 qkv projection of GPT-2 medium)
     d3, n3 = 1024, 3072
@@ -172,7 +174,7 @@ def main():
 
     # ---- K14 / K16: MoE dispatch and combine (8 experts, top-2, capacity 1.25, d = 1024)
     T, dm, E = 8192, 1024, 8
-    if E % world == 0:
+    if E % world == 0 and not args.gathers_only:
         ep = ExpertParallel(g, dev, tokens=T, d_model=dm, n_experts=E)
         bufs = ep.new_layer_buffers()
         xt = bf(T, dm)
@@ -203,6 +205,8 @@ def main():
 
     # ---- NVLS: multimem.st all-gather and multimem.ld_reduce all-reduce against NCCL
     try:
+        if args.gathers_only:
+            raise RuntimeError('skipped (--gathers-only)')
         from frankentorch_b200.parallel.nvls import MulticastBuffer, NvlsCollectives, NvlsUnavailable
         nel = 8 << 20                                            # 32 MiB of fp32 per rank
         mb = MulticastBuffer(world * nel * 4 + nel * 4, None, dev)

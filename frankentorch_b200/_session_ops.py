@@ -16,7 +16,8 @@ from typing import Any, Callable, List, Optional, Sequence, Tuple
 import torch
 
 from .autograd.functions import OPS, OpDef
-from .autograd.tape import BackwardOptions, BorrowedInputVersionMismatch, TensorBackwardReport, TensorHookHandle
+from .autograd.tape import (AutogradError, BackwardOptions, BorrowedInputVersionMismatch, TensorBackwardReport,
+                            TensorHookHandle)
 from .core.dtype import DType
 from .runtime.ledger import EvidenceKind
 
@@ -319,6 +320,43 @@ def tensor_apply_function(self, inputs: Sequence[int], forward_fn, backward_fn, 
     return tape.record("custom_function", list(inputs), out, vjp, "custom autograd function backward")
 
 
+def tensor_apply_complex_bridge(self, inputs: Sequence[int], output: torch.Tensor, backward_fn) -> int:
+    """A complex <-> real bridge node (ft-autograd/src/lib.rs:8884): the caller builds the forward output
+    itself, so it may be a complex tensor, and ``backward_fn(ctx, grad_out) -> list of grads or None`` maps the
+    output's gradient to one gradient per input.
+
+    A complex node carries its gradient as a REAL tensor with a trailing dimension of 2 (real, imaginary:
+    the ``view_as_real`` convention, interleaved in memory), a real node as a tensor of its own shape;
+    ``backward_fn`` receives and returns gradients in that form.  With no input that needs a gradient (or with
+    recording off) the output is a plain leaf.  The node is an ordinary custom-function node for the scheduler.
+    """
+    from .session import FunctionCtx
+    tape = self.tensor_tape
+    needs = [tape.nodes[i].requires_grad and tape.grad_enabled for i in inputs]
+    if not any(needs):
+        return tape.leaf(output, requires_grad=False)
+    ctx = FunctionCtx(needs)
+    want = [tuple(tape.value(i).shape) + ((2,) if tape.value(i).is_complex() else ()) for i in inputs]
+    out_shape = tuple(output.shape) + ((2,) if output.is_complex() else ())
+    self._record_dispatch("complex_bridge", True, "custom_function")
+
+    def vjp(g, targets):
+        if tuple(g.shape) != out_shape:
+            raise AutogradError(f"complex bridge: output gradient has shape {tuple(g.shape)}, expected {out_shape} "
+                                "(complex nodes carry [..., 2] real gradients)")
+        res = list(backward_fn(ctx, g))
+        if len(res) != len(inputs):
+            raise AutogradError(f"complex bridge backward returned {len(res)} gradients for {len(inputs)} inputs")
+        for k, (r, w) in enumerate(zip(res, want)):
+            if r is not None and (r.is_complex() or tuple(r.shape) != w):
+                raise AutogradError(f"complex bridge backward: gradient {k} must be real with shape {w}, "
+                                    f"got {r.dtype} {tuple(r.shape)}")
+        return res
+
+    return tape.record("complex_bridge", list(inputs), output, vjp,
+                       "complex bridge: interleaved (re, im) gradient of the output -> per-input gradients")
+
+
 def checkpoint(self, fn: Callable, inputs: Sequence[int]) -> int:
     """Recompute-on-backward: run ``fn(session, *ids)`` without recording, replay it in backward."""
     tape = self.tensor_tape
@@ -421,7 +459,7 @@ def install(cls) -> None:
                tensor_accumulated_gradient_tensor, tensor_accumulated_gradient_len, tensor_set_accumulated_gradient,
                tensor_zero_grad, tensor_zero_grads, tensor_retain_grad, tensor_autograd_grad, tensor_functional_hessian,
                truncate_autograd_graph, autograd_graph_len, register_tensor_hook, remove_tensor_hook,
-               tensor_apply_function, tensor_apply_function_with_create_graph, checkpoint, tensor_add_, tensor_sub_, tensor_mul_, tensor_div_, tensor_neg_,
+               tensor_apply_function, tensor_apply_function_with_create_graph, tensor_apply_complex_bridge, checkpoint, tensor_add_, tensor_sub_, tensor_mul_, tensor_div_, tensor_neg_,
                tensor_zero_, tensor_fill_, tensor_clamp_, tensor_update_param_values, tensor_update_param_values_f64_with,
                tensor_update_param_values_f64_with_accumulated_gradient):
         setattr(cls, fn.__name__, fn)

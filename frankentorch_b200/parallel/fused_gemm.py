@@ -12,11 +12,12 @@ few CTAs move data between GPUs while the rest multiply:
   fetch the peers' shards) and the *push* form (staging buffer in symmetric memory, passed as a
   :class:`SymmTensor`: every rank delivers its own shard into all peers' staging buffers in the
   order the consumers need them, and consumers poll flags in their own memory only).  The push
-  form has two transports (``FT_GATHER_TRANSPORT``): ``ce`` (default) enqueues the deliveries as
-  device-to-device copies on a second stream, each followed by a one-block kernel that sets the
-  arrival flags at the consumer, so the copy engines move the bytes at the full NVLink rate and
-  all SMs multiply; ``sm`` moves them with copy CTAs inside the GEMM kernel (a handful of SMs
-  cannot keep NVLink full: 8-17 GB/s per copy CTA measured, whatever the instruction mix);
+  form has two transports (``FT_GATHER_TRANSPORT``): ``sm`` (default) moves the shards with copy
+  CTAs inside the GEMM kernel; ``ce`` enqueues the deliveries as device-to-device copies on
+  other streams, each followed by a one-warp kernel that sets the arrival flags at the consumer,
+  so the copy engines move the bytes and all SMs multiply.  Measured on two GPUs the hand-over
+  between the copy engines and that kernel costs tens of microseconds per delivery, which makes
+  ``ce`` the slowest of the three forms there; it is kept as an option for large chunks;
 * :meth:`FusedCollectives.gemm_reduce_scatter` - the epilogue stores bf16 partial tiles into the
   owning rank's inbox and the owner adds them in ascending rank order (row-parallel Linear,
   ZeRO-3 weight-gradient reduce-scatter).
@@ -106,9 +107,13 @@ class FusedCollectives:
             self.inbox = SymmetricBuffer(3 * max_inbox_elems * 2, group, device)
         self._slot = 0
         self._first = True
-        self.transport = os.environ.get("FT_GATHER_TRANSPORT", "ce")
-        self.ce_parts = max(1, int(os.environ.get("FT_GATHER_CE_PARTS", "4")))   # copies per (chunk, destination)
-        self.comm_stream = torch.cuda.Stream(device=device)
+        self.transport = os.environ.get("FT_GATHER_TRANSPORT", "sm")
+        # copy-engine transport: copies per (chunk, destination) and streams the destinations are dealt to.  Every
+        # copy -> flag kernel -> copy hand-over between the copy engines and the SMs on one stream costs ~10 us, so
+        # few, large copies on alternating streams beat many small ones in one queue.
+        self.ce_parts = 1
+        self.comm_streams = [torch.cuda.Stream(device=device)
+                             for _ in range(max(1, int(os.environ.get("FT_GATHER_CE_STREAMS", "2"))))]
         torch.cuda.synchronize(device)
         if self.world > 1:
             dist.barrier(group=group)
@@ -195,12 +200,13 @@ class FusedCollectives:
         """Copy-engine transport of the push form: on the communication stream, behind everything the launching
         stream has queued so far (the shard is final, the epoch is ticked), copy this rank's shard into every
         rank's staging buffer - destinations in the order they will need it, each chunk in ``ce_parts`` copies -
-        and set the arrival flags of each part at its consumer.  Returns the event the launching stream must
+        and set the arrival flags of each part at its consumer.  Returns the events the launching stream must
         wait for after the GEMM (the shard may then be rewritten, the own staged copy is complete)."""
-        main, cs = torch.cuda.current_stream(self.device), self.comm_stream
+        main = torch.cuda.current_stream(self.device)
         ev = torch.cuda.Event()
         ev.record(main)
-        cs.wait_event(ev)
+        for cs in self.comm_streams:
+            cs.wait_event(ev)
         rows, cols = shard.t.shape
         row_bytes = cols * 2
         piece = min(TILE_M * row_bytes, 32768)
@@ -213,16 +219,20 @@ class FusedCollectives:
             dests = [r] + [(r - d) % W for d in range(1, W)]
         parts = min(self.ce_parts, ppc)
         bounds = [ppc * k // parts for k in range(parts + 1)]
-        src, lib, raw = shard.peer_ptrs[r], self.lib, C.c_void_p(cs.cuda_stream)
-        for dest in dests:
+        src, lib = shard.peer_ptrs[r], self.lib
+        for n, dest in enumerate(dests):
+            raw = C.c_void_p(self.comm_streams[n % len(self.comm_streams)].cuda_stream)
             for k in range(parts):
                 p0, p1 = bounds[k], bounds[k + 1]
                 K._chk(lib.ftk_copy_async(full.peer_ptrs[dest] + r * chunk_bytes + p0 * piece, src + p0 * piece,
                                           (p1 - p0) * piece, raw), "ftk_copy_async")
                 K._chk(lib.ftk_set_flags_sys(self.gflags.peer_ptrs[dest] + 4 * (r * ppc + p0), p1 - p0,
                                              self.epoch.data_ptr(), raw), "ftk_set_flags_sys")
-        done = torch.cuda.Event()
-        done.record(cs)
+        done = []
+        for cs in self.comm_streams:
+            e = torch.cuda.Event()
+            e.record(cs)
+            done.append(e)
         return done
 
     # ------------------------------------------------------------------ all-gather -> GEMM (A)
@@ -249,8 +259,8 @@ class FusedCollectives:
         self._tick()
         done = self._ce_deliver(x_shard, full_sym, own_last=True) if c.push == 2 else None
         K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(gather A)")
-        if done is not None:
-            torch.cuda.current_stream(self.device).wait_event(done)
+        for e in done or ():
+            torch.cuda.current_stream(self.device).wait_event(e)
         return out
 
     # ------------------------------------------------------------------ all-gather -> GEMM (B)
@@ -277,8 +287,8 @@ class FusedCollectives:
         self._tick()
         done = self._ce_deliver(w_shard, full_sym, own_last=False) if c.push == 2 else None
         K._chk(self.lib.ftk_gemm_comm_bf16(C.byref(g), C.byref(c), K._stream()), "ftk_gemm_comm_bf16(gather B)")
-        if done is not None:
-            torch.cuda.current_stream(self.device).wait_event(done)
+        for e in done or ():
+            torch.cuda.current_stream(self.device).wait_event(e)
         return out
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter

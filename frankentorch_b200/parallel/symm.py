@@ -80,6 +80,19 @@ class SymmetricBuffer:
         return arr
 
     def close(self) -> None:
+        """Unmap the peers' buffers and, once every rank has done so (a barrier of the group), free this
+        rank's own allocation.  Collective over the group; tensors handed out by :meth:`tensor` are dead
+        afterwards.  A buffer that is never closed lives until the process ends."""
+        if self.local_ptr == 0:
+            return
+        torch.cuda.synchronize(self.device)
         for p in self._opened:
             self.lib.ftk_ipc_close(p)
         self._opened = []
+        if self.world > 1 and self.group is not None and dist.is_initialized():
+            dist.barrier(group=self.group)          # nobody maps this rank's memory any more
+        self.bytes = None
+        self._holder = None
+        self.lib.ftk_ipc_free(self.local_ptr)
+        self.local_ptr = 0
+        self.peer_ptrs = [0] * self.world

@@ -127,3 +127,40 @@ def test_custom_function_needs_a_tape_building_backward_for_create_graph():
                           torch.tensor([0.75, 6.75], dtype=torch.float64))
     H = s.tensor_functional_hessian(s.tensor_sum(y), x)
     assert torch.allclose(H, torch.diag(torch.tensor([3.0, -9.0], dtype=torch.float64)))
+
+
+def test_complex_bridge_carries_interleaved_gradients():
+    """A real -> complex -> real chain through two bridge nodes (FFT of a real signal, then |z|^2): the complex
+    node's gradient travels as a real [..., 2] tensor and the result equals torch.autograd's."""
+    import torch
+
+    from frankentorch_b200.session import FrankenTorchSession
+    s = FrankenTorchSession("strict", ledger_dispatch=False)
+    x0 = torch.randn(16, dtype=torch.float64, generator=torch.Generator().manual_seed(3))
+    x = s.tensor_variable_from_storage(x0.clone(), True)
+    z_val = torch.fft.fft(s.tensor(x))
+
+    def fft_bwd(ctx, g):                          # g: [16, 2] real view of the conjugate-Wirtinger gradient
+        return [torch.fft.ifft(torch.view_as_complex(g.contiguous()), norm="forward").real]
+    z = s.tensor_apply_complex_bridge([x], z_val, fft_bwd)
+    assert s.tensor(z).is_complex()
+    w_val = (s.tensor(z).abs() ** 2)
+
+    def abs2_bwd(ctx, g):                         # d|z|^2 -> 2 g z, as [..., 2]
+        return [torch.view_as_real(2.0 * g * s.tensor(z))]
+    w = s.tensor_apply_complex_bridge([z], w_val, abs2_bwd)
+    loss = s.tensor_sum(w)
+    rep = s.tensor_backward(loss)
+    xt = x0.clone().requires_grad_(True)
+    (torch.fft.fft(xt).abs() ** 2).sum().backward()
+    assert torch.allclose(rep.gradient(x), xt.grad, atol=1e-10)
+    # a bridge whose inputs need no gradient is a plain leaf
+    c = s.tensor_variable_from_storage(x0.clone(), False)
+    leaf = s.tensor_apply_complex_bridge([c], torch.fft.fft(x0), fft_bwd)
+    assert not s.tensor_tape.nodes[leaf].requires_grad
+    # a backward that returns a complex gradient is refused
+    bad = s.tensor_apply_complex_bridge([x], z_val, lambda ctx, g: [torch.view_as_complex(g.contiguous())])
+    w2 = s.tensor_apply_complex_bridge([bad], w_val, abs2_bwd)
+    import pytest
+    with pytest.raises(Exception, match="must be real"):
+        s.tensor_backward(s.tensor_sum(w2))

@@ -220,3 +220,20 @@ def test_sharded_checkpoint_of_bucketed_optimizer_state_resumes(cuda_device, tmp
     load_training_state(resumed, stem)
     tail = [resumed.step(*b) for b in batches[3:]]
     assert head + tail == ref
+
+
+def test_symmetric_buffer_close_frees_the_local_allocation(cuda_device):
+    """``close()`` unmaps the peers, then frees the rank's own ``cudaMalloc`` block; a second call is a no-op."""
+    from frankentorch_b200.parallel.symm import SymmetricBuffer
+    before = torch.cuda.mem_get_info(cuda_device)[0]
+    buf = SymmetricBuffer(64 << 20, None, cuda_device)
+    t = buf.tensor(torch.float32, 1024)
+    t.fill_(3.0)
+    assert float(t.sum()) == 3.0 * 1024 and buf.peer_ptrs[0] == buf.local_ptr != 0
+    held = torch.cuda.mem_get_info(cuda_device)[0]
+    assert before - held >= 60 << 20
+    del t
+    buf.close()
+    assert buf.local_ptr == 0 and buf.bytes is None
+    assert torch.cuda.mem_get_info(cuda_device)[0] - held >= 60 << 20     # the block went back to the driver
+    buf.close()
