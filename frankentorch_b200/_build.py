@@ -34,6 +34,11 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
 ]
+# FT_BUILD_DEBUG_BOUNDS=1: a debug build in which the kernels' FT_IDX() index guards are compiled in (an index
+# outside its range is reported through the status word and replaced by 0 instead of being dereferenced).  The
+# flags are part of the build manifest, so switching the variable rebuilds the library.
+if os.environ.get("FT_BUILD_DEBUG_BOUNDS", "0") == "1":
+    NVCC_FLAGS.append("-DFT_DEBUG_BOUNDS")
 CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function"]
 
 

@@ -11,6 +11,7 @@
 // as the serial kernel, whatever the width and whatever the size gate
 // (ft-kernel-cpu/src/lib.rs:21-40, :4120; tests/threshold_serial_parallel_equivalence.rs).
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -181,6 +182,91 @@ FTC_API void ftc_adamw_f64_par(double* p, const double* g, double* m, double* v,
       v[i] = b2 * v[i] + (1.0 - b2) * g[i] * g[i];
       const double mh = m[i] / bc1, vh = v[i] / bc2;
       p[i] -= p[i] * lr * wd + lr * mh / (std::sqrt(vh) + eps);
+    }
+  });
+}
+
+// ---- blocked scaled dot-product attention with a tunable query-row tile ------------------------------
+// Counterpart of the reference's `sdpa_forward_f32` tile controls (ft-kernel-cpu/src/lib.rs:4912-4990):
+// the work items are (batch*head, block of BR query rows); BR is a process-wide setting with a fixed
+// default of 64, a programmatic setter (so one process can sweep it) and an environment override read once
+// (FT_SDPA_BR, 8..512); 0 selects the adaptive rule: 128 when the heads alone fill the pool or when
+// heads x blocks stays above four tasks per thread, else 64.  Every output row is computed by one thread
+// with the same loop as the serial oracle, so the result is bit-identical for every BR and every pool width:
+// BR can only change scheduling.
+namespace {
+std::atomic<int> g_sdpa_br{64};
+std::once_flag g_sdpa_env_once;
+constexpr int SDPA_BR_SMALL = 64, SDPA_BR_LARGE = 128, SDPA_TASKS_PER_THREAD = 4;
+
+void sdpa_env_init() {
+  std::call_once(g_sdpa_env_once, [] {
+    if (const char* e = std::getenv("FT_SDPA_BR")) {
+      char* end = nullptr;
+      const long b = std::strtol(e, &end, 10);
+      if (end != e && *end == 0 && b >= 8 && b <= 512) g_sdpa_br.store((int)b);
+    }
+  });
+}
+int sdpa_br_pick(int64_t sq, int64_t num_bh, int threads) {
+  threads = std::max(1, threads);
+  if (num_bh >= threads) return SDPA_BR_LARGE;
+  const int64_t blocks = (sq + SDPA_BR_LARGE - 1) / SDPA_BR_LARGE;
+  return num_bh * blocks >= (int64_t)SDPA_TASKS_PER_THREAD * threads ? SDPA_BR_LARGE : SDPA_BR_SMALL;
+}
+void sdpa_rows(const double* q, const double* k, const double* v, double* o, int64_t r0, int64_t r1, int64_t sk,
+               int64_t d, double scale, int causal, std::vector<double>& p) {
+  for (int64_t i = r0; i < r1; ++i) {
+    double m = -INFINITY;
+    const int64_t lim = causal ? std::min<int64_t>(sk, i + 1) : sk;
+    for (int64_t j = 0; j < lim; ++j) {
+      double s = 0.0;
+      for (int64_t e = 0; e < d; ++e) s += q[i * d + e] * k[j * d + e];
+      p[j] = s * scale;
+      m = std::max(m, p[j]);
+    }
+    double z = 0.0;
+    for (int64_t j = 0; j < lim; ++j) {
+      p[j] = std::exp(p[j] - m);
+      z += p[j];
+    }
+    for (int64_t e = 0; e < d; ++e) {
+      double s = 0.0;
+      for (int64_t j = 0; j < lim; ++j) s += p[j] * v[j * d + e];
+      o[i * d + e] = s / z;
+    }
+  }
+}
+}  // namespace
+
+// br: 0 = adaptive, otherwise clamped to [8, 512].  Returns the value now stored.
+FTC_API int ftc_set_sdpa_br(int br) {
+  sdpa_env_init();
+  if (br != 0) br = std::min(512, std::max(8, br));
+  g_sdpa_br.store(br);
+  return br;
+}
+FTC_API int ftc_get_sdpa_br() {
+  sdpa_env_init();
+  return g_sdpa_br.load();
+}
+// The tile the kernel would use for this problem (the stored value, or the adaptive choice when it is 0).
+FTC_API int ftc_sdpa_br_for(int64_t sq, int64_t num_bh) {
+  sdpa_env_init();
+  const int b = g_sdpa_br.load();
+  return b != 0 ? b : sdpa_br_pick(sq, num_bh, g_width);
+}
+// q, k, v, o: [num_bh, s, d] contiguous.  Work items (bh, row block) are dealt to the pool in order.
+FTC_API void ftc_sdpa_f64_blocked(const double* q, const double* k, const double* v, double* o, int64_t num_bh,
+                                  int64_t sq, int64_t sk, int64_t d, double scale, int causal) {
+  const int br = ftc_sdpa_br_for(sq, num_bh);
+  const int64_t blocks = (sq + br - 1) / br, items = num_bh * blocks;
+  parallel_rows(items, (int64_t)br * sk * d * 2, [=](int64_t i0, int64_t i1) {
+    std::vector<double> p((size_t)sk);
+    for (int64_t it = i0; it < i1; ++it) {
+      const int64_t bh = it / blocks, blk = it % blocks;
+      const int64_t r0 = blk * br, r1 = std::min(sq, r0 + br);
+      sdpa_rows(q + bh * sq * d, k + bh * sk * d, v + bh * sk * d, o + bh * sq * d, r0, r1, sk, d, scale, causal, p);
     }
   });
 }

@@ -148,9 +148,11 @@ dropout_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ 
 __global__ void __launch_bounds__(128)
 embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ wte,
                      const __nv_bfloat16* __restrict__ wpe, __nv_bfloat16* __restrict__ out, int S,
-                     int d) {
+                     int d, long long vocab, int* status) {
   const int r = blockIdx.x;
-  const long long id = ids[r];
+  long long id = ids[r];
+  // a token id outside the table: reported through the status word, row 0 is read instead
+  if (!ft_index_ok(id, vocab, status)) id = 0;
   const uint4* te = reinterpret_cast<const uint4*>(wte + (size_t)id * d);
   const uint4* pe = wpe ? reinterpret_cast<const uint4*>(wpe + (size_t)(r % S) * d) : nullptr;
   uint4* o = reinterpret_cast<uint4*>(out + (size_t)r * d);
@@ -172,16 +174,17 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __r
 __global__ void __launch_bounds__(128)
 embedding_bwd_wte_kernel(const long long* __restrict__ sorted_ids, const int* __restrict__ order,
                          int rows, const __nv_bfloat16* __restrict__ dout,
-                         float* __restrict__ dwte, int d) {
+                         float* __restrict__ dwte, int d, long long vocab, int* status) {
   const int b = blockIdx.x;
   const long long id = sorted_ids[b];
   if (b > 0 && sorted_ids[b - 1] == id) return;
+  if (!ft_index_ok(id, vocab, status)) return;     // no table row to add into
   int e = b + 1;
   while (e < rows && sorted_ids[e] == id) ++e;
   for (int c = threadIdx.x * 2; c < d; c += blockDim.x * 2) {
     float s0 = 0.f, s1 = 0.f;
     for (int i = b; i < e; ++i) {
-      float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + (size_t)order[i] * d + c));
+      float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + (size_t)FT_IDX(order[i], rows, status) * d + c));
       s0 += v.x;
       s1 += v.y;
     }
@@ -377,16 +380,18 @@ extern "C" int ftk_dropout_bf16(const void* x, void* y, long long n, float p,
   return (int)cudaGetLastError();
 }
 extern "C" int ftk_embedding_fwd(const long long* ids, const void* wte, const void* wpe, void* out,
-                                 int rows, int S, int d, void* stream) {
-  if (rows <= 0 || d % 8 || S <= 0) return -2;
-  embedding_fwd_kernel<<<rows, 128, 0, STREAM(stream)>>>(ids, BF(wte), BF(wpe), BFW(out), S, d);
+                                 int rows, int S, int d, long long vocab, void* stream) {
+  if (rows <= 0 || d % 8 || S <= 0 || vocab <= 0) return -2;
+  embedding_fwd_kernel<<<rows, 128, 0, STREAM(stream)>>>(ids, BF(wte), BF(wpe), BFW(out), S, d, vocab,
+                                                         ftk_status_word());
   return (int)cudaGetLastError();
 }
 extern "C" int ftk_embedding_bwd(const long long* sorted_ids, const int* order, const void* dout,
-                                 float* dwte, float* dwpe, int rows, int S, int d, void* stream) {
-  if (rows <= 0 || d % 2) return -2;
+                                 float* dwte, float* dwpe, int rows, int S, int d, long long vocab, void* stream) {
+  if (rows <= 0 || d % 2 || (dwte && vocab <= 0)) return -2;
   if (dwte)
-    embedding_bwd_wte_kernel<<<rows, 128, 0, STREAM(stream)>>>(sorted_ids, order, rows, BF(dout), dwte, d);
+    embedding_bwd_wte_kernel<<<rows, 128, 0, STREAM(stream)>>>(sorted_ids, order, rows, BF(dout), dwte, d, vocab,
+                                                               ftk_status_word());
   if (dwpe) embedding_bwd_wpe_kernel<<<S, 128, 0, STREAM(stream)>>>(BF(dout), dwpe, rows, S, d);
   return (int)cudaGetLastError();
 }

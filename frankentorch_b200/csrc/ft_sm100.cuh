@@ -28,7 +28,24 @@ enum : int {
   FT_ERR_WAIT_SOFTMAX = 6,    // attention: MMA issuer waited for probabilities that never arrived
   FT_ERR_BAD_ARG = 7,
   FT_ERR_WAIT_WARPS = 8,      // a barrier among a CTA's warps was abandoned by one of them (abort elsewhere)
+  FT_ERR_BAD_INDEX = 9,       // an index read from device memory (token id, guarded index) was out of range
 };
+
+// Index guard.  ft_index_ok() is for indices that come from DATA (token ids, expert ids): always compiled,
+// it records FT_ERR_BAD_INDEX with the CTA in the status word and tells the caller to skip the access, so a
+// bad value in a tensor ends in a host-side exception instead of a faulted GPU.  FT_IDX() is for indices the
+// kernel computes itself: in debug builds (-DFT_DEBUG_BOUNDS) it checks them the same way and substitutes 0;
+// in release builds it is the index, with no code.
+static __device__ __forceinline__ bool ft_index_ok(long long i, long long n, int* status) {
+  if (i >= 0 && i < n) return true;
+  if (status) atomicCAS(status, 0, FT_ERR_BAD_INDEX | (int(blockIdx.x) << 8));
+  return false;
+}
+#ifdef FT_DEBUG_BOUNDS
+#define FT_IDX(i, n, status) (ftk::ft_index_ok((long long)(i), (long long)(n), (status)) ? (i) : 0)
+#else
+#define FT_IDX(i, n, status) (i)
+#endif
 
 // One second at ~1.9 GHz; legitimate waits inside one kernel are far shorter.
 #ifndef FT_WAIT_BUDGET_CYCLES

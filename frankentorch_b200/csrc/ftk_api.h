@@ -218,14 +218,16 @@ int ftk_colsum_bf16(const void* x, float* out, float* partial, int rows, int col
 int ftk_colsum_blocks(int rows);
 
 // ---- embedding --------------------------------------------------------------------------
-// out[r, :] = wte[ids[r], :] + wpe[r % S, :]  (wpe may be NULL)
+// out[r, :] = wte[ids[r], :] + wpe[r % S, :]  (wpe may be NULL).  `vocab` = rows of wte: an id outside
+// [0, vocab) is reported through the status word (BAD_INDEX) and row 0 is read in its place.
 int ftk_embedding_fwd(const long long* ids, const void* wte, const void* wpe, void* out, int rows,
-                      int S, int d, void* stream);
+                      int S, int d, long long vocab, void* stream);
 // Deterministic scatter-add: `sorted_ids`/`order` come from a stable sort of the ids, so
 // each table row is summed by one CTA in ascending source-row order.
-// dwte fp32 [vocab, d] (+=), dwpe fp32 [S, d] (+=); either may be NULL.
+// dwte fp32 [vocab, d] (+=), dwpe fp32 [S, d] (+=); either may be NULL.  Rows of ids outside [0, vocab)
+// are skipped and reported through the status word.
 int ftk_embedding_bwd(const long long* sorted_ids, const int* order, const void* dout, float* dwte,
-                      float* dwpe, int rows, int S, int d, void* stream);
+                      float* dwpe, int rows, int S, int d, long long vocab, void* stream);
 
 // ---- optimizer --------------------------------------------------------------------------
 // Fused AdamW on fp32 master weights with bf16 shadow write-back.  grad fp32.

@@ -24,6 +24,7 @@ _STATUS_NAMES = {
     5: "WAIT_PEER (peer flag never arrived)", 6: "WAIT_SOFTMAX (probabilities never arrived)",
     7: "BAD_ARG (misaligned shared memory or invalid argument)",
     8: "WAIT_WARPS (a warp barrier was abandoned after an abort elsewhere in the CTA)",
+    9: "BAD_INDEX (an index read from a tensor, e.g. a token id, was out of range; the access was skipped)",
 }
 
 # launch counter: how many of this package's kernels launchers were called (bench reporting)
@@ -434,7 +435,7 @@ def embedding_fwd(ids, wte, wpe, S):
     d = wte.shape[1]
     out = torch.empty((rows, d), dtype=torch.bfloat16, device=wte.device)
     _chk(_lib.load().ftk_embedding_fwd(ids.data_ptr(), wte.data_ptr(), _ptr(wpe), out.data_ptr(), rows, S, d,
-                                       _stream()), "ftk_embedding_fwd")
+                                       wte.shape[0], _stream()), "ftk_embedding_fwd")
     return out
 
 
@@ -449,7 +450,8 @@ def embedding_bwd(ids, dout, dwte, dwpe, S):
     sorted_ids, order = torch.sort(flat, stable=True)
     order32 = order.to(torch.int32)
     _chk(_lib.load().ftk_embedding_bwd(sorted_ids.data_ptr(), order32.data_ptr(), dout.data_ptr(),
-                                       _ptr(dwte), _ptr(dwpe), rows, S, d, _stream()), "ftk_embedding_bwd")
+                                       _ptr(dwte), _ptr(dwpe), rows, S, d,
+                                       dwte.shape[0] if dwte is not None else 0, _stream()), "ftk_embedding_bwd")
 
 
 # --------------------------------------------------------------------------------------- optimizer

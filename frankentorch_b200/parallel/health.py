@@ -100,7 +100,8 @@ class RankHealth:
 _STATUS_NAMES = {1: "TMA data never landed", 2: "pipeline stage never released", 3: "accumulator never completed",
                  4: "accumulator never drained", 5: "a flag owned by another rank never reached the expected value",
                  6: "probabilities never arrived", 7: "bad argument",
-                 8: "a warp barrier was abandoned after an abort elsewhere in the CTA"}
+                 8: "a warp barrier was abandoned after an abort elsewhere in the CTA",
+                 9: "an index read from a tensor (a token id) was out of range; the access was skipped"}
 
 
 def device_status_error(status_word: int) -> Optional[DeviceWaitTimeout]:

@@ -55,3 +55,39 @@ def pool_width() -> int:
 
 def auto_width() -> int:
     return int(native.load().ftc_pool_auto_width())
+
+
+# ---- runtime toggles of the CPU reference kernels (ft-kernel-cpu/src/lib.rs:4912-4990) -----------------------
+def set_sdpa_br(br: int) -> int:
+    """Query-row tile of the blocked CPU attention kernel: clamped to [8, 512]; 0 selects the adaptive rule
+    (128 rows when heads x blocks keeps the pool busy, else 64).  Returns the value stored.  The environment
+    variable ``FT_SDPA_BR`` sets the initial value (read once).  Results are bit-identical for every value."""
+    return int(native.load().ftc_set_sdpa_br(int(br)))
+
+
+def set_sdpa_br_auto() -> int:
+    return set_sdpa_br(0)
+
+
+def sdpa_br() -> int:
+    return int(native.load().ftc_get_sdpa_br())
+
+
+def sdpa_br_for(seq_q: int, num_bh: int) -> int:
+    """The tile the kernel uses for ``num_bh`` (batch x head) problems of ``seq_q`` query rows."""
+    return int(native.load().ftc_sdpa_br_for(int(seq_q), int(num_bh)))
+
+
+def sdpa_blocked(q, k, v, *, causal: bool = False, scale=None):
+    """Blocked, pool-parallel f64 attention: ``q`` ``[..., sq, d]``, ``k`` / ``v`` ``[..., sk, d]`` CPU tensors."""
+    import math
+
+    import torch
+    lead = q.shape[:-2]
+    sq, d = q.shape[-2:]
+    sk = k.shape[-2]
+    q2, k2, v2 = (t.to(torch.float64).reshape(-1, t.shape[-2], d).contiguous() for t in (q, k, v))
+    out = torch.empty_like(q2)
+    native.load().ftc_sdpa_f64_blocked(q2.data_ptr(), k2.data_ptr(), v2.data_ptr(), out.data_ptr(), q2.shape[0], sq, sk,
+                                       d, float(scale if scale is not None else 1.0 / math.sqrt(d)), int(causal))
+    return out.reshape(*lead, sq, d)

@@ -54,6 +54,8 @@ def load():
         "ftc_linear_f64_par": ([vp, vp, vp, vp, i64, i64, i64], None),
         "ftc_layer_norm_f64_par": ([vp, vp, vp, vp, i64, i64, dbl], None),
         "ftc_adamw_f64_par": ([vp, vp, vp, vp, i64, dbl, dbl, dbl, dbl, dbl, i64], None),
+        "ftc_set_sdpa_br": ([i32], i32), "ftc_get_sdpa_br": ([], i32), "ftc_sdpa_br_for": ([i64, i64], i32),
+        "ftc_sdpa_f64_blocked": ([vp, vp, vp, vp, i64, i64, i64, i64, dbl, i32], None),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)

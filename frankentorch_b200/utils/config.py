@@ -46,6 +46,8 @@ ENV_FLAGS: Dict[str, EnvFlag] = {f.name: f for f in (
             "thread width of the CPU reference kernels: unset = serial, 'auto' = min(16, physical cores), or a count"),
     EnvFlag("FT_DP_OVERLAP", True, _bool, "start each gradient bucket's reduction under the backward pass"),
     EnvFlag("FT_DP_DEFER", True, _bool, "run the sharded AdamW + parameter all-gather under the next forward pass"),
+    EnvFlag("FT_SDPA_BR", "64", str, "query-row tile of the blocked CPU attention kernel (8..512; set_sdpa_br(0) = adaptive)"),
+    EnvFlag("FT_GATHER_TRANSPORT", "sm", str, "push-form gathers of the fused GEMMs: copy CTAs (sm) or copy engines (ce)"),
     EnvFlag("FT_DP_NVLS", "auto", str, "data-parallel parameter all-gather through NVSwitch multimem stores: 0, 1, or "
             "auto (jobs of four or more ranks, where the system offers a multicast object)"),
     EnvFlag("FT_DP_WIRE", "bf16", str, "gradient type on NVLink for the fused data-parallel path: bf16 or fp32"),

@@ -172,6 +172,31 @@ def test_embedding(cuda_device):
     k.check_status()
 
 
+def test_embedding_reports_token_ids_outside_the_table(cuda_device):
+    """A token id that is not a row of the table never becomes an address: the lookup reads row 0 in its place, the
+    scatter-add skips it, the status word says BAD_INDEX, and the device keeps working."""
+    k = _k()
+    torch.manual_seed(7)
+    V, S, d = 100, 4, 64
+    wte = _bf(torch.randn(V, d), cuda_device)
+    ids = torch.tensor([[1, 5, V, -3]], device=cuda_device)
+    out = k.embedding_fwd(ids, wte, None, S)
+    with pytest.raises(k.KernelError, match="BAD_INDEX"):
+        k.check_status()
+    assert torch.equal(out[0], wte[1]) and torch.equal(out[1], wte[5])
+    assert torch.equal(out[2], wte[0]) and torch.equal(out[3], wte[0])
+    k.check_status()                                   # the word was cleared; nothing else is wrong
+    dout = _bf(torch.randn(S, d), cuda_device)
+    dwte = torch.zeros(V, d, device=cuda_device)
+    k.embedding_bwd(ids, dout, dwte, None, S)
+    with pytest.raises(k.KernelError, match="BAD_INDEX"):
+        k.check_status()
+    assert torch.allclose(dwte[1], dout[0].float()) and torch.allclose(dwte[5], dout[1].float())
+    assert float(dwte.abs().sum()) == pytest.approx(float(dout[:2].float().abs().sum()), rel=1e-5)
+    assert torch.equal(k.embedding_fwd(ids[:, :2].contiguous(), wte, None, 2), wte[[1, 5]])
+    k.check_status()
+
+
 def test_adamw_matches_reference_formula(cuda_device):
     k = _k()
     torch.manual_seed(7)

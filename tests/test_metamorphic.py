@@ -258,3 +258,47 @@ def test_committed_files_name_no_closed_call_and_no_machine_path():
         if machine.search(p.read_text()):
             bad.append(f"{p.name} names a path or tool of the build machine")
     assert not bad, "\n".join(bad)
+
+
+def test_cpu_attention_tile_is_a_scheduling_knob_only():
+    """The query-row tile of the blocked CPU attention kernel (``set_sdpa_br``, ``FT_SDPA_BR``) and the pool width
+    never change a bit of the result; the adaptive rule coarsens only while heads x blocks keeps the pool busy."""
+    import math
+
+    import torch
+
+    from frankentorch_b200.runtime import cpu_pool, native
+    lib = native.load()
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(3, 2, 150, 16, generator=g, dtype=torch.float64) for _ in range(3))
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    old_br = cpu_pool.sdpa_br()
+    lib.ftc_pool_reset_for_tests()
+    lib.ftc_pool_set_min_work(1)
+    try:
+        outs = []
+        for width in ("1", "3", "8"):
+            lib.ftc_pool_reset_for_tests()
+            assert lib.ftc_pool_configure(width.encode(), None) == int(width)
+            for br in (8, 64, 100, 512, 0):
+                cpu_pool.set_sdpa_br(br)
+                outs.append(cpu_pool.sdpa_blocked(q, k, v, causal=True))
+        assert all(torch.equal(outs[0], o) for o in outs)
+        assert torch.allclose(outs[0], ref, atol=1e-12)
+        # one (batch, head) problem at a time through the serial oracle gives the same bits
+        one = torch.empty(150, 16, dtype=torch.float64)
+        lib.ftc_sdpa_f64(q[1, 0].contiguous().data_ptr(), k[1, 0].contiguous().data_ptr(),
+                         v[1, 0].contiguous().data_ptr(), one.data_ptr(), 150, 150, 16, 1.0 / math.sqrt(16), 1)
+        assert torch.equal(one, outs[0][1, 0])
+        # setter clamps; adaptive rule
+        assert cpu_pool.set_sdpa_br(3) == 8 and cpu_pool.set_sdpa_br(4096) == 512
+        cpu_pool.set_sdpa_br_auto()
+        lib.ftc_pool_reset_for_tests()
+        lib.ftc_pool_configure(b"8", None)
+        assert cpu_pool.sdpa_br_for(1500, 8) == 128          # heads fill the pool
+        assert cpu_pool.sdpa_br_for(1500, 4) == 128          # 4 x 12 blocks >= 4 x 8
+        assert cpu_pool.sdpa_br_for(300, 2) == 64            # 2 x 3 blocks would starve the pool
+    finally:
+        cpu_pool.set_sdpa_br(old_br)
+        lib.ftc_pool_reset_for_tests()
+        lib.ftc_pool_set_min_work(1 << 15)
