@@ -48,8 +48,8 @@ ENV_FLAGS: Dict[str, EnvFlag] = {f.name: f for f in (
     EnvFlag("FT_DP_DEFER", True, _bool, "run the sharded AdamW + parameter all-gather under the next forward pass"),
     EnvFlag("FT_SDPA_BR", "64", str, "query-row tile of the blocked CPU attention kernel (8..512; set_sdpa_br(0) = adaptive)"),
     EnvFlag("FT_GATHER_TRANSPORT", "sm", str, "push-form gathers of the fused GEMMs: copy CTAs (sm) or copy engines (ce)"),
-    EnvFlag("FT_DP_NVLS", "auto", str, "data-parallel parameter all-gather through NVSwitch multimem stores: 0, 1, or "
-            "auto (jobs of four or more ranks, where the system offers a multicast object)"),
+    EnvFlag("FT_DP_NVLS", "0", str, "data-parallel parameter all-gather through NVSwitch multimem stores: 0, 1, or "
+            "auto (jobs of eight or more ranks, where the system offers a multicast object)"),
     EnvFlag("FT_DP_WIRE", "bf16", str, "gradient type on NVLink for the fused data-parallel path: bf16 or fp32"),
     EnvFlag("FT_DP_BUCKET_MB", 0.0, float, "gradient bucket size in MB of bf16 (0 = 32)"),
     EnvFlag("FT_DP_CTAS", 296, int, "CTAs of a bucket's push / reduce kernels while the backward pass runs"),
