@@ -382,7 +382,10 @@ def main():
         dp = (NcclDataParallel if args.dp_impl == "nccl" else FusedDataParallel)(model.arena, dist.group.WORLD, dev)
     if dp is not None and hasattr(dp, "record_stamps"):
         dp.record_stamps = True      # four one-thread time-mark kernels per step: the exposed-communication figure
-    engine = TrainEngine(model, mb, seq, OptimConfig(lr=3e-4, grad_clip=1.0), use_cuda_graph=not args.no_graph, dp=dp)
+    from frankentorch_b200.runtime.ledger import EvidenceLedger
+    ledger = EvidenceLedger()        # the eager step before graph capture is written down here, once
+    engine = TrainEngine(model, mb, seq, OptimConfig(lr=3e-4, grad_clip=1.0), use_cuda_graph=not args.no_graph, dp=dp,
+                         ledger=ledger)
 
     # synthetic data: tokens uniform over the vocabulary, a fresh pinned batch per step
     g = torch.Generator().manual_seed(1000 + rank)
@@ -526,6 +529,7 @@ def main():
             "l2": "no flush: one step streams >3 GB of activations, weights and optimizer state (L2 is 126 MB)",
         },
         "clocks": clocks,
+        "ledger_entries": len(ledger),
         "gpu_launches": engine.launches_per_step * args.steps,
         "gpu_launches_per_step": engine.launches_per_step,
         "final_loss": losses[-1] if losses and losses[-1] is not None else None,

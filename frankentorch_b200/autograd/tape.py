@@ -289,6 +289,12 @@ class TensorTape:
         # gradient in place (the kernel is already on the stream); the data-parallel engine uses it
         # to start a bucket's reduction as soon as its last gradient is in
         self.leaf_grad_written_fn: Optional[Callable[[int], None]] = None
+        # optional observer of every recorded (non-leaf) node: called with (node id, operator, output value)
+        # right after the node was appended, i.e. after its forward kernels were queued
+        self.record_hook: Optional[Callable[[int, str, torch.Tensor], None]] = None
+        # optional queue of deferred weight-gradient products (ops/fused.py WgradQueue): flushed when a
+        # backward pass ends, so every gradient is on the stream when backward() returns
+        self.wgrad_queue = None
         self.last_plan_cache: Dict[Tuple[int, int], Tuple] = {}
 
     def __del__(self):
@@ -330,6 +336,8 @@ class TensorTape:
         nid = self._append(op, tuple(inputs), value, rg, False, vjp if rg else None, rule)
         self.nodes[nid].saved = saved if rg else None
         self.nodes[nid].cg = cg if rg else None
+        if self.record_hook is not None:
+            self.record_hook(nid, op, value)
         return nid
 
     def value(self, nid: int) -> torch.Tensor:
@@ -546,6 +554,9 @@ class TensorTape:
                     t = grads.get(inp)
                     if t is not None and not bool(torch.isfinite(t).all()):
                         raise AnomalyDetected(f"non-finite gradient produced by node {nid} ({node.rule})")
+
+        if self.wgrad_queue is not None:
+            self.wgrad_queue.flush()        # weight gradients that rules handed to the queue are launched now
 
         # persistent gradients: leaves that require grad and nodes marked retain_grad
         for nid in order:

@@ -69,6 +69,10 @@ int ftk_gemm_bf16(const FtkGemmDesc* g, void* stream);
 // Which kernel ftk_gemm_bf16 would launch: *bn = 128 / 192 / 256 (one CTA per 128 x bn tile) or
 // 512 (CTA-pair kernel, 256 x 256 tiles, cta_group::2); *splits = split-K factor.  No launch.
 int ftk_gemm_plan(const FtkGemmDesc* g, int* bn, int* splits);
+// `n` (1..8) products with one K and one pair of operand layouts, fp32 outputs (store or accumulate), no other
+// epilogue, as one persistent launch of 128 x 192 tiles: the weight gradients of a transformer block fill the
+// GPU together where each alone would need split-K and a reduction kernel.
+int ftk_gemm_group_bf16(const FtkGemmDesc* descs, int n, void* stream);
 
 // ---- GEMM fused with a collective over NVLink peer memory --------------------------------
 // One kernel: `comm_ctas` CTAs move shards / reduce partials while the rest run the GEMM.

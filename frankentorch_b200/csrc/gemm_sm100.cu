@@ -22,6 +22,7 @@
 // (all-gather -> GEMM, GEMM -> reduce-scatter), lives in gemm_kernel.cuh; this file holds
 // the split-K reduction and the host launchers.
 #include "gemm2_kernel.cuh"
+#include "gemm_group_kernel.cuh"
 
 namespace ftk {
 
@@ -317,6 +318,55 @@ static int plan_gemm(const FtkGemmDesc* g, int* bn_out, int* splits_out) {
   *bn_out = bn;
   *splits_out = splits;
   return 0;
+}
+
+// Grouped launch: `n` (1..8) independent products with the same K and operand layouts, fp32 outputs with a plain
+// store or accumulate epilogue, in one persistent kernel of 128 x 192 tiles (see gemm_group_kernel.cuh).
+extern "C" int ftk_gemm_group_bf16(const FtkGemmDesc* descs, int n, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (!descs || n < 1 || n > GG_MAX) return -2;
+  GroupArgs ga;
+  GroupMaps maps;
+  memset(&ga, 0, sizeof(ga));
+  memset(&maps, 0, sizeof(maps));
+  const FtkGemmDesc& g0 = descs[0];
+  ga.n = n; ga.K = g0.K; ga.a_mn = g0.a_mn ? 1 : 0; ga.b_mn = g0.b_mn ? 1 : 0; ga.alpha = g0.alpha;
+  ga.status = ftk_status_word();
+  if (!ga.status) return -6;
+  int total = 0;
+  for (int p = 0; p < n; ++p) {
+    const FtkGemmDesc* g = &descs[p];
+    if (g->M <= 0 || g->N <= 0 || g->K != g0.K || (g->a_mn ? 1 : 0) != ga.a_mn || (g->b_mn ? 1 : 0) != ga.b_mn ||
+        g->alpha != g0.alpha)
+      return -2;
+    if ((g->L0 > 1) || (g->L1 > 1) || !g->out_fp32 || g->epi != FTK_EPI_NONE || g->bias || g->resid || g->aux ||
+        g->seg_counts || !g->D)
+      return -7;
+    if ((reinterpret_cast<uintptr_t>(g->A) & 15) || (reinterpret_cast<uintptr_t>(g->B) & 15)) return -3;
+    if ((g->lda % 8) || (g->ldb % 8)) return -4;
+    int rc = make_operand_maps(g, 1, 1, GG_BN, &maps.a[p], &maps.b[p]);
+    if (rc) return rc;
+    ga.M[p] = g->M; ga.N[p] = g->N;
+    ga.D[p] = reinterpret_cast<float*>(g->D);
+    ga.ldd[p] = g->ldd;
+    ga.accumulate[p] = g->accumulate ? 1 : 0;
+    total += ((g->M + G_BM - 1) / G_BM) * ((g->N + GG_BN - 1) / GG_BN);
+    ga.tile_end[p] = total;
+  }
+  for (int p = n; p < GG_MAX; ++p) ga.tile_end[p] = total;
+  using Cfg = GemmCfg<GG_BN>;
+  static PerDeviceOnce once;
+  bool* attr_set_p = once.slot();
+  if (!*attr_set_p) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_group_bf16_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    *attr_set_p = true;
+  }
+  const int sms = g0.max_ctas > 0 ? g0.max_ctas : num_sms();
+  const int grid = total < sms ? total : sms;
+  gemm_group_bf16_sm100_kernel<<<grid, G_THREADS, Cfg::SMEM, stream>>>(maps, ga);
+  return (int)cudaGetLastError();
 }
 
 // Which kernel ftk_gemm_bf16 would launch for this problem: *bn = 128 / 192 / 256 (single-CTA tile

@@ -170,6 +170,9 @@ class GPT:
         # the embeddings' gradients are complete only when the backward pass ends (the token table is
         # also the LM head): they form one bucket of their own
         self.arena.bucket_cuts.append(self.arena.slot_end("wpe.weight"))
+        # the weight gradients of a block are launched together (two full waves, no split-K)
+        from ..ops.fused import enable_grouped_wgrad
+        enable_grouped_wgrad(tape)
         self._init_weights(seed)
         # parameters are the lowest-index leaves of the tape; the per-step graph is truncated above
         self.leaf: Dict[str, int] = {}

@@ -104,6 +104,8 @@ def load(build_if_missing: bool = True):
     lib.ftk_gemm_bf16.argtypes = [C.POINTER(FtkGemmDesc), C.c_void_p]
     lib.ftk_gemm_plan.argtypes = [C.POINTER(FtkGemmDesc), C.POINTER(C.c_int), C.POINTER(C.c_int)]
     lib.ftk_gemm_plan.restype = C.c_int
+    lib.ftk_gemm_group_bf16.argtypes = [C.POINTER(FtkGemmDesc), C.c_int, C.c_void_p]
+    lib.ftk_gemm_group_bf16.restype = C.c_int
     lib.ftk_gemm_comm_bf16.argtypes = [C.POINTER(FtkGemmDesc), C.POINTER(FtkCommDesc), C.c_void_p]
     lib.ftk_tick_i32.argtypes = [C.c_void_p, C.c_void_p]
     lib.ftk_set_flags_sys.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]

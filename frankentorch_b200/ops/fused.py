@@ -87,10 +87,80 @@ class SideWork:
             return K.colsum(dy2d, out=out, accumulate=accumulate)
 
 
+class WgradQueue:
+    """Weight gradients of consecutive backward rules, collected and launched together.
+
+    A weight gradient ``dW = dy^T x`` of a transformer block has 24 - 96 output tiles: alone it needs split-K
+    and a reduction kernel to occupy 148 SMs.  The four of a block together are two full waves of 128 x 192
+    tiles (``K.gemm_grouped``), each output element reduced over the tokens by one CTA in order.  A rule hands
+    its weight gradient to the queue instead of launching it; the queue launches when it holds enough tiles
+    (or eight problems) and when the backward pass ends (``TensorTape.backward`` calls :meth:`flush`).  The
+    operands stay referenced until then; nothing in a backward pass writes them in place.  The observer of
+    finished parameter gradients (data-parallel buckets) is told at the launch, not when a rule queued its
+    part.  Large products (the LM head) and gradients without a bound buffer keep the direct path.
+    ``FT_WGRAD_GROUP=0`` turns the queue off."""
+
+    enabled = os.environ.get("FT_WGRAD_GROUP", "1") != "0"
+    FLUSH_TILES = 266          # ~0.9 x two waves of 148
+    MAX_TILES_PER_PROBLEM = 200
+
+    def __init__(self, tape: TensorTape):
+        self.tape = tape
+        self.items = []        # (dy, x, buf, accumulate, leaf id)
+        self.tiles = 0
+        self.launches = 0
+
+    @staticmethod
+    def tiles_of(M: int, N: int) -> int:
+        return -(-M // 128) * -(-N // 192)
+
+    def accepts(self, dy2d, x2d) -> bool:
+        if not (dy2d.is_cuda and dy2d.dtype == torch.bfloat16 and x2d.dtype == torch.bfloat16):
+            return False
+        if dy2d.stride(1) != 1 or x2d.stride(1) != 1 or dy2d.stride(0) % 8 or x2d.stride(0) % 8:
+            return False
+        if dy2d.data_ptr() % 16 or x2d.data_ptr() % 16:
+            return False
+        return self.tiles_of(dy2d.shape[1], x2d.shape[1]) <= self.MAX_TILES_PER_PROBLEM
+
+    def add(self, dy2d, x2d, buf, accumulate: bool, nid: int) -> None:
+        if self.items and (self.items[0][0].shape[0] != dy2d.shape[0] or any(it[4] == nid for it in self.items)):
+            self.flush()       # another reduction length, or a second contribution to the same buffer
+        self.items.append((dy2d, x2d, buf, accumulate, nid))
+        self.tiles += self.tiles_of(dy2d.shape[1], x2d.shape[1])
+        if self.tiles >= self.FLUSH_TILES or len(self.items) == 8:
+            self.flush()
+
+    def flush(self) -> None:
+        if not self.items:
+            return
+        items, self.items, self.tiles = self.items, [], 0
+        K.gemm_grouped([(dy, x, buf, acc) for dy, x, buf, acc, _ in items])
+        self.launches += 1
+        fn = self.tape.leaf_grad_written_fn
+        if fn is not None:
+            for it in items:
+                fn(it[4])
+
+
+def enable_grouped_wgrad(tape: TensorTape) -> bool:
+    """Give ``tape`` a :class:`WgradQueue` (the fused rules use it when present).  Returns whether it is on."""
+    if WgradQueue.enabled and getattr(tape, "wgrad_queue", None) is None:
+        tape.wgrad_queue = WgradQueue(tape)
+    return getattr(tape, "wgrad_queue", None) is not None
+
+
 def _wgrad_into(targets, idx, dy2d, x2d, side: Optional["SideWork"] = None):
     """dW (+)= dy^T x, written into the bound gradient buffer when there is one."""
     run = side.wgrad if side is not None else K.linear_wgrad
     tgt = targets.leaf_target(idx)
+    queue = getattr(targets._tape, "wgrad_queue", None)
+    if tgt is not None and queue is not None and queue.accepts(dy2d, x2d):
+        buf, filled = tgt
+        nid = targets._node.inputs[idx]
+        targets._tape.nodes[nid].grad_buffer_filled = True       # the observer hears of it at the launch
+        queue.add(dy2d, x2d, buf, filled, nid)
+        return ACCUMULATED
     if tgt is not None:
         buf, filled = tgt
         run(dy2d, x2d, out=buf, accumulate=filled)

@@ -52,9 +52,36 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+# optional launch trace: while a list is installed, every launcher call appends its name (GEMMs with the tile
+# the planner picked); the training engine uses it to put the kernels of a step on the evidence ledger
+_TRACE: Optional[list] = None
+
+
+def trace_begin() -> None:
+    global _TRACE
+    _TRACE = []
+
+
+def trace_take() -> list:
+    """The launcher calls since the last take (or since ``trace_begin``); empties the trace."""
+    global _TRACE
+    if _TRACE is None:
+        return []
+    out, _TRACE = _TRACE, []
+    return out
+
+
+def trace_end() -> list:
+    global _TRACE
+    out, _TRACE = (_TRACE or []), None
+    return out
+
+
 def _chk(rc: int, what: str) -> None:
     global _launches
     _launches += 1
+    if _TRACE is not None:
+        _TRACE.append(what)
     if rc != 0:
         raise KernelError(f"{what}: launcher returned {rc}")
 
@@ -145,12 +172,49 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                     _WS_BUSY.pop(dev_key, None)
             else:
                 g.reduce_stream = reduce_stream = None
-    _chk(lib.ftk_gemm_bf16(C.byref(g), _stream()), "ftk_gemm_bf16")
+    what = "ftk_gemm_bf16"
+    if _TRACE is not None:          # name the tile the planner picks for this problem
+        bn, sp = C.c_int(0), C.c_int(1)
+        if lib.ftk_gemm_plan(C.byref(g), C.byref(bn), C.byref(sp)) == 0:
+            what = ("ftk::gemm2_bf16_sm100<256x256,cta_group2,splitK=%d>" % sp.value) if bn.value == 512 else \
+                ("ftk::gemm_bf16_sm100<128x%d,splitK=%d>" % (bn.value, sp.value))
+    _chk(lib.ftk_gemm_bf16(C.byref(g), _stream()), what)
     if reduce_stream is not None and g.workspace:
         ev = torch.cuda.Event()
         ev.record(torch.cuda.ExternalStream(reduce_stream, device=a.device))
         _WS_BUSY[dev_key] = ev
     return out
+
+
+def gemm_grouped(problems, *, a_mn: bool = True, b_mn: bool = True, max_ctas: int = 0) -> None:
+    """Several products with one reduction length in one launch: ``problems`` is a sequence of
+    ``(a, b, out, accumulate)`` with ``out`` fp32 ``[M_p, N_p]`` (``+=`` when ``accumulate``); operands as in
+    :func:`gemm` (the default layouts are those of a weight gradient, ``dW = dy^T x`` with ``a = dy [K, M]``,
+    ``b = x [K, N]``).  At most eight problems; every output element is reduced over K by one CTA, in order."""
+    n = len(problems)
+    if not 1 <= n <= 8:
+        raise KernelError("gemm_grouped takes 1 to 8 problems")
+    arr = (FtkGemmDesc * n)()
+    Kd = None
+    for g, (a, b, out, accumulate) in zip(arr, problems):
+        _bf16(a, "a"), _bf16(b, "b")
+        if a.dim() != 2 or b.dim() != 2 or a.stride(1) != 1 or b.stride(1) != 1:
+            raise KernelError("gemm operands must be 2-D with unit inner stride")
+        M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+        N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+        if K != Kb or (Kd is not None and K != Kd):
+            raise KernelError("gemm_grouped: all problems share one reduction length")
+        Kd = K
+        if out.dtype != torch.float32 or out.shape != (M, N) or out.stride(1) != 1:
+            raise KernelError("gemm_grouped outputs are fp32 [M, N] with unit inner stride")
+        g.M, g.N, g.K, g.L0, g.L1 = M, N, K, 1, 1
+        g.a_mn, g.b_mn = int(a_mn), int(b_mn)
+        g.A, g.lda = a.data_ptr(), a.stride(0)
+        g.B, g.ldb = b.data_ptr(), b.stride(0)
+        g.D, g.ldd = out.data_ptr(), out.stride(0)
+        g.alpha, g.out_fp32, g.accumulate, g.max_ctas = 1.0, 1, int(bool(accumulate)), int(max_ctas)
+    _chk(_lib.load().ftk_gemm_group_bf16(arr, n, _stream()),
+         "ftk::gemm_group_bf16_sm100<128x192,problems=%d>" % n)
 
 
 _WORKSPACES = {}

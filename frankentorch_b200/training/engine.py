@@ -35,7 +35,7 @@ class OptimConfig:
 
 class TrainEngine:
     def __init__(self, model, micro_batch: int, seq_len: int, optim: Optional[OptimConfig] = None, *,
-                 use_cuda_graph: bool = True, dp=None):
+                 use_cuda_graph: bool = True, dp=None, ledger=None):
         self.model = model
         self.tape = model.tape
         install_tape_ranges(self.tape)       # NVTX range per backward rule when FT_NVTX=1
@@ -68,6 +68,10 @@ class TrainEngine:
         self.launches_per_step = 0
         self.last_report = None
         self.steps_done = 0
+        # evidence ledger of the GPU path: the first step that runs eagerly (the one before graph capture, or
+        # the first step of an eager engine) is observed and written down once, see training/step_ledger.py
+        self.ledger = ledger
+        self._ledger_done = ledger is None
 
     def _wire_param_gates(self) -> None:
         """A model with a ``param_gate`` slot tells the data-parallel object which parameters its
@@ -123,6 +127,16 @@ class TrainEngine:
                             beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay)
 
     def _step_body(self) -> None:
+        if not self._ledger_done and not torch.cuda.is_current_stream_capturing():
+            self._ledger_done = True
+            from .step_ledger import StepLedger
+            with StepLedger(self.tape, self.ledger) as sl:
+                self._step_body_inner(sl)
+            sl.record_backward(self.last_report)
+            return
+        self._step_body_inner(None)
+
+    def _step_body_inner(self, sl) -> None:
         n0 = K.launch_count()
         if self.dp is not None and hasattr(self.dp, "begin_step"):
             self.dp.begin_step()
@@ -132,6 +146,8 @@ class TrainEngine:
         loss_id = self.model.forward(self.ids, self.targets)
         self.last_report = self.tape.backward(loss_id, BackwardOptions())
         self.loss_dev.copy_(self.tape.value(loss_id))
+        if sl is not None:
+            K.trace_take()          # accumulation kernels after the last rule belong to no operator
         self._optimizer()
         self.tape.truncate_graph_to(self.model.param_boundary)
         self.launches_per_step = K.launch_count() - n0

@@ -145,6 +145,37 @@ def test_gemm_split_k_deterministic_and_correct(cuda_device):
     k.check_status()
 
 
+def test_gemm_grouped_weight_gradients(cuda_device):
+    """Four weight gradients of different extents in one launch: each against its fp32 reference per 128 x 128
+    tile, with accumulation into one of them, on ragged extents, identical on a smaller grid and run to run."""
+    k = _ops()
+    T = 2048
+    shapes = ((2304, 768), (768, 768), (3072, 768), (768, 3072), (200, 136))
+    dys = [_rand((T, m), cuda_device, 0.5, 40 + i) for i, (m, n) in enumerate(shapes)]
+    xs = [_rand((T, n), cuda_device, 0.5, 50 + i) for i, (m, n) in enumerate(shapes)]
+    refs = [dy.float().t() @ x.float() for dy, x in zip(dys, xs)]
+
+    def run(max_ctas=0):
+        outs = [torch.full((m, n), 3.0 if i == 1 else float("nan"), dtype=torch.float32, device=cuda_device)
+                for i, (m, n) in enumerate(shapes)]
+        k.gemm_grouped([(dy, x, o, i == 1) for i, (dy, x, o) in enumerate(zip(dys, xs, outs))], max_ctas=max_ctas)
+        return outs
+    outs = run()
+    k.check_status()
+    for i, (o, r) in enumerate(zip(outs, refs)):
+        want = r + 3.0 if i == 1 else r
+        _check(o, want, 5e-3, f"grouped problem {i}")     # includes the per-tile check
+    again, small = run(), run(max_ctas=37)
+    for a, b, c in zip(outs, again, small):
+        assert torch.equal(a, b) and torch.equal(a, c)
+    # one problem alone equals the plain GEMM without split-K, bit for bit (same k-block order)
+    solo = torch.empty((768, 768), dtype=torch.float32, device=cuda_device)
+    k.gemm_grouped([(dys[1], xs[1], solo, False)])
+    plain = k.gemm(dys[1], xs[1], a_mn=True, b_mn=True, out_dtype=torch.float32, split_k=1, force_bn=192)
+    assert torch.equal(solo, plain)
+    k.check_status()
+
+
 def test_gemm_batched(cuda_device):
     k = _ops()
     L0, L1, M, N, K = 3, 2, 256, 128, 64

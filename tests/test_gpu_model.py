@@ -101,6 +101,77 @@ def test_engine_trains(cuda_device, graph):
     assert int(eng.step_dev.item()) == 8
 
 
+def test_grouped_weight_gradients_match_the_direct_path(cuda_device, monkeypatch):
+    """The queue that launches a block's weight gradients together changes the schedule, not the gradients:
+    against the direct path (one GEMM per weight gradient, split-K where the planner wants it) every parameter
+    gradient agrees to fp32 summation-order accuracy, and the queue really was used."""
+    from frankentorch_b200.autograd.tape import BackwardOptions
+    from frankentorch_b200.ops import fused
+    grads, launches = [], []
+    for on in (True, False):
+        monkeypatch.setattr(fused.WgradQueue, "enabled", on)
+        cfg, tape, model = _build(cuda_device, seed=9)
+        assert (getattr(tape, "wgrad_queue", None) is not None) == on
+        g = torch.Generator().manual_seed(4)
+        tok = torch.randint(0, cfg.vocab_size, (2, 129), generator=g).to(cuda_device)
+        model.reset_grads()
+        loss = model.forward(tok[:, :-1].contiguous(), tok[:, 1:].contiguous())
+        tape.backward(loss, BackwardOptions())
+        torch.cuda.synchronize()
+        grads.append(model.arena.grads.clone())
+        launches.append(tape.wgrad_queue.launches if on else 0)
+    assert launches[0] >= 1
+    scale = float(grads[1].abs().max())
+    assert float((grads[0] - grads[1]).abs().max()) <= 2e-4 * scale
+    for name, _ in model.arena.specs:
+        a, b = model.arena.view(grads[0], name), model.arena.view(grads[1], name)
+        assert float((a - b).abs().max()) <= 1e-3 * float(b.abs().max()) + 1e-7, name
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_training_step_is_on_the_evidence_ledger(cuda_device, graph):
+    """The GPU training path writes what it dispatches to an EvidenceLedger: once (the eager step before the
+    capture), one interned entry per (phase, operator, shape, kernels) naming launcher calls that were really
+    made, plus the backward telemetry; replays add nothing."""
+    from frankentorch_b200.ops import kernels as K
+    from frankentorch_b200.runtime.ledger import EvidenceKind, EvidenceLedger
+    from frankentorch_b200.training.engine import OptimConfig, TrainEngine
+    cfg, tape, model = _build(cuda_device, seed=6)
+    ledger = EvidenceLedger()
+    eng = TrainEngine(model, 2, 128, OptimConfig(lr=1e-3, grad_clip=1.0), use_cuda_graph=graph, ledger=ledger)
+    g = torch.Generator().manual_seed(2)
+    tok = torch.randint(0, cfg.vocab_size, (2, 129), generator=g)
+    ids, tgt = tok[:, :-1].contiguous().pin_memory(), tok[:, 1:].contiguous().pin_memory()
+    eng.step(ids, tgt)
+    n = len(ledger)
+    assert n > 10
+    for _ in range(3):
+        eng.step(ids, tgt)
+    K.check_status()
+    assert len(ledger) == n, "replayed steps must not grow the ledger"
+    entries = ledger.entries()
+    disp = [e.summary for e in entries if e.kind == EvidenceKind.Dispatch]
+    back = [e.summary for e in entries if e.kind == EvidenceKind.Backward]
+    assert len(back) == 1 and "order_fnv1a=" in back[0] and "nodes=" in back[0]
+    fwd = [s for s in disp if "phase=fwd" in s]
+    bwd = [s for s in disp if "phase=bwd" in s]
+    opt = [s for s in disp if "phase=optimizer" in s]
+    assert fwd and bwd and len(opt) == 1
+    assert all("backend=sm100" in s and "mode=strict" in s for s in disp)
+    # every forward GEMM-bearing operator names the tcgen05 kernel and the tile the planner chose
+    lin = [s for s in fwd if s.startswith("op=linear")]
+    assert lin and all("ftk::gemm" in s and "splitK=" in s for s in lin)
+    assert any("ftk_attn_fwd" in s for s in fwd) and any("ftk_attn_bwd" in s for s in bwd)
+    assert "ftk_adamw_dev" in opt[0]
+    # the counts add up to the nodes of the step: 2 layers x the operators of a block, not one entry per node
+    total = sum(int(s.rsplit("count=", 1)[1]) for s in fwd)
+    assert total >= 2 * 6 and len(fwd) < total
+    # nothing on the ledger names a kernel that was not launched: the trace saw exactly launches_per_step calls
+    launched = sum(int(s.rsplit("count=", 1)[1]) * len(s.split("kernel=[", 1)[1].split("] out=", 1)[0].split(", "))
+                   for s in disp if "kernel=[-]" not in s)
+    assert launched <= eng.launches_per_step
+
+
 def _tile_rel_err(got, want, tile=128):
     """Max over ``tile x tile`` tiles of (max abs error in the tile) / (max abs reference in the tile):
     a wrong low-magnitude tile cannot hide behind large values elsewhere in the matrix."""
