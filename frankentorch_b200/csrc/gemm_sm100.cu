@@ -278,16 +278,27 @@ static int plan_gemm(const FtkGemmDesc* g, int* bn_out, int* splits_out) {
                           (g->N % 4 == 0) && (g->ldd % 4 == 0) && L0 * L1 == 1 && !g->seg_counts;
   // Option 512 is the CTA-pair kernel: 256 x 256 tiles on sms / 2 clusters; per SM it does the
   // work of a 128 x 256 tile with a third less operand traffic.
+  // The unit is the time of one 128 x 256 tile over all of K on one SM at the sustained rate (~6.9 ns per
+  // unit of K).  A split costs the reduction kernel: s fp32 partials read, the output written (and read when
+  // it accumulates) at ~4 TB/s plus a launch - 17 us for an [8192, 768] bf16 output with two splits, which is
+  // why an activation-sized output is hardly ever worth splitting while a weight gradient is.
+  const double unit_us = 6.93e-3 * (double)g->K;
+  auto split_penalty = [&](int s) {
+    if (s <= 1) return 0.0;
+    const double mn = (double)g->M * (double)g->N;
+    const double bytes = mn * 4.0 * s + mn * (g->out_fp32 ? 4.0 : 2.0) * (g->accumulate ? 2.0 : 1.0);
+    return (bytes / 4.0e6 + 3.0) / unit_us;
+  };
   auto cost = [&](int bn, int s) {
     if (bn == 512) {
       const long long tiles = ((g->M + 255) / 256) * ((g->N + 255) / 256) * L0 * L1;
       const long long waves = (tiles * s + sms / 2 - 1) / (sms / 2);
-      return (double)waves * pair_tile_cost() / s + (s > 1 ? 0.08 + 0.01 * s : 0.0);
+      return (double)waves * pair_tile_cost() / s + split_penalty(s);
     }
     const long long tiles = tiles_m * ((g->N + bn - 1) / bn) * L0 * L1;
     const long long waves = (tiles * s + sms - 1) / sms;
     const double w = bn == 256 ? 1.0 : (bn == 192 ? 0.80 : 0.86);
-    return (double)waves * w / s + (s > 1 ? 0.08 + 0.01 * s : 0.0);
+    return (double)waves * w / s + split_penalty(s);
   };
   auto split_ok = [&](int s) {
     if (s == 1) return true;

@@ -81,6 +81,8 @@ class MoEGPT:
                 tape.bind_grad_buffer(nid, arena.view(arena.grads, name))
                 self.leaf[name] = nid
         self.param_boundary = len(tape)
+        from ..ops.fused import enable_grouped_wgrad
+        enable_grouped_wgrad(tape)       # a block's weight gradients are launched together
 
     def _init_weights(self, seed: int) -> None:
         cfg = self.cfg

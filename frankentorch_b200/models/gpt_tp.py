@@ -71,6 +71,8 @@ class TensorParallelGPT:
                 tape.bind_grad_buffer(nid, arena.view(arena.grads, name))
                 self.leaf[name] = nid
         self.param_boundary = len(tape)
+        from ..ops.fused import enable_grouped_wgrad
+        enable_grouped_wgrad(tape)       # a block's weight gradients are launched together
 
     # ------------------------------------------------------------------ initialisation
     def _init_weights(self, seed: int) -> None:
