@@ -245,9 +245,26 @@ def bench_dp_world1(n_params, iters, warm):
     ops.check_status()
 
 
+def bench_group(tokens, d, iters, warm):
+    """The four weight gradients of a transformer block (qkv, proj, fc1, fc2) as one grouped launch, against
+    the same four as separate GEMMs (split-K where the planner wants it) and against cuBLAS."""
+    pk = peaks()
+    shapes = ((3 * d, d), (d, d), (4 * d, d), (d, 4 * d))
+    dys = [bf(tokens, m) for m, n in shapes]
+    xs = [bf(tokens, n) for m, n in shapes]
+    outs = [torch.zeros(m, n, device="cuda") for m, n in shapes]
+    flops = sum(2.0 * tokens * m * n for m, n in shapes)
+    t_g = timeit(lambda: ops.gemm_grouped([(dy, x, o, False) for dy, x, o in zip(dys, xs, outs)]), iters, warm)
+    t_s = timeit(lambda: [ops.gemm(dy, x, a_mn=True, b_mn=True, out=o) for dy, x, o in zip(dys, xs, outs)], iters, warm)
+    t_c = timeit(lambda: [torch.matmul(dy.t(), x) for dy, x in zip(dys, xs)], iters, warm)
+    print(f"grouped wgrad T{tokens} d{d}: {t_g*1e3:8.1f} us {flops/t_g/1e9:7.1f} TF/s ({flops/t_g/1e9/pk['bf16_tflops']:.2f} of "
+          f"{pk['src']} peak) | four separate launches {t_s*1e3:8.1f} us | cuBLAS x4 (bf16 out) {t_c*1e3:8.1f} us", flush=True)
+    ops.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "sweep", "rows", "dp"])
+    ap.add_argument("what", choices=["gemm", "attn", "sweep", "rows", "dp", "group"])
     ap.add_argument("--case", default="all")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--cols", type=int, default=768)
@@ -279,6 +296,8 @@ def _dispatch(a):
         bench_rows(a.case, a.rows, a.cols, a.iters, a.warmup)
     elif a.what == "dp":
         bench_dp_world1(a.params, a.iters, a.warmup)
+    elif a.what == "group":
+        bench_group(a.m, a.k, a.iters, a.warmup)
     else:
         for (N, Kd) in [(2304, 768), (768, 768), (3072, 768), (768, 3072), (50304, 768),
                         (3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (8192, 8192)]:
