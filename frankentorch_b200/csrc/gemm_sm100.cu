@@ -293,7 +293,15 @@ static int plan_gemm(const FtkGemmDesc* g, int* bn_out, int* splits_out) {
     if (bn == 512) {
       const long long tiles = ((g->M + 255) / 256) * ((g->N + 255) / 256) * L0 * L1;
       const long long waves = (tiles * s + sms / 2 - 1) / (sms / 2);
-      return (double)waves * pair_tile_cost() / s + split_penalty(s);
+      // A pair tile has twice the epilogue of a single one and a longer pipeline fill, which a long K
+      // amortises: measured against 128 x 192 tiles it costs ~1.0 at K = 768 and ~0.72 at K = 3072
+      // (8192 x 768 x 2304: 37.5 vs 45.8 us, x 3072: 47.5 vs 53.0 us), and about a tenth more when B is given
+      // [K, N] (8192 x 3072 x 768: 65.2 vs 54.3 us).  The base value is the K = 768 calibration.
+      double kr = 768.0 * s / (double)g->K;
+      if (kr > 1.5) kr = 1.5;
+      static const bool k_scaled = !(getenv("FT_GEMM_PAIR_KSCALE") && atoi(getenv("FT_GEMM_PAIR_KSCALE")) == 0);
+      const double c = k_scaled ? pair_tile_cost() * (0.608 + 0.392 * kr) * (g->b_mn ? 1.08 : 1.0) : pair_tile_cost();
+      return (double)waves * c / s + split_penalty(s);
     }
     const long long tiles = tiles_m * ((g->N + bn - 1) / bn) * L0 * L1;
     const long long waves = (tiles * s + sms - 1) / sms;
