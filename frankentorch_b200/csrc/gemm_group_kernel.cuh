@@ -8,7 +8,7 @@
 // reduced over K by one CTA in k-block order, which is also the simplest deterministic order there is.
 //
 // The kernel is the single-CTA tcgen05 GEMM of gemm_kernel.cuh (TMA producer warp, MMA issuer warp, eight
-// epilogue warps, four-stage operand ring, two TMEM accumulators, bounded waits with the shared status word)
+// epilogue warps, operand ring, two TMEM accumulators, bounded waits with the shared status word)
 // reduced to what a weight gradient needs - fp32 output with optional accumulation, no bias / activation /
 // residual, no split, no collective - plus a table of problems: a work item is (problem, n tile, m tile),
 // items are dealt round robin to the CTAs, and each problem brings its own pair of tensor maps.
@@ -21,6 +21,11 @@ namespace ftk {
 
 constexpr int GG_MAX = 8;   // problems per launch
 constexpr int GG_BN = 192;
+// Five operand stages (the single-product kernel has four plus 32 KB of output staging tiles, which an fp32
+// store epilogue does not need): with both operands MN-major a stage is five TMA boxes, and at four stages
+// the tensor pipe sat at 50 % waiting for them.
+constexpr int GG_STAGES = 5;
+constexpr int GG_SMEM = GG_STAGES * (G_BM * G_BK * 2 + GG_BN * G_BK * 2) + 1024 /*align*/ + 256 /*barriers*/;
 
 struct GroupArgs {
   int n;                       // number of problems
@@ -62,11 +67,11 @@ gemm_group_bf16_sm100_kernel(const __grid_constant__ GroupMaps maps, const Group
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
-  uint8_t* sB = smem + Cfg::STAGES * Cfg::A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * (Cfg::A_BYTES + Cfg::B_BYTES));
+  uint8_t* sB = smem + GG_STAGES * Cfg::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GG_STAGES * (Cfg::A_BYTES + Cfg::B_BYTES));
   uint64_t* full = bars;
-  uint64_t* empty = bars + Cfg::STAGES;
-  uint64_t* tfull = bars + 2 * Cfg::STAGES;
+  uint64_t* empty = bars + GG_STAGES;
+  uint64_t* tfull = bars + 2 * GG_STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   int* abort_f = reinterpret_cast<int*>(tmem_slot + 1);
@@ -76,7 +81,7 @@ gemm_group_bf16_sm100_kernel(const __grid_constant__ GroupMaps maps, const Group
   WaitCtx ctx{g.status, abort_f};
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < Cfg::STAGES; ++i) {
+    for (int i = 0; i < GG_STAGES; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
@@ -138,7 +143,7 @@ gemm_group_bf16_sm100_kernel(const __grid_constant__ GroupMaps maps, const Group
           }
         }
         __syncwarp();
-        if (++s == Cfg::STAGES) {
+        if (++s == GG_STAGES) {
           s = 0;
           ph ^= 1u;
         }
@@ -177,7 +182,7 @@ gemm_group_bf16_sm100_kernel(const __grid_constant__ GroupMaps maps, const Group
           if (kb == kblocks - 1) umma_commit(&tfull[acc]);
         }
         __syncwarp();
-        if (++s == Cfg::STAGES) {
+        if (++s == GG_STAGES) {
           s = 0;
           ph ^= 1u;
         }

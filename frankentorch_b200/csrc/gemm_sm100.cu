@@ -378,13 +378,13 @@ extern "C" int ftk_gemm_group_bf16(const FtkGemmDesc* descs, int n, void* stream
   bool* attr_set_p = once.slot();
   if (!*attr_set_p) {
     cudaError_t e = cudaFuncSetAttribute(gemm_group_bf16_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM);
+                                         GG_SMEM);
     if (e != cudaSuccess) return (int)e;
     *attr_set_p = true;
   }
   const int sms = g0.max_ctas > 0 ? g0.max_ctas : num_sms();
   const int grid = total < sms ? total : sms;
-  gemm_group_bf16_sm100_kernel<<<grid, G_THREADS, Cfg::SMEM, stream>>>(maps, ga);
+  gemm_group_bf16_sm100_kernel<<<grid, G_THREADS, GG_SMEM, stream>>>(maps, ga);
   return (int)cudaGetLastError();
 }
 
