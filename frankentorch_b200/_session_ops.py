@@ -23,6 +23,7 @@ from .runtime.ledger import EvidenceKind
 
 _INDEX_INPUT_OPS = {"index_select": (1,), "gather": (1,), "scatter": (1,), "scatter_add": (1,), "masked_fill": (1,),
                     "where": (0,), "embedding": (1,), "index_select_sparse": (1,), "cross_entropy": (1,), "nll_loss": (1,), "multi_margin_loss": (1,),
+                    "multilabel_margin_loss": (1,), "max_unpool1d": (1,), "max_unpool2d": (1,), "max_unpool3d": (1,),
                     "embedding_bag": (1, 2), "index_put": (1,), "masked_select": (1,), "ctc_loss": (1, 2, 3)}
 _MATMUL_CLASS = {"matmul", "bmm", "linear", "addmm", "mv", "baddbmm", "addbmm", "conv1d", "conv2d", "conv3d", "sdpa"}
 

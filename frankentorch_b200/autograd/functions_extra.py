@@ -323,6 +323,38 @@ _generic("fractional_max_pool2d", _fractional_max_pool2d, "max pool over pseudo-
 _nograd("max_pool2d_indices", lambda x, kernel_size=2, stride=None, padding=0:
         torch.nn.functional.max_pool2d(x, kernel_size, stride, padding, return_indices=True)[1].to(torch.float64),
         "flat arg-max positions of max_pool2d; no gradient")
+_generic("max_unpool1d", lambda x, indices, kernel_size=2, stride=None, padding=0, output_size=None:
+         torch.nn.functional.max_unpool1d(x, indices.long(), kernel_size, stride, padding, output_size),
+         "d(max_unpool)/dx = gather of g at the indices")
+_generic("max_unpool3d", lambda x, indices, kernel_size=2, stride=None, padding=0, output_size=None:
+         torch.nn.functional.max_unpool3d(x, indices.long(), kernel_size, stride, padding, output_size),
+         "d(max_unpool)/dx = gather of g at the indices")
+_nograd("max_pool1d_indices", lambda x, kernel_size=2, stride=None, padding=0:
+        torch.nn.functional.max_pool1d(x, kernel_size, stride, padding, return_indices=True)[1].to(torch.float64),
+        "flat arg-max positions of max_pool1d; no gradient")
+_nograd("max_pool3d_indices", lambda x, kernel_size=2, stride=None, padding=0:
+        torch.nn.functional.max_pool3d(x, kernel_size, stride, padding, return_indices=True)[1].to(torch.float64),
+        "flat arg-max positions of max_pool3d; no gradient")
+
+
+def _fractional_max_pool3d(x, kernel_size=2, output_size=None, output_ratio=None, samples=None):
+    """Fractional max pooling over volumes with caller-supplied ``samples[N,C,3]`` in [0,1) (deterministic)."""
+    if samples is None:
+        samples = torch.full((x.shape[0], x.shape[1], 3), 0.5, dtype=x.dtype, device=x.device)
+    return torch.nn.functional.fractional_max_pool3d(x, kernel_size, output_size, output_ratio,
+                                                     _random_samples=samples)
+
+
+_generic("fractional_max_pool3d", _fractional_max_pool3d, "max pool over pseudo-random windows: gradient to the arg-max")
+_generic("lp_pool3d", lambda x, norm_type=2.0, kernel_size=2, stride=None:
+         torch.nn.functional.lp_pool3d(x, norm_type, kernel_size, stride),
+         "d((sum |x|^p)^(1/p))/dx over each window")
+_generic("multilabel_margin_loss", lambda x, t, reduction="mean":
+         torch.nn.functional.multilabel_margin_loss(x, t.long(), reduction=reduction),
+         "d(sum_j sum_i max(0, 1 - (x[y_j] - x_i)) / C)/dx")
+_generic("multilabel_soft_margin_loss", lambda x, t, reduction="mean":
+         torch.nn.functional.multilabel_soft_margin_loss(x, t, reduction=reduction),
+         "d(-mean_c [y log sigmoid(x) + (1-y) log sigmoid(-x)])/dx")
 _generic("max_unpool2d", lambda x, indices, kernel_size=2, stride=None, padding=0, output_size=None:
          torch.nn.functional.max_unpool2d(x, indices.long(), kernel_size, stride, padding, output_size),
          "d(max_unpool)/dx = gather of g at the indices")

@@ -203,7 +203,8 @@ _generic("group_norm", lambda x, w=None, b=None, groups=1, eps=1e-5: TF.group_no
 _generic("batch_norm", lambda x, w=None, b=None, eps=1e-5: TF.batch_norm(x, None, None, w, b, True, 0.0, eps))
 _generic("instance_norm", lambda x, w=None, b=None, eps=1e-5: TF.instance_norm(x, None, None, w, b, True, 0.0, eps))
 _generic("local_response_norm", lambda x, size=5, alpha=1e-4, beta=0.75, k=1.0: TF.local_response_norm(x, size, alpha, beta, k))
-_generic("interpolate", lambda x, size=None, scale_factor=None, mode="nearest": TF.interpolate(x, size=size, scale_factor=scale_factor, mode=mode))
+_generic("interpolate", lambda x, size=None, scale_factor=None, mode="nearest", align_corners=None:
+         TF.interpolate(x, size=size, scale_factor=scale_factor, mode=mode, align_corners=align_corners))
 _generic("grid_sample", lambda x, grid, mode="bilinear", padding_mode="zeros", align_corners=False: TF.grid_sample(x, grid, mode=mode, padding_mode=padding_mode, align_corners=align_corners))
 _generic("affine_grid", lambda theta, size=(), align_corners=False: TF.affine_grid(theta, list(size), align_corners=align_corners))
 _generic("pixel_shuffle", lambda x, r=2: TF.pixel_shuffle(x, r))

@@ -6,8 +6,11 @@ from .module import (LoadStateDictReport, Module, ModuleDict, ModuleError, Modul
                      module_state_dict, named_buffers, named_modules, named_parameters, parameters_to_vector,
                      vector_to_parameters)
 from .transformer import *  # noqa: F401,F403
-from .extra import (AdaptiveLogSoftmaxWithLoss, FractionalMaxPool2d, LazyConv1d, LazyConv2d, LazyConv3d,  # noqa: F401
-                    MaxPool2dWithIndices, MaxUnpool2d)
+from .extra import (AdaptiveLogSoftmaxWithLoss, FractionalMaxPool2d, FractionalMaxPool3d, GRUOutput,  # noqa: F401
+                    LazyConv1d, LazyConv2d, LazyConv3d, LPPool3d, LSTMOutput, MaxPool2dWithIndices, MaxUnpool1d,
+                    MaxUnpool2d, MaxUnpool3d, MultiLabelMarginLoss, MultiLabelSoftMarginLoss, RNNConfig, RNNOutput,
+                    TripletMarginWithDistanceLoss, Upsample, Upsample1d, Upsample2d, Upsample3d,
+                    UpsamplingBilinear2d, UpsamplingNearest2d)
 from .utils import (MinMaxObserver, PackedSequence, QParams, QuantizedLinear, SpectralNorm, WeightNorm, dequantize,
                     pack_padded_sequence, pack_sequence, pad_packed_sequence, pad_sequence, quantize_per_tensor,
                     spectral_norm, weight_norm)

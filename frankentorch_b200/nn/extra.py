@@ -118,3 +118,158 @@ class AdaptiveLogSoftmaxWithLoss(Module):
 
     def predict(self, session, x) -> int:
         return session.tensor_argmax(self.log_prob(session, x), 1)
+
+
+# ---------------------------------------------------------------------------------- remaining pools / unpools
+class FractionalMaxPool3d(FractionalMaxPool2d):
+    """Volume form of :class:`FractionalMaxPool2d` (``samples[N, C, 3]``)."""
+
+    def forward(self, session, x):
+        samples = None
+        if self.training:
+            n, c = session.tensor_shape(x)[:2]
+            samples = session.tensor(session.rand([n, c, 3])).to(session.tensor(x).dtype)
+        return session.tensor_fractional_max_pool3d(x, kernel_size=self.kernel_size, output_size=self.output_size,
+                                                    output_ratio=self.output_ratio, samples=samples)
+
+
+class LPPool3d(Module):
+    def __init__(self, norm_type: float, kernel_size, stride=None):
+        super().__init__()
+        self.kw = dict(norm_type=float(norm_type), kernel_size=kernel_size, stride=stride)
+
+    def forward(self, session, x):
+        return session.tensor_lp_pool3d(x, **self.kw)
+
+
+class MaxUnpool1d(MaxUnpool2d):
+    def forward(self, session, x, indices, output_size=None):
+        return session.tensor_max_unpool1d(x, indices, output_size=output_size, **self.kw)
+
+
+class MaxUnpool3d(MaxUnpool2d):
+    def forward(self, session, x, indices, output_size=None):
+        return session.tensor_max_unpool3d(x, indices, output_size=output_size, **self.kw)
+
+
+# ---------------------------------------------------------------------------------- upsampling
+class Upsample(Module):
+    """``interpolate`` as a module: give ``size`` or ``scale_factor``; ``mode`` as in ``tensor_interpolate``."""
+
+    ndim = 0        # 0: any
+
+    def __init__(self, size=None, scale_factor=None, mode: str = "nearest", align_corners=None):
+        super().__init__()
+        if (size is None) == (scale_factor is None):
+            raise ValueError("give exactly one of size and scale_factor")
+        self.kw = dict(size=size, scale_factor=scale_factor, mode=mode, align_corners=align_corners)
+
+    def forward(self, session, x):
+        if self.ndim and len(session.tensor_shape(x)) != self.ndim + 2:
+            raise ValueError(f"{type(self).__name__} expects a [N, C, {self.ndim} spatial dims] input")
+        return session.tensor_interpolate(x, **{k: v for k, v in self.kw.items() if v is not None})
+
+
+class Upsample1d(Upsample):
+    ndim = 1
+
+
+class Upsample2d(Upsample):
+    ndim = 2
+
+
+class Upsample3d(Upsample):
+    ndim = 3
+
+
+class UpsamplingNearest2d(Upsample2d):
+    def __init__(self, size=None, scale_factor=None):
+        super().__init__(size, scale_factor, mode="nearest")
+
+
+class UpsamplingBilinear2d(Upsample2d):
+    def __init__(self, size=None, scale_factor=None):
+        super().__init__(size, scale_factor, mode="bilinear", align_corners=True)
+
+
+# ---------------------------------------------------------------------------------- losses
+class MultiLabelMarginLoss(Module):
+    def __init__(self, reduction: str = "mean"):
+        super().__init__()
+        self.reduction = reduction
+
+    def forward(self, session, x, target):
+        return session.tensor_multilabel_margin_loss(x, target, reduction=self.reduction)
+
+
+class MultiLabelSoftMarginLoss(Module):
+    def __init__(self, reduction: str = "mean"):
+        super().__init__()
+        self.reduction = reduction
+
+    def forward(self, session, x, target):
+        return session.tensor_multilabel_soft_margin_loss(x, target, reduction=self.reduction)
+
+
+class TripletMarginWithDistanceLoss(Module):
+    """``mean(max(d(a, p) - d(a, n) + margin, 0))`` with a caller-supplied distance
+    ``distance_function(session, x, y) -> node`` (default: pairwise L2 distance); ``swap`` uses
+    ``min(d(a, n), d(p, n))`` for the negative distance."""
+
+    def __init__(self, distance_function=None, margin: float = 1.0, swap: bool = False, reduction: str = "mean"):
+        super().__init__()
+        self.distance_function, self.margin, self.swap, self.reduction = distance_function, float(margin), swap, reduction
+
+    def forward(self, session, anchor, positive, negative):
+        dist = self.distance_function or (lambda s, x, y: s.tensor_pairwise_distance(x, y))
+        d_ap, d_an = dist(session, anchor, positive), dist(session, anchor, negative)
+        if self.swap:
+            d_pn = dist(session, positive, negative)           # min(a, b) = a - relu(a - b)
+            d_an = session.tensor_sub(d_an, session.tensor_relu(session.tensor_sub(d_an, d_pn)))
+        loss = session.tensor_relu(session.tensor_add_scalar(session.tensor_sub(d_ap, d_an), self.margin))
+        if self.reduction == "mean":
+            return session.tensor_mean(loss)
+        if self.reduction == "sum":
+            return session.tensor_sum(loss)
+        return loss
+
+
+# ---------------------------------------------------------------------------------- recurrent records
+from dataclasses import dataclass as _dataclass  # noqa: E402
+from typing import NamedTuple as _NamedTuple  # noqa: E402
+
+
+@_dataclass(frozen=True)
+class RNNConfig:
+    """Constructor arguments of the recurrent stacks (ft-nn's ``RNNConfig``); ``build`` makes the module."""
+    input_size: int
+    hidden_size: int
+    num_layers: int = 1
+    bias: bool = True
+    batch_first: bool = False
+    dropout: float = 0.0
+    bidirectional: bool = False
+
+    def build(self, session, kind: str = "rnn"):
+        from . import transformer as _t
+        cls = {"rnn": _t.RNN, "gru": _t.GRU, "lstm": _t.LSTM}[kind]
+        import inspect
+        allowed = set(inspect.signature(cls.__init__).parameters)
+        kw = {k: v for k, v in self.__dict__.items() if k in allowed}
+        return cls(session, **kw)
+
+
+class RNNOutput(_NamedTuple):
+    output: int          # node id of the output sequence
+    h_n: int             # node id of the final hidden state
+
+
+class GRUOutput(_NamedTuple):
+    output: int
+    h_n: int
+
+
+class LSTMOutput(_NamedTuple):
+    output: int
+    h_n: int
+    c_n: int

@@ -256,3 +256,51 @@ def test_core_tensors_pool_and_sparse():
     assert recycle(big) and stats().parked == 1
     again = take_zeroed(1 << 16)
     assert stats().hits >= 1 and again.numel() == 1 << 16
+
+
+def test_remaining_pool_upsample_and_margin_modules_match_torch():
+    """Modules that complete the reference's ft-nn inventory: upsampling family, 3-d pools and unpools, the
+    multilabel margin losses, the triplet loss with a distance function, the recurrent records."""
+    import torch
+    import torch.nn.functional as TF
+
+    import frankentorch_b200.nn as nn
+    from frankentorch_b200.session import FrankenTorchSession
+    s = FrankenTorchSession("strict", ledger_dispatch=False)
+    x = s.randn([2, 3, 8, 8], requires_grad=True)
+    xt = s.tensor(x)
+    up = nn.UpsamplingBilinear2d(scale_factor=2).forward(s, x)
+    assert torch.allclose(s.tensor(up), TF.interpolate(xt, scale_factor=2, mode="bilinear", align_corners=True))
+    assert torch.equal(s.tensor(nn.UpsamplingNearest2d(size=(5, 7)).forward(s, x)), TF.interpolate(xt, size=(5, 7)))
+    with __import__("pytest").raises(ValueError):
+        nn.Upsample1d(scale_factor=2).forward(s, x)
+    v = s.randn([1, 2, 6, 6, 6], requires_grad=True)
+    vt = s.tensor(v)
+    assert torch.allclose(s.tensor(nn.LPPool3d(2.0, 2).forward(s, v)), TF.lp_pool3d(vt, 2.0, 2))
+    pooled, idx = TF.max_pool3d(vt, 2, return_indices=True)
+    p = s.tensor_max_pool3d(v, kernel_size=2)
+    un = nn.MaxUnpool3d(2).forward(s, p, s.tensor_max_pool3d_indices(v, kernel_size=2))
+    assert torch.equal(s.tensor(un), TF.max_unpool3d(pooled, idx, 2))
+    w = s.randn([2, 3, 10], requires_grad=True)
+    p1, i1 = TF.max_pool1d(s.tensor(w), 2, return_indices=True)
+    un1 = nn.MaxUnpool1d(2).forward(s, s.tensor_max_pool1d(w, kernel_size=2), s.tensor_max_pool1d_indices(w, kernel_size=2))
+    assert torch.equal(s.tensor(un1), TF.max_unpool1d(p1, i1, 2))
+    fm = nn.FractionalMaxPool3d(2, output_size=(3, 3, 3))
+    fm.training = False
+    assert s.tensor_shape(fm.forward(s, v)) == [1, 2, 3, 3, 3]
+    a, b, c = (s.randn([4, 5], requires_grad=True) for _ in range(3))
+    loss = nn.TripletMarginWithDistanceLoss(swap=True, margin=0.7).forward(s, a, b, c)
+    rep = s.tensor_backward(loss)
+    ta, tb, tc = (s.tensor(t).clone().requires_grad_(True) for t in (a, b, c))
+    ref = TF.triplet_margin_with_distance_loss(ta, tb, tc, swap=True, margin=0.7)
+    ref.backward()
+    assert torch.allclose(s.tensor(loss), ref) and torch.allclose(rep.gradient(a), ta.grad, atol=1e-12)
+    t = s.tensor_variable_from_storage(torch.tensor([[3, 0, -1, 1], [1, 2, 3, -1]], dtype=torch.float64), False)
+    xx = s.randn([2, 4], requires_grad=True)
+    got = nn.MultiLabelMarginLoss().forward(s, xx, t)
+    assert torch.allclose(s.tensor(got), TF.multilabel_margin_loss(s.tensor(xx), s.tensor(t).long()))
+    y = s.tensor_variable_from_storage((torch.rand(2, 4, dtype=torch.float64) > 0.5).double(), False)
+    got = nn.MultiLabelSoftMarginLoss().forward(s, xx, y)
+    assert torch.allclose(s.tensor(got), TF.multilabel_soft_margin_loss(s.tensor(xx), s.tensor(y)))
+    assert type(nn.RNNConfig(4, 8).build(s, "gru")).__name__ == "GRU"
+    assert nn.LSTMOutput(1, 2, 3).c_n == 3 and nn.RNNOutput(1, 2).h_n == 2 and nn.GRUOutput(5, 6).output == 5
