@@ -114,7 +114,7 @@ def main():
         turn[0] ^= 1
         fc.allgather_a_gemm(xs, w, stg[turn[0]], out=out)
     want = torch.matmul(x_full, w.t())
-    for transport, label in (("ce", "push, copy engines"), ("sm", "push, copy CTAs")):
+    for transport, label in (("ew", "push, epilogue warps"), ("ce", "push, copy engines"), ("sm", "push, copy CTAs")):
         fc.transport = transport
         t_p = timeit(push_ag, args.iters, args.warmup, flush)
         K.check_status()
@@ -164,7 +164,7 @@ def main():
     def push_agw():
         turn[0] ^= 1
         fc.allgather_b_gemm(x3, ws, wstg[turn[0]], out=out3)
-    for transport, label in (("ce", "push, copy engines"), ("sm", "push, copy CTAs")):
+    for transport, label in (("ew", "push, epilogue warps"), ("ce", "push, copy engines"), ("sm", "push, copy CTAs")):
         fc.transport = transport
         t_p = timeit(push_agw, args.iters, args.warmup, flush)
         K.check_status()

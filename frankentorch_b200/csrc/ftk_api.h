@@ -108,6 +108,8 @@ typedef struct FtkCommDesc {
   // sub_flags must be flags_peer[rank].  Consecutive calls must alternate two staging buffers.
   // push == 2: the shards are delivered from outside the kernel (ftk_copy_async + ftk_set_flags_sys on
   // another stream, i.e. by the copy engines); the kernel has no copy CTAs and only polls the flags.
+  // push == 3: no copy CTAs either; the epilogue warps of every CTA store the shard into the peers' staging
+  // buffers while they wait for their accumulators.
   int push;
   void* full_peer[FTK_MAX_RANKS];
   int* flags_peer[FTK_MAX_RANKS];

@@ -583,6 +583,87 @@ __device__ __forceinline__ void comm_reduce(const GemmArgs& p, const CommArgs& c
   }
 }
 
+// ------------------------------------------------------------------ gather, pushed by the epilogue warps
+// Third form of the gather (c.push == 3): no CTA is set aside for copying.  The eight epilogue warps of EVERY
+// CTA spend most of a tile's main loop waiting for the accumulator; in that time they store this rank's shard
+// into the peers' staging buffers, 4 KB per poll of the accumulator barrier, so all 148 SMs issue peer stores
+// (a single SM sustains 8 - 17 GB/s over NVLink, the link needs many of them) and none is taken from the
+// product.  Pieces are numbered destination-major in the order the consumers need them and dealt round robin
+// to the (CTA, warp) pairs; a warp publishes the flags of up to four finished pieces behind one system fence.
+// Pushing never waits for anything, and a warp with pieces left never blocks on its accumulator without
+// pushing, so every shard is delivered whatever the peers' tiles are waiting for.
+struct EpiPusher {
+  const CommArgs& c;
+  int lane, ppc, n_total, stride, nv, own_last;
+  uint32_t piece;
+  int pj;          // piece this warp is working on (>= n_total: done)
+  int pv;          // vectors of it already stored
+  int* pend[4];
+  int n_pend;
+  int batch;       // finished pieces whose flags go out behind one fence
+
+  __device__ __forceinline__ EpiPusher(const CommArgs& c_, bool active, int gw, int n_warps, int lane_,
+                                       bool own_last_)
+      : c(c_), lane(lane_), own_last(own_last_ ? 1 : 0), pv(0), n_pend(0) {
+    if (!active) {        // not a pushing launch: nothing to do, nothing of `c` is looked at
+      ppc = n_total = stride = nv = batch = 0;
+      piece = 0;
+      pj = 1;
+      return;
+    }
+    const int spc = c.chunk_rows / G_BM;
+    piece = c.sub_bytes < G_COPY_SLOT ? (uint32_t)c.sub_bytes : (uint32_t)G_COPY_SLOT;
+    ppc = spc * (int)(c.sub_bytes / piece);
+    n_total = ppc * c.world;
+    stride = n_warps;
+    nv = (int)(piece >> 4);
+    pj = gw;
+    // a warp with few pieces publishes each at once (a consumer waits for it), one with many amortises the fence
+    const int per_warp = (n_total + n_warps - 1) / n_warps;
+    batch = per_warp >= 16 ? 4 : (per_warp >= 8 ? 2 : 1);
+  }
+  __device__ __forceinline__ bool busy() const { return pj < n_total; }
+  __device__ __forceinline__ int dest_of(int d) const {
+    if (own_last) return d == c.world - 1 ? c.rank : (c.rank - 1 - d + 2 * c.world) % c.world;
+    return (c.rank - d + c.world) % c.world;
+  }
+  __device__ __forceinline__ void publish() {
+    if (n_pend == 0) return;
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0)
+      for (int k = 0; k < n_pend; ++k) st_rel_sys(pend[k], *c.epoch);
+    __syncwarp();
+    n_pend = 0;
+  }
+  // stores the next 4 KB (8 vectors per lane) of the current piece
+  __device__ __forceinline__ void step() {
+    if (pj >= n_total) return;
+    const int d = pj / ppc, q = pj - d * ppc;
+    const int dest = dest_of(d);
+    const uint4* src = reinterpret_cast<const uint4*>(c.src[c.rank] + (long long)q * piece);
+    uint4* dst = reinterpret_cast<uint4*>(c.full_peer[dest] + ((long long)c.rank * ppc + q) * piece);
+    uint4 u[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int v = pv + k * 32 + lane;
+      if (v < nv) u[k] = __ldg(src + v);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int v = pv + k * 32 + lane;
+      if (v < nv) dst[v] = u[k];
+    }
+    pv += 256;
+    if (pv >= nv) {
+      pend[n_pend++] = c.flags_peer[dest] + c.rank * ppc + q;
+      pv = 0;
+      pj += stride;
+      if (n_pend >= batch || pj >= n_total) publish();
+    }
+  }
+};
+
 // ------------------------------------------------------------------ the kernel
 template <int BN, int COMM>
 __global__ void __launch_bounds__(G_THREADS, 1)
@@ -839,12 +920,24 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
     uint32_t acc_ph = 0;
     int pend_owner[G_SCATTER_BATCH], pend_tile[G_SCATTER_BATCH], n_pend = 0;   // scatter: unpublished tiles
     bool epi_ok = true;   // false once this warp gave up a wait: it then skips every later barrier
+    const bool ew_push = COMM && c.push == 3 && (c.mode == FTK_COMM_GATHER_A || c.mode == FTK_COMM_GATHER_B);
+    EpiPusher pusher(c, ew_push, (int)blockIdx.x * G_EPI_WARPS + ew, n_compute * G_EPI_WARPS, lane,
+                     c.mode == FTK_COMM_GATHER_A);
     for (int item = blockIdx.x; item < total; item += n_compute) {
       const TileCoord t = decode_item<BN, COMM>(item, p, c, tiles_m, tiles_n, nbatch);
       if (!tile_has_rows(p, t.l, t.m_t)) continue;
       const int sp = t.sp, l = t.l, m_t = t.m_t, n_t = t.n_t;
       const int l0 = l % p.L0, l1 = l / p.L0;
       const bool empty_split = (sp * kb_per_split >= kblocks_all);
+      if (COMM && ew_push) {
+        // push 4 KB of the shard per poll while the accumulator is not ready
+        while (pusher.busy()) {
+          int ready = (lane == 0 && mbar_try_wait(&tfull[acc], (acc_ph >> acc) & 1u)) ? 1 : 0;
+          ready = __shfl_sync(0xffffffffu, ready, 0);
+          if (ready || aborted(ctx)) break;
+          pusher.step();
+        }
+      }
       if (!mbar_wait(&tfull[acc], (acc_ph >> acc) & 1u, ctx, FT_ERR_WAIT_TMEM_FULL)) {
         epi_ok = false;
         break;
@@ -1054,6 +1147,11 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA,
       if (lane == 0) mbar_arrive(&tempty[acc]);
       acc_ph ^= (1u << acc);
       acc ^= 1;
+    }
+    if (COMM && ew_push) {
+      // whatever of the shard is still here goes out now (also after an abort: the peers wait for it)
+      while (pusher.busy()) pusher.step();
+      pusher.publish();
     }
     // A warp that gave up a wait (epi_ok false) goes straight to the teardown: its siblings are
     // at, or will reach, a bounded warps_barrier and leave the same way once they see the abort flag.

@@ -459,8 +459,8 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
   // gathers: CTAs that only move data (default 20); reduce-scatter: every CTA reduces after its
   // GEMM tiles, dedicated CTAs are optional (default none)
   c.comm_ctas = cd->comm_ctas > 0 ? cd->comm_ctas : (cd->mode == FTK_COMM_SCATTER_D ? 0 : 20);
-  if (cd->mode != FTK_COMM_SCATTER_D && cd->push == 2) {
-    c.comm_ctas = 0;    // the shards arrive by copy engine: every CTA multiplies, the producers poll the flags
+  if (cd->mode != FTK_COMM_SCATTER_D && (cd->push == 2 || cd->push == 3)) {
+    c.comm_ctas = 0;    // 2: the shards arrive by copy engine; 3: the epilogue warps of every CTA push them
   } else if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D && cd->push) {
     c.comm_ctas = 16;
   } else if (cd->comm_ctas <= 0 && cd->mode != FTK_COMM_SCATTER_D) {
@@ -502,7 +502,7 @@ extern "C" int ftk_gemm_comm_bf16(const FtkGemmDesc* g, const FtkCommDesc* cd, v
     c.full = reinterpret_cast<uint8_t*>(const_cast<void*>(ga ? g->A : g->B));
     c.sub_flags = cd->sub_flags;
     c.ready_local = cd->push ? nullptr : cd->ready_local;
-    c.push = cd->push ? 1 : 0;
+    c.push = cd->push == 3 ? 3 : (cd->push ? 1 : 0);
     for (int r = 0; r < cd->world; ++r) {
       if (cd->push) {
         // only the own shard is read; peers' staging buffers and flag arrays are written

@@ -12,8 +12,9 @@ few CTAs move data between GPUs while the rest multiply:
   fetch the peers' shards) and the *push* form (staging buffer in symmetric memory, passed as a
   :class:`SymmTensor`: every rank delivers its own shard into all peers' staging buffers in the
   order the consumers need them, and consumers poll flags in their own memory only).  The push
-  form has two transports (``FT_GATHER_TRANSPORT``): ``sm`` (default) moves the shards with copy
-  CTAs inside the GEMM kernel; ``ce`` enqueues the deliveries as device-to-device copies on
+  form has three transports (``FT_GATHER_TRANSPORT``): ``ew`` lets the epilogue warps of EVERY CTA
+  store the shard into the peers' buffers while they wait for their accumulators (no SM is set aside,
+  all of them issue peer stores); ``sm`` (default) moves the shards with copy CTAs inside the GEMM kernel; ``ce`` enqueues the deliveries as device-to-device copies on
   other streams, each followed by a one-warp kernel that sets the arrival flags at the consumer,
   so the copy engines move the bytes and all SMs multiply.  Measured on two GPUs the hand-over
   between the copy engines and that kernel costs tens of microseconds per delivery, which makes
@@ -178,7 +179,7 @@ class FusedCollectives:
             n_flags = c.chunk_rows // TILE_M * self.world * max(1, TILE_M * row_bytes // 32768)
             if n_flags > self.sub_flags.numel():
                 raise K.KernelError("gathered operand needs more flag words than were allocated")
-            c.push = 2 if self.transport == "ce" else 1
+            c.push = {"ce": 2, "ew": 3}.get(self.transport, 1)
             c.sub_flags = self.gflags.local_ptr
             for r in range(self.world):
                 c.full_peer[r] = full.peer_ptrs[r]

@@ -44,8 +44,8 @@ def main():
 
     for it in range(3):                    # several epochs over the same flag arrays
         base = 1000 * it
-        # push form: copy-engine deliveries in epochs 0 and 2, copy CTAs inside the kernel in epoch 1
-        fc.transport = "sm" if it == 1 else "ce"
+        # push form: one transport per epoch (epilogue warps of every CTA, copy CTAs, copy engines)
+        fc.transport = ("ew", "sm", "ce")[it]
         # ---- all-gather(A) -> GEMM, ranks hold different weights (column-parallel)
         xs = [rnd((ms, kdim), base + r, dev) for r in range(world)]
         w = rnd((n, kdim), base + 100 + rank, dev)
