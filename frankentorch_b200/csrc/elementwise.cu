@@ -193,6 +193,75 @@ embedding_bwd_wte_kernel(const long long* __restrict__ sorted_ids, const int* __
     dst[1] += s1;
   }
 }
+// The same scatter-add without a sort: one CTA per position i.  It first looks for an earlier position with the
+// same token (then it has nothing to do: the first occurrence owns the row), otherwise it walks the later
+// positions in ascending order, 1024 at a time, and adds the rows of those that carry its token: the sum of a
+// table row is taken in ascending position order, exactly as after a stable sort, so both forms give the same
+// bits.  The ids (64 KB for 8192 positions) stay in L2; chunks without a match cost one load and one block-wide
+// vote.  No library sort, no atomics.
+__global__ void __launch_bounds__(128)
+embedding_bwd_wte_scan_kernel(const long long* __restrict__ ids, int rows, const __nv_bfloat16* __restrict__ dout,
+                              float* __restrict__ dwte, int d, long long vocab, int* status) {
+  constexpr int BLK = 1024;                               // positions looked at per vote: 8 loads in flight per thread
+  __shared__ unsigned char match[BLK];
+  const int i = blockIdx.x;
+  const long long id = ids[i];
+  if (!ft_index_ok(id, vocab, status)) return;            // no table row to add into
+  for (int j0 = 0; j0 < i; j0 += BLK) {                   // an earlier occurrence owns this token's row
+    int any = 0;
+#pragma unroll
+    for (int k = 0; k < BLK / 128; ++k) {
+      const int j = j0 + threadIdx.x + 128 * k;
+      any |= (j < i && ids[j] == id) ? 1 : 0;
+    }
+    if (__syncthreads_or(any)) return;
+  }
+  float acc[8];                                           // this thread's column pairs: c = 2 * (tid + 128 k)
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = 2 * (threadIdx.x + 128 * k);
+    float2 v = make_float2(0.f, 0.f);
+    if (c < d) v = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + (size_t)i * d + c));
+    acc[2 * k] = v.x;
+    acc[2 * k + 1] = v.y;
+  }
+  for (int j0 = i + 1; j0 < rows; j0 += BLK) {
+    unsigned char m[BLK / 128];
+    int any = 0;
+#pragma unroll
+    for (int k = 0; k < BLK / 128; ++k) {
+      const int j = j0 + threadIdx.x + 128 * k;
+      m[k] = (j < rows && ids[j] == id) ? 1 : 0;
+      any |= m[k];
+    }
+    if (!__syncthreads_or(any)) continue;                 // (also orders the previous block's reads of match[])
+#pragma unroll
+    for (int k = 0; k < BLK / 128; ++k) match[threadIdx.x + 128 * k] = m[k];
+    __syncthreads();
+    const int lim = min(BLK, rows - j0);
+    for (int t = 0; t < lim; ++t) {                       // ascending position order
+      if (!match[t]) continue;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = 2 * (threadIdx.x + 128 * k);
+        if (c < d) {
+          const float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + (size_t)(j0 + t) * d + c));
+          acc[2 * k] += v.x;
+          acc[2 * k + 1] += v.y;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = 2 * (threadIdx.x + 128 * k);
+    if (c < d) {
+      float* dst = dwte + (size_t)id * d + c;
+      dst[0] += acc[2 * k];
+      dst[1] += acc[2 * k + 1];
+    }
+  }
+}
 // dwpe[s, :] += sum over batch (ascending b) of dout[b*S + s, :]
 __global__ void __launch_bounds__(128)
 embedding_bwd_wpe_kernel(const __nv_bfloat16* __restrict__ dout, float* __restrict__ dwpe, int rows,
@@ -392,6 +461,16 @@ extern "C" int ftk_embedding_bwd(const long long* sorted_ids, const int* order, 
   if (dwte)
     embedding_bwd_wte_kernel<<<rows, 128, 0, STREAM(stream)>>>(sorted_ids, order, rows, BF(dout), dwte, d, vocab,
                                                                ftk_status_word());
+  if (dwpe) embedding_bwd_wpe_kernel<<<S, 128, 0, STREAM(stream)>>>(BF(dout), dwpe, rows, S, d);
+  return (int)cudaGetLastError();
+}
+// Sort-free form: `ids` in their original order (int64 [rows]); d <= 1024 (wider tables use the sorted form).
+extern "C" int ftk_embedding_bwd_scan(const long long* ids, const void* dout, float* dwte, float* dwpe, int rows,
+                                      int S, int d, long long vocab, void* stream) {
+  if (rows <= 0 || d % 2 || d > 1024 || (dwte && vocab <= 0)) return -2;
+  if (dwte)
+    embedding_bwd_wte_scan_kernel<<<rows, 128, 0, STREAM(stream)>>>(ids, rows, BF(dout), dwte, d, vocab,
+                                                                    ftk_status_word());
   if (dwpe) embedding_bwd_wpe_kernel<<<S, 128, 0, STREAM(stream)>>>(BF(dout), dwpe, rows, S, d);
   return (int)cudaGetLastError();
 }

@@ -235,6 +235,11 @@ int ftk_embedding_fwd(const long long* ids, const void* wte, const void* wpe, vo
 int ftk_embedding_bwd(const long long* sorted_ids, const int* order, const void* dout, float* dwte,
                       float* dwpe, int rows, int S, int d, long long vocab, void* stream);
 
+// The same sums without a sort (ids in their original order, d <= 1024): the CTA of a token's first occurrence adds
+// the rows of all its occurrences in ascending position order; bit-identical to the sorted form.
+int ftk_embedding_bwd_scan(const long long* ids, const void* dout, float* dwte, float* dwpe, int rows, int S,
+                           int d, long long vocab, void* stream);
+
 // ---- optimizer --------------------------------------------------------------------------
 // Fused AdamW on fp32 master weights with bf16 shadow write-back.  grad fp32.
 // Reference math: ft-optim/src/lib.rs:1040-1054.

@@ -143,6 +143,7 @@ def load(build_if_missing: bool = True):
         "ftk_colsum_blocks": [i],
         "ftk_embedding_fwd": [vp, vp, vp, vp, i, i, i, ll, vp],
         "ftk_embedding_bwd": [vp, vp, vp, vp, vp, i, i, i, ll, vp],
+        "ftk_embedding_bwd_scan": [vp, vp, vp, vp, i, i, i, ll, vp],
         "ftk_adamw": [vp, vp, vp, vp, vp, ll, f, f, f, f, f, f, f, f, vp],
         "ftk_adamw_tick": [vp, vp, C.c_double, C.c_double, vp],
         "ftk_clip_scale": [vp, f, vp, vp, vp],

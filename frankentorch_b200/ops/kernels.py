@@ -503,19 +503,25 @@ def embedding_fwd(ids, wte, wpe, S):
     return out
 
 
-def embedding_bwd(ids, dout, dwte, dwpe, S):
+def embedding_bwd(ids, dout, dwte, dwpe, S, *, sorted_form: bool = False):
     """Deterministic scatter-add of ``dout`` rows into fp32 ``dwte`` / ``dwpe`` (both ``+=``).
 
-    Rows are grouped by token id with a stable sort so that each table row is summed by
-    one CTA in ascending row order; the result does not depend on scheduling.
+    Every table row is summed by one CTA in ascending position order, so the result does not depend on
+    scheduling.  The default form needs no sort: the CTA of a token's first occurrence scans the later positions
+    for the same token.  ``sorted_form`` (and tables wider than 1024 columns) groups the rows with a stable sort
+    first; both forms give the same bits.
     """
     rows, d = dout.shape
     flat = ids.reshape(-1)
+    vocab = dwte.shape[0] if dwte is not None else 0
+    if not sorted_form and d <= 1024 and flat.dtype == torch.int64 and flat.is_contiguous():
+        _chk(_lib.load().ftk_embedding_bwd_scan(flat.data_ptr(), dout.data_ptr(), _ptr(dwte), _ptr(dwpe), rows, S, d,
+                                                vocab, _stream()), "ftk_embedding_bwd_scan")
+        return
     sorted_ids, order = torch.sort(flat, stable=True)
     order32 = order.to(torch.int32)
     _chk(_lib.load().ftk_embedding_bwd(sorted_ids.data_ptr(), order32.data_ptr(), dout.data_ptr(),
-                                       _ptr(dwte), _ptr(dwpe), rows, S, d,
-                                       dwte.shape[0] if dwte is not None else 0, _stream()), "ftk_embedding_bwd")
+                                       _ptr(dwte), _ptr(dwpe), rows, S, d, vocab, _stream()), "ftk_embedding_bwd")
 
 
 # --------------------------------------------------------------------------------------- optimizer

@@ -169,6 +169,20 @@ def test_embedding(cuda_device):
     dwte2 = torch.zeros(V, d, device=cuda_device)
     k.embedding_bwd(ids, dout, dwte2, None, S)
     assert torch.equal(dwte, dwte2)
+    # the sort-free form and the sorted form add each table row in the same order: same bits
+    dwte3 = torch.zeros(V, d, device=cuda_device)
+    k.embedding_bwd(ids, dout, dwte3, None, S, sorted_form=True)
+    assert torch.equal(dwte, dwte3)
+    # one token everywhere (a single CTA owns all rows), a wide table, a ragged number of positions
+    for (rows, dd, hi) in ((300, 768, 1), (257, 1024, 7), (129, 64, 1000)):
+        ids2 = torch.randint(0, hi, (1, rows), device=cuda_device)
+        do2 = _bf(torch.randn(rows, dd), cuda_device)
+        a, b = torch.zeros(V, dd, device=cuda_device), torch.zeros(V, dd, device=cuda_device)
+        k.embedding_bwd(ids2, do2, a, None, rows)
+        k.embedding_bwd(ids2, do2, b, None, rows, sorted_form=True)
+        assert torch.equal(a, b)
+        ref = torch.zeros(V, dd, device=cuda_device).index_add_(0, ids2.reshape(-1), do2.float())
+        assert (a - ref).abs().max().item() < 2e-3 * max(1.0, ref.abs().max().item())
     k.check_status()
 
 
