@@ -197,6 +197,9 @@ def _row_cases(rows, cols):
         "colsum": (lambda: ops.colsum(dy), 2 * n),
         "embedding_fwd": (lambda: ops.embedding_fwd(ids, wte, wpe, 1024), 4 * T * d + 2 * T * d),
         "embedding_bwd": (lambda: ops.embedding_bwd(ids, dy, dwte, dwpe, 1024), 2 * T * d + 8 * T * d),
+        "embedding_bwd_sorted": (lambda: ops.embedding_bwd(ids, dy, dwte, dwpe, 1024, sorted_form=True),
+                                 2 * T * d + 8 * T * d),
+        "embedding_bwd_repeats": (lambda: ops.embedding_bwd(ids % 50, dy, dwte, dwpe, 1024), 2 * T * d + 8 * T * d),
         "adamw_dev": (lambda: ops.adamw_dev(master, shadow, gr, m, v, hyper, beta1=0.9, beta2=0.999, eps=1e-8,
                                             weight_decay=0.01), 30 * N),
         "sumsq": (lambda: ops.sumsq(gr, out=ss), 4 * N),

@@ -204,16 +204,21 @@ embedding_bwd_wte_scan_kernel(const long long* __restrict__ ids, int rows, const
                               float* __restrict__ dwte, int d, long long vocab, int* status) {
   constexpr int BLK = 1024;                               // positions looked at per vote: 8 loads in flight per thread
   __shared__ unsigned char match[BLK];
+  __shared__ unsigned short list[BLK];
+  __shared__ int n_list;
   const int i = blockIdx.x;
   const long long id = ids[i];
   if (!ft_index_ok(id, vocab, status)) return;            // no table row to add into
   for (int j0 = 0; j0 < i; j0 += BLK) {                   // an earlier occurrence owns this token's row
-    int any = 0;
+    long long v[BLK / 128];                               // all loads issued before the first compare
 #pragma unroll
     for (int k = 0; k < BLK / 128; ++k) {
       const int j = j0 + threadIdx.x + 128 * k;
-      any |= (j < i && ids[j] == id) ? 1 : 0;
+      v[k] = j < i ? __ldg(ids + j) : -1;
     }
+    int any = 0;
+#pragma unroll
+    for (int k = 0; k < BLK / 128; ++k) any |= (v[k] == id) ? 1 : 0;
     if (__syncthreads_or(any)) return;
   }
   float acc[8];                                           // this thread's column pairs: c = 2 * (tid + 128 k)
@@ -226,30 +231,63 @@ embedding_bwd_wte_scan_kernel(const long long* __restrict__ ids, int rows, const
     acc[2 * k + 1] = v.y;
   }
   for (int j0 = i + 1; j0 < rows; j0 += BLK) {
+    long long v[BLK / 128];
+#pragma unroll
+    for (int k = 0; k < BLK / 128; ++k) {
+      const int j = j0 + threadIdx.x + 128 * k;
+      v[k] = j < rows ? __ldg(ids + j) : -1;
+    }
     unsigned char m[BLK / 128];
     int any = 0;
 #pragma unroll
     for (int k = 0; k < BLK / 128; ++k) {
-      const int j = j0 + threadIdx.x + 128 * k;
-      m[k] = (j < rows && ids[j] == id) ? 1 : 0;
+      m[k] = (v[k] == id) ? 1 : 0;
       any |= m[k];
     }
-    if (!__syncthreads_or(any)) continue;                 // (also orders the previous block's reads of match[])
+    if (!__syncthreads_or(any)) continue;                 // (also orders the previous block's reads of list[])
 #pragma unroll
     for (int k = 0; k < BLK / 128; ++k) match[threadIdx.x + 128 * k] = m[k];
     __syncthreads();
-    const int lim = min(BLK, rows - j0);
-    for (int t = 0; t < lim; ++t) {                       // ascending position order
-      if (!match[t]) continue;
+    // warp 0 compacts the matching positions of the block into an ascending list: lane l owns positions
+    // [32 l, 32 l + 32), a warp scan of the counts gives each lane its place
+    if (threadIdx.x < 32) {
+      int cnt = 0;
+      for (int t = 0; t < 32; ++t) cnt += match[32 * threadIdx.x + t];
+      int pos = cnt;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int c = 2 * (threadIdx.x + 128 * k);
-        if (c < d) {
-          const float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + (size_t)(j0 + t) * d + c));
-          acc[2 * k] += v.x;
-          acc[2 * k + 1] += v.y;
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, pos, o);
+        if ((int)threadIdx.x >= o) pos += up;
+      }
+      if (threadIdx.x == 31) n_list = pos;
+      pos -= cnt;
+      for (int t = 0; t < 32; ++t)
+        if (match[32 * threadIdx.x + t]) list[pos++] = (unsigned short)(32 * threadIdx.x + t);
+    }
+    __syncthreads();
+    const int n = n_list;
+    for (int q0 = 0; q0 < n; q0 += 4) {                   // four rows in flight, added in ascending position order
+      float2 v[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const bool on = q0 + u < n;
+        const size_t r = on ? (size_t)(j0 + list[q0 + u]) : 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = 2 * (threadIdx.x + 128 * k);
+          v[u][k] = (on && c < d) ? unpack_bf16(*reinterpret_cast<const uint32_t*>(dout + r * d + c))
+                                  : make_float2(0.f, 0.f);
         }
       }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (q0 + u < n) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            acc[2 * k] += v[u][k].x;
+            acc[2 * k + 1] += v[u][k].y;
+          }
+        }
     }
   }
 #pragma unroll
