@@ -268,7 +268,9 @@ class TorchArm:
         group = dist.group.WORLD if world > 1 else None
         vocab = c.get("vocab", VOCAB)
         if parallel == "tp" and world > 1:
-            model = TPGPT(c["n_layer"], c["d"], c["h"], c["ff"], c["seq"], world, group, c["mb"], vocab).to(dev)
+            # the job's batch is micro_batch x world sequences (the same on every rank; each rank owns the rows
+            # of micro_batch sequences between the blocks' collectives), as in this repository's TP + SP model
+            model = TPGPT(c["n_layer"], c["d"], c["h"], c["ff"], c["seq"], world, group, c["mb"] * world, vocab).to(dev)
             self.manual_sync, self.grad_div = True, 1.0          # the loss is already divided by the world size
         elif parallel == "ep":
             tokens = c["mb"] * c["seq"]
@@ -302,7 +304,8 @@ class TorchArm:
             self.wrapped = model
         self.opt = torch.optim.AdamW(self.wrapped.parameters(), lr=3e-4, weight_decay=0.01, fused=True)
         g = torch.Generator().manual_seed(1000 + (0 if parallel == "tp" else rank))    # tensor parallel: one batch
-        tok = torch.randint(0, vocab, (c["mb"], c["seq"] + 1), generator=g).to(dev)
+        n_seq = c["mb"] * (world if (parallel == "tp" and world > 1) else 1)
+        tok = torch.randint(0, vocab, (n_seq, c["seq"] + 1), generator=g).to(dev)
         self.ids, self.tgt = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
         self.loss = None
 
