@@ -1,0 +1,738 @@
+"""Session methods whose argument order, return shape or side effect differs from the plain
+``tensor_<op>(tensor ids..., **params)`` form that the rule table generates (installed onto
+``FrankenTorchSession`` by ``install``).
+
+The reference's per-operator benches and probes call these names with positional arguments
+(ft-api/benches/ops_bench.rs, special_bench.rs, distributions in ft-api/examples/*_probe.rs), so each
+wrapper takes them in that order: ``tensor_index_add(x, dim, index, src)``, ``tensor_renorm(x, p, dim,
+maxnorm)``, ``tensor_lu_solve(lu, pivots, b)`` and so on.  Groups:
+
+* positional wrappers over rules of ``autograd/functions_parity.py``;
+* second names of operators that already exist (``tensor_cholesky`` for ``tensor_linalg_cholesky``);
+* multi-output forms (``tensor_aminmax``, ``tensor_var_mean``, ``tensor_qr``, ``tensor_histogram``);
+* in-place variants (``tensor_hypot_`` ...), which follow the version-counter rules of ``tensor_add_``;
+* samplers of the session's xoshiro256++ stream (``tensor_exponential``, ``tensor_gamma`` ...);
+* the raw recurrent forwards ``tensor_rnn / tensor_lstm / tensor_gru`` (outputs are leaves without history).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ._session_factories import _new, _numel
+from ._session_ops import _inplace
+
+
+def _opt(ids):
+    return [i for i in ids if i is not None]
+
+
+# ------------------------------------------------------------------------------------ positional wrappers
+def tensor_logit(self, x, eps=None):
+    return self._apply("logit", [x], eps=eps)
+
+
+def tensor_nan_to_num(self, x, nan=0.0, posinf=None, neginf=None):
+    return self._apply("nan_to_num", [x], nan=nan, posinf=posinf, neginf=neginf)
+
+
+def tensor_polygamma(self, n, x):
+    return self._apply("polygamma", [x], n=int(n))
+
+
+def tensor_amax(self, x, dim=None, keepdim=False):
+    return self._apply("amax", [x], dim=dim, keepdim=keepdim)
+
+
+def tensor_amin(self, x, dim=None, keepdim=False):
+    return self._apply("amin", [x], dim=dim, keepdim=keepdim)
+
+
+def tensor_aminmax(self, x, dim=None) -> Tuple[int, int]:
+    return tensor_amin(self, x, dim), tensor_amax(self, x, dim)
+
+
+def tensor_kthvalue(self, x, k, dim=-1, keepdim=False) -> Tuple[int, int]:
+    """``(values, indices)`` of the k-th smallest element along ``dim`` (k counts from 1)."""
+    v = self._apply("kthvalue", [x], k=int(k), dim=dim, keepdim=keepdim)
+    idx = torch.kthvalue(self.tensor(x), int(k), dim, keepdim).indices
+    return v, _new(self, idx.to(torch.float64), False)
+
+
+def tensor_dist(self, a, b, p=2.0):
+    return self._apply("dist", [a, b], p=float(p))
+
+
+def tensor_diff(self, x, dim=-1):
+    return self._apply("diff", [x], dim=dim)
+
+
+def tensor_diff_full(self, x, n=1, dim=-1, prepend=None, append=None):
+    if prepend is not None and append is not None:
+        return self._apply("diff_full_both", [x, prepend, append], n=n, dim=dim)
+    if prepend is not None:
+        return self._apply("diff_full_prepend", [x, prepend], n=n, dim=dim)
+    if append is not None:
+        return self._apply("diff_full_append", [x, append], n=n, dim=dim)
+    return self._apply("diff_full", [x], n=n, dim=dim)
+
+
+def tensor_trapezoid(self, y, x=None, dim=-1, dx=1.0):
+    return self._apply("trapezoid", [y], dx=dx, dim=dim) if x is None else self._apply("trapezoid_x", [y, x], dim=dim)
+
+
+def tensor_cumulative_trapezoid(self, y, x=None, dim=-1, dx=1.0):
+    if x is None:
+        return self._apply("cumulative_trapezoid", [y], dx=dx, dim=dim)
+    return self._apply("cumulative_trapezoid_x", [y, x], dim=dim)
+
+
+def tensor_gradient_dim(self, x, dim=0, spacing=1.0, edge_order=1):
+    return self._apply("gradient_dim", [x], dim=dim, spacing=spacing, edge_order=edge_order)
+
+
+def tensor_select(self, x, dim, index):
+    return self._apply("select", [x], dim=dim, index=index)
+
+
+def tensor_select_scatter(self, x, src, dim, index):
+    return self._apply("select_scatter", [x, src], dim=dim, index=index)
+
+
+def tensor_slice_scatter(self, x, src, dim=0, start=None, end=None, step=1):
+    return self._apply("slice_scatter", [x, src], dim=dim, start=start, end=end, step=step)
+
+
+def tensor_rot90(self, x, k=1, dims=(0, 1)):
+    return self._apply("rot90", [x], k=k, dims=tuple(dims))
+
+
+def tensor_renorm(self, x, p, dim, maxnorm):
+    return self._apply("renorm", [x], p=float(p), dim=dim, maxnorm=float(maxnorm))
+
+
+def tensor_normalize(self, x, p=2.0, dim=1, eps=1e-12):
+    return self._apply("normalize", [x], p=float(p), dim=dim, eps=eps)
+
+
+def tensor_index_add(self, x, dim, index, src, alpha=1.0):
+    return self._apply("index_add", [x, index, src], dim=dim, alpha=alpha)
+
+
+def tensor_index_copy(self, x, dim, index, src):
+    return self._apply("index_copy", [x, index, src], dim=dim)
+
+
+def tensor_index_fill(self, x, dim, index, value):
+    return self._apply("index_fill", [x, index], dim=dim, value=value)
+
+
+def tensor_index_reduce(self, x, dim, index, src, reduce, include_self=True):
+    return self._apply("index_reduce", [x, index, src], dim=dim, reduce=reduce, include_self=include_self)
+
+
+def tensor_scatter_reduce(self, x, dim, index, src, reduce, include_self=True):
+    return self._apply("scatter_reduce", [x, index, src], dim=dim, reduce=reduce, include_self=include_self)
+
+
+def tensor_take_along_dim(self, x, index, dim):
+    return self._apply("take_along_dim", [x, index], dim=dim)
+
+
+def tensor_put(self, x, index, values, accumulate=False):
+    return self._apply("put", [x, index, values], accumulate=accumulate)
+
+
+def tensor_repeat_interleave(self, x, repeats, dim=None):
+    return self._apply("repeat_interleave", [x], repeats=int(repeats), dim=dim)
+
+
+def tensor_repeat_interleave_tensor(self, x, repeats, dim=None):
+    return self._apply("repeat_interleave_tensor", [x], repeats=tuple(int(r) for r in repeats), dim=dim)
+
+
+def tensor_repeat_interleave_repeats(self, x, repeats, dim=None):
+    """``repeats`` is a tensor node: one count per element (or per slice of ``dim``), or a single count for all."""
+    reps = [float(v) for v in self.tensor(repeats).detach().reshape(-1).tolist()]
+    if any(r < 0 or r != int(r) for r in reps):
+        raise ValueError("repeat_interleave: repeats must be non-negative integers")
+    n = self.tensor_numel(x) if dim is None else self.tensor_shape(x)[dim]
+    if len(reps) == 1:
+        reps = reps * n
+    if len(reps) != n:
+        raise ValueError(f"repeat_interleave: {len(reps)} repeat counts for {n} positions")
+    return tensor_repeat_interleave_tensor(self, x, reps, dim)
+
+
+def tensor_addcmul(self, x, t1, t2, value=1.0):
+    return self._apply("addcmul", [x, t1, t2], value=value)
+
+
+def tensor_addcdiv(self, x, t1, t2, value=1.0):
+    return self._apply("addcdiv", [x, t1, t2], value=value)
+
+
+def tensor_addr(self, x, v1, v2, beta=1.0, alpha=1.0):
+    return self._apply("addr", [x, v1, v2], beta=beta, alpha=alpha)
+
+
+def tensor_where_scalar(self, cond, x, y):
+    return self._apply("where_scalar", [cond], x=float(x), y=float(y))
+
+
+def tensor_isclose(self, a, b, rtol=1e-5, atol=1e-8, equal_nan=False):
+    return self._apply("isclose", [a, b], rtol=rtol, atol=atol, equal_nan=equal_nan)
+
+
+def tensor_float_power(self, x, exponent):
+    return self._apply("float_power", [x], exponent=float(exponent))
+
+
+def tensor_clamp_min(self, x, min):
+    return self._apply("clamp_min", [x], min=float(min))
+
+
+def tensor_clamp_max(self, x, max):
+    return self._apply("clamp_max", [x], max=float(max))
+
+
+def tensor_round_decimals(self, x, decimals):
+    return self._apply("round_decimals", [x], decimals=int(decimals))
+
+
+def tensor_mvlgamma(self, x, p):
+    return self._apply("mvlgamma", [x], p=int(p))
+
+
+def tensor_one_hot(self, index, num_classes=-1):
+    return self._apply("one_hot", [index], num_classes=num_classes)
+
+
+def tensor_vander(self, x, n=None, increasing=False):
+    return self._apply("vander", [x], n=n, increasing=increasing)
+
+
+def tensor_combinations(self, x, r=2, with_replacement=False):
+    return self._apply("combinations", [x], r=r, with_replacement=with_replacement)
+
+
+def tensor_nanvar(self, x, correction=1, dim=None, keepdim=False):
+    return self._apply("nanvar", [x], correction=correction, dim=dim, keepdim=keepdim)
+
+
+def tensor_nanstd(self, x, correction=1, dim=None, keepdim=False):
+    return self._apply("nanstd", [x], correction=correction, dim=dim, keepdim=keepdim)
+
+
+def tensor_var_mean(self, x, dim, correction=1, keepdim=False) -> Tuple[int, int]:
+    return (self.tensor_var_dim(x, dim=dim, keepdim=keepdim, correction=correction),
+            self.tensor_mean_dim(x, dim=dim, keepdim=keepdim))
+
+
+def tensor_std_mean(self, x, dim, correction=1, keepdim=False) -> Tuple[int, int]:
+    return (self.tensor_std_dim(x, dim=dim, keepdim=keepdim, correction=correction),
+            self.tensor_mean_dim(x, dim=dim, keepdim=keepdim))
+
+
+def _quantile(self, x, q, dim, keepdim, interpolation, ignore_nan=False):
+    q = [float(v) for v in q] if isinstance(q, (list, tuple)) else float(q)
+    return self._apply("quantile_full", [x], q=q, dim=dim, keepdim=keepdim, interpolation=interpolation, ignore_nan=ignore_nan)
+
+
+def tensor_quantile_dim(self, x, q, dim, keepdim=False, interpolation="linear"):
+    return _quantile(self, x, q, dim, keepdim, interpolation)
+
+
+def tensor_quantile_multi(self, x, qs, interpolation="linear"):
+    return _quantile(self, x, list(qs), None, False, interpolation)
+
+
+def tensor_quantile_dim_multi(self, x, qs, dim, keepdim=False, interpolation="linear"):
+    return _quantile(self, x, list(qs), dim, keepdim, interpolation)
+
+
+def tensor_nanquantile(self, x, q, dim=None, keepdim=False, interpolation="linear"):
+    return _quantile(self, x, q, dim, keepdim, interpolation, ignore_nan=True)
+
+
+def tensor_cross_entropy_full(self, logits, target, weight=None, ignore_index=None, reduction="mean", label_smoothing=0.0):
+    return self._apply("cross_entropy_full", _opt([logits, target, weight]),
+                       ignore_index=-100 if ignore_index is None else int(ignore_index), reduction=reduction,
+                       label_smoothing=label_smoothing)
+
+
+def tensor_nll_loss_full(self, lp, target, weight=None, ignore_index=None, reduction="mean"):
+    return self._apply("nll_loss_full", _opt([lp, target, weight]),
+                       ignore_index=-100 if ignore_index is None else int(ignore_index), reduction=reduction)
+
+
+def tensor_bce_with_logits_pos_weight(self, x, t, pos_weight, reduction="mean"):
+    return self._apply("bce_with_logits_pos_weight", [x, t], pos_weight=float(pos_weight), reduction=reduction)
+
+
+def tensor_binary_cross_entropy(self, p, t, reduction="mean"):
+    return self.tensor_bce_loss(p, t, reduction=reduction)
+
+
+def tensor_block_diag(self, ids):
+    return self._apply("block_diag", list(ids))
+
+
+def tensor_cartesian_prod(self, ids):
+    return self._apply("cartesian_prod", list(ids))
+
+
+def tensor_column_stack(self, ids):
+    return self._apply("column_stack", list(ids))
+
+
+def tensor_meshgrid(self, ids, indexing="ij") -> List[int]:
+    """One expanded view per input (``indexing`` 'ij' or 'xy'); each output's gradient sums back onto its vector."""
+    ids = list(ids)
+    sizes = [self.tensor_shape(i)[0] for i in ids]
+    order = list(range(len(ids)))
+    if indexing == "xy" and len(ids) >= 2:
+        order[0], order[1] = 1, 0
+    out_shape = [sizes[k] for k in order]
+    outs = []
+    for k, i in enumerate(ids):
+        shape = [1] * len(ids)
+        shape[order.index(k)] = sizes[k]
+        outs.append(self.tensor_expand(self.tensor_reshape(i, shape=shape), shape=tuple(out_shape)))
+    return outs
+
+
+def tensor_rfft2(self, x, s=None, norm=None):
+    return self._apply("rfft2", [x], s=s, norm=norm)
+
+
+def tensor_rfftn(self, x, s=None, dim=None, norm=None):
+    return self._apply("rfftn", [x], s=s, dim=None if dim is None else tuple(dim), norm=norm)
+
+
+def tensor_irfft2(self, z, s=None, norm=None):
+    return self._apply("irfft2", [z], s=s, norm=norm)
+
+
+def tensor_fft_norm(self, x, n=None, norm="backward"):
+    return self.tensor_fft(x, n=n, norm=norm)
+
+
+def tensor_split_with_sizes(self, x, sizes, dim=0) -> List[int]:
+    outs, off = [], 0
+    for s in sizes:
+        outs.append(self.tensor_narrow(x, dim=dim, start=off, length=int(s)))
+        off += int(s)
+    return outs
+
+
+def tensor_roll_dims(self, x, shifts, dims):
+    return self.tensor_roll(x, shifts=tuple(shifts), dims=tuple(dims))
+
+
+def tensor_swapaxes(self, x, a, b):
+    return self.tensor_transpose(x, dim0=a, dim1=b)
+
+
+def tensor_broadcast_to(self, x, shape):
+    return self.tensor_expand(x, shape=tuple(shape))
+
+
+def tensor_cummax_dim(self, x, dim):
+    return self.tensor_cummax(x, dim=dim)
+
+
+def tensor_cummin_dim(self, x, dim):
+    return self.tensor_cummin(x, dim=dim)
+
+
+def tensor_scaled_dot_product_attention_gqa(self, q, k, v, mask=None, is_causal=False, scale=None, enable_gqa=True):
+    """Attention with fewer key / value heads than query heads: each key / value head serves a group of
+    ``Hq / Hkv`` consecutive query heads (the heads are repeated with ``repeat_interleave``, whose rule sums the
+    group's gradients back)."""
+    hq, hkv = self.tensor_shape(q)[-3], self.tensor_shape(k)[-3]
+    if hq != hkv:
+        if not enable_gqa or hq % hkv:
+            raise ValueError(f"query heads ({hq}) must be a multiple of key/value heads ({hkv}) with enable_gqa")
+        hd = len(self.tensor_shape(k)) - 3
+        k = tensor_repeat_interleave(self, k, hq // hkv, dim=hd)
+        v = tensor_repeat_interleave(self, v, hq // hkv, dim=hd)
+    return self.tensor_sdpa(q, k, v, mask, is_causal=is_causal, scale=scale)
+
+
+# ------------------------------------------------------------------------------------ matrices: second names, factor pairs
+def tensor_cholesky(self, a, upper=False):
+    l = self.tensor_linalg_cholesky(a)
+    return self._apply("matrix_transpose", [l]) if upper else l
+
+
+def tensor_cholesky_solve(self, b, l, upper=False):
+    return self.tensor_linalg_cholesky_solve(b, l, upper=upper)
+
+
+def tensor_cholesky_inverse(self, l, upper=False):
+    return self._apply("cholesky_inverse", [l], upper=upper)
+
+
+def tensor_triangular_solve(self, a, b, upper=True):
+    return self.tensor_linalg_triangular_solve(a, b, upper=upper)
+
+
+def tensor_matrix_power(self, a, n):
+    return self.tensor_linalg_matrix_power(a, n=int(n))
+
+
+def tensor_matrix_norm(self, a, ord="fro"):
+    return self.tensor_linalg_matrix_norm(a, ord=ord)
+
+
+def tensor_qr(self, a, reduced=True) -> Tuple[int, int]:
+    if reduced:
+        return self.tensor_linalg_qr(a)
+    q, r = torch.linalg.qr(self.tensor(a), mode="complete")
+    return _new(self, q, False, self.tensor_dtype(a)), _new(self, r, False, self.tensor_dtype(a))
+
+
+def tensor_lu_factor(self, a) -> Tuple[int, List[int]]:
+    """Packed ``LU`` (unit lower below the diagonal, upper on and above) and the 1-based row pivots."""
+    lu, piv = torch.linalg.lu_factor(self.tensor(a))
+    return _new(self, lu, False, self.tensor_dtype(a)), [int(p) for p in piv.reshape(-1).tolist()]
+
+
+def tensor_lu_solve(self, lu, pivots, b):
+    """Solve ``A x = b`` from ``tensor_lu_factor``'s outputs.  The solve is linear in ``b``: its rule is the
+    transposed solve ``db = A^-T grad``."""
+    LU = self.tensor(lu)
+    piv = torch.as_tensor(list(pivots), dtype=torch.int32, device=LU.device).reshape(LU.shape[:-1])
+
+    def fwd(ctx, ts):
+        return torch.linalg.lu_solve(LU, piv, ts[0])
+
+    def bwd(ctx, g):
+        return [torch.linalg.lu_solve(LU.to(g.dtype), piv, g, adjoint=True)]
+
+    return self.tensor_apply_function([b], fwd, bwd)
+
+
+def tensor_ormqr(self, a, tau, c, left=True, transpose=False):
+    out = torch.ormqr(self.tensor(a), self.tensor(tau), self.tensor(c), left, transpose)
+    return _new(self, out, False, self.tensor_dtype(c))
+
+
+def tensor_linalg_pinv_hermitian(self, a):
+    """Pseudo-inverse of a symmetric matrix from its eigendecomposition (eigenvalues below ``eps * max|w| * n`` dropped)."""
+    A = self.tensor(a)
+    return _new(self, torch.linalg.pinv(A, hermitian=True), False, self.tensor_dtype(a))
+
+
+def tensor_eigh(self, a) -> Tuple[int, int]:
+    return self.tensor_linalg_eigh(a)
+
+
+# ------------------------------------------------------------------------------------ non-differentiable multi-output forms
+def tensor_histogram(self, x, bins, min=0.0, max=0.0, weight=None, density=False) -> Tuple[int, int]:
+    """``(hist, bin_edges)``; ``min == max`` means the data range."""
+    t = self.tensor(x).detach().to("cpu", torch.float64).reshape(-1)
+    w = None if weight is None else self.tensor(weight).detach().to("cpu", torch.float64).reshape(-1)
+    rng = None if min == max else (float(min), float(max))
+    h = torch.histogram(t, int(bins), range=rng, weight=w, density=bool(density))
+    return _new(self, h.hist, False), _new(self, h.bin_edges, False)
+
+
+def tensor_histogramdd(self, x, bins, ranges=None, density=False) -> Tuple[int, List[int]]:
+    t = self.tensor(x).detach().to("cpu", torch.float64)
+    rng = None if ranges is None else [float(v) for v in ranges]
+    h = torch.histogramdd(t, [int(b) for b in bins], range=rng, density=bool(density))
+    return _new(self, h.hist, False), [_new(self, e, False) for e in h.bin_edges]
+
+
+def tensor_unique_consecutive(self, x, return_inverse=False, return_counts=False):
+    """``(values, inverse or None, counts or None)`` of runs of equal elements (flattened input)."""
+    v, inv, cnt = torch.unique_consecutive(self.tensor(x).reshape(-1), return_inverse=True, return_counts=True)
+    dt = self.tensor_dtype(x)
+    return (_new(self, v, False, dt), _new(self, inv.to(torch.float64), False) if return_inverse else None,
+            _new(self, cnt.to(torch.float64), False) if return_counts else None)
+
+
+def tensor_gradients_iter(self, report):
+    """Iterate ``(node id, gradient values)`` over every gradient a backward report holds, in node order."""
+    for nid in sorted(report.gradients):
+        yield nid, report.gradients[nid].detach().to("cpu", torch.float64).reshape(-1).tolist()
+
+
+def tensor_register_hook(self, nid, fn):
+    return self.register_tensor_hook(nid, fn)
+
+
+# ------------------------------------------------------------------------------------ in-place variants
+def _inplace_binary(name, fn):
+    def method(self, a, b, *extra):
+        return _inplace(self, a, lambda t: fn(t, self.tensor(b), *extra))
+    method.__name__ = name
+    method.__doc__ = f"In-place ``{name[7:-1]}``: overwrites the first tensor, bumps its version, returns its id."
+    return method
+
+
+def tensor_where_(self, a, cond, other):
+    """``a = where(cond, a, other)`` in place."""
+    return _inplace(self, a, lambda t: t.copy_(torch.where(self.tensor(cond).bool(), t, self.tensor(other))))
+
+
+def tensor_masked_fill_(self, a, mask, value):
+    return _inplace(self, a, lambda t: t.masked_fill_(self.tensor(mask).bool(), value))
+
+
+def tensor_addcmul_(self, a, t1, t2, value=1.0):
+    return _inplace(self, a, lambda t: t.addcmul_(self.tensor(t1), self.tensor(t2), value=value))
+
+
+def tensor_lerp_(self, a, end, weight):
+    """``a += weight * (end - a)`` in place; ``weight`` is a number."""
+    return _inplace(self, a, lambda t: t.lerp_(self.tensor(end), float(weight)))
+
+
+def tensor_sigmoid_(self, a):
+    return _inplace(self, a, lambda t: t.sigmoid_())
+
+
+def tensor_acosh_(self, a):
+    return _inplace(self, a, lambda t: t.acosh_())
+
+
+def tensor_ones_(self, a):
+    return _inplace(self, a, lambda t: t.fill_(1.0))
+
+
+# ------------------------------------------------------------------------------------ samplers (session stream)
+def _u(self, n):
+    return self.rng.uniform(n)
+
+
+def _shape_out(self, t, shape, requires_grad):
+    return _new(self, t.reshape(tuple(shape)), requires_grad)
+
+
+def tensor_1d(self, values, requires_grad=False):
+    return self.tensor_variable(list(values), [len(values)], requires_grad)
+
+
+def tensor_normal(self, mean, std, shape, requires_grad=False):
+    return _shape_out(self, mean + std * self.rng.normal(_numel(shape)), shape, requires_grad)
+
+
+def tensor_log_normal(self, mean, std, shape, requires_grad=False):
+    return _shape_out(self, torch.exp(mean + std * self.rng.normal(_numel(shape))), shape, requires_grad)
+
+
+def tensor_half_normal(self, scale, shape, requires_grad=False):
+    return _shape_out(self, scale * self.rng.normal(_numel(shape)).abs(), shape, requires_grad)
+
+
+def tensor_cauchy(self, median, sigma, shape, requires_grad=False):
+    u = _u(self, _numel(shape))
+    return _shape_out(self, median + sigma * torch.tan(math.pi * (u - 0.5)), shape, requires_grad)
+
+
+def tensor_exponential(self, rate, shape, requires_grad=False):
+    u = _u(self, _numel(shape))
+    return _shape_out(self, -torch.log1p(-u) / rate, shape, requires_grad)
+
+
+def tensor_weibull(self, scale, concentration, shape, requires_grad=False):
+    u = _u(self, _numel(shape))
+    return _shape_out(self, scale * (-torch.log1p(-u)).pow(1.0 / concentration), shape, requires_grad)
+
+
+def _gamma_draws(self, alpha: float, n: int) -> torch.Tensor:
+    """Marsaglia-Tsang squeeze for shape ``alpha`` (boosted by ``u^(1/alpha)`` below 1), vectorised: each round
+    draws candidates for the positions still open."""
+    boost = alpha < 1.0
+    a = alpha + 1.0 if boost else alpha
+    d = a - 1.0 / 3.0
+    c = 1.0 / math.sqrt(9.0 * d)
+    out = torch.empty(n, dtype=torch.float64)
+    open_idx = torch.arange(n)
+    while open_idx.numel():
+        m = open_idx.numel()
+        z = self.rng.normal(m)
+        u = _u(self, m)
+        v = (1.0 + c * z) ** 3
+        ok = (v > 0) & (torch.log(u) < 0.5 * z * z + d - d * v + d * torch.log(torch.where(v > 0, v, torch.ones_like(v))))
+        out[open_idx[ok]] = d * v[ok]
+        open_idx = open_idx[~ok]
+    if boost:
+        out = out * _u(self, n).pow(1.0 / alpha)
+    return out
+
+
+def tensor_gamma(self, concentration, rate, shape, requires_grad=False):
+    return _shape_out(self, _gamma_draws(self, float(concentration), _numel(shape)) / rate, shape, requires_grad)
+
+
+def tensor_chi2(self, df, shape, requires_grad=False):
+    return _shape_out(self, 2.0 * _gamma_draws(self, 0.5 * float(df), _numel(shape)), shape, requires_grad)
+
+
+def tensor_beta(self, a, b, shape, requires_grad=False):
+    n = _numel(shape)
+    x, y = _gamma_draws(self, float(a), n), _gamma_draws(self, float(b), n)
+    return _shape_out(self, x / (x + y), shape, requires_grad)
+
+
+def tensor_studentt(self, df, shape, requires_grad=False):
+    n = _numel(shape)
+    z = self.rng.normal(n)
+    chi2 = 2.0 * _gamma_draws(self, 0.5 * float(df), n)
+    return _shape_out(self, z / torch.sqrt(chi2 / df), shape, requires_grad)
+
+
+def tensor_dirichlet(self, alphas, shape, requires_grad=False):
+    """Samples of shape ``shape + [len(alphas)]``: independent gammas normalised over the last dimension."""
+    n = _numel(shape)
+    g = torch.stack([_gamma_draws(self, float(a), n) for a in alphas], -1)
+    return _new(self, (g / g.sum(-1, keepdim=True)).reshape(tuple(shape) + (len(alphas),)), requires_grad)
+
+
+def tensor_binomial(self, total_count, p, shape, requires_grad=False):
+    n = _numel(shape)
+    u = _u(self, n * int(total_count)).reshape(n, int(total_count))
+    return _shape_out(self, (u < p).sum(-1).to(torch.float64), shape, requires_grad)
+
+
+def _fill_from(self, nid, values):
+    t = self.tensor(nid)
+    t.copy_(values.reshape(t.shape).to(device=t.device, dtype=t.dtype))
+    self.tensor_tape.bump_version(nid)
+    return nid
+
+
+def tensor_log_normal_(self, nid, mean=1.0, std=2.0):
+    return _fill_from(self, nid, torch.exp(mean + std * self.rng.normal(self.tensor_numel(nid))))
+
+
+def tensor_cauchy_(self, nid, median=0.0, sigma=1.0):
+    return _fill_from(self, nid, median + sigma * torch.tan(math.pi * (_u(self, self.tensor_numel(nid)) - 0.5)))
+
+
+def tensor_exponential_(self, nid, rate=1.0):
+    return _fill_from(self, nid, -torch.log1p(-_u(self, self.tensor_numel(nid))) / rate)
+
+
+def tensor_geometric_(self, nid, p):
+    """Number of Bernoulli(p) trials up to and including the first success (support 1, 2, ...)."""
+    u = _u(self, self.tensor_numel(nid))
+    return _fill_from(self, nid, torch.ceil(torch.log1p(-u) / math.log1p(-p)).clamp_min(1.0))
+
+
+# ------------------------------------------------------------------------------------ raw recurrent forwards
+def _cell_step(kind, x_t, h, c, w, nonlinearity):
+    w_ih, w_hh, b_ih, b_hh = w
+    gi = x_t @ w_ih.t() + (b_ih if b_ih is not None else 0)
+    gh = h @ w_hh.t() + (b_hh if b_hh is not None else 0)
+    if kind == "rnn":
+        return (torch.tanh if nonlinearity == "tanh" else torch.relu)(gi + gh), None
+    if kind == "lstm":
+        i, f, g, o = (gi + gh).chunk(4, -1)
+        c = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(g)
+        return torch.sigmoid(o) * torch.tanh(c), c
+    ir, iz, inn = gi.chunk(3, -1)
+    hr, hz, hn = gh.chunk(3, -1)
+    r, z = torch.sigmoid(ir + hr), torch.sigmoid(iz + hz)
+    n = torch.tanh(inn + r * hn)
+    return (1 - z) * n + z * h, None
+
+
+def _recurrent(self, kind, input, hx, weights, bidirectional, batch_first, nonlinearity="tanh"):
+    """Stacked (optionally bidirectional) recurrence over ``input`` [T, B, I] (or [B, T, I] with ``batch_first``).
+    ``weights`` holds one ``(w_ih, w_hh, b_ih or None, b_hh or None)`` tuple of node ids per layer and direction
+    (forward then reverse).  Gate order: LSTM i, f, g, o; GRU r, z, n.  Outputs are history-free leaves."""
+    x = self.tensor(input).detach()
+    unbatched = x.dim() == 2
+    if unbatched:
+        x = x.unsqueeze(1)
+    elif batch_first:
+        x = x.transpose(0, 1)
+    ndir = 2 if bidirectional else 1
+    layers = len(weights) // ndir
+    W = [tuple(None if i is None else self.tensor(i).detach() for i in w) for w in weights]
+    hid = W[0][1].shape[1]
+    B = x.shape[1]
+
+    def state(idx):
+        if hx is None:
+            return torch.zeros(layers * ndir, B, hid, dtype=x.dtype, device=x.device)
+        t = self.tensor(hx[idx] if kind == "lstm" else hx).detach()
+        return t.unsqueeze(1) if unbatched else t
+
+    h0 = state(0)
+    c0 = state(1) if kind == "lstm" else None
+    hs, cs = [], []
+    for l in range(layers):
+        outs = []
+        for d in range(ndir):
+            k = l * ndir + d
+            h, c = h0[k], (c0[k] if c0 is not None else None)
+            steps = range(x.shape[0] - 1, -1, -1) if d == 1 else range(x.shape[0])
+            seq = [None] * x.shape[0]
+            for t in steps:
+                h, c = _cell_step(kind, x[t], h, c, W[k], nonlinearity)
+                seq[t] = h
+            outs.append(torch.stack(seq))
+            hs.append(h)
+            cs.append(c)
+        x = torch.cat(outs, -1)
+    out = x.squeeze(1) if unbatched else (x.transpose(0, 1) if batch_first else x)
+    hn = torch.stack(hs)
+    dt = self.tensor_dtype(input)
+    mk = lambda t: _new(self, (t.squeeze(1) if unbatched else t).contiguous(), False, dt)   # noqa: E731
+    if kind == "lstm":
+        return _new(self, out.contiguous(), False, dt), (mk(hn), mk(torch.stack(cs)))
+    return _new(self, out.contiguous(), False, dt), mk(hn)
+
+
+def tensor_rnn(self, input, hx, weights, bidirectional=False, batch_first=False, nonlinearity="tanh"):
+    return _recurrent(self, "rnn", input, hx, weights, bidirectional, batch_first, nonlinearity)
+
+
+def tensor_lstm(self, input, hx, weights, bidirectional=False, batch_first=False):
+    return _recurrent(self, "lstm", input, hx, weights, bidirectional, batch_first)
+
+
+def tensor_gru(self, input, hx, weights, bidirectional=False, batch_first=False):
+    return _recurrent(self, "gru", input, hx, weights, bidirectional, batch_first)
+
+
+# ------------------------------------------------------------------------------------ installation
+_SECOND_NAMES = {
+    # matrices
+    "tensor_inverse": "tensor_inverse", "tensor_pinv": "tensor_linalg_pinv", "tensor_matrix_exp": "tensor_linalg_matrix_exp",
+    "tensor_lstsq": "tensor_linalg_lstsq", "tensor_solve": "tensor_linalg_solve", "tensor_eigvalsh": "tensor_linalg_eigvalsh",
+    "tensor_householder_product": "tensor_linalg_householder_product", "tensor_multi_dot": "tensor_linalg_multi_dot",
+    # shape
+    "tensor_swapdims": "tensor_swapaxes", "tensor_unsafe_chunk": "tensor_chunk",
+    # factories and samplers under the tensor_ prefix
+    "tensor_randn": "randn", "tensor_rand": "rand", "tensor_zeros": "zeros", "tensor_poisson": "poisson",
+    "tensor_fft_fftfreq": "tensor_fftfreq", "tensor_fft_rfftfreq": "tensor_rfftfreq",
+}
+
+_INPLACE_BINARY = {
+    "tensor_maximum_": lambda t, o: t.copy_(torch.maximum(t, o)), "tensor_xlogy_": lambda t, o: t.xlogy_(o),
+    "tensor_remainder_": lambda t, o: t.remainder_(o), "tensor_hypot_": lambda t, o: t.hypot_(o),
+    "tensor_heaviside_": lambda t, o: t.heaviside_(o), "tensor_fmod_": lambda t, o: t.fmod_(o),
+    "tensor_copysign_": lambda t, o: t.copysign_(o), "tensor_atan2_": lambda t, o: t.atan2_(o),
+}
+
+
+def install(cls) -> None:
+    from ._session_extras import _alias
+    g = globals()
+    for name, fn in list(g.items()):
+        if name.startswith("tensor_") and callable(fn):
+            setattr(cls, name, fn)
+    for name, fn in _INPLACE_BINARY.items():
+        setattr(cls, name, _inplace_binary(name, fn))
+    for name, target in _SECOND_NAMES.items():
+        if name != target and hasattr(cls, target):
+            setattr(cls, name, _alias(target, name))

@@ -36,6 +36,7 @@ from .autograd import functions_nn as _f3  # noqa: F401
 from .autograd import functions_shape as _f2  # noqa: F401
 from .autograd import functions_extra as _f4  # noqa: F401
 from .autograd import functions_sparse as _f5  # noqa: F401
+from .autograd import functions_parity as _f6  # noqa: F401
 from .autograd.functions import OPS, OpDef
 from .autograd.scalar_tape import BackwardReport, Tape
 from .autograd.tape import (BackwardOptions, BorrowedInputVersionMismatch, TensorBackwardReport, TensorHookHandle,
@@ -317,3 +318,7 @@ _fac_install.install(FrankenTorchSession)
 from . import _session_extras as _extra_install  # noqa: E402
 
 _extra_install.install(FrankenTorchSession)
+
+from . import _session_parity as _parity_install  # noqa: E402
+
+_parity_install.install(FrankenTorchSession)
