@@ -1,7 +1,9 @@
 """``frankentorch_b200.nn``: module system and layers on the DAC tape (mirror of ft-nn)."""
 from .layers import *  # noqa: F401,F403
 from .layers import _param  # noqa: F401
-from .module import (LoadStateDictReport, Module, ModuleDict, ModuleError, ModuleList, ParameterDict, ParameterList,
+from .enums import (CTCReduction, DistanceKind, EmbeddingBagMode, PaddingMode, Reduction, TransformerActivation,  # noqa: F401
+                    UpsampleMode)
+from .module import (LoadStateDictReport, Module, ModuleDict, ModuleError, ModuleList, ModuleRegistrationError, StateDictError, ParameterDict, ParameterList,
                      Sequential, StateDict, clip_grad_norm_, clip_grad_value_, module_load_state_dict,
                      module_state_dict, named_buffers, named_modules, named_parameters, parameters_to_vector,
                      vector_to_parameters)
@@ -11,6 +13,7 @@ from .extra import (AdaptiveLogSoftmaxWithLoss, FractionalMaxPool2d, FractionalM
                     MaxUnpool2d, MaxUnpool3d, MultiLabelMarginLoss, MultiLabelSoftMarginLoss, RNNConfig, RNNOutput,
                     TripletMarginWithDistanceLoss, Upsample, Upsample1d, Upsample2d, Upsample3d,
                     UpsamplingBilinear2d, UpsamplingNearest2d)
-from .utils import (MinMaxObserver, PackedSequence, QParams, QuantizedLinear, SpectralNorm, WeightNorm, dequantize,
+from .utils import (MinMaxObserver, PackedSequence, QParams, QuantizedLinear, QuantizedLinearQParams,
+                    QuantizedLinearWeightStorage, QuantizedStorageDType, SpectralNorm, WeightNorm, dequantize,
                     pack_padded_sequence, pack_sequence, pad_packed_sequence, pad_sequence, quantize_per_tensor,
                     spectral_norm, weight_norm)

@@ -25,6 +25,26 @@ class ModuleError(RuntimeError):
         self.reason_code = reason_code
 
 
+class ModuleRegistrationError(ModuleError):
+    """Refused registration of a parameter, buffer or child (ft-nn/src/lib.rs:133).  ``kind`` is ``InvalidName``
+    (with ``what``: parameter / buffer / module), ``NameConflict`` (with ``name``) or ``Unsupported`` (with
+    ``module_type`` and ``operation``)."""
+
+    def __init__(self, kind: str, reason_code: str, message: str, **fields):
+        super().__init__(reason_code, message)
+        self.kind, self.fields = kind, fields
+
+
+class StateDictError(ModuleError):
+    """Failure to build or load a state dict (ft-nn/src/lib.rs:177).  ``kind`` is ``DuplicateStateKey``,
+    ``UnsupportedDType``, ``StrictKeyMismatch`` (with ``missing_keys`` / ``unexpected_keys``), ``ShapeMismatch``
+    (with ``key``, ``expected``, ``found``) or ``DTypeMismatch``."""
+
+    def __init__(self, kind: str, reason_code: str, message: str, **fields):
+        super().__init__(reason_code, message)
+        self.kind, self.fields = kind, fields
+
+
 @dataclass
 class LoadStateDictReport:
     missing_keys: List[str] = field(default_factory=list)
@@ -46,21 +66,21 @@ class Module:
     # ------------------------------------------------------------------ registration
     def register_parameter(self, name: str, node_id: Optional[int]) -> None:
         if not _valid_name(name):
-            raise ModuleError("invalid_parameter_name", f"invalid parameter name {name!r}")
+            raise ModuleRegistrationError("InvalidName", "invalid_parameter_name", f"invalid parameter name {name!r}", what="parameter")
         if name in self._buffers or name in self._modules:
-            raise ModuleError("name_collision", f"{name!r} is already registered as a buffer or child")
+            raise ModuleRegistrationError("NameConflict", "name_collision", f"{name!r} is already registered as a buffer or child", name=name)
         self._parameters[name] = node_id
 
     def register_buffer(self, name: str, node_id: Optional[int], persistent: bool = True) -> None:
         if not _valid_name(name):
-            raise ModuleError("invalid_buffer_name", f"invalid buffer name {name!r}")
+            raise ModuleRegistrationError("InvalidName", "invalid_buffer_name", f"invalid buffer name {name!r}", what="buffer")
         if name in self._parameters or name in self._modules:
-            raise ModuleError("name_collision", f"{name!r} is already registered as a parameter or child")
+            raise ModuleRegistrationError("NameConflict", "name_collision", f"{name!r} is already registered as a parameter or child", name=name)
         self._buffers[name] = (node_id, persistent)
 
     def add_module(self, name: str, module: Optional["Module"]) -> None:
         if not _valid_name(name):
-            raise ModuleError("invalid_module_name", f"invalid child name {name!r}")
+            raise ModuleRegistrationError("InvalidName", "invalid_module_name", f"invalid child name {name!r}", what="module")
         self._modules[name] = module
 
     def __setattr__(self, name, value):
@@ -147,6 +167,8 @@ class Module:
     def state_dict(self, session, prefix: str = "") -> StateDict:
         sd = {}
         for name, nid in self.named_parameters(prefix) + self.named_buffers(prefix, persistent_only=True):
+            if name in sd:
+                raise StateDictError("DuplicateStateKey", "state_dict_duplicate_key", f"duplicate state key '{name}'", key=name)
             sd[name] = session.tensor(nid).detach().clone()
         return dict(sorted(sd.items()))
 
@@ -155,18 +177,20 @@ class Module:
         report = LoadStateDictReport(sorted(k for k in targets if k not in state),
                                      sorted(k for k in state if k not in targets))
         if strict and (report.missing_keys or report.unexpected_keys):
-            raise ModuleError("state_dict_key_mismatch",
-                              f"missing keys {report.missing_keys}, unexpected keys {report.unexpected_keys}")
+            raise StateDictError("StrictKeyMismatch", "state_dict_key_mismatch",
+                                 f"missing keys {report.missing_keys}, unexpected keys {report.unexpected_keys}",
+                                 missing_keys=report.missing_keys, unexpected_keys=report.unexpected_keys)
         # validate everything before touching anything
         for k, src in state.items():
             if k not in targets:
                 continue
             dst = session.tensor(targets[k])
             if tuple(dst.shape) != tuple(src.shape):
-                raise ModuleError("state_dict_shape_mismatch",
-                                  f"shape mismatch for {k}: expected {tuple(dst.shape)}, got {tuple(src.shape)}")
+                raise StateDictError("ShapeMismatch", "state_dict_shape_mismatch",
+                                     f"shape mismatch for {k}: expected {tuple(dst.shape)}, got {tuple(src.shape)}",
+                                     key=k, expected=tuple(dst.shape), found=tuple(src.shape))
             if strict and dst.dtype != src.dtype and dst.is_floating_point() != src.is_floating_point():
-                raise ModuleError("state_dict_dtype_mismatch", f"dtype mismatch for {k}: {dst.dtype} vs {src.dtype}")
+                raise StateDictError("DTypeMismatch", "state_dict_dtype_mismatch", f"dtype mismatch for {k}: {dst.dtype} vs {src.dtype}", key=k)
         with session.no_grad():
             for k, src in state.items():
                 if k in targets:

@@ -5,8 +5,10 @@ spectral_norm :19457-19601, QParams / MinMaxObserver / QuantizedLinear :20024-20
 """
 from __future__ import annotations
 
+import enum
+import math
 from dataclasses import dataclass
-from typing import List, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 
@@ -141,11 +143,124 @@ def dequantize(q: torch.Tensor, qp: QParams) -> torch.Tensor:
     return (q.to(torch.float32) - qp.zero_point) * qp.scale
 
 
-class QuantizedLinear(Module):
-    """int8 weight (per-tensor affine), dynamic per-call activation quantisation, fp32 accumulate."""
+class QuantizedStorageDType(enum.Enum):
+    """Physical dtype of packed affine-quantized weights (ft-nn/src/lib.rs:20192)."""
+    QInt8 = "qint8"
+    QUInt8 = "quint8"
 
-    def __init__(self, session, linear: Linear):
+    def qrange(self) -> Tuple[int, int]:
+        return (-128, 127) if self is QuantizedStorageDType.QInt8 else (0, 255)
+
+    def torch_dtype(self) -> torch.dtype:
+        return torch.int8 if self is QuantizedStorageDType.QInt8 else torch.uint8
+
+    def validate_qparams(self, qp: QParams) -> None:
+        if not math.isfinite(qp.scale) or qp.scale <= 0:
+            raise ValueError("QuantizedLinear: scale must be finite and > 0")
+        if qp.qmin >= qp.qmax:
+            raise ValueError("QuantizedLinear: qmin must be < qmax")
+        if not qp.qmin <= qp.zero_point <= qp.qmax:
+            raise ValueError("QuantizedLinear: zero_point must lie in [qmin, qmax]")
+        lo, hi = self.qrange()
+        if qp.qmin < lo or qp.qmax > hi:
+            raise ValueError("QuantizedLinear: qparams exceed storage dtype range")
+
+
+@dataclass
+class QuantizedLinearQParams:
+    """Layout of the weight's quantization parameters (ft-nn/src/lib.rs:20233): one set for the whole tensor, or
+    one per slice of ``axis`` (0 = per output feature, 1 = per input feature)."""
+    per_tensor: Optional[QParams] = None
+    axis: Optional[int] = None
+    channels: Optional[List[QParams]] = None
+
+    @staticmethod
+    def PerTensor(qp: QParams) -> "QuantizedLinearQParams":
+        return QuantizedLinearQParams(per_tensor=qp)
+
+    @staticmethod
+    def PerChannel(axis: int, channels: Sequence[QParams]) -> "QuantizedLinearQParams":
+        return QuantizedLinearQParams(axis=int(axis), channels=list(channels))
+
+    @property
+    def is_per_channel(self) -> bool:
+        return self.channels is not None
+
+    def validate(self, dtype: QuantizedStorageDType, in_features: int, out_features: int) -> None:
+        if not self.is_per_channel:
+            dtype.validate_qparams(self.per_tensor)
+            return
+        if self.axis not in (0, 1):
+            raise ValueError("QuantizedLinear: per-channel axis must be 0 (out_features) or 1 (in_features)")
+        want = out_features if self.axis == 0 else in_features
+        if len(self.channels) != want:
+            raise ValueError(f"QuantizedLinear: {len(self.channels)} channel qparams for {want} channels")
+        for qp in self.channels:
+            dtype.validate_qparams(qp)
+
+    def broadcast(self, out_features: int, in_features: int, dtype=torch.float64):
+        """``(scale, zero_point, qmin, qmax)`` tensors broadcastable against the ``[out, in]`` weight."""
+        if not self.is_per_channel:
+            q = self.per_tensor
+            return (torch.tensor(q.scale, dtype=dtype), torch.tensor(float(q.zero_point), dtype=dtype),
+                    torch.tensor(float(q.qmin), dtype=dtype), torch.tensor(float(q.qmax), dtype=dtype))
+        shape = (out_features, 1) if self.axis == 0 else (1, in_features)
+        col = lambda f: torch.tensor([float(f(q)) for q in self.channels], dtype=dtype).reshape(shape)   # noqa: E731
+        return col(lambda q: q.scale), col(lambda q: q.zero_point), col(lambda q: q.qmin), col(lambda q: q.qmax)
+
+
+class QuantizedLinearWeightStorage:
+    """Packed integer codes of a quantized ``[out, in]`` weight (ft-nn/src/lib.rs:20310): int8 or uint8."""
+
+    def __init__(self, dtype: QuantizedStorageDType, codes: torch.Tensor):
+        if codes.dtype != dtype.torch_dtype():
+            raise ValueError(f"{dtype.name} storage needs {dtype.torch_dtype()} codes")
+        self.dtype, self.codes = dtype, codes.contiguous()
+
+    @staticmethod
+    def from_float_values(values: torch.Tensor, dtype: QuantizedStorageDType, layout: QuantizedLinearQParams) -> "QuantizedLinearWeightStorage":
+        """Round-to-nearest-even affine quantisation, clamped to ``[qmin, qmax]``."""
+        w = values.to(torch.float64)
+        if not torch.isfinite(w).all():
+            raise ValueError("QuantizedLinear: weights must be finite")
+        scale, zp, qmin, qmax = layout.broadcast(*w.shape)
+        q = torch.minimum(torch.maximum(torch.round(w / scale) + zp, qmin), qmax)
+        return QuantizedLinearWeightStorage(dtype, q.to(dtype.torch_dtype()))
+
+    def __len__(self) -> int:
+        return self.codes.numel()
+
+    def qint8_values(self) -> Optional[List[int]]:
+        return self.codes.reshape(-1).tolist() if self.dtype is QuantizedStorageDType.QInt8 else None
+
+    def quint8_values(self) -> Optional[List[int]]:
+        return self.codes.reshape(-1).tolist() if self.dtype is QuantizedStorageDType.QUInt8 else None
+
+    def dequantized(self, layout: QuantizedLinearQParams) -> torch.Tensor:
+        scale, zp, _, _ = layout.broadcast(*self.codes.shape)
+        return (self.codes.to(torch.float64) - zp) * scale
+
+    def dequantized_values(self, qp: QParams) -> List[float]:
+        return self.dequantized(QuantizedLinearQParams.PerTensor(qp)).reshape(-1).tolist()
+
+
+class QuantizedLinear(Module):
+    """Linear layer with an affine-quantized weight.
+
+    Two forms (ft-nn/src/lib.rs:20530):
+
+    * ``QuantizedLinear(session, linear)`` quantizes an existing layer per tensor to int8 and quantizes the
+      activations dynamically per call (integer-valued product, fp32 accumulate); its output is a leaf.
+    * ``from_float_weights`` / ``from_float_weights_per_channel`` pack given float weights with given quantization
+      parameters (int8 or uint8 storage).  The forward dequantizes the weight and runs ``x @ W^T + b`` through the
+      session's operators, so a gradient reaches the input; the module has no trainable parameters.
+    """
+
+    def __init__(self, session=None, linear: Optional[Linear] = None):
         super().__init__()
+        self._packed = None
+        if linear is None:
+            return
         w = session.tensor(linear.weight).detach().float()
         obs = MinMaxObserver()
         obs.observe(w)
@@ -153,7 +268,85 @@ class QuantizedLinear(Module):
         self.wq = quantize_per_tensor(w, self.wq_params)
         self.bias = None if linear.bias is None else session.tensor(linear.bias).detach().float()
 
+    # ------------------------------------------------------------------ packed constructors
+    @classmethod
+    def _pack(cls, weight_values, bias, in_features, out_features, dtype, layout) -> "QuantizedLinear":
+        if in_features <= 0:
+            raise ValueError("QuantizedLinear: in_features must be > 0")
+        if out_features <= 0:
+            raise ValueError("QuantizedLinear: out_features must be > 0")
+        w = torch.as_tensor(weight_values, dtype=torch.float64).reshape(-1)
+        if w.numel() != in_features * out_features:
+            raise ValueError("QuantizedLinear: weight length must equal out_features * in_features")
+        if bias is not None and len(bias) != out_features:
+            raise ValueError("QuantizedLinear: bias length must equal out_features")
+        layout.validate(dtype, in_features, out_features)
+        m = cls()
+        storage = QuantizedLinearWeightStorage.from_float_values(w.reshape(out_features, in_features), dtype, layout)
+        m._packed = (storage, layout, None if bias is None else [float(b) for b in bias], int(in_features), int(out_features))
+        return m
+
+    @classmethod
+    def from_float_weights(cls, weight_values, bias, in_features: int, out_features: int,
+                           weight_dtype: QuantizedStorageDType, weight_qparams: QParams) -> "QuantizedLinear":
+        return cls._pack(weight_values, bias, in_features, out_features, weight_dtype,
+                         QuantizedLinearQParams.PerTensor(weight_qparams))
+
+    @classmethod
+    def from_float_weights_per_channel(cls, weight_values, bias, in_features: int, out_features: int,
+                                       weight_dtype: QuantizedStorageDType, channel_axis: int,
+                                       channel_qparams: Sequence[QParams]) -> "QuantizedLinear":
+        return cls._pack(weight_values, bias, in_features, out_features, weight_dtype,
+                         QuantizedLinearQParams.PerChannel(channel_axis, channel_qparams))
+
+    # ------------------------------------------------------------------ accessors of the packed form
+    def _need_packed(self):
+        if self._packed is None:
+            raise ValueError("this QuantizedLinear was built from a Linear layer, not from packed weights")
+        return self._packed
+
+    def weight_storage(self) -> QuantizedLinearWeightStorage:
+        return self._need_packed()[0]
+
+    def weight_tensor(self) -> torch.Tensor:
+        """The integer codes as an ``[out, in]`` tensor."""
+        return self._need_packed()[0].codes
+
+    def weight_qparam_layout(self) -> QuantizedLinearQParams:
+        return self._need_packed()[1]
+
+    def weight_qparams(self) -> Optional[QParams]:
+        return self._need_packed()[1].per_tensor
+
+    def weight_quantization_axis(self) -> Optional[int]:
+        return self._need_packed()[1].axis
+
+    def weight_channel_qparams(self) -> Optional[List[QParams]]:
+        return self._need_packed()[1].channels
+
+    def bias_values(self) -> Optional[List[float]]:
+        return self._need_packed()[2]
+
+    def in_features(self) -> int:
+        return self._need_packed()[3]
+
+    def out_features(self) -> int:
+        return self._need_packed()[4]
+
+    def parameters(self):
+        return []
+
+    # ------------------------------------------------------------------ forward
     def forward(self, session, x):
+        if self._packed is not None:
+            storage, layout, bias, in_f, out_f = self._packed
+            dt = session.tensor_dtype(x)
+            w = session.tensor_tape.leaf(storage.dequantized(layout).to(device=session.device, dtype=dt.to_torch()), False)
+            y = session.tensor_matmul(x, session.tensor_transpose(w, dim0=0, dim1=1))
+            if bias is None:
+                return y
+            b = session.tensor_tape.leaf(torch.tensor(bias, dtype=dt.to_torch(), device=session.device), False)
+            return session.tensor_add(y, b)
         xt = session.tensor(x).detach().float()
         obs = MinMaxObserver()
         obs.observe(xt)

@@ -16,6 +16,7 @@ session's storage layer.
 """
 from __future__ import annotations
 
+import enum
 import math
 from typing import Callable, Dict, List, Optional, Sequence
 
@@ -442,8 +443,29 @@ class Muon(Optimizer):
         _apply(w, wf - self.lr * u)
 
 
+class LBFGSLineSearch(enum.Enum):
+    """Step-length rule of :class:`LBFGS` (ft-optim/src/lib.rs:1818)."""
+    NoSearch = "none"                       # the reference's ``None`` variant: a fixed step of ``lr``
+    BacktrackingArmijo = "backtracking_armijo"
+    StrongWolfe = "strong_wolfe"
+
+    @staticmethod
+    def parse(v) -> "LBFGSLineSearch":
+        if isinstance(v, LBFGSLineSearch):
+            return v
+        if v is None:
+            return LBFGSLineSearch.NoSearch
+        key = str(v).lower()
+        alias = {"none": "none", "backtracking": "backtracking_armijo", "armijo": "backtracking_armijo",
+                 "backtracking_armijo": "backtracking_armijo", "strong_wolfe": "strong_wolfe"}
+        if key not in alias:
+            raise ValueError(f"unknown LBFGS line search {v!r}")
+        return LBFGSLineSearch(alias[key])
+
+
 class LBFGS(Optimizer):
-    """Limited-memory BFGS with an optional backtracking (Armijo) line search (ft-optim :1829)."""
+    """Limited-memory BFGS (ft-optim :1829) with a fixed step, a backtracking Armijo search, or a strong-Wolfe
+    search (bracketing, then a zoom phase with safeguarded cubic interpolation; c1 = 1e-4, c2 = 0.9)."""
 
     def __init__(self, params, lr=1.0, max_iter=20, history_size=100, tolerance_grad=1e-7, tolerance_change=1e-9,
                  line_search: Optional[str] = None):
@@ -466,6 +488,62 @@ class LBFGS(Optimizer):
             session.tensor_update_param_values(p, flat[off: off + n])
             off += n
 
+    def _phi(self, session, closure, x0, d, t):
+        """Loss and directional derivative at ``x0 + t d`` (leaves the parameters there)."""
+        self._set(session, x0 + t * d)
+        f = float(closure())
+        return f, float(self._flat(session, True) @ d)
+
+    @staticmethod
+    def _cubic_min(a, fa, ga, b, fb, gb):
+        """Minimiser of the cubic through (a, fa, ga), (b, fb, gb), kept inside the middle 80 % of the interval."""
+        lo, hi = (a, b) if a <= b else (b, a)
+        d1 = ga + gb - 3 * (fa - fb) / (a - b)
+        sq = d1 * d1 - ga * gb
+        if sq >= 0:
+            d2 = math.sqrt(sq)
+            t = b - (b - a) * ((gb + d2 - d1) / (gb - ga + 2 * d2)) if a <= b else a - (a - b) * ((ga + d2 - d1) / (ga - gb + 2 * d2))
+        else:
+            t = 0.5 * (lo + hi)
+        return min(max(t, lo + 0.1 * (hi - lo)), hi - 0.1 * (hi - lo))
+
+    def _strong_wolfe(self, session, closure, x0, d, f0, g0, t, c1=1e-4, c2=0.9, max_ls=25):
+        """Step ``t`` with ``f(t) <= f0 + c1 t g0`` and ``|g(t)| <= c2 |g0|``; returns ``(t, f(t))`` with the
+        parameters (and their gradients) left at that point."""
+        if g0 >= 0:                       # not a descent direction: take no step
+            self._set(session, x0)
+            return 0.0, float(closure())
+        t_prev, f_prev, g_prev = 0.0, f0, g0
+        bracket = None
+        for it in range(max_ls):
+            f, gt = self._phi(session, closure, x0, d, t)
+            if f > f0 + c1 * t * g0 or (it > 0 and f >= f_prev):
+                bracket = (t_prev, f_prev, g_prev, t, f, gt)
+                break
+            if abs(gt) <= -c2 * g0:
+                return t, f
+            if gt >= 0:
+                bracket = (t, f, gt, t_prev, f_prev, g_prev)
+                break
+            t_prev, f_prev, g_prev, t = t, f, gt, t * 2.0
+        if bracket is None:
+            return t_prev, self._phi(session, closure, x0, d, t_prev)[0]
+        lo, f_lo, g_lo, hi, f_hi, g_hi = bracket
+        for _ in range(max_ls):
+            if abs(hi - lo) < 1e-12:
+                break
+            t = self._cubic_min(lo, f_lo, g_lo, hi, f_hi, g_hi)
+            f, gt = self._phi(session, closure, x0, d, t)
+            if f > f0 + c1 * t * g0 or f >= f_lo:
+                hi, f_hi, g_hi = t, f, gt
+            else:
+                if abs(gt) <= -c2 * g0:
+                    return t, f
+                if gt * (hi - lo) >= 0:
+                    hi, f_hi, g_hi = lo, f_lo, g_lo
+                lo, f_lo, g_lo = t, f, gt
+        return lo, self._phi(session, closure, x0, d, lo)[0]
+
     def step(self, session, closure: Callable[[], float]) -> float:
         """``closure`` zeroes the gradients, runs forward + backward and returns the loss value."""
         loss = float(closure())
@@ -484,7 +562,8 @@ class LBFGS(Optimizer):
                 q += (a - float(y @ q) / float(y @ s)) * s
             d = -q
             x0, t = self._flat(session, False), self.lr
-            if self.line_search in ("backtracking", "armijo", "strong_wolfe"):
+            ls = LBFGSLineSearch.parse(self.line_search)
+            if ls is LBFGSLineSearch.BacktrackingArmijo:
                 gd = float(g @ d)
                 for _ls in range(20):
                     self._set(session, x0 + t * d)
@@ -492,6 +571,8 @@ class LBFGS(Optimizer):
                     if new_loss <= loss + 1e-4 * t * gd:
                         break
                     t *= 0.5
+            elif ls is LBFGSLineSearch.StrongWolfe:
+                t, new_loss = self._strong_wolfe(session, closure, x0, d, loss, float(g @ d), t)
             else:
                 self._set(session, x0 + t * d)
                 new_loss = float(closure())

@@ -178,12 +178,40 @@ class OneCycleLR(LRScheduler):
         return self._interp(self.max_lr, self.min_lr, (e - up) / (self.total - 1 - up))
 
 
+class CyclicLRMode:
+    """Amplitude policy of :class:`CyclicLR` (ft-optim/src/lib.rs:4381): ``Triangular`` (constant), ``Triangular2``
+    (halved every cycle) or ``ExpRange(gamma)`` (scaled by ``gamma ** iteration``)."""
+
+    def __init__(self, name: str, gamma: float = 1.0):
+        if name not in ("triangular", "triangular2", "exp_range"):
+            raise ValueError(f"unknown CyclicLR mode {name!r}")
+        self.name, self.gamma = name, float(gamma)
+
+    @staticmethod
+    def ExpRange(gamma: float) -> "CyclicLRMode":
+        return CyclicLRMode("exp_range", gamma)
+
+    def scale(self, cycle: int, iteration: int) -> float:
+        return {"triangular": 1.0, "triangular2": 1.0 / (2 ** (cycle - 1)), "exp_range": self.gamma ** iteration}[self.name]
+
+    def __eq__(self, other):
+        return isinstance(other, CyclicLRMode) and (other.name, other.gamma) == (self.name, self.gamma)
+
+    def __repr__(self):
+        return f"CyclicLRMode.ExpRange(gamma={self.gamma})" if self.name == "exp_range" else f"CyclicLRMode.{self.name.title()}"
+
+
+CyclicLRMode.Triangular = CyclicLRMode("triangular")
+CyclicLRMode.Triangular2 = CyclicLRMode("triangular2")
+
+
 class CyclicLR(LRScheduler):
     def __init__(self, optimizer, base_lr: float, max_lr: float, step_size_up: int = 2000,
-                 step_size_down: Optional[int] = None, mode: str = "triangular", gamma: float = 1.0):
+                 step_size_down: Optional[int] = None, mode="triangular", gamma: float = 1.0):
         super().__init__(optimizer)
         self.lo, self.hi, self.up, self.down = base_lr, max_lr, step_size_up, step_size_down or step_size_up
-        self.mode, self.gamma = mode, gamma
+        self.policy = mode if isinstance(mode, CyclicLRMode) else CyclicLRMode(mode, gamma)
+        self.mode, self.gamma = self.policy.name, self.policy.gamma
         optimizer.set_lr(base_lr)
         self.last_lr = base_lr
 
@@ -192,8 +220,7 @@ class CyclicLR(LRScheduler):
         cycle = math.floor(1 + e / total)
         x = 1 + e / total - cycle
         pos = x / (self.up / total) if x <= self.up / total else (x - 1) / (self.up / total - 1)
-        scale = {"triangular": 1.0, "triangular2": 1 / (2 ** (cycle - 1)), "exp_range": self.gamma ** e}[self.mode]
-        return self.lo + (self.hi - self.lo) * pos * scale
+        return self.lo + (self.hi - self.lo) * pos * self.policy.scale(cycle, e)
 
 
 class ReduceLROnPlateau(LRScheduler):

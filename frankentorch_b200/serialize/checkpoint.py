@@ -25,6 +25,7 @@ about 1/255, vanishing with every surplus symbol).
 """
 from __future__ import annotations
 
+import enum
 import json
 import math
 import struct
@@ -96,6 +97,67 @@ def encode_checkpoint(entries: Sequence[SnapshotEntry], mode: ExecutionMode = Ex
     if len(text.encode()) > MAX_PAYLOAD_BYTES:
         raise SerializeError("PayloadTooLarge", f"payload exceeds {MAX_PAYLOAD_BYTES} bytes")
     return text
+
+
+class CheckpointMode(enum.Enum):
+    """Mode stamped into an envelope when it is written (ft-serialize/src/lib.rs:49)."""
+    Strict = "strict"
+    Hardened = "hardened"
+
+    def execution_mode(self) -> ExecutionMode:
+        return ExecutionMode.parse(self.value)
+
+
+class DecodeMode(enum.Enum):
+    """Diagnostic style of the decoder (ft-serialize/src/lib.rs:55): strict reports the parser's position, hardened
+    classifies the payload as incompatible and says why."""
+    Strict = "strict"
+    Hardened = "hardened"
+
+    def execution_mode(self) -> ExecutionMode:
+        return ExecutionMode.parse(self.value)
+
+
+def _exec_mode(mode) -> ExecutionMode:
+    return mode.execution_mode() if isinstance(mode, (CheckpointMode, DecodeMode)) else ExecutionMode.parse(mode)
+
+
+@dataclass(frozen=True)
+class CheckpointEnvelope:
+    """The decoded document (ft-serialize/src/lib.rs:62): version, writer's mode, normalised entries and the hash
+    that binds them."""
+    schema_version: int
+    mode: CheckpointMode
+    entries: Tuple[SnapshotEntry, ...]
+    source_hash: str
+
+    def to_json(self) -> str:
+        return json.dumps({"schema_version": self.schema_version, "mode": self.mode.value,
+                           "entries": [{"node_id": e.node_id, "value": e.value, "grad": e.grad} for e in self.entries],
+                           "source_hash": self.source_hash}, separators=(",", ":"))
+
+
+def encode_envelope(entries: Sequence[SnapshotEntry], mode=CheckpointMode.Strict) -> CheckpointEnvelope:
+    """Validate and normalise ``entries`` and bind them with the source hash, without rendering JSON."""
+    text = encode_checkpoint(entries, _exec_mode(mode))
+    return decode_envelope(text, DecodeMode.Strict)
+
+
+def decode_envelope(text: str, mode=DecodeMode.Strict, runtime=None) -> CheckpointEnvelope:
+    """``decode_checkpoint`` returning the whole envelope record."""
+    m, entries = decode_checkpoint(text, _exec_mode(mode), runtime)
+    doc = json.loads(text)
+    return CheckpointEnvelope(int(doc["schema_version"]), CheckpointMode(m.value), tuple(entries), doc["source_hash"])
+
+
+def encode_snapshot(entries: Sequence[SnapshotEntry]) -> str:
+    """Strict-mode envelope of ``entries`` (ft-serialize/src/lib.rs:166)."""
+    return encode_checkpoint(entries, ExecutionMode.Strict)
+
+
+def decode_snapshot(text: str) -> List[SnapshotEntry]:
+    """Entries of a strict-mode decode (ft-serialize/src/lib.rs:170)."""
+    return decode_checkpoint(text, ExecutionMode.Strict)[1]
 
 
 _TOP_KEYS = {"schema_version", "mode", "entries", "source_hash"}
@@ -201,6 +263,15 @@ class RepairSymbol:
     bytes: str      # hex
 
 
+@dataclass(frozen=True)
+class RepairSymbolRecord:
+    """Manifest line of one repair symbol (ft-serialize/src/lib.rs:71): its encoding symbol id, how many source
+    symbols it combines, and its length in bytes; the payload itself stays in the sidecar."""
+    esi: int
+    degree: int
+    bytes: int
+
+
 @dataclass
 class RepairSidecar:
     """Repair symbols stored next to an artifact (field set of the reference's sidecar record,
@@ -218,6 +289,9 @@ class RepairSidecar:
 
     def to_json(self) -> str:
         return json.dumps(asdict(self), separators=(",", ":"))
+
+    def symbol_records(self) -> List[RepairSymbolRecord]:
+        return [RepairSymbolRecord(r.esi, r.degree, len(r.bytes) // 2) for r in self.repair_manifest]
 
 
 # Name under which the reference exposes this record.  The record's ``code`` field says which

@@ -190,7 +190,46 @@ _ST_NAME = {torch.float64: "F64", torch.float32: "F32", torch.float16: "F16", to
 _ST_DTYPE = {v: k for k, v in _ST_NAME.items()}
 
 
-def save_safetensors(sd: Dict[str, torch.Tensor], path: str, metadata: Optional[Dict[str, str]] = None) -> None:
+class TensorIOError(SerializeError):
+    """Failure of a tensor file operation (ft-serialize/src/lib.rs:608).  ``kind`` is one of ``Io`` (with ``path``),
+    ``InvalidMagic``, ``UnsupportedVersion`` (with ``found`` / ``max``), ``Corrupt`` (with ``reason``) and
+    ``TensorError``; decoders of this module raise the parent class with finer kinds, and ``classify`` maps those
+    onto this set."""
+
+    KINDS = ("Io", "InvalidMagic", "UnsupportedVersion", "Corrupt", "TensorError")
+
+    def __init__(self, kind: str, message: str, **fields):
+        if kind not in self.KINDS:
+            raise ValueError(f"unknown TensorIOError kind {kind!r}")
+        super().__init__(kind, message)
+        self.fields = fields
+
+    @staticmethod
+    def classify(err: Exception, path: Optional[str] = None) -> "TensorIOError":
+        if isinstance(err, TensorIOError):
+            return err
+        if isinstance(err, OSError):
+            return TensorIOError("Io", f"I/O error at '{path}': {err.strerror or err}", path=path, detail=str(err))
+        if isinstance(err, SerializeError):
+            if err.kind in ("InvalidMagic", "UnsupportedVersion"):
+                return TensorIOError(err.kind, str(err))
+            if err.kind in ("InvalidShape", "ShapeOverflow", "InvalidDType", "UnsupportedDType"):
+                return TensorIOError("TensorError", str(err))
+            return TensorIOError("Corrupt", f"corrupt file: {err}", reason=str(err))
+        return TensorIOError("Corrupt", f"corrupt file: {err}", reason=str(err))
+
+
+def load_tensor_file(path: str) -> Dict[str, torch.Tensor]:
+    """Load an FTSV or SafeTensors file (told apart by the magic bytes); every failure is a ``TensorIOError``."""
+    try:
+        with open(path, "rb") as f:
+            data = f.read()
+        return load_state_dict_from_bytes(data) if data[:4] == b"FTSV" else load_safetensors_from_bytes(data)
+    except (OSError, SerializeError, ValueError, KeyError, struct.error) as e:
+        raise TensorIOError.classify(e, path) from e
+
+
+def save_safetensors_to_bytes(sd: Dict[str, torch.Tensor], metadata: Optional[Dict[str, str]] = None) -> bytes:
     header, chunks, off = {}, [], 0
     if metadata:
         header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
@@ -204,11 +243,13 @@ def save_safetensors(sd: Dict[str, torch.Tensor], path: str, metadata: Optional[
         off += len(b)
     hb = json.dumps(header, separators=(",", ":")).encode()
     hb += b" " * ((8 - len(hb) % 8) % 8)
+    return struct.pack("<Q", len(hb)) + hb + b"".join(chunks)
+
+
+def save_safetensors(sd: Dict[str, torch.Tensor], path: str, metadata: Optional[Dict[str, str]] = None) -> None:
+    data = save_safetensors_to_bytes(sd, metadata)
     with open(path, "wb") as f:
-        f.write(struct.pack("<Q", len(hb)))
-        f.write(hb)
-        for c in chunks:
-            f.write(c)
+        f.write(data)
 
 
 def _st_header(data: bytes):
@@ -224,7 +265,11 @@ def _st_header(data: bytes):
 
 
 def load_safetensors(path: str) -> Dict[str, torch.Tensor]:
-    data = open(path, "rb").read()
+    with open(path, "rb") as f:
+        return load_safetensors_from_bytes(f.read())
+
+
+def load_safetensors_from_bytes(data: bytes) -> Dict[str, torch.Tensor]:
     header, base = _st_header(data)
     out = {}
     for k, info in header.items():
@@ -311,3 +356,11 @@ def export_linear_onnx_to_bytes(weight: torch.Tensor, bias: Optional[torch.Tenso
              + _field(11, 2, _value_info("x", ["batch", in_f])) + _field(12, 2, _value_info("y", ["batch", out_f])))
     model = _int(1, 8) + _str(2, producer) + _field(7, 2, graph) + _field(8, 2, _str(1, "") + _int(2, 17))
     return model
+
+
+def save_linear_onnx(weight: torch.Tensor, bias: Optional[torch.Tensor], path: str, producer: str = "frankentorch_b200") -> int:
+    """Write ``export_linear_onnx_to_bytes`` to ``path``; returns the byte count (ft-serialize/src/lib.rs:1539)."""
+    data = export_linear_onnx_to_bytes(weight, bias, producer)
+    with open(path, "wb") as f:
+        f.write(data)
+    return len(data)

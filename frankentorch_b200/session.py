@@ -129,6 +129,9 @@ class FrankenTorchSession:
         self._autocast: Optional[DType] = None
         self._ledger_dispatch = ledger_dispatch
         self.last_decision: Optional[DispatchDecision] = None
+        # typed record of the last operator run through autograd/events.py; set ``operation_events`` to a list to keep all
+        self.last_operation_event = None
+        self.operation_events: Optional[list] = None
         self._dropout_calls = 0          # Philox offset of the next dropout on the GPU backend
         self._device_enum = Device.Cuda if self.is_cuda else Device.Cpu
         self.runtime.ledger.record(EvidenceKind.Policy,

@@ -1,0 +1,207 @@
+"""Public types that the reference's crates export next to their functions: serializer envelope / modes / error kinds
+(ft-serialize/src/lib.rs:49-75, :166-175, :608), optimizer option enums (ft-optim/src/lib.rs:1818, :4381), ``nn`` option
+enums, typed registration / state-dict errors and packed quantized linear weights (ft-nn/src/lib.rs:133, :177, :20192-20700)."""
+import os
+
+import pytest
+import torch
+
+from frankentorch_b200 import nn, serialize as S
+from frankentorch_b200.optim import LBFGS, SGD, CyclicLR, CyclicLRMode, LBFGSLineSearch
+from frankentorch_b200.session import FrankenTorchSession
+
+
+def test_checkpoint_envelope_modes_and_snapshot_shorthands():
+    entries = [S.SnapshotEntry(2, 1.5, None), S.SnapshotEntry(0, -2.0, 0.25)]
+    env = S.encode_envelope(entries, S.CheckpointMode.Hardened)
+    assert env.mode is S.CheckpointMode.Hardened and env.schema_version == 1 and [e.node_id for e in env.entries] == [0, 2]
+    assert env.source_hash.startswith("det64:")
+    assert S.decode_envelope(env.to_json(), S.DecodeMode.Hardened) == env
+    assert env.to_json() == S.encode_checkpoint(entries, "hardened")
+    assert S.decode_snapshot(S.encode_snapshot(entries)) == list(env.entries)
+    with pytest.raises(S.SerializeError) as strict:
+        S.decode_envelope("{", S.DecodeMode.Strict)
+    with pytest.raises(S.SerializeError) as hard:
+        S.decode_envelope("{", S.DecodeMode.Hardened)
+    assert "invalid json" in str(strict.value) and "incompatible payload" in str(hard.value)
+    side, _ = S.generate_repair_sidecar(b"frankentorch" * 400, 3)
+    recs = side.symbol_records()
+    assert len(recs) == side.repair_symbols and all(isinstance(r, S.RepairSymbolRecord) and r.bytes == side.symbol_size for r in recs)
+    assert [r.esi for r in recs] == [m.esi for m in side.repair_manifest]
+
+
+def test_tensor_io_error_kinds_and_byte_level_safetensors(tmp_path):
+    sd = {"w": torch.arange(6, dtype=torch.float32).reshape(2, 3), "b": torch.ones(2, dtype=torch.bfloat16)}
+    blob = S.save_safetensors_to_bytes(sd, {"note": "x"})
+    back = S.load_safetensors_from_bytes(blob)
+    assert all(torch.equal(back[k], sd[k]) for k in sd)
+    p = str(tmp_path / "a.safetensors")
+    S.save_safetensors(sd, p, {"note": "x"})
+    assert open(p, "rb").read() == blob and S.load_tensor_file(p).keys() == sd.keys()
+    f = str(tmp_path / "a.ftsv")
+    S.save_state_dict({"w": sd["w"]}, f)
+    assert torch.equal(S.load_tensor_file(f)["w"], sd["w"])
+    with pytest.raises(S.TensorIOError) as e:
+        S.load_tensor_file(str(tmp_path / "missing"))
+    assert e.value.kind == "Io" and e.value.fields["path"].endswith("missing")
+    open(f, "wb").write(b"FTSV" + (99).to_bytes(4, "little") + b"\0" * 8)
+    with pytest.raises(S.TensorIOError) as e:
+        S.load_tensor_file(f)
+    assert e.value.kind == "UnsupportedVersion"
+    open(p, "wb").write(blob[:24])
+    with pytest.raises(S.TensorIOError) as e:
+        S.load_tensor_file(p)
+    assert e.value.kind == "Corrupt" and "reason" in e.value.fields
+    with pytest.raises(ValueError):
+        S.TensorIOError("Nope", "x")
+    n = S.save_linear_onnx(torch.ones(2, 3), torch.zeros(2), str(tmp_path / "l.onnx"))
+    assert n == os.path.getsize(str(tmp_path / "l.onnx")) == len(S.export_linear_onnx_to_bytes(torch.ones(2, 3), torch.zeros(2)))
+
+
+def _rosenbrock(s, w):
+    x, y = s.tensor_select(w, 0, 0), s.tensor_select(w, 0, 1)
+    one, hundred = s.tensor_variable([1.0], []), s.tensor_variable([100.0], [])
+    return s.tensor_add(s.tensor_square(s.tensor_sub(one, x)), s.tensor_mul(hundred, s.tensor_square(s.tensor_sub(y, s.tensor_square(x)))))
+
+
+def test_lbfgs_strong_wolfe_search_converges_on_rosenbrock_with_fewer_evaluations():
+    def run(ls):
+        s = FrankenTorchSession(ledger_dispatch=False)
+        w = s.tensor_variable([-1.2, 1.0], [2], True)
+        opt = LBFGS([w], lr=1.0, max_iter=60, line_search=ls)
+        evals = [0]
+
+        def closure():
+            evals[0] += 1
+            s.tensor_zero_grads([w])
+            loss = _rosenbrock(s, w)
+            s.tensor_backward(loss)
+            return s.tensor_item(loss)
+        for _ in range(3):
+            loss = opt.step(s, closure)
+        return loss, s.tensor(w).tolist(), evals[0]
+    loss, w, n_wolfe = run(LBFGSLineSearch.StrongWolfe)
+    assert loss < 1e-12 and abs(w[0] - 1) < 1e-5 and abs(w[1] - 1) < 1e-5
+    loss_fixed, _, n_fixed = run(LBFGSLineSearch.NoSearch)
+    assert loss_fixed < 1e-8 and n_wolfe < n_fixed
+    assert LBFGSLineSearch.parse("strong_wolfe") is LBFGSLineSearch.StrongWolfe and LBFGSLineSearch.parse(None) is LBFGSLineSearch.NoSearch
+    assert LBFGSLineSearch.parse("armijo") is LBFGSLineSearch.BacktrackingArmijo
+    with pytest.raises(ValueError):
+        LBFGSLineSearch.parse("golden")
+
+
+def test_strong_wolfe_step_satisfies_both_conditions_on_a_quadratic():
+    s = FrankenTorchSession(ledger_dispatch=False)
+    w = s.tensor_variable([3.0, -2.0], [2], True)
+    scale = s.tensor_variable([1.0, 10.0], [2])
+    opt = LBFGS([w], line_search="strong_wolfe")
+
+    def closure():
+        s.tensor_zero_grads([w])
+        loss = s.tensor_sum(s.tensor_mul(scale, s.tensor_square(w)))
+        s.tensor_backward(loss)
+        return s.tensor_item(loss)
+    f0 = closure()
+    g = opt._flat(s, True)
+    d, x0 = -g, opt._flat(s, False)
+    g0 = float(g @ d)
+    t, f = opt._strong_wolfe(s, closure, x0, d, f0, g0, 1.0)
+    gt = float(opt._flat(s, True) @ d)
+    assert t > 0 and f <= f0 + 1e-4 * t * g0 and abs(gt) <= 0.9 * abs(g0)
+
+
+def test_cyclic_lr_mode_objects_drive_the_schedule():
+    def lrs(mode, gamma=1.0, n=9):
+        s = FrankenTorchSession(ledger_dispatch=False)
+        w = s.tensor_variable([0.0], [1], True)
+        opt = SGD([w], lr=0.1)
+        sched = CyclicLR(opt, 0.1, 1.0, step_size_up=2, mode=mode, gamma=gamma)
+        out = []
+        for _ in range(n):
+            out.append(round(opt.get_lr(), 10))
+            sched.step(opt)
+        return out
+    assert lrs(CyclicLRMode.Triangular) == lrs("triangular")
+    assert lrs(CyclicLRMode.Triangular2) == lrs("triangular2") and lrs(CyclicLRMode.Triangular2)[6] < lrs(CyclicLRMode.Triangular)[6]
+    assert lrs(CyclicLRMode.ExpRange(0.9)) == lrs("exp_range", 0.9)
+    assert CyclicLRMode.ExpRange(0.9) == CyclicLRMode("exp_range", 0.9) and CyclicLRMode.Triangular != CyclicLRMode.Triangular2
+    with pytest.raises(ValueError):
+        CyclicLRMode("sawtooth")
+
+
+def test_nn_option_enums_are_the_strings_the_modules_take():
+    assert nn.Reduction.Mean == "mean" and nn.Reduction.parse("SUM") is nn.Reduction.Sum and str(nn.Reduction.NoReduction) == "none"
+    assert nn.UpsampleMode.parse("nearest_exact") is nn.UpsampleMode.NearestExact and f"{nn.UpsampleMode.Bilinear}" == "bilinear"
+    assert nn.PaddingMode.Zeros.pad_mode() == "constant" and nn.PaddingMode.Reflect.pad_mode() == "reflect"
+    assert {m.value for m in nn.DistanceKind} == {"l2", "l1", "cosine"} and {m.value for m in nn.EmbeddingBagMode} == {"sum", "mean", "max"}
+    assert [m.value for m in nn.CTCReduction] == ["none", "sum", "mean"] and [m.value for m in nn.TransformerActivation] == ["relu", "gelu"]
+    with pytest.raises(ValueError):
+        nn.Reduction.parse("median")
+    s = FrankenTorchSession(ledger_dispatch=False)
+    a, b = s.tensor_variable([1.0, 2.0], [2]), s.tensor_variable([0.0, 0.0], [2])
+    assert s.tensor_item(nn.MSELoss(reduction=nn.Reduction.Sum)(s, a, b)) == 5.0
+    assert s.tensor_item(nn.MSELoss(reduction=nn.Reduction.Mean)(s, a, b)) == 2.5
+    x = s.tensor_variable(list(range(8)), [1, 1, 2, 4])
+    up = nn.Upsample(scale_factor=2, mode=nn.UpsampleMode.Nearest)(s, x)
+    assert s.tensor_shape(up) == [1, 1, 4, 8]
+
+
+def test_registration_and_state_dict_errors_are_typed():
+    s = FrankenTorchSession(ledger_dispatch=False)
+    m = nn.Linear(s, 3, 2)
+    with pytest.raises(nn.ModuleRegistrationError) as e:
+        m.register_parameter("a.b", None)
+    assert e.value.kind == "InvalidName" and e.value.fields == {"what": "parameter"} and isinstance(e.value, nn.ModuleError)
+    with pytest.raises(nn.ModuleRegistrationError) as e:
+        m.register_buffer("weight", None)
+    assert e.value.kind == "NameConflict" and e.value.fields == {"name": "weight"}
+    sd = m.state_dict(s)
+    with pytest.raises(nn.StateDictError) as e:
+        m.load_state_dict(s, {"weight": sd["weight"], "extra": sd["bias"]})
+    assert e.value.kind == "StrictKeyMismatch" and e.value.fields == {"missing_keys": ["bias"], "unexpected_keys": ["extra"]}
+    with pytest.raises(nn.StateDictError) as e:
+        m.load_state_dict(s, {"weight": torch.zeros(2, 2, dtype=torch.float64), "bias": sd["bias"]})
+    assert e.value.kind == "ShapeMismatch" and e.value.fields["expected"] == (2, 3) and e.value.fields["found"] == (2, 2)
+    assert e.value.reason_code == "state_dict_shape_mismatch"
+
+
+def test_packed_quantized_linear_per_tensor_and_per_channel():
+    w = [0.5, -0.25, 1.0, 0.1, 0.2, -0.3]
+    W = torch.tensor(w, dtype=torch.float64).reshape(2, 3)
+    q = nn.QuantizedLinear.from_float_weights(w, [0.5, -0.5], 3, 2, nn.QuantizedStorageDType.QInt8, nn.QParams(0.01, 0, -128, 127))
+    assert q.weight_storage().qint8_values() == [50, -25, 100, 10, 20, -30] and q.weight_storage().quint8_values() is None
+    assert q.weight_qparams() == nn.QParams(0.01, 0, -128, 127) and q.weight_quantization_axis() is None
+    assert (q.in_features(), q.out_features(), q.bias_values(), q.parameters()) == (3, 2, [0.5, -0.5], [])
+    assert q.weight_tensor().dtype == torch.int8 and tuple(q.weight_tensor().shape) == (2, 3)
+    s = FrankenTorchSession(ledger_dispatch=False)
+    X = torch.tensor([[1.0, 2.0, 3.0], [-1.0, 0.5, 0.25]], dtype=torch.float64)
+    x = s.tensor_variable(X.reshape(-1).tolist(), [2, 3], True)
+    y = q(s, x)
+    assert torch.allclose(s.tensor(y), X @ W.t() + torch.tensor([0.5, -0.5]), atol=1e-12)
+    rep = s.tensor_backward(s.tensor_sum(y))
+    assert torch.allclose(rep.gradient(x), W.sum(0).expand(2, 3))
+    # clamping at the storage range and round-to-nearest-even
+    c = nn.QuantizedLinear.from_float_weights([2.0, 0.005, 0.015], None, 3, 1, nn.QuantizedStorageDType.QInt8, nn.QParams(0.01, 0, -128, 127))
+    assert c.weight_storage().qint8_values() == [127, 0, 2]
+    pc = nn.QuantizedLinear.from_float_weights_per_channel(
+        w, None, 3, 2, nn.QuantizedStorageDType.QUInt8, 0, [nn.QParams(0.01, 128, 0, 255), nn.QParams(0.005, 100, 0, 255)])
+    assert pc.weight_storage().quint8_values() == [178, 103, 228, 120, 140, 40] and pc.weight_quantization_axis() == 0
+    assert len(pc.weight_channel_qparams()) == 2 and pc.weight_qparams() is None
+    assert torch.allclose(pc.weight_storage().dequantized(pc.weight_qparam_layout()), W, atol=1e-12)
+    assert torch.allclose(s.tensor(pc(s, x)), X @ W.t(), atol=1e-12)
+    for bad in (lambda: nn.QuantizedLinear.from_float_weights(w, None, 0, 2, nn.QuantizedStorageDType.QInt8, nn.QParams(0.01, 0)),
+                lambda: nn.QuantizedLinear.from_float_weights(w[:5], None, 3, 2, nn.QuantizedStorageDType.QInt8, nn.QParams(0.01, 0)),
+                lambda: nn.QuantizedLinear.from_float_weights(w, [0.0], 3, 2, nn.QuantizedStorageDType.QInt8, nn.QParams(0.01, 0)),
+                lambda: nn.QuantizedLinear.from_float_weights(w, None, 3, 2, nn.QuantizedStorageDType.QInt8, nn.QParams(0.0, 0)),
+                lambda: nn.QuantizedLinear.from_float_weights(w, None, 3, 2, nn.QuantizedStorageDType.QInt8, nn.QParams(0.01, 0, 0, 255)),
+                lambda: nn.QuantizedLinear.from_float_weights(w, None, 3, 2, nn.QuantizedStorageDType.QUInt8, nn.QParams(0.01, 300, 0, 255)),
+                lambda: nn.QuantizedLinear.from_float_weights_per_channel(w, None, 3, 2, nn.QuantizedStorageDType.QInt8, 0, [nn.QParams(0.01, 0)]),
+                lambda: nn.QuantizedLinear.from_float_weights_per_channel(w, None, 3, 2, nn.QuantizedStorageDType.QInt8, 2, [nn.QParams(0.01, 0)] * 2)):
+        with pytest.raises(ValueError):
+            bad()
+    assert nn.QuantizedStorageDType.QUInt8.qrange() == (0, 255)
+    # the layer-derived form still works and reports that it has no packed weights
+    lin = nn.QuantizedLinear(s, nn.Linear(s, 3, 2))
+    assert s.tensor_shape(lin(s, x)) == [2, 2]
+    with pytest.raises(ValueError):
+        lin.weight_storage()

@@ -165,6 +165,35 @@ def test_operator_without_kernel_strict_refuses_hardened_records_fallback(cuda_d
     assert sm100.DEVIATION_ID in ids and "dispatch.composite_backend_fallback" in ids
 
 
+def test_typed_dispatch_families_on_the_gpu_name_the_launched_kernel(cuda_device):
+    """``dispatch_tensor_*`` with CUDA operands goes through the sm_100a route table: routed operators report the
+    kernel that ran, strict mode refuses an operator without one, hardened mode records the library fallback."""
+    from frankentorch_b200.dispatch import families as F, sm100
+    from frankentorch_b200.dispatch.keys import DispatchKey
+    from frankentorch_b200.ops import kernels as K
+    from frankentorch_b200.runtime.ledger import ExecutionMode as M
+    x = torch.randn(64, 128).to(torch.bfloat16).cuda()
+    n0 = K.launch_count()
+    out = F.dispatch_tensor_unary(F.UnaryOp.Gelu, M.Strict, x, requires_grad=True)
+    assert _rel(out.values, torch.nn.functional.gelu(x.float())) < 2e-2
+    d = out.decision
+    assert d.kernel.startswith("ftk::") and d.backend_key is DispatchKey.SM100 and d.selected_key is DispatchKey.AutogradSM100
+    assert not d.fallback_used and out.storage.dtype.value == "BF16" and out.storage.data.is_cuda
+    mm = F.dispatch_tensor_binary(F.BinaryOp.MatMul, M.Strict, x, x.t().contiguous())
+    assert "gemm" in mm.decision.kernel and _rel(mm.values, x.float() @ x.float().t()) < 2e-2
+    sm = F.dispatch_tensor_normalize_dim(F.NormalizeOp.Softmax, M.Strict, x, 1)
+    assert sm.decision.kernel.startswith("ftk::") and sm.decision.dim == 1 and _rel(sm.values, torch.softmax(x.float(), 1)) < 2e-2
+    j = F.dispatch_tensor_join(F.JoinOp.Cat, M.Strict, [x, x], 0)
+    assert j.decision.kernel == "layout::cat" and tuple(j.values.shape) == (128, 128)
+    assert K.launch_count() - n0 >= 3
+    with pytest.raises(sm100.NoKernelForBackend):
+        F.dispatch_tensor_unary(F.UnaryOp.Sigmoid, M.Strict, x)
+    h = F.dispatch_tensor_unary(F.UnaryOp.Sigmoid, M.Hardened, x)
+    assert h.decision.kernel == "torch::sigmoid" and h.decision.fallback_used
+    assert _rel(h.values, torch.sigmoid(x.float())) < 1e-2
+    K.check_status()
+
+
 def test_gpt_from_nn_modules_on_a_cuda_session_follows_the_fused_model(cuda_device):
     """A 2-layer GPT composed of ``ft.nn`` modules on a CUDA session against ``models/gpt.py`` with the
     same weights.  The two routes cut the computation into kernels at different places (the model
