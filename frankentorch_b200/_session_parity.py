@@ -462,6 +462,50 @@ def tensor_gradients_iter(self, report):
         yield nid, report.gradients[nid].detach().to("cpu", torch.float64).reshape(-1).tolist()
 
 
+def tensor_is_leaf(self, nid) -> bool:
+    return self.tensor_tape.tensor_is_leaf(nid)
+
+
+def tensor_grad_fn(self, nid):
+    return self.tensor_tape.tensor_grad_fn(nid)
+
+
+def tensor_has_hooks(self, nid) -> bool:
+    return self.tensor_tape.tensor_has_hooks(nid)
+
+
+def tensor_retains_grad(self, nid) -> bool:
+    return self.tensor_tape.tensor_retains_grad(nid)
+
+
+def tensor_node_count(self) -> int:
+    return self.tensor_tape.node_count()
+
+
+def tensor_detach_(self, nid) -> int:
+    """Detach a node in place: it becomes a leaf without history that does not require grad."""
+    self.tensor_tape.detach_in_place(nid)
+    return nid
+
+
+def set_detect_anomaly(self, enabled: bool) -> None:
+    """Tape-level anomaly mode: every backward pass of this session checks its gradients for NaN / Inf."""
+    self.tensor_tape.set_detect_anomaly(enabled)
+
+
+def is_detect_anomaly(self) -> bool:
+    return self.tensor_tape.is_detect_anomaly()
+
+
+def set_grad_enabled(self, enabled: bool) -> bool:
+    """Switch gradient recording; returns the previous setting (nesting is the caller's business, unlike
+    ``no_grad_enter`` / ``no_grad_exit`` which count)."""
+    prev = self.is_grad_enabled()
+    self._no_grad_depth = 0 if enabled else max(self._no_grad_depth, 1)
+    self.tensor_tape.grad_enabled = bool(enabled)
+    return prev
+
+
 def tensor_register_hook(self, nid, fn):
     return self.register_tensor_hook(nid, fn)
 
@@ -729,7 +773,7 @@ def install(cls) -> None:
     from ._session_extras import _alias
     g = globals()
     for name, fn in list(g.items()):
-        if name.startswith("tensor_") and callable(fn):
+        if (name.startswith("tensor_") or name in ("set_detect_anomaly", "is_detect_anomaly", "set_grad_enabled")) and callable(fn):
             setattr(cls, name, fn)
     for name, fn in _INPLACE_BINARY.items():
         setattr(cls, name, _inplace_binary(name, fn))

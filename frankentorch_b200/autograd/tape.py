@@ -296,6 +296,9 @@ class TensorTape:
         # backward pass ends, so every gradient is on the stream when backward() returns
         self.wgrad_queue = None
         self.last_plan_cache: Dict[Tuple[int, int], Tuple] = {}
+        # tape-level anomaly mode (ft-autograd/src/lib.rs:4424-4434): every backward pass checks the gradients it
+        # produces for NaN / Inf, whatever the pass's own options say
+        self.detect_anomaly = False
 
     def __del__(self):
         try:
@@ -358,7 +361,52 @@ class TensorTape:
         self._lib.ftc_tape_set_requires_grad(self._h, nid, int(flag))
 
     def retain_grad(self, nid: int) -> None:
-        self._node(nid).retain_grad = True
+        n = self._node(nid)
+        if not n.requires_grad:
+            raise AutogradError("retain_grad() can only be called on tensors with requires_grad=True")
+        if not n.is_leaf:          # a leaf keeps its gradient anyway
+            n.retain_grad = True
+
+    # ------------------------------------------------------------------ introspection (ft-autograd/src/lib.rs:4424-4520)
+    def is_detect_anomaly(self) -> bool:
+        return self.detect_anomaly
+
+    def set_detect_anomaly(self, enabled: bool) -> None:
+        self.detect_anomaly = bool(enabled)
+
+    def set_grad_enabled(self, enabled: bool) -> bool:
+        """Switch recording on or off; returns the previous setting."""
+        prev, self.grad_enabled = self.grad_enabled, bool(enabled)
+        return prev
+
+    def node_count(self) -> int:
+        return len(self.nodes)
+
+    def tensor_is_leaf(self, nid: int) -> bool:
+        return self._node(nid).is_leaf
+
+    def tensor_retains_grad(self, nid: int) -> bool:
+        n = self._node(nid)
+        return bool(n.retain_grad) and not n.is_leaf
+
+    def tensor_has_hooks(self, nid: int) -> bool:
+        return bool(self._node(nid).hooks)
+
+    def tensor_grad_fn(self, nid: int) -> Optional[str]:
+        """Name of the backward function of a computed node that requires grad (``"MulBackward"``); ``None`` for
+        leaves and for nodes outside the graph."""
+        n = self._node(nid)
+        if n.is_leaf or not n.requires_grad:
+            return None
+        return "".join(p.capitalize() for p in str(n.op).split("_")) + "Backward"
+
+    def detach_in_place(self, nid: int) -> None:
+        """Cut a node out of the graph: it becomes a leaf that does not require grad (its value is kept, its rule
+        and inputs are dropped), so nothing upstream of it receives a gradient through it."""
+        n = self._node(nid)
+        n.is_leaf, n.requires_grad, n.vjp, n.inputs, n.retain_grad = True, False, None, [], False
+        self._lib.ftc_tape_set_requires_grad(self._h, nid, 0)
+        self.last_plan_cache.clear()
 
     def bump_version(self, nid: int) -> int:
         n = self._node(nid)
@@ -549,7 +597,7 @@ class TensorTape:
                     grads[inp] = g                      # first contribution: stored verbatim
                 else:
                     grads[inp] = self.accumulate_fn(prev, g)   # later contributions: added in rule order
-            if opts.detect_anomaly:
+            if opts.detect_anomaly or self.detect_anomaly:
                 for inp in node.inputs:
                     t = grads.get(inp)
                     if t is not None and not bool(torch.isfinite(t).all()):

@@ -245,15 +245,23 @@ class Adagrad(Optimizer):
 
 
 class RAdam(Optimizer):
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, decoupled_weight_decay=False):
         super().__init__(params, lr)
-        self._betas, self._eps, self._wd = tuple(betas), eps, weight_decay
+        self._betas, self._eps, self._wd, self._decoupled = tuple(betas), eps, weight_decay, bool(decoupled_weight_decay)
+
+    def decoupled_weight_decay(self, flag: bool = True):
+        """Decay the parameter directly (``w *= 1 - lr * wd``) instead of adding ``wd * w`` to the gradient."""
+        self._decoupled = bool(flag)
+        return self
 
     def _update(self, p, w, g, t):
         b1, b2 = self._betas
         wf = w.to(g.dtype)
         if self._wd:
-            g = g + self._wd * wf
+            if self._decoupled:
+                wf = wf * (1 - self.lr * self._wd)
+            else:
+                g = g + self._wd * wf
         m, v = self._st(p, "m", g), self._st(p, "v", g)
         m.mul_(b1).add_(g, alpha=1 - b1)
         v.mul_(b2).addcmul_(g, g, value=1 - b2)
@@ -301,16 +309,25 @@ class Adadelta(Optimizer):
 
 
 class NAdam(Optimizer):
-    def __init__(self, params, lr=2e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, momentum_decay=4e-3):
+    def __init__(self, params, lr=2e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, momentum_decay=4e-3,
+                 decoupled_weight_decay=False):
         super().__init__(params, lr)
         self._betas, self._eps, self._wd, self._md = tuple(betas), eps, weight_decay, momentum_decay
+        self._decoupled = bool(decoupled_weight_decay)
         self._mu_prod: Dict[int, float] = {}
+
+    def decoupled_weight_decay(self, flag: bool = True):
+        self._decoupled = bool(flag)
+        return self
 
     def _update(self, p, w, g, t):
         b1, b2 = self._betas
         wf = w.to(g.dtype)
         if self._wd:
-            g = g + self._wd * wf
+            if self._decoupled:
+                wf = wf * (1 - self.lr * self._wd)
+            else:
+                g = g + self._wd * wf
         m, v = self._st(p, "m", g), self._st(p, "v", g)
         mu = b1 * (1 - 0.5 * 0.96 ** (t * self._md))
         mu_next = b1 * (1 - 0.5 * 0.96 ** ((t + 1) * self._md))
@@ -343,6 +360,11 @@ class ASGD(Optimizer):
         st["eta_f"] = self.lr / ((1 + self._lambd * self.lr * t) ** self._alpha)
         st["mu_f"] = 1.0 / max(1.0, t - self._t0)
         _apply(w, wf)
+
+    def averaged_parameters(self) -> List[Optional[torch.Tensor]]:
+        """The running averages ``ax`` of the parameters, in parameter order (``None`` before a parameter's first
+        step); use them in place of the raw iterates once training is over."""
+        return [self.state[p]["ax"].clone() if "ax" in self.state[p] else None for p in self.params]
 
     def state_dict(self):
         sd = super().state_dict()
@@ -468,9 +490,11 @@ class LBFGS(Optimizer):
     search (bracketing, then a zoom phase with safeguarded cubic interpolation; c1 = 1e-4, c2 = 0.9)."""
 
     def __init__(self, params, lr=1.0, max_iter=20, history_size=100, tolerance_grad=1e-7, tolerance_change=1e-9,
-                 line_search: Optional[str] = None):
+                 line_search: Optional[str] = None, max_eval: Optional[int] = None):
         super().__init__(params, lr)
         self.max_iter, self.history, self.tol_g, self.tol_c, self.line_search = max_iter, history_size, tolerance_grad, tolerance_change, line_search
+        self.max_eval = max_eval if max_eval is not None else max_iter * 5 // 4      # closure evaluations per step()
+        self.n_evals = 0
         self._s: List[torch.Tensor] = []
         self._y: List[torch.Tensor] = []
 
@@ -544,12 +568,27 @@ class LBFGS(Optimizer):
                 lo, f_lo, g_lo = t, f, gt
         return lo, self._phi(session, closure, x0, d, lo)[0]
 
+    def line_search_fn(self, ls):
+        self.line_search = ls
+        return self
+
+    def step_with_closure(self, session, closure: Callable[[], float]) -> float:
+        return self.step(session, closure)
+
     def step(self, session, closure: Callable[[], float]) -> float:
-        """``closure`` zeroes the gradients, runs forward + backward and returns the loss value."""
+        """``closure`` zeroes the gradients, runs forward + backward and returns the loss value.  Iterates until
+        ``max_iter`` directions were taken, ``max_eval`` closure evaluations were spent, or a tolerance is met."""
+        evals = [0]
+        inner = closure
+
+        def closure():                                   # noqa: F811  (counts evaluations of the user's closure)
+            evals[0] += 1
+            self.n_evals += 1
+            return inner()
         loss = float(closure())
         g = self._flat(session, True)
         for _ in range(self.max_iter):
-            if float(g.abs().max()) <= self.tol_g:
+            if float(g.abs().max()) <= self.tol_g or evals[0] >= self.max_eval:
                 break
             q, alphas = g.clone(), []
             for s, y in zip(reversed(self._s), reversed(self._y)):

@@ -156,26 +156,126 @@ class MultiplicativeLR(LRScheduler):
 
 
 class OneCycleLR(LRScheduler):
+    """One-cycle policy (ft-optim/src/lib.rs:3798-4030).  Two phases (warm-up to ``max_lr``, anneal to the final
+    rate) or, with ``three_phase``, three (up, back down to the initial rate, then down to the final rate).  The
+    phase boundaries are the real numbers ``pct_start * total - 1`` and ``2 * pct_start * total - 2`` over steps
+    ``0 .. total - 1``.  With ``cycle_momentum`` the optimizer's momentum moves against the rate between
+    ``max_momentum`` and ``base_momentum``.  ``step(optimizer, epoch=k)`` jumps to step ``k``."""
+
     def __init__(self, optimizer, max_lr: float, total_steps: int, pct_start: float = 0.3, div_factor: float = 25.0,
-                 final_div_factor: float = 1e4, anneal: str = "cos"):
+                 final_div_factor: float = 1e4, anneal: str = "cos", three_phase: bool = False,
+                 cycle_momentum: bool = False, base_momentum: float = 0.85, max_momentum: float = 0.95):
         super().__init__(optimizer)
+        if total_steps <= 0:
+            raise ValueError("total_steps must be positive")
+        if not 0.0 <= pct_start <= 1.0:
+            raise ValueError("pct_start must lie in [0, 1]")
+        if anneal not in ("cos", "linear"):
+            raise ValueError("anneal must be 'cos' or 'linear'")
         self.max_lr, self.total, self.pct = max_lr, total_steps, pct_start
-        self.initial, self.min_lr, self.anneal = max_lr / div_factor, max_lr / div_factor / final_div_factor, anneal
+        self.div_factor, self.final_div_factor = div_factor, final_div_factor
+        self.anneal = anneal
+        self._three_phase, self._cycle_momentum = bool(three_phase), bool(cycle_momentum)
+        self._base_momentum, self._max_momentum = float(base_momentum), float(max_momentum)
+        self.last_momentum: Optional[float] = None
         optimizer.set_lr(self.initial)
         self.last_lr = self.initial
+        if self._cycle_momentum:
+            self._apply_momentum(optimizer, self._max_momentum)
+
+    initial = property(lambda self: self.max_lr / self.div_factor)
+    min_lr = property(lambda self: self.max_lr / self.div_factor / self.final_div_factor)
+
+    # builder-style options
+    def three_phase(self, flag: bool = True):
+        self._three_phase = bool(flag)
+        return self
+
+    def cycle_momentum(self, flag: bool = True):
+        self._cycle_momentum = bool(flag)
+        return self
+
+    def base_momentum(self, v: float):
+        self._base_momentum = float(v)
+        return self
+
+    def max_momentum(self, v: float):
+        self._max_momentum = float(v)
+        return self
+
+    def anneal_strategy_cos(self):
+        self.anneal = "cos"
+        return self
+
+    def anneal_strategy_linear(self):
+        self.anneal = "linear"
+        return self
+
+    def get_last_momentum(self) -> Optional[float]:
+        return self.last_momentum
+
+    def _apply_momentum(self, optimizer, m: float) -> None:
+        if optimizer.get_momentum() is None:
+            raise ValueError("cycle_momentum needs an optimizer with a momentum (SGD momentum, Adam-family beta1)")
+        optimizer.set_momentum(m)
+        self.last_momentum = m
 
     def _interp(self, a, b, pct):
+        pct = min(max(pct, 0.0), 1.0)
         if self.anneal == "cos":
             return b + (a - b) * (1 + math.cos(math.pi * pct)) / 2
         return a + (b - a) * pct
 
+    def _phases(self):
+        """``(end_step, start_lr, end_lr, start_momentum, end_momentum)`` per phase."""
+        t, hi_m, lo_m = float(self.total), self._max_momentum, self._base_momentum
+        if self._three_phase:
+            return [(self.pct * t - 1, self.initial, self.max_lr, hi_m, lo_m),
+                    (2 * self.pct * t - 2, self.max_lr, self.initial, lo_m, hi_m),
+                    (t - 1, self.initial, self.min_lr, hi_m, hi_m)]
+        return [(self.pct * t - 1, self.initial, self.max_lr, hi_m, lo_m), (t - 1, self.max_lr, self.min_lr, lo_m, hi_m)]
+
+    def _values_at(self, e: int):
+        phases, start = self._phases(), 0.0
+        for k, (end, lr_a, lr_b, m_a, m_b) in enumerate(phases):
+            if e <= end or k == len(phases) - 1:
+                pct = 0.0 if end == start else (e - start) / (end - start)      # a zero-width phase pins to its start
+                return self._interp(lr_a, lr_b, pct), (self._interp(m_a, m_b, pct) if self._cycle_momentum else None)
+            start = end
+        return self.initial, None
+
     def _lr_at(self, e):
         if e > self.total:
             raise ValueError("OneCycleLR stepped past total_steps")
-        up = float(self.pct * self.total) - 1
-        if e <= up:
-            return self._interp(self.initial, self.max_lr, e / up)
-        return self._interp(self.max_lr, self.min_lr, (e - up) / (self.total - 1 - up))
+        return self._values_at(e)[0]
+
+    def step(self, optimizer, metric=None, epoch: Optional[int] = None) -> float:
+        self.last_epoch = self.last_epoch + 1 if epoch is None else int(epoch)
+        if self.last_epoch > self.total:
+            raise ValueError("OneCycleLR stepped past total_steps")
+        self.last_lr, m = self._values_at(max(self.last_epoch, 0))
+        optimizer.set_lr(self.last_lr)
+        if m is not None:
+            self._apply_momentum(optimizer, m)
+        return self.last_lr
+
+    def state(self):
+        st = super().state()
+        st.extra.update(max_lr=self.max_lr, total=self.total, pct=self.pct, div_factor=self.div_factor,
+                        final_div_factor=self.final_div_factor, anneal=self.anneal, three_phase=self._three_phase,
+                        cycle_momentum=self._cycle_momentum, base_momentum=self._base_momentum,
+                        max_momentum=self._max_momentum, last_momentum=self.last_momentum)
+        return st
+
+    def load_state(self, st):
+        super().load_state(st)
+        x = st.extra
+        self.max_lr, self.total, self.pct = x.get("max_lr", self.max_lr), int(x.get("total", self.total)), x.get("pct", self.pct)
+        self.div_factor, self.final_div_factor = x.get("div_factor", self.div_factor), x.get("final_div_factor", self.final_div_factor)
+        self.anneal = x.get("anneal", self.anneal)
+        self._three_phase, self._cycle_momentum = bool(x.get("three_phase", self._three_phase)), bool(x.get("cycle_momentum", self._cycle_momentum))
+        self._base_momentum, self._max_momentum = x.get("base_momentum", self._base_momentum), x.get("max_momentum", self._max_momentum)
+        self.last_momentum = x.get("last_momentum", self.last_momentum)
 
 
 class CyclicLRMode:
@@ -207,36 +307,95 @@ CyclicLRMode.Triangular2 = CyclicLRMode("triangular2")
 
 class CyclicLR(LRScheduler):
     def __init__(self, optimizer, base_lr: float, max_lr: float, step_size_up: int = 2000,
-                 step_size_down: Optional[int] = None, mode="triangular", gamma: float = 1.0):
+                 step_size_down: Optional[int] = None, mode="triangular", gamma: float = 1.0,
+                 cycle_momentum: bool = False, base_momentum: float = 0.8, max_momentum: float = 0.9):
         super().__init__(optimizer)
         self.lo, self.hi, self.up, self.down = base_lr, max_lr, step_size_up, step_size_down or step_size_up
         self.policy = mode if isinstance(mode, CyclicLRMode) else CyclicLRMode(mode, gamma)
         self.mode, self.gamma = self.policy.name, self.policy.gamma
+        self._cycle_momentum, self._base_momentum, self._max_momentum = bool(cycle_momentum), float(base_momentum), float(max_momentum)
+        self.last_momentum: Optional[float] = None
         optimizer.set_lr(base_lr)
         self.last_lr = base_lr
+        if self._cycle_momentum:
+            if optimizer.get_momentum() is None:
+                raise ValueError("cycle_momentum needs an optimizer with a momentum")
+            optimizer.set_momentum(self._max_momentum)
+            self.last_momentum = self._max_momentum
 
-    def _lr_at(self, e):
+    def cycle_momentum(self, flag: bool = True):
+        self._cycle_momentum = bool(flag)
+        return self
+
+    def base_momentum(self, v: float):
+        self._base_momentum = float(v)
+        return self
+
+    def max_momentum(self, v: float):
+        self._max_momentum = float(v)
+        return self
+
+    def get_last_momentum(self) -> Optional[float]:
+        return self.last_momentum
+
+    def _position(self, e):
         total = self.up + self.down
         cycle = math.floor(1 + e / total)
         x = 1 + e / total - cycle
         pos = x / (self.up / total) if x <= self.up / total else (x - 1) / (self.up / total - 1)
-        return self.lo + (self.hi - self.lo) * pos * self.policy.scale(cycle, e)
+        return pos * self.policy.scale(cycle, e)
+
+    def _lr_at(self, e):
+        return self.lo + (self.hi - self.lo) * self._position(e)
+
+    def step(self, optimizer, metric=None) -> float:
+        lr = super().step(optimizer, metric)
+        if self._cycle_momentum:      # the momentum runs against the rate: highest where the rate is lowest
+            self.last_momentum = self._max_momentum - (self._max_momentum - self._base_momentum) * self._position(self.last_epoch)
+            optimizer.set_momentum(self.last_momentum)
+        return lr
 
 
 class ReduceLROnPlateau(LRScheduler):
     def __init__(self, optimizer, mode: str = "min", factor: float = 0.1, patience: int = 10, threshold: float = 1e-4,
-                 cooldown: int = 0, min_lr: float = 0.0):
+                 cooldown: int = 0, min_lr: float = 0.0, threshold_mode: str = "rel"):
         super().__init__(optimizer)
+        if mode not in ("min", "max") or threshold_mode not in ("rel", "abs"):
+            raise ValueError("mode must be 'min' or 'max' and threshold_mode 'rel' or 'abs'")
+        if factor >= 1.0:
+            raise ValueError("factor must be below 1")
         self.mode, self.factor, self.patience, self.threshold, self.cooldown, self.min_lr = mode, factor, patience, threshold, cooldown, min_lr
+        self.threshold_mode = threshold_mode
         self.best = math.inf if mode == "min" else -math.inf
         self.bad, self.cool = 0, 0
+
+    # builder-style options (ft-optim/src/lib.rs ReduceLROnPlateau)
+    def mode_min(self):
+        self.mode, self.best = "min", math.inf
+        return self
+
+    def mode_max(self):
+        self.mode, self.best = "max", -math.inf
+        return self
+
+    def threshold_mode_rel(self):
+        self.threshold_mode = "rel"
+        return self
+
+    def threshold_mode_abs(self):
+        self.threshold_mode = "abs"
+        return self
+
+    def _is_better(self, metric: float) -> bool:
+        if self.threshold_mode == "rel":
+            return metric < self.best * (1 - self.threshold) if self.mode == "min" else metric > self.best * (1 + self.threshold)
+        return metric < self.best - self.threshold if self.mode == "min" else metric > self.best + self.threshold
 
     def step(self, optimizer, metric: Optional[float] = None) -> float:
         if metric is None:
             raise ValueError("ReduceLROnPlateau.step needs the monitored metric")
         self.last_epoch += 1
-        better = metric < self.best * (1 - self.threshold) if self.mode == "min" else metric > self.best * (1 + self.threshold)
-        if better:
+        if self._is_better(metric):
             self.best, self.bad = metric, 0
         else:
             self.bad += 1
@@ -304,6 +463,21 @@ class GradScaler:
         self.scale, self.growth, self.backoff, self.interval, self.enabled = init_scale, growth_factor, backoff_factor, growth_interval, enabled
         self._good_steps = 0
         self._found_inf = False
+        self._last_skipped = False
+
+    def enable(self) -> None:
+        self.enabled = True
+
+    def disable(self) -> None:
+        """Scaling off: ``scale_loss`` returns the loss itself and ``step`` always steps."""
+        self.enabled = False
+
+    def is_enabled(self) -> bool:
+        return self.enabled
+
+    def last_step_was_skipped(self) -> bool:
+        """Whether the latest ``step`` found a non-finite gradient and left the parameters untouched."""
+        return self._last_skipped
 
     def get_scale(self) -> float:
         return self.scale
@@ -331,10 +505,13 @@ class GradScaler:
         """Unscale and step; skips the step (returns False) when an inf/nan gradient was found."""
         if not self.enabled:
             optimizer.step(session, report)
+            self._last_skipped = False
             return True
         if self.unscale_(session, optimizer):
             optimizer.step(session, report)
+            self._last_skipped = False
             return True
+        self._last_skipped = True
         return False
 
     def update(self) -> None:

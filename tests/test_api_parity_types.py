@@ -205,3 +205,192 @@ def test_packed_quantized_linear_per_tensor_and_per_channel():
     assert s.tensor_shape(lin(s, x)) == [2, 2]
     with pytest.raises(ValueError):
         lin.weight_storage()
+
+
+# ------------------------------------------------------------------------------------ optimizer / scheduler options
+def _sgd(momentum=0.95):
+    s = FrankenTorchSession(ledger_dispatch=False)
+    x = s.tensor_variable([1.0], [1], True)
+    return s, x, SGD([x], 1.0, momentum=momentum)
+
+
+def _torch_sgd(momentum=0.95):
+    p = torch.nn.Parameter(torch.zeros(1))
+    return torch.optim.SGD([p], lr=1.0, momentum=momentum)
+
+
+@pytest.mark.parametrize("three_phase,anneal", [(False, "cos"), (True, "linear"), (True, "cos")])
+def test_one_cycle_lr_phases_and_momentum_match_pytorch(three_phase, anneal):
+    from frankentorch_b200.optim import OneCycleLR
+    o = _torch_sgd()
+    ts = torch.optim.lr_scheduler.OneCycleLR(o, 2.0, total_steps=20, pct_start=0.25, three_phase=three_phase, anneal_strategy=anneal,
+                                             div_factor=10.0, final_div_factor=100.0, base_momentum=0.8, max_momentum=0.95)
+    _, _, opt = _sgd()
+    sc = OneCycleLR(opt, 2.0, 20, pct_start=0.25, div_factor=10.0, final_div_factor=100.0, anneal=anneal, three_phase=three_phase,
+                    cycle_momentum=True, base_momentum=0.8, max_momentum=0.95)
+    for i in range(20):
+        assert abs(opt.get_lr() - o.param_groups[0]["lr"]) < 1e-12 and abs(opt.get_momentum() - o.param_groups[0]["momentum"]) < 1e-12, i
+        if i < 19:
+            o.step()
+            ts.step()
+            sc.step(opt)
+    assert sc.get_last_momentum() == opt.get_momentum()
+    with pytest.raises(ValueError):
+        sc.step(opt, epoch=21)
+    # builder spelling, explicit epochs, state round trip
+    _, _, opt2 = _sgd()
+    b = OneCycleLR(opt2, 2.0, 30).three_phase(True).anneal_strategy_linear().cycle_momentum(True).base_momentum(0.8).max_momentum(0.95)
+    b.step(opt2, epoch=11)
+    st = b.state()
+    c = OneCycleLR(opt2, 1.0, 5)
+    c.load_state(st)
+    assert c.state().extra == st.extra and c.last_epoch == 11
+    s3 = FrankenTorchSession(ledger_dispatch=False)
+    from frankentorch_b200.optim import Adagrad
+    with pytest.raises(ValueError):
+        OneCycleLR(Adagrad([s3.tensor_variable([1.0], [1], True)], lr=0.1), 1.0, 10, cycle_momentum=True)
+
+
+def test_cyclic_lr_momentum_cycles_against_the_rate_as_in_pytorch():
+    o = _torch_sgd(0.9)
+    ts = torch.optim.lr_scheduler.CyclicLR(o, 0.1, 1.0, step_size_up=3, step_size_down=5, mode="triangular2", cycle_momentum=True,
+                                           base_momentum=0.8, max_momentum=0.9)
+    _, _, opt = _sgd(0.9)
+    sc = CyclicLR(opt, 0.1, 1.0, step_size_up=3, step_size_down=5, mode=CyclicLRMode.Triangular2, cycle_momentum=True,
+                  base_momentum=0.8, max_momentum=0.9)
+    for i in range(20):
+        assert abs(opt.get_lr() - o.param_groups[0]["lr"]) < 1e-12 and abs(opt.get_momentum() - o.param_groups[0]["momentum"]) < 1e-12, i
+        o.step()
+        ts.step()
+        sc.step(opt)
+
+
+def test_reduce_lr_on_plateau_threshold_modes_match_pytorch():
+    from frankentorch_b200.optim import ReduceLROnPlateau
+    metrics = [1.0, 0.99995, 0.9999, 0.9998, 0.9, 0.9, 0.9, 0.9, 0.85, 0.85, 0.85, 0.85, 0.85]
+    for mode, tmode in (("min", "rel"), ("min", "abs"), ("max", "rel"), ("max", "abs")):
+        o = _torch_sgd()
+        ts = torch.optim.lr_scheduler.ReduceLROnPlateau(o, mode=mode, factor=0.5, patience=1, threshold=1e-3, threshold_mode=tmode)
+        _, _, opt = _sgd()
+        sc = ReduceLROnPlateau(opt, mode=mode, factor=0.5, patience=1, threshold=1e-3, threshold_mode=tmode)
+        for m in metrics:
+            v = m if mode == "min" else -m + 2
+            ts.step(v)
+            sc.step(opt, v)
+            assert abs(opt.get_lr() - o.param_groups[0]["lr"]) < 1e-15, (mode, tmode, m)
+    _, _, opt = _sgd()
+    b = ReduceLROnPlateau(opt).mode_max().threshold_mode_abs()
+    assert (b.mode, b.threshold_mode, b.best) == ("max", "abs", -float("inf"))
+    assert ReduceLROnPlateau(opt).mode_min().threshold_mode_rel().threshold_mode == "rel"
+    with pytest.raises(ValueError):
+        ReduceLROnPlateau(opt, threshold_mode="pct")
+
+
+def test_grad_scaler_switches_and_skip_flag():
+    from frankentorch_b200.optim import GradScaler
+    s, x, opt = _sgd(0.0)
+    sc = GradScaler(init_scale=4.0)
+    loss = s.tensor_sum(s.tensor_mul(x, x))
+    s.tensor_backward(sc.scale_loss(s, loss))
+    assert sc.step(s, opt) and not sc.last_step_was_skipped() and abs(s.tensor(x).item() - (1.0 - 2.0)) < 1e-12
+    s.tensor_set_accumulated_gradient(x, [float("inf")])
+    before = s.tensor(x).item()
+    assert not sc.step(s, opt) and sc.last_step_was_skipped() and s.tensor(x).item() == before
+    sc.update()
+    assert sc.get_scale() == 2.0
+    sc.disable()
+    assert not sc.is_enabled() and sc.scale_loss(s, loss) == loss
+    s.tensor_set_accumulated_gradient(x, [0.5])
+    assert sc.step(s, opt) and not sc.last_step_was_skipped()
+    sc.enable()
+    assert sc.is_enabled()
+
+
+@pytest.mark.parametrize("name", ["RAdam", "NAdam"])
+def test_decoupled_weight_decay_of_radam_and_nadam_matches_pytorch(name):
+    import frankentorch_b200.optim as O
+    w0 = torch.tensor([0.5, -1.5, 2.0], dtype=torch.float64)
+    for decoupled in (False, True):
+        p = torch.nn.Parameter(w0.clone())
+        to = getattr(torch.optim, name)([p], lr=0.05, weight_decay=0.1, decoupled_weight_decay=decoupled)
+        s = FrankenTorchSession(ledger_dispatch=False)
+        w = s.tensor_variable(w0.tolist(), [3], True)
+        mine = getattr(O, name)([w], lr=0.05, weight_decay=0.1).decoupled_weight_decay(decoupled)
+        for _ in range(8):
+            to.zero_grad()
+            (p ** 3).sum().backward()
+            to.step()
+            mine.zero_grad(s)
+            s.tensor_backward(s.tensor_sum(s.tensor_pow(w, 3.0)))
+            mine.step(s)
+        assert torch.allclose(s.tensor(w), p.detach(), atol=1e-10), (name, decoupled)
+
+
+def test_asgd_averaged_parameters_and_lbfgs_evaluation_budget():
+    from frankentorch_b200.optim import ASGD
+    s = FrankenTorchSession(ledger_dispatch=False)
+    w = s.tensor_variable([1.0, -2.0], [2], True)
+    opt = ASGD([w], lr=0.1, t0=2)
+    assert opt.averaged_parameters() == [None]
+    p = torch.nn.Parameter(torch.tensor([1.0, -2.0], dtype=torch.float64))
+    to = torch.optim.ASGD([p], lr=0.1, t0=2)
+    for _ in range(6):
+        opt.zero_grad(s)
+        s.tensor_backward(s.tensor_sum(s.tensor_square(w)))
+        opt.step(s)
+        to.zero_grad()
+        (p ** 2).sum().backward()
+        to.step()
+    (ax,) = opt.averaged_parameters()
+    assert torch.allclose(ax, to.state[p]["ax"], atol=1e-12) and not torch.equal(ax, s.tensor(w))
+    s2 = FrankenTorchSession(ledger_dispatch=False)
+    v = s2.tensor_variable([-1.2, 1.0], [2], True)
+    lb = LBFGS([v], max_iter=50, max_eval=7).line_search_fn("strong_wolfe")
+
+    def closure():
+        s2.tensor_zero_grads([v])
+        loss = _rosenbrock(s2, v)
+        s2.tensor_backward(loss)
+        return s2.tensor_item(loss)
+    lb.step_with_closure(s2, closure)
+    assert 7 <= lb.n_evals <= 7 + 30          # the budget is checked between directions; one line search may overrun it
+    assert LBFGS([v], max_iter=20).max_eval == 25
+
+
+def test_tape_introspection_and_session_spellings():
+    s = FrankenTorchSession(ledger_dispatch=False)
+    x = s.tensor_variable([1.0, 2.0], [2], True)
+    y = s.tensor_mul(x, x)
+    w = s.tensor_variable([3.0, 4.0], [2], True)
+    z = s.tensor_log_softmax(s.tensor_mul(y, w), dim=0)
+    assert s.tensor_is_leaf(x) and not s.tensor_is_leaf(y) and s.tensor_grad_fn(x) is None
+    assert s.tensor_grad_fn(y) == "MulBackward" and s.tensor_grad_fn(z) == "LogSoftmaxBackward"
+    assert s.tensor_node_count() == s.autograd_graph_len() == 5
+    assert not s.tensor_has_hooks(y)
+    h = s.register_tensor_hook(y, lambda g: None)
+    assert s.tensor_has_hooks(y) and s.remove_tensor_hook(h) and not s.tensor_has_hooks(y)
+    assert not s.tensor_retains_grad(y)
+    s.tensor_retain_grad(y)
+    assert s.tensor_retains_grad(y) and not s.tensor_retains_grad(x)        # a leaf keeps its gradient without asking
+    c = s.tensor_variable([1.0], [1], False)
+    with pytest.raises(Exception):
+        s.tensor_retain_grad(c)
+    # detaching in place cuts the path to x; w still receives its gradient
+    s.tensor_detach_(y)
+    assert s.tensor_is_leaf(y) and not s.tensor_requires_grad(y)
+    rep = s.tensor_backward(s.tensor_sum(z))
+    assert rep.gradient(w) is not None and (rep.gradient(x) is None or float(rep.gradient(x).abs().sum()) == 0.0)
+    # tape-level anomaly mode
+    assert not s.is_detect_anomaly()
+    s.set_detect_anomaly(True)
+    a = s.tensor_variable([0.0], [1], True)
+    from frankentorch_b200.autograd.tape import AnomalyDetected
+    with pytest.raises(AnomalyDetected):
+        s.tensor_backward(s.tensor_sum(s.tensor_log(a)))
+    s.set_detect_anomaly(False)
+    s.tensor_backward(s.tensor_sum(s.tensor_log(s.tensor_variable([0.0], [1], True))))
+    # grad mode as a setter that returns the previous value
+    assert s.set_grad_enabled(False) is True and not s.is_grad_enabled()
+    n = s.tensor_mul(x, x)
+    assert not s.tensor_requires_grad(n)
+    assert s.set_grad_enabled(True) is False and s.is_grad_enabled()
