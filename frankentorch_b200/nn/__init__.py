@@ -16,4 +16,4 @@ from .extra import (AdaptiveLogSoftmaxWithLoss, FractionalMaxPool2d, FractionalM
 from .utils import (MinMaxObserver, PackedSequence, QParams, QuantizedLinear, QuantizedLinearQParams,
                     QuantizedLinearWeightStorage, QuantizedStorageDType, SpectralNorm, WeightNorm, dequantize,
                     pack_padded_sequence, pack_sequence, pad_packed_sequence, pad_sequence, quantize_per_tensor,
-                    spectral_norm, weight_norm)
+                    spectral_norm, weight_norm, weight_norm_decompose, weight_norm_reconstruct)

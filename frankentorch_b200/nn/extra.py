@@ -18,13 +18,23 @@ def _lazy_conv(nd: int):
             super().__init__()
             self.out_channels, self.kernel_size, self.kw, self._inner = out_channels, kernel_size, kw, None
 
-        def forward(self, session, x):
+        def is_materialized(self) -> bool:
+            return self._inner is not None
+
+        def materialize(self, session, in_channels: int) -> None:
             if self._inner is None:
-                in_ch = session.tensor_shape(x)[1]
-                object.__setattr__(self, "_inner", _ConvNd(session, nd, in_ch, self.out_channels, self.kernel_size, **self.kw))
+                object.__setattr__(self, "_inner", _ConvNd(session, nd, in_channels, self.out_channels, self.kernel_size, **self.kw))
                 self.register_parameter("weight", self._inner._parameters["weight"])
                 self.register_parameter("bias", self._inner._parameters["bias"])
+
+        def forward(self, session, x):
+            shape = session.tensor_shape(x)
+            if len(shape) != nd + 2:
+                raise ValueError(f"LazyConv{nd}d expects a {nd + 2}-D input [N, C, ...]")
+            self.materialize(session, shape[1])
             return self._inner.forward(session, x)
+
+        forward_lazy = forward
     _Lazy.__name__ = f"LazyConv{nd}d"
     return _Lazy
 

@@ -61,6 +61,16 @@ class LazyLinear(Module):
         super().__init__()
         self.out_features, self._bias, self._inner = out_features, bias, None
 
+    def is_materialized(self) -> bool:
+        return self._inner is not None
+
+    def materialize(self, session, in_features: int) -> None:
+        """Create the parameters for ``in_features`` now instead of at the first forward (no-op when they exist)."""
+        if self._inner is None:
+            object.__setattr__(self, "_inner", Linear(session, in_features, self.out_features, self._bias))
+            self.register_parameter("weight", self._inner._parameters["weight"])
+            self.register_parameter("bias", self._inner._parameters["bias"])
+
     def forward(self, session, x):
         if self._inner is None:
             # bypass child registration: the parameters are registered on this module itself

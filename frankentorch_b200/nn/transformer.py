@@ -70,6 +70,37 @@ class MultiheadAttention(Module):
     def forward(self, session, x, attn_mask: Optional[int] = None, is_causal: bool = False):
         return self.forward_qkv(session, x, x, x, attn_mask, is_causal)
 
+    def forward_qkv_with_weights(self, session, q, k, v, attn_mask: Optional[int] = None, is_causal: bool = False,
+                                 average_attn_weights: bool = True):
+        """Attention output and the attention probabilities (ft-nn/src/lib.rs:5212): ``[N, Sq, Sk]`` averaged over
+        the heads, or ``[N, heads, Sq, Sk]`` per head.  The probabilities are formed explicitly (scores, mask,
+        softmax) out of session operators, so both results are differentiable; the output equals ``forward_qkv``."""
+        n, sq, _ = session.tensor_shape(q)
+        sk = session.tensor_shape(k)[1]
+        qh = self._split(session, self.q_proj(session, q))
+        kh = self._split(session, self.k_proj(session, k))
+        vh = self._split(session, self.v_proj(session, v))
+        scores = session.tensor_mul_scalar(session.tensor_bmm(qh, session.tensor_transpose(kh, dim0=1, dim1=2)),
+                                           c=1.0 / math.sqrt(self.head_dim))
+        add = None
+        if is_causal:
+            add = torch.triu(torch.full((sq, sk), float("-inf"), dtype=session.tensor(q).dtype, device=session.device), 1)
+        if attn_mask is not None:
+            m = session.tensor(attn_mask)
+            m = torch.zeros_like(m, dtype=session.tensor(q).dtype).masked_fill(m, float("-inf")) if m.dtype == torch.bool else m
+            add = m if add is None else add + m
+        if add is not None:
+            scores = session.tensor_add(scores, session.tensor_tape.leaf(add.expand(n * self.num_heads, sq, sk).contiguous(), False))
+        probs = session.tensor_softmax(scores, dim=-1)
+        o = session.tensor_bmm(session.functional_dropout(probs, self.dropout.p, self.training) if self.dropout.p else probs, vh)
+        o = session.tensor_reshape(o, shape=(n, self.num_heads, sq, self.head_dim))
+        o = session.tensor_permute(o, dims=(0, 2, 1, 3))
+        o = session.tensor_reshape(o, shape=(n, sq, self.embed_dim))
+        w = session.tensor_reshape(probs, shape=(n, self.num_heads, sq, sk))
+        if average_attn_weights:
+            w = session.tensor_mean_dim(w, dim=1)
+        return self.out_proj(session, o), w
+
     def forward_qkv_causal(self, session, q, k, v):
         return self.forward_qkv(session, q, k, v, None, True)
 

@@ -84,6 +84,42 @@ def weight_norm(session, linear: Linear) -> WeightNorm:
     return WeightNorm(session, linear)
 
 
+def _wn_check(session, t, dim):
+    shape = session.tensor_shape(t)
+    if not 0 <= dim < len(shape):
+        raise ValueError("weight_norm: dim out of range")
+    if shape[dim] == 0:
+        raise ValueError("weight_norm: dimension size must be > 0")
+    return shape
+
+
+def weight_norm_decompose(session, weight: int, dim: int = 0) -> Tuple[int, int]:
+    """``w = g * v / ||v||`` with the norm over every dimension but ``dim`` (ft-nn/src/lib.rs:19457): returns two
+    new trainable leaves, the magnitudes ``g`` ``[shape[dim]]`` (floored at 1e-12) and the direction ``v = w``."""
+    shape = _wn_check(session, weight, dim)
+    w = session.tensor(weight).detach()
+    others = [d for d in range(len(shape)) if d != dim]
+    g = torch.sqrt((w.to(torch.float64) ** 2).sum(others)) if others else w.to(torch.float64).abs()
+    g = g.clamp_min(1e-12).to(w.dtype)
+    return session.tensor_tape.leaf(g.clone(), True), session.tensor_tape.leaf(w.clone(), True)
+
+
+def weight_norm_reconstruct(session, g: int, v: int, dim: int = 0) -> int:
+    """``g * v / ||v||`` built from session operators, so gradients reach both ``g`` and ``v``
+    (ft-nn/src/lib.rs:19508)."""
+    shape = _wn_check(session, v, dim)
+    if session.tensor_numel(g) != shape[dim]:
+        raise ValueError("weight_norm: magnitude length mismatch")
+    bshape = [1] * len(shape)
+    bshape[dim] = shape[dim]
+    sq = session.tensor_square(v)
+    for d in sorted((d for d in range(len(shape)) if d != dim), reverse=True):
+        sq = session.tensor_sum_dim(sq, dim=d, keepdim=True)
+    nrm = session.tensor_clamp_min(session.tensor_sqrt(sq), 1e-12)
+    scale = session.tensor_div(session.tensor_reshape(g, shape=tuple(bshape)), session.tensor_reshape(nrm, shape=tuple(bshape)))
+    return session.tensor_mul(v, scale)
+
+
 class SpectralNorm(Module):
     """Divides the weight by its largest singular value estimated by power iteration."""
 

@@ -394,3 +394,60 @@ def test_tape_introspection_and_session_spellings():
     n = s.tensor_mul(x, x)
     assert not s.tensor_requires_grad(n)
     assert s.set_grad_enabled(True) is False and s.is_grad_enabled()
+
+
+def test_attention_weights_output_matches_pytorch_and_is_differentiable():
+    s = FrankenTorchSession(ledger_dispatch=False)
+    mha = nn.MultiheadAttention(s, 8, 2)
+    x = s.randn([2, 5, 8], requires_grad=True)
+    out, w = mha.forward_qkv_with_weights(s, x, x, x, None, True, True)
+    assert torch.allclose(s.tensor(out), s.tensor(mha.forward_qkv(s, x, x, x, None, True)), atol=1e-12)
+    assert s.tensor_shape(w) == [2, 5, 5] and torch.allclose(s.tensor(w).sum(-1), torch.ones(2, 5, dtype=torch.float64))
+    assert float(s.tensor(w)[0, 0, 1:].abs().sum()) == 0.0                       # causal: the first query sees one key
+    tm = torch.nn.MultiheadAttention(8, 2, batch_first=True, dtype=torch.float64)
+    sd = mha.state_dict(s)
+    with torch.no_grad():
+        tm.in_proj_weight.copy_(torch.cat([sd["q_proj.weight"], sd["k_proj.weight"], sd["v_proj.weight"]]))
+        tm.in_proj_bias.copy_(torch.cat([sd["q_proj.bias"], sd["k_proj.bias"], sd["v_proj.bias"]]))
+        tm.out_proj.weight.copy_(sd["out_proj.weight"])
+        tm.out_proj.bias.copy_(sd["out_proj.bias"])
+    xt = s.tensor(x).detach()
+    mask = torch.zeros(5, 5, dtype=torch.bool)
+    mask[:, 3] = True
+    o2, w2 = mha.forward_qkv_with_weights(s, x, x, x, s.tensor_tape.leaf(mask, False), False, False)
+    to, tw = tm(xt, xt, xt, attn_mask=mask, need_weights=True, average_attn_weights=False)
+    assert s.tensor_shape(w2) == [2, 2, 5, 5] and torch.allclose(to, s.tensor(o2), atol=1e-10) and torch.allclose(tw, s.tensor(w2), atol=1e-10)
+    rep = s.tensor_backward(s.tensor_sum(s.tensor_square(w)))
+    assert float(rep.gradient(x).abs().sum()) > 0
+
+
+def test_weight_norm_functions_and_lazy_materialisation():
+    s = FrankenTorchSession(ledger_dispatch=False)
+    conv = nn.Conv2d(s, 3, 4, 3)
+    for dim in (0, 1):
+        cw = conv._parameters["weight"]
+        g, v = nn.weight_norm_decompose(s, cw, dim)
+        W = s.tensor(cw)
+        assert s.tensor_shape(g) == [W.shape[dim]] and s.tensor_requires_grad(g) and s.tensor_requires_grad(v)
+        others = [d for d in range(4) if d != dim]
+        assert torch.allclose(s.tensor(g), W.pow(2).sum(others).sqrt())
+        w = nn.weight_norm_reconstruct(s, g, v, dim)
+        assert torch.allclose(s.tensor(w), W, atol=1e-12)
+        rep = s.tensor_backward(s.tensor_sum(s.tensor_square(w)))
+        # d/dg sum(w^2) = 2 g (the direction has unit norm); the direction's gradient is orthogonal to v per slice
+        assert torch.allclose(rep.gradient(g), 2 * s.tensor(g), atol=1e-10)
+        assert torch.allclose((rep.gradient(v) * s.tensor(v)).sum(others), torch.zeros(W.shape[dim], dtype=W.dtype), atol=1e-10)
+    with pytest.raises(ValueError):
+        nn.weight_norm_decompose(s, conv._parameters["weight"], 4)
+    with pytest.raises(ValueError):
+        nn.weight_norm_reconstruct(s, s.tensor_variable([1.0, 2.0], [2]), conv._parameters["weight"], 0)
+    lazy = nn.LazyLinear(s, 3)
+    assert not lazy.is_materialized() and lazy.parameters() == []
+    lazy.materialize(s, 5)
+    assert lazy.is_materialized() and s.tensor_shape(lazy.weight if hasattr(lazy, "weight") else lazy._parameters["weight"]) == [3, 5]
+    lc = nn.LazyConv2d(s, 4, 3)
+    assert not lc.is_materialized()
+    y = lc.forward_lazy(s, s.randn([1, 2, 6, 6]))
+    assert lc.is_materialized() and s.tensor_shape(y) == [1, 4, 4, 4] and s.tensor_shape(lc._parameters["weight"]) == [4, 2, 3, 3]
+    with pytest.raises(ValueError):
+        nn.LazyConv1d(s, 4, 3)(s, s.randn([1, 2, 6, 6]))

@@ -85,3 +85,42 @@ def test_packet_contract_artifacts_are_emitted_and_validated(tmp_path):
     # the committed artifacts are current
     here = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
     assert packets.validate(__import__("os").path.join(here, "artifacts", "phase2c")) == []
+
+
+def test_conformance_harness_library_entry_points(tmp_path):
+    """``HarnessConfig`` / ``HarnessReport`` / per-family runners / forensics matrix / micro-benchmarks
+    (ft-conformance/src/lib.rs:38, :580, :1685, :1777-2680, :2682, :4834)."""
+    import json
+    from frankentorch_b200.conformance import harness as H
+    from frankentorch_b200.conformance.runner_more import FAMILIES
+    cfg = H.HarnessConfig.default_paths()
+    smoke = H.run_smoke(cfg)
+    assert smoke.suite == "smoke" and smoke.fixture_count == len(FAMILIES) and smoke.oracle_present and smoke.cases_total == 0
+    for fam in FAMILIES:
+        assert callable(getattr(H, f"run_{ {'scalar_autograd': 'scalar', 'dispatch_key': 'dispatch'}.get(fam, fam)}_conformance"))
+    rep, cases = H.run_dispatch_conformance(cfg, "hardened")
+    assert rep.ok() and rep.cases_total == len(cases) > 0 and not rep.strict_mode and all(c.mode == "hardened" for c in cases)
+    rep, _ = H.run_tensor_sort_conformance(cfg, "strict")
+    assert rep.ok() and rep.strict_mode and rep.suite == "tensor_sort"
+    with __import__("pytest").raises(ValueError):
+        H.run_family_conformance(cfg, "no_such_family", "strict")
+    out = str(tmp_path / "sub" / "e2e.jsonl")
+    summ = H.emit_e2e_forensics_matrix_filtered(cfg, out, (), "FT-P2C-004")
+    lines = [json.loads(l) for l in open(out)]
+    assert summ.log_entries == len(lines) > 0 and summ.failed_entries == 0 and [m.value for m in summ.modes] == ["strict", "hardened"]
+    assert {l["packet_id"] for l in lines} == {"FT-P2C-004"} and {l["mode"] for l in lines} == {"strict", "hardened"}
+    assert {l["scenario_id"].split("/")[0] for l in lines} == {"autograd_scheduler", "scalar_autograd"}
+    one = H.emit_e2e_forensics_matrix_filtered(cfg, out, ["strict"], "FT-P2C-003")
+    assert one.log_entries * 1 == sum(1 for _ in open(out)) and [m.value for m in one.modes] == ["strict"]
+    with __import__("pytest").raises(ValueError):
+        H.emit_e2e_forensics_matrix_filtered(cfg, out, (), "FT-P2C-042")
+    assert sorted(sum(H.PACKET_FAMILIES.values(), [])) == sorted(list(FAMILIES) + ["dispatch_key"])     # every family has a packet
+    b = H.BenchReport.from_samples([5, 1, 3, 2, 4, 100])
+    assert (b.iterations, b.p50_ns, b.p95_ns, b.p99_ns, b.mean_ns) == (6, 3, 100, 100, 19)
+    assert H.BenchReport.from_samples([]).iterations == 0
+    assert H.BenchReport(1, 10, 110, 0, 0).regression_pct(H.BenchReport(1, 10, 100, 0, 0)) == 10.0
+    mb = H.run_scalar_microbench(5, "strict")
+    assert mb.iterations == 5 and 0 < mb.p50_ns <= mb.p95_ns <= mb.p99_ns
+    pb = H.run_packet_e2e_microbench(cfg, 1, "FT-P2C-003", tmp_dir=str(tmp_path))
+    assert pb.iterations == 1 and pb.p50_ns > 0
+    assert H.mode_label("Strict") == "strict" and H.now_unix_ms() > 1_600_000_000_000
