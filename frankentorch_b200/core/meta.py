@@ -8,6 +8,7 @@ ft-device/src/lib.rs - ``DeviceGuard`` :35, ``ensure_same_device`` :62.
 from __future__ import annotations
 
 import enum
+import math
 import struct
 from dataclasses import dataclass, field
 from typing import Optional, Sequence, Tuple
@@ -46,10 +47,75 @@ class DeviceError(ValueError):
     pass
 
 
-@dataclass(frozen=True)
 class QuantizationParams:
-    scale: float = 1.0
-    zero_point: int = 0
+    """Affine quantization parameters of a tensor (ft-core/src/lib.rs:188): one ``(scale, zero_point)`` for the whole
+    tensor, or one per slice of ``axis``.  Scales must be finite and positive; equality and hashing use the scales'
+    bit patterns."""
+    __slots__ = ("_scales", "_zero_points", "_axis")
+
+    def __init__(self, scale: float = 1.0, zero_point: int = 0):
+        self._scales = (self._check(scale),)
+        self._zero_points = (int(zero_point),)
+        self._axis: Optional[int] = None
+
+    @staticmethod
+    def _check(scale: float) -> float:
+        scale = float(scale)
+        if not math.isfinite(scale) or scale <= 0.0:
+            raise TensorMetaError(f"invalid quantization scale {scale!r}: must be finite and > 0")
+        return scale
+
+    @staticmethod
+    def per_channel(scales: Sequence[float], zero_points: Sequence[int], axis: int) -> "QuantizationParams":
+        if len(scales) == 0:
+            raise TensorMetaError("per-channel quantization needs at least one channel")
+        if len(scales) != len(zero_points):
+            raise TensorMetaError(f"quantization vector length mismatch: {len(scales)} scales vs {len(zero_points)} zero points")
+        q = QuantizationParams.__new__(QuantizationParams)
+        q._scales = tuple(QuantizationParams._check(s) for s in scales)
+        q._zero_points = tuple(int(z) for z in zero_points)
+        q._axis = int(axis)
+        return q
+
+    scale = property(lambda self: self._scales[0])
+    zero_point = property(lambda self: self._zero_points[0])
+    axis = property(lambda self: self._axis)
+
+    def scales(self):
+        return list(self._scales)
+
+    def zero_points(self):
+        return list(self._zero_points)
+
+    def __len__(self) -> int:
+        return len(self._scales)
+
+    def is_per_channel(self) -> bool:
+        return self._axis is not None
+
+    def validate_for_shape(self, shape: Sequence[int]) -> None:
+        if self._axis is None:
+            if len(self._scales) != 1:
+                raise TensorMetaError("per-tensor quantization carries exactly one scale")
+            return
+        if not 0 <= self._axis < len(shape):
+            raise TensorMetaError(f"quantization axis {self._axis} out of range for rank {len(shape)}")
+        if shape[self._axis] != len(self._scales):
+            raise TensorMetaError(f"{len(self._scales)} quantization channels for extent {shape[self._axis]} of axis {self._axis}")
+
+    def _key(self):
+        return (tuple(struct.pack("<d", s) for s in self._scales), self._zero_points, self._axis)
+
+    def __eq__(self, other):
+        return isinstance(other, QuantizationParams) and other._key() == self._key()
+
+    def __hash__(self):
+        return hash(self._key())
+
+    def __repr__(self):
+        if self._axis is None:
+            return f"QuantizationParams(scale={self.scale}, zero_point={self.zero_point})"
+        return f"QuantizationParams.per_channel(scales={list(self._scales)}, zero_points={list(self._zero_points)}, axis={self._axis})"
 
 
 def contiguous_strides(shape: Sequence[int]) -> Tuple[int, ...]:
@@ -98,6 +164,49 @@ class TensorMeta:
         if storage_offset + span > U64_MAX:
             raise TensorMetaError(f"storage offset overflow: offset {storage_offset} + span {span}")
         return TensorMeta(shape, strides, int(storage_offset), dtype, device)
+
+    @staticmethod
+    def quantized_from_shape(shape, dtype: DType, device: Device, scale: float, zero_point: int) -> "TensorMeta":
+        return TensorMeta.from_shape(shape, dtype, device).with_quantization(QuantizationParams(scale, zero_point)).validated()
+
+    @staticmethod
+    def quantized_per_channel_from_shape(shape, dtype: DType, device: Device, scales, zero_points, axis: int) -> "TensorMeta":
+        q = QuantizationParams.per_channel(scales, zero_points, axis)
+        return TensorMeta.from_shape(shape, dtype, device).with_quantization(q).validated()
+
+    @staticmethod
+    def quantized_from_shape_and_strides(shape, strides, storage_offset, dtype: DType, device: Device, scale: float,
+                                         zero_point: int) -> "TensorMeta":
+        m = TensorMeta.from_shape_and_strides(shape, strides, storage_offset, dtype, device)
+        return m.with_quantization(QuantizationParams(scale, zero_point)).validated()
+
+    @staticmethod
+    def quantized_per_channel_from_shape_and_strides(shape, strides, storage_offset, dtype: DType, device: Device, scales,
+                                                     zero_points, axis: int) -> "TensorMeta":
+        m = TensorMeta.from_shape_and_strides(shape, strides, storage_offset, dtype, device)
+        return m.with_quantization(QuantizationParams.per_channel(scales, zero_points, axis)).validated()
+
+    def with_quantization(self, quantization: QuantizationParams) -> "TensorMeta":
+        return TensorMeta(self.shape, self.strides, self.storage_offset, self.dtype, self.device, quantization)
+
+    def with_dtype(self, dtype: DType) -> "TensorMeta":
+        """Same layout with another element type; quantization parameters survive only on a quantized dtype."""
+        return TensorMeta(self.shape, self.strides, self.storage_offset, dtype, self.device,
+                          self.quantization if dtype.is_quantized() else None)
+
+    def validate(self) -> None:
+        """A quantized dtype needs quantization parameters that fit the shape; any other dtype must carry none."""
+        if self.dtype.is_quantized():
+            if self.quantization is None:
+                raise TensorMetaError(f"dtype {self.dtype.value} needs quantization parameters")
+            self.quantization.validate_for_shape(self.shape)
+        elif self.quantization is not None:
+            raise TensorMetaError(f"dtype {self.dtype.value} must not carry quantization parameters")
+        TensorMeta.from_shape_and_strides(self.shape, self.strides, self.storage_offset, self.dtype, self.device)
+
+    def validated(self) -> "TensorMeta":
+        self.validate()
+        return self
 
     # ------------------------------------------------------------------ queries
     @property
@@ -150,7 +259,13 @@ class TensorMeta:
         if self.quantization is None:
             buf += struct.pack("<Q", 0)
         else:
-            buf += struct.pack("<Qdq", 1, self.quantization.scale, self.quantization.zero_point)
+            q = self.quantization
+            if not q.is_per_channel():           # the per-tensor encoding is unchanged
+                buf += struct.pack("<Qdq", 1, q.scale, q.zero_point)
+            else:
+                buf += struct.pack("<QQQ", 2, q.axis, len(q))
+                for sc, zp in zip(q.scales(), q.zero_points()):
+                    buf += struct.pack("<dq", sc, zp)
         return native.fnv1a64(bytes(buf))
 
 

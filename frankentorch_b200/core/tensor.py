@@ -26,13 +26,14 @@ class DenseTensorError(ValueError):
 
 
 class DenseTensor:
-    __slots__ = ("id", "storage_id", "_version", "data")
+    __slots__ = ("id", "storage_id", "_version", "data", "quantization")
 
     def __init__(self, data: torch.Tensor, storage_id: Optional[int] = None, version=None):
         self.id = next(_NEXT_TENSOR_ID)
         self.storage_id = next(_NEXT_STORAGE_ID) if storage_id is None else storage_id
         self._version = version if version is not None else [0]   # shared cell between views
         self.data = data
+        self.quantization = None                                   # QuantizationParams of a quantized tensor
 
     # ------------------------------------------------------------------ constructors
     @staticmethod
@@ -48,11 +49,82 @@ class DenseTensor:
     def scalar(value: float, dtype: DType = DType.F64) -> "DenseTensor":
         return DenseTensor(torch.tensor(value, dtype=dtype.to_torch()))
 
+    @staticmethod
+    def from_typed_storage(meta: TensorMeta, storage) -> "DenseTensor":
+        """Tensor over an existing typed buffer (ft-core/src/lib.rs:1151): the dtype of ``meta`` must be the
+        storage's variant and the layout must fit inside the buffer.  Quantized tensors keep their integer codes;
+        ``meta.quantization`` says how to read them."""
+        meta.validate()
+        if meta.dtype != storage.dtype:
+            raise DenseTensorError(f"meta dtype {meta.dtype.value} does not match storage variant {storage.dtype.value}")
+        need = meta.storage_offset + sum((n - 1) * st for n, st in zip(meta.shape, meta.strides) if n) + (1 if meta.numel else 0)
+        if meta.numel and need > len(storage):
+            raise DenseTensorError(f"layout needs {need} storage elements, the buffer holds {len(storage)}")
+        t = DenseTensor(torch.as_strided(storage.data, meta.shape, meta.strides, meta.storage_offset))
+        t.quantization = meta.quantization
+        return t
+
+    @staticmethod
+    def from_storage(meta: TensorMeta, values) -> "DenseTensor":
+        """``from_typed_storage`` over a fresh buffer of ``meta.dtype`` holding ``values``
+        (``from_storage`` / ``from_storage_f32`` / ``_f16`` / ``_bf16`` / ``_qint8`` / ``_quint8`` of the reference)."""
+        from .storage import TensorStorage
+        return DenseTensor.from_typed_storage(meta, TensorStorage.from_values(values, meta.dtype))
+
+    @staticmethod
+    def from_contiguous_values(values, shape: Sequence[int], device=Device.Cpu, dtype: DType = DType.F64) -> "DenseTensor":
+        t = DenseTensor.from_storage(TensorMeta.from_shape(shape, dtype, Device.Cpu), values)
+        if Device.parse(device) == Device.Cuda:
+            t.data = t.data.cuda()
+        return t
+
+    @staticmethod
+    def from_contiguous_values_quantized(codes, shape: Sequence[int], dtype: DType, scale: float, zero_point: int) -> "DenseTensor":
+        """Quantized tensor from integer codes with per-tensor parameters (``from_contiguous_values_qint8 / _quint8``)."""
+        return DenseTensor.from_storage(TensorMeta.quantized_from_shape(shape, dtype, Device.Cpu, scale, zero_point), codes)
+
+    @staticmethod
+    def from_contiguous_values_quantized_per_channel(codes, shape: Sequence[int], dtype: DType, scales, zero_points,
+                                                     axis: int) -> "DenseTensor":
+        meta = TensorMeta.quantized_per_channel_from_shape(shape, dtype, Device.Cpu, scales, zero_points, axis)
+        return DenseTensor.from_storage(meta, codes)
+
+    def typed_storage(self):
+        """The whole underlying buffer as a :class:`TensorStorage` (views share it)."""
+        from .storage import TensorStorage
+        base = self.data._base if self.data._base is not None else self.data
+        flat = base.reshape(-1) if base.is_contiguous() else base.contiguous().reshape(-1)
+        return TensorStorage.from_tensor(flat)
+
+    def shares_storage_with(self, other: "DenseTensor") -> bool:
+        return self.storage_id == other.storage_id
+
+    def contiguous_values_as_f64(self) -> list:
+        """Values in row-major order as f64; a quantized tensor is dequantized with its parameters."""
+        return self.dequantized_values_as_f64() if getattr(self, "quantization", None) is not None else \
+            self.data.contiguous().reshape(-1).to(torch.float64).tolist()
+
+    def dequantized_values_as_f64(self) -> list:
+        q = getattr(self, "quantization", None)
+        if q is None:
+            raise DenseTensorError("tensor carries no quantization parameters")
+        codes = self.data.to(torch.float64)
+        if not q.is_per_channel():
+            return ((codes - q.zero_point) * q.scale).contiguous().reshape(-1).tolist()
+        shape = [1] * codes.dim()
+        shape[q.axis] = len(q)
+        sc = torch.tensor(q.scales(), dtype=torch.float64).reshape(shape)
+        zp = torch.tensor(q.zero_points(), dtype=torch.float64).reshape(shape)
+        return ((codes - zp) * sc).contiguous().reshape(-1).tolist()
+
     # ------------------------------------------------------------------ metadata
     @property
     def meta(self) -> TensorMeta:
         t = self.data
         dev = Device.Cuda if t.is_cuda else Device.Cpu
+        if self.quantization is not None:
+            dt = DType.QInt8 if t.dtype == torch.int8 else DType.QUInt8
+            return TensorMeta.from_shape_and_strides(t.shape, t.stride(), t.storage_offset(), dt, dev).with_quantization(self.quantization)
         return TensorMeta.from_shape_and_strides(t.shape, t.stride(), t.storage_offset(), DType.from_torch(t.dtype), dev)
 
     @property
@@ -101,6 +173,24 @@ def DenseBoolTensor(values, shape) -> DenseTensor:
     return DenseTensor(torch.tensor(list(values), dtype=torch.bool).reshape(tuple(shape)))
 
 
+def dense_bool_from_bools(values: Sequence[bool], shape: Sequence[int], device=Device.Cpu) -> DenseTensor:
+    """``DenseBoolTensor::from_bools`` (ft-core/src/lib.rs:2051)."""
+    n = 1
+    for s_ in shape:
+        n *= s_
+    if len(values) != n:
+        raise DenseTensorError(f"value count {len(values)} does not match shape {tuple(shape)}")
+    t = DenseBoolTensor([bool(v) for v in values], shape)
+    if Device.parse(device) == Device.Cuda:
+        t.data = t.data.cuda()
+    return t
+
+
+def contiguous_bools(t: DenseTensor) -> list:
+    """Row-major ``bool`` list of a bool (or integer) tensor: non-zero is true."""
+    return [bool(v) for v in t.data.contiguous().reshape(-1).tolist()]
+
+
 class SparseTensorError(ValueError):
     pass
 
@@ -120,12 +210,43 @@ class SparseCOOTensor:
                 raise SparseTensorError(f"index out of bounds in sparse dim {d}")
         self.indices, self.values, self.shape = indices, values, tuple(shape)
 
+    @staticmethod
+    def from_coords(coords: Sequence[Sequence[int]], values, dense_shape: Sequence[int], dtype: DType = DType.F64,
+                    device=Device.Cpu) -> "SparseCOOTensor":
+        """One coordinate list per non-zero (``coords[k]`` is the index tuple of ``values[k]``); an empty list gives
+        an all-zero tensor whose sparse dimension is the full rank (ft-core/src/lib.rs:2515)."""
+        nnz = len(coords)
+        sd = len(dense_shape) if nnz == 0 else len(coords[0])
+        if any(len(c) != sd for c in coords):
+            raise SparseTensorError("every coordinate must have the same length")
+        if len(values) != nnz:
+            raise SparseTensorError(f"{len(values)} values for {nnz} coordinates")
+        idx = torch.tensor(list(coords), dtype=torch.int64).reshape(nnz, sd).t().contiguous()
+        dev = "cuda" if Device.parse(device) == Device.Cuda else "cpu"
+        return SparseCOOTensor(idx.to(dev), torch.tensor(list(values), dtype=dtype.to_torch(), device=dev), dense_shape)
+
     @property
     def nnz(self) -> int:
         return int(self.indices.shape[1])
 
+    def dense_shape(self):
+        return list(self.shape)
+
+    @property
+    def sparse_dim(self) -> int:
+        return int(self.indices.shape[0])
+
+    def is_coalesced(self) -> bool:
+        """True when the coordinates are unique and in row-major order."""
+        if self.nnz <= 1:
+            return True
+        key = torch.zeros(self.nnz, dtype=torch.int64, device=self.indices.device)
+        for d in range(self.sparse_dim):
+            key = key * int(self.shape[d]) + self.indices[d]
+        return bool((key[1:] > key[:-1]).all())
+
     def _torch(self) -> torch.Tensor:
-        return torch.sparse_coo_tensor(self.indices, self.values, self.shape)
+        return torch.sparse_coo_tensor(self.indices, self.values, self.shape, check_invariants=False)   # bounds were checked at construction
 
     def to_dense(self) -> torch.Tensor:
         return self._torch().to_dense()
@@ -158,6 +279,16 @@ class SparseCSRTensor:
             raise SparseTensorError("CSR row pointers must be non-decreasing")
         if self.col.numel() and (self.col.min() < 0 or self.col.max() >= self.shape[1]):
             raise SparseTensorError("CSR column index out of bounds")
+
+    def nrows(self) -> int:
+        return self.shape[0]
+
+    def ncols(self) -> int:
+        return self.shape[1]
+
+    @property
+    def nnz(self) -> int:
+        return int(self.col.numel())
 
     def to_dense(self) -> torch.Tensor:
         return torch.sparse_csr_tensor(self.crow, self.col, self.values, self.shape).to_dense()

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import ctypes as C
 import enum
+import time
 from dataclasses import dataclass, field
 from typing import List, Optional
 
@@ -117,6 +118,10 @@ class RuntimeContext:
     def evidence(self) -> List[EvidenceEntry]:
         return self.ledger.entries()
 
+    def ledger_mut(self) -> EvidenceLedger:
+        """The ledger itself, for callers that record their own evidence (ft-runtime/src/lib.rs:116)."""
+        return self.ledger
+
 
 class ScrubStatus(enum.Enum):
     Ok = "ok"
@@ -144,3 +149,12 @@ class DurabilityEnvelope:
     scrub_status: ScrubStatus = ScrubStatus.Ok
     last_ok_unix_ms: Optional[int] = None
     decode_proofs: List[DecodeProof] = field(default_factory=list)
+
+    def mark_scrub_status(self, status: ScrubStatus) -> None:
+        """Result of the latest scrub; an ``Ok`` scrub also stamps ``last_ok_unix_ms``."""
+        self.scrub_status = status
+        if status is ScrubStatus.Ok:
+            self.last_ok_unix_ms = int(time.time() * 1000)
+
+    def add_decode_proof(self, reason: str, proof_hash: str, recovered_blocks: int = 0) -> None:
+        self.decode_proofs.append(DecodeProof(int(time.time() * 1000), str(reason), int(recovered_blocks), str(proof_hash)))

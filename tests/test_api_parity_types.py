@@ -451,3 +451,91 @@ def test_weight_norm_functions_and_lazy_materialisation():
     assert lc.is_materialized() and s.tensor_shape(y) == [1, 4, 4, 4] and s.tensor_shape(lc._parameters["weight"]) == [4, 2, 3, 3]
     with pytest.raises(ValueError):
         nn.LazyConv1d(s, 4, 3)(s, s.randn([1, 2, 6, 6]))
+
+
+def test_quantized_metadata_typed_storage_constructors_and_sparse_accessors():
+    from frankentorch_b200.core.dtype import DType
+    from frankentorch_b200.core.meta import Device, QuantizationParams, TensorMeta, TensorMetaError
+    from frankentorch_b200.core.storage import TensorStorage
+    from frankentorch_b200.core.tensor import (DenseTensor, DenseTensorError, SparseCOOTensor, SparseCSRTensor, SparseTensorError,
+                                                contiguous_bools, dense_bool_from_bools)
+    q = QuantizationParams(0.5, 3)
+    assert (q.scale, q.zero_point, q.axis, len(q), q.is_per_channel()) == (0.5, 3, None, 1, False)
+    assert q == QuantizationParams(0.5, 3) and hash(q) == hash(QuantizationParams(0.5, 3)) and q != QuantizationParams(0.5, 4)
+    pc = QuantizationParams.per_channel([0.5, 0.25], [0, 10], 0)
+    assert pc.scales() == [0.5, 0.25] and pc.zero_points() == [0, 10] and pc.axis == 0 and pc.is_per_channel()
+    for bad in (lambda: QuantizationParams(0.0, 0), lambda: QuantizationParams(float("nan"), 0), lambda: QuantizationParams(-1.0, 0),
+                lambda: QuantizationParams.per_channel([], [], 0), lambda: QuantizationParams.per_channel([1.0], [0, 1], 0)):
+        with pytest.raises(TensorMetaError):
+            bad()
+    m = TensorMeta.quantized_per_channel_from_shape([2, 3], DType.QInt8, Device.Cpu, [0.5, 0.25], [0, 10], 0)
+    t = DenseTensor.from_storage(m, [2, 4, 6, 14, 18, 10])
+    assert t.dequantized_values_as_f64() == [1.0, 2.0, 3.0, 1.0, 2.0, 0.0] == t.contiguous_values_as_f64()
+    assert t.meta.dtype is DType.QInt8 and t.meta.quantization == pc
+    pt = TensorMeta.quantized_from_shape([3], DType.QUInt8, Device.Cpu, 0.1, 128)
+    assert pt.fingerprint64() != TensorMeta.quantized_from_shape([3], DType.QUInt8, Device.Cpu, 0.2, 128).fingerprint64()
+    assert m.fingerprint64() != TensorMeta.quantized_per_channel_from_shape([2, 3], DType.QInt8, Device.Cpu, [0.5, 0.25], [0, 11], 0).fingerprint64()
+    assert DenseTensor.from_contiguous_values_quantized([0, 128, 255], [3], DType.QUInt8, 0.1, 128).contiguous_values_as_f64()[1] == 0.0
+    with pytest.raises(TensorMetaError):
+        TensorMeta.quantized_per_channel_from_shape([2, 3], DType.QInt8, Device.Cpu, [0.5], [0], 0)       # 1 channel for extent 2
+    with pytest.raises(TensorMetaError):
+        TensorMeta.quantized_per_channel_from_shape([2, 3], DType.QInt8, Device.Cpu, [0.5, 0.25], [0, 0], 2)
+    with pytest.raises(TensorMetaError):
+        TensorMeta.from_shape([2], DType.QInt8).validate()
+    with pytest.raises(TensorMetaError):
+        TensorMeta.from_shape([2], DType.F32).with_quantization(q).validate()
+    assert m.with_dtype(DType.F32).quantization is None and m.with_dtype(DType.QUInt8).quantization == pc
+    sm = TensorMeta.quantized_from_shape_and_strides([2, 2], [1, 2], 0, DType.QInt8, Device.Cpu, 1.0, 0)
+    assert sm.strides == (1, 2) and sm.quantization.scale == 1.0
+    st = TensorStorage.from_values([1., 2., 3., 4., 5., 6.], DType.F32)
+    v = DenseTensor.from_typed_storage(TensorMeta.from_shape_and_strides([2, 2], [2, 1], 2, DType.F32), st)
+    assert v.data.tolist() == [[3.0, 4.0], [5.0, 6.0]] and len(v.typed_storage()) == 6 and v.typed_storage().dtype is DType.F32
+    with pytest.raises(DenseTensorError):
+        DenseTensor.from_typed_storage(TensorMeta.from_shape([7], DType.F32), st)
+    with pytest.raises(DenseTensorError):
+        DenseTensor.from_typed_storage(TensorMeta.from_shape([6], DType.F64), st)
+    assert DenseTensor.from_contiguous_values([1.0, 2.0], [2], dtype=DType.BF16).data.dtype == torch.bfloat16
+    a = DenseTensor.from_values([1., 2., 3., 4.], [4])
+    assert a.shares_storage_with(a.view([2, 2])) and not a.shares_storage_with(t)
+    b = dense_bool_from_bools([True, False, True, True], [2, 2])
+    assert contiguous_bools(b) == [True, False, True, True] and b.data.dtype == torch.bool
+    with pytest.raises(DenseTensorError):
+        dense_bool_from_bools([True], [2])
+    s = SparseCOOTensor.from_coords([[0, 1], [1, 0], [0, 1]], [1., 2., 3.], [2, 2])
+    assert not s.is_coalesced() and s.coalesce().is_coalesced() and s.dense_shape() == [2, 2] and s.sparse_dim == 2
+    assert s.to_dense().tolist() == [[0.0, 4.0], [2.0, 0.0]]
+    e = SparseCOOTensor.from_coords([], [], [2, 3])
+    assert e.nnz == 0 and e.sparse_dim == 2 and float(e.to_dense().abs().sum()) == 0.0 and e.is_coalesced()
+    with pytest.raises(SparseTensorError):
+        SparseCOOTensor.from_coords([[0, 1], [1]], [1., 2.], [2, 2])
+    c = SparseCSRTensor([0, 1, 2], [1, 0], [5., 6.], [2, 2])
+    assert (c.nrows(), c.ncols(), c.nnz) == (2, 2, 2)
+
+
+def test_runtime_durability_envelope_updates_and_integration_hooks():
+    from frankentorch_b200.runtime.integrations import (Budget, Style, asupersync_infinite_budget, frankentui_default_style,
+                                                        render_ledger_panel)
+    from frankentorch_b200.runtime.ledger import DurabilityEnvelope, EvidenceKind, RuntimeContext, ScrubStatus
+    env = DurabilityEnvelope("ckpt-1", "checkpoint", "det64:00")
+    env.mark_scrub_status(ScrubStatus.Failed)
+    assert env.scrub_status is ScrubStatus.Failed and env.last_ok_unix_ms is None
+    env.mark_scrub_status(ScrubStatus.Ok)
+    assert env.last_ok_unix_ms is not None
+    env.add_decode_proof("two source symbols dropped", "det64:ab", 2)
+    assert len(env.decode_proofs) == 1 and env.decode_proofs[0].proof_hash == "det64:ab" and env.decode_proofs[0].recovered_blocks == 2
+    rt = RuntimeContext("hardened")
+    rt.ledger_mut().record(EvidenceKind.Durability, "scrub ok artifact=ckpt-1")
+    assert rt.ledger_mut() is rt.ledger and rt.evidence()[-1].summary == "scrub ok artifact=ckpt-1"
+    b = asupersync_infinite_budget()
+    assert b is Budget.INFINITE and b.is_infinite() and not b.exhausted(10 ** 15, 10 ** 9, 10 ** 9)
+    tight = b.meet(Budget(deadline_unix_ms=1000, poll_quota=5)).meet(Budget(deadline_unix_ms=2000, cost_quota=7, priority=3))
+    assert (tight.deadline_unix_ms, tight.poll_quota, tight.cost_quota, tight.priority) == (1000, 5, 7, 3) and not tight.is_infinite()
+    assert tight.exhausted(1000) and tight.exhausted(0, polls=5) and tight.exhausted(0, cost=7) and not tight.exhausted(999, 4, 6)
+    st = frankentui_default_style()
+    assert st == Style() and st.border == "plain" and st.width == 100
+    panel = render_ledger_panel(rt.ledger, st, last=1)
+    lines = panel.split("\n")
+    assert lines[0] == "+" + "-" * 98 + "+" == lines[-1] and all(len(l) == 100 for l in lines)
+    assert "Durability=1" in lines[1] and "Policy=1" in lines[1] and "scrub ok artifact=ckpt-1" in lines[2]
+    bare = render_ledger_panel(rt.ledger, Style(border="none", width=40), last=5)
+    assert not bare.startswith("+") and all(len(l) <= 40 for l in bare.split("\n"))
