@@ -34,6 +34,7 @@ std::mutex g_mu;
 int g_width = 1;             // 1 = serial
 bool g_configured = false;
 int64_t g_par_min_work = 1 << 15;   // below this many elements of work a kernel stays serial
+int g_target_workers = 0;           // 0 = split into one chunk per pool thread; n = into about n chunks
 
 // Distinct (physical id, core id) pairs of /proc/cpuinfo; falls back to the logical count.
 int physical_cores() {
@@ -58,6 +59,7 @@ int physical_cores() {
 template <typename F>
 void parallel_rows(int64_t rows, int64_t work_per_row, F fn) {
   int w = g_width;
+  if (w > 1 && g_target_workers > 0) w = g_target_workers;
   if (w <= 1 || rows < 2 || rows * work_per_row < g_par_min_work) {
     fn(0, rows);
     return;
@@ -131,6 +133,16 @@ FTC_API int64_t ftc_pool_set_min_work(int64_t elems) {
   if (elems >= 0) g_par_min_work = elems;
   return old;
 }
+
+// Number of chunks a row-parallel kernel is cut into (0 = the pool width).  Returns the previous value, so a
+// measurement can flip it inside one process and restore it.  Every row is computed by one thread whatever the
+// split, so results do not depend on it.
+FTC_API int ftc_pool_set_target_workers(int workers) {
+  const int old = g_target_workers;
+  if (workers >= 0 && workers <= 4096) g_target_workers = workers;
+  return old;
+}
+FTC_API int ftc_pool_target_workers() { return g_target_workers; }
 
 FTC_API double ftc_pairwise_sum_par(const double* x, int64_t n) {
   int w = g_width, depth = 0;

@@ -65,6 +65,22 @@ def set_sdpa_br(br: int) -> int:
     return int(native.load().ftc_set_sdpa_br(int(br)))
 
 
+def set_parallel_target_workers(workers: int) -> int:
+    """Number of chunks the row-parallel CPU kernels are cut into (0 = one per pool thread); returns the previous
+    value so a paired measurement can restore it (ft-kernel-cpu/src/lib.rs:2758).  Each row is computed by one
+    thread whatever the split: results do not change."""
+    return int(native.load().ftc_pool_set_target_workers(int(workers)))
+
+
+def parallel_target_workers() -> int:
+    return int(native.load().ftc_pool_target_workers())
+
+
+def set_par_min_work(elems: int) -> int:
+    """Elements of work below which a kernel stays serial; returns the previous gate."""
+    return int(native.load().ftc_pool_set_min_work(int(elems)))
+
+
 def set_sdpa_br_auto() -> int:
     return set_sdpa_br(0)
 

@@ -50,6 +50,7 @@ def load():
         "ftc_pool_configure": ([C.c_char_p, P(i32)], i32), "ftc_pool_width": ([], i32),
         "ftc_pool_physical_cores": ([], i32), "ftc_pool_auto_width": ([], i32),
         "ftc_pool_reset_for_tests": ([], None), "ftc_pool_set_min_work": ([i64], i64),
+        "ftc_pool_set_target_workers": ([C.c_int], C.c_int), "ftc_pool_target_workers": ([], C.c_int),
         "ftc_pairwise_sum_par": ([vp, i64], dbl),
         "ftc_linear_f64_par": ([vp, vp, vp, vp, i64, i64, i64], None),
         "ftc_layer_norm_f64_par": ([vp, vp, vp, vp, i64, i64, dbl], None),

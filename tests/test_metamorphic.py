@@ -156,6 +156,37 @@ def test_row_parallel_kernels_are_bitwise_serial_at_every_width_and_gate(pool):
             assert torch.equal(ln.view(torch.int64), ln0.view(torch.int64)), (width, gate)
 
 
+def test_chunk_target_of_row_parallel_kernels_changes_scheduling_not_results(pool):
+    """``set_parallel_target_workers`` (ft-kernel-cpu/src/lib.rs:2758): the number of chunks of the row split is a
+    measurement lever that returns the previous value; every row is computed by one thread whatever the split."""
+    from frankentorch_b200.runtime import cpu_pool
+    lib = pool
+    g = torch.Generator().manual_seed(3)
+    m, k, n = 37, 64, 48
+    x, w, b = (torch.randn(*s, generator=g, dtype=torch.float64) for s in ((m, k), (n, k), (n,)))
+    y0 = torch.empty(m, n, dtype=torch.float64)
+    lib.ftc_linear_f64(x.data_ptr(), w.data_ptr(), b.data_ptr(), y0.data_ptr(), m, k, n)
+
+    def run():
+        y = torch.full((m, n), float("nan"), dtype=torch.float64)
+        lib.ftc_linear_f64_par(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), m, k, n)
+        return y
+    assert cpu_pool.parallel_target_workers() == 0
+    try:
+        prev = 0
+        for target in (1, 3, 7, 37, 100, 0):
+            assert cpu_pool.set_parallel_target_workers(target) == prev
+            prev = target
+            for width in (1, 4):
+                y = _with_width(lib, width, 0, run)
+                assert torch.equal(y.view(torch.int64), y0.view(torch.int64)), (target, width)
+        assert cpu_pool.set_parallel_target_workers(-5) == 0 and cpu_pool.parallel_target_workers() == 0   # out of range: ignored
+        old_gate = cpu_pool.set_par_min_work(123)
+        assert cpu_pool.set_par_min_work(old_gate) == 123
+    finally:
+        cpu_pool.set_parallel_target_workers(0)
+
+
 def test_pool_policy_auto_caps_at_sixteen_and_is_decided_once(pool):
     from frankentorch_b200.runtime.cpu_pool import configure_cpu_threads
     lib = pool
