@@ -43,6 +43,12 @@ def g1_static(work: Path):
     rc, out = _run([PY, "-c", "import __graft_entry__ as g; g.build()"])
     if rc:
         return rc, out
+    rc, out = _run([PY, "-m", "frankentorch_b200.conformance.source_scan"])
+    if rc:
+        return rc, out
+    rc, out = _run(["sh", "hooks/pre-commit", "--self-test"])
+    if rc:
+        return rc, out
     return _run([PY, "-m", "pytest", "-q", "tests/test_metamorphic.py", "-k", "kernels or spin or multicast or "
                  "placeholders or closed_call"])
 

@@ -45,6 +45,31 @@ def set_enabled(flag: bool) -> None:
     _enabled = bool(flag)
 
 
+def is_enabled() -> bool:
+    return _enabled
+
+
+def clear() -> None:
+    """Drop every parked buffer of this thread (the counters of hits and misses are kept)."""
+    st = _state()
+    st.free.clear()
+    st.stats.parked = 0
+    st.stats.parked_bytes = 0
+
+
+def build_overwritten(n: int, fill) -> torch.Tensor:
+    """A buffer of ``n`` f64 elements that ``fill(buf)`` writes completely (ft-core/src/buffer_pool.rs:276).
+
+    A parked buffer arrives holding its previous user's values, a fresh one holds zeros: ``fill`` must write every
+    element before reading it, so a kernel using this carries a test that parks a poisoned buffer and compares bit
+    patterns with the unpooled result."""
+    buf = try_take_exact(n)
+    if buf is None:
+        buf = torch.zeros(n, dtype=torch.float64)
+    fill(buf)
+    return buf
+
+
 def try_take_exact(n: int):
     st = _state()
     if not _enabled or n * 8 < MIN_POOLED_BYTES:

@@ -124,3 +124,105 @@ def test_conformance_harness_library_entry_points(tmp_path):
     pb = H.run_packet_e2e_microbench(cfg, 1, "FT-P2C-003", tmp_dir=str(tmp_path))
     assert pb.iterations == 1 and pb.p50_ns > 0
     assert H.mode_label("Strict") == "strict" and H.now_unix_ms() > 1_600_000_000_000
+
+
+def test_source_scanner_rules_and_the_pre_commit_gate(tmp_path):
+    """The repository passes its own scanner, every rule fires on a planted sample, and the hook's summary parsing
+    passes its self-test (ft-conformance/tests/smoke.rs source scan; hooks/pre-commit)."""
+    import os
+    import subprocess
+    import sys
+    from frankentorch_b200.conformance import source_scan as S
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    n, findings = S.scan_paths([os.path.join(root, p) for p in ("frankentorch_b200", "tests", "benchmarks", "bench.py", "__graft_entry__.py")])
+    assert n > 100 and [f.render() for f in findings if f.severity == S.CRITICAL] == []
+    batch = "cuda" + "Memcpy" + "Batch" + "Async"
+    mc = "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes." + "multicast" + "::cluster"
+    cu = tmp_path / "k.cu"
+    cu.write_text("\n".join([
+        "__global__ void spin(int* f) { while (true) { if (*f) break; } }",
+        "__global__ void ok(int* f) { long long t0 = clock64(); while (true) { if (*f) break; if (clock64() - t0 > 100) break; } }",
+        "__global__ void t() { __trap(); }",
+        "// while (true) in a comment is not code",
+        "__global__ void a() { assert(0); }",
+        f"void h() {{ {batch}(0, 0, 0, 0, 0, 0, 0, 0); }}",
+        f'asm volatile("{mc} [%0], [%1, {{%2, %3}}], [%4], %5;");',
+        'asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.' + "multicast" + '::cluster.b64 [%0], %1;");',
+    ]))
+    py = tmp_path / "m.py"
+    py.write_text("\n".join([
+        "import os, pickle",
+        "def f(x):",
+        "    return eval(x)",
+        "def g(p):",
+        "    return pickle.load(open(p, 'rb'))",
+        "def h():",
+        "    os.system('ls')",
+        "def later():",
+        "    raise NotImplementedError",
+        "class Base:",
+        "    def forward(self, x):",
+        "        raise NotImplementedError",
+        "# TODO finish",
+        "try:",
+        "    pass",
+        "except:",
+        "    pass",
+        "try:",
+        "    pass",
+        "except ValueError: pass",
+        "print('debug')",
+        "s = 'eval(x) inside a string is data'  # and exec( in a comment is not code",
+        "import subprocess; subprocess.run('x', shell=True)",
+        "subprocess.run(['pk' 'ill', '-f', 'python'])",
+        "subprocess.run(['" + "pk" + "ill', '-f', 'python'])",
+    ]))
+    n, f = S.scan_paths([str(tmp_path)])
+    assert n == 2
+    by_rule = {}
+    for x in f:
+        by_rule.setdefault(x.rule, []).append((os.path.basename(x.path), x.line))
+    assert by_rule["spin loop without a bound"] == [("k.cu", 1)]
+    assert by_rule["device-side trap"] == [("k.cu", 3), ("k.cu", 5)]
+    assert by_rule["batched memcpy entry point"] == [("k.cu", 6)]
+    assert by_rule["bulk / TMA load with cluster multicast"] == [("k.cu", 7)]          # the tcgen05.commit form on line 8 is allowed
+    assert by_rule["dynamic code execution"] == [("m.py", 3)]
+    assert by_rule["pickle loading"] == [("m.py", 5)]
+    assert by_rule["shell command execution"] == [("m.py", 7), ("m.py", 23)]
+    assert by_rule["placeholder in production code"] == [("m.py", 9)]                   # the abstract method on line 12 is allowed
+    assert by_rule["unfinished-work marker"] == [("m.py", 13)]
+    assert by_rule["bare except"] == [("m.py", 16)]
+    assert by_rule["exception swallowed without a reason"] == [("m.py", 20)]
+    assert by_rule["print in a library module"] == [("m.py", 21)]
+    assert by_rule["process kill by pattern"] == [("m.py", 25)]
+    assert S.summary(n, f).split("\n") == ["Files: 2", f"Critical: {sum(1 for x in f if x.severity == S.CRITICAL)}",
+                                            f"Warning: {sum(1 for x in f if x.severity == S.WARNING)}"]
+    assert S.main([str(tmp_path), "--quiet"]) == 1 and S.main([os.path.join(root, "bench.py"), "--quiet"]) == 0
+    r = subprocess.run(["sh", os.path.join(root, "hooks", "pre-commit"), "--self-test"], capture_output=True, text=True)
+    assert r.returncode == 0 and "self-test passed" in r.stdout and "FAIL" not in r.stdout
+
+
+def test_buffer_pool_build_overwritten_with_a_poisoned_parked_buffer():
+    from frankentorch_b200.core import buffer_pool as P
+    import torch
+    P.clear()
+    assert P.is_enabled()
+    n = 64 * 1024                     # 512 KiB of f64: above the pooling threshold
+    poison = torch.full((n,), float("nan"), dtype=torch.float64)
+    assert P.recycle(poison)
+    src = torch.arange(n, dtype=torch.float64)
+    hits0 = P.stats().hits
+    pooled = P.build_overwritten(n, lambda b: b.copy_(src * 0.5))
+    assert P.stats().hits == hits0 + 1 and pooled.data_ptr() == poison.data_ptr()          # the parked buffer was reused
+    fresh = torch.zeros(n, dtype=torch.float64).copy_(src * 0.5)
+    assert torch.equal(pooled.view(torch.int64), fresh.view(torch.int64))                  # bit patterns, no stale NaN
+    cold = P.build_overwritten(n, lambda b: b[: n // 2].fill_(1.0))                        # a partial fill on a cold pool shows zeros
+    assert float(cold[n // 2:].abs().sum()) == 0.0
+    P.set_enabled(False)
+    try:
+        assert not P.is_enabled() and not P.recycle(torch.zeros(n, dtype=torch.float64)) and P.try_take_exact(n) is None
+    finally:
+        P.set_enabled(True)
+    assert P.recycle(torch.zeros(n, dtype=torch.float64)) and P.stats().parked == 1
+    P.clear()
+    assert P.stats().parked == 0 and P.stats().parked_bytes == 0 and P.try_take_exact(n) is None
