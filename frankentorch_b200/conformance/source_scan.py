@@ -33,7 +33,7 @@ from typing import Iterable, List, Optional, Sequence, Tuple
 CRITICAL, WARNING = "critical", "warning"
 _CUDA_EXT = (".cu", ".cuh")
 _PY_EXT = (".py",)
-_SKIP_DIRS = {".git", "__pycache__", "build", "gpurun_out", "_work", "baseline", "lib"}
+_SKIP_DIRS = {".git", "__pycache__", "build", "baseline", "lib"}       # plus the directories .gitignore names
 
 # Names are assembled from pieces so that this file does not itself contain what it looks for.
 _BATCH_COPY = [p + "Batch" + "Async" for p in ("cuda" + "Memcpy", "cuda" + "Memcpy3D", "cu" + "Memcpy", "cu" + "Memcpy3D")]
@@ -173,12 +173,27 @@ def scan_text(path: str, text: str) -> List[Finding]:
     return sorted(out, key=lambda x: (x.path, x.line, x.rule))
 
 
+def _ignored_dirs(start: str) -> set:
+    """Directory names that the nearest ``.gitignore`` above ``start`` lists (``name/`` entries): scratch space."""
+    d = os.path.abspath(start if os.path.isdir(start) else os.path.dirname(start))
+    while True:
+        gi = os.path.join(d, ".gitignore")
+        if os.path.isfile(gi):
+            with open(gi) as fh:
+                return {ln.strip().strip("/") for ln in fh if ln.strip().endswith("/") and "*" not in ln}
+        up = os.path.dirname(d)
+        if up == d:
+            return set()
+        d = up
+
+
 def _walk(root: str) -> Iterable[str]:
     if os.path.isfile(root):
         yield root
         return
+    skip = _SKIP_DIRS | _ignored_dirs(root)
     for d, dirs, files in os.walk(root):
-        dirs[:] = sorted(x for x in dirs if x not in _SKIP_DIRS)
+        dirs[:] = sorted(x for x in dirs if x not in skip)
         for name in sorted(files):
             if name.endswith(_PY_EXT + _CUDA_EXT + (".cpp", ".h", ".sh")):
                 yield os.path.join(d, name)
