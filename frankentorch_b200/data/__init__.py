@@ -74,6 +74,15 @@ class DataItem:
         self.tensors[name] = (list(values), tuple(shape))
         return self
 
+    @staticmethod
+    def input_target(input_values, input_shape, target_values, target_shape) -> "DataItem":
+        """One sample with an ``input`` and a ``target`` tensor (ft-data/src/lib.rs:57)."""
+        return DataItem().insert("input", input_values, input_shape).insert("target", target_values, target_shape)
+
+    @staticmethod
+    def single(name: str, values, shape) -> "DataItem":
+        return DataItem().insert(name, values, shape)
+
 
 class Dataset:
     def __len__(self) -> int:
@@ -88,6 +97,32 @@ class Dataset:
 
 class TensorDataset(Dataset):
     """Columns of equal leading length; collation gathers rows of the pre-packed columns."""
+
+    @staticmethod
+    def from_items(items: Sequence[DataItem]) -> "TensorDataset":
+        """Columnar dataset from samples that all carry the same named tensors with the same shapes."""
+        if not items:
+            raise DataError("TensorDataset needs at least one item")
+        names = list(items[0].tensors)
+        cols = {}
+        for n in names:
+            shape = items[0].tensors[n][1]
+            rows = []
+            for k, it in enumerate(items):
+                if n not in it.tensors or it.tensors[n][1] != shape:
+                    raise DataError(f"item {k}: tensor '{n}' is missing or its shape differs from item 0")
+                rows.append(it.tensors[n][0])
+            cols[n] = torch.tensor(rows, dtype=torch.float64).reshape((len(items),) + tuple(shape))
+        return TensorDataset(cols)
+
+    @staticmethod
+    def from_inputs_targets(inputs: Sequence[Tuple[Sequence[float], Sequence[int]]],
+                            targets: Sequence[Tuple[Sequence[float], Sequence[int]]]) -> "TensorDataset":
+        """Parallel lists of ``(values, shape)``: pair ``k`` becomes sample ``k`` with tensors ``input`` and ``target``
+        (ft-data/src/lib.rs:136)."""
+        if len(inputs) != len(targets):
+            raise DataError("inputs and targets must have same length")
+        return TensorDataset.from_items([DataItem.input_target(iv, ish, tv, tsh) for (iv, ish), (tv, tsh) in zip(inputs, targets)])
 
     def __init__(self, columns: Dict[str, torch.Tensor]):
         if not columns:

@@ -539,3 +539,20 @@ def test_runtime_durability_envelope_updates_and_integration_hooks():
     assert "Durability=1" in lines[1] and "Policy=1" in lines[1] and "scrub ok artifact=ckpt-1" in lines[2]
     bare = render_ledger_panel(rt.ledger, Style(border="none", width=40), last=5)
     assert not bare.startswith("+") and all(len(l) <= 40 for l in bare.split("\n"))
+
+
+def test_dataset_constructors_from_items_and_input_target_pairs():
+    from frankentorch_b200.data import DataError, DataItem, TensorDataset
+    ds = TensorDataset.from_inputs_targets([([1., 2.], [2]), ([3., 4.], [2]), ([5., 6.], [2])], [([0.], [1]), ([1.], [1]), ([0.], [1])])
+    assert len(ds) == 3 and ds.get(1).tensors == {"input": ([3.0, 4.0], (2,)), "target": ([1.0], (1,))}
+    got = ds.collate_indices([2, 0])
+    assert got["input"].tolist() == [[5.0, 6.0], [1.0, 2.0]] and got["target"].tolist() == [[0.0], [0.0]]
+    it = DataItem.input_target([1., 2., 3., 4.], [2, 2], [7.], [1])
+    assert list(it.tensors) == ["input", "target"] and it.tensors["input"][1] == (2, 2)
+    assert DataItem.single("x", [1., 2.], [2]).tensors == {"x": ([1.0, 2.0], (2,))}
+    with pytest.raises(DataError):
+        TensorDataset.from_inputs_targets([([1.], [1])], [])
+    with pytest.raises(DataError):
+        TensorDataset.from_items([DataItem.single("x", [1.], [1]), DataItem.single("x", [1., 2.], [2])])
+    with pytest.raises(DataError):
+        DataItem.input_target([1., 2.], [3], [0.], [1])
