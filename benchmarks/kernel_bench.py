@@ -182,7 +182,9 @@ def _row_cases(rows, cols):
     hyper = torch.tensor([1e-3, 0.1, 0.001, 1.0], device="cuda")
     ss, nrm = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
     xf = f32(rows, cols)
+    logits = bf(rows, V, scale=1.0)
     cases = {
+        "cross_entropy": (lambda: ops.cross_entropy_fwd_bwd(logits, ids, 50257, 1.0 / rows, inplace=True), 4 * rows * V),
         "layernorm_fwd": (lambda: ops.layernorm_fwd(x, g, b), 4 * n),
         "layernorm_bwd": (lambda: ops.layernorm_bwd(dy, x, g, mean, rstd, dx_add=dy), 8 * n),
         "rmsnorm_fwd": (lambda: ops.rmsnorm_fwd(x, g), 4 * n),

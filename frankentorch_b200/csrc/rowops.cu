@@ -497,9 +497,24 @@ softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __r
 }
 
 // ----------------------------------------------------------------------------- cross entropy
-// One CTA per row.  The bf16 row is staged in shared memory when it fits, so the
-// logits are read from HBM once and the gradient is written once (in place allowed).
+// One CTA per row.  The bf16 row is staged in shared memory when it fits, so the logits are read from HBM once
+// and the gradient is written once (in place allowed).  The kernel is bound by instruction issue and by the
+// exponential unit (two exponentials per logit), so both walks over the row are written for a short instruction
+// stream: bf16 pairs are widened with one shift / mask each, every exponential is one FFMA into ex2.approx
+// (log2(e) folded into the operands), and the vectors past the vocabulary are not visited by the first walk.
 constexpr int CE_THREADS = 512;
+constexpr float CE_LOG2E = 1.4426950408889634f;
+__device__ __forceinline__ float ce_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void ce_widen(const uint4& u, float* f) {
+  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+}
 __global__ void __launch_bounds__(CE_THREADS)
 cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
                      float* __restrict__ losses, __nv_bfloat16* __restrict__ dlogits, int vocab,
@@ -510,73 +525,79 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* 
   const __nv_bfloat16* xr = logits + row * ld;
   const uint4* xv = reinterpret_cast<const uint4*>(xr);
   const int nvec = ld >> 3;
+  const int nfull = vocab >> 3;                 // vectors that lie wholly inside the vocabulary
+  const int nvalid = (vocab + 7) >> 3;          // vectors that hold at least one logit
   const long long tgt = targets[row];
-  float m = -INFINITY;
-  // four 16-byte loads in flight per thread: a 100 KB row is otherwise fetched 8 KB at a time and
-  // the kernel sits at memory latency instead of bandwidth
-  for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * CE_THREADS) {
+  // Online softmax statistics while the row streams in: each thread keeps a running maximum mt (in units of
+  // log2, i.e. x * log2(e)) and the sum st of 2^(x' - mt) over its own vectors, rescaled when the maximum moves,
+  // so the exponentials of the first walk run under the latency of the loads.  Four 16-byte loads are in flight
+  // per thread: a 100 KB row is otherwise fetched 8 KB at a time and the kernel sits at memory latency.
+  float mt = -INFINITY, st = 0.f;
+  for (int v0 = threadIdx.x; v0 < nvalid; v0 += 4 * CE_THREADS) {
     uint4 u[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int v = v0 + k * CE_THREADS;
-      u[k] = v < nvec ? xv[v] : make_uint4(0u, 0u, 0u, 0u);
+      if (v < nvalid) u[k] = xv[v];
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int v = v0 + k * CE_THREADS;
-      if (v >= nvec) break;
+      if (v >= nvalid) break;
       if (use_smem) ce_smem[v] = u[k];
       float f[8];
-      unpack8(u[k], f);
-      if (v * 8 + 8 <= vocab) {
-        m = fmaxf(m, fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7]))));
-      } else {
+      ce_widen(u[k], f);
+      if (v >= nfull) {             // the one vector that straddles the end of the vocabulary: padding never counts
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          if (v * 8 + i < vocab) m = fmaxf(m, f[i]);
+          if (v * 8 + i >= vocab) f[i] = -INFINITY;
       }
+      const float vm = fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
+      const float mn = fmaxf(mt, vm * CE_LOG2E);
+      const float sc = (mt == mn) ? 1.f : ce_ex2(mt - mn);      // mt = -inf on the first vector: 2^-inf = 0
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        a0 += ce_ex2(fmaf(f[i], CE_LOG2E, -mn));
+        a1 += ce_ex2(fmaf(f[i + 1], CE_LOG2E, -mn));
+      }
+      st = fmaf(st, sc, a0 + a1);
+      mt = mn;
     }
   }
-  m = block_reduce(m, red, true);
+  const float m2 = block_reduce(mt, red, true);                  // row maximum times log2(e)
+  // per-thread sums are brought to the common maximum and added in the fixed order of the block reduction
+  const float s = block_reduce(mt == -INFINITY ? 0.f : st * ce_ex2(mt - m2), red, false);
   const uint4* src = use_smem ? ce_smem : xv;
-  float s = 0.f;
-  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
-    float f[8];
-    unpack8(src[v], f);
-    if (v * 8 + 8 <= vocab) {       // whole vector inside the vocabulary: no per-element guard
-#pragma unroll
-      for (int i = 0; i < 8; ++i) s += __expf(f[i] - m);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (v * 8 + i < vocab) s += __expf(f[i] - m);
-    }
-  }
-  s = block_reduce(s, red, false);
-  const float lse = m + __logf(s);
+  const bool ignore = !(tgt >= 0 && tgt < vocab);
   if (threadIdx.x == 0) {
-    float xt = (tgt >= 0 && tgt < vocab) ? __bfloat162float(xr[tgt]) : 0.f;
-    losses[row] = (tgt >= 0 && tgt < vocab) ? lse - xt : 0.f;
+    const float xt = ignore ? 0.f : __bfloat162float(use_smem ? reinterpret_cast<const __nv_bfloat16*>(ce_smem)[tgt] : xr[tgt]);
+    losses[row] = ignore ? 0.f : (m2 + __log2f(s)) * 0.6931471805599453f - xt;
   }
   if (dlogits) {
     __syncthreads();  // the target logit was read before any in-place write
-    const float inv = 1.f / s;
-    const bool ignore = !(tgt >= 0 && tgt < vocab);
     uint4* ov = reinterpret_cast<uint4*>(dlogits + row * ld);
-    const int vt = ignore ? -1 : (int)(tgt >> 3);     // the vector that holds the target column
+    if (ignore) {
+      for (int v = threadIdx.x; v < nvec; v += CE_THREADS) ov[v] = make_uint4(0u, 0u, 0u, 0u);
+      return;
+    }
+    const float k = grad_scale / s;                 // softmax normalisation and loss scale in one factor
+    const int vt = (int)(tgt >> 3);                 // the vector that holds the target column
     for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+      if (v >= nvalid) {                            // padding columns carry no gradient
+        ov[v] = make_uint4(0u, 0u, 0u, 0u);
+        continue;
+      }
       float f[8];
-      unpack8(src[v], f);
-      if (!ignore && v != vt && v * 8 + 8 <= vocab) {
+      ce_widen(src[v], f);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = (__expf(f[i] - m) * inv - 0.f) * grad_scale;
-      } else {
+      for (int i = 0; i < 8; ++i) f[i] = ce_ex2(fmaf(f[i], CE_LOG2E, -m2)) * k;
+      if (v == vt || v >= nfull) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int c = v * 8 + i;
-          float g = 0.f;
-          if (c < vocab && !ignore) g = (__expf(f[i] - m) * inv - (c == tgt ? 1.f : 0.f)) * grad_scale;
-          f[i] = g;
+          if (c == tgt) f[i] -= grad_scale;
+          if (c >= vocab) f[i] = 0.f;
         }
       }
       ov[v] = pack8(f);
@@ -795,7 +816,8 @@ extern "C" int ftk_cross_entropy_fwd_bwd(const void* logits, const long long* ta
                                          float grad_scale, void* stream) {
   if (ld % 8 || vocab > ld || rows <= 0) return -2;
   const size_t bytes = (size_t)ld * 2;
-  const int use_smem = bytes <= 200 * 1024;
+  static const int smem_mode = [] { const char* e = getenv("FT_CE_SMEM"); return e ? atoi(e) : 1; }();
+  const int use_smem = smem_mode && bytes <= 200 * 1024;
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(cross_entropy_kernel,

@@ -96,9 +96,17 @@ def test_cross_entropy(cuda_device, rows, vocab, ld):
     ref.mean().backward()
     losses, dl = k.cross_entropy_fwd_bwd(logits, tgt, vocab, 1.0 / rows, inplace=False)
     k.check_status()
-    assert (losses - ref).abs().max().item() < 2e-2
-    assert (dl.float()[:, :vocab] - lf.grad).abs().max().item() < 2e-3
+    assert (losses - ref).abs().max().item() < 2e-4          # fp32 statistics over bf16 logits
+    # the gradient is rounded to bf16 once: 2^-9 relative, i.e. at most 2^-8 of the loss scale with margin
+    err = (dl.float()[:, :vocab] - lf.grad).abs()
+    assert (err <= lf.grad.abs() * 2.0 ** -8 + 1e-9).all(), err.max().item()
     assert dl[:, vocab:].abs().sum().item() == 0
+    # rows whose target is out of range (the ignore convention) give no loss and no gradient
+    tgt2 = tgt.clone()
+    tgt2[0], tgt2[-1] = -100, vocab
+    l2, d2 = k.cross_entropy_fwd_bwd(logits, tgt2, vocab, 1.0 / rows, inplace=False)
+    assert l2[0].item() == 0 and l2[-1].item() == 0 and d2[0].abs().sum().item() == 0 and d2[-1].abs().sum().item() == 0
+    assert torch.equal(d2[1:-1], dl[1:-1]) and torch.equal(l2[1:-1], losses[1:-1])
     m = k.reduce_mean(losses)
     assert abs(m.item() - losses.double().mean().item()) < 1e-4
 
