@@ -816,8 +816,7 @@ extern "C" int ftk_cross_entropy_fwd_bwd(const void* logits, const long long* ta
                                          float grad_scale, void* stream) {
   if (ld % 8 || vocab > ld || rows <= 0) return -2;
   const size_t bytes = (size_t)ld * 2;
-  static const int smem_mode = [] { const char* e = getenv("FT_CE_SMEM"); return e ? atoi(e) : 1; }();
-  const int use_smem = smem_mode && bytes <= 200 * 1024;
+  const int use_smem = bytes <= 200 * 1024;     // longer rows are re-read from L2 by the second walk
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(cross_entropy_kernel,
