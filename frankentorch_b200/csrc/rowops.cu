@@ -502,7 +502,7 @@ softmax_bwd_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __r
 // exponential unit (two exponentials per logit), so both walks over the row are written for a short instruction
 // stream: bf16 pairs are widened with one shift / mask each, every exponential is one FFMA into ex2.approx
 // (log2(e) folded into the operands), and the vectors past the vocabulary are not visited by the first walk.
-constexpr int CE_THREADS = 512;
+constexpr int CE_THREADS = 1024;
 constexpr float CE_LOG2E = 1.4426950408889634f;
 __device__ __forceinline__ float ce_ex2(float x) {
   float y;
@@ -515,7 +515,7 @@ __device__ __forceinline__ void ce_widen(const uint4& u, float* f) {
   f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
   f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
 }
-__global__ void __launch_bounds__(CE_THREADS)
+__global__ void __launch_bounds__(CE_THREADS, 2)
 cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
                      float* __restrict__ losses, __nv_bfloat16* __restrict__ dlogits, int vocab,
                      int ld, float grad_scale, int use_smem) {
@@ -530,39 +530,75 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const long long* 
   const long long tgt = targets[row];
   // Online softmax statistics while the row streams in: each thread keeps a running maximum mt (in units of
   // log2, i.e. x * log2(e)) and the sum st of 2^(x' - mt) over its own vectors, rescaled when the maximum moves,
-  // so the exponentials of the first walk run under the latency of the loads.  Four 16-byte loads are in flight
-  // per thread: a 100 KB row is otherwise fetched 8 KB at a time and the kernel sits at memory latency.
+  // so the exponentials of the first walk run under the latency of the loads.
   float mt = -INFINITY, st = 0.f;
-  for (int v0 = threadIdx.x; v0 < nvalid; v0 += 4 * CE_THREADS) {
-    uint4 u[4];
+  auto absorb = [&](const uint4& u, int v) {
+    float f[8];
+    ce_widen(u, f);
+    if (v >= nfull) {               // the one vector that straddles the end of the vocabulary: padding never counts
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int v = v0 + k * CE_THREADS;
-      if (v < nvalid) u[k] = xv[v];
+      for (int i = 0; i < 8; ++i)
+        if (v * 8 + i >= vocab) f[i] = -INFINITY;
     }
+    const float vm = fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
+    const float mn = fmaxf(mt, vm * CE_LOG2E);
+    const float sc = (mt == mn) ? 1.f : ce_ex2(mt - mn);        // mt = -inf on the first vector: 2^-inf = 0
+    float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int v = v0 + k * CE_THREADS;
-      if (v >= nvalid) break;
-      if (use_smem) ce_smem[v] = u[k];
-      float f[8];
-      ce_widen(u[k], f);
-      if (v >= nfull) {             // the one vector that straddles the end of the vocabulary: padding never counts
+    for (int i = 0; i < 8; i += 2) {
+      a0 += ce_ex2(fmaf(f[i], CE_LOG2E, -mn));
+      a1 += ce_ex2(fmaf(f[i + 1], CE_LOG2E, -mn));
+    }
+    st = fmaf(st, sc, a0 + a1);
+    mt = mn;
+  };
+  if (use_smem) {
+    // The whole row is requested at once with 16-byte asynchronous copies straight into shared memory (no
+    // registers hold data in flight), committed in groups of four per thread; each thread then waits for its
+    // own groups in order and absorbs the vectors it copied itself, so no CTA barrier separates copy and use.
+    const uint32_t sbase = smem_u32(ce_smem);
+    int groups = 0;
+    for (int v0 = threadIdx.x; v0 < nvalid; v0 += 4 * CE_THREADS) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (v * 8 + i >= vocab) f[i] = -INFINITY;
+      for (int k = 0; k < 4; ++k) {
+        const int v = v0 + k * CE_THREADS;
+        if (v < nvalid)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + 16u * v), "l"(xv + v) : "memory");
       }
-      const float vm = fmaxf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])));
-      const float mn = fmaxf(mt, vm * CE_LOG2E);
-      const float sc = (mt == mn) ? 1.f : ce_ex2(mt - mn);      // mt = -inf on the first vector: 2^-inf = 0
-      float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; i += 2) {
-        a0 += ce_ex2(fmaf(f[i], CE_LOG2E, -mn));
-        a1 += ce_ex2(fmaf(f[i + 1], CE_LOG2E, -mn));
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      ++groups;
+    }
+    int g = 0;
+    for (int v0 = threadIdx.x; v0 < nvalid; v0 += 4 * CE_THREADS, ++g) {
+      switch (groups - 1 - g) {     // groups still allowed to be in flight
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
       }
-      st = fmaf(st, sc, a0 + a1);
-      mt = mn;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int v = v0 + k * CE_THREADS;
+        if (v < nvalid) absorb(ce_smem[v], v);
+      }
+    }
+  } else {
+    // rows too long for shared memory: four 16-byte loads in flight per thread, second walk re-reads from L2
+    for (int v0 = threadIdx.x; v0 < nvalid; v0 += 4 * CE_THREADS) {
+      uint4 u[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int v = v0 + k * CE_THREADS;
+        if (v < nvalid) u[k] = xv[v];
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int v = v0 + k * CE_THREADS;
+        if (v < nvalid) absorb(u[k], v);
+      }
     }
   }
   const float m2 = block_reduce(mt, red, true);                  // row maximum times log2(e)
