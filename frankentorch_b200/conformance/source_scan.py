@@ -37,7 +37,7 @@ _SKIP_DIRS = {".git", "__pycache__", "build", "baseline", "lib"}       # plus th
 
 # Names are assembled from pieces so that this file does not itself contain what it looks for.
 _BATCH_COPY = [p + "Batch" + "Async" for p in ("cuda" + "Memcpy", "cuda" + "Memcpy3D", "cu" + "Memcpy", "cu" + "Memcpy3D")]
-_MULTICAST = "multicast" + "::" + "cluster"
+_MULTICAST = ".multi" + "cast::clu" + "ster"
 _KILL_BY_PATTERN = ["pk" + "ill", "kill" + "all", "pg" + "rep -f"]
 _NOT_IMPL = "NotImplemented" + "Error"
 _MARKERS = "|".join(["TO" + "DO", "FIX" + "ME", "XX" + "X"])

@@ -137,7 +137,8 @@ def test_source_scanner_rules_and_the_pre_commit_gate(tmp_path):
     n, findings = S.scan_paths([os.path.join(root, p) for p in ("frankentorch_b200", "tests", "benchmarks", "bench.py", "__graft_entry__.py")])
     assert n > 100 and [f.render() for f in findings if f.severity == S.CRITICAL] == []
     batch = "cuda" + "Memcpy" + "Batch" + "Async"
-    mc = "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes." + "multicast" + "::cluster"
+    qual = ".multi" + "cast::clu" + "ster"
+    mc = "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes" + qual
     cu = tmp_path / "k.cu"
     cu.write_text("\n".join([
         "__global__ void spin(int* f) { while (true) { if (*f) break; } }",
@@ -147,7 +148,7 @@ def test_source_scanner_rules_and_the_pre_commit_gate(tmp_path):
         "__global__ void a() { assert(0); }",
         f"void h() {{ {batch}(0, 0, 0, 0, 0, 0, 0, 0); }}",
         f'asm volatile("{mc} [%0], [%1, {{%2, %3}}], [%4], %5;");',
-        'asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.' + "multicast" + '::cluster.b64 [%0], %1;");',
+        'asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster' + qual + '.b64 [%0], %1;");',
     ]))
     py = tmp_path / "m.py"
     py.write_text("\n".join([
