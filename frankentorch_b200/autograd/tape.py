@@ -15,7 +15,7 @@ golden ft_autograd__tests__tensor_scheduler_telemetry_golden.snap.
 from __future__ import annotations
 
 import ctypes as C
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -88,6 +88,17 @@ class BackwardOptions:
     policy: str = ReentrantPolicy.StrictFail
     detect_anomaly: bool = False
 
+    # builder spelling of the reference (ft-autograd/src/lib.rs BackwardOptions::with_*): each returns a copy
+    def with_retain_graph(self, flag: bool = True) -> "BackwardOptions":
+        return replace(self, retain_graph=bool(flag))
+
+    def with_create_graph(self, flag: bool = True) -> "BackwardOptions":
+        """``create_graph`` implies that the graph is kept."""
+        return replace(self, create_graph=bool(flag), retain_graph=self.retain_graph or bool(flag))
+
+    def with_detect_anomaly(self, flag: bool = True) -> "BackwardOptions":
+        return replace(self, detect_anomaly=bool(flag))
+
     @staticmethod
     def strict_default() -> "BackwardOptions":
         return BackwardOptions(policy=ReentrantPolicy.StrictFail, max_reentrant_depth=0)
@@ -157,6 +168,52 @@ class TensorBackwardReport:
 
     def gradient_node(self, node: int) -> Optional[int]:
         return self.gradient_nodes.get(int(node))
+
+    def gradient_value(self, node: int) -> Optional["GradientValue"]:
+        """The gradient of ``node`` in the form it was produced: dense, or row-sparse for a table read through
+        ``index_select_sparse`` (ft-autograd/src/lib.rs:1113 ``GradientValue``)."""
+        node = int(node)
+        if node in self.sparse_gradients:
+            return GradientValue(sparse=self.sparse_gradients[node])
+        g = self.gradients.get(node)
+        return None if g is None else GradientValue(dense=g)
+
+
+class GradientValue:
+    """A gradient that is either a dense tensor or a row-sparse one."""
+    __slots__ = ("_dense", "_sparse")
+
+    def __init__(self, dense: Optional[torch.Tensor] = None, sparse: Optional["RowSparseGradient"] = None):
+        if (dense is None) == (sparse is None):
+            raise ValueError("exactly one of dense / sparse")
+        self._dense, self._sparse = dense, sparse
+
+    def is_sparse(self) -> bool:
+        return self._sparse is not None
+
+    def as_dense(self) -> Optional[torch.Tensor]:
+        return self._dense
+
+    def as_sparse(self):
+        """The COO form of a sparse gradient (``None`` for a dense one)."""
+        return None if self._sparse is None else self._sparse.to_coo()
+
+    def to_dense(self, numel: Optional[int] = None) -> torch.Tensor:
+        """Dense tensor; with ``numel`` a flat tensor cut or zero-padded to that length."""
+        d = self._dense if self._dense is not None else self._sparse.to_dense()
+        if numel is None:
+            return d
+        flat = d.reshape(-1)
+        if flat.numel() >= numel:
+            return flat[:numel].clone()
+        return torch.cat([flat, torch.zeros(numel - flat.numel(), dtype=flat.dtype, device=flat.device)])
+
+    def scaled_clone(self, factor: float) -> "GradientValue":
+        """A copy multiplied by ``factor``; a sparse gradient stays sparse."""
+        if self._dense is not None:
+            return GradientValue(dense=self._dense * factor)
+        s = self._sparse
+        return GradientValue(sparse=RowSparseGradient(s.rows.clone(), s.values * factor, s.shape))
 
 
 class RowSparseGradient:

@@ -556,3 +556,31 @@ def test_dataset_constructors_from_items_and_input_target_pairs():
         TensorDataset.from_items([DataItem.single("x", [1.], [1]), DataItem.single("x", [1., 2.], [2])])
     with pytest.raises(DataError):
         DataItem.input_target([1., 2.], [3], [0.], [1])
+
+
+def test_backward_option_builders_and_gradient_values():
+    from frankentorch_b200.autograd.tape import BackwardOptions, GradientValue
+    o = BackwardOptions.strict_default()
+    o2 = o.with_create_graph(True)
+    assert o2.create_graph and o2.retain_graph and not o.create_graph and not o.retain_graph      # copies, not mutation
+    assert o.with_retain_graph().retain_graph and o.with_detect_anomaly().detect_anomaly
+    s = FrankenTorchSession(ledger_dispatch=False)
+    table = s.tensor_variable([float(i) for i in range(12)], [4, 3], True)
+    idx = s.tensor_variable([2.0, 0.0, 2.0], [3])
+    w = s.tensor_variable([1.0, 2.0, 3.0], [3], True)
+    picked = s.tensor_index_select_sparse(table, idx)
+    loss = s.tensor_sum(s.tensor_mul(picked, w))
+    rep = s.tensor_backward_with_options(loss, BackwardOptions.strict_default().with_retain_graph())
+    gv = rep.gradient_value(table)
+    assert gv.is_sparse() and gv.as_dense() is None
+    coo = gv.as_sparse()
+    assert coo.indices.tolist() == [[0, 2]] and coo.values.tolist() == [[1.0, 2.0, 3.0], [2.0, 4.0, 6.0]]
+    assert gv.to_dense().tolist() == [[1.0, 2.0, 3.0], [0.0, 0.0, 0.0], [2.0, 4.0, 6.0], [0.0, 0.0, 0.0]]
+    assert gv.to_dense(5).tolist() == [1.0, 2.0, 3.0, 0.0, 0.0] and gv.to_dense(14).numel() == 14
+    half = gv.scaled_clone(0.5)
+    assert half.is_sparse() and half.as_sparse().values.tolist() == [[0.5, 1.0, 1.5], [1.0, 2.0, 3.0]]
+    gw = rep.gradient_value(w)
+    assert not gw.is_sparse() and gw.as_sparse() is None and gw.as_dense().tolist() == [12.0, 15.0, 18.0]
+    assert gw.scaled_clone(2.0).as_dense().tolist() == [24.0, 30.0, 36.0] and rep.gradient_value(idx) is None
+    with pytest.raises(ValueError):
+        GradientValue()
