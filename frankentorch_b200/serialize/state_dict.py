@@ -107,6 +107,8 @@ def load_state_dict_from_bytes(data: bytes) -> Dict[str, torch.Tensor]:
         off += 8 * ndim
         numel = 1
         for d in dims:
+            if d > (1 << 62):           # a zero extent elsewhere would hide this one from the volume check
+                raise SerializeError("ShapeOverflow", f"extent {d} is not representable")
             numel *= d
             if numel > (1 << 62):
                 raise SerializeError("ShapeOverflow", "shape volume overflows")

@@ -584,3 +584,15 @@ def test_backward_option_builders_and_gradient_values():
     assert gw.scaled_clone(2.0).as_dense().tolist() == [24.0, 30.0, 36.0] and rep.gradient_value(idx) is None
     with pytest.raises(ValueError):
         GradientValue()
+
+
+def test_ftsv_rejects_an_extent_beyond_the_index_range_even_next_to_a_zero_extent():
+    """A corrupted shape such as [0, 2^63] has volume 0, so the volume check alone lets it through to reshape."""
+    import struct
+    blob = bytearray(S.state_dict_to_bytes({"w": torch.zeros(0, 3)}))
+    needle = struct.pack("<QQ", 0, 3)
+    at = bytes(blob).index(needle)
+    blob[at + 8: at + 16] = struct.pack("<Q", 1 << 63)
+    with pytest.raises(S.SerializeError) as e:
+        S.load_state_dict_from_bytes(bytes(blob))
+    assert e.value.kind == "ShapeOverflow"
