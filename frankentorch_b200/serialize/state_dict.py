@@ -105,12 +105,11 @@ def load_state_dict_from_bytes(data: bytes) -> Dict[str, torch.Tensor]:
         need(8 * ndim, "shape dims")
         dims = struct.unpack_from(f"<{ndim}Q", data, off) if ndim else ()
         off += 8 * ndim
-        numel = 1
+        numel, span = 1, 1
         for d in dims:
-            if d > (1 << 62):           # a zero extent elsewhere would hide this one from the volume check
-                raise SerializeError("ShapeOverflow", f"extent {d} is not representable")
             numel *= d
-            if numel > (1 << 62):
+            span *= max(d, 1)           # strides are built from the non-zero extents: a zero extent elsewhere
+            if span > (1 << 62):        # must not hide an extent (or a product of extents) beyond the index range
                 raise SerializeError("ShapeOverflow", "shape volume overflows")
         need(1, "dtype tag")
         tag = data[off]
@@ -264,6 +263,8 @@ def _st_header(data: bytes):
         return json.loads(data[8: 8 + hl]), 8 + hl
     except json.JSONDecodeError as e:
         raise SerializeError("InvalidJson", f"safetensors header is not valid json: {e.msg}")
+    except (UnicodeDecodeError, RecursionError) as e:
+        raise SerializeError("InvalidJson", f"safetensors header is not valid json: {type(e).__name__}")
 
 
 def load_safetensors(path: str) -> Dict[str, torch.Tensor]:
@@ -272,32 +273,54 @@ def load_safetensors(path: str) -> Dict[str, torch.Tensor]:
 
 
 def load_safetensors_from_bytes(data: bytes) -> Dict[str, torch.Tensor]:
+    """Every malformed input ends in a ``SerializeError``: the header must be an object of tensor records with a
+    known dtype, integer offsets inside the file, a shape of non-negative integers whose volume fits the index
+    range, and exactly ``volume * element size`` bytes of data."""
     header, base = _st_header(data)
+    if not isinstance(header, dict):
+        raise SerializeError("InvalidJson", "safetensors header is not an object")
     out = {}
     for k, info in header.items():
         if k == "__metadata__":
             continue
-        if info["dtype"] not in _ST_DTYPE:
-            raise SerializeError("UnsupportedDType", f"{k}: dtype {info['dtype']} is not supported")
-        a, b = info["data_offsets"]
+        if not isinstance(info, dict) or not {"dtype", "shape", "data_offsets"} <= set(info):
+            raise SerializeError("InvalidJson", f"{k}: a tensor record needs dtype, shape and data_offsets")
+        if not isinstance(info["dtype"], str) or info["dtype"] not in _ST_DTYPE:
+            raise SerializeError("UnsupportedDType", f"{k}: dtype {info['dtype']!r} is not supported")
+        offs, shape = info["data_offsets"], info["shape"]
+        if not (isinstance(offs, list) and len(offs) == 2 and all(type(o) is int for o in offs)):
+            raise SerializeError("InvalidJson", f"{k}: data_offsets must be two integers")
+        a, b = offs
         if not (0 <= a <= b <= len(data) - base):
             raise SerializeError("Truncated", f"{k}: data offsets outside the file")
+        if not (isinstance(shape, list) and all(type(d) is int and d >= 0 for d in shape)) or len(shape) > 64:
+            raise SerializeError("InvalidShape", f"{k}: shape must be a list of non-negative integers")
+        numel, span = 1, 1
+        for d in shape:
+            numel *= d
+            span *= max(d, 1)
+            if span > (1 << 62):
+                raise SerializeError("ShapeOverflow", f"{k}: shape volume overflows")
         dt = _ST_DTYPE[info["dtype"]]
+        esize = torch.empty(0, dtype=dt).element_size()
+        if b - a != numel * esize:
+            raise SerializeError("Truncated", f"{k}: {b - a} bytes of data for {numel} elements of {esize} bytes")
         raw = bytearray(data[base + a: base + b])
         if dt == torch.bfloat16:
             t = torch.frombuffer(raw, dtype=torch.int16).view(torch.bfloat16) if raw else torch.empty(0, dtype=dt)
         else:
             t = torch.frombuffer(raw, dtype=dt) if raw else torch.empty(0, dtype=dt)
-        out[k] = t.reshape(info["shape"]).clone()
+        out[k] = t.reshape(shape).clone()
     return out
 
 
 def load_safetensors_metadata(path: str) -> Dict[str, str]:
     with open(path, "rb") as f:
-        head = f.read(8)
-        (hl,) = struct.unpack("<Q", head)
-        header = json.loads(f.read(hl))
-    return dict(header.get("__metadata__", {}))
+        header, _ = _st_header(f.read())
+    meta = header.get("__metadata__", {}) if isinstance(header, dict) else {}
+    if not isinstance(meta, dict):
+        raise SerializeError("InvalidJson", "__metadata__ is not an object")
+    return {str(k): str(v) for k, v in meta.items()}
 
 
 # -------------------------------------------------------------------------------------- ONNX (one Linear)

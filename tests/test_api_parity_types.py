@@ -596,3 +596,10 @@ def test_ftsv_rejects_an_extent_beyond_the_index_range_even_next_to_a_zero_exten
     with pytest.raises(S.SerializeError) as e:
         S.load_state_dict_from_bytes(bytes(blob))
     assert e.value.kind == "ShapeOverflow"
+    # no single extent is out of range, but the strides of [0, 2^40, 2^40] are
+    blob3 = bytearray(S.state_dict_to_bytes({"w": torch.zeros(0, 2, 3)}))
+    at = bytes(blob3).index(struct.pack("<QQQ", 0, 2, 3))
+    blob3[at + 8: at + 24] = struct.pack("<QQ", 1 << 40, 1 << 40)
+    with pytest.raises(S.SerializeError) as e:
+        S.load_state_dict_from_bytes(bytes(blob3))
+    assert e.value.kind == "ShapeOverflow"
