@@ -22,6 +22,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from ._session_factories import _new, _numel
+from .core.dtype import DType
 from ._session_ops import _inplace
 
 
@@ -748,6 +749,243 @@ def tensor_gru(self, input, hx, weights, bidirectional=False, batch_first=False)
     return _recurrent(self, "gru", input, hx, weights, bidirectional, batch_first)
 
 
+# ------------------------------------------------------------------------------------ second batch (parity matrix names)
+def tensor_cross_entropy_label_smoothing(self, logits, target, label_smoothing, reduction="mean"):
+    return tensor_cross_entropy_full(self, logits, target, None, None, reduction, float(label_smoothing))
+
+
+def tensor_cross_entropy_soft(self, logits, probs, reduction="mean"):
+    """Cross-entropy against class probabilities (soft targets)."""
+    return self._apply("cross_entropy_soft", [logits, probs], reduction=reduction)
+
+
+def tensor_triplet_margin_loss_swap(self, anchor, positive, negative, margin=1.0, p=2.0, swap=True, reduction="mean"):
+    """Triplet loss with the distance swap: the negative distance is the smaller of d(a, n) and d(p, n)."""
+    eps = 1e-6
+
+    def dist(a, b):
+        d = self.tensor_add_scalar(self.tensor_sub(a, b), c=eps)
+        return self.tensor_norm_dim(d, p=float(p), dim=-1 % len(self.tensor_shape(a)))
+    dap, dan = dist(anchor, positive), dist(anchor, negative)
+    if swap:
+        dpn = dist(positive, negative)
+        dan = self.tensor_sub(dan, self.tensor_relu(self.tensor_sub(dan, dpn)))          # min(dan, dpn)
+    loss = self.tensor_relu(self.tensor_add_scalar(self.tensor_sub(dap, dan), c=float(margin)))
+    if reduction == "mean":
+        return self.tensor_mean(loss)
+    return self.tensor_sum(loss) if reduction == "sum" else loss
+
+
+def tensor_linalg_solve_triangular(self, a, b, upper=True):
+    return self.tensor_linalg_triangular_solve(a, b, upper=upper)
+
+
+def tensor_unflatten_dim(self, x, dim, sizes):
+    shape = self.tensor_shape(x)
+    dim = dim % len(shape)
+    return self.tensor_reshape(x, shape=tuple(shape[:dim]) + tuple(int(v) for v in sizes) + tuple(shape[dim + 1:]))
+
+
+def tensor_flatten_dims(self, x, start_dim=0, end_dim=-1):
+    return self.tensor_flatten(x, start=start_dim, end=end_dim)
+
+
+def tensor_movedim_multi(self, x, sources, destinations):
+    return self.tensor_movedim(x, source=tuple(sources), destination=tuple(destinations))
+
+
+def tensor_unsqueeze_dim(self, x, dim):
+    return self.tensor_unsqueeze(x, dim=dim)
+
+
+def tensor_squeeze_neg_dim(self, x, dim):
+    return self.tensor_squeeze(x, dim=dim % len(self.tensor_shape(x)))
+
+
+def tensor_var_dims(self, x, dims, correction=1, keepdim=False):
+    return self._apply("var_dims", [x], dims=tuple(dims), correction=correction, keepdim=keepdim)
+
+
+def tensor_std_dims(self, x, dims, correction=1, keepdim=False):
+    return self._apply("std_dims", [x], dims=tuple(dims), correction=correction, keepdim=keepdim)
+
+
+def tensor_quantile_interpolation(self, x, q, interpolation="linear"):
+    return _quantile(self, x, q, None, False, interpolation)
+
+
+def tensor_nanquantile_interpolation(self, x, q, interpolation="linear"):
+    return _quantile(self, x, q, None, False, interpolation, ignore_nan=True)
+
+
+def tensor_searchsorted_side(self, sorted_seq, values, side="left"):
+    if side not in ("left", "right"):
+        raise ValueError("side must be 'left' or 'right'")
+    return self.tensor_searchsorted(sorted_seq, values, right=(side == "right"))
+
+
+def tensor_searchsorted_sorter(self, seq, values, sorter, right=False):
+    """``seq`` need not be sorted: ``sorter`` holds the indices that sort it."""
+    idx = torch.searchsorted(self.tensor(seq), self.tensor(values), right=right, sorter=self.tensor(sorter).long())
+    return _new(self, idx.to(torch.float64), False)
+
+
+def tensor_linalg_inv_ex(self, a):
+    A = self.tensor(a)
+    inv, info = torch.linalg.inv_ex(A)
+    if int(info.max()) != 0:
+        return None, int(info.max())
+    return self.tensor_inverse(a), 0
+
+
+def tensor_linalg_cholesky_ex(self, a, upper=False):
+    _, info = torch.linalg.cholesky_ex(self.tensor(a), upper=upper)
+    if int(info.max()) != 0:
+        return None, int(info.max())
+    return tensor_cholesky(self, a, upper), 0
+
+
+def tensor_linalg_solve_ex(self, a, b):
+    _, info = torch.linalg.solve_ex(self.tensor(a), self.tensor(b))
+    if int(info.max()) != 0:
+        return None, int(info.max())
+    return self.tensor_linalg_solve(a, b), 0
+
+
+def tensor_linalg_lu_factor_ex(self, a):
+    lu, piv, info = torch.linalg.lu_factor_ex(self.tensor(a))
+    return _new(self, lu, False, self.tensor_dtype(a)), [int(p) for p in piv.reshape(-1).tolist()], int(info.max())
+
+
+def tensor_linalg_ldl_factor(self, a, hermitian=False):
+    """``(LD, pivots)`` of a symmetric matrix (compact Bunch-Kaufman form)."""
+    ld, piv = torch.linalg.ldl_factor(self.tensor(a), hermitian=hermitian)
+    return _new(self, ld, False, self.tensor_dtype(a)), [int(p) for p in piv.reshape(-1).tolist()]
+
+
+def tensor_linalg_ldl_solve(self, ld, pivots, b, hermitian=False):
+    LD = self.tensor(ld)
+    piv = torch.as_tensor(list(pivots), dtype=torch.int32, device=LD.device).reshape(LD.shape[:-1])
+    return _new(self, torch.linalg.ldl_solve(LD, piv, self.tensor(b), hermitian=hermitian), False, self.tensor_dtype(b))
+
+
+def tensor_geqrf(self, a):
+    """``(packed Householder reflectors and R, tau)``; ``tensor_householder_product`` rebuilds Q."""
+    qr, tau = torch.geqrf(self.tensor(a))
+    dt = self.tensor_dtype(a)
+    return _new(self, qr, False, dt), _new(self, tau, False, dt)
+
+
+def tensor_cfloat(self, x):
+    """Complex tensor with zero imaginary part (the ``[..., 2]`` layout), components in f32."""
+    re = self.tensor_to_dtype(x, DType.F32)
+    return self.tensor_complex(re, self.zeros_like(re))
+
+
+def tensor_cdouble(self, x):
+    re = self.tensor_to_dtype(x, DType.F64)
+    return self.tensor_complex(re, self.zeros_like(re))
+
+
+def tensor_conj(self, z):
+    return self.tensor_complex_conj(z)
+
+
+def tensor_ihfft(self, x, n=None, dim=-1):
+    return self._apply("ihfft", [x], n=n, dim=dim)
+
+
+def tensor_ihfft_norm(self, x, n=None, norm="backward", dim=-1):
+    return self._apply("ihfft", [x], n=n, dim=dim, norm=norm)
+
+
+def tensor_irfftn(self, z, s=None, dim=None):
+    return self._apply("irfftn", [z], s=s, dim=None if dim is None else tuple(dim))
+
+
+def tensor_irfftn_norm(self, z, s=None, dim=None, norm="backward"):
+    return self._apply("irfftn", [z], s=s, dim=None if dim is None else tuple(dim), norm=norm)
+
+
+def tensor_rfftn_norm(self, x, s=None, dim=None, norm="backward"):
+    return tensor_rfftn(self, x, s, dim, norm)
+
+
+def tensor_irfft_norm(self, z, n=None, norm="backward"):
+    s = None if n is None else (int(n),)
+    return self._apply("irfftn", [z], s=s, dim=(-1,), norm=norm)
+
+
+def tensor_hfft_norm(self, z, n=None, norm="backward"):
+    """``hfft`` of a half spectrum under ``norm``: the default-norm transform rescaled (the transform is linear)."""
+    out = self.tensor_hfft(z, n=n)
+    length = self.tensor_shape(out)[-1]
+    scale = {"backward": 1.0, None: 1.0, "ortho": 1.0 / math.sqrt(length), "forward": 1.0 / length}[norm]
+    return out if scale == 1.0 else self.tensor_mul_scalar(out, c=scale)
+
+
+def tensor_fftn_norm(self, x, norm="backward"):
+    return self.tensor_fftn(x, norm=norm)
+
+
+def tensor_ifftn_norm(self, z, norm="backward"):
+    return self.tensor_ifftn(z, norm=norm)
+
+
+def tensor_ifft2_norm(self, z, norm="backward"):
+    return self.tensor_ifft2(z, norm=norm)
+
+
+def tensor_fft_along_dim(self, x, dim, n=None, norm=None):
+    return self.tensor_fft(x, n=n, dim=dim, norm=norm)
+
+
+def tensor_any(self, x, dim=None, keepdim=False):
+    return self._apply("any", [x], dim=dim, keepdim=keepdim)
+
+
+def tensor_all(self, x, dim=None, keepdim=False):
+    return self._apply("all", [x], dim=dim, keepdim=keepdim)
+
+
+def tensor_trapezoid_dx(self, y, dx=1.0, dim=-1):
+    return tensor_trapezoid(self, y, None, dim, dx)
+
+
+def tensor_trapz(self, y, x=None, dim=-1):
+    return tensor_trapezoid(self, y, x, dim)
+
+
+def tensor_cumulative_trapezoid_dx(self, y, dx=1.0, dim=-1):
+    return tensor_cumulative_trapezoid(self, y, None, dim, dx)
+
+
+def tensor_vecdot(self, a, b, dim=-1):
+    return self._apply("vecdot", [a, b], dim=dim)
+
+
+def tensor_roll_flat(self, x, shift):
+    return self._apply("roll_flat", [x], shift=int(shift))
+
+
+def tensor_linalg_tensorinv(self, x, ind=2):
+    return self._apply("linalg_tensorinv", [x], ind=int(ind))
+
+
+def tensor_slogdet(self, a):
+    return self.tensor_linalg_slogdet(a)
+
+
+def tensor_unique_dim(self, x, dim):
+    """Unique slices along ``dim`` in sorted order: ``(values, inverse, counts)``."""
+    v, inv, cnt = torch.unique(self.tensor(x), dim=dim, return_inverse=True, return_counts=True)
+    return (_new(self, v, False, self.tensor_dtype(x)), _new(self, inv.to(torch.float64), False), _new(self, cnt.to(torch.float64), False))
+
+
+def tensor_addmm_scaled(self, x, m1, m2, beta, alpha):
+    return self.tensor_addmm(x, m1, m2, beta=float(beta), alpha=float(alpha))
+
+
 # ------------------------------------------------------------------------------------ installation
 _SECOND_NAMES = {
     # matrices
@@ -759,6 +997,7 @@ _SECOND_NAMES = {
     # factories and samplers under the tensor_ prefix
     "tensor_randn": "randn", "tensor_rand": "rand", "tensor_zeros": "zeros", "tensor_poisson": "poisson",
     "tensor_fft_fftfreq": "tensor_fftfreq", "tensor_fft_rfftfreq": "tensor_rfftfreq",
+    "tensor_special_gammaln": "tensor_gammaln", "tensor_svdvals": "tensor_linalg_svdvals", "tensor_linalg_cross": "tensor_cross",
 }
 
 _INPLACE_BINARY = {

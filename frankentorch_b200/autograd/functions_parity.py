@@ -1104,3 +1104,173 @@ def _irfft2_vjp(g, i, o, kw):
 
 
 _reg("irfft2", _irfft2_fwd, _irfft2_vjp, "d(irfft2(z))/dz_k=c*w_k*rfft2(grad)_k, w=1 at DC and Nyquist else 2")
+
+
+# ---------------------------------------------------------------------------------- second batch
+# Operators named in the reference's parity matrix and profiling notes (FEATURE_PARITY.md, docs/NEGATIVE_EVIDENCE.md):
+# soft-target cross-entropy, multi-dimension variance, the remaining Chebyshev families, clamps against tensors,
+# vecdot, inverse real FFTs, boolean reductions.
+def _ce_soft_fwd(logits, probs, reduction="mean"):
+    return torch.nn.functional.cross_entropy(logits, probs, reduction=reduction)
+
+
+def _ce_soft_vjp(g, i, o, kw):
+    logits, p = i
+    cdim = 1 if logits.dim() > 1 else 0
+    red = kw.get("reduction", "mean")
+    ls = torch.log_softmax(logits, cdim)
+    n = logits.numel() // logits.shape[cdim] if logits.dim() > 1 else 1
+    k = g / n if red == "mean" else (g if red == "sum" else g.unsqueeze(cdim))
+    return [k * (torch.exp(ls) * p.sum(cdim, keepdim=True) - p), -k * ls]
+
+
+_reg("cross_entropy_soft", _ce_soft_fwd, _ce_soft_vjp,
+     "loss=-sum_c p_c*log_softmax(x)_c: dx=softmax(x)*sum_c(p_c)-p; dp=-log_softmax(x); mean divides by the batch")
+
+
+def _dims_tuple(dims, ndim):
+    return tuple(sorted(int(d) % ndim for d in dims))
+
+
+def _var_dims_fwd(x, dims=(0,), correction=1, keepdim=False):
+    return torch.var(x, dim=_dims_tuple(dims, x.dim()), correction=correction, keepdim=keepdim)
+
+
+def _var_dims_vjp(g, i, o, kw):
+    x = i[0]
+    dims = _dims_tuple(kw.get("dims", (0,)), x.dim())
+    n = 1
+    for d in dims:
+        n *= x.shape[d]
+    if not kw.get("keepdim", False):
+        for d in dims:
+            g = g.unsqueeze(d)
+    return [g * 2.0 * (x - x.mean(dims, keepdim=True)) / (n - kw.get("correction", 1))]
+
+
+_reg("var_dims", _var_dims_fwd, _var_dims_vjp, "d(var over dims)/dx=2*(x-mean)/(n-correction)")
+
+
+def _std_dims_vjp(g, i, o, kw):
+    og = o
+    if not kw.get("keepdim", False):
+        for d in _dims_tuple(kw.get("dims", (0,)), i[0].dim()):
+            og = og.unsqueeze(d)
+            g = g.unsqueeze(d)
+        kw = dict(kw, keepdim=True)
+    return _var_dims_vjp(g / (2.0 * og), i, o, kw)
+
+
+_reg("std_dims", lambda x, dims=(0,), correction=1, keepdim=False: torch.std(x, dim=_dims_tuple(dims, x.dim()), correction=correction, keepdim=keepdim),
+     _std_dims_vjp, "d(std over dims)/dx=(x-mean)/((n-correction)*std)")
+
+
+def _cheb_u_d(x, n, un=None):
+    """U_n'(x) = ((n+1)*T_{n+1}(x) - x*U_n(x)) / (x^2 - 1); (+-1)^(n+1) * n(n+1)(n+2)/3 at x = +-1."""
+    if n <= 0:
+        return torch.zeros_like(x)
+    un = _S.chebyshev_polynomial_u(x, n) if un is None else un
+    edge = x.abs() == 1
+    den = torch.where(edge, torch.ones_like(x), x * x - 1)
+    d = ((n + 1) * _S.chebyshev_polynomial_t(x, n + 1) - x * un) / den
+    return torch.where(edge, torch.sign(x) ** (n + 1) * (n * (n + 1) * (n + 2) / 3.0), d)
+
+
+def _cheb_t_d(x, n):
+    return n * _S.chebyshev_polynomial_u(x, n - 1) if n > 0 else torch.zeros_like(x)
+
+
+_poly("special_chebyshev_polynomial_u", _S.chebyshev_polynomial_u, lambda x, n, o: _cheb_u_d(x, n, o),
+      "d(U_n(x))/dx=((n+1)*T_{n+1}(x)-x*U_n(x))/(x^2-1)")
+# V_n = U_n - U_{n-1}, W_n = U_n + U_{n-1}
+_poly("special_chebyshev_polynomial_v", _S.chebyshev_polynomial_v, lambda x, n, o: _cheb_u_d(x, n) - _cheb_u_d(x, n - 1),
+      "d(V_n)/dx=U_n'-U_{n-1}'")
+_poly("special_chebyshev_polynomial_w", _S.chebyshev_polynomial_w, lambda x, n, o: _cheb_u_d(x, n) + _cheb_u_d(x, n - 1),
+      "d(W_n)/dx=U_n'+U_{n-1}'")
+# shifted families: P*_n(x) = P_n(2x - 1), so the derivative carries a factor 2
+_poly("special_shifted_chebyshev_polynomial_t", _S.shifted_chebyshev_polynomial_t, lambda x, n, o: 2 * _cheb_t_d(2 * x - 1, n),
+      "d(T*_n(x))/dx=2*T_n'(2x-1)")
+_poly("special_shifted_chebyshev_polynomial_u", _S.shifted_chebyshev_polynomial_u, lambda x, n, o: 2 * _cheb_u_d(2 * x - 1, n),
+      "d(U*_n(x))/dx=2*U_n'(2x-1)")
+_poly("special_shifted_chebyshev_polynomial_v", _S.shifted_chebyshev_polynomial_v,
+      lambda x, n, o: 2 * (_cheb_u_d(2 * x - 1, n) - _cheb_u_d(2 * x - 1, n - 1)), "d(V*_n(x))/dx=2*V_n'(2x-1)")
+_poly("special_shifted_chebyshev_polynomial_w", _S.shifted_chebyshev_polynomial_w,
+      lambda x, n, o: 2 * (_cheb_u_d(2 * x - 1, n) + _cheb_u_d(2 * x - 1, n - 1)), "d(W*_n(x))/dx=2*W_n'(2x-1)")
+
+_bin("clamp_min_tensor", torch.maximum, lambda g, a, b, o: g * (a >= b), lambda g, a, b, o: g * (a < b),
+     "d(max(x,lo))/dx=1(x>=lo); dlo=1(x<lo)")
+_bin("clamp_max_tensor", torch.minimum, lambda g, a, b, o: g * (a <= b), lambda g, a, b, o: g * (a > b),
+     "d(min(x,hi))/dx=1(x<=hi); dhi=1(x>hi)")
+
+
+def _vecdot_vjp(g, i, o, kw):
+    a, b = i
+    ge = g.unsqueeze(int(kw.get("dim", -1)))
+    return [unbroadcast(ge * b, a.shape), unbroadcast(ge * a, b.shape)]
+
+
+_reg("vecdot", lambda a, b, dim=-1: torch.linalg.vecdot(a, b, dim=int(dim)), _vecdot_vjp, "d(sum_k a_k*b_k)/da=grad*b; db=grad*a (real)")
+_nograd("any", lambda x, dim=None, keepdim=False: torch.any(x != 0) if dim is None else torch.any(x != 0, dim=int(dim), keepdim=keepdim))
+_nograd("all", lambda x, dim=None, keepdim=False: torch.all(x != 0) if dim is None else torch.all(x != 0, dim=int(dim), keepdim=keepdim))
+_reg("roll_flat", lambda x, shift=1: torch.roll(x, int(shift)), lambda g, i, o, kw: [torch.roll(g, -int(kw.get("shift", 1)))],
+     "d(roll of the flattened tensor)/dx=roll(grad,-shift)")
+_reg("frobenius_norm", lambda x: torch.linalg.vector_norm(x, 2.0),
+     lambda g, i, o, kw: [g * i[0] / torch.where(o == 0, torch.ones_like(o), o)], "d(||x||_F)/dx=x/||x||_F")
+
+
+def _tensorinv_vjp(g, i, o, kw):
+    x, ind = i[0], int(kw.get("ind", 2))
+    n = 1
+    for d in x.shape[:ind]:
+        n *= d
+    y = o.reshape(n, n)            # inverse of the flattened square matrix
+    ga = -(y.mT @ g.reshape(n, n) @ y.mT)
+    return [ga.reshape(x.shape)]
+
+
+_reg("linalg_tensorinv", lambda x, ind=2: torch.linalg.tensorinv(x, ind=int(ind)), _tensorinv_vjp,
+     "tensorinv = inverse of the matrix flattened at ind: dA=-A^-T@grad@A^-T, reshaped")
+
+
+def _irfftn_fwd(z, s=None, dim=None, norm=None):
+    return torch.fft.irfftn(_cplx(z), s=s, dim=dim, norm=norm)
+
+
+def _irfftn_vjp(g, i, o, kw):
+    z = i[0]
+    dims = _fft_dims(z.dim() - 1, kw.get("s"), kw.get("dim"))
+    n_total = 1
+    for d in dims:
+        n_total *= g.shape[d]
+    n_last = g.shape[dims[-1]]
+    m = n_last // 2 + 1
+    w = torch.full((m,), 2.0, dtype=g.dtype, device=g.device)
+    w[0] = 1.0
+    if n_last % 2 == 0:
+        w[-1] = 1.0
+    shape = [1] * g.dim()
+    shape[dims[-1]] = m
+    gz = torch.fft.rfftn(g, dim=dims) * w.reshape(shape) * _norm_scale(kw.get("norm"), n_total, True)
+    return [torch.view_as_real(_fit(gz, z.shape[:-1])).contiguous()]
+
+
+_reg("irfftn", _irfftn_fwd, _irfftn_vjp, "d(irfftn(z))/dz_k=c*w_k*rfftn(grad)_k, w=1 at DC and Nyquist of the last dimension else 2")
+
+
+def _ihfft_fwd(x, n=None, dim=-1, norm=None):
+    return torch.view_as_real(torch.fft.ihfft(x, n=n, dim=int(dim), norm=norm).resolve_conj()).contiguous()
+
+
+def _ihfft_vjp(g, i, o, kw):
+    # ihfft(x) = conj(rfft(x)) / n (under the default norm): linear in the real input
+    x, dim = i[0], int(kw.get("dim", -1)) % i[0].dim()
+    n = x.shape[dim] if kw.get("n") is None else int(kw["n"])
+    gc = torch.conj(_cplx(g))
+    full = list(gc.shape)
+    full[dim] = n
+    scale = {"forward": 1.0, "ortho": 1.0 / math.sqrt(n)}.get(kw.get("norm"), 1.0 / n)
+    dx = torch.fft.ifft(_fit(gc, full), dim=dim).real * (n * scale)
+    return [_fit(dx, x.shape)]
+
+
+_reg("ihfft", _ihfft_fwd, _ihfft_vjp, "ihfft(x)=conj(rfft(x))*c: dx=n*c*Re(ifft(zero-extended conj(grad)))")

@@ -440,6 +440,129 @@ tensor_absolute tensor_1d
 """.split()
 
 
+PARITY_MATRIX_NAMES = """
+tensor_cross_entropy_label_smoothing tensor_triplet_margin_loss_swap tensor_linalg_solve_triangular tensor_unflatten_dim
+tensor_nanquantile_interpolation tensor_searchsorted_sorter tensor_movedim_multi tensor_flatten_dims tensor_var_dims tensor_unsqueeze_dim
+tensor_searchsorted_side tensor_cross_entropy_soft tensor_quantile_interpolation tensor_linalg_inv_ex
+tensor_special_shifted_chebyshev_polynomial_w tensor_special_shifted_chebyshev_polynomial_v tensor_special_shifted_chebyshev_polynomial_u
+tensor_special_shifted_chebyshev_polynomial_t tensor_special_chebyshev_polynomial_w tensor_special_chebyshev_polynomial_v
+tensor_special_chebyshev_polynomial_u tensor_cfloat tensor_ihfft tensor_conj tensor_any tensor_all tensor_trapezoid_dx tensor_squeeze_neg_dim
+tensor_special_gammaln tensor_linalg_cholesky_ex tensor_vecdot tensor_trapz tensor_svdvals tensor_roll_flat tensor_linalg_solve_ex
+tensor_linalg_lu_factor_ex tensor_irfftn_norm tensor_cumulative_trapezoid_dx tensor_linalg_tensorinv tensor_irfftn tensor_cdouble
+tensor_linalg_cross tensor_ihfft_norm tensor_frobenius_norm tensor_linalg_ldl_factor tensor_std_dims tensor_rfftn_norm tensor_irfft_norm
+tensor_ifftn_norm tensor_ifft2_norm tensor_fftn_norm tensor_clamp_min_tensor tensor_hfft_norm tensor_clamp_max_tensor tensor_slogdet
+tensor_linalg_ldl_solve tensor_geqrf tensor_unique_dim tensor_addmm_scaled tensor_fft_along_dim
+""".split()
+
+
 def test_every_session_method_the_reference_benches_call_exists():
-    missing = [n for n in REFERENCE_NAMES if not callable(getattr(FrankenTorchSession, n, None))]
+    missing = [n for n in REFERENCE_NAMES + PARITY_MATRIX_NAMES if not callable(getattr(FrankenTorchSession, n, None))]
     assert not missing, missing
+
+
+# ------------------------------------------------------------------------------------ second batch
+SQ = T(2, 0.3, -0.4, 1.5, shape=[2, 2])
+BATCH2 = [
+    ("ce_label_smoothing", lambda s, i: s.tensor_cross_entropy_label_smoothing(i[0], i[1], 0.15), [(X, True), (T(2, 0), False)]),
+    ("ce_soft_mean", lambda s, i: s.tensor_cross_entropy_soft(i[0], i[1], "mean"), [(X, True), (U / U.sum(1, keepdim=True), True)]),
+    ("ce_soft_none", lambda s, i: s.tensor_cross_entropy_soft(i[0], i[1], "none"), [(X, True), (U, True)]),
+    ("triplet_swap", lambda s, i: s.tensor_triplet_margin_loss_swap(i[0], i[1], i[2], 1.0, 2.0, True, "mean"), [(X, True), (Y, True), (P, True)]),
+    ("triplet_noswap_sum", lambda s, i: s.tensor_triplet_margin_loss_swap(i[0], i[1], i[2], 0.5, 1.0, False, "sum"), [(X, True), (Y, True), (P, True)]),
+    ("var_dims", lambda s, i: s.tensor_var_dims(i[0], [0, 2], 1, False), [(torch.stack([X, Y, P]), True)]),
+    ("std_dims_keep", lambda s, i: s.tensor_std_dims(i[0], [1, 2], 0, True), [(torch.stack([X, Y, P]), True)]),
+    ("cheb_u", lambda s, i: s.tensor_special_chebyshev_polynomial_u(i[0], 4), [(U, True)]),
+    ("cheb_v", lambda s, i: s.tensor_special_chebyshev_polynomial_v(i[0], 4), [(U, True)]),
+    ("cheb_w", lambda s, i: s.tensor_special_chebyshev_polynomial_w(i[0], 3), [(U, True)]),
+    ("shifted_t", lambda s, i: s.tensor_special_shifted_chebyshev_polynomial_t(i[0], 4), [(U, True)]),
+    ("shifted_u", lambda s, i: s.tensor_special_shifted_chebyshev_polynomial_u(i[0], 3), [(U, True)]),
+    ("shifted_v", lambda s, i: s.tensor_special_shifted_chebyshev_polynomial_v(i[0], 3), [(U, True)]),
+    ("shifted_w", lambda s, i: s.tensor_special_shifted_chebyshev_polynomial_w(i[0], 4), [(U, True)]),
+    ("clamp_min_tensor", lambda s, i: s.tensor_clamp_min_tensor(i[0], i[1]), [(X, True), (Y, True)]),
+    ("clamp_max_tensor", lambda s, i: s.tensor_clamp_max_tensor(i[0], i[1]), [(X, True), (Y, True)]),
+    ("vecdot", lambda s, i: s.tensor_vecdot(i[0], i[1], 1), [(X, True), (Y, True)]),
+    ("roll_flat", lambda s, i: s.tensor_roll_flat(i[0], 2), [(X, True)]),
+    ("frobenius_norm", lambda s, i: s.tensor_frobenius_norm(i[0]), [(X, True)]),
+    ("tensorinv", lambda s, i: s.tensor_linalg_tensorinv(i[0], 2), [((torch.eye(4, dtype=torch.float64) * 2 + torch.arange(16, dtype=torch.float64).reshape(4, 4).sin() * 0.3).reshape(2, 2, 2, 2), True)]),
+    ("irfftn", lambda s, i: s.tensor_irfftn(i[0], None, None), [(torch.stack([X, Y], -1), True)]),
+    ("irfftn_ortho_odd", lambda s, i: s.tensor_irfftn_norm(i[0], [2, 5], None, "ortho"), [(torch.stack([X, Y], -1), True)]),
+    ("irfft_norm", lambda s, i: s.tensor_irfft_norm(i[0], None, "forward"), [(torch.stack([X, Y], -1), True)]),
+    ("ihfft", lambda s, i: s.tensor_ihfft(i[0], None, 1), [(torch.cat([X, Y], 1), True)]),
+    ("ihfft_ortho", lambda s, i: s.tensor_ihfft_norm(i[0], None, "ortho", 0), [(torch.cat([X, Y, P], 0), True)]),
+    ("hfft_norm", lambda s, i: s.tensor_hfft_norm(i[0], None, "ortho"), [(torch.stack([X, Y], -1), True)]),
+    ("rfftn_norm", lambda s, i: s.tensor_rfftn_norm(i[0], None, None, "forward"), [(X, True)]),
+    ("fftn_norm", lambda s, i: s.tensor_fftn_norm(i[0], "ortho"), [(X, True)]),
+    ("fft_along_dim", lambda s, i: s.tensor_fft_along_dim(i[0], 0), [(X, True)]),
+    ("trapezoid_dx", lambda s, i: s.tensor_trapezoid_dx(i[0], 0.5, 1), [(X, True)]),
+    ("cumtrap_dx", lambda s, i: s.tensor_cumulative_trapezoid_dx(i[0], 0.25, 0), [(X, True)]),
+    ("trapz", lambda s, i: s.tensor_trapz(i[0], i[1], 1), [(X, True), (T(0.0, 0.4, 1.5), True)]),
+    ("unflatten_dim", lambda s, i: s.tensor_unflatten_dim(i[0], 1, [3, 1]), [(X, True)]),
+    ("flatten_dims", lambda s, i: s.tensor_flatten_dims(i[0], 0, 1), [(X, True)]),
+    ("movedim_multi", lambda s, i: s.tensor_movedim_multi(i[0], [0, 1], [1, 0]), [(X, True)]),
+    ("cfloat_conj", lambda s, i: s.tensor_conj(s.tensor_cdouble(i[0])), [(X, True)]),
+    ("slogdet", lambda s, i: s.tensor_slogdet(i[0])[1], [(SQ, True)]),
+    ("svdvals", lambda s, i: s.tensor_svdvals(i[0]), [(X, True)]),
+    ("linalg_cross", lambda s, i: s.tensor_linalg_cross(i[0], i[1]), [(X, True), (Y, True)]),
+    ("solve_triangular", lambda s, i: s.tensor_linalg_solve_triangular(i[0], i[1], True), [(torch.triu(SQ), True), (T(1.0, 2.0, shape=[2, 1]), True)]),
+    ("addmm_scaled", lambda s, i: s.tensor_addmm_scaled(i[0], i[1], i[2], 0.5, 2.0), [(SQ, True), (X, True), (X.t().contiguous(), True)]),
+    ("inv_ex", lambda s, i: s.tensor_linalg_inv_ex(i[0])[0], [(SQ, True)]),
+    ("solve_ex", lambda s, i: s.tensor_linalg_solve_ex(i[0], i[1])[0], [(SQ, True), (T(1.0, 2.0, shape=[2, 1]), True)]),
+    ("cholesky_ex", lambda s, i: s.tensor_linalg_cholesky_ex(s.tensor_matmul(i[0], s.tensor_transpose(i[0], dim0=0, dim1=1)), False)[0], [(SQ, True)]),
+]
+
+
+@pytest.mark.parametrize("name,call,vals", BATCH2, ids=[p[0] for p in BATCH2])
+def test_second_batch_rules_match_central_differences(name, call, vals):
+    check_grad(call, vals)
+
+
+def test_second_batch_values_and_non_differentiable_forms():
+    s = FrankenTorchSession(ledger_dispatch=False)
+    v = lambda t: s.tensor_variable(t.reshape(-1).tolist(), list(t.shape))   # noqa: E731
+    val = lambda i: s.tensor(i)                                               # noqa: E731
+    x, u = v(X), v(U)
+    for name, fn in (("u", torch.special.chebyshev_polynomial_u), ("v", torch.special.chebyshev_polynomial_v), ("w", torch.special.chebyshev_polynomial_w)):
+        assert torch.allclose(val(getattr(s, f"tensor_special_chebyshev_polynomial_{name}")(u, 5)), fn(U, 5))
+        shifted = getattr(torch.special, f"shifted_chebyshev_polynomial_{name}")
+        assert torch.allclose(val(getattr(s, f"tensor_special_shifted_chebyshev_polynomial_{name}")(u, 5)), shifted(U, 5))
+    # the closed forms at the end points, where the generic formula divides by zero
+    e = s.tensor_variable([1.0, -1.0], [2], True)
+    rep = s.tensor_backward(s.tensor_sum(s.tensor_special_chebyshev_polynomial_u(e, 3)))
+    assert rep.gradient(e).tolist() == [20.0, 20.0]                              # (+-1)^(n+1) * n(n+1)(n+2)/3
+    assert val(s.tensor_any(x)).item() is True and val(s.tensor_all(v(T(1.0, 0.0)))).item() is False
+    assert val(s.tensor_any(v(T(0.0, 0.0, 1.0, 0.0, shape=[2, 2])), 1)).tolist() == [False, True]
+    assert val(s.tensor_searchsorted_side(v(T(1.0, 2.0, 2.0, 3.0)), v(T(2.0)), "right")).tolist() == [3.0]
+    assert val(s.tensor_searchsorted_side(v(T(1.0, 2.0, 2.0, 3.0)), v(T(2.0)), "left")).tolist() == [1.0]
+    assert val(s.tensor_searchsorted_sorter(v(T(3.0, 1.0, 2.0)), v(T(2.5)), v(T(1, 2, 0)))).tolist() == [2.0]
+    with pytest.raises(ValueError):
+        s.tensor_searchsorted_side(x, x, "middle")
+    assert val(s.tensor_quantile_interpolation(x, 0.4, "nearest")).item() == torch.quantile(X, 0.4, interpolation="nearest").item()
+    assert val(s.tensor_nanquantile_interpolation(v(T(1.0, float("nan"), 3.0)), 0.5, "higher")).item() == 3.0
+    assert s.tensor_shape(s.tensor_unsqueeze_dim(x, 1)) == [2, 1, 3] and s.tensor_shape(s.tensor_squeeze_neg_dim(s.tensor_unsqueeze_dim(x, 2), -1)) == [2, 3]
+    singular = v(T(1.0, 2.0, 2.0, 4.0, shape=[2, 2]))
+    out, info = s.tensor_linalg_inv_ex(singular)
+    assert out is None and info > 0
+    out, info = s.tensor_linalg_cholesky_ex(v(T(1.0, 2.0, 2.0, 1.0, shape=[2, 2])))
+    assert out is None and info == 2
+    out, info = s.tensor_linalg_solve_ex(singular, v(T(1.0, 1.0, shape=[2, 1])))
+    assert out is None and info > 0
+    good, info = s.tensor_linalg_inv_ex(v(SQ))
+    assert info == 0 and torch.allclose(val(good) @ SQ, torch.eye(2, dtype=torch.float64))
+    lu, piv, info = s.tensor_linalg_lu_factor_ex(v(SQ))
+    assert info == 0 and torch.allclose(SQ @ val(s.tensor_lu_solve(lu, piv, v(T(1.0, 2.0, shape=[2, 1])))), T(1.0, 2.0, shape=[2, 1]))
+    sym = SQ + SQ.t()
+    ld, lp = s.tensor_linalg_ldl_factor(v(sym))
+    b = T(1.0, -2.0, shape=[2, 1])
+    assert torch.allclose(sym @ val(s.tensor_linalg_ldl_solve(ld, lp, v(b))), b)
+    qr, tau = s.tensor_geqrf(x)
+    rq, rt = torch.geqrf(X)
+    assert torch.allclose(val(qr), rq) and torch.allclose(val(tau), rt)
+    uq, inv, cnt = s.tensor_unique_dim(v(T(1, 2, 1, 2, 3, 4, shape=[3, 2])), 0)
+    assert val(uq).tolist() == [[1.0, 2.0], [3.0, 4.0]] and val(inv).tolist() == [0.0, 0.0, 1.0] and val(cnt).tolist() == [2.0, 1.0]
+    assert tuple(val(s.tensor_cfloat(x)).shape) == (2, 3, 2) and val(s.tensor_cfloat(x)).dtype == torch.float32
+    assert torch.allclose(val(s.tensor_special_gammaln(v(P))), torch.lgamma(P))
+    assert torch.allclose(val(s.tensor_ihfft(x, None, 1)), torch.view_as_real(torch.fft.ihfft(X, dim=1).resolve_conj()))
+    z = torch.stack([X, Y], -1)
+    assert torch.allclose(val(s.tensor_irfftn(v(z), None, None)), torch.fft.irfftn(torch.view_as_complex(z.contiguous())))
+    assert torch.allclose(val(s.tensor_hfft_norm(v(z), None, "forward")), torch.fft.hfft(torch.view_as_complex(z.contiguous()), norm="forward"))
+    assert torch.allclose(val(s.tensor_ifft2_norm(v(z), "ortho")), torch.view_as_real(torch.fft.ifft2(torch.view_as_complex(z.contiguous()), norm="ortho")))
+    assert torch.allclose(val(s.tensor_ifftn_norm(v(z), "forward")), torch.view_as_real(torch.fft.ifftn(torch.view_as_complex(z.contiguous()), norm="forward")))
