@@ -986,6 +986,202 @@ def tensor_addmm_scaled(self, x, m1, m2, beta, alpha):
     return self.tensor_addmm(x, m1, m2, beta=float(beta), alpha=float(alpha))
 
 
+# ------------------------------------------------------------------------------------ metadata, splits, misc (third batch)
+def tensor_stride(self, x) -> List[int]:
+    return list(self.tensor(x).stride())
+
+
+def tensor_dim(self, x) -> int:
+    return self.tensor(x).dim()
+
+
+def tensor_nelement(self, x) -> int:
+    return self.tensor(x).numel()
+
+
+def tensor_clone(self, x):
+    """A copy that stays in the graph: its gradient flows to ``x`` unchanged."""
+    return self.tensor_contiguous(self.tensor_mul_scalar(x, c=1.0))
+
+
+def tensor_bool(self, x):
+    """0 / 1 mask of the non-zero elements (a node without history)."""
+    return _new(self, (self.tensor(x) != 0).to(torch.float64), False, self.tensor_dtype(x))
+
+
+def tensor_int_long(self, x):
+    """Values truncated toward zero, as an int64 node (indices, labels)."""
+    return self.tensor_tape.leaf(self.tensor(x).detach().to(torch.int64), False)
+
+
+def tensor_broadcast_shapes(self, *shapes) -> List[int]:
+    return list(torch.broadcast_shapes(*[tuple(s) for s in shapes]))
+
+
+def tensor_array_split(self, x, sections, dim=0) -> List[int]:
+    """``sections`` pieces along ``dim``: the first ``n % sections`` get one element more (numpy's rule)."""
+    n = self.tensor_shape(x)[dim]
+    base, extra = divmod(n, int(sections))
+    return tensor_split_with_sizes(self, x, [base + (1 if k < extra else 0) for k in range(int(sections))], dim)
+
+
+def tensor_nonzero_as_tuple(self, x) -> List[int]:
+    return [_new(self, t.to(torch.float64), False) for t in torch.nonzero(self.tensor(x), as_tuple=True)]
+
+
+def tensor_matrix_rank(self, a):
+    return self.tensor_linalg_matrix_rank(a)
+
+
+def tensor_kthvalue_dim(self, x, k, dim, keepdim=False):
+    return tensor_kthvalue(self, x, k, dim, keepdim)
+
+
+def tensor_ger(self, a, b):
+    return self.tensor_outer(a, b)
+
+
+def tensor_tensordot_dims(self, a, b, dims_a, dims_b):
+    return self.tensor_tensordot(a, b, dims=(list(dims_a), list(dims_b)))
+
+
+def tensor_fft_fftshift(self, x, dim=None):
+    return self.tensor_fftshift(x, dim=dim) if dim is not None else self.tensor_fftshift(x)
+
+
+def tensor_fft_ifftshift(self, x, dim=None):
+    return self.tensor_ifftshift(x, dim=dim) if dim is not None else self.tensor_ifftshift(x)
+
+
+def tensor_scalbn(self, x, n):
+    """``x * 2^n`` for an integer ``n``."""
+    return self.tensor_mul_scalar(x, c=float(2.0 ** int(n)))
+
+
+def tensor_frexp(self, x) -> Tuple[int, int]:
+    """``(mantissa in [0.5, 1), integer exponent)`` with ``x = mantissa * 2^exponent``.  The mantissa is ``x``
+    scaled by a constant power of two per element, so its gradient is ``grad * 2^-exponent``."""
+    m, e = torch.frexp(self.tensor(x).detach())
+    scale = self.tensor_tape.leaf(torch.exp2(-e.to(self.tensor(x).dtype)), False)
+    return self.tensor_mul(x, scale), _new(self, e.to(torch.float64), False)
+
+
+def tensor_modf(self, x) -> Tuple[int, int]:
+    """``(fractional part, integral part)``, both with the sign of ``x``."""
+    return self.tensor_frac(x), self.tensor_trunc(x)
+
+
+def tensor_lobpcg(self, a, k=1, niter=200, tol=1e-10, seed=0x4654) -> Tuple[int, int]:
+    """The ``k`` largest eigenpairs of a symmetric matrix by locally optimal block preconditioned conjugate
+    gradients (no preconditioner): Rayleigh-Ritz over ``[X, R, P]`` each iteration.  Outputs are leaves."""
+    A = self.tensor(a).detach().to(torch.float64)
+    n = A.shape[-1]
+    k = int(k)
+    if A.dim() != 2 or A.shape[0] != n or not 0 < k <= n:
+        raise ValueError("lobpcg needs a square matrix and 0 < k <= n")
+    g = torch.Generator().manual_seed(int(seed))
+    X = torch.linalg.qr(torch.randn(n, k, generator=g, dtype=torch.float64)).Q
+    P = None
+    for _ in range(int(niter)):
+        AX = A @ X
+        lam = (X * AX).sum(0)
+        R = AX - X * lam
+        if float(R.norm()) <= tol * max(1.0, float(lam.abs().max())):
+            break
+        S_ = torch.cat([X, R] + ([P] if P is not None else []), 1)
+        Q = torch.linalg.qr(S_).Q
+        keep = torch.linalg.matrix_rank(S_)
+        Q = Q[:, : int(keep)] if int(keep) >= k else Q
+        w, V = torch.linalg.eigh(Q.t() @ A @ Q)
+        C = V[:, -k:].flip(1)                                # the k largest, descending
+        Xn = Q @ C
+        P = Xn - X @ (X.t() @ Xn)
+        P = None if float(P.norm()) < 1e-14 else P
+        X = Xn
+    lam = (X * (A @ X)).sum(0)
+    order = torch.argsort(lam, descending=True)
+    dt = self.tensor_dtype(a)
+    return _new(self, lam[order], False, dt), _new(self, X[:, order], False, dt)
+
+
+def tensor_von_mises(self, loc, concentration, shape, requires_grad=False):
+    """Best-Fisher rejection sampler of the von Mises distribution on ``(-pi, pi]``."""
+    n = _numel(shape)
+    kappa = float(concentration)
+    if kappa < 1e-8:
+        return _shape_out(self, (2 * math.pi * _u(self, n) - math.pi), shape, requires_grad)
+    tau = 1.0 + math.sqrt(1.0 + 4.0 * kappa * kappa)
+    rho = (tau - math.sqrt(2.0 * tau)) / (2.0 * kappa)
+    r = (1.0 + rho * rho) / (2.0 * rho)
+    out = torch.empty(n, dtype=torch.float64)
+    open_idx = torch.arange(n)
+    while open_idx.numel():
+        m = open_idx.numel()
+        u1, u2, u3 = _u(self, m), _u(self, m), _u(self, m)
+        z = torch.cos(math.pi * u1)
+        f = (1.0 + r * z) / (r + z)
+        c = kappa * (r - f)
+        ok = (c * (2.0 - c) - u2 > 0) | (torch.log(c / u2) + 1.0 - c >= 0)
+        theta = torch.sign(u3 - 0.5) * torch.acos(f.clamp(-1.0, 1.0))
+        out[open_idx[ok]] = theta[ok]
+        open_idx = open_idx[~ok]
+    out = torch.remainder(out + float(loc) + math.pi, 2 * math.pi) - math.pi
+    return _shape_out(self, out, shape, requires_grad)
+
+
+def tensor_fishersnedecor(self, df1, df2, shape, requires_grad=False):
+    """F distribution: the ratio of two chi-square variates, each divided by its degrees of freedom."""
+    n = _numel(shape)
+    a = 2.0 * _gamma_draws(self, 0.5 * float(df1), n) / float(df1)
+    b = 2.0 * _gamma_draws(self, 0.5 * float(df2), n) / float(df2)
+    return _shape_out(self, a / b, shape, requires_grad)
+
+
+def tensor_negative_binomial(self, total_count, p, shape, requires_grad=False):
+    """Failures before ``total_count`` successes of probability ``1 - p`` each (torch's convention: ``p`` is the
+    probability of a failure... of the counted kind), drawn as a gamma-Poisson mixture."""
+    n = _numel(shape)
+    lam = _gamma_draws(self, float(total_count), n) * (float(p) / (1.0 - float(p)))
+    out = torch.zeros(n, dtype=torch.float64)
+    for i, l in enumerate(lam.tolist()):                 # Poisson by inversion, as ``poisson`` does
+        u = float(_u(self, 1)[0])
+        pr = math.exp(-l)
+        s_, x = pr, 0
+        while u > s_ and x < 100000:
+            x += 1
+            pr *= l / x
+            s_ += pr
+        out[i] = x
+    return _shape_out(self, out, shape, requires_grad)
+
+
+def _inplace_from_op(name, op, n_tensors=1):
+    """In-place form of a rule-table operator: ``a <- op(a, ...)``; follows the version rules of ``tensor_add_``."""
+    def method(self, a, *rest, **kw):
+        others = [self.tensor(r) for r in rest[: n_tensors - 1]]
+        extra = rest[n_tensors - 1:]
+        from .autograd.functions import OPS
+        fwd = OPS[op].fwd
+        return _inplace(self, a, lambda t: t.copy_(fwd(t, *others, *extra, **kw).to(t.dtype)))
+    method.__name__ = name
+    method.__doc__ = f"In-place ``{op}``: overwrites the first tensor, bumps its version, returns its id."
+    return method
+
+
+_INPLACE_UNARY_OPS = ["erf", "erfc", "logit", "nan_to_num", "asin", "acos", "atan", "sinh", "cosh", "tanh", "asinh", "atanh", "sin", "cos",
+                      "tan", "exp", "exp2", "expm1", "log", "log2", "log10", "log1p", "sqrt", "rsqrt", "reciprocal", "abs", "sign",
+                      "floor", "ceil", "round", "trunc", "frac", "relu", "relu6", "gelu", "silu", "mish", "elu", "selu", "celu",
+                      "leaky_relu", "hardswish", "hardsigmoid", "hardtanh", "hardshrink", "softshrink", "threshold", "softplus",
+                      "deg2rad", "rad2deg", "square", "tril", "triu", "pow", "float_power", "clamp_min", "clamp_max"]
+_INPLACE_BINARY_OPS = ["logaddexp", "logaddexp2", "gcd", "lcm", "fmax", "fmin", "minimum", "nextafter", "ldexp", "pow_tensor", "atan2"]
+_INPLACE_TERNARY_OPS = ["addcdiv"]
+
+
+def tensor_bernoulli_(self, nid, p=0.5):
+    """Fill with Bernoulli(p) draws of the session stream (1.0 where ``u < p``)."""
+    return _fill_from(self, nid, (_u(self, self.tensor_numel(nid)) < float(p)).to(torch.float64))
+
+
 # ------------------------------------------------------------------------------------ installation
 _SECOND_NAMES = {
     # matrices
@@ -1019,3 +1215,9 @@ def install(cls) -> None:
     for name, target in _SECOND_NAMES.items():
         if name != target and hasattr(cls, target):
             setattr(cls, name, _alias(target, name))
+    from .autograd.functions import OPS
+    for ops, n in ((_INPLACE_UNARY_OPS, 1), (_INPLACE_BINARY_OPS, 2), (_INPLACE_TERNARY_OPS, 3)):
+        for op in ops:
+            name = "tensor_" + ("pow" if op == "pow_tensor" else op) + "_"
+            if op in OPS and not hasattr(cls, name):
+                setattr(cls, name, _inplace_from_op(name, op, n))

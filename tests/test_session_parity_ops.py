@@ -566,3 +566,113 @@ def test_second_batch_values_and_non_differentiable_forms():
     assert torch.allclose(val(s.tensor_hfft_norm(v(z), None, "forward")), torch.fft.hfft(torch.view_as_complex(z.contiguous()), norm="forward"))
     assert torch.allclose(val(s.tensor_ifft2_norm(v(z), "ortho")), torch.view_as_real(torch.fft.ifft2(torch.view_as_complex(z.contiguous()), norm="ortho")))
     assert torch.allclose(val(s.tensor_ifftn_norm(v(z), "forward")), torch.view_as_real(torch.fft.ifftn(torch.view_as_complex(z.contiguous()), norm="forward")))
+
+
+# ------------------------------------------------------------------------------------ third batch
+def test_metadata_splits_and_small_utilities():
+    s = FrankenTorchSession(ledger_dispatch=False)
+    v = lambda t, rg=False: s.tensor_variable(t.reshape(-1).tolist(), list(t.shape), rg)   # noqa: E731
+    val = lambda i: s.tensor(i)                                                            # noqa: E731
+    x = v(X)
+    assert (s.tensor_dim(x), s.tensor_nelement(x), s.tensor_stride(x)) == (2, 6, [3, 1])
+    assert s.tensor_stride(s.tensor_transpose(x, dim0=0, dim1=1)) in ([1, 3], [2, 1])       # a view or a fresh copy
+    assert s.tensor_broadcast_shapes([2, 1, 3], [4, 1]) == [2, 4, 3]
+    assert val(s.tensor_bool(x)).tolist() == [[1.0] * 3, [1.0] * 3] and val(s.tensor_bool(v(T(0.0, 2.0)))).tolist() == [0.0, 1.0]
+    assert val(s.tensor_int_long(v(T(1.7, -2.9)))).tolist() == [1, -2] and val(s.tensor_int_long(x)).dtype == torch.int64
+    parts = s.tensor_array_split(v(torch.arange(7, dtype=torch.float64)), 3)
+    assert [val(p).tolist() for p in parts] == [[0.0, 1.0, 2.0], [3.0, 4.0], [5.0, 6.0]]
+    nz = s.tensor_nonzero_as_tuple(v(T(0.0, 1.0, 2.0, 0.0, shape=[2, 2])))
+    assert [val(t).tolist() for t in nz] == [[0.0, 1.0], [1.0, 0.0]]
+    assert val(s.tensor_matrix_rank(v(T(1.0, 2.0, 2.0, 4.0, shape=[2, 2])))).item() == 1
+    kv, ki = s.tensor_kthvalue_dim(x, 2, 1)
+    assert val(kv).tolist() == [0.3, 0.2] and val(ki).tolist() == [0.0, 1.0]
+    assert torch.equal(val(s.tensor_ger(v(T(1.0, 2.0)), v(T(3.0, 4.0, 5.0)))), torch.outer(T(1.0, 2.0), T(3.0, 4.0, 5.0)))
+    assert torch.allclose(val(s.tensor_tensordot_dims(x, v(Y), [1], [1])), torch.tensordot(X, Y, dims=([1], [1])))
+    assert torch.equal(val(s.tensor_fft_fftshift(x)), torch.fft.fftshift(X)) and torch.equal(val(s.tensor_fft_ifftshift(x)), torch.fft.ifftshift(X))
+    assert torch.equal(val(s.tensor_scalbn(x, 3)), X * 8)
+    fr, it = s.tensor_modf(x)
+    assert torch.allclose(val(fr) + val(it), X) and torch.equal(val(it), torch.trunc(X))
+    m, e = s.tensor_frexp(v(T(8.0, 0.3, -5.0)))
+    rm, re_ = torch.frexp(T(8.0, 0.3, -5.0))
+    assert torch.equal(val(m), rm) and val(e).tolist() == re_.tolist()
+    # clone and frexp's mantissa stay in the graph
+    check_grad(lambda s2, i: s2.tensor_clone(i[0]), [(X, True)])
+    check_grad(lambda s2, i: s2.tensor_frexp(i[0])[0], [(P + 0.01, True)])       # away from the powers of two, where the mantissa jumps
+    check_grad(lambda s2, i: s2.tensor_scalbn(i[0], -2), [(X, True)])
+
+
+def test_lobpcg_finds_the_largest_eigenpairs():
+    s = FrankenTorchSession(ledger_dispatch=False)
+    g = torch.Generator().manual_seed(5)
+    B = torch.randn(12, 12, generator=g, dtype=torch.float64)
+    A = B @ B.t() + torch.diag(torch.arange(12, dtype=torch.float64))
+    lam, V = s.tensor_lobpcg(s.tensor_variable(A.reshape(-1).tolist(), [12, 12]), 3, 500, 1e-11)
+    ref = torch.linalg.eigvalsh(A).flip(0)[:3]
+    assert torch.allclose(s.tensor(lam), ref, rtol=1e-8)
+    Vt = s.tensor(V)
+    assert torch.allclose(A @ Vt, Vt * s.tensor(lam), atol=1e-6) and torch.allclose(Vt.t() @ Vt, torch.eye(3, dtype=torch.float64), atol=1e-8)
+    with pytest.raises(ValueError):
+        s.tensor_lobpcg(s.tensor_variable([1.0, 2.0], [1, 2]), 1)
+
+
+def test_in_place_families_match_their_out_of_place_forms():
+    """Every generated ``tensor_<op>_`` writes what ``tensor_<op>`` returns, bumps the version and returns its
+    argument (the reference's ``inplace_matches_out_of_place`` suite, ft-conformance/tests)."""
+    unary = [("erf", X), ("erfc", X), ("logit", U), ("asin", U), ("acos", U), ("atan", X), ("sinh", X), ("cosh", X), ("tanh", X),
+             ("asinh", X), ("atanh", U), ("sin", X), ("cos", X), ("tan", X), ("exp", X), ("exp2", X), ("expm1", X), ("log", P),
+             ("log2", P), ("log10", P), ("log1p", P), ("sqrt", P), ("rsqrt", P), ("reciprocal", P), ("abs", X), ("sign", X),
+             ("floor", X), ("ceil", X), ("round", X), ("trunc", X), ("frac", X), ("relu", X), ("relu6", X * 5), ("gelu", X), ("silu", X),
+             ("mish", X), ("elu", X), ("selu", X), ("celu", X), ("leaky_relu", X), ("hardswish", X * 3), ("hardsigmoid", X * 3),
+             ("hardtanh", X), ("hardshrink", X), ("softshrink", X), ("softplus", X), ("deg2rad", X), ("rad2deg", X), ("square", X),
+             ("tril", X), ("triu", X), ("nan_to_num", T(float("nan"), 1.0, float("inf")))]
+    for name, t in unary:
+        s = FrankenTorchSession(ledger_dispatch=False)
+        a = s.tensor_variable(t.reshape(-1).tolist(), list(t.shape))
+        want = s.tensor(getattr(s, "tensor_" + name)(a)).clone()
+        before = s.tensor_version(a)
+        assert getattr(s, f"tensor_{name}_")(a) == a and s.tensor_version(a) == before + 1, name
+        assert torch.equal(s.tensor(a), want.to(s.tensor(a).dtype)), name
+    binary = [("logaddexp", X, Y), ("logaddexp2", X, Y), ("fmax", X, Y), ("fmin", X, Y), ("minimum", X, Y), ("ldexp", X, Y.round()),
+              ("nextafter", X, Y), ("gcd", T(12.0, 18.0), T(8.0, 27.0)), ("lcm", T(4.0, 6.0), T(6.0, 15.0))]
+    for name, t, u in binary:
+        s = FrankenTorchSession(ledger_dispatch=False)
+        a, b = s.tensor_variable(t.reshape(-1).tolist(), list(t.shape)), s.tensor_variable(u.reshape(-1).tolist(), list(u.shape))
+        want = s.tensor(getattr(s, "tensor_" + name)(a, b)).clone()
+        assert getattr(s, f"tensor_{name}_")(a, b) == a
+        assert torch.equal(s.tensor(a), want.to(s.tensor(a).dtype)), name
+    s = FrankenTorchSession(ledger_dispatch=False)
+    a, b, c = (s.tensor_variable(t.reshape(-1).tolist(), [2, 3]) for t in (X, Y, P))
+    s.tensor_addcdiv_(a, b, c, value=0.7)
+    assert torch.allclose(s.tensor(a), torch.addcdiv(X, Y, P, value=0.7))
+    p = s.tensor_variable(P.reshape(-1).tolist(), [2, 3])
+    s.tensor_pow_(p, 2.0)
+    assert torch.allclose(s.tensor(p), P ** 2)
+    s.tensor_clamp_min_(p, 1.0)
+    assert float(s.tensor(p).min()) == 1.0
+    s.tensor_threshold_(p, threshold=2.0, value=-1.0)
+    assert torch.equal(s.tensor(p), torch.nn.functional.threshold((P ** 2).clamp_min(1.0), 2.0, -1.0))
+    z = s.zeros([4000])
+    s.manual_seed(3)
+    s.tensor_bernoulli_(z, 0.25)
+    assert set(s.tensor(z).unique().tolist()) <= {0.0, 1.0} and abs(s.tensor(z).mean().item() - 0.25) < 0.03
+    leaf = s.tensor_variable([0.5], [1], True)
+    with pytest.raises(RuntimeError):
+        s.tensor_erf_(leaf)
+
+
+def test_third_batch_samplers():
+    def draw(name, *args):
+        s = FrankenTorchSession(ledger_dispatch=False)
+        s.manual_seed(99)
+        return s.tensor(getattr(s, name)(*args, [20000], False))
+    vm = draw("tensor_von_mises", 0.5, 4.0)
+    assert float(vm.min()) > -math.pi - 1e-9 and float(vm.max()) <= math.pi + 1e-9
+    assert abs(torch.atan2(torch.sin(vm).mean(), torch.cos(vm).mean()).item() - 0.5) < 0.03          # circular mean
+    r = torch.sqrt(torch.sin(vm).mean() ** 2 + torch.cos(vm).mean() ** 2).item()                      # = I1(k)/I0(k)
+    assert abs(r - (torch.special.i1(torch.tensor(4.0)) / torch.i0(torch.tensor(4.0))).item()) < 0.02
+    assert abs(draw("tensor_von_mises", 0.0, 0.0).mean().item()) < 0.06                               # uniform on the circle
+    f = draw("tensor_fishersnedecor", 5.0, 8.0)
+    assert abs(f.mean().item() - 8.0 / 6.0) < 0.06 and float(f.min()) > 0
+    s = FrankenTorchSession(ledger_dispatch=False)
+    nb = s.tensor(s.tensor_negative_binomial(5, 0.3, [4000], False))
+    assert abs(nb.mean().item() - 5 * 0.3 / 0.7) < 0.12 and float(nb.min()) >= 0 and torch.equal(nb, nb.round())
