@@ -453,6 +453,7 @@ def main():
             for _ in range(3):
                 arm.step()
             hs = max(1, args.h2h_steps)
+            load_start = H.load_average_1m()
             h2h_sampler = ClockSampler(local_rank, "GPU-" + str(getattr(torch.cuda.get_device_properties(dev), "uuid", "")))
             h2h_sampler.start()
 
@@ -480,6 +481,14 @@ def main():
                                         incumbent_steps=H.parse_timed_steps(arm.timed_steps_line()) or ())
             vs_torch = dict(res.as_dict(), impl=arm.impl, steps_per_sample=hs, clocks=h2h_sampler.stop(),
                             **H.incumbent_provenance_block(version))
+            try:            # the window the ratio was taken in; a host record must never take the bench down
+                load_end = H.load_average_1m()
+                vs_torch["host"] = {
+                    "code_sha256": H.executing_code_sha256()[:16], "arm_ordering": H.arm_ordering_from_env().label(),
+                    "load_1m": [load_start, load_end], "load_drift_quotable": H.load_drift_is_quotable(load_start, load_end),
+                    "concurrent": H.concurrent_measurement_block(), "host": H.measurement_host_block().split("\n")[0]}
+            except Exception as e:      # noqa: BLE001
+                vs_torch["host"] = {"error": f"{type(e).__name__}: {e}"}
             arm.release()
             if hasattr(engine, "sync_parameters"):
                 engine.sync_parameters()

@@ -227,3 +227,58 @@ def test_buffer_pool_build_overwritten_with_a_poisoned_parked_buffer():
     assert P.recycle(torch.zeros(n, dtype=torch.float64)) and P.stats().parked == 1
     P.clear()
     assert P.stats().parked == 0 and P.stats().parked_bytes == 0 and P.try_take_exact(n) is None
+
+
+def test_measurement_host_provenance(tmp_path, monkeypatch):
+    """Host-side provenance of a head-to-head window (ft-api/src/harness_provenance.rs:140-830,
+    harness_interleave.rs:299-365)."""
+    import os
+    from frankentorch_b200 import harness as H
+    # load drift: steady load is quotable at any level, drift and missing readings are not
+    assert H.load_drift_is_quotable(8.63, 9.25) and H.load_drift_is_quotable(25.0, 26.0) and H.load_drift_is_quotable(0.2, 0.5)
+    assert not H.load_drift_is_quotable(8.0, 12.0) and not H.load_drift_is_quotable(12.0, 8.0)
+    assert not H.load_drift_is_quotable(None, 3.0) and not H.load_drift_is_quotable(3.0, None)
+    assert H.load_series_is_quotable([4.0, 4.4, 4.9]) and not H.load_series_is_quotable([4.0, 9.0, 4.1])
+    assert not H.load_series_is_quotable([4.0]) and not H.load_series_is_quotable([4.0, float("nan")]) and not H.load_series_is_quotable([4.0, -1.0])
+    assert H.load_series_drift([2.0, 3.0, 2.5]) == 1.5 and H.load_series_drift([0.1, 0.4]) == 1.0
+    assert H.load_series_drift([1.0]) is None and H.load_series_drift([1.0, float("inf")]) is None and H.MAX_LOAD_DRIFT == 1.25
+    l = H.load_average_1m()
+    assert l is None or l >= 0
+    # arm ordering
+    assert H.arm_ordering_from_env("") is H.ArmOrdering.Interleaved and H.arm_ordering_from_env(" TRUE ") is H.ArmOrdering.LegacyBlock
+    assert H.arm_ordering_from_env("yes") is H.ArmOrdering.LegacyBlock and H.arm_ordering_from_env("0") is H.ArmOrdering.Interleaved
+    assert H.ArmOrdering.Interleaved.is_quotable() and not H.ArmOrdering.LegacyBlock.is_quotable() and "NOT quotable" in H.ArmOrdering.LegacyBlock.label()
+    monkeypatch.setenv(H.LEGACY_BLOCK_ARMS_ENV, "1")
+    assert H.arm_ordering_from_env() is H.ArmOrdering.LegacyBlock
+    assert H.interpreter_args("print(1)") == ["-c", "print(1)"]
+    # code digest and the same-binary trap
+    d = H.executing_code_sha256()
+    assert len(d) == 64 and d == H.executing_code_sha256() == H.executing_elf_sha256()
+    assert H.identical_arm_digests(d, d + "\n".replace("\\\n", "")) is not None or True
+    assert "SAME code" in H.identical_arm_digests(d, " " + d + " ") and H.identical_arm_digests(d, "0" * 64) is None and H.identical_arm_digests("", "") is None
+    # host and clock blocks always render
+    hb = H.measurement_host_block(8)
+    assert hb.startswith("measurement_host=") and "cpu_threads=8" in hb and hb.split("\n")[-1].startswith("host_rule=")
+    cb = H.cpu_clock_block()
+    assert cb.startswith("cpu_mhz")
+    st = H.cpu_mhz_stats()
+    if st is not None:
+        lo, med, hi, spread = st
+        assert lo <= med <= hi and abs(spread - hi / lo) < 1e-9 and H.cpu_mhz_sorted() == sorted(H.cpu_mhz_sorted())
+        assert "pinned to the SAME core set [0-7]" in H.cpu_clock_block("0-7")
+    assert H.concurrent_measurement_block().startswith("concurrent_measurements=")
+    assert all(p != os.getpid() for p, _, _ in H.concurrent_measurement_processes())
+    # measurement slots: announce, see a live peer, reclaim a dead one
+    monkeypatch.setenv("FT_H2H_SLOT_DIR", str(tmp_path / "slots"))
+    slot, line = H.announce_measurement("lane_a")
+    assert slot is not None and "measurement_slot=held" in line and os.path.exists(slot.path) and "lanes=lane_a" in open(slot.path).read()
+    (tmp_path / "slots" / "999999.slot").write_text("pid=999999 host=x code=abc lanes=other\n")
+    (tmp_path / "slots" / "999998.slot").write_text("pid=999998 host=x code=abc lanes=dead\n")
+    slot2, line2 = H.announce_measurement("lane_b", is_live=lambda pid: pid == 999999)
+    assert "OVERLAPPED" in line2 and "lanes=other" in line2 and "lanes=dead" not in line2 and "no row from an overlapped window is quotable" in line2
+    assert not os.path.exists(tmp_path / "slots" / "999998.slot") and os.path.exists(tmp_path / "slots" / "999999.slot")
+    slot2.release()
+    assert not os.path.exists(slot.path)                       # same pid, same file: released
+    with H.announce_measurement("lane_c", is_live=lambda pid: False)[0] as s3:
+        assert os.path.exists(s3.path) and not os.path.exists(tmp_path / "slots" / "999999.slot")
+    assert not os.path.exists(s3.path)
