@@ -24,6 +24,7 @@ import torch
 from ._session_factories import _new, _numel
 from .core.dtype import DType
 from ._session_ops import _inplace
+from .autograd.tape import AutogradError
 
 
 def _opt(ids):
@@ -1180,6 +1181,143 @@ _INPLACE_TERNARY_OPS = ["addcdiv"]
 def tensor_bernoulli_(self, nid, p=0.5):
     """Fill with Bernoulli(p) draws of the session stream (1.0 where ``u < p``)."""
     return _fill_from(self, nid, (_u(self, self.tensor_numel(nid)) < float(p)).to(torch.float64))
+
+
+# ------------------------------------------------------------------------------------ custom functions over live inputs
+# The reference has one entry point per ownership pattern of a custom autograd function
+# (ft-autograd/src/lib.rs:9065 ``apply_function_f64_borrowed_inputs``, :9161 ``..._borrowed_forward``, :9250
+# ``..._saved_forward``, :9435 ``apply_function_f32_output_borrowed_inputs``, plus the create-graph forms).  Tensors
+# here are device buffers that the tape already holds by reference, so the patterns differ only in what the
+# backward closure receives and in which dtype is enforced.
+def _custom_inputs(self, inputs, dtype):
+    from .session import FunctionCtx
+    tape = self.tensor_tape
+    inputs = list(inputs)
+    vals = [tape.value(i) for i in inputs]
+    if dtype is not None:
+        for i, v in zip(inputs, vals):
+            if v.dtype != dtype:
+                raise AutogradError(f"custom function input {i} holds {v.dtype}; this entry point takes {dtype}")
+    ctx = FunctionCtx([tape.nodes[i].requires_grad and tape.grad_enabled for i in inputs])
+    return tape, inputs, vals, ctx
+
+
+def _check_versions(tape, inputs, versions):
+    from .autograd.tape import BorrowedInputVersionMismatch
+    for i, rec in zip(inputs, versions):
+        if tape.version(i) != rec:
+            raise BorrowedInputVersionMismatch(i, rec, tape.version(i))
+
+
+def _custom_record(self, tape, inputs, ctx, out, out_dtype, vjp, cg=None):
+    if out_dtype is not None and out.dtype != out_dtype:
+        raise AutogradError(f"custom function returned {out.dtype}; this entry point produces {out_dtype}")
+    self._record_dispatch("custom_function", any(ctx.needs_input_grad), "custom_function")
+    if not any(ctx.needs_input_grad):
+        return tape.leaf(out, requires_grad=False)
+    return tape.record("custom_function", inputs, out, vjp, "custom autograd function backward", cg=cg)
+
+
+def tensor_apply_function_borrowed_inputs(self, inputs, forward_fn, backward_fn, dtype=None, out_dtype=None) -> int:
+    """``forward_fn(ctx, tensors) -> tensor``; ``backward_fn(ctx, grad_out, tensors) -> grads`` re-reads the LIVE
+    inputs, so nothing is saved.  An input mutated in place between forward and backward is an error."""
+    tape, inputs, vals, ctx = _custom_inputs(self, inputs, dtype)
+    out = forward_fn(ctx, vals)
+    versions = [tape.version(i) for i in inputs]
+
+    def vjp(g, targets):
+        _check_versions(tape, inputs, versions)
+        return list(backward_fn(ctx, g, [tape.value(i) for i in inputs]))
+    return _custom_record(self, tape, inputs, ctx, out, out_dtype, vjp)
+
+
+def tensor_apply_function_f64_borrowed_inputs(self, inputs, forward_fn, backward_fn) -> int:
+    return tensor_apply_function_borrowed_inputs(self, inputs, forward_fn, backward_fn, torch.float64, torch.float64)
+
+
+def tensor_apply_function_f32_output_borrowed_inputs(self, inputs, forward_fn, backward_fn) -> int:
+    """f32 inputs and output; the incoming gradient and the returned input gradients stay in the tape's gradient
+    dtype (f64 by default), as in the reference's f32 conv / linear fast paths."""
+    return tensor_apply_function_borrowed_inputs(self, inputs, forward_fn, backward_fn, torch.float32, torch.float32)
+
+
+def tensor_apply_function_f64_borrowed_forward(self, inputs, forward_fn, backward_fn) -> int:
+    """The forward reads the inputs in place; ``backward_fn(ctx, grad_out)`` uses only what ``ctx`` saved."""
+    tape, inputs, vals, ctx = _custom_inputs(self, inputs, torch.float64)
+    out = forward_fn(ctx, vals)
+    return _custom_record(self, tape, inputs, ctx, out, torch.float64, lambda g, targets: list(backward_fn(ctx, g)))
+
+
+def tensor_apply_function_f64_saved_forward(self, inputs, forward_fn, backward_fn) -> int:
+    """``forward_fn(ctx) -> tensor``: the result was computed elsewhere (a fused loss cached by its producer) and
+    only has to be attached to ``inputs``; the inputs are not handed to the forward at all."""
+    tape, inputs, _, ctx = _custom_inputs(self, inputs, torch.float64)
+    out = forward_fn(ctx)
+    return _custom_record(self, tape, inputs, ctx, out, torch.float64, lambda g, targets: list(backward_fn(ctx, g)))
+
+
+def tensor_apply_function_with_create_graph_borrowed_inputs(self, inputs, forward_fn, backward_fn, dtype=None,
+                                                            out_dtype=None) -> int:
+    """Twice-differentiable form: ``backward_fn(session, ctx, grad_id, input_ids) -> node ids`` builds the input
+    gradients from session operators over the live input nodes (version-checked)."""
+    tape, inputs, vals, ctx = _custom_inputs(self, inputs, dtype)
+    out = forward_fn(ctx, vals)
+    versions = [tape.version(i) for i in inputs]
+
+    def vjp(g, targets):
+        _check_versions(tape, inputs, versions)
+        mark = len(tape)
+        prev, tape.grad_enabled = tape.grad_enabled, False
+        try:
+            ids = backward_fn(self, ctx, tape.leaf(g, requires_grad=False), inputs)
+            res = [None if i is None else tape.value(i) for i in ids]
+        finally:
+            tape.grad_enabled = prev
+        tape.truncate_graph_to(mark)
+        return res
+
+    def cg(g_id):
+        _check_versions(tape, inputs, versions)
+        prev, tape.grad_enabled = tape.grad_enabled, True
+        try:
+            return list(backward_fn(self, ctx, g_id, inputs))
+        finally:
+            tape.grad_enabled = prev
+    return _custom_record(self, tape, inputs, ctx, out, out_dtype, vjp, cg)
+
+
+def tensor_apply_function_f32_output_with_create_graph_borrowed_inputs(self, inputs, forward_fn, backward_fn) -> int:
+    return tensor_apply_function_with_create_graph_borrowed_inputs(self, inputs, forward_fn, backward_fn,
+                                                                   torch.float32, torch.float32)
+
+
+# value-level tape entry points under the session (the optimizer-facing forms of the reference)
+def _tape_forward(name):
+    def f(self, *args, **kwargs):
+        return getattr(self.tensor_tape, name)(*args, **kwargs)
+    f.__name__ = "tensor_" + name if not name.startswith("tensor_") else name
+    f.__doc__ = f"``TensorTape.{name}`` of this session's tape."
+    return f
+
+
+tensor_leaf_tensor = _tape_forward("leaf_tensor")
+tensor_leaf_f32 = _tape_forward("leaf_f32")
+tensor_set_requires_grad = _tape_forward("set_tensor_requires_grad")
+tensor_accumulated_gradient_values = _tape_forward("tensor_accumulated_gradient_values")
+tensor_set_accumulated_gradient = _tape_forward("set_tensor_accumulated_gradient")
+tensor_zero_accumulated_gradient = _tape_forward("zero_tensor_accumulated_gradient")
+tensor_update_values = _tape_forward("update_tensor_values")
+tensor_update_values_f32 = _tape_forward("update_tensor_values_f32")
+tensor_update_values_with = _tape_forward("update_tensor_values_with")
+tensor_update_values_with_accumulated_gradient = _tape_forward("update_tensor_values_with_accumulated_gradient")
+
+
+def tensor_to_f16(self, a):
+    return self.tensor_to_dtype(a, DType.F16)
+
+
+def tensor_to_bf16(self, a):
+    return self.tensor_to_dtype(a, DType.BF16)
 
 
 # ------------------------------------------------------------------------------------ installation

@@ -167,7 +167,8 @@ _generic("poisson_nll_loss", lambda x, t, log_input=True: TF.poisson_nll_loss(x,
 _generic("hinge_embedding_loss", lambda x, y, margin=1.0: TF.hinge_embedding_loss(x, y, margin=margin))
 _generic("soft_margin_loss", lambda x, y: TF.soft_margin_loss(x, y))
 _generic("margin_ranking_loss", lambda a, b, y, margin=0.0: TF.margin_ranking_loss(a, b, y, margin=margin))
-_generic("ctc_loss", lambda lp, t, il, tl, blank=0: TF.ctc_loss(lp, t.long(), il.long(), tl.long(), blank=blank))
+_generic("ctc_loss", lambda lp, t, il, tl, blank=0, reduction="mean", zero_infinity=False:
+         TF.ctc_loss(lp, t.long(), il.long(), tl.long(), blank=blank, reduction=reduction, zero_infinity=zero_infinity))
 
 
 def _focal(x, t, alpha=0.25, gamma=2.0):
@@ -193,8 +194,10 @@ _generic("conv_transpose1d", lambda x, w, b=None, stride=1, padding=0, output_pa
 _generic("conv_transpose2d", lambda x, w, b=None, stride=1, padding=0, output_padding=0, groups=1, dilation=1: TF.conv_transpose2d(x, w, b, stride, padding, output_padding, groups, dilation))
 _generic("conv_transpose3d", lambda x, w, b=None, stride=1, padding=0, output_padding=0, groups=1, dilation=1: TF.conv_transpose3d(x, w, b, stride, padding, output_padding, groups, dilation))
 for _d in (1, 2, 3):
-    _generic(f"avg_pool{_d}d", (lambda f: (lambda x, kernel_size=2, stride=None, padding=0: f(x, kernel_size, stride, padding)))(getattr(TF, f"avg_pool{_d}d")))
-    _generic(f"max_pool{_d}d", (lambda f: (lambda x, kernel_size=2, stride=None, padding=0: f(x, kernel_size, stride, padding)))(getattr(TF, f"max_pool{_d}d")))
+    _generic(f"avg_pool{_d}d", (lambda f: (lambda x, kernel_size=2, stride=None, padding=0, ceil_mode=False, count_include_pad=True:
+                                           f(x, kernel_size, stride, padding, ceil_mode, count_include_pad)))(getattr(TF, f"avg_pool{_d}d")))
+    _generic(f"max_pool{_d}d", (lambda f: (lambda x, kernel_size=2, stride=None, padding=0, dilation=1, ceil_mode=False:
+                                           f(x, kernel_size, stride, padding, dilation, ceil_mode)))(getattr(TF, f"max_pool{_d}d")))
     _generic(f"adaptive_avg_pool{_d}d", (lambda f: (lambda x, output_size=1: f(x, output_size)))(getattr(TF, f"adaptive_avg_pool{_d}d")))
     _generic(f"adaptive_max_pool{_d}d", (lambda f: (lambda x, output_size=1: f(x, output_size)))(getattr(TF, f"adaptive_max_pool{_d}d")))
 _generic("lp_pool1d", lambda x, norm_type=2.0, kernel_size=2: TF.lp_pool1d(x, norm_type, kernel_size))
@@ -215,7 +218,7 @@ _generic("pad_mode", lambda x, padding=(), mode="reflect": TF.pad(x, list(paddin
 _generic("embedding_bag", lambda w, ids, offsets, mode="mean": TF.embedding_bag(ids.long(), w, offsets.long(), mode=mode))
 _generic("bilinear", lambda a, b, w, bias=None: TF.bilinear(a, b, w, bias))
 _generic("cosine_similarity", lambda a, b, dim=1, eps=1e-8: TF.cosine_similarity(a, b, dim, eps))
-_generic("pairwise_distance", lambda a, b, p=2.0, eps=1e-6: TF.pairwise_distance(a, b, p, eps))
+_generic("pairwise_distance", lambda a, b, p=2.0, eps=1e-6, keepdim=False: TF.pairwise_distance(a, b, p, eps, keepdim))
 _generic("cdist", lambda a, b, p=2.0: torch.cdist(a, b, p))
 _generic("pdist", lambda a, p=2.0: TF.pdist(a, p))
 _generic("glu", lambda x, dim=-1: TF.glu(x, dim))

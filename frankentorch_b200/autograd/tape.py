@@ -169,6 +169,10 @@ class TensorBackwardReport:
     def gradient_node(self, node: int) -> Optional[int]:
         return self.gradient_nodes.get(int(node))
 
+    def is_sparse_gradient(self, node: int) -> bool:
+        """Whether the whole gradient of ``node`` arrived row-sparse in this backward."""
+        return int(node) in self.sparse_gradients
+
     def gradient_value(self, node: int) -> Optional["GradientValue"]:
         """The gradient of ``node`` in the form it was produced: dense, or row-sparse for a table read through
         ``index_select_sparse`` (ft-autograd/src/lib.rs:1113 ``GradientValue``)."""
@@ -549,6 +553,134 @@ class TensorTape:
             raise TensorRequiresGradNonLeaf(f"node {nid} is not a leaf")
         n.grad_buffer = buf
         n.grad_buffer_filled = False
+
+    # ------------------------------------------------------------------ value-level entry points
+    # The reference's tape is also usable without a session: leaves are made from dense tensors or value
+    # lists, parameters are updated in place by an optimizer, and the persistent gradient is read, set and
+    # cleared by node id (ft-autograd/src/lib.rs:4490 ``set_tensor_requires_grad``, :4512
+    # ``detach_tensor_in_place``, :4570 ``leaf_tensor``, :4614-4651 the accumulated-gradient accessors, :4653
+    # ``leaf_f32``, :4798-4811 ``to_f16 / to_bf16 / to_dtype``, :21239-21290 ``update_tensor_values*``).
+    def leaf_tensor(self, tensor, requires_grad: bool = False) -> int:
+        """Leaf over a :class:`DenseTensor` (its buffer is shared, not copied).  Under ``set_grad_enabled(False)``
+        the leaf does not require grad, whatever was asked."""
+        data = tensor.data if hasattr(tensor, "data") and not isinstance(tensor, torch.Tensor) else tensor
+        return self.leaf(data, requires_grad and self.grad_enabled)
+
+    def leaf_f32(self, values, shape, requires_grad: bool = False) -> int:
+        t = torch.as_tensor(values, dtype=torch.float32)
+        if t.numel() != int(torch.Size(shape).numel()):
+            raise AutogradError(f"leaf_f32: {t.numel()} values do not fill shape {tuple(shape)}")
+        return self.leaf(t.reshape(tuple(shape)).clone(), requires_grad and self.grad_enabled)
+
+    def leaf_f64(self, values, shape, requires_grad: bool = False) -> int:
+        t = torch.as_tensor(values, dtype=torch.float64)
+        if t.numel() != int(torch.Size(shape).numel()):
+            raise AutogradError(f"leaf_f64: {t.numel()} values do not fill shape {tuple(shape)}")
+        return self.leaf(t.reshape(tuple(shape)).clone(), requires_grad and self.grad_enabled)
+
+    def values(self, nid: int) -> list:
+        return self._node(nid).value.detach().reshape(-1).to("cpu", torch.float64).tolist()
+
+    def values_f32(self, nid: int) -> torch.Tensor:
+        v = self._node(nid).value
+        if v.dtype != torch.float32:
+            raise AutogradError(f"node {nid} holds {v.dtype}, not float32")
+        return v.detach().reshape(-1)
+
+    def set_tensor_requires_grad(self, nid: int, requires_grad: bool) -> None:
+        self.requires_grad_(nid, requires_grad)
+
+    def detach_tensor_in_place(self, nid: int) -> None:
+        self.detach_in_place(nid)
+        self.zero_accumulated_gradient(nid)
+
+    def tensor_accumulated_gradient(self, nid: int) -> Optional[torch.Tensor]:
+        return self.accumulated_gradient(nid)
+
+    def tensor_accumulated_gradient_values(self, nid: int) -> Optional[list]:
+        g = self.accumulated_gradient(nid)
+        return None if g is None else g.detach().reshape(-1).to("cpu", torch.float64).tolist()
+
+    def tensor_accumulated_gradient_len(self, nid: int) -> Optional[int]:
+        g = self.accumulated_gradient(nid)
+        return None if g is None else g.numel()
+
+    def set_tensor_accumulated_gradient(self, nid: int, gradient) -> None:
+        """Replace the persistent gradient; the length must be the node's element count."""
+        v = self._node(nid).value
+        g = torch.as_tensor(gradient, dtype=self.grad_dtype or v.dtype, device=v.device)
+        if g.numel() != v.numel():
+            raise TensorGradientShapeMismatch(f"node {nid}: gradient has {g.numel()} elements, the tensor {v.numel()}")
+        self.set_accumulated_gradient(nid, g.reshape(v.shape))
+
+    def zero_tensor_accumulated_gradient(self, nid: int) -> None:
+        """Fill the persistent gradient with zeros, keeping it allocated (a node without one stays without)."""
+        n = self._node(nid)
+        if n.grad_buffer is not None:
+            n.grad_buffer.zero_()
+        elif n.grad is not None or n.sparse_grad is not None:
+            shape = n.value.shape
+            n.grad = torch.zeros(shape, dtype=(n.grad.dtype if n.grad is not None else self.grad_dtype or n.value.dtype),
+                                 device=n.value.device)
+            n.sparse_grad = None
+
+    def update_tensor_values(self, nid: int, new_values) -> None:
+        """Overwrite a node's values in place; the version counter moves, so a backward that saved the old
+        contents by reference refuses to run."""
+        n = self._node(nid)
+        src = torch.as_tensor(new_values, dtype=n.value.dtype, device=n.value.device)
+        if src.numel() != n.value.numel():
+            raise AutogradError(f"node {nid}: update has {src.numel()} values, the tensor {n.value.numel()}")
+        with torch.no_grad():
+            n.value.copy_(src.reshape(n.value.shape))
+        n.version += 1
+
+    def update_tensor_values_f32(self, nid: int, new_values) -> None:
+        if self._node(nid).value.dtype != torch.float32:
+            raise AutogradError(f"node {nid} holds {self._node(nid).value.dtype}, not float32")
+        self.update_tensor_values(nid, new_values)
+
+    def update_tensor_values_with(self, nid: int, update: Callable[[torch.Tensor], None]) -> None:
+        """``update(values)`` mutates the node's buffer in place (one version bump)."""
+        n = self._node(nid)
+        with torch.no_grad():
+            update(n.value)
+        n.version += 1
+
+    def update_tensor_values_with_accumulated_gradient(self, nid: int,
+                                                       update: Callable[[torch.Tensor, torch.Tensor], None]) -> bool:
+        """``update(gradient, values)`` for an optimizer step without copying either; False (and no call) when
+        the node has no persistent gradient."""
+        n = self._node(nid)
+        g = self.accumulated_gradient(nid)
+        if g is None:
+            return False
+        with torch.no_grad():
+            update(g, n.value)
+        n.version += 1
+        return True
+
+    def to_dtype(self, nid: int, dtype) -> int:
+        """Differentiable cast between floating dtypes; the gradient is cast back to the input's dtype.  The
+        input is returned as it is when it already has the dtype; integer, bool, complex and quantized targets
+        are refused."""
+        tdt = dtype if isinstance(dtype, torch.dtype) else dtype.to_torch()
+        if tdt not in (torch.float16, torch.bfloat16, torch.float32, torch.float64):
+            raise AutogradError(f"to_dtype: unsupported target {tdt}")
+        v = self._node(nid).value
+        if not v.is_floating_point():
+            raise AutogradError(f"to_dtype: node {nid} holds {v.dtype}, not a floating dtype")
+        if v.dtype == tdt:
+            return nid
+        src = v.dtype
+        return self.record("to_dtype", [nid], v.to(tdt), lambda g, targets: [g.to(src) if self.grad_dtype is None else g],
+                           "cast: gradient passes through in the input dtype")
+
+    def to_f16(self, nid: int) -> int:
+        return self.to_dtype(nid, torch.float16)
+
+    def to_bf16(self, nid: int) -> int:
+        return self.to_dtype(nid, torch.bfloat16)
 
     # ------------------------------------------------------------------ backward
     def schedule(self, root: int, check_consumed: bool = True):

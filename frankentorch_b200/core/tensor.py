@@ -117,6 +117,105 @@ class DenseTensor:
         zp = torch.tensor(q.zero_points(), dtype=torch.float64).reshape(shape)
         return ((codes - zp) * sc).contiguous().reshape(-1).tolist()
 
+    # ------------------------------------------------------------------ per-dtype forms
+    # The reference spells one constructor and one accessor per storage variant
+    # (ft-core/src/lib.rs:1178-1245 ``from_storage_f64 / _f64_inline4 / _f32 / _f16 / _bf16 / _qint8 / _quint8``,
+    # :1247-1370 ``from_contiguous_values_<dtype>``, :1392-1466 ``dispatch_values`` /
+    # ``contiguous_values_<dtype>[_mut]``, :1778 ``update_contiguous_values_f32``).  Here they are the generic
+    # forms with the dtype pinned and the same refusals: a meta of another dtype, a strided layout.
+    @staticmethod
+    def _from_storage_of(dtype: DType, meta: TensorMeta, values) -> "DenseTensor":
+        if meta.dtype != dtype:
+            raise DenseTensorError(f"unsupported dtype {meta.dtype.value} for a {dtype.value} buffer")
+        return DenseTensor.from_storage(meta, values)
+
+    @staticmethod
+    def from_storage_f64(meta, values): return DenseTensor._from_storage_of(DType.F64, meta, values)          # noqa: E704
+    @staticmethod
+    def from_storage_f32(meta, values): return DenseTensor._from_storage_of(DType.F32, meta, values)          # noqa: E704
+    @staticmethod
+    def from_storage_f16(meta, values): return DenseTensor._from_storage_of(DType.F16, meta, values)          # noqa: E704
+    @staticmethod
+    def from_storage_bf16(meta, values): return DenseTensor._from_storage_of(DType.BF16, meta, values)        # noqa: E704
+    @staticmethod
+    def from_storage_qint8(meta, values): return DenseTensor._from_storage_of(DType.QInt8, meta, values)      # noqa: E704
+    @staticmethod
+    def from_storage_quint8(meta, values): return DenseTensor._from_storage_of(DType.QUInt8, meta, values)    # noqa: E704
+
+    @staticmethod
+    def from_storage_f64_inline4(meta: TensorMeta, values) -> "DenseTensor":
+        """A tensor of at most four f64 values held inline (no heap buffer in the reference; a 4-element buffer
+        here): scalar losses and tiny parameters."""
+        values = list(values)
+        if len(values) != 4:
+            raise DenseTensorError(f"inline storage holds exactly 4 values, got {len(values)}")
+        return DenseTensor._from_storage_of(DType.F64, meta, values)
+
+    @staticmethod
+    def from_contiguous_values_f32(values, shape, device=Device.Cpu): return DenseTensor.from_contiguous_values(values, shape, device, DType.F32)    # noqa: E704
+    @staticmethod
+    def from_contiguous_values_f16(values, shape, device=Device.Cpu): return DenseTensor.from_contiguous_values(values, shape, device, DType.F16)    # noqa: E704
+    @staticmethod
+    def from_contiguous_values_bf16(values, shape, device=Device.Cpu): return DenseTensor.from_contiguous_values(values, shape, device, DType.BF16)  # noqa: E704
+
+    @staticmethod
+    def from_contiguous_values_qint8(codes, shape, scale: float, zero_point: int) -> "DenseTensor":
+        return DenseTensor.from_contiguous_values_quantized(codes, shape, DType.QInt8, scale, zero_point)
+
+    @staticmethod
+    def from_contiguous_values_quint8(codes, shape, scale: float, zero_point: int) -> "DenseTensor":
+        return DenseTensor.from_contiguous_values_quantized(codes, shape, DType.QUInt8, scale, zero_point)
+
+    @staticmethod
+    def from_contiguous_values_qint8_per_channel(codes, shape, scales, zero_points, axis: int) -> "DenseTensor":
+        return DenseTensor.from_contiguous_values_quantized_per_channel(codes, shape, DType.QInt8, scales, zero_points, axis)
+
+    @staticmethod
+    def from_contiguous_values_quint8_per_channel(codes, shape, scales, zero_points, axis: int) -> "DenseTensor":
+        return DenseTensor.from_contiguous_values_quantized_per_channel(codes, shape, DType.QUInt8, scales, zero_points, axis)
+
+    def _typed_view(self, want: DType, contiguous: bool = True) -> torch.Tensor:
+        have = self.meta.dtype
+        if have != want:
+            raise DenseTensorError(f"unsupported dtype {have.value}: this accessor reads {want.value}")
+        if contiguous and not self.data.is_contiguous():
+            raise DenseTensorError("unsupported layout: the tensor is not contiguous")
+        return self.data
+
+    def dispatch_values(self) -> torch.Tensor:
+        """The f64 storage span the layout covers, from the view's offset to its last element, as a flat
+        zero-copy tensor: what a kernel that applies the strides itself receives (a strided view is allowed)."""
+        t = self._typed_view(DType.F64, contiguous=False)
+        if t.numel() == 0:
+            return t.reshape(-1)
+        span = 1 + sum((n - 1) * st for n, st in zip(t.shape, t.stride()))
+        return torch.as_strided(t, (span,), (1,), t.storage_offset())
+
+    def contiguous_values_f32(self) -> torch.Tensor:
+        """The values of a contiguous f32 tensor as a flat zero-copy tensor."""
+        return self._typed_view(DType.F32).reshape(-1)
+
+    def contiguous_values_f32_mut(self) -> torch.Tensor:
+        """The same, for writing: an inference-only consumer overwrites a dead intermediate in place.  The
+        version counter moves, so a tape node that borrowed the old contents is caught at backward."""
+        out = self._typed_view(DType.F32).reshape(-1)
+        self._version[0] += 1
+        return out
+
+    def contiguous_values_qint8(self) -> torch.Tensor:
+        return self._typed_view(DType.QInt8).reshape(-1)
+
+    def contiguous_values_quint8(self) -> torch.Tensor:
+        return self._typed_view(DType.QUInt8).reshape(-1)
+
+    def update_contiguous_values_f32(self, values) -> None:
+        dst = self._typed_view(DType.F32)
+        src = torch.as_tensor(values, dtype=torch.float32).reshape(-1)
+        if src.numel() != dst.numel():
+            raise DenseTensorError(f"insufficient storage: needed {dst.numel()}, got {src.numel()}")
+        dst.reshape(-1).copy_(src)
+        self._version[0] += 1
+
     # ------------------------------------------------------------------ metadata
     @property
     def meta(self) -> TensorMeta:

@@ -17,3 +17,5 @@ from .utils import (MinMaxObserver, PackedSequence, QParams, QuantizedLinear, Qu
                     QuantizedLinearWeightStorage, QuantizedStorageDType, SpectralNorm, WeightNorm, dequantize,
                     pack_padded_sequence, pack_sequence, pad_packed_sequence, pad_sequence, quantize_per_tensor,
                     spectral_norm, weight_norm, weight_norm_decompose, weight_norm_reconstruct)
+from . import builders  # noqa: F401,E402  (reference-style constructors and named forwards, attached to the classes above)
+from .utils import qint8_range, quint8_range  # noqa: F401,E402

@@ -52,6 +52,10 @@ class MultiheadAttention(Module):
         kh = self._split(session, self.k_proj(session, k))
         vh = self._split(session, self.v_proj(session, v))
         mask = attn_mask
+        if mask is not None and session.tensor(mask).dtype == torch.bool:
+            # module convention (as torch.nn.MultiheadAttention): True = this key is blocked for this query
+            m = session.tensor(mask)
+            mask = session.tensor_tape.leaf(torch.zeros_like(m, dtype=session.tensor(q).dtype).masked_fill(m, float("-inf")), False)
         if key_padding_mask is not None:
             kp = session.tensor(key_padding_mask).bool()            # [N, Sk], True = ignore
             add = torch.zeros(n, 1, 1, sk, dtype=session.tensor(q).dtype, device=session.device)
@@ -67,8 +71,9 @@ class MultiheadAttention(Module):
         o = session.tensor_reshape(o, shape=(n, sq, self.embed_dim))
         return self.out_proj(session, o)
 
-    def forward(self, session, x, attn_mask: Optional[int] = None, is_causal: bool = False):
-        return self.forward_qkv(session, x, x, x, attn_mask, is_causal)
+    def forward(self, session, x, attn_mask: Optional[int] = None, is_causal: bool = False,
+                key_padding_mask: Optional[int] = None):
+        return self.forward_qkv(session, x, x, x, attn_mask, is_causal, key_padding_mask)
 
     def forward_qkv_with_weights(self, session, q, k, v, attn_mask: Optional[int] = None, is_causal: bool = False,
                                  average_attn_weights: bool = True):
@@ -132,12 +137,24 @@ class TransformerEncoderLayer(Module):
         h = session.tensor_relu(h) if self.activation == "relu" else session.tensor_gelu(h)
         return self.dropout2(session, self.linear2(session, self.dropout(session, h)))
 
-    def forward(self, session, x, src_mask: Optional[int] = None, is_causal: bool = False):
+    def forward(self, session, x, src_mask: Optional[int] = None, is_causal: bool = False,
+                src_key_padding_mask: Optional[int] = None):
+        """``src_mask`` is ``[S, S]`` (bool: True = blocked, or additive); ``src_key_padding_mask`` is ``[N, S]``
+        with True at padded keys, which no query attends to."""
+        sa = lambda t: self.self_attn(session, t, src_mask, is_causal, src_key_padding_mask)   # noqa: E731
         if self.norm_first:
-            x = session.tensor_add(x, self.dropout1(session, self.self_attn(session, self.norm1(session, x), src_mask, is_causal)))
+            x = session.tensor_add(x, self.dropout1(session, sa(self.norm1(session, x))))
             return session.tensor_add(x, self._ff(session, self.norm2(session, x)))
-        x = self.norm1(session, session.tensor_add(x, self.dropout1(session, self.self_attn(session, x, src_mask, is_causal))))
+        x = self.norm1(session, session.tensor_add(x, self.dropout1(session, sa(x))))
         return self.norm2(session, session.tensor_add(x, self._ff(session, x)))
+
+    def forward_layer(self, session, src):
+        """ft-nn/src/lib.rs:14696."""
+        return self.forward(session, src)
+
+    def forward_layer_masked(self, session, src, src_mask=None, src_key_padding_mask=None, is_causal: bool = False):
+        """ft-nn/src/lib.rs:14709 (the reference's argument order)."""
+        return self.forward(session, src, src_mask, is_causal, src_key_padding_mask)
 
 
 class TransformerEncoder(Module):
@@ -148,10 +165,15 @@ class TransformerEncoder(Module):
             self.norm = norm
         self._has_norm = norm is not None
 
-    def forward(self, session, x, mask: Optional[int] = None, is_causal: bool = False):
+    def forward(self, session, x, mask: Optional[int] = None, is_causal: bool = False,
+                src_key_padding_mask: Optional[int] = None):
         for l in self.layers:
-            x = l(session, x, mask, is_causal)
+            x = l(session, x, mask, is_causal, src_key_padding_mask)
         return self.norm(session, x) if self._has_norm else x
+
+    def forward_masked(self, session, src, mask=None, src_key_padding_mask=None, is_causal: bool = False):
+        """ft-nn/src/lib.rs:14856."""
+        return self.forward(session, src, mask, is_causal, src_key_padding_mask)
 
 
 class TransformerDecoderLayer(Module):
@@ -175,16 +197,29 @@ class TransformerDecoderLayer(Module):
         return self.dropout3(session, self.linear2(session, self.dropout(session, h)))
 
     def forward(self, session, tgt, memory, tgt_mask: Optional[int] = None, memory_mask: Optional[int] = None,
-                tgt_is_causal: bool = False):
+                tgt_is_causal: bool = False, tgt_key_padding_mask: Optional[int] = None,
+                memory_key_padding_mask: Optional[int] = None, memory_is_causal: bool = False):
         add = session.tensor_add
+        sa = lambda t: self.self_attn(session, t, tgt_mask, tgt_is_causal, tgt_key_padding_mask)   # noqa: E731
+        ca = lambda t: self.multihead_attn.forward_qkv(session, t, memory, memory, memory_mask, memory_is_causal,   # noqa: E731
+                                                       memory_key_padding_mask)
         if self.norm_first:
-            t = self.norm1(session, tgt)
-            x = add(tgt, self.dropout1(session, self.self_attn(session, t, tgt_mask, tgt_is_causal)))
-            x = add(x, self.dropout2(session, self.multihead_attn.forward_qkv(session, self.norm2(session, x), memory, memory, memory_mask)))
+            x = add(tgt, self.dropout1(session, sa(self.norm1(session, tgt))))
+            x = add(x, self.dropout2(session, ca(self.norm2(session, x))))
             return add(x, self._ff(session, self.norm3(session, x)))
-        x = self.norm1(session, add(tgt, self.dropout1(session, self.self_attn(session, tgt, tgt_mask, tgt_is_causal))))
-        x = self.norm2(session, add(x, self.dropout2(session, self.multihead_attn.forward_qkv(session, x, memory, memory, memory_mask))))
+        x = self.norm1(session, add(tgt, self.dropout1(session, sa(tgt))))
+        x = self.norm2(session, add(x, self.dropout2(session, ca(x))))
         return self.norm3(session, add(x, self._ff(session, x)))
+
+    def forward_layer(self, session, tgt, memory):
+        """ft-nn/src/lib.rs:15066."""
+        return self.forward(session, tgt, memory)
+
+    def forward_layer_masked(self, session, tgt, memory, tgt_mask=None, memory_mask=None, tgt_key_padding_mask=None,
+                             memory_key_padding_mask=None, tgt_is_causal: bool = False, memory_is_causal: bool = False):
+        """ft-nn/src/lib.rs:15082 (the reference's argument order)."""
+        return self.forward(session, tgt, memory, tgt_mask, memory_mask, tgt_is_causal, tgt_key_padding_mask,
+                            memory_key_padding_mask, memory_is_causal)
 
 
 class TransformerDecoder(Module):
@@ -195,11 +230,23 @@ class TransformerDecoder(Module):
             self.norm = norm
         self._has_norm = norm is not None
 
-    def forward(self, session, tgt, memory, tgt_mask=None, memory_mask=None, tgt_is_causal=False):
+    def forward(self, session, tgt, memory, tgt_mask=None, memory_mask=None, tgt_is_causal=False,
+                tgt_key_padding_mask=None, memory_key_padding_mask=None, memory_is_causal=False):
         x = tgt
         for l in self.layers:
-            x = l(session, x, memory, tgt_mask, memory_mask, tgt_is_causal)
+            x = l(session, x, memory, tgt_mask, memory_mask, tgt_is_causal, tgt_key_padding_mask,
+                  memory_key_padding_mask, memory_is_causal)
         return self.norm(session, x) if self._has_norm else x
+
+    def forward_decoder(self, session, tgt, memory):
+        """ft-nn/src/lib.rs:15277."""
+        return self.forward(session, tgt, memory)
+
+    def forward_decoder_masked(self, session, tgt, memory, tgt_mask=None, memory_mask=None, tgt_key_padding_mask=None,
+                               memory_key_padding_mask=None, tgt_is_causal: bool = False, memory_is_causal: bool = False):
+        """ft-nn/src/lib.rs:15292."""
+        return self.forward(session, tgt, memory, tgt_mask, memory_mask, tgt_is_causal, tgt_key_padding_mask,
+                            memory_key_padding_mask, memory_is_causal)
 
 
 class Transformer(Module):
@@ -212,9 +259,22 @@ class Transformer(Module):
         self.encoder = TransformerEncoder(session, enc, num_encoder_layers, LayerNorm(session, d_model))
         self.decoder = TransformerDecoder(session, dec, num_decoder_layers, LayerNorm(session, d_model))
 
-    def forward(self, session, src, tgt, src_mask=None, tgt_mask=None, memory_mask=None):
-        memory = self.encoder(session, src, src_mask)
-        return self.decoder(session, tgt, memory, tgt_mask, memory_mask)
+    def forward(self, session, src, tgt, src_mask=None, tgt_mask=None, memory_mask=None, src_key_padding_mask=None,
+                tgt_key_padding_mask=None, memory_key_padding_mask=None, tgt_is_causal: bool = False):
+        memory = self.encoder(session, src, src_mask, False, src_key_padding_mask)
+        return self.decoder(session, tgt, memory, tgt_mask, memory_mask, tgt_is_causal, tgt_key_padding_mask,
+                            memory_key_padding_mask)
+
+    def forward_transformer(self, session, src, tgt):
+        """ft-nn/src/lib.rs:15449."""
+        return self.forward(session, src, tgt)
+
+    def forward_transformer_masked(self, session, src, tgt, src_mask=None, tgt_mask=None, memory_mask=None,
+                                   src_key_padding_mask=None, tgt_key_padding_mask=None, memory_key_padding_mask=None,
+                                   tgt_is_causal: bool = False):
+        """ft-nn/src/lib.rs:15469."""
+        return self.forward(session, src, tgt, src_mask, tgt_mask, memory_mask, src_key_padding_mask,
+                            tgt_key_padding_mask, memory_key_padding_mask, tgt_is_causal)
 
 
 # -------------------------------------------------------------------------------------- recurrent
@@ -232,6 +292,11 @@ class _CellBase(Module):
         P = self._parameters
         return (session.tensor_linear(x, P["weight_ih"], P["bias_ih"]),
                 session.tensor_linear(h, P["weight_hh"], P["bias_hh"]))
+
+    def forward_cell(self, session, x, hx):
+        """One step under the reference's name (ft-nn/src/lib.rs:12576, :12738); ``hx`` is the hidden state, or the
+        ``(h, c)`` pair of an LSTM cell."""
+        return self.forward(session, x, hx)
 
 
 class RNNCell(_CellBase):
@@ -278,49 +343,105 @@ class GRUCell(_CellBase):
 
 
 class _Recurrent(Module):
-    """Multi-layer, batch-first, unidirectional recurrent stack built from cells."""
+    """Multi-layer recurrent stack built from cells, one cell per (layer, direction).
+
+    Reference: ft-nn/src/lib.rs:13195 (``LSTM::new``: ``bidirectional``, ``dropout`` between layers,
+    ``batch_first``), :13271 ``forward_lstm``, :13778 ``forward_gru``, :14245 ``forward_rnn``.  A bidirectional
+    layer runs a second cell over the reversed sequence and concatenates the two outputs on the feature axis,
+    so the next layer reads ``2 * hidden_size`` features.  States are ordered ``layer * num_directions +
+    direction``, as in torch.  ``forward`` takes and returns per-cell lists of ``[N, H]`` nodes;
+    ``forward_rnn / forward_gru / forward_lstm`` take and return the stacked ``[L * D, N, H]`` form."""
 
     cell_cls = RNNCell
     has_cell_state = False
 
     def __init__(self, session, input_size: int, hidden_size: int, num_layers: int = 1, bias: bool = True,
-                 dropout: float = 0.0):
+                 dropout: float = 0.0, bidirectional: bool = False, batch_first: bool = True):
         super().__init__()
-        self.hidden_size, self.num_layers = hidden_size, num_layers
-        self.cells = ModuleList([self.cell_cls(session, input_size if l == 0 else hidden_size, hidden_size, bias)
-                                 for l in range(num_layers)])
+        if num_layers < 1:
+            raise ValueError(f"{type(self).__name__} num_layers must be >= 1")
+        if not (math.isfinite(dropout) and 0.0 <= dropout <= 1.0):
+            raise ValueError(f"{type(self).__name__} dropout probability must be finite and in [0, 1]")
+        self.input_size, self.hidden_size, self.num_layers = input_size, hidden_size, num_layers
+        self.bidirectional, self.batch_first = bool(bidirectional), bool(batch_first)
+        d = self.num_directions
+        self.cells = ModuleList([self.cell_cls(session, input_size if l == 0 else hidden_size * d, hidden_size, bias)
+                                 for l in range(num_layers) for _ in range(d)])
         self.drop = Dropout(dropout)
 
+    @property
+    def num_directions(self) -> int:
+        return 2 if self.bidirectional else 1
+
+    def is_bidirectional(self) -> bool:
+        return self.bidirectional
+
+    def _run_cell(self, session, cell, steps, h, c):
+        outs = []
+        for t in steps:
+            if self.has_cell_state:
+                h, c = cell(session, t, (h, c))
+            else:
+                h = cell(session, t, h)
+            outs.append(h)
+        return outs, h, c
+
     def forward(self, session, x, state=None):
-        n, s, _ = session.tensor_shape(x)
-        steps = session.tensor_unbind(x, dim=1)
-        hs: List = []
-        for l, cell in enumerate(self.cells):
-            h = session.zeros([n, self.hidden_size], dtype=session.tensor_dtype(x)) if state is None else state[0][l]
-            c = (session.zeros([n, self.hidden_size], dtype=session.tensor_dtype(x)) if state is None else state[1][l]) \
-                if self.has_cell_state else None
-            outs = []
-            for t in steps:
-                if self.has_cell_state:
-                    h, c = cell(session, t, (h, c))
-                else:
-                    h = cell(session, t, h)
-                outs.append(h)
-            hs.append((h, c))
+        time_dim = 1 if self.batch_first else 0
+        shape = session.tensor_shape(x)
+        if len(shape) != 3:
+            raise ValueError(f"{type(self).__name__} expects a 3-D input, got shape {tuple(shape)}")
+        n = shape[0] if self.batch_first else shape[1]
+        steps = session.tensor_unbind(x, dim=time_dim)
+        d, dt = self.num_directions, session.tensor_dtype(x)
+        if state is not None and len(state[0]) != self.num_layers * d:
+            raise ValueError(f"initial state has {len(state[0])} entries, the stack has {self.num_layers * d} cells")
+        finals: List = []
+        for l in range(self.num_layers):
+            per_dir = []
+            for k in range(d):
+                idx = l * d + k
+                h = session.zeros([n, self.hidden_size], dtype=dt) if state is None else state[0][idx]
+                c = (session.zeros([n, self.hidden_size], dtype=dt) if state is None else state[1][idx]) \
+                    if self.has_cell_state else None
+                seq = steps if k == 0 else steps[::-1]
+                outs, h, c = self._run_cell(session, self.cells[idx], seq, h, c)
+                per_dir.append(outs if k == 0 else outs[::-1])
+                finals.append((h, c))
+            outs = per_dir[0] if d == 1 else [session.tensor_cat([f, r], dim=1) for f, r in zip(*per_dir)]
             steps = [self.drop(session, o) for o in outs] if l + 1 < self.num_layers else outs
-        out = session.tensor_stack(steps, dim=1)
+        out = session.tensor_stack(steps, dim=time_dim)
         if self.has_cell_state:
-            return out, ([h for h, _ in hs], [c for _, c in hs])
-        return out, [h for h, _ in hs]
+            return out, ([h for h, _ in finals], [c for _, c in finals])
+        return out, [h for h, _ in finals]
+
+    def _split_state(self, session, packed):
+        return None if packed is None else list(session.tensor_unbind(packed, dim=0))
+
+    def _forward_packed(self, session, x, h_0=None, c_0=None):
+        hs = self._split_state(session, h_0)
+        if self.has_cell_state:
+            if (h_0 is None) != (c_0 is None):
+                raise ValueError("LSTM takes both initial states or neither")
+            state = None if hs is None else (hs, self._split_state(session, c_0))
+        else:
+            state = None if hs is None else (hs, None)
+        out, fin = _Recurrent.forward(self, session, x, state)
+        if self.has_cell_state:
+            return out, session.tensor_stack(fin[0], dim=0), session.tensor_stack(fin[1], dim=0)
+        return out, session.tensor_stack(fin, dim=0), None
 
 
 class RNN(_Recurrent):
     cell_cls = RNNCell
 
     def forward(self, session, x, state=None):
-        st = None if state is None else (state, None)
-        r = super().forward(session, x, st)
-        return r
+        return super().forward(session, x, None if state is None else (state, None))
+
+    def forward_rnn(self, session, x, h_0=None):
+        from .extra import RNNOutput
+        out, h_n, _ = self._forward_packed(session, x, h_0)
+        return RNNOutput(out, h_n)
 
 
 class GRU(_Recurrent):
@@ -329,10 +450,20 @@ class GRU(_Recurrent):
     def forward(self, session, x, state=None):
         return super().forward(session, x, None if state is None else (state, None))
 
+    def forward_gru(self, session, x, h_0=None):
+        from .extra import GRUOutput
+        out, h_n, _ = self._forward_packed(session, x, h_0)
+        return GRUOutput(out, h_n)
+
 
 class LSTM(_Recurrent):
     cell_cls = LSTMCell
     has_cell_state = True
+
+    def forward_lstm(self, session, x, h_0=None, c_0=None):
+        from .extra import LSTMOutput
+        out, h_n, c_n = self._forward_packed(session, x, h_0, c_0)
+        return LSTMOutput(out, h_n, c_n)
 
 
 # -------------------------------------------------------------------------------------- losses

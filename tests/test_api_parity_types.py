@@ -603,3 +603,171 @@ def test_ftsv_rejects_an_extent_beyond_the_index_range_even_next_to_a_zero_exten
     with pytest.raises(S.SerializeError) as e:
         S.load_state_dict_from_bytes(bytes(blob3))
     assert e.value.kind == "ShapeOverflow"
+
+
+# ----------------------------------------------------------------------------- per-dtype tensor forms, value-level tape
+def test_dense_tensor_per_dtype_constructors_and_accessors():
+    import torch
+    from frankentorch_b200.core.dtype import DType
+    from frankentorch_b200.core.meta import Device, TensorMeta
+    from frankentorch_b200.core.tensor import DenseTensor, DenseTensorError
+
+    t = DenseTensor.from_contiguous_values_f32([1, 2, 3, 4, 5, 6], [2, 3])
+    assert t.meta.dtype is DType.F32 and t.contiguous_values_f32().tolist() == [1, 2, 3, 4, 5, 6] and t.version == 0
+    t.update_contiguous_values_f32([0.0] * 6)
+    assert t.version == 1
+    t.contiguous_values_f32_mut().add_(2.0)
+    assert t.version == 2 and t.contiguous_values_f32().tolist() == [2.0] * 6
+    with pytest.raises(DenseTensorError):
+        t.update_contiguous_values_f32([1.0])
+    with pytest.raises(DenseTensorError):
+        t.contiguous_values_qint8()
+    with pytest.raises(DenseTensorError):
+        t.dispatch_values()                                    # f64 only
+    for ctor, dt in ((DenseTensor.from_contiguous_values_f16, DType.F16), (DenseTensor.from_contiguous_values_bf16, DType.BF16)):
+        assert ctor([1.5, 2.5], [2]).meta.dtype is dt
+    q = DenseTensor.from_contiguous_values_quint8([1, 2, 3, 4], [4], 0.5, 2)
+    assert q.meta.dtype is DType.QUInt8 and q.contiguous_values_quint8().tolist() == [1, 2, 3, 4]
+    assert DenseTensor.from_contiguous_values_qint8([-1, 2], [2], 0.25, 0).dequantized_values_as_f64() == [-0.25, 0.5]
+    qc = DenseTensor.from_contiguous_values_qint8_per_channel([1, 2, 3, 4], [2, 2], [0.5, 1.0], [0, 0], 0)
+    assert qc.dequantized_values_as_f64() == [0.5, 1.0, 3.0, 4.0]
+    assert DenseTensor.from_contiguous_values_quint8_per_channel([1, 2, 3, 4], [2, 2], [1.0, 2.0], [1, 0], 1) \
+        .dequantized_values_as_f64() == [0.0, 4.0, 2.0, 8.0]
+
+    m = TensorMeta.from_shape([2, 2], DType.F64, Device.Cpu)
+    assert DenseTensor.from_storage_f64_inline4(m, [1, 2, 3, 4]).dispatch_values().tolist() == [1, 2, 3, 4]
+    with pytest.raises(DenseTensorError):
+        DenseTensor.from_storage_f64_inline4(m, [1, 2, 3])
+    for ctor in (DenseTensor.from_storage_f32, DenseTensor.from_storage_f16, DenseTensor.from_storage_bf16,
+                 DenseTensor.from_storage_qint8, DenseTensor.from_storage_quint8):
+        with pytest.raises(DenseTensorError):
+            ctor(m, [1, 2, 3, 4])                              # the meta says f64
+    assert DenseTensor.from_storage_f64(m, [1, 2, 3, 4]).contiguous_values() == [1, 2, 3, 4]
+    view = DenseTensor(torch.arange(12, dtype=torch.float64).reshape(3, 4)[:, 1:3])
+    assert view.dispatch_values().tolist() == list(range(1, 11))      # offset .. last element, strides not applied
+
+
+def test_tape_value_level_entry_points():
+    import torch
+    from frankentorch_b200.autograd.tape import AutogradError, TensorGradientShapeMismatch, TensorRequiresGradNonLeaf, TensorTape
+    from frankentorch_b200.core.tensor import DenseTensor
+
+    tape = TensorTape()
+    w = tape.leaf_tensor(DenseTensor.from_contiguous_values_f32([1, 2, 3], [3]), True)
+    x = tape.leaf_f32([4, 5, 6], [3])
+    assert tape.values(w) == [1, 2, 3] and tape.values_f32(x).dtype == torch.float32
+    with pytest.raises(AutogradError):
+        tape.leaf_f32([1, 2], [3])
+    tape.set_tensor_requires_grad(x, True)
+    assert tape.nodes[x].requires_grad
+    h = tape.to_bf16(w)
+    assert tape.value(h).dtype == torch.bfloat16 and tape.to_bf16(h) == h and tape.to_f16(h) != h
+    with pytest.raises(TensorRequiresGradNonLeaf):
+        tape.set_tensor_requires_grad(h, False)
+    with pytest.raises(AutogradError):
+        tape.to_dtype(w, torch.int32)
+    y = tape.record("mul", [h, x], tape.value(h).float() * tape.value(x),
+                    lambda g, targets: [g * tape.value(x).to(g.dtype), g * tape.value(h).to(g.dtype)], "product")
+    s = tape.record("sum", [y], tape.value(y).sum(), lambda g, targets: [g.expand(3)], "sum")
+    rep = tape.backward(s)
+    assert rep.gradient(w).tolist() == [4, 5, 6] and not rep.is_sparse_gradient(w)
+    assert tape.tensor_accumulated_gradient_values(w) == [4, 5, 6] and tape.tensor_accumulated_gradient_len(w) == 3
+
+    # an SGD step through the no-copy form, then the gradient slot is cleared but stays allocated
+    v0 = tape.version(w)
+    assert tape.update_tensor_values_with_accumulated_gradient(w, lambda g, p: p.sub_(0.5 * g.to(p.dtype)))
+    assert tape.values(w) == [-1.0, -0.5, 0.0] and tape.version(w) == v0 + 1
+    tape.zero_tensor_accumulated_gradient(w)
+    assert tape.tensor_accumulated_gradient_values(w) == [0, 0, 0]
+    fresh = tape.leaf_f32([1.0], [1], True)
+    assert not tape.update_tensor_values_with_accumulated_gradient(fresh, lambda g, p: p.zero_())
+    tape.zero_tensor_accumulated_gradient(fresh)
+    assert tape.tensor_accumulated_gradient_values(fresh) is None
+
+    tape.set_tensor_accumulated_gradient(w, [1, 1, 1])
+    with pytest.raises(TensorGradientShapeMismatch):
+        tape.set_tensor_accumulated_gradient(w, [1, 1])
+    tape.update_tensor_values(w, [7, 8, 9])
+    tape.update_tensor_values_f32(w, [1, 1, 1])
+    tape.update_tensor_values_with(w, lambda p: p.mul_(3))
+    assert tape.values(w) == [3, 3, 3] and tape.version(w) == v0 + 4
+    with pytest.raises(AutogradError):
+        tape.update_tensor_values(w, [1])
+    d = tape.leaf_f64([1.0, 2.0], [2], True)
+    with pytest.raises(AutogradError):
+        tape.update_tensor_values_f32(d, [1, 2])
+
+    tape.detach_tensor_in_place(w)
+    assert not tape.nodes[w].requires_grad and tape.tensor_accumulated_gradient(w) is None
+    tape.set_grad_enabled(False)
+    assert not tape.nodes[tape.leaf_tensor(torch.ones(2), True)].requires_grad
+
+
+def test_session_custom_functions_over_live_inputs():
+    import torch
+    from frankentorch_b200.autograd.tape import AutogradError, BorrowedInputVersionMismatch
+    from frankentorch_b200.core.dtype import DType
+    from frankentorch_b200.session import FrankenTorchSession
+
+    s = FrankenTorchSession(mode="strict")
+    x = s.tensor_variable([1.0, 2.0, 3.0], [3], requires_grad=True)
+
+    def fwd(ctx, ts):
+        return ts[0] ** 2
+
+    out = s.tensor_apply_function_f64_borrowed_inputs([x], fwd, lambda ctx, g, ts: [2.0 * ts[0] * g])
+    loss = s.tensor_sum(out)
+    assert s.tensor_backward(loss).gradient(x).tolist() == [2.0, 4.0, 6.0]
+
+    # a mutated input is caught at backward
+    out = s.tensor_apply_function_f64_borrowed_inputs([x], fwd, lambda ctx, g, ts: [2.0 * ts[0] * g])
+    loss = s.tensor_sum(out)
+    s.tensor_update_values(x, [0.0, 0.0, 0.0])
+    with pytest.raises(BorrowedInputVersionMismatch):
+        s.tensor_backward(loss)
+    s.tensor_update_values(x, [1.0, 2.0, 3.0])
+
+    def fwd_saving(ctx, ts):
+        ctx.save_for_backward(ts[0].cos())
+        return ts[0].sin()
+
+    out = s.tensor_apply_function_f64_borrowed_forward([x], fwd_saving, lambda ctx, g: [ctx.saved_tensors[0] * g])
+    g = s.tensor_backward(s.tensor_sum(out)).gradient(x)
+    assert torch.allclose(g, torch.tensor([1.0, 2.0, 3.0], dtype=torch.float64).cos())
+
+    cached = torch.tensor(14.0, dtype=torch.float64)           # sum of squares, computed by the producer
+    out = s.tensor_apply_function_f64_saved_forward([x], lambda ctx: cached, lambda ctx, g: [2.0 * s.tensor(x) * g])
+    assert s.tensor_values(out) == [14.0]
+    assert s.tensor_backward(out).gradient(x).tolist() == [2.0, 4.0, 6.0]
+
+    with pytest.raises(AutogradError):                          # f32 entry point, f64 input
+        s.tensor_apply_function_f32_output_borrowed_inputs([x], fwd, lambda ctx, g, ts: [g])
+    xf = s.tensor_leaf_f32([1.0, 2.0], [2], True)
+    out = s.tensor_apply_function_f32_output_borrowed_inputs([xf], lambda ctx, ts: ts[0] * 3.0,
+                                                             lambda ctx, g, ts: [3.0 * g])
+    assert s.tensor(out).dtype == torch.float32
+    assert s.tensor_backward(s.tensor_sum(out)).gradient(xf).tolist() == [3.0, 3.0]
+    with pytest.raises(AutogradError):                          # the forward must give the promised dtype
+        s.tensor_apply_function_f32_output_borrowed_inputs([xf], lambda ctx, ts: ts[0].double(), lambda ctx, g, ts: [g])
+
+    # twice differentiable: d/dx sum(x^3) = 3x^2, d/dx of that summed = 6x
+    def bwd_cg(sess, ctx, gid, ids):
+        sq = sess.tensor_mul(ids[0], ids[0])
+        return [sess.tensor_mul(sess.tensor_mul_scalar(sq, 3.0), gid)]
+
+    out = s.tensor_apply_function_with_create_graph_borrowed_inputs([x], lambda ctx, ts: ts[0] ** 3, bwd_cg)
+    (g1,) = s.tensor_autograd_grad(s.tensor_sum(out), [x], create_graph=True)
+    assert s.tensor_values(g1) == [3.0, 12.0, 27.0]
+    (g2,) = s.tensor_autograd_grad(s.tensor_sum(g1), [x])
+    assert g2.tolist() == [6.0, 12.0, 18.0]
+
+    # constant inputs: the result is a plain leaf
+    c = s.tensor_variable([1.0], [1])
+    k = s.tensor_apply_function_f64_borrowed_inputs([c], fwd, lambda ctx, g, ts: [g])
+    assert s.tensor_is_leaf(k) and not s.tensor_requires_grad(k)
+
+    h = s.tensor_to_bf16(x)
+    assert s.tensor(h).dtype == torch.bfloat16 and s.tensor(s.tensor_to_f16(x)).dtype == torch.float16
+    s.tensor_set_requires_grad(c, True)
+    assert s.tensor_requires_grad(c)
+    assert s.tensor_leaf_tensor(torch.ones(2, dtype=torch.float64), False) >= 0

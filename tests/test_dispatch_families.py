@@ -210,3 +210,74 @@ def test_tensor_storage_variants_and_accessors():
         TensorStorage(DType.I64, torch.zeros(2, dtype=torch.int64))
     with pytest.raises(ValueError):
         TensorStorage(DType.F32, torch.zeros(2, dtype=torch.float64))
+
+
+# ----------------------------------------------------------------------------- scalar entry points
+def test_scalar_dispatch_entry_points_resolve_keys_and_version_the_result():
+    import math
+    from frankentorch_b200.core.storage import ScalarTensor
+    from frankentorch_b200.dispatch import scalar as S
+    from frankentorch_b200.dispatch.keys import DispatchKey, DispatchKeyError, DispatchKeySet
+    from frankentorch_b200.dispatch.schema import OpSchemaError, SchemaRegistry, SchemaRegistryError, parse_schema_or_name
+    from frankentorch_b200.runtime.ledger import ExecutionMode
+
+    x, y = ScalarTensor(-2.5), ScalarTensor(4.0)
+    out = S.dispatch_scalar_unary(F.UnaryOp.Abs, ExecutionMode.Strict, x, requires_grad=True)
+    assert out.tensor.value == 2.5 and out.tensor.version == x.version + 1 and out.tensor.id != x.id
+    assert out.decision.kernel == "autograd_cpu::abs_scalar" and out.decision.selected_key is DispatchKey.AutogradCPU
+    assert S.dispatch_scalar_unary("sqrt", ExecutionMode.Strict, x).tensor.value != S.dispatch_scalar_unary("sqrt", ExecutionMode.Strict, x).tensor.value   # NaN
+    assert S.dispatch_scalar_unary("log", ExecutionMode.Strict, ScalarTensor(0.0)).tensor.value == -math.inf
+    assert S.dispatch_scalar_unary("exp", ExecutionMode.Strict, ScalarTensor(1e4)).tensor.value == math.inf
+    # every unary member has a scalar kernel that agrees with torch in f64
+    for op in F.UnaryOp:
+        for v in (-1.7, 0.3, 2.2):
+            got = S.dispatch_scalar_unary(op, ExecutionMode.Strict, ScalarTensor(v)).tensor.value
+            fn = {"isnan": torch.isnan, "isinf": torch.isinf, "isfinite": torch.isfinite}.get(op.value) or getattr(torch, op.value, None) \
+                or getattr(torch.nn.functional, op.value)
+            want = float(fn(torch.tensor(v, dtype=torch.float64)))
+            assert (got != got and want != want) or abs(got - want) <= 1e-12 * max(1.0, abs(want)), (op, v, got, want)
+
+    cmp = S.dispatch_scalar_comparison(F.ComparisonOp.Lt, ExecutionMode.Strict, x, y)
+    assert cmp.tensor.value == 1.0 and cmp.decision.kernel == "cpu::lt_scalar"
+    nan = ScalarTensor(math.nan)
+    assert S.dispatch_scalar_comparison("eq", ExecutionMode.Strict, nan, nan).tensor.value == 0.0
+    assert S.dispatch_scalar_comparison("ne", ExecutionMode.Strict, nan, nan).tensor.value == 1.0
+
+    assert S.dispatch_scalar_pow(ExecutionMode.Strict, y, 0.5).tensor.value == 2.0
+    assert math.isnan(S.dispatch_scalar_pow(ExecutionMode.Strict, x, 0.5).tensor.value)
+    assert S.dispatch_scalar_clamp(ExecutionMode.Strict, x, -1.0, 1.0).tensor.value == -1.0
+    assert math.isnan(S.dispatch_scalar_clamp(ExecutionMode.Strict, nan, -1.0, 1.0).tensor.value)
+
+    ks = S.dispatch_keyset_for_tensors(x, y, True)
+    assert ks == S.dispatch_keyset_for_tensor_meta(x.meta, y.meta, True) and ks.has(DispatchKey.AutogradCPU)
+    assert S.dispatch_keyset_for_single_tensor(x, False) == S.dispatch_keyset_for_single_tensor_meta(x.meta, False)
+    assert ks.highest_priority_type_id() is DispatchKey.AutogradCPU
+    assert ks.highest_priority_backend_type_id() is DispatchKey.CPU
+    with pytest.raises(DispatchKeyError):
+        S.highest_priority_type_id(DispatchKeySet.empty())
+    with pytest.raises(DispatchKeyError):
+        S.highest_priority_backend_type_id(DispatchKeySet.from_keys([DispatchKey.BackendSelect]))
+
+    b = S.dispatch_scalar_binary_with_keyset(F.BinaryOp.Div, ExecutionMode.Strict, y, ScalarTensor(0.0), ks)
+    assert b.tensor.value == math.inf and b.decision.kernel == "autograd_cpu::div_scalar"
+    with pytest.raises(DispatchKeyError):
+        S.dispatch_scalar_binary_with_keyset(F.BinaryOp.MatMul, ExecutionMode.Strict, x, y, ks)
+    with pytest.raises(DispatchKeyError):      # composite-only set: strict refuses, hardened falls back
+        S.dispatch_scalar_binary_with_keyset("add", ExecutionMode.Strict, x, y,
+                                             DispatchKeySet.from_keys([DispatchKey.CompositeExplicitAutograd, DispatchKey.CPU]))
+    h = S.dispatch_scalar_binary_with_keyset("add", ExecutionMode.Hardened, x, y,
+                                             DispatchKeySet.from_keys([DispatchKey.CompositeExplicitAutograd, DispatchKey.CPU]))
+    assert h.tensor.value == 1.5 and h.decision.fallback_used
+    assert S.dispatch_scalar_binary_tensors("max", ExecutionMode.Strict, x, y).tensor.value == 4.0
+
+    assert S.schema_dispatch_key_from_tag("AutogradCPU") is DispatchKey.AutogradCPU
+    with pytest.raises(OpSchemaError):
+        S.schema_dispatch_key_from_tag("XLA")
+    with pytest.raises(OpSchemaError):
+        S.schema_dispatch_keyset_from_tags(["AutogradCPU"])          # autograd without its backend
+    reg = SchemaRegistry()
+    name = reg.register(parse_schema_or_name("aten::mul.Tensor"), S.schema_dispatch_keyset_from_tags(["CPU", "AutogradCPU"]))
+    r = S.dispatch_scalar_binary_registered(reg, name, ExecutionMode.Strict, x, y)
+    assert r.tensor.value == -10.0 and r.decision.op == "mul"
+    with pytest.raises(SchemaRegistryError):
+        S.dispatch_scalar_binary_registered(reg, "aten::nope", ExecutionMode.Strict, x, y)
