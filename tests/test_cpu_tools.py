@@ -282,3 +282,21 @@ def test_measurement_host_provenance(tmp_path, monkeypatch):
     with H.announce_measurement("lane_c", is_live=lambda pid: False)[0] as s3:
         assert os.path.exists(s3.path) and not os.path.exists(tmp_path / "slots" / "999999.slot")
     assert not os.path.exists(s3.path)
+
+
+def test_fused_session_reports_unavailable_without_a_device_and_checks_shapes_first():
+    import pytest
+    import torch
+    from frankentorch_b200.ops import fused_session as fsn
+    w = fsn.GpuWeight.upload(torch.randn(4, 6), device="cpu")
+    assert (w.rows, w.cols) == (4, 6) and tuple(w.data.shape) == (6, 4) and w.data.dtype == torch.bfloat16
+    with pytest.raises(fsn.FusedKernelError):
+        fsn.GpuWeight.upload(torch.randn(4), device="cpu")
+    with pytest.raises(fsn.FusedKernelError):            # shapes are checked before the device is touched
+        fsn.sgemm([1.0] * 5, [1.0] * 6, 2, 3, 2)
+    if not torch.cuda.is_available():
+        assert not fsn.is_available()
+        with pytest.raises(fsn.FusedUnavailable):
+            fsn.sgemm([1.0] * 6, [1.0] * 6, 2, 3, 2)
+        with pytest.raises(fsn.FusedUnavailable):
+            fsn.FusedSession()

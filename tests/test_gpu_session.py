@@ -279,3 +279,36 @@ def test_gpt_from_nn_modules_on_a_cuda_session_follows_the_fused_model(cuda_devi
     assert all("kernel=ftk::" in ln and "fallback_path=false" in ln for ln in hot), [ln for ln in hot if "ftk::" not in ln][:3]
     assert all(("kernel=ftk::" in ln) or ("kernel=layout::" in ln) for ln in lines)
     assert K.launch_count() - n0 >= len(hot)           # at least one launcher call of this package per hot operator
+
+
+@pytest.mark.gpu
+def test_fused_session_operators_match_fp32_references():
+    import math
+    from frankentorch_b200.ops.fused_session import FusedSession, sgemm
+    torch.manual_seed(0)
+    fs = FusedSession("cuda:0")
+    S, D, F, H = 256, 512, 1024, 8
+    x, w, b = torch.randn(S, D), torch.randn(D, F) * 0.05, torch.randn(F) * 0.1
+    xd, bd = fs.upload(x), fs.upload(b)
+    xr, wr, br = xd.float().cpu(), w.bfloat16().float(), bd.float().cpu()
+    y1 = fs.download(fs.matmul_bias(xd, fs.upload(w), bd))
+    y2 = fs.download(fs.matmul_bias_w16(xd, fs.weight(w), bd))
+    ref = xr @ wr + br
+    assert torch.allclose(y1, ref, atol=0.05, rtol=0.02) and torch.equal(y1, y2)
+    y3 = fs.download(fs.matmul_bias_w16(xd, fs.weight(w), bd, gelu=True))
+    assert torch.allclose(y3, torch.nn.functional.gelu(ref, approximate="tanh"), atol=0.05, rtol=0.02)
+    g, be = fs.upload(torch.rand(D) + 0.5), fs.upload(torch.randn(D) * 0.1)
+    ln = fs.download(fs.layernorm(xd, g, be))
+    assert torch.allclose(ln, torch.nn.functional.layer_norm(xr, (D,), g.float().cpu(), be.float().cpu()), atol=0.03, rtol=0.02)
+    assert torch.allclose(fs.download(fs.gelu(xd)), torch.nn.functional.gelu(xr, approximate="tanh"), atol=0.02, rtol=0.02)
+    assert torch.allclose(fs.download(fs.add(xd, xd)), 2 * xr, atol=0.02, rtol=0.01)
+    assert torch.allclose(fs.download(fs.softmax(xd)), torch.softmax(xr, -1), atol=2e-3, rtol=0.02)
+    q, k, v = (fs.upload(torch.randn(S, D)) for _ in range(3))
+    o = fs.download(fs.mha(q, k, v, H))
+    heads = lambda t: t.float().cpu().view(S, H, D // H).transpose(0, 1)     # noqa: E731
+    want = torch.softmax(heads(q) @ heads(k).transpose(1, 2) / math.sqrt(D // H), -1) @ heads(v)
+    assert torch.allclose(o, want.transpose(0, 1).reshape(S, D), atol=0.03, rtol=0.03)
+    fs.finish()
+    a, bb = torch.randn(128, 256), torch.randn(256, 128)
+    c = sgemm(a.reshape(-1).tolist(), bb, 128, 256, 128)
+    assert c.dtype == torch.float32 and torch.allclose(c, a.bfloat16().float() @ bb.bfloat16().float(), atol=0.05, rtol=0.02)
