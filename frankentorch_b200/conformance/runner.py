@@ -76,6 +76,69 @@ def structured_log(result: CaseResult, seed: int = 42, packet: str = "FT-P2C-005
     }
 
 
+def canonicalize(name: str) -> str:
+    """Scenario-id form of a case name: lower case, runs of other characters become one underscore."""
+    out, prev = [], False
+    for ch in name.lower():
+        if ch.isalnum():
+            out.append(ch)
+            prev = False
+        elif not prev:
+            out.append("_")
+            prev = True
+    return "".join(out).strip("_")
+
+
+def deterministic_seed(parts: Sequence[str]) -> int:
+    """Seed of a scenario: FNV-1a 64 over its identifying strings, so a replay draws the same numbers."""
+    return fnv1a64("\x1f".join(parts).encode())
+
+
+@dataclass
+class StructuredCaseLog:
+    """One record of the structured conformance log, built from the identifiers of a case
+    (ft-conformance/src/logging.rs:30 ``StructuredCaseLog::new``, :79 ``with_extra_fields``).  The scenario id
+    is ``suite/mode:case``, the seed is derived from the identifiers, and family-specific values ride in
+    ``extra_fields``, which flatten into the JSON record beside the fixed fields without replacing one."""
+    suite_id: str
+    fixture_id: str
+    packet_id: str
+    case_name: str
+    mode: str
+    artifact_refs: List[str]
+    replay_command: str
+    outcome: str
+    reason_code: str
+    extra_fields: Dict[str, object] = field(default_factory=dict)
+    ts_unix_ms: int = field(default_factory=lambda: int(time.time() * 1000))
+
+    def __post_init__(self):
+        self.mode = getattr(self.mode, "value", self.mode)
+        if self.mode not in ("strict", "hardened"):
+            raise ValueError(f"mode must be strict or hardened, got {self.mode!r}")
+        self.scenario_id = f"{self.suite_id}/{self.mode}:{canonicalize(self.case_name)}"
+        self.seed = deterministic_seed([self.suite_id, self.fixture_id, self.packet_id, self.scenario_id, self.mode])
+
+    def with_extra_fields(self, extra_fields: Dict[str, object]) -> "StructuredCaseLog":
+        self.extra_fields = dict(sorted(extra_fields.items()))
+        return self
+
+    def to_record(self) -> dict:
+        rec = {
+            "schema_version": LOG_SCHEMA, "ts_unix_ms": self.ts_unix_ms, "suite_id": self.suite_id,
+            "scenario_id": self.scenario_id, "fixture_id": self.fixture_id, "packet_id": self.packet_id,
+            "mode": self.mode, "seed": self.seed, "env_fingerprint": env_fingerprint(),
+            "artifact_refs": list(self.artifact_refs), "replay_command": self.replay_command,
+            "outcome": self.outcome, "reason_code": self.reason_code,
+        }
+        for k, v in self.extra_fields.items():
+            rec.setdefault(k, v)
+        return rec
+
+    def to_json_line(self) -> str:
+        return json.dumps(self.to_record(), sort_keys=True)
+
+
 def _close(got: Sequence[float], want: Sequence[float], tol: float) -> Optional[str]:
     if len(got) != len(want):
         return f"length {len(got)} != {len(want)}"

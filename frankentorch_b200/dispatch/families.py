@@ -27,7 +27,7 @@ import torch
 from ..core.dtype import DType
 from ..core.meta import Device, TensorMeta
 from ..runtime.ledger import ExecutionMode
-from .keys import DispatchDecision, DispatchError, DispatchKey, DispatchKeyError, ensure_meta_compatible
+from .keys import DispatchDecision, DispatchError, DispatchKey, DispatchKeyError, DispatchKeySet, ensure_meta_compatible
 
 
 class _SchemaEnum(enum.Enum):
@@ -455,3 +455,41 @@ for _fam in ("binary", "unary", "comparison", "reduction", "reduction_dim", "sca
              "norm", "norm_dim", "lerp", "addmm", "addmv", "sort", "topk"):
     for _suffix in ("f64", "f32", "typed"):
         globals()[f"dispatch_tensor_{_fam}_contiguous_{_suffix}"] = globals()[f"dispatch_tensor_{_fam}"]
+
+
+def dispatch_tensor_binary_contiguous_f64_with_keyset(op, mode: ExecutionMode, lhs: Operand, rhs: Operand,
+                                                      keyset: DispatchKeySet) -> TensorOutcome:
+    """Binary family under an explicit key set (ft-dispatch/src/lib.rs:1523): the set is resolved first, so an
+    empty set, a set without a backend key or, in strict mode, a composite-only set is refused with the typed
+    key error before any kernel runs.  The decision carries the resolution of the given set; whether the result
+    is recorded for autograd follows from the effective key."""
+    from dataclasses import replace
+    from .keys import resolve
+    selected, backend, effective, fallback = resolve(mode, keyset)
+    autograd = effective in (DispatchKey.AutogradCPU, DispatchKey.AutogradSM100)
+    t = _as_tensor(lhs)
+    on_device = backend is DispatchKey.SM100
+    if on_device != t.is_cuda:
+        raise DispatchKeyError("IncompatibleSet", f"backend key {backend.name} does not match operands on {t.device.type}")
+    out = dispatch_tensor_binary(op, mode, lhs, rhs, autograd)
+    d = out.decision
+    ns = {DispatchKey.AutogradCPU: "autograd_cpu", DispatchKey.CPU: "cpu", DispatchKey.AutogradSM100: "autograd_sm100",
+          DispatchKey.SM100: "sm100"}[effective]
+    kernel = d.kernel if "::" not in d.kernel or d.kernel.startswith(("ftk::", "torch::")) else ns + "::" + d.kernel.split("::", 1)[1]
+    return TensorOutcome(out.values, replace(d, kernel=kernel, selected_key=selected, backend_key=backend,
+                                             keyset_bits=keyset.bits, fallback_used=fallback or d.fallback_used))
+
+
+def _f32_only(fn, name):
+    def native(mode: ExecutionMode, input: Operand, *args, **kw):
+        if _as_tensor(input).dtype != torch.float32:
+            raise DispatchError(f"{name}: the native f32 entry point takes float32 operands, got {_as_tensor(input).dtype}")
+        return fn(mode, input, *args, **kw)
+    native.__name__ = name
+    native.__doc__ = (f"``{fn.__name__}`` for float32 operands only: no widening to f64 and back on the way "
+                      "(ft-dispatch's ``*_contiguous_f32_native`` forms).")
+    return native
+
+
+dispatch_tensor_pow_contiguous_f32_native = _f32_only(dispatch_tensor_pow, "dispatch_tensor_pow_contiguous_f32_native")
+dispatch_tensor_clamp_contiguous_f32_native = _f32_only(dispatch_tensor_clamp, "dispatch_tensor_clamp_contiguous_f32_native")

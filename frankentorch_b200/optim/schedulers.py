@@ -126,6 +126,17 @@ class CosineAnnealingWarmRestarts(LRScheduler):
             raise ValueError("T_0 must be positive and T_mult >= 1")
         self.T_0, self.T_mult, self.eta_min = T_0, T_mult, eta_min
 
+    def t_mult(self, t_mult: int) -> "CosineAnnealingWarmRestarts":
+        """Builder form (ft-optim/src/lib.rs:2802): growth factor of the cycle length, at least 1."""
+        self.T_mult = max(int(t_mult), 1)
+        return self
+
+    def with_eta_min(self, eta_min: float) -> "CosineAnnealingWarmRestarts":
+        """Builder form (ft-optim/src/lib.rs:2809): the floor of the schedule; a negative or non-finite value
+        is taken as 0."""
+        self.eta_min = float(eta_min) if math.isfinite(eta_min) and eta_min >= 0.0 else 0.0
+        return self
+
     def _lr_at(self, e):
         t_i, t_cur = self.T_0, e
         while t_cur >= t_i:
@@ -464,6 +475,11 @@ class GradScaler:
         self._good_steps = 0
         self._found_inf = False
         self._last_skipped = False
+
+    @staticmethod
+    def with_config(init_scale: float, growth_factor: float, backoff_factor: float, growth_interval: int) -> "GradScaler":
+        """Explicit parameters (ft-optim/src/lib.rs:6128); the scaler starts enabled."""
+        return GradScaler(init_scale, growth_factor, backoff_factor, growth_interval, True)
 
     def enable(self) -> None:
         self.enabled = True

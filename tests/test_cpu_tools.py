@@ -300,3 +300,43 @@ def test_fused_session_reports_unavailable_without_a_device_and_checks_shapes_fi
             fsn.sgemm([1.0] * 6, [1.0] * 6, 2, 3, 2)
         with pytest.raises(fsn.FusedUnavailable):
             fsn.FusedSession()
+
+
+def test_structured_case_log_builder_and_scheduler_builders():
+    import json
+    import math
+    import pytest
+    import torch
+    from frankentorch_b200.conformance.runner import StructuredCaseLog, canonicalize, deterministic_seed
+    from frankentorch_b200.optim.schedulers import CosineAnnealingWarmRestarts, GradScaler
+    from frankentorch_b200.runtime.ledger import ExecutionMode
+
+    assert canonicalize("Add  Broadcast/[2,3]") == "add_broadcast_2_3"
+    mk = lambda mode: StructuredCaseLog("tensor_binary", "tensor_binary.json", "FT-P2C-002", "Add Broadcast", mode,   # noqa: E731
+                                        ["artifacts/phase2c/FT-P2C-002/parity_report.json"], "python -m x", "pass", "ok")
+    a, b, h = mk(ExecutionMode.Strict), mk("strict"), mk("hardened")
+    assert a.scenario_id == "tensor_binary/strict:add_broadcast" and a.seed == b.seed != h.seed
+    assert a.seed == deterministic_seed(["tensor_binary", "tensor_binary.json", "FT-P2C-002", a.scenario_id, "strict"])
+    rec = json.loads(a.with_extra_fields({"zeta": 1, "alpha": [1, 2], "mode": "overridden"}).to_json_line())
+    assert rec["alpha"] == [1, 2] and rec["zeta"] == 1 and rec["mode"] == "strict"      # a fixed field is never replaced
+    for key in ("schema_version", "ts_unix_ms", "suite_id", "scenario_id", "fixture_id", "packet_id", "mode", "seed",
+                "env_fingerprint", "artifact_refs", "replay_command", "outcome", "reason_code"):
+        assert key in rec
+    with pytest.raises(ValueError):
+        mk("fast")
+
+    class _Opt:
+        def get_lr(self):
+            return 1.0
+
+    sched = CosineAnnealingWarmRestarts(_Opt(), 2).t_mult(0).with_eta_min(-1.0)
+    assert sched.T_mult == 1 and sched.eta_min == 0.0
+    sched.t_mult(2).with_eta_min(0.1)
+    ref_opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=sched.base_lr)
+    ref = torch.optim.lr_scheduler.CosineAnnealingWarmRestarts(ref_opt, 2, 2, 0.1)
+    for e in range(9):
+        assert math.isclose(sched._lr_at(e), ref_opt.param_groups[0]["lr"], rel_tol=1e-12, abs_tol=1e-15), e
+        ref_opt.step()
+        ref.step()
+    g = GradScaler.with_config(1024.0, 3.0, 0.25, 7)
+    assert (g.scale, g.growth, g.backoff, g.interval, g.enabled) == (1024.0, 3.0, 0.25, 7, True)

@@ -281,3 +281,33 @@ def test_scalar_dispatch_entry_points_resolve_keys_and_version_the_result():
     assert r.tensor.value == -10.0 and r.decision.op == "mul"
     with pytest.raises(SchemaRegistryError):
         S.dispatch_scalar_binary_registered(reg, "aten::nope", ExecutionMode.Strict, x, y)
+
+
+def test_binary_with_explicit_keyset_and_native_f32_entry_points():
+    from frankentorch_b200.dispatch.keys import DispatchKey, DispatchKeyError, DispatchKeySet
+    from frankentorch_b200.runtime.ledger import ExecutionMode
+    a = torch.tensor([1.0, 2.0, 3.0], dtype=torch.float64)
+    b = torch.tensor([4.0, 5.0, 6.0], dtype=torch.float64)
+    ks = DispatchKeySet.from_keys([DispatchKey.BackendSelect, DispatchKey.CPU, DispatchKey.AutogradCPU])
+    out = F.dispatch_tensor_binary_contiguous_f64_with_keyset(F.BinaryOp.Mul, ExecutionMode.Strict, a, b, ks)
+    assert out.values.tolist() == [4.0, 10.0, 18.0]
+    assert out.decision.selected_key is DispatchKey.AutogradCPU and out.decision.keyset_bits == ks.bits
+    assert out.decision.kernel.startswith("autograd_cpu::mul_tensor_contiguous")
+    plain = DispatchKeySet.from_keys([DispatchKey.CPU])
+    d = F.dispatch_tensor_binary_contiguous_f64_with_keyset("add", ExecutionMode.Strict, a, b, plain).decision
+    assert d.selected_key is DispatchKey.CPU and d.kernel.startswith("cpu::add_tensor_contiguous") and not d.fallback_used
+    comp = DispatchKeySet.from_keys([DispatchKey.CompositeExplicitAutograd, DispatchKey.CPU])
+    with pytest.raises(DispatchKeyError):
+        F.dispatch_tensor_binary_contiguous_f64_with_keyset("add", ExecutionMode.Strict, a, b, comp)
+    h = F.dispatch_tensor_binary_contiguous_f64_with_keyset("add", ExecutionMode.Hardened, a, b, comp)
+    assert h.decision.fallback_used and h.values.tolist() == [5.0, 7.0, 9.0]
+    with pytest.raises(DispatchKeyError):
+        F.dispatch_tensor_binary_contiguous_f64_with_keyset("add", ExecutionMode.Strict, a, b, DispatchKeySet.empty())
+    with pytest.raises(DispatchKeyError):       # a device key set over host operands
+        F.dispatch_tensor_binary_contiguous_f64_with_keyset("add", ExecutionMode.Strict, a, b,
+                                                            DispatchKeySet.from_keys([DispatchKey.SM100]))
+    x = torch.tensor([-2.0, 0.5, 3.0])
+    assert F.dispatch_tensor_pow_contiguous_f32_native(ExecutionMode.Strict, x, 2.0).values.tolist() == [4.0, 0.25, 9.0]
+    assert F.dispatch_tensor_clamp_contiguous_f32_native(ExecutionMode.Strict, x, -1.0, 1.0).values.tolist() == [-1.0, 0.5, 1.0]
+    with pytest.raises(F.DispatchError):
+        F.dispatch_tensor_pow_contiguous_f32_native(ExecutionMode.Strict, a, 2.0)
